@@ -1,0 +1,155 @@
+"""In-tree build of the native code.
+
+Two artefacts, both placed next to this file so that they travel with the source tree:
+
+* `_C.so`        - the PyTorch extension: every CUDA kernel of `csrc/cuda` (compiled by nvcc
+                   for sm_100a only) plus `csrc/cuda/bindings.cpp`.
+* `libnanochat_core.so` - the host runtime of `csrc/host` (formats, tokenizer, BPE trainer, data
+                   loader, parquet reader, C ABI); plain C++20, no CUDA, no torch.
+
+`python -m nanochat_cpp_b200.build` builds what is stale. Objects are cached under `_build/`
+keyed by a hash of the source, the headers beside it and the flags.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import glob
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from typing import List
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC_CUDA = os.path.join(HERE, "csrc", "cuda")
+CSRC_HOST = os.path.join(HERE, "csrc", "host")
+BUILD_DIR = os.path.join(HERE, "_build")
+EXT_PATH = os.path.join(HERE, "_C.so")
+CORE_PATH = os.path.join(HERE, "libnanochat_core.so")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+CXX_FLAGS = ["-O2", "-fPIC", "-std=c++17", "-Wall", "-Wno-unused-function"]
+HOST_FLAGS = ["-O2", "-fPIC", "-std=c++20", "-Wall", "-Wextra", "-pthread"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _hash(paths: List[str], extra: str) -> str:
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        with open(p, "rb") as f:
+            h.update(p.encode())
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def _run(cmd: List[str], log: str) -> None:
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    with open(log, "w") as f:
+        f.write(" ".join(cmd) + "\n" + r.stdout)
+    if r.returncode != 0:
+        raise RuntimeError(f"build step failed: {' '.join(cmd)}\n{r.stdout[-6000:]}")
+
+
+def _compile_many(jobs) -> List[str]:
+    objs = []
+    todo = []
+    for src, obj, cmd in jobs:
+        objs.append(obj)
+        if not os.path.exists(obj):
+            todo.append((src, obj, cmd))
+    if todo:
+        with cf.ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
+            futs = [ex.submit(_run, cmd, obj + ".log") for _, obj, cmd in todo]
+            for f in futs:
+                f.result()
+    return objs
+
+
+def build_extension(verbose: bool = False) -> str:
+    """Compile every CUDA source for sm_100a and link the PyTorch extension."""
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    headers = glob.glob(os.path.join(CSRC_CUDA, "*.h")) + glob.glob(os.path.join(CSRC_CUDA, "*.cuh"))
+    cu_sources = sorted(glob.glob(os.path.join(CSRC_CUDA, "*.cu")))
+    cpp_sources = sorted(glob.glob(os.path.join(CSRC_CUDA, "*.cpp")))
+    nvcc = _nvcc()
+    cuda_home = os.path.dirname(os.path.dirname(nvcc))
+    jobs = []
+    for src in cu_sources:
+        tag = _hash([src] + headers, " ".join(NVCC_FLAGS))
+        obj = os.path.join(BUILD_DIR, os.path.basename(src) + "." + tag + ".o")
+        jobs.append((src, obj, [nvcc] + NVCC_FLAGS + ["-I", CSRC_CUDA, "-c", src, "-o", obj]))
+    inc = []
+    for p in ce.include_paths("cuda") if hasattr(ce, "include_paths") else []:
+        inc += ["-I", p]
+    inc += ["-I", os.path.join(cuda_home, "include"), "-I", sysconfig.get_paths()["include"], "-I", CSRC_CUDA]
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI) if hasattr(torch._C, "_GLIBCXX_USE_CXX11_ABI") else 1
+    defs = ["-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={abi}"]
+    for src in cpp_sources:
+        tag = _hash([src] + headers, " ".join(CXX_FLAGS) + torch.__version__)
+        obj = os.path.join(BUILD_DIR, os.path.basename(src) + "." + tag + ".o")
+        jobs.append((src, obj, ["g++"] + CXX_FLAGS + defs + inc + ["-c", src, "-o", obj]))
+    objs = _compile_many(jobs)
+    stamp = os.path.join(BUILD_DIR, "ext.stamp")
+    key = _hash(objs, "link")
+    if os.path.exists(EXT_PATH) and os.path.exists(stamp) and open(stamp).read() == key:
+        return EXT_PATH
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-shared", "-o", EXT_PATH] + objs + [
+        "-L", torch_lib, "-L", os.path.join(cuda_home, "lib64"), "-lc10", "-lc10_cuda", "-ltorch_cpu",
+        "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart", f"-Wl,-rpath,{torch_lib}",
+        f"-Wl,-rpath,{os.path.join(cuda_home, 'lib64')}"]
+    _run(cmd, os.path.join(BUILD_DIR, "link_ext.log"))
+    with open(stamp, "w") as f:
+        f.write(key)
+    if verbose:
+        print("built", EXT_PATH)
+    return EXT_PATH
+
+
+def build_core(verbose: bool = False) -> str:
+    """Compile the host runtime (no CUDA, no torch)."""
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    sources = sorted(glob.glob(os.path.join(CSRC_HOST, "*.cc")))
+    if not sources:
+        return ""
+    headers = glob.glob(os.path.join(CSRC_HOST, "*.h")) + glob.glob(
+        os.path.join(os.path.dirname(HERE), "include", "nanochat", "*.h"))
+    inc = ["-I", CSRC_HOST, "-I", os.path.join(os.path.dirname(HERE), "include")]
+    jobs = []
+    for src in sources:
+        tag = _hash([src] + headers, " ".join(HOST_FLAGS))
+        obj = os.path.join(BUILD_DIR, "host_" + os.path.basename(src) + "." + tag + ".o")
+        jobs.append((src, obj, ["g++"] + HOST_FLAGS + inc + ["-c", src, "-o", obj]))
+    objs = _compile_many(jobs)
+    stamp = os.path.join(BUILD_DIR, "core.stamp")
+    key = _hash(objs, "link-core")
+    if os.path.exists(CORE_PATH) and os.path.exists(stamp) and open(stamp).read() == key:
+        return CORE_PATH
+    _run(["g++", "-shared", "-pthread", "-o", CORE_PATH] + objs, os.path.join(BUILD_DIR, "link_core.log"))
+    with open(stamp, "w") as f:
+        f.write(key)
+    if verbose:
+        print("built", CORE_PATH)
+    return CORE_PATH
+
+
+def build_all(verbose: bool = False) -> None:
+    build_core(verbose)
+    build_extension(verbose)
+
+
+if __name__ == "__main__":
+    build_all(verbose=True)
+    sys.exit(0)
