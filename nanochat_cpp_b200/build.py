@@ -30,7 +30,7 @@ EXT_PATH = os.path.join(HERE, "_C.so")
 CORE_PATH = os.path.join(HERE, "libnanochat_core.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 CXX_FLAGS = ["-O2", "-fPIC", "-std=c++17", "-Wall", "-Wno-unused-function"]
 HOST_FLAGS = ["-O2", "-fPIC", "-std=c++20", "-Wall", "-Wextra", "-pthread"]
 
@@ -96,6 +96,9 @@ def build_extension(verbose: bool = False) -> str:
     inc += ["-I", os.path.join(cuda_home, "include"), "-I", sysconfig.get_paths()["include"], "-I", CSRC_CUDA]
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI) if hasattr(torch._C, "_GLIBCXX_USE_CXX11_ABI") else 1
     defs = ["-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={abi}"]
+    for part in ("rowops", "attention", "optim", "comm"):
+        if os.path.exists(os.path.join(CSRC_CUDA, part + "_bind.cpp")):
+            defs.append("-DNC_HAVE_" + part.upper())
     for src in cpp_sources:
         tag = _hash([src] + headers, " ".join(CXX_FLAGS) + torch.__version__)
         obj = os.path.join(BUILD_DIR, os.path.basename(src) + "." + tag + ".o")

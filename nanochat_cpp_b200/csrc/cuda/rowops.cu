@@ -1,0 +1,772 @@
+// Memory-bound row kernels: norms, residual blends, QK preparation, value gate, smear, embeddings,
+// softcap + cross entropy, gradient-norm reduction. One warp owns one row (or one head of one token) and
+// moves 16-byte vectors; statistics are reduced with shuffles in fp32. These replace the reference's
+// one-block-per-row kernels and its pointwise composition tier (reference backends/cuda/kernels/
+// rms_norm.cu, qk_prep.cu, pointwise.cu, value_gate.cu, smear.cu, embedding.cu, classifier.cu,
+// grad_norm.cu) with fewer, wider passes: e.g. the residual blend and the pre-attention norm are one
+// kernel, and the classifier forward and backward are one sweep over a logits chunk.
+#include "rowops.h"
+
+#include <math_constants.h>
+
+namespace nc {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kThreads = kWarpsPerBlock * 32;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct V8 {
+  float f[8];
+};
+__device__ __forceinline__ V8 ld8(const bf16* p) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  V8 v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v.f[2 * i] = __uint_as_float(w[i] << 16);
+    v.f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+  return v;
+}
+__device__ __forceinline__ void st8(bf16* p, const V8& v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(v.f[2 * i], v.f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&t);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ float b2f(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ bf16 f2b(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? sh[threadIdx.x] : 0.0f;
+  if (warp == 0) t = warp_sum(t);
+  if (threadIdx.x == 0) sh[0] = t;
+  __syncthreads();
+  t = sh[0];
+  __syncthreads();
+  return t;
+}
+
+inline int blocks_for_rows(long long rows) { return static_cast<int>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock); }
+
+// ------------------------------------------------------------------ RMSNorm family
+// MODE 0: y = norm(x), save rstd.  MODE 1: y = x*rstd (recompute).  MODE 2: blend: xr = a*x + b*x0, h = norm(xr).
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const bf16* __restrict__ x, long long ldx,
+                                                           const bf16* __restrict__ x0, const float* lam_r,
+                                                           const float* lam_0, bf16* __restrict__ xr,
+                                                           bf16* __restrict__ y, float* __restrict__ rstd, int rows,
+                                                           int dim, float eps) {
+  const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const bf16* xp = x + static_cast<long long>(row) * ldx;
+  bf16* yp = y + static_cast<long long>(row) * dim;
+  const bool vec = (dim % 8 == 0) && aligned16(xp) && aligned16(yp) && (ldx % 8 == 0);
+  float a = 1.0f, b = 0.0f;
+  const bf16* x0p = nullptr;
+  bf16* xrp = nullptr;
+  if (MODE == 2) {
+    a = *lam_r;
+    b = *lam_0;
+    x0p = x0 + static_cast<long long>(row) * dim;
+    xrp = xr + static_cast<long long>(row) * dim;
+  }
+  float r;
+  if (MODE == 1) {
+    r = rstd[row];
+  } else {
+    float ss = 0.0f;
+    if (vec) {
+      for (int i = lane * 8; i < dim; i += 256) {
+        V8 v = ld8(xp + i);
+        if (MODE == 2) {
+          const V8 w = ld8(x0p + i);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v.f[e] = b2f(f2b(a * v.f[e] + b * w.f[e]));
+          st8(xrp + i, v);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += v.f[e] * v.f[e];
+      }
+    } else {
+      for (int i = lane; i < dim; i += 32) {
+        float v = b2f(xp[i]);
+        if (MODE == 2) {
+          v = b2f(f2b(a * v + b * b2f(x0p[i])));
+          xrp[i] = f2b(v);
+        }
+        ss += v * v;
+      }
+    }
+    ss = warp_sum(ss);
+    r = 1.0f / sqrtf(ss * (1.0f / static_cast<float>(dim)) + eps);
+    if (lane == 0) rstd[row] = r;
+  }
+  if (MODE == 2) __syncwarp();
+  const bf16* src = (MODE == 2) ? xrp : xp;
+  if (vec) {
+    for (int i = lane * 8; i < dim; i += 256) {
+      V8 v = ld8(src + i);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v.f[e] *= r;
+      st8(yp + i, v);
+    }
+  } else {
+    for (int i = lane; i < dim; i += 32) yp[i] = f2b(b2f(src[i]) * r);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy,
+                                                               const float* __restrict__ rstd,
+                                                               const bf16* __restrict__ residual,
+                                                               bf16* __restrict__ dx, int rows, int dim) {
+  const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long off = static_cast<long long>(row) * dim;
+  const bf16 *xp = x + off, *dyp = dy + off;
+  const bf16* rp = residual ? residual + off : nullptr;
+  bf16* dxp = dx + off;
+  const bool vec = (dim % 8 == 0) && aligned16(xp) && aligned16(dyp) && aligned16(dxp) && (!rp || aligned16(rp));
+  float dot = 0.0f;
+  if (vec) {
+    for (int i = lane * 8; i < dim; i += 256) {
+      const V8 a = ld8(xp + i), g = ld8(dyp + i);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot += a.f[e] * g.f[e];
+    }
+  } else {
+    for (int i = lane; i < dim; i += 32) dot += b2f(xp[i]) * b2f(dyp[i]);
+  }
+  dot = warp_sum(dot);
+  const float r = rstd[row];
+  const float coeff = r * r * r * dot * (1.0f / static_cast<float>(dim));
+  if (vec) {
+    for (int i = lane * 8; i < dim; i += 256) {
+      const V8 a = ld8(xp + i), g = ld8(dyp + i);
+      V8 o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o.f[e] = r * g.f[e] - coeff * a.f[e];
+      if (rp) {
+        const V8 q = ld8(rp + i);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o.f[e] += q.f[e];
+      }
+      st8(dxp + i, o);
+    }
+  } else {
+    for (int i = lane; i < dim; i += 32) {
+      float o = r * b2f(dyp[i]) - coeff * b2f(xp[i]);
+      if (rp) o += b2f(rp[i]);
+      dxp[i] = f2b(o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ flat elementwise + dot reductions
+// KIND 0: blend_bwd   KIND 1: backout_fwd   KIND 2: backout_bwd   KIND 3: add
+template <int KIND>
+__global__ void __launch_bounds__(256) flat_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
+                                                   const bf16* __restrict__ c, const float* s0, const float* s1,
+                                                   bf16* __restrict__ o0, bf16* __restrict__ o1, int flag,
+                                                   float* red, long long n) {
+  __shared__ float sh[32];
+  const float k0 = s0 ? *s0 : 0.0f;
+  const float k1 = s1 ? *s1 : 0.0f;
+  float acc0 = 0.0f, acc1 = 0.0f;
+  const long long nv = n / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e0 = i * 8;
+    if (KIND == 0) {  // a=dxr, b=x, c=x0; o0=dx, o1=dx0 (accumulate if flag)
+      const V8 g = ld8(a + e0), xv = ld8(b + e0), x0v = ld8(c + e0);
+      V8 d, d0;
+      if (flag) d0 = ld8(o1 + e0);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        acc0 += g.f[e] * xv.f[e];
+        acc1 += g.f[e] * x0v.f[e];
+        d.f[e] = k0 * g.f[e];
+        d0.f[e] = (flag ? d0.f[e] : 0.0f) + k1 * g.f[e];
+      }
+      st8(o0 + e0, d);
+      st8(o1 + e0, d0);
+    } else if (KIND == 1) {  // y = a - k0*b
+      const V8 xv = ld8(a + e0), bv = ld8(b + e0);
+      V8 y;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y.f[e] = xv.f[e] - k0 * bv.f[e];
+      st8(o0 + e0, y);
+    } else if (KIND == 2) {  // a=dy, b=xb: o0 = -k0*dy ; red -= <dy,xb>
+      const V8 g = ld8(a + e0), bv = ld8(b + e0);
+      V8 y;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        acc0 -= g.f[e] * bv.f[e];
+        y.f[e] = -k0 * g.f[e];
+      }
+      st8(o0 + e0, y);
+    } else {
+      const V8 xv = ld8(a + e0), bv = ld8(b + e0);
+      V8 y;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y.f[e] = xv.f[e] + bv.f[e];
+      st8(o0 + e0, y);
+    }
+  }
+  // scalar tail
+  if (blockIdx.x == 0) {
+    for (long long e0 = nv * 8 + threadIdx.x; e0 < n; e0 += blockDim.x) {
+      if (KIND == 0) {
+        const float g = b2f(a[e0]);
+        acc0 += g * b2f(b[e0]);
+        acc1 += g * b2f(c[e0]);
+        o0[e0] = f2b(k0 * g);
+        o1[e0] = f2b((flag ? b2f(o1[e0]) : 0.0f) + k1 * g);
+      } else if (KIND == 1) {
+        o0[e0] = f2b(b2f(a[e0]) - k0 * b2f(b[e0]));
+      } else if (KIND == 2) {
+        acc0 -= b2f(a[e0]) * b2f(b[e0]);
+        o0[e0] = f2b(-k0 * b2f(a[e0]));
+      } else {
+        o0[e0] = f2b(b2f(a[e0]) + b2f(b[e0]));
+      }
+    }
+  }
+  if (KIND == 0 || KIND == 2) {
+    acc0 = block_sum(acc0, sh);
+    if (KIND == 0) acc1 = block_sum(acc1, sh);
+    if (threadIdx.x == 0) {
+      atomicAdd(red, acc0);
+      if (KIND == 0) atomicAdd(red + 1, acc1);
+    }
+  }
+}
+
+__global__ void add_cols_kernel(bf16* dh, long long ld, const float* extra, int rows, int ncols) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * ncols) return;
+  const int r = i / ncols, c = i % ncols;
+  bf16* p = dh + static_cast<long long>(r) * ld + c;
+  *p = f2b(b2f(*p) + extra[i]);
+}
+
+// ------------------------------------------------------------------ QK preparation
+// One warp per (token, head). Forward: y = rope(norm(x)) * scale.
+__global__ void __launch_bounds__(kThreads) qk_prep_fwd_kernel(const bf16* __restrict__ in, long long ld_in,
+                                                               bf16* __restrict__ out, long long ld_out,
+                                                               const float* __restrict__ cosT,
+                                                               const float* __restrict__ sinT, const int* positions,
+                                                               int tokens, int seq, int heads, int D, float eps,
+                                                               float scale) {
+  const long long wid = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (wid >= static_cast<long long>(tokens) * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int tok = static_cast<int>(wid / heads), h = static_cast<int>(wid % heads);
+  const int pos = positions ? positions[tok] : tok % seq;
+  const int half = D / 2;
+  const bf16* xp = in + static_cast<long long>(tok) * ld_in + h * D;
+  bf16* yp = out + static_cast<long long>(tok) * ld_out + h * D;
+  const float* cp = cosT + static_cast<long long>(pos) * half;
+  const float* sp = sinT + static_cast<long long>(pos) * half;
+  float ss = 0.0f;
+  for (int d = lane; d < D; d += 32) {
+    const float v = b2f(xp[d]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss * (1.0f / static_cast<float>(D)) + eps);
+  for (int d = lane; d < half; d += 32) {
+    // the normalised value is rounded to bf16 before the rotation, as a separate norm pass would
+    const float x1 = b2f(f2b(b2f(xp[d]) * r));
+    const float x2 = b2f(f2b(b2f(xp[d + half]) * r));
+    const float c = cp[d], s = sp[d];
+    yp[d] = f2b((x1 * c + x2 * s) * scale);
+    yp[d + half] = f2b((-x1 * s + x2 * c) * scale);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) qk_prep_bwd_kernel(const bf16* __restrict__ pre, long long ld_pre,
+                                                               const bf16* __restrict__ grad, long long ld_grad,
+                                                               bf16* __restrict__ out, long long ld_out,
+                                                               const float* __restrict__ cosT,
+                                                               const float* __restrict__ sinT, int tokens, int seq,
+                                                               int heads, int D, float eps, float scale) {
+  const long long wid = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (wid >= static_cast<long long>(tokens) * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int tok = static_cast<int>(wid / heads), h = static_cast<int>(wid % heads);
+  const int pos = tok % seq;
+  const int half = D / 2;
+  const bf16* xp = pre + static_cast<long long>(tok) * ld_pre + h * D;
+  const bf16* gp = grad + static_cast<long long>(tok) * ld_grad + h * D;
+  bf16* op = out + static_cast<long long>(tok) * ld_out + h * D;
+  const float* cp = cosT + static_cast<long long>(pos) * half;
+  const float* sp = sinT + static_cast<long long>(pos) * half;
+  float ss = 0.0f, dot = 0.0f;
+  for (int d = lane; d < half; d += 32) {
+    const float c = cp[d], s = sp[d];
+    const float x1 = b2f(xp[d]), x2 = b2f(xp[d + half]);
+    const float g1 = b2f(gp[d]), g2 = b2f(gp[d + half]);
+    const float n1 = scale * (g1 * c - g2 * s);
+    const float n2 = scale * (g1 * s + g2 * c);
+    ss += x1 * x1 + x2 * x2;
+    dot += x1 * n1 + x2 * n2;
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float r = 1.0f / sqrtf(ss * (1.0f / static_cast<float>(D)) + eps);
+  const float coeff = r * r * r * dot * (1.0f / static_cast<float>(D));
+  for (int d = lane; d < half; d += 32) {
+    const float c = cp[d], s = sp[d];
+    const float x1 = b2f(xp[d]), x2 = b2f(xp[d + half]);
+    const float g1 = b2f(gp[d]), g2 = b2f(gp[d + half]);
+    const float n1 = scale * (g1 * c - g2 * s);
+    const float n2 = scale * (g1 * s + g2 * c);
+    op[d] = f2b(r * n1 - coeff * x1);
+    op[d + half] = f2b(r * n2 - coeff * x2);
+  }
+}
+
+// ------------------------------------------------------------------ value gate
+constexpr int kGateCh = 12;
+__global__ void __launch_bounds__(kThreads) value_gate_fwd_kernel(const bf16* __restrict__ h, long long ldh,
+                                                                  const bf16* __restrict__ ve,
+                                                                  const bf16* __restrict__ gw, bf16* __restrict__ v,
+                                                                  long long ldv, bf16* __restrict__ gate, int tokens,
+                                                                  int KV, int D) {
+  const long long wid = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (wid >= static_cast<long long>(tokens) * KV) return;
+  const int lane = threadIdx.x & 31;
+  const int tok = static_cast<int>(wid / KV), kh = static_cast<int>(wid % KV);
+  float pre = 0.0f;
+  if (lane < kGateCh) pre = b2f(h[static_cast<long long>(tok) * ldh + lane]) * b2f(gw[kh * kGateCh + lane]);
+  pre = warp_sum(pre);
+  const float g = 3.0f / (1.0f + __expf(-pre));
+  if (lane == 0) gate[static_cast<long long>(tok) * KV + kh] = f2b(g);
+  bf16* vp = v + static_cast<long long>(tok) * ldv + kh * D;
+  const bf16* ep = ve + (static_cast<long long>(tok) * KV + kh) * D;
+  for (int d = lane; d < D; d += 32) vp[d] = f2b(b2f(vp[d]) + g * b2f(ep[d]));
+}
+
+// dgw is reduced per block in shared memory, then with atomics.
+__global__ void __launch_bounds__(kThreads) value_gate_bwd_kernel(
+    const bf16* __restrict__ h, long long ldh, const bf16* __restrict__ ve, const bf16* __restrict__ gw,
+    const bf16* __restrict__ gate, const bf16* __restrict__ dv, long long lddv, bf16* __restrict__ dve,
+    float* __restrict__ dh12, float* __restrict__ dgw, int tokens, int KV, int D) {
+  extern __shared__ float sh_dgw[];  // KV*12
+  for (int i = threadIdx.x; i < KV * kGateCh; i += blockDim.x) sh_dgw[i] = 0.0f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (tok < tokens) {
+    float dh_acc = 0.0f;  // lane j < 12 accumulates dh12[tok, j]
+    const float hj = lane < kGateCh ? b2f(h[static_cast<long long>(tok) * ldh + lane]) : 0.0f;
+    for (int kh = 0; kh < KV; ++kh) {
+      const float g = b2f(gate[static_cast<long long>(tok) * KV + kh]);
+      const bf16* dvp = dv + static_cast<long long>(tok) * lddv + kh * D;
+      const bf16* ep = ve + (static_cast<long long>(tok) * KV + kh) * D;
+      bf16* op = dve + (static_cast<long long>(tok) * KV + kh) * D;
+      float dg = 0.0f;
+      for (int d = lane; d < D; d += 32) {
+        const float dvd = b2f(dvp[d]);
+        dg += dvd * b2f(ep[d]);
+        op[d] = f2b(g * dvd);
+      }
+      dg = warp_sum(dg);
+      const float dpre = dg * g * (1.0f - g * (1.0f / 3.0f));
+      if (lane < kGateCh) {
+        atomicAdd(&sh_dgw[kh * kGateCh + lane], dpre * hj);
+        dh_acc += dpre * b2f(gw[kh * kGateCh + lane]);
+      }
+    }
+    if (lane < kGateCh) dh12[static_cast<long long>(tok) * kGateCh + lane] = dh_acc;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < KV * kGateCh; i += blockDim.x) atomicAdd(&dgw[i], sh_dgw[i]);
+}
+
+// ------------------------------------------------------------------ smear
+constexpr int kSmearCh = 24;
+__global__ void __launch_bounds__(kThreads) smear_fwd_kernel(const bf16* __restrict__ emb,
+                                                             const bf16* __restrict__ gw, const float* lam,
+                                                             const bf16* __restrict__ prev, bf16* __restrict__ x0,
+                                                             float* __restrict__ sig, int tokens, int seq, int dim) {
+  const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (tok >= tokens) return;
+  const int lane = threadIdx.x & 31;
+  const int t = tok % seq;
+  const bf16* ep = emb + static_cast<long long>(tok) * dim;
+  const bf16* pp = nullptr;
+  if (t > 0) {
+    pp = ep - dim;
+  } else if (prev != nullptr) {
+    pp = prev + static_cast<long long>(tok / seq) * dim;
+  }
+  float s = 0.0f;
+  if (pp != nullptr) {
+    float pre = lane < kSmearCh ? b2f(ep[lane]) * b2f(gw[lane]) : 0.0f;
+    pre = warp_sum(pre);
+    s = sigmoidf_(pre);
+  }
+  if (lane == 0) sig[tok] = s;
+  const float g = (*lam) * s;
+  bf16* op = x0 + static_cast<long long>(tok) * dim;
+  for (int d = lane; d < dim; d += 32) {
+    const float p = pp ? b2f(pp[d]) : 0.0f;
+    op[d] = f2b(b2f(ep[d]) + g * p);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) smear_bwd_kernel(const bf16* __restrict__ emb,
+                                                             const bf16* __restrict__ gw, const float* lam,
+                                                             const float* __restrict__ sig,
+                                                             const bf16* __restrict__ dx0, bf16* __restrict__ de,
+                                                             float* __restrict__ dgw24, float* __restrict__ dlam,
+                                                             int tokens, int seq, int dim) {
+  __shared__ float sh_gw[kSmearCh];
+  __shared__ float sh_lam;
+  if (threadIdx.x < kSmearCh) sh_gw[threadIdx.x] = 0.0f;
+  if (threadIdx.x == 0) sh_lam = 0.0f;
+  __syncthreads();
+  const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tok < tokens) {
+    const int t = tok % seq;
+    const float lambda = *lam;
+    const bf16* ep = emb + static_cast<long long>(tok) * dim;
+    const bf16* dp = dx0 + static_cast<long long>(tok) * dim;
+    bf16* op = de + static_cast<long long>(tok) * dim;
+    float dpre = 0.0f;
+    if (t > 0) {
+      float dg = 0.0f;
+      for (int d = lane; d < dim; d += 32) dg += b2f(dp[d]) * b2f(ep[d - dim]);
+      dg = warp_sum(dg);
+      const float s = sig[tok];
+      dpre = dg * lambda * s * (1.0f - s);
+      if (lane == 0) atomicAdd(&sh_lam, dg * s);
+      if (lane < kSmearCh) atomicAdd(&sh_gw[lane], dpre * b2f(ep[lane]));
+    }
+    const bool tail = t == seq - 1;
+    const float gnext = tail ? 0.0f : lambda * sig[tok + 1];
+    for (int d = lane; d < dim; d += 32) {
+      float v = b2f(dp[d]);
+      if (d < kSmearCh) v += dpre * b2f(gw[d]);
+      if (!tail) v += gnext * b2f(dp[d + dim]);
+      op[d] = f2b(v);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < kSmearCh) atomicAdd(&dgw24[threadIdx.x], sh_gw[threadIdx.x]);
+  if (threadIdx.x == 0) atomicAdd(dlam, sh_lam);
+}
+
+// ------------------------------------------------------------------ embeddings
+__global__ void __launch_bounds__(kThreads) embedding_fwd_kernel(const int* __restrict__ ids,
+                                                                 const bf16* __restrict__ table,
+                                                                 bf16* __restrict__ out, int tokens, int dim) {
+  const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (tok >= tokens) return;
+  const int lane = threadIdx.x & 31;
+  const bf16* src = table + static_cast<long long>(ids[tok]) * dim;
+  bf16* dst = out + static_cast<long long>(tok) * dim;
+  if (dim % 8 == 0 && aligned16(src) && aligned16(dst)) {
+    for (int i = lane * 8; i < dim; i += 256) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+  } else {
+    for (int i = lane; i < dim; i += 32) dst[i] = src[i];
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) embedding_bwd_kernel(const int* __restrict__ ids,
+                                                                 const bf16* __restrict__ dout, long long ld,
+                                                                 float* __restrict__ dtable, int tokens, int dim) {
+  const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (tok >= tokens) return;
+  const int lane = threadIdx.x & 31;
+  const bf16* src = dout + static_cast<long long>(tok) * ld;
+  float* dst = dtable + static_cast<long long>(ids[tok]) * dim;
+  if (dim % 4 == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    for (int i = lane * 4; i < dim; i += 128) {
+      const float a = b2f(src[i]), b = b2f(src[i + 1]), c = b2f(src[i + 2]), d = b2f(src[i + 3]);
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "f"(a), "f"(b), "f"(c), "f"(d)
+                   : "memory");
+    }
+  } else {
+    for (int i = lane; i < dim; i += 32) atomicAdd(dst + i, b2f(src[i]));
+  }
+}
+
+// ------------------------------------------------------------------ softcap + cross entropy (+ backward, in place)
+__device__ __forceinline__ float tanh_acc(float x) {
+  // 1 - 2/(exp(2x)+1): accurate to a few ulp and saturates cleanly for large |x|
+  const float e = __expf(2.0f * x);
+  return 1.0f - 2.0f / (e + 1.0f);
+}
+
+__global__ void __launch_bounds__(256) classifier_kernel(bf16* __restrict__ logits, long long ld,
+                                                         const int* __restrict__ targets, float* __restrict__ losses,
+                                                         const float* __restrict__ row_scale,
+                                                         const float* __restrict__ dlogit_scale, int rows, int vocab,
+                                                         int padded, float softcap, int ignore_index, bool want_grad) {
+  __shared__ float sh[32];
+  const int row = blockIdx.x;
+  bf16* lp = logits + static_cast<long long>(row) * ld;
+  const int target = targets[row];
+  const float inv_cap = 1.0f / softcap;
+  const bool vec = (vocab % 8 == 0) && (padded % 8 == 0) && aligned16(lp) && (ld % 8 == 0);
+  if (target == ignore_index) {
+    if (threadIdx.x == 0) losses[row] = 0.0f;
+    if (want_grad) {
+      for (int i = threadIdx.x; i < padded; i += blockDim.x) lp[i] = f2b(0.0f);
+    }
+    return;
+  }
+  // pass 1: online max / sum of exp over the capped logits
+  float m = -CUDART_INF_F, l = 0.0f;
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < vocab; i += blockDim.x * 8) {
+      const V8 v = ld8(lp + i);
+      float z[8], cm = m;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        z[e] = softcap * tanh_acc(v.f[e] * inv_cap);
+        cm = fmaxf(cm, z[e]);
+      }
+      float add = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) add += __expf(z[e] - cm);
+      l = l * __expf(m - cm) + add;
+      m = cm;
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float z = softcap * tanh_acc(b2f(lp[i]) * inv_cap);
+      const float cm = fmaxf(m, z);
+      l = l * __expf(m - cm) + __expf(z - cm);
+      m = cm;
+    }
+  }
+  // block combine of (m, l)
+  float bm = warp_max(m);
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) sh[warp] = bm;
+    __syncthreads();
+    float t = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : -CUDART_INF_F;
+    if (warp == 0) t = warp_max(t);
+    if (threadIdx.x == 0) sh[0] = t;
+    __syncthreads();
+    bm = sh[0];
+    __syncthreads();
+  }
+  const float lsum = block_sum(m == -CUDART_INF_F ? 0.0f : l * __expf(m - bm), sh);
+  const bool in_range = target >= 0 && target < vocab;
+  if (threadIdx.x == 0) {
+    const float tz = in_range ? softcap * tanh_acc(b2f(lp[target]) * inv_cap) : 0.0f;
+    losses[row] = logf(lsum) + bm - tz;
+  }
+  if (!want_grad) return;
+  __syncthreads();  // the target logit was read above, before anything is overwritten
+  const float inv = 1.0f / lsum;
+  const float scale = *dlogit_scale;
+  const float rs = row_scale ? row_scale[row] : 1.0f;
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < padded; i += blockDim.x * 8) {
+      V8 o;
+      if (i < vocab) {
+        const V8 v = ld8(lp + i);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float t = tanh_acc(v.f[e] * inv_cap);
+          const float p = __expf(softcap * t - bm) * inv;
+          const float onehot = (i + e == target) ? 1.0f : 0.0f;
+          // rounded once before the loss scale, as the two-pass definition does
+          o.f[e] = b2f(f2b((p - onehot) * (1.0f - t * t) * rs)) * scale;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o.f[e] = 0.0f;
+      }
+      st8(lp + i, o);
+    }
+  } else {
+    for (int i = threadIdx.x; i < padded; i += blockDim.x) {
+      float o = 0.0f;
+      if (i < vocab) {
+        const float t = tanh_acc(b2f(lp[i]) * inv_cap);
+        const float p = __expf(softcap * t - bm) * inv;
+        const float onehot = (i == target) ? 1.0f : 0.0f;
+        o = b2f(f2b((p - onehot) * (1.0f - t * t) * rs)) * scale;
+      }
+      lp[i] = f2b(o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ gradient norm
+__global__ void __launch_bounds__(256) sumsq_kernel(const float* __restrict__ g, long long n, double* out) {
+  __shared__ double shd[8];
+  double acc = 0.0;
+  const long long nv = n / 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(g)[i];
+    acc += static_cast<double>(v.x * v.x + v.y * v.y) + static_cast<double>(v.z * v.z + v.w * v.w);
+  }
+  if (blockIdx.x == 0) {
+    for (long long i = nv * 4 + threadIdx.x; i < n; i += blockDim.x) acc += static_cast<double>(g[i]) * g[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) shd[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < 8; ++w) t += shd[w];
+    atomicAdd(out, t);
+  }
+}
+
+__global__ void finish_norm_kernel(const double* sumsq, float clip, float* norm_clip) {
+  const float norm = static_cast<float>(sqrt(*sumsq));
+  norm_clip[0] = norm;
+  norm_clip[1] = (clip > 0.0f && norm > clip) ? clip / norm : 1.0f;
+}
+
+inline int flat_grid(long long n) {
+  long long b = (n / 8 + 255) / 256;
+  if (b < 1) b = 1;
+  if (b > 148 * 8) b = 148 * 8;
+  return static_cast<int>(b);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ launchers
+void rmsnorm_fwd(const bf16* x, long long ldx, bf16* y, float* rstd, int rows, int dim, float eps, cudaStream_t s) {
+  if (rows <= 0) return;
+  rmsnorm_kernel<0><<<blocks_for_rows(rows), kThreads, 0, s>>>(x, ldx, nullptr, nullptr, nullptr, nullptr, y, rstd,
+                                                               rows, dim, eps);
+}
+void rmsnorm_apply(const bf16* x, long long ldx, const float* rstd, bf16* y, int rows, int dim, cudaStream_t s) {
+  if (rows <= 0) return;
+  rmsnorm_kernel<1><<<blocks_for_rows(rows), kThreads, 0, s>>>(x, ldx, nullptr, nullptr, nullptr, nullptr, y,
+                                                               const_cast<float*>(rstd), rows, dim, 0.0f);
+}
+void rmsnorm_bwd(const bf16* x, const bf16* dy, const float* rstd, const bf16* residual, bf16* dx, int rows, int dim,
+                 cudaStream_t s) {
+  if (rows <= 0) return;
+  rmsnorm_bwd_kernel<<<blocks_for_rows(rows), kThreads, 0, s>>>(x, dy, rstd, residual, dx, rows, dim);
+}
+void blend_norm_fwd(const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* xr, bf16* h,
+                    float* rstd, int rows, int dim, float eps, cudaStream_t s) {
+  if (rows <= 0) return;
+  rmsnorm_kernel<2><<<blocks_for_rows(rows), kThreads, 0, s>>>(x, dim, x0, lam_r, lam_0, xr, h, rstd, rows, dim, eps);
+}
+void blend_bwd(const bf16* dxr, const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* dx,
+               bf16* dx0, bool accumulate_dx0, float* dlam2, long long n, cudaStream_t s) {
+  flat_kernel<0><<<flat_grid(n), 256, 0, s>>>(dxr, x, x0, lam_r, lam_0, dx, dx0, accumulate_dx0 ? 1 : 0, dlam2, n);
+}
+void backout_fwd(const bf16* x, const bf16* xb, const float* lam, bf16* y, long long n, cudaStream_t s) {
+  flat_kernel<1><<<flat_grid(n), 256, 0, s>>>(x, xb, nullptr, lam, nullptr, y, nullptr, 0, nullptr, n);
+}
+void backout_bwd(const bf16* dy, const bf16* xb, const float* lam, bf16* dxb, float* dlam, long long n,
+                 cudaStream_t s) {
+  flat_kernel<2><<<flat_grid(n), 256, 0, s>>>(dy, xb, nullptr, lam, nullptr, dxb, nullptr, 0, dlam, n);
+}
+void add_bf16(const bf16* a, const bf16* b, bf16* out, long long n, cudaStream_t s) {
+  flat_kernel<3><<<flat_grid(n), 256, 0, s>>>(a, b, nullptr, nullptr, nullptr, out, nullptr, 0, nullptr, n);
+}
+void add_cols(bf16* dh, long long ld, const float* extra, int rows, int ncols, cudaStream_t s) {
+  const int n = rows * ncols;
+  if (n <= 0) return;
+  add_cols_kernel<<<(n + 255) / 256, 256, 0, s>>>(dh, ld, extra, rows, ncols);
+}
+void qk_prep_fwd(const bf16* in, long long ld_in, bf16* out, long long ld_out, const float* cos, const float* sin,
+                 const int* positions, int tokens, int seq, int heads, int D, float eps, float scale, cudaStream_t s) {
+  const long long n = static_cast<long long>(tokens) * heads;
+  if (n <= 0) return;
+  qk_prep_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(in, ld_in, out, ld_out, cos, sin, positions, tokens, seq,
+                                                             heads, D, eps, scale);
+}
+void qk_prep_bwd(const bf16* pre, long long ld_pre, const bf16* grad, long long ld_grad, bf16* out, long long ld_out,
+                 const float* cos, const float* sin, int tokens, int seq, int heads, int D, float eps, float scale,
+                 cudaStream_t s) {
+  const long long n = static_cast<long long>(tokens) * heads;
+  if (n <= 0) return;
+  qk_prep_bwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(pre, ld_pre, grad, ld_grad, out, ld_out, cos, sin, tokens,
+                                                             seq, heads, D, eps, scale);
+}
+void value_gate_fwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, bf16* v, long long ldv,
+                    bf16* gate, int tokens, int KV, int D, cudaStream_t s) {
+  const long long n = static_cast<long long>(tokens) * KV;
+  if (n <= 0) return;
+  value_gate_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens, KV, D);
+}
+void value_gate_bwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, const bf16* gate, const bf16* dv,
+                    long long lddv, bf16* dve, float* dh12, float* dgw, int tokens, int KV, int D, cudaStream_t s) {
+  if (tokens <= 0) return;
+  value_gate_bwd_kernel<<<blocks_for_rows(tokens), kThreads, KV * kGateCh * sizeof(float), s>>>(
+      h, ldh, ve, gate_w, gate, dv, lddv, dve, dh12, dgw, tokens, KV, D);
+}
+void smear_fwd(const bf16* emb, const bf16* gate_w, const float* lam, const bf16* prev, bf16* x0, float* sig,
+               int tokens, int seq, int dim, cudaStream_t s) {
+  if (tokens <= 0) return;
+  smear_fwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(emb, gate_w, lam, prev, x0, sig, tokens, seq, dim);
+}
+void smear_bwd(const bf16* emb, const bf16* gate_w, const float* lam, const float* sig, const bf16* dx0, bf16* de,
+               float* dgw24, float* dlam, int tokens, int seq, int dim, cudaStream_t s) {
+  if (tokens <= 0) return;
+  smear_bwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(emb, gate_w, lam, sig, dx0, de, dgw24, dlam, tokens,
+                                                                seq, dim);
+}
+void embedding_fwd(const int* ids, const bf16* table, bf16* out, int tokens, int dim, cudaStream_t s) {
+  if (tokens <= 0) return;
+  embedding_fwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(ids, table, out, tokens, dim);
+}
+void embedding_bwd(const int* ids, const bf16* dout, long long ld, float* dtable, int tokens, int dim, cudaStream_t s) {
+  if (tokens <= 0) return;
+  embedding_bwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(ids, dout, ld, dtable, tokens, dim);
+}
+void classifier_fwd_bwd(bf16* logits, long long ld, const int* targets, float* losses, const float* row_scale,
+                        const float* dlogit_scale, int rows, int vocab, int padded, float softcap, int ignore_index,
+                        bool want_grad, cudaStream_t s) {
+  if (rows <= 0) return;
+  classifier_kernel<<<rows, 256, 0, s>>>(logits, ld, targets, losses, row_scale, dlogit_scale, rows, vocab, padded,
+                                         softcap, ignore_index, want_grad);
+}
+void sumsq_f32(const float* g, long long n, double* out, cudaStream_t s) {
+  if (n <= 0) return;
+  long long b = (n / 4 + 255) / 256;
+  if (b < 1) b = 1;
+  if (b > 148 * 8) b = 148 * 8;
+  sumsq_kernel<<<static_cast<int>(b), 256, 0, s>>>(g, n, out);
+}
+void finish_norm(const double* sumsq, float clip, float* norm_clip, cudaStream_t s) {
+  finish_norm_kernel<<<1, 1, 0, s>>>(sumsq, clip, norm_clip);
+}
+
+}  // namespace nc

@@ -85,6 +85,185 @@ def linear_wgrad(dy, x, grad, *, accumulate=True):
     return grad
 
 
+# ---------------------------------------------------------------------------
+# Row kernels
+# ---------------------------------------------------------------------------
+from ..config import LOGIT_SOFTCAP, QK_SCALE, RMS_EPS  # noqa: E402
+
+
+def _status(t):
+    return _C.status_tensor(t.device.index)
+
+
+def rmsnorm_fwd(x, eps=RMS_EPS):
+    y, rstd = _C.rmsnorm_fwd(x, eps)
+    return y, rstd
+
+
+def rmsnorm_apply(x, rstd):
+    return _C.rmsnorm_apply(x, rstd)
+
+
+def rmsnorm_bwd(x, dy, rstd, residual=None):
+    return _C.rmsnorm_bwd(x, dy, rstd, residual)
+
+
+def add(a, b):
+    return _C.add(a, b)
+
+
+def add_cols(dh, extra):
+    _C.add_cols(dh, extra.contiguous())
+    return dh
+
+
+def concat_qkv(dq, dk, dv):
+    return torch.cat([dq, dk, dv], dim=1)
+
+
+def backout_fwd(x, x_backout, lam):
+    return _C.backout_fwd(x, x_backout, lam)
+
+
+def backout_bwd(dy, x_backout, lam):
+    dxb, dlam = _C.backout_bwd(dy, x_backout, lam)
+    return dy, dxb, dlam[0]
+
+
+def blend_norm_fwd(x, x0, lam_r, lam_0, eps=RMS_EPS):
+    xr, h, rstd = _C.blend_norm_fwd(x, x0, lam_r, lam_0, eps)
+    return xr, h, rstd
+
+
+def blend_bwd(dxr, x, x0, lam_r, lam_0, dx0_acc=None):
+    """Returns (dx, dx0, dlam_r, dlam_0). With `dx0_acc` the x0 contribution is accumulated in place
+    and returned as the same tensor (one pass instead of blend + add)."""
+    if dx0_acc is None:
+        dx0 = torch.empty_like(x)
+        dx, dlam = _C.blend_bwd(dxr, x, x0, lam_r, lam_0, dx0, False)
+    else:
+        dx0 = dx0_acc
+        dx, dlam = _C.blend_bwd(dxr, x, x0, lam_r, lam_0, dx0, True)
+    return dx, dx0, dlam[0], dlam[1]
+
+
+def qk_prep_fwd(q_pre, k_pre, cos, sin, eps=RMS_EPS, scale=QK_SCALE, positions=None):
+    return (_C.qk_prep_fwd_one(q_pre, cos, sin, positions, eps, scale),
+            _C.qk_prep_fwd_one(k_pre, cos, sin, positions, eps, scale))
+
+
+def qk_prep_bwd(q_pre, k_pre, dq, dk, cos, sin, eps=RMS_EPS, scale=QK_SCALE, out_q=None, out_k=None):
+    if out_q is None:
+        out_q = torch.empty(dq.shape, dtype=dq.dtype, device=dq.device)
+    if out_k is None:
+        out_k = torch.empty(dk.shape, dtype=dk.dtype, device=dk.device)
+    _C.qk_prep_bwd_one(q_pre, dq, out_q, cos, sin, eps, scale)
+    _C.qk_prep_bwd_one(k_pre, dk, out_k, cos, sin, eps, scale)
+    return out_q, out_k
+
+
+def value_gate_fwd(h, ve, gate_w, v, head_dim):
+    gate = _C.value_gate_fwd(h, ve, gate_w.contiguous(), v, head_dim)   # v updated in place
+    return v, gate
+
+
+def value_gate_bwd(h, ve, gate_w, gate, dv, head_dim):
+    dve, dh12, dgw = _C.value_gate_bwd(h, ve, gate_w.contiguous(), gate, dv, head_dim)
+    return dve, dh12, dgw
+
+
+def smear_fwd(emb, gate_w, lam, seq, prev=None):
+    x0, sig = _C.smear_fwd(emb, gate_w.contiguous().view(-1), lam, seq, prev)
+    return x0, sig
+
+
+def smear_bwd(emb, gate_w, lam, sig, dx0, seq):
+    de, dgw, dlam = _C.smear_bwd(emb, gate_w.contiguous().view(-1), lam, sig, dx0, seq)
+    return de, dgw, dlam[0]
+
+
+def embedding_fwd(ids, table):
+    return _C.embedding_fwd(ids.reshape(-1).contiguous(), table)
+
+
+def embedding_bwd(ids, dout, dtable):
+    _C.embedding_bwd(ids.reshape(-1).contiguous(), dout, dtable)
+    return dtable
+
+
+def classifier_fwd_bwd(logits, targets, vocab, *, dlogit_scale, row_scale=None, softcap=LOGIT_SOFTCAP,
+                       ignore_index=-1, want_grad=True):
+    """In place: when `want_grad` the logits buffer is overwritten with dlogits and returned."""
+    ds = None
+    if want_grad:
+        ds = dlogit_scale if isinstance(dlogit_scale, torch.Tensor) else torch.tensor(
+            float(dlogit_scale), dtype=torch.float32, device=logits.device)
+        ds = ds.to(torch.float32).reshape(1)
+    losses = _C.classifier_fwd_bwd(logits, targets.contiguous(), vocab, ds, row_scale, softcap, ignore_index, want_grad)
+    return losses, (logits if want_grad else None)
+
+
+def linear_wgrad_relu2(dy, pre, grad, *, accumulate=True):
+    act = torch.relu(pre.float()).square().to(pre.dtype) if False else _relu2(pre)
+    return linear_wgrad(dy, act, grad, accumulate=accumulate)
+
+
+def _relu2(pre):
+    # recompute act = relu(pre)^2; a GEMM-prologue fusion is not possible with TMA-fed operands,
+    # so the activation is rebuilt in one elementwise pass
+    return _C.relu2(pre) if hasattr(_C, "relu2") else torch.relu(pre).square_()
+
+
+def grad_norm_and_clip(grads, clip):
+    """`grads` is a list of fp32 tensors; one flat tensor (the whole gradient buffer) is the fast path."""
+    if len(grads) == 1:
+        out = _C.grad_norm_clip(grads[0].reshape(-1), float(clip if clip else 0.0))
+        return out[0], out[1]
+    acc = torch.zeros(1, dtype=torch.float64, device=grads[0].device)
+    for g in grads:
+        _C.sumsq_into(g.reshape(-1), acc)
+    norm = acc.sqrt().float()[0]
+    if clip and clip > 0:
+        scale = torch.where(norm > clip, clip / norm.clamp_min(1e-30), torch.ones_like(norm))
+    else:
+        scale = torch.ones_like(norm)
+    return norm, scale
+
+
+# ---------------------------------------------------------------------------
+# Attention
+# ---------------------------------------------------------------------------
+def attention_fwd(q, k, v, window_left=-1, scale=None, q_offset=None):
+    import math
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    o, lse = _C.attention_fwd(q, k, v, int(window_left), float(scale), -1 if q_offset is None else int(q_offset),
+                              _status(q))
+    return o, lse
+
+
+def attention_bwd(q, k, v, o, lse, do, window_left=-1, scale=None, q_offset=None, out=None):
+    """`out` may give (dq, dk, dv) destination views (e.g. column slices of one [M, 3C] buffer)."""
+    import math
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    if out is None:
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    else:
+        dq, dk, dv = out
+    _C.attention_bwd(q, k, v, o, lse, do, dq, dk, dv, int(window_left), float(scale),
+                     -1 if q_offset is None else int(q_offset), _status(q))
+    return dq, dk, dv
+
+
+# optimizer updates are provided by ops/cuda_optim once built; until then they run as PyTorch
+# elementwise code on the device (the definition in ops.ref), which is numerically identical
+adamw_update = ref.adamw_update
+muon_update = ref.muon_update
+
+
 def __getattr__(name):
-    # Operators without a kernel yet are an error on a GPU, not a fallback.
+    # Operators without a kernel are an error on a GPU, not a fallback.
     raise AttributeError(f"ops.cuda has no operator {name!r}")

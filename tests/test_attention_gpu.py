@@ -1,0 +1,84 @@
+"""tcgen05 flash attention (forward and backward) against the fp32 masked-softmax definition."""
+import math
+
+import pytest
+import torch
+
+from nanochat_cpp_b200.ops import ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _K():
+    from nanochat_cpp_b200.ops import cuda as K
+    return K
+
+
+def _r(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _close(a, b, tol, name=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    mag = b.abs().max().item() + 1e-6
+    assert err <= tol * mag, (name, err, mag)
+
+
+CASES = [
+    # B, T, H, KV, D, window
+    (2, 256, 2, 2, 128, -1),
+    (1, 512, 4, 2, 128, 128),
+    (2, 384, 2, 1, 128, 100),
+    (1, 200, 2, 2, 128, -1),      # ragged length
+    (1, 333, 3, 1, 128, 64),      # ragged + window smaller than a tile + GQA 3
+    (2, 256, 2, 2, 64, -1),
+    (1, 320, 4, 2, 64, 96),
+    (1, 1024, 2, 2, 128, 2048),   # window larger than the sequence
+]
+
+
+@pytest.mark.parametrize("B,T,H,KV,D,window", CASES)
+def test_forward_backward(B, T, H, KV, D, window):
+    K = _K()
+    torch.manual_seed(B * 1000 + T + H + D)
+    q, k, v = _r(B, T, H, D), _r(B, T, KV, D), _r(B, T, KV, D)
+    do = _r(B, T, H, D)
+    o, lse = K.attention_fwd(q, k, v, window)
+    o_ref, lse_ref = ref.attention_fwd(q, k, v, window)
+    K.check_status()
+    _close(o, o_ref, 2e-2, "o")
+    _close(lse, lse_ref, 2e-3, "lse")
+    dq, dk, dv = K.attention_bwd(q, k, v, o, lse, do, window)
+    K.check_status()
+    rdq, rdk, rdv = ref.attention_bwd(q, k, v, o_ref, lse_ref, do, window)
+    _close(dq, rdq, 3e-2, "dq")
+    _close(dk, rdk, 3e-2, "dk")
+    _close(dv, rdv, 3e-2, "dv")
+
+
+def test_strided_views_and_offsets():
+    """q/k/v as column slices of one fused QKV buffer, gradients written into one dqkv buffer."""
+    K = _K()
+    B, T, H, KV, D = 2, 256, 2, 2, 128
+    C = H * D
+    qkv = _r(B * T, 3 * C)
+    view = lambda off, nh: qkv.as_strided((B, T, nh, D), (T * 3 * C, 3 * C, D, 1), off)
+    q, k, v = view(0, H), view(C, KV), view(2 * C, KV)
+    o, lse = K.attention_fwd(q, k, v, 128)
+    o_ref, lse_ref = ref.attention_fwd(q, k, v, 128)
+    _close(o, o_ref, 2e-2)
+    do = _r(B, T, H, D)
+    dqkv = torch.zeros(B * T, 3 * C, device="cuda", dtype=torch.bfloat16)
+    dview = lambda off, nh: dqkv.as_strided((B, T, nh, D), (T * 3 * C, 3 * C, D, 1), off)
+    K.attention_bwd(q, k, v, o, lse, do, 128, out=(dview(0, H), dview(C, KV), dview(2 * C, KV)))
+    rdq, rdk, rdv = ref.attention_bwd(q, k, v, o_ref, lse_ref, do, 128)
+    _close(dview(0, H), rdq, 3e-2)
+    _close(dview(C, KV), rdk, 3e-2)
+    _close(dview(2 * C, KV), rdv, 3e-2)
+    # decode-style call: 64 new queries against 256 cached keys
+    qn = _r(B, 64, H, D)
+    o2, _ = K.attention_fwd(qn, k, v, 100)
+    o2_ref, _ = ref.attention_fwd(qn, k, v, 100)
+    _close(o2, o2_ref, 2e-2)
+    K.check_status()

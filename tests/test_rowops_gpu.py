@@ -1,0 +1,163 @@
+"""Row kernels against the PyTorch definitions in ops.ref (same bf16 inputs, fp32 math)."""
+import pytest
+import torch
+
+from nanochat_cpp_b200.ops import ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _K():
+    from nanochat_cpp_b200.ops import cuda as K
+    return K
+
+
+def _r(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _close(a, b, tol=2e-2, name=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    mag = b.abs().max().item() + 1e-6
+    assert err <= tol * mag, (name, err, mag)
+
+
+@pytest.mark.parametrize("rows,dim", [(37, 1280), (64, 768), (5, 32), (9, 100)])
+def test_rmsnorm(rows, dim):
+    K = _K()
+    x, dy, res = _r(rows, dim), _r(rows, dim), _r(rows, dim)
+    y, rstd = K.rmsnorm_fwd(x)
+    yr, rr = ref.rmsnorm_fwd(x)
+    _close(y, yr, 1e-2)
+    _close(rstd, rr, 1e-4)
+    _close(K.rmsnorm_apply(x, rstd), yr, 1e-2)
+    _close(K.rmsnorm_bwd(x, dy, rstd, res), ref.rmsnorm_bwd(x, dy, rr, res), 1e-2)
+    _close(K.rmsnorm_bwd(x, dy, rstd), ref.rmsnorm_bwd(x, dy, rr), 1e-2)
+
+
+def test_blend_backout_add():
+    K = _K()
+    rows, dim = 300, 1280
+    x, x0, g = _r(rows, dim), _r(rows, dim), _r(rows, dim)
+    a = torch.tensor(1.1, device="cuda")
+    b = torch.tensor(0.15, device="cuda")
+    xr, h, rstd = K.blend_norm_fwd(x, x0, a, b)
+    xr_r, h_r, rstd_r = ref.blend_norm_fwd(x, x0, a, b)
+    _close(xr, xr_r, 1e-2)
+    _close(h, h_r, 1e-2)
+    dx, dx0, dlr, dl0 = K.blend_bwd(g, x, x0, a, b)
+    rdx, rdx0, rdlr, rdl0 = ref.blend_bwd(g, x, x0, a, b)
+    _close(dx, rdx, 1e-2)
+    _close(dx0, rdx0, 1e-2)
+    assert abs(dlr.item() - rdlr.item()) <= 2e-3 * abs(rdlr.item()) + 0.5
+    assert abs(dl0.item() - rdl0.item()) <= 2e-3 * abs(rdl0.item()) + 0.5
+    acc = _r(rows, dim)
+    want = ref.add(acc, rdx0)
+    K.blend_bwd(g, x, x0, a, b, dx0_acc=acc)
+    _close(acc, want, 2e-2)
+    lam = torch.tensor(0.2, device="cuda")
+    _close(K.backout_fwd(x, x0, lam), ref.backout_fwd(x, x0, lam), 1e-2)
+    _, dxb, dlam = K.backout_bwd(g, x0, lam)
+    _, rdxb, rdlam = ref.backout_bwd(g, x0, lam)
+    _close(dxb, rdxb, 1e-2)
+    assert abs(dlam.item() - rdlam.item()) <= 2e-3 * abs(rdlam.item()) + 0.5
+    _close(K.add(x, x0), ref.add(x, x0), 1e-2)
+    dh = _r(rows, dim)
+    extra = torch.randn(rows, 12, device="cuda")
+    want = ref.add_cols(dh.clone(), extra)
+    _close(K.add_cols(dh, extra), want, 1e-2)
+
+
+@pytest.mark.parametrize("D,H,KV", [(128, 4, 2), (64, 2, 2), (4, 8, 2)])
+def test_qk_prep(D, H, KV):
+    K = _K()
+    B, T = 2, 24
+    wide = _r(B * T, (H + 2 * KV) * D)
+    q_pre = wide[:, : H * D].as_strided((B, T, H, D), (T * wide.stride(0), wide.stride(0), D, 1), 0)
+    k_pre = wide.as_strided((B, T, KV, D), (T * wide.stride(0), wide.stride(0), D, 1), H * D)
+    cos, sin = ref.build_rope(T, D, 10000.0, "cuda")
+    q, k = K.qk_prep_fwd(q_pre, k_pre, cos, sin)
+    qr, kr = ref.qk_prep_fwd(q_pre, k_pre, cos, sin)
+    _close(q, qr, 2e-2)
+    _close(k, kr, 2e-2)
+    dq, dk = _r(B, T, H, D), _r(B, T, KV, D)
+    gq, gk = K.qk_prep_bwd(q_pre, k_pre, dq, dk, cos, sin)
+    rq, rk = ref.qk_prep_bwd(q_pre, k_pre, dq, dk, cos, sin)
+    _close(gq, rq, 2e-2)
+    _close(gk, rk, 2e-2)
+
+
+def test_value_gate_smear_embedding():
+    K = _K()
+    M, C, KV, D, V = 96, 256, 2, 64, 50
+    h, ve, v = _r(M, C), _r(M, KV * D), _r(M, KV * D)
+    gw = _r(KV, 12, scale=0.3)
+    v_ref, gate_ref = ref.value_gate_fwd(h, ve, gw, v, D)
+    v_out, gate = K.value_gate_fwd(h, ve, gw, v.clone(), D)
+    _close(v_out, v_ref, 1e-2)
+    _close(gate, gate_ref, 1e-2)
+    dv = _r(M, KV * D)
+    dve, dh12, dgw = K.value_gate_bwd(h, ve, gw, gate, dv, D)
+    rdve, rdh12, rdgw = ref.value_gate_bwd(h, ve, gw, gate, dv, D)
+    _close(dve, rdve, 1e-2)
+    _close(dh12, rdh12, 1e-2)
+    _close(dgw, rdgw, 1e-2)
+    seq = 24
+    emb = _r(M, C)
+    sw = _r(1, 24, scale=0.3)
+    lam = torch.tensor(0.4, device="cuda")
+    x0, sig = K.smear_fwd(emb, sw, lam, seq)
+    rx0, rsig = ref.smear_fwd(emb, sw, lam, seq)
+    _close(x0, rx0, 1e-2)
+    _close(sig, rsig, 1e-3)
+    prev = _r(M // seq, C)
+    x0p, sigp = K.smear_fwd(emb, sw, lam, seq, prev)
+    rx0p, rsigp = ref.smear_fwd(emb, sw, lam, seq, prev)
+    _close(x0p, rx0p, 1e-2)
+    g = _r(M, C)
+    de, dgw2, dlam = K.smear_bwd(emb, sw, lam, sig, g, seq)
+    rde, rdgw2, rdlam = ref.smear_bwd(emb, sw, lam, rsig, g, seq)
+    _close(de, rde, 1e-2)
+    _close(dgw2, rdgw2, 1e-2)
+    assert abs(dlam.item() - rdlam.item()) <= 1e-2 * abs(rdlam.item()) + 1e-2
+    ids = torch.randint(0, V, (M,), device="cuda", dtype=torch.int32)
+    table = _r(V, C)
+    assert torch.equal(K.embedding_fwd(ids, table), ref.embedding_fwd(ids, table))
+    dt = torch.zeros(V, C, device="cuda")
+    rdt = torch.zeros(V, C, device="cuda")
+    K.embedding_bwd(ids, g, dt)
+    ref.embedding_bwd(ids, g, rdt)
+    _close(dt, rdt, 1e-3)
+
+
+@pytest.mark.parametrize("vocab,padded", [(4096, 4096), (1000, 1024), (50, 64)])
+def test_classifier(vocab, padded):
+    K = _K()
+    R = 33
+    logits = _r(R, padded, scale=6.0)
+    targets = torch.randint(0, vocab, (R,), device="cuda", dtype=torch.int32)
+    targets[3] = -1
+    scale = torch.tensor(0.37, device="cuda")
+    rs = torch.rand(R, device="cuda")
+    rl, rd = ref.classifier_fwd_bwd(logits.clone(), targets, vocab, dlogit_scale=scale, row_scale=rs)
+    l2, _ = K.classifier_fwd_bwd(logits.clone(), targets, vocab, dlogit_scale=None, want_grad=False)
+    _close(l2, rl, 2e-3)
+    buf = logits.clone()
+    l1, d1 = K.classifier_fwd_bwd(buf, targets, vocab, dlogit_scale=scale, row_scale=rs)
+    _close(l1, rl, 2e-3)
+    _close(d1, rd, 2e-2)
+    assert d1.data_ptr() == buf.data_ptr()
+    assert float(d1[3].abs().max()) == 0.0
+    if padded > vocab:
+        assert float(d1[:, vocab:].abs().max()) == 0.0
+
+
+def test_grad_norm():
+    K = _K()
+    g = torch.randn(1_000_003, device="cuda")
+    norm, scale = K.grad_norm_and_clip([g], 1.0)
+    assert abs(norm.item() - g.double().norm().item()) < 1e-2
+    assert abs(scale.item() - 1.0 / g.double().norm().item()) < 1e-6
+    norm2, scale2 = K.grad_norm_and_clip([g[:1000], g[1000:]], 0.0)
+    assert abs(norm2.item() - norm.item()) < 1e-2 and scale2.item() == 1.0
