@@ -1,0 +1,30 @@
+// Host launchers of the optimizer kernels (optim.cu). fp32 state, bf16 compute copies.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace nc {
+
+// Decoupled-decay AdamW on an fp32 master span; writes the bf16 compute copy when `value` != null.
+// `grad_scale` is a device scalar (the clip scale). Arithmetic: reference backends/cpu/kernels.cc:1557-1580.
+void adamw_update(float* master, __nv_bfloat16* value, const float* grad, float* m, float* v, long long n, float lr,
+                  float beta1, float beta2, float eps, float weight_decay, int step, const float* grad_scale,
+                  cudaStream_t s);
+
+// Muon stage 1 for one matrix [rows, cols]: buf1 += (1-mu)(g*scale - buf1); x = (1-mu) g*scale + mu*buf1;
+// row_sumsq[r] = sum_c x[r,c]^2.
+void muon_nesterov(const float* grad, float* buf1, float* x, float* row_sumsq, int rows, int cols, float momentum,
+                   const float* grad_scale, cudaStream_t s);
+// x[r,:] *= row_scale[r] * all_scale[0]; out bf16 copy; also out_sumsq (optional, double) of the scaled matrix
+void muon_scale_rows(const float* x, const float* row_scale, const float* all_scale, __nv_bfloat16* out, int rows,
+                     int cols, cudaStream_t s);
+// Cautious decay + update: p -= lr*x*line_scale + (x*p >= 0 ? lr*wd*p : 0), x = xb * scale[0] * line_scale[line].
+void muon_apply(float* master, __nv_bfloat16* value, const __nv_bfloat16* xb, const float* scale0,
+                const float* line_scale, bool lines_are_rows, int rows, int cols, float lr, float weight_decay,
+                cudaStream_t s);
+// relu(x)^2 elementwise (bf16)
+void relu2_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, cudaStream_t s);
+// bf16 <- fp32 cast of a span
+void cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s);
+
+}  // namespace nc

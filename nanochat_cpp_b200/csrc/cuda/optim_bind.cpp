@@ -1,0 +1,76 @@
+// Tensor-level wrappers of the optimizer kernels.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "optim.h"
+
+namespace {
+
+using torch::Tensor;
+inline cudaStream_t cur() { return at::cuda::getCurrentCUDAStream(); }
+inline __nv_bfloat16* bptr(const Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); }
+
+void adamw_update(Tensor& master, const c10::optional<Tensor>& value, const Tensor& grad, Tensor& m, Tensor& v,
+                  double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
+                  const c10::optional<Tensor>& grad_scale) {
+  TORCH_CHECK(master.is_cuda() && master.is_contiguous() && grad.is_contiguous() && m.is_contiguous() &&
+                  v.is_contiguous(),
+              "adamw: contiguous CUDA tensors expected");
+  TORCH_CHECK(master.scalar_type() == torch::kFloat32 && grad.scalar_type() == torch::kFloat32, "adamw: fp32 state");
+  const c10::cuda::CUDAGuard g(master.device());
+  __nv_bfloat16* vp = nullptr;
+  if (value.has_value()) {
+    TORCH_CHECK(value->scalar_type() == torch::kBFloat16 && value->is_contiguous(), "adamw: bf16 compute copy");
+    vp = bptr(*value);
+  }
+  nc::adamw_update(master.data_ptr<float>(), vp, grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                   master.numel(), lr, beta1, beta2, eps, weight_decay, step,
+                   grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, cur());
+}
+
+void muon_nesterov(const Tensor& grad, Tensor& buf1, Tensor& x, Tensor& row_sumsq, double momentum,
+                   const c10::optional<Tensor>& grad_scale) {
+  const c10::cuda::CUDAGuard g(grad.device());
+  TORCH_CHECK(grad.dim() == 2 && grad.is_contiguous() && buf1.is_contiguous() && x.is_contiguous(), "muon_nesterov");
+  nc::muon_nesterov(grad.data_ptr<float>(), buf1.data_ptr<float>(), x.data_ptr<float>(), row_sumsq.data_ptr<float>(),
+                    grad.size(0), grad.size(1), momentum,
+                    grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, cur());
+}
+void muon_scale_rows(const Tensor& x, const Tensor& row_scale, const Tensor& all_scale, Tensor& out) {
+  const c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_contiguous(), "muon_scale_rows");
+  nc::muon_scale_rows(x.data_ptr<float>(), row_scale.data_ptr<float>(), all_scale.data_ptr<float>(), bptr(out),
+                      x.size(0), x.size(1), cur());
+}
+void muon_apply(Tensor& master, const c10::optional<Tensor>& value, const Tensor& xb, const Tensor& scale0,
+                const Tensor& line_scale, bool lines_are_rows, double lr, double wd) {
+  const c10::cuda::CUDAGuard g(master.device());
+  TORCH_CHECK(master.dim() == 2 && master.is_contiguous() && xb.is_contiguous(), "muon_apply");
+  nc::muon_apply(master.data_ptr<float>(), value.has_value() ? bptr(*value) : nullptr, bptr(xb),
+                 scale0.data_ptr<float>(), line_scale.data_ptr<float>(), lines_are_rows, master.size(0),
+                 master.size(1), lr, wd, cur());
+}
+Tensor relu2(const Tensor& x) {
+  const c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "relu2: contiguous bf16");
+  Tensor y = torch::empty_like(x);
+  nc::relu2_bf16(bptr(x), bptr(y), x.numel(), cur());
+  return y;
+}
+void cast_f32_bf16(const Tensor& x, Tensor& y) {
+  const c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.numel() == y.numel(), "cast");
+  nc::cast_f32_bf16(x.data_ptr<float>(), bptr(y), x.numel(), cur());
+}
+
+}  // namespace
+
+void register_optim(pybind11::module_& m) {
+  m.def("adamw_update", &adamw_update);
+  m.def("muon_nesterov", &muon_nesterov);
+  m.def("muon_scale_rows", &muon_scale_rows);
+  m.def("muon_apply", &muon_apply);
+  m.def("relu2", &relu2);
+  m.def("cast_f32_bf16", &cast_f32_bf16);
+}

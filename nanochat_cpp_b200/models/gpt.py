@@ -237,44 +237,45 @@ class GPT:
             attn2 = s["attn"].view(M, H * D)
             ops.linear_wgrad(dx_mid, attn2, self._g(i, "attn.c_proj"))
             dattn = ops.linear_dgrad(dx_mid, self._w(i, "attn.c_proj"))
-            dq, dk, dv = ops.attention_bwd(s["q"], s["k"], s["v"], s["attn"], s["lse"],
-                                           dattn.view(B, T, H, D), cfg.window_left(i))
+            qd, kd = cfg.query_dim, cfg.kv_dim
+            dqkv = torch.empty(M, qd + 2 * kd, dtype=dx_mid.dtype, device=dx_mid.device)
+            dv4 = _heads(dqkv[:, qd + kd:], B, T, KV, D)
+            dq, dk, _ = ops.attention_bwd(s["q"], s["k"], s["v"], s["attn"], s["lse"], dattn.view(B, T, H, D),
+                                          cfg.window_left(i), out=(None, None, dv4))
             del dattn
-            dq_pre, dk_pre = ops.qk_prep_bwd(_heads(s["q_pre"], B, T, H, D), _heads(s["k_pre"], B, T, KV, D),
-                                             dq, dk, cos, sin)
+            ops.qk_prep_bwd(_heads(s["q_pre"], B, T, H, D), _heads(s["k_pre"], B, T, KV, D), dq, dk, cos, sin,
+                            out_q=_heads(dqkv[:, :qd], B, T, H, D), out_k=_heads(dqkv[:, qd:qd + kd], B, T, KV, D))
+            del dq, dk
             h = ops.rmsnorm_apply(s["xr"], s["rstd1"])
-            dv2 = dv.view(M, KV * D)
+            dv2 = dqkv[:, qd + kd:]
             dh12 = None
             if cfg.has_value_embedding(i):
                 dve, dh12, dgw = ops.value_gate_bwd(h, s["ve"], self._w(i, "attn.ve_gate"), s["gate"], dv2, D)
                 self._g(i, "attn.ve_gate").add_(dgw)
                 ops.embedding_bwd(tok, dve, P.g(f"value_embeds.{i}.weight"))
                 del dve
-            dqkv = ops.concat_qkv(dq_pre.view(M, H * D), dk_pre.view(M, KV * D), dv2)
             gqkv = P.qkv_view(i, "g")
             wqkv = P.qkv_view(i)
             if gqkv is not None:
                 ops.linear_wgrad(dqkv, h, gqkv)
                 dh = ops.linear_dgrad(dqkv, wqkv)
             else:
-                qd, kd = cfg.query_dim, cfg.kv_dim
                 ops.linear_wgrad(dqkv[:, :qd], h, self._g(i, "attn.c_q"))
                 ops.linear_wgrad(dqkv[:, qd:qd + kd], h, self._g(i, "attn.c_k"))
                 ops.linear_wgrad(dqkv[:, qd + kd:], h, self._g(i, "attn.c_v"))
                 dh = ops.linear_dgrad(dqkv[:, :qd], self._w(i, "attn.c_q"))
                 dh = ops.linear_dgrad(dqkv[:, qd:qd + kd], self._w(i, "attn.c_k"), residual=dh)
                 dh = ops.linear_dgrad(dqkv[:, qd + kd:], self._w(i, "attn.c_v"), residual=dh)
-            del dqkv, dq, dk, dv, dq_pre, dk_pre
+            del dqkv, dv2, dv4
             if dh12 is not None:
                 dh = ops.add_cols(dh, dh12)
             dxr = ops.rmsnorm_bwd(s["xr"], dh, s["rstd1"], residual=dx_mid)
             del dh, dx_mid, h
-            dx, dx0_c, dlr, dl0 = ops.blend_bwd(dxr, s["x"], x0, self._lam("resid_lambdas", i),
-                                                self._lam("x0_lambdas", i))
+            dx, dx0, dlr, dl0 = ops.blend_bwd(dxr, s["x"], x0, self._lam("resid_lambdas", i),
+                                              self._lam("x0_lambdas", i), dx0_acc=dx0)
             P.g("resid_lambdas")[i] += dlr
             P.g("x0_lambdas")[i] += dl0
-            dx0 = dx0_c if dx0 is None else ops.add(dx0, dx0_c)
-            del dxr, dx0_c
+            del dxr
             save["layers"][i] = None
             if self.on_layer_grads_ready is not None:
                 self.on_layer_grads_ready(i)

@@ -247,20 +247,28 @@ def attention_bwd(q, k, v, o, lse, do, window_left=-1, scale=None, q_offset=None
     import math
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    if out is None:
+    dq, dk, dv = out if out is not None else (None, None, None)
+    if dq is None:
         dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    if dk is None:
         dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    if dv is None:
         dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-    else:
-        dq, dk, dv = out
     _C.attention_bwd(q, k, v, o, lse, do, dq, dk, dv, int(window_left), float(scale),
                      -1 if q_offset is None else int(q_offset), _status(q))
     return dq, dk, dv
 
 
-# optimizer updates are provided by ops/cuda_optim once built; until then they run as PyTorch
-# elementwise code on the device (the definition in ops.ref), which is numerically identical
-adamw_update = ref.adamw_update
+def adamw_update(master, value, grad, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0):
+    gs = grad_scale if isinstance(grad_scale, torch.Tensor) else None
+    if gs is None and grad_scale != 1.0:
+        gs = torch.tensor(float(grad_scale), dtype=torch.float32, device=master.device)
+    _C.adamw_update(master, value, grad, m, v, lr, beta1, beta2, eps, weight_decay, step,
+                    None if gs is None else gs.reshape(1))
+
+
+# small or oddly shaped matrices (the 12-channel value gates) take the PyTorch definition on the device;
+# every real matrix goes through optim.muon_cuda.muon_group_step
 muon_update = ref.muon_update
 
 

@@ -141,13 +141,18 @@ def blend_norm_fwd(x, x0, lam_r, lam_0, eps=RMS_EPS):
     return xr, h, rstd
 
 
-def blend_bwd(dxr, x, x0, lam_r, lam_0):
-    """Backward of the blend. Returns (dx, dx0_contrib, dlam_r, dlam_0)."""
+def blend_bwd(dxr, x, x0, lam_r, lam_0, dx0_acc=None):
+    """Backward of the blend. Returns (dx, dx0, dlam_r, dlam_0); with `dx0_acc` the x0 term is
+    accumulated into that tensor (in place) and it is what is returned as dx0."""
     acc = _acc(x)
     dlr = (dxr.to(acc) * x.to(acc)).sum().float()
     dl0 = (dxr.to(acc) * x0.to(acc)).sum().float()
     dx = (lam_r.float() * dxr.float()).to(x.dtype)
-    dx0 = (lam_0.float() * dxr.float()).to(x.dtype)
+    if dx0_acc is None:
+        dx0 = (lam_0.float() * dxr.float()).to(x.dtype)
+    else:
+        dx0_acc.copy_((dx0_acc.float() + lam_0.float() * dxr.float()).to(x.dtype))
+        dx0 = dx0_acc
     return dx, dx0, dlr, dl0
 
 
@@ -198,9 +203,16 @@ def _qk_prep_bwd_one(pre, grad, cos, sin, eps, scale):
     return (r * g - coeff * pre.float()).to(pre.dtype)
 
 
-def qk_prep_bwd(q_pre, k_pre, dq, dk, cos, sin, eps=RMS_EPS, scale=QK_SCALE):
-    return (_qk_prep_bwd_one(q_pre, dq, cos, sin, eps, scale),
-            _qk_prep_bwd_one(k_pre, dk, cos, sin, eps, scale))
+def qk_prep_bwd(q_pre, k_pre, dq, dk, cos, sin, eps=RMS_EPS, scale=QK_SCALE, out_q=None, out_k=None):
+    gq = _qk_prep_bwd_one(q_pre, dq, cos, sin, eps, scale)
+    gk = _qk_prep_bwd_one(k_pre, dk, cos, sin, eps, scale)
+    if out_q is not None:
+        out_q.copy_(gq)
+        gq = out_q
+    if out_k is not None:
+        out_k.copy_(gk)
+        gk = out_k
+    return gq, gk
 
 
 # --------------------------------------------------------------------------
@@ -238,7 +250,7 @@ def attention_fwd(q, k, v, window_left=-1, scale=None, q_offset=None):
     return o.permute(0, 2, 1, 3).to(q.dtype).contiguous(), lse
 
 
-def attention_bwd(q, k, v, o, lse, do, window_left=-1, scale=None, q_offset=None):
+def attention_bwd(q, k, v, o, lse, do, window_left=-1, scale=None, q_offset=None, out=None):
     B, T, H, D = q.shape
     S, KV = k.shape[1], k.shape[2]
     group = H // KV
@@ -264,9 +276,15 @@ def attention_bwd(q, k, v, o, lse, do, window_left=-1, scale=None, q_offset=None
     dk = torch.matmul(ds.transpose(-1, -2), qf)
     dk = dk.view(B, KV, group, S, D).sum(2)
     dv = dv.view(B, KV, group, S, D).sum(2)
-    return (dq.permute(0, 2, 1, 3).to(q.dtype).contiguous(),
-            dk.permute(0, 2, 1, 3).to(k.dtype).contiguous(),
-            dv.permute(0, 2, 1, 3).to(v.dtype).contiguous())
+    res = [dq.permute(0, 2, 1, 3).to(q.dtype).contiguous(),
+           dk.permute(0, 2, 1, 3).to(k.dtype).contiguous(),
+           dv.permute(0, 2, 1, 3).to(v.dtype).contiguous()]
+    if out is not None:
+        for i in range(3):
+            if out[i] is not None:
+                out[i].copy_(res[i])
+                res[i] = out[i]
+    return tuple(res)
 
 
 # --------------------------------------------------------------------------

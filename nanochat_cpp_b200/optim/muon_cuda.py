@@ -1,0 +1,98 @@
+"""Muon on the GPU: fused elementwise stages + batched tcgen05 products.
+
+Same arithmetic as `ops.ref.muon_update` (reference `backends/cpu/kernels.cc:1614-1810`) with the
+Polar Express iterate kept in bf16 between products, as the reference's bf16 CUDA build does
+(docs/model.md:402-416). Per shape group `[P, rows, cols]`:
+
+  1. `muon_nesterov`  momentum + Nesterov blend, per-row sum of squares         (1 launch / matrix)
+  2. row equilibration + Frobenius normalisation folded into one row scale      (tiny [P, rows] math)
+  3. `muon_scale_rows` applies it and writes the bf16 iterate                   (1 launch / matrix)
+  4. 5 x { A = X X^T (or X^T X), B = b A + c A A, X = a X + B X (or X B) }      (3 batched GEMMs / step,
+     residual-add epilogue, no separate axpby passes)
+  5. line sums of squares -> Muon+ rescale, NorMuon second moment and step size ([P, lines] math)
+  6. `muon_apply`  cautious decay + update of the fp32 master and bf16 copy     (1 launch / matrix)
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from ..ops.ref import POLAR_COEFFS
+
+
+def polar_express_bf16(X: torch.Tensor, ns_steps: int) -> torch.Tensor:
+    """X: [P, rows, cols] bf16, normalised. Returns the orthogonalised stack (bf16)."""
+    from ..ops import cuda as K
+    P, rows, cols = X.shape
+    tall = rows > cols
+    k = cols if tall else rows
+    A = torch.empty(P, k, k, dtype=torch.bfloat16, device=X.device)
+    B = torch.empty_like(A)
+    Y = torch.empty_like(X)
+    for it in range(min(max(ns_steps, 0), 5)):
+        ca, cb, cc = POLAR_COEFFS[it]
+        if tall:
+            K.gemm(X, X, a_mn=True, b_mn=True, out=A)                       # X^T X
+            K.gemm(A, A, epi=K.EPI_BF16_RES, r=A, alpha=cc, beta=cb, out=B)  # b A + c A A   (A symmetric)
+            K.gemm(X, B, epi=K.EPI_BF16_RES, r=X, alpha=1.0, beta=ca, out=Y)  # a X + X B     (B symmetric)
+        else:
+            K.gemm(X, X, out=A)                                              # X X^T
+            K.gemm(A, A, epi=K.EPI_BF16_RES, r=A, alpha=cc, beta=cb, out=B)
+            K.gemm(B, X, b_mn=True, epi=K.EPI_BF16_RES, r=X, alpha=1.0, beta=ca, out=Y)  # a X + B X
+        X, Y = Y, X
+    return X
+
+
+class MuonGroupState:
+    """Scratch of one shape group, allocated once."""
+
+    def __init__(self, P: int, rows: int, cols: int, device):
+        self.x32 = torch.empty(P, rows, cols, dtype=torch.float32, device=device)
+        self.X = torch.empty(P, rows, cols, dtype=torch.bfloat16, device=device)
+        self.row_ss = torch.empty(P, rows, dtype=torch.float32, device=device)
+
+
+@torch.no_grad()
+def muon_group_step(grads: List[torch.Tensor], masters: List[torch.Tensor], values: List[Optional[torch.Tensor]],
+                    buf1: List[torch.Tensor], buf2: List[torch.Tensor], scratch: MuonGroupState, *, lr: float,
+                    momentum: float, beta2: float, weight_decay: float, ns_steps: int,
+                    grad_scale: Optional[torch.Tensor]) -> None:
+    from ..ops import cuda as K
+    C = K._C
+    P = len(grads)
+    rows, cols = masters[0].shape
+    reduce_cols = rows >= cols
+    gs = None if grad_scale is None else grad_scale.reshape(1)
+    for p in range(P):
+        C.muon_nesterov(grads[p], buf1[p], scratch.x32[p], scratch.row_ss[p], momentum, gs)
+    row_ss = scratch.row_ss[:P]
+    frob = torch.sqrt(row_ss.sum(-1, keepdim=True))
+    target = frob / math.sqrt(float(rows))
+    row_norm = torch.sqrt(row_ss).clamp_min(1e-6)
+    row_scale = target / row_norm
+    frob2 = torch.sqrt((row_ss * row_scale * row_scale).sum(-1))
+    all_scale = 1.0 / (frob2 * 1.01 + 1e-6)
+    row_scale = row_scale.contiguous()
+    for p in range(P):
+        C.muon_scale_rows(scratch.x32[p], row_scale[p], all_scale[p:p + 1], scratch.X[p])
+    X = polar_express_bf16(scratch.X[:P], ns_steps)
+    red = -1 if reduce_cols else -2
+    line_len = cols if reduce_cols else rows
+    line_ss = X.float().square().sum(red)                       # [P, lines]
+    frob_post = torch.sqrt(line_ss.sum(-1, keepdim=True))
+    scale = math.sqrt(float(min(rows, cols))) / frob_post.clamp_min(1e-6)   # [P, 1]
+    v_mean = line_ss * (scale * scale) / float(line_len)
+    v_norm = torch.sqrt(v_mean.sum(-1, keepdim=True) * float(line_len))
+    b2 = torch.stack(buf2)
+    b2.add_((1.0 - beta2) * (v_mean - b2))
+    for p in range(P):
+        buf2[p].copy_(b2[p])
+    step_size = torch.rsqrt(b2.clamp_min(1e-10))
+    sum_scaled = (v_mean * float(line_len) * step_size * step_size).sum(-1, keepdim=True)
+    denom = torch.sqrt(sum_scaled).clamp_min(1e-10)
+    line_scale = (step_size * (v_norm / denom)).contiguous()
+    scale = scale.contiguous()
+    for p in range(P):
+        C.muon_apply(masters[p], values[p], X[p], scale[p], line_scale[p], reduce_cols, lr, weight_decay)

@@ -92,7 +92,8 @@ def build_groups(store: ParamStore, cfg: OptimizerConfig):
 
 class Optimizer:
     def __init__(self, store: ParamStore, config: OptimizerConfig = None, sched: SchedulerConfig = None,
-                 owned: Optional[Callable[[ParamSpec], bool]] = None):
+                 owned: Optional[Callable[[ParamSpec], bool]] = None,
+                 adamw_slices: Optional[Dict[str, tuple]] = None):
         self.store = store
         self.config = config or OptimizerConfig()
         self.scheduler = Scheduler(sched or SchedulerConfig())
@@ -100,17 +101,20 @@ class Optimizer:
         self.owned = owned or (lambda s: True)
         dev = store.device
         self.state: Dict[str, Dict[str, torch.Tensor]] = {}
+        self.adamw_slices = dict(adamw_slices or {})  # name -> (begin, end) owned by this rank
         for g in self.adamw_groups:
             for s in g.params:
                 if self.owned(s):
-                    self.state[s.name] = dict(m=torch.zeros(s.shape, dtype=torch.float32, device=dev),
-                                              v=torch.zeros(s.shape, dtype=torch.float32, device=dev))
+                    a, b = self.adamw_slices.get(s.name, (0, s.count))
+                    self.state[s.name] = dict(m=torch.zeros(max(b - a, 0), dtype=torch.float32, device=dev),
+                                              v=torch.zeros(max(b - a, 0), dtype=torch.float32, device=dev))
         for g in self.muon_groups:
             lines = g.rows if g.rows >= g.cols else g.cols
             for s in g.params:
                 if self.owned(s):
                     self.state[s.name] = dict(buf1=torch.zeros(s.shape, dtype=torch.float32, device=dev),
                                               buf2=torch.zeros(lines, dtype=torch.float32, device=dev))
+        self._muon_scratch = {}
         self.lr_multiplier_override: float = -1.0
         self.last_grad_norm: Optional[torch.Tensor] = None
         self.step_count = 0
@@ -137,8 +141,9 @@ class Optimizer:
         st = self.store
         cfg = self.config
         if clip_scale is None:
-            norm, clip_scale = ops.grad_norm_and_clip([st.g(s.name) for s in st.specs if self.owned(s)],
-                                                      cfg.clip)
+            all_owned = all(self.owned(s) for s in st.specs)
+            spans = [st.grad] if all_owned else [st.g(s.name) for s in st.specs if self.owned(s)]
+            norm, clip_scale = ops.grad_norm_and_clip(spans, cfg.clip)
             self.last_grad_norm = norm
         lrm = self.lr_multiplier_override if self.lr_multiplier_override >= 0.0 \
             else self.scheduler.lr_multiplier(step)
@@ -147,15 +152,31 @@ class Optimizer:
                 if not self.owned(s):
                     continue
                 stt = self.state[s.name]
-                ops.adamw_update(st.m(s.name), None if st.value is st.master else st.v(s.name),
-                                 st.g(s.name), stt["m"], stt["v"], lr=g.lr * lrm, beta1=g.beta1,
-                                 beta2=g.beta2, eps=g.eps, weight_decay=g.weight_decay, step=step,
+                a, b = self.adamw_slices.get(s.name, (0, s.count))
+                if b <= a:
+                    continue
+                lo, hi = s.offset + a, s.offset + b
+                ops.adamw_update(st.master[lo:hi], None if st.value is st.master else st.value[lo:hi],
+                                 st.grad[lo:hi], stt["m"].view(-1), stt["v"].view(-1), lr=g.lr * lrm,
+                                 beta1=g.beta1, beta2=g.beta2, eps=g.eps, weight_decay=g.weight_decay, step=step,
                                  grad_scale=clip_scale)
         momentum = self.scheduler.muon_momentum(step)
         wd = self.scheduler.weight_decay(step)
+        use_kernels = st.device.type == "cuda" and ops.get_mode() == "kernels" and st.value is not st.master
         for g in self.muon_groups:
             mine = [s for s in g.params if self.owned(s)]
             if not mine:
+                continue
+            if use_kernels and min(g.rows, g.cols) >= 64 and g.rows % 8 == 0 and g.cols % 8 == 0:
+                from .muon_cuda import MuonGroupState, muon_group_step
+                key = (g.rows, g.cols)
+                if key not in self._muon_scratch:
+                    self._muon_scratch[key] = MuonGroupState(len(mine), g.rows, g.cols, st.device)
+                muon_group_step([st.g(s.name) for s in mine], [st.m(s.name) for s in mine],
+                                [st.v(s.name) for s in mine], [self.state[s.name]["buf1"] for s in mine],
+                                [self.state[s.name]["buf2"] for s in mine], self._muon_scratch[key],
+                                lr=g.lr * lrm, momentum=momentum, beta2=cfg.muon_beta2, weight_decay=wd,
+                                ns_steps=cfg.muon_ns_steps, grad_scale=clip_scale)
                 continue
             grads = torch.stack([st.g(s.name) for s in mine])
             master = torch.stack([st.m(s.name) for s in mine])

@@ -1,0 +1,118 @@
+"""Data parallelism with an owner-sharded optimizer.
+
+Every parameter has one owner rank that holds its optimizer state and computes its update; the
+result equals "one rank on the global batch" (the reference's contract, `src/train_parallel_test.cc`)
+because gradients are summed over ranks after each rank scaled its backward by `1/(accum * world)`
+(`src/train.h:117-122`).
+
+* Muon matrices are owned whole (Newton-Schulz needs the full matrix), dealt round-robin inside each
+  shape group so every rank gets the same mix of shapes.
+* AdamW tensors (embeddings, LM head, scalars) are elementwise, so each is split into `world` equal
+  contiguous slices.
+
+Two transports implement the same step:
+  `nccl`   - baseline: NCCL all-reduce of the flat gradient, owner update, NCCL all-reduce of the
+             masked bf16 parameter buffer (acts as the all-gather).
+  `fused`  - the sm_100a kernels of `parallel.fused` over NVLink peer memory (reduce-scatter fused with
+             the owner's update, all-gather fused into the first consuming GEMM).
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..models.params import ParamSpec, ParamStore
+from ..optim.optimizer import build_groups, OptimizerConfig
+
+
+def assign_owners(store: ParamStore, world: int) -> Dict[str, int]:
+    """Owner rank of every Muon matrix (AdamW tensors are sliced, not owned whole: owner -1)."""
+    _, muon = build_groups(store, OptimizerConfig())
+    owners: Dict[str, int] = {}
+    k = 0
+    for g in muon:
+        for s in g.params:
+            owners[s.name] = k % world
+            k += 1
+    for s in store.specs:
+        owners.setdefault(s.name, -1)
+    return owners
+
+
+def adamw_slice(spec: ParamSpec, rank: int, world: int) -> Tuple[int, int]:
+    """[begin, end) of `rank`'s slice inside the flattened parameter (multiples of 64 elements)."""
+    n = spec.count
+    per = ((n + world - 1) // world + 63) // 64 * 64
+    a = min(n, rank * per)
+    b = min(n, a + per)
+    return a, b
+
+
+class DataParallel:
+    def __init__(self, rank: int, world_size: int, transport: str = "nccl", group=None):
+        self.rank, self.world_size = rank, world_size
+        self.transport = transport
+        self.group = group
+        self.model = None
+        self.optimizer = None
+        self.owners: Dict[str, int] = {}
+        self._last_micro = True
+
+    # ------------------------------------------------------------------------------------------
+    def prepare(self, store: ParamStore) -> None:
+        """Fix the ownership map; must run before the optimizer allocates its state."""
+        self.owners = assign_owners(store, self.world_size)
+        self.slices: Dict[str, Tuple[int, int]] = {}
+        for s in store.specs:
+            if self.owners[s.name] == -1:
+                self.slices[s.name] = adamw_slice(s, self.rank, self.world_size)
+
+    def owned(self, spec: ParamSpec) -> bool:
+        """True for parameters this rank updates (its Muon matrices, and its slice of every AdamW tensor)."""
+        return self.owners[spec.name] in (-1, self.rank)
+
+    def attach(self, model, optimizer) -> None:
+        self.model, self.optimizer = model, optimizer
+        store = model.params
+        if self.world_size > 1:  # every rank must start from identical weights
+            dist.broadcast(store.master, src=0, group=self.group)
+            store.sync_compute()
+
+    def begin_step(self) -> None:
+        pass
+
+    def set_last_micro(self, last: bool) -> None:
+        self._last_micro = last
+
+    @torch.no_grad()
+    def finish_step(self, step: int) -> None:
+        store = self.model.params
+        opt = self.optimizer
+        if self.world_size > 1:
+            dist.all_reduce(store.grad, op=dist.ReduceOp.SUM, group=self.group)
+        from .. import ops
+        norm, clip = ops.grad_norm_and_clip([store.grad], opt.config.clip)
+        opt.last_grad_norm = norm
+        opt.step(step, clip_scale=clip)
+        if self.world_size > 1:
+            self._gather_params()
+
+    @torch.no_grad()
+    def _gather_params(self) -> None:
+        """Every rank zeroes what it does not own in the compute copy; a sum all-reduce rebuilds it."""
+        store = self.model.params
+        val = store.value
+        keep = torch.zeros_like(val)
+        for s in store.specs:
+            o = self.owners[s.name]
+            if o == self.rank:
+                keep[s.offset:s.offset + s.count] = val[s.offset:s.offset + s.count]
+            elif o == -1:
+                a, b = self.slices[s.name]
+                keep[s.offset + a:s.offset + b] = val[s.offset + a:s.offset + b]
+        dist.all_reduce(keep, op=dist.ReduceOp.SUM, group=self.group)
+        val.copy_(keep)
+        if store.value is store.master:
+            return
