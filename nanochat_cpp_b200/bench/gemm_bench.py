@@ -40,6 +40,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=65536)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default="")
+    ap.add_argument("--only", default="", help="run a single row, e.g. fc.fwd")
+    ap.add_argument("--no-lib", action="store_true", help="skip the cuBLAS timing")
     args = ap.parse_args()
     cfg = preset(args.preset)
     peaks = {}
@@ -51,6 +53,8 @@ def main():
     out = open(args.json, "w") if args.json else None
     dev = "cuda"
     for name, kind, m, n, k in shapes_for(cfg, args.tokens):
+        if args.only and args.only != name:
+            continue
         # the GEMM is C[m,n] = sum_k; operands are laid out as the training step meets them
         if kind == "fwd":
             a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
@@ -69,7 +73,7 @@ def main():
             ours = lambda: K.gemm(a, b, a_mn=True, b_mn=True, epi=K.EPI_F32, out=g, beta=1.0)
             lib = lambda: g.add_(torch.matmul(a.t(), b))
         t_ours = time_cuda(ours, iters=args.iters)
-        t_lib = time_cuda(lib, iters=args.iters)
+        t_lib = t_ours if args.no_lib else time_cuda(lib, iters=args.iters)
         fl = 2.0 * m * n * k
         row = dict(name=name, m=m, n=n, k=k, ours_ms=round(t_ours["median_ms"], 4),
                    cublas_ms=round(t_lib["median_ms"], 4),

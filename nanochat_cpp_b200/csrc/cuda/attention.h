@@ -29,7 +29,10 @@ struct AttnArgs {
   int* status = nullptr;
 };
 
+// one 128-row query tile per CTA, running output in registers
 const char* attention_fwd(const AttnArgs& args, cudaStream_t stream);
+// two query tiles per CTA, running output in TMEM with lazy rescaling (the default)
+const char* attention_fwd2(const AttnArgs& args, cudaStream_t stream);
 const char* attention_bwd(const AttnArgs& args, cudaStream_t stream);
 
 }  // namespace nc

@@ -38,7 +38,7 @@ void fill_common(nc::AttnArgs& a, const Tensor& q, const Tensor& k, const Tensor
 }
 
 std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, int64_t window_left, double scale,
-                                  int64_t q_offset, Tensor status) {
+                                  int64_t q_offset, Tensor status, int64_t variant) {
   const c10::cuda::CUDAGuard guard(q.device());
   nc::AttnArgs a;
   fill_common(a, q, k, v, window_left, scale, q_offset);
@@ -48,7 +48,8 @@ std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor
   a.o_stride_b = o.stride(0), a.o_stride_t = o.stride(1), a.o_stride_h = o.stride(2);
   a.lse = lse.data_ptr<float>();
   a.status = status.data_ptr<int>();
-  const char* err = nc::attention_fwd(a, at::cuda::getCurrentCUDAStream());
+  const char* err = variant == 1 ? nc::attention_fwd(a, at::cuda::getCurrentCUDAStream())
+                                 : nc::attention_fwd2(a, at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(err == nullptr, err);
   return {o, lse};
 }

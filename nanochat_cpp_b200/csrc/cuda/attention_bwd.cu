@@ -11,7 +11,7 @@
 // ring, and run per secondary tile
 //      T1 = X1 * Y1^T   (scores, or scores transposed)        tcgen05.mma -> TMEM, double buffered
 //      T2 = X2 * Y2^T   (dP, or dP transposed)                tcgen05.mma -> TMEM, double buffered
-//      p  = exp2(T1 * c - lse),  ds = p * (T2 - delta) * scale  by 128 threads, one TMEM lane each
+//      p  = exp2(T1 * c - lse),  ds = p * (T2 - delta) * scale  by 256 threads (two per TMEM lane)
 //      acc1 += ds * Y1  (dQ += dS K   |  dK += dS^T Q)        A = ds from shared memory,
 //      acc2 += p  * Y2  (             |  dV += P^T dO)        B = the SAME shared-memory tile re-read
 //                                                             through an MN-major descriptor
@@ -29,7 +29,8 @@ namespace {
 
 constexpr int BP = 128;  // primary rows per CTA (TMEM lanes)
 constexpr int BS = 64;   // secondary rows per step
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_COMPUTE_WARPS = 8;  // two warps per TMEM lane quadrant, each takes half of the columns
+constexpr int NUM_THREADS = 64 + NUM_COMPUTE_WARPS * 32;
 constexpr int YSTAGES = 3;
 
 enum { kModeDQ = 0, kModeDKV = 1 };
@@ -131,10 +132,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1);
-      mbar_init(&t_empty[i], 4);
-      mbar_init(&w_full[i], 4);
+      mbar_init(&t_empty[i], NUM_COMPUTE_WARPS);
+      mbar_init(&w_full[i], NUM_COMPUTE_WARPS);
       mbar_init(&w_empty[i], 1);
-      mbar_init(&stats_full[i], 128);
+      mbar_init(&stats_full[i], NUM_COMPUTE_WARPS * 32);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -189,8 +190,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     if (lane == 0 && n_iters > 0) {
       constexpr uint32_t idesc_t = make_idesc_bf16(BP, BS, false, false);
       constexpr uint32_t idesc_a = make_idesc_bf16(BP, D, false, true);
-      const uint32_t sX1 = smem_u32(smem + L::kOffX1);
-      const uint32_t sX2 = smem_u32(smem + L::kOffX2);
+      const uint64_t x1_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffX1), 16, 1024);
+      const uint64_t x2_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffX2), 16, 1024);
+      const uint64_t y_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffY), 16, 1024);           // K-major view
+      const uint64_t ymn_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffY), BS * 128, 1024);  // MN-major view
+      const uint64_t w_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffW), 16, 1024);
       auto issue_t = [&](int it) -> bool {
         const int yst = it % YSTAGES;
         const uint32_t yph = (it / YSTAGES) & 1;
@@ -199,21 +203,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         if (!mbar_wait(&y_full[yst], yph, abort_flag, p.status, kErrWaitFull)) return false;
         if (!mbar_wait(&t_empty[tb], tph ^ 1, abort_flag, p.status, kErrWaitTmemEmpty)) return false;
         tc_fence_after();
-        const uint32_t sY1 = smem_u32(smem + L::kOffY + yst * 2 * L::kY);
-        const uint32_t sY2 = sY1 + L::kY;
+        const uint64_t dy1 = y_desc0 + static_cast<uint64_t>(yst * ((2 * L::kY) >> 4));
+        const uint64_t dy2 = dy1 + static_cast<uint64_t>(L::kY >> 4);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t xo = (k / 4) * (BP * 128) + (k % 4) * 32;
-          const uint32_t yo = (k / 4) * (BS * 128) + (k % 4) * 32;
-          mma_f16_ss(tmem_T1 + tb * BS, make_smem_desc_sw128(sX1 + xo, 16, 1024),
-                     make_smem_desc_sw128(sY1 + yo, 16, 1024), idesc_t, k > 0 ? 1u : 0u);
+          const uint64_t xo = static_cast<uint64_t>(((k / 4) * (BP * 128) + (k % 4) * 32) >> 4);
+          const uint64_t yo = static_cast<uint64_t>(((k / 4) * (BS * 128) + (k % 4) * 32) >> 4);
+          mma_f16_ss(tmem_T1 + tb * BS, x1_desc0 + xo, dy1 + yo, idesc_t, k > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t xo = (k / 4) * (BP * 128) + (k % 4) * 32;
-          const uint32_t yo = (k / 4) * (BS * 128) + (k % 4) * 32;
-          mma_f16_ss(tmem_T2 + tb * BS, make_smem_desc_sw128(sX2 + xo, 16, 1024),
-                     make_smem_desc_sw128(sY2 + yo, 16, 1024), idesc_t, k > 0 ? 1u : 0u);
+          const uint64_t xo = static_cast<uint64_t>(((k / 4) * (BP * 128) + (k % 4) * 32) >> 4);
+          const uint64_t yo = static_cast<uint64_t>(((k / 4) * (BS * 128) + (k % 4) * 32) >> 4);
+          mma_f16_ss(tmem_T2 + tb * BS, x2_desc0 + xo, dy2 + yo, idesc_t, k > 0 ? 1u : 0u);
         }
         mma_commit(&t_full[tb]);
         return true;
@@ -224,21 +226,20 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         const uint32_t tph = (it >> 1) & 1;
         if (!mbar_wait(&w_full[tb], tph, abort_flag, p.status, kErrWaitOther)) return false;
         tc_fence_after();
-        const uint32_t sW = smem_u32(smem + L::kOffW + tb * NW * L::kW);
-        const uint32_t sY1 = smem_u32(smem + L::kOffY + yst * 2 * L::kY);
-        const uint32_t sY2 = sY1 + L::kY;
+        const uint64_t dw = w_desc0 + static_cast<uint64_t>(tb * ((NW * L::kW) >> 4));
+        const uint64_t dy1 = ymn_desc0 + static_cast<uint64_t>(yst * ((2 * L::kY) >> 4));
+        const uint64_t dy2 = dy1 + static_cast<uint64_t>(L::kY >> 4);
 #pragma unroll
         for (int k = 0; k < BS / 16; ++k) {
           // A: ds tile, K-major, one 64-wide chunk; B: Y1 re-read MN-major (64-row K extent)
-          mma_f16_ss(tmem_A1, make_smem_desc_sw128(sW + k * 32, 16, 1024),
-                     make_smem_desc_sw128(sY1 + k * (16 * 128), BS * 128, 1024), idesc_a, (it > 0 || k > 0) ? 1u : 0u);
+          mma_f16_ss(tmem_A1, dw + static_cast<uint64_t>((k * 32) >> 4), dy1 + static_cast<uint64_t>((k * 16 * 128) >> 4),
+                     idesc_a, (it > 0 || k > 0) ? 1u : 0u);
         }
         if (MODE == kModeDKV) {
 #pragma unroll
           for (int k = 0; k < BS / 16; ++k) {
-            mma_f16_ss(tmem_A2, make_smem_desc_sw128(sW + L::kW + k * 32, 16, 1024),
-                       make_smem_desc_sw128(sY2 + k * (16 * 128), BS * 128, 1024), idesc_a,
-                       (it > 0 || k > 0) ? 1u : 0u);
+            mma_f16_ss(tmem_A2, dw + static_cast<uint64_t>((L::kW + k * 32) >> 4),
+                       dy2 + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_a, (it > 0 || k > 0) ? 1u : 0u);
           }
         }
         mma_commit(&y_empty[yst]);
@@ -258,7 +259,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     // -------------------------------------------------------------- compute warps
     const int qd = warp & 3;
     const int row = qd * 32 + lane;  // primary row inside the tile
-    const int tid128 = (warp - 2) * 32 + lane;
+    const int tid128 = (warp - 2) * 32 + lane;  // 0..255
+    const int ch = (warp - 2) >> 2;              // column half of this warp
     const uint32_t lane_sel = static_cast<uint32_t>(qd * 32) << 16;
     const int prow = p0 + row;
     const float kLog2e = 1.4426950408889634f;
@@ -269,6 +271,20 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       my_delta = p.delta[si];
     }
     bool ok = true;
+    // DKV mode: threads 0..63 carry lse (log2 units), threads 64..127 carry delta of query row s0 + (tid & 63)
+    auto load_stat = [&](int it) -> float {
+      const int g = it / n_sub;
+      const int q = (s_lo + it % n_sub) * BS + (tid128 & (BS - 1));
+      if (tid128 >= 2 * BS || q >= p.Tq) return 0.0f;
+      const long long si = (static_cast<long long>(b) * p.H + (kvh * group + g)) * p.Tq + q;
+      return tid128 < BS ? p.lse[si] * kLog2e : p.delta[si];
+    };
+    auto publish_stat = [&](int buf, float v) {
+      float* base = stats + buf * 2 * BS;
+      if (tid128 < 2 * BS) base[tid128] = v;  // [0,64) lse, [64,128) delta
+      mbar_arrive(&stats_full[buf]);
+    };
+    if (MODE == kModeDKV && n_iters > 0) publish_stat(0, load_stat(0));
     for (int it = 0; it < n_iters && ok; ++it) {
       const int tb = it & 1;
       const uint32_t tph = (it >> 1) & 1;
@@ -277,19 +293,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       const int s0 = sub * BS;  // first secondary row (key for DQ, query row for DKV)
       float* st_lse = stats + tb * 2 * BS;
       float* st_delta = st_lse + BS;
+      float next_stat = 0.0f;
       if (MODE == kModeDKV) {
-        // stage the per-query statistics of this sub-tile; buffer tb was last read two iterations ago
-        const int hq = kvh * group + g;
-        const int c = tid128 & (BS - 1);
-        const int q = s0 + c;
-        const long long si = (static_cast<long long>(b) * p.H + hq) * p.Tq + q;
-        if (tid128 < BS) {
-          st_lse[c] = q < p.Tq ? p.lse[si] * kLog2e : 0.0f;
-        } else {
-          st_delta[c] = q < p.Tq ? p.delta[si] : 0.0f;
-        }
-        // a bounded mbarrier, not bar.sync: a thread that gave up elsewhere must not strand the rest
-        mbar_arrive(&stats_full[tb]);
+        // fetch the statistics of the NEXT sub-tile now; they are published at the end of this iteration,
+        // so the global-load latency never sits on the critical path
+        if (it + 1 < n_iters) next_stat = load_stat(it + 1);
         if (!mbar_wait(&stats_full[tb], tph, abort_flag, p.status, kErrWaitOther)) { ok = false; break; }
       }
       // does any element of this 128 x 64 block need masking?
@@ -306,8 +314,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       tc_fence_after();
       if (!mbar_wait(&w_empty[tb], tph ^ 1, abort_flag, p.status, kErrWaitOther)) { ok = false; break; }
       uint8_t* sW = smem + L::kOffW + tb * NW * L::kW + row * 128;
-#pragma unroll 1
-      for (int c32 = 0; c32 < BS / 32; ++c32) {
+      {
+        const int c32 = ch;
         uint32_t t1[32], t2[32];
         tmem_ld_32x32(tmem_T1 + tb * BS + c32 * 32 + lane_sel, t1);
         tmem_ld_32x32(tmem_T2 + tb * BS + c32 * 32 + lane_sel, t2);
@@ -359,6 +367,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         mbar_arrive(&t_empty[tb]);
         mbar_arrive(&w_full[tb]);
       }
+      if (MODE == kModeDKV && it + 1 < n_iters) publish_stat(tb ^ 1, next_stat);
     }
     // ---- epilogue: accumulators -> bf16 -> global
     const bool have = n_iters > 0;
@@ -376,7 +385,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         __nv_bfloat16* op = base + b * sb + static_cast<long long>(prow) * stt + static_cast<long long>(hp) * sh;
         const uint32_t tacc = which == 0 ? tmem_A1 : tmem_A2;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = ch * (D / 64); c < (ch + 1) * (D / 64); ++c) {
           uint32_t r[32];
           if (have) {
             tmem_ld_32x32(tacc + c * 32 + lane_sel, r);

@@ -172,19 +172,21 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BQ, BKV, false, false);
       constexpr uint32_t idesc_o = make_idesc_bf16(BQ, D, false, true);
-      const uint32_t sQ = smem_u32(smem + L::kOffQ);
+      const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffQ), 16, 1024);
+      const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffK), 16, 1024);
+      const uint64_t p_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffP), 16, 1024);
+      const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem + L::kOffV), BKV * 128, 1024);
       auto issue_s = [&](int it) -> bool {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(&k_full[st], ph, abort_flag, p.status, kErrWaitFull)) return false;
         if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.status, kErrWaitTmemEmpty)) return false;
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + L::kOffK + st * L::kKV);
+        const uint64_t dk = k_desc0 + static_cast<uint64_t>(st * (L::kKV >> 4));
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * (128 * 128) + (k % 4) * 32;
-          mma_f16_ss(tmem_S + st * 128, make_smem_desc_sw128(sQ + off, 16, 1024),
-                     make_smem_desc_sw128(sK + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>(((k / 4) * (128 * 128) + (k % 4) * 32) >> 4);
+          mma_f16_ss(tmem_S + st * 128, q_desc0 + off, dk + off, idesc_s, k > 0 ? 1u : 0u);
         }
         mma_commit(&k_empty[st]);
         mma_commit(&s_full[st]);
@@ -197,14 +199,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (!mbar_wait(&p_full[st], ph, abort_flag, p.status, kErrWaitOther)) return false;
         if (!mbar_wait(&o_empty[st], ph ^ 1, abort_flag, p.status, kErrWaitTmemEmpty)) return false;
         tc_fence_after();
-        const uint32_t sP = smem_u32(smem + L::kOffP + st * L::kP);
-        const uint32_t sV = smem_u32(smem + L::kOffV + st * L::kKV);
+        const uint64_t dp = p_desc0 + static_cast<uint64_t>(st * (L::kP >> 4));
+        const uint64_t dv = v_desc0 + static_cast<uint64_t>(st * (L::kKV >> 4));
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
-          const uint32_t a_off = (k / 4) * (BQ * 128) + (k % 4) * 32;
-          const uint32_t b_off = k * (16 * 128);
-          mma_f16_ss(tmem_O + st * D, make_smem_desc_sw128(sP + a_off, 16, 1024),
-                     make_smem_desc_sw128(sV + b_off, BKV * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
+          const uint64_t a_off = static_cast<uint64_t>(((k / 4) * (BQ * 128) + (k % 4) * 32) >> 4);
+          const uint64_t b_off = static_cast<uint64_t>((k * (16 * 128)) >> 4);
+          mma_f16_ss(tmem_O + st * D, dp + a_off, dv + b_off, idesc_o, k > 0 ? 1u : 0u);
         }
         mma_commit(&v_empty[st]);
         mma_commit(&p_empty[st]);

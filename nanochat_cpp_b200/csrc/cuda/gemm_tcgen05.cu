@@ -67,8 +67,11 @@ struct Unit {
 
 __device__ __forceinline__ Unit decode_unit(const KernelParams& p, int unit) {
   Unit u;
-  const int split = unit % p.splits;
-  int t = unit / p.splits;
+  // split-major: consecutive units (the ones in flight together) share a k-range, so operand panels of
+  // neighbouring tiles are still shared through L2 when K is split
+  const int tiles = p.batch * p.m_blocks * p.n_blocks;
+  const int split = unit / tiles;
+  int t = unit - split * tiles;
   const int per_batch = p.m_blocks * p.n_blocks;
   u.b = t / per_batch;
   t -= u.b * per_batch;
@@ -171,6 +174,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      // per-UMMA_K advance of the start address, in 16-byte units
+      constexpr int kStepA = A_MN ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+      constexpr int kStepB = B_MN ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), A_MN ? CHUNK_BYTES : 16, 1024);
+      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem) + A_BYTES, B_MN ? CHUNK_BYTES : 16, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -188,15 +196,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sb = sa + A_BYTES;
+          // descriptors differ from the stage-0 ones only in the 16-byte-unit start address field
+          const uint64_t da0 = a_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
+          const uint64_t db0 = b_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = A_MN ? make_smem_desc_sw128(sa + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
-                                     : make_smem_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
-            const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
-                                     : make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
-            mma_f16_ss(d_tmem, da, db, idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
+            mma_f16_ss(d_tmem, da0 + static_cast<uint64_t>(k * kStepA), db0 + static_cast<uint64_t>(k * kStepB), idesc,
+                       (kb > u.kb0 || k > 0) ? 1u : 0u);
           }
           mma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
           if (++stage == STAGES) {
@@ -389,12 +395,21 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (dev < 64 && cached_sms[dev] == 0) cudaDeviceGetAttribute(&cached_sms[dev], cudaDevAttrMultiProcessorCount, dev);
   if (dev < 64 && cached_sms[dev] > 0) sms = cached_sms[dev];
   const long long tiles = static_cast<long long>(kp.batch) * kp.m_blocks * kp.n_blocks;
+  // K is split when whole tiles would leave SMs idle (fewer tiles than SMs, or a ragged last wave).
+  // The split count maximises wave efficiency minus a small charge per split for the red.add traffic.
   int splits = 1;
-  if (f32 && a.allow_split_k && tiles < sms) {
-    splits = static_cast<int>((sms + tiles - 1) / tiles);
-    const int max_splits = (kp.k_blocks + 7) / 8;  // at least 8 k-blocks per split
-    if (splits > max_splits) splits = max_splits;
-    if (splits < 1) splits = 1;
+  if (f32 && a.allow_split_k && (a.beta == 0.0f || a.beta == 1.0f)) {
+    double best = -1.0;
+    const int max_splits = kp.k_blocks / 16 > 0 ? (kp.k_blocks / 16 < 24 ? kp.k_blocks / 16 : 24) : 1;
+    for (int s = 1; s <= max_splits; ++s) {
+      const long long units = tiles * s;
+      const long long waves = (units + sms - 1) / sms;
+      const double score = static_cast<double>(units) / static_cast<double>(waves * sms) - 0.004 * (s - 1);
+      if (score > best + 1e-9) {
+        best = score;
+        splits = s;
+      }
+    }
   }
   kp.kb_per_split = (kp.k_blocks + splits - 1) / splits;
   splits = (kp.k_blocks + kp.kb_per_split - 1) / kp.kb_per_split;  // no empty split

@@ -275,37 +275,75 @@ __global__ void add_cols_kernel(bf16* dh, long long ld, const float* extra, int 
 }
 
 // ------------------------------------------------------------------ QK preparation
-// One warp per (token, head). Forward: y = rope(norm(x)) * scale.
+// One warp per token walks every head of the row, so the rotary row (cos/sin of the token's position)
+// is loaded once and reused by all heads. Forward: y = rope(norm(x)) * scale.
 __global__ void __launch_bounds__(kThreads) qk_prep_fwd_kernel(const bf16* __restrict__ in, long long ld_in,
                                                                bf16* __restrict__ out, long long ld_out,
                                                                const float* __restrict__ cosT,
                                                                const float* __restrict__ sinT, const int* positions,
                                                                int tokens, int seq, int heads, int D, float eps,
                                                                float scale) {
-  const long long wid = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (wid >= static_cast<long long>(tokens) * heads) return;
+  const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (tok >= tokens) return;
   const int lane = threadIdx.x & 31;
-  const int tok = static_cast<int>(wid / heads), h = static_cast<int>(wid % heads);
   const int pos = positions ? positions[tok] : tok % seq;
   const int half = D / 2;
-  const bf16* xp = in + static_cast<long long>(tok) * ld_in + h * D;
-  bf16* yp = out + static_cast<long long>(tok) * ld_out + h * D;
+  const bf16* row_in = in + static_cast<long long>(tok) * ld_in;
+  bf16* row_out = out + static_cast<long long>(tok) * ld_out;
   const float* cp = cosT + static_cast<long long>(pos) * half;
   const float* sp = sinT + static_cast<long long>(pos) * half;
-  float ss = 0.0f;
-  for (int d = lane; d < D; d += 32) {
-    const float v = b2f(xp[d]);
-    ss += v * v;
+  const float inv_d = 1.0f / static_cast<float>(D);
+  const bool vec = (half % 2 == 0) && half <= 64 && (reinterpret_cast<uintptr_t>(cp) & 7) == 0 &&
+                   (reinterpret_cast<uintptr_t>(sp) & 7) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(row_in) | reinterpret_cast<uintptr_t>(row_out)) & 3) == 0 && (D % 2 == 0);
+  if (vec) {
+    const int d = lane * 2;
+    const bool act = d < half;
+    float2 c = make_float2(0.f, 0.f), sn = make_float2(0.f, 0.f);
+    if (act) {
+      c = *reinterpret_cast<const float2*>(cp + d);
+      sn = *reinterpret_cast<const float2*>(sp + d);
+    }
+    for (int h = 0; h < heads; ++h) {
+      const bf16* xp = row_in + h * D;
+      bf16* yp = row_out + h * D;
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+      if (act) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(xp + d);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(xp + d + half);
+        a0 = b2f(a.x), a1 = b2f(a.y), b0 = b2f(b.x), b1 = b2f(b.y);
+      }
+      const float ss = warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1);
+      const float r = 1.0f / sqrtf(ss * inv_d + eps);
+      if (act) {
+        // the normalised value is rounded to bf16 before the rotation, as a separate norm pass would
+        const float x10 = b2f(f2b(a0 * r)), x11 = b2f(f2b(a1 * r));
+        const float x20 = b2f(f2b(b0 * r)), x21 = b2f(f2b(b1 * r));
+        *reinterpret_cast<__nv_bfloat162*>(yp + d) =
+            __floats2bfloat162_rn((x10 * c.x + x20 * sn.x) * scale, (x11 * c.y + x21 * sn.y) * scale);
+        *reinterpret_cast<__nv_bfloat162*>(yp + d + half) =
+            __floats2bfloat162_rn((-x10 * sn.x + x20 * c.x) * scale, (-x11 * sn.y + x21 * c.y) * scale);
+      }
+    }
+    return;
   }
-  ss = warp_sum(ss);
-  const float r = 1.0f / sqrtf(ss * (1.0f / static_cast<float>(D)) + eps);
-  for (int d = lane; d < half; d += 32) {
-    // the normalised value is rounded to bf16 before the rotation, as a separate norm pass would
-    const float x1 = b2f(f2b(b2f(xp[d]) * r));
-    const float x2 = b2f(f2b(b2f(xp[d + half]) * r));
-    const float c = cp[d], s = sp[d];
-    yp[d] = f2b((x1 * c + x2 * s) * scale);
-    yp[d + half] = f2b((-x1 * s + x2 * c) * scale);
+  for (int h = 0; h < heads; ++h) {
+    const bf16* xp = row_in + h * D;
+    bf16* yp = row_out + h * D;
+    float ss = 0.0f;
+    for (int d = lane; d < D; d += 32) {
+      const float v = b2f(xp[d]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss * inv_d + eps);
+    for (int d = lane; d < half; d += 32) {
+      const float x1 = b2f(f2b(b2f(xp[d]) * r));
+      const float x2 = b2f(f2b(b2f(xp[d + half]) * r));
+      const float c = cp[d], s = sp[d];
+      yp[d] = f2b((x1 * c + x2 * s) * scale);
+      yp[d + half] = f2b((-x1 * s + x2 * c) * scale);
+    }
   }
 }
 
@@ -315,39 +353,84 @@ __global__ void __launch_bounds__(kThreads) qk_prep_bwd_kernel(const bf16* __res
                                                                const float* __restrict__ cosT,
                                                                const float* __restrict__ sinT, int tokens, int seq,
                                                                int heads, int D, float eps, float scale) {
-  const long long wid = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (wid >= static_cast<long long>(tokens) * heads) return;
+  const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (tok >= tokens) return;
   const int lane = threadIdx.x & 31;
-  const int tok = static_cast<int>(wid / heads), h = static_cast<int>(wid % heads);
   const int pos = tok % seq;
   const int half = D / 2;
-  const bf16* xp = pre + static_cast<long long>(tok) * ld_pre + h * D;
-  const bf16* gp = grad + static_cast<long long>(tok) * ld_grad + h * D;
-  bf16* op = out + static_cast<long long>(tok) * ld_out + h * D;
+  const bf16* row_x = pre + static_cast<long long>(tok) * ld_pre;
+  const bf16* row_g = grad + static_cast<long long>(tok) * ld_grad;
+  bf16* row_o = out + static_cast<long long>(tok) * ld_out;
   const float* cp = cosT + static_cast<long long>(pos) * half;
   const float* sp = sinT + static_cast<long long>(pos) * half;
-  float ss = 0.0f, dot = 0.0f;
-  for (int d = lane; d < half; d += 32) {
-    const float c = cp[d], s = sp[d];
-    const float x1 = b2f(xp[d]), x2 = b2f(xp[d + half]);
-    const float g1 = b2f(gp[d]), g2 = b2f(gp[d + half]);
-    const float n1 = scale * (g1 * c - g2 * s);
-    const float n2 = scale * (g1 * s + g2 * c);
-    ss += x1 * x1 + x2 * x2;
-    dot += x1 * n1 + x2 * n2;
+  const float inv_d = 1.0f / static_cast<float>(D);
+  const bool vec = (half % 2 == 0) && half <= 64 && (reinterpret_cast<uintptr_t>(cp) & 7) == 0 &&
+                   (reinterpret_cast<uintptr_t>(sp) & 7) == 0 && (D % 2 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(row_x) | reinterpret_cast<uintptr_t>(row_g) |
+                     reinterpret_cast<uintptr_t>(row_o)) & 3) == 0;
+  if (vec) {
+    const int d = lane * 2;
+    const bool act = d < half;
+    float cc[2] = {0.f, 0.f}, sc[2] = {0.f, 0.f};
+    if (act) {
+      const float2 c = *reinterpret_cast<const float2*>(cp + d);
+      const float2 sn = *reinterpret_cast<const float2*>(sp + d);
+      cc[0] = c.x, cc[1] = c.y, sc[0] = sn.x, sc[1] = sn.y;
+    }
+    for (int h = 0; h < heads; ++h) {
+      const bf16* xp = row_x + h * D;
+      const bf16* gp = row_g + h * D;
+      bf16* op = row_o + h * D;
+      float x1[2] = {0.f, 0.f}, x2[2] = {0.f, 0.f}, n1[2] = {0.f, 0.f}, n2[2] = {0.f, 0.f};
+      if (act) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(xp + d);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(xp + d + half);
+        const __nv_bfloat162 ga = *reinterpret_cast<const __nv_bfloat162*>(gp + d);
+        const __nv_bfloat162 gb = *reinterpret_cast<const __nv_bfloat162*>(gp + d + half);
+        x1[0] = b2f(a.x), x1[1] = b2f(a.y), x2[0] = b2f(b.x), x2[1] = b2f(b.y);
+        const float g1[2] = {b2f(ga.x), b2f(ga.y)}, g2[2] = {b2f(gb.x), b2f(gb.y)};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          n1[u] = scale * (g1[u] * cc[u] - g2[u] * sc[u]);
+          n2[u] = scale * (g1[u] * sc[u] + g2[u] * cc[u]);
+        }
+      }
+      const float ss = warp_sum(x1[0] * x1[0] + x1[1] * x1[1] + x2[0] * x2[0] + x2[1] * x2[1]);
+      const float dot = warp_sum(x1[0] * n1[0] + x1[1] * n1[1] + x2[0] * n2[0] + x2[1] * n2[1]);
+      const float r = 1.0f / sqrtf(ss * inv_d + eps);
+      const float coeff = r * r * r * dot * inv_d;
+      if (act) {
+        *reinterpret_cast<__nv_bfloat162*>(op + d) =
+            __floats2bfloat162_rn(r * n1[0] - coeff * x1[0], r * n1[1] - coeff * x1[1]);
+        *reinterpret_cast<__nv_bfloat162*>(op + d + half) =
+            __floats2bfloat162_rn(r * n2[0] - coeff * x2[0], r * n2[1] - coeff * x2[1]);
+      }
+    }
+    return;
   }
-  ss = warp_sum(ss);
-  dot = warp_sum(dot);
-  const float r = 1.0f / sqrtf(ss * (1.0f / static_cast<float>(D)) + eps);
-  const float coeff = r * r * r * dot * (1.0f / static_cast<float>(D));
-  for (int d = lane; d < half; d += 32) {
-    const float c = cp[d], s = sp[d];
-    const float x1 = b2f(xp[d]), x2 = b2f(xp[d + half]);
-    const float g1 = b2f(gp[d]), g2 = b2f(gp[d + half]);
-    const float n1 = scale * (g1 * c - g2 * s);
-    const float n2 = scale * (g1 * s + g2 * c);
-    op[d] = f2b(r * n1 - coeff * x1);
-    op[d + half] = f2b(r * n2 - coeff * x2);
+  for (int h = 0; h < heads; ++h) {
+    const bf16* xp = row_x + h * D;
+    const bf16* gp = row_g + h * D;
+    bf16* op = row_o + h * D;
+    float ss = 0.0f, dot = 0.0f;
+    for (int d = lane; d < half; d += 32) {
+      const float c = cp[d], s = sp[d];
+      const float x1 = b2f(xp[d]), x2 = b2f(xp[d + half]);
+      const float g1 = b2f(gp[d]), g2 = b2f(gp[d + half]);
+      ss += x1 * x1 + x2 * x2;
+      dot += x1 * scale * (g1 * c - g2 * s) + x2 * scale * (g1 * s + g2 * c);
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float r = 1.0f / sqrtf(ss * inv_d + eps);
+    const float coeff = r * r * r * dot * inv_d;
+    for (int d = lane; d < half; d += 32) {
+      const float c = cp[d], s = sp[d];
+      const float x1 = b2f(xp[d]), x2 = b2f(xp[d + half]);
+      const float g1 = b2f(gp[d]), g2 = b2f(gp[d + half]);
+      op[d] = f2b(r * scale * (g1 * c - g2 * s) - coeff * x1);
+      op[d + half] = f2b(r * scale * (g1 * s + g2 * c) - coeff * x2);
+    }
   }
 }
 
@@ -707,17 +790,15 @@ void add_cols(bf16* dh, long long ld, const float* extra, int rows, int ncols, c
 }
 void qk_prep_fwd(const bf16* in, long long ld_in, bf16* out, long long ld_out, const float* cos, const float* sin,
                  const int* positions, int tokens, int seq, int heads, int D, float eps, float scale, cudaStream_t s) {
-  const long long n = static_cast<long long>(tokens) * heads;
-  if (n <= 0) return;
-  qk_prep_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(in, ld_in, out, ld_out, cos, sin, positions, tokens, seq,
+  if (tokens <= 0 || heads <= 0) return;
+  qk_prep_fwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(in, ld_in, out, ld_out, cos, sin, positions, tokens, seq,
                                                              heads, D, eps, scale);
 }
 void qk_prep_bwd(const bf16* pre, long long ld_pre, const bf16* grad, long long ld_grad, bf16* out, long long ld_out,
                  const float* cos, const float* sin, int tokens, int seq, int heads, int D, float eps, float scale,
                  cudaStream_t s) {
-  const long long n = static_cast<long long>(tokens) * heads;
-  if (n <= 0) return;
-  qk_prep_bwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(pre, ld_pre, grad, ld_grad, out, ld_out, cos, sin, tokens,
+  if (tokens <= 0 || heads <= 0) return;
+  qk_prep_bwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(pre, ld_pre, grad, ld_grad, out, ld_out, cos, sin, tokens,
                                                              seq, heads, D, eps, scale);
 }
 void value_gate_fwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, bf16* v, long long ldv,

@@ -240,12 +240,14 @@ class GPT:
             qd, kd = cfg.query_dim, cfg.kv_dim
             dqkv = torch.empty(M, qd + 2 * kd, dtype=dx_mid.dtype, device=dx_mid.device)
             dv4 = _heads(dqkv[:, qd + kd:], B, T, KV, D)
+            dqk = torch.empty(M, qd + kd, dtype=dx_mid.dtype, device=dx_mid.device)
             dq, dk, _ = ops.attention_bwd(s["q"], s["k"], s["v"], s["attn"], s["lse"], dattn.view(B, T, H, D),
-                                          cfg.window_left(i), out=(None, None, dv4))
+                                          cfg.window_left(i),
+                                          out=(_heads(dqk[:, :qd], B, T, H, D), _heads(dqk[:, qd:], B, T, KV, D), dv4))
             del dattn
             ops.qk_prep_bwd(_heads(s["q_pre"], B, T, H, D), _heads(s["k_pre"], B, T, KV, D), dq, dk, cos, sin,
                             out_q=_heads(dqkv[:, :qd], B, T, H, D), out_k=_heads(dqkv[:, qd:qd + kd], B, T, KV, D))
-            del dq, dk
+            del dq, dk, dqk
             h = ops.rmsnorm_apply(s["xr"], s["rstd1"])
             dv2 = dqkv[:, qd + kd:]
             dh12 = None

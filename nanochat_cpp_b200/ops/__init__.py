@@ -55,13 +55,58 @@ def _first_tensor(args, kwargs):
     return None
 
 
+class OpProfile:
+    """Per-operator device time, measured with CUDA events around every operator call.
+
+    `with ops.profile() as prof: step()` then `prof.table()` gives milliseconds and call counts per
+    operator. Events are recorded on the current stream, so the numbers are what the stream spent
+    between the two records (launch gaps included)."""
+
+    def __init__(self):
+        self.events = []
+
+    def __enter__(self):
+        global _PROFILE
+        _PROFILE = self
+        return self
+
+    def __exit__(self, *exc):
+        global _PROFILE
+        _PROFILE = None
+
+    def table(self):
+        torch.cuda.synchronize()
+        agg = {}
+        for name, a, b in self.events:
+            ms = a.elapsed_time(b)
+            t = agg.setdefault(name, [0.0, 0])
+            t[0] += ms
+            t[1] += 1
+        return sorted(((k, v[0], v[1]) for k, v in agg.items()), key=lambda r: -r[1])
+
+
+_PROFILE = None
+
+
+def profile() -> OpProfile:
+    return OpProfile()
+
+
 def _dispatch(name: str) -> Callable:
     ref_fn = getattr(ref, name)
 
     def fn(*args, **kwargs):
         t = _first_tensor(args, kwargs)
         if t is not None and t.is_cuda and _MODE == "kernels":
-            return getattr(cuda_module(), name)(*args, **kwargs)
+            impl = getattr(cuda_module(), name)
+            if _PROFILE is not None:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                out = impl(*args, **kwargs)
+                b.record()
+                _PROFILE.events.append((name, a, b))
+                return out
+            return impl(*args, **kwargs)
         return ref_fn(*args, **kwargs)
 
     fn.__name__ = name
@@ -82,4 +127,4 @@ for _n in _NAMES:
 
 build_rope = ref.build_rope
 
-__all__ = _NAMES + ["build_rope", "ref", "set_mode", "get_mode", "cuda_module"]
+__all__ = _NAMES + ["profile", "OpProfile", "build_rope", "ref", "set_mode", "get_mode", "cuda_module"]

@@ -180,7 +180,25 @@ def blend_bwd(dxr, x, x0, lam_r, lam_0, dx0_acc=None):
     return dx, dx0, dlam[0], dlam[1]
 
 
+def _fused_heads(a, b):
+    """If `b` ([B,T,Hb,D]) starts right after the heads of `a` ([B,T,Ha,D]) in the same token rows, return
+    the [B,T,Ha+Hb,D] view covering both, else None."""
+    if a.stride() != b.stride() or a.shape[:2] != b.shape[:2] or a.shape[3] != b.shape[3]:
+        return None
+    if b.data_ptr() != a.data_ptr() + a.shape[2] * a.shape[3] * a.element_size():
+        return None
+    if a.stride(1) < (a.shape[2] + b.shape[2]) * a.shape[3]:
+        return None
+    B, T, Ha, D = a.shape
+    return a.as_strided((B, T, Ha + b.shape[2], D), a.stride(), a.storage_offset())
+
+
 def qk_prep_fwd(q_pre, k_pre, cos, sin, eps=RMS_EPS, scale=QK_SCALE, positions=None):
+    both = _fused_heads(q_pre, k_pre)
+    if both is not None:   # q and k of a fused QKV row: one launch, one output buffer
+        out = _C.qk_prep_fwd_one(both, cos, sin, positions, eps, scale)
+        H = q_pre.shape[2]
+        return out[:, :, :H], out[:, :, H:]
     return (_C.qk_prep_fwd_one(q_pre, cos, sin, positions, eps, scale),
             _C.qk_prep_fwd_one(k_pre, cos, sin, positions, eps, scale))
 
@@ -190,6 +208,10 @@ def qk_prep_bwd(q_pre, k_pre, dq, dk, cos, sin, eps=RMS_EPS, scale=QK_SCALE, out
         out_q = torch.empty(dq.shape, dtype=dq.dtype, device=dq.device)
     if out_k is None:
         out_k = torch.empty(dk.shape, dtype=dk.dtype, device=dk.device)
+    pre, grad, out = _fused_heads(q_pre, k_pre), _fused_heads(dq, dk), _fused_heads(out_q, out_k)
+    if pre is not None and grad is not None and out is not None:
+        _C.qk_prep_bwd_one(pre, grad, out, cos, sin, eps, scale)
+        return out_q, out_k
     _C.qk_prep_bwd_one(q_pre, dq, out_q, cos, sin, eps, scale)
     _C.qk_prep_bwd_one(k_pre, dk, out_k, cos, sin, eps, scale)
     return out_q, out_k
@@ -266,12 +288,13 @@ def grad_norm_and_clip(grads, clip):
 # ---------------------------------------------------------------------------
 # Attention
 # ---------------------------------------------------------------------------
-def attention_fwd(q, k, v, window_left=-1, scale=None, q_offset=None):
+def attention_fwd(q, k, v, window_left=-1, scale=None, q_offset=None, variant=2):
+    """variant 2 (default): two query tiles per CTA, output accumulated in TMEM; variant 1: one tile per CTA."""
     import math
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     o, lse = _C.attention_fwd(q, k, v, int(window_left), float(scale), -1 if q_offset is None else int(q_offset),
-                              _status(q))
+                              _status(q), variant)
     return o, lse
 
 

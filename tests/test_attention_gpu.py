@@ -35,6 +35,8 @@ CASES = [
     (2, 256, 2, 2, 64, -1),
     (1, 320, 4, 2, 64, 96),
     (1, 1024, 2, 2, 128, 2048),   # window larger than the sequence
+    (1, 777, 2, 2, 128, 40),      # window far below a tile: rows fully masked inside edge tiles
+    (2, 2048, 2, 2, 128, 1024),
 ]
 
 
@@ -44,11 +46,12 @@ def test_forward_backward(B, T, H, KV, D, window):
     torch.manual_seed(B * 1000 + T + H + D)
     q, k, v = _r(B, T, H, D), _r(B, T, KV, D), _r(B, T, KV, D)
     do = _r(B, T, H, D)
-    o, lse = K.attention_fwd(q, k, v, window)
     o_ref, lse_ref = ref.attention_fwd(q, k, v, window)
-    K.check_status()
-    _close(o, o_ref, 2e-2, "o")
-    _close(lse, lse_ref, 2e-3, "lse")
+    for variant in (1, 2):
+        o, lse = K.attention_fwd(q, k, v, window, variant=variant)
+        K.check_status()
+        _close(o, o_ref, 2e-2, f"o v{variant}")
+        _close(lse, lse_ref, 2e-3, f"lse v{variant}")
     dq, dk, dv = K.attention_bwd(q, k, v, o, lse, do, window)
     K.check_status()
     rdq, rdk, rdv = ref.attention_bwd(q, k, v, o_ref, lse_ref, do, window)
