@@ -129,8 +129,8 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
         from nanochat_cpp_b200.parallel.dp import DataParallel
-        transport = "nccl" if args.transport == "auto" else args.transport
-        dp = DataParallel(rank, world, transport=transport)
+        transport = "fused" if args.transport == "auto" else args.transport
+        dp = DataParallel(rank, world, transport=transport, device=dev)
 
     cfg = preset(args.preset)
     micro = args.micro_batch or args.batch

@@ -40,7 +40,8 @@ void check_bf16_cuda(const torch::Tensor& t, const char* name) {
 //   b_mn == false: B is [.., N, K]   (K contiguous);   b_mn == true: B is [.., K, N]  (N contiguous)
 void gemm(const torch::Tensor& A, const torch::Tensor& B, torch::Tensor& C, bool a_mn, bool b_mn, int64_t epi,
           const c10::optional<torch::Tensor>& R, const c10::optional<torch::Tensor>& C2, double alpha, double beta,
-          bool allow_split_k) {
+          bool allow_split_k, const c10::optional<torch::Tensor>& wait_flags, int64_t wait_value, int64_t gather_src,
+          const c10::optional<torch::Tensor>& gather_counter, int64_t gather_base) {
   check_bf16_cuda(A, "A");
   check_bf16_cuda(B, "B");
   TORCH_CHECK(C.is_cuda() && C.stride(-1) == 1, "C must be a CUDA tensor with a contiguous last dimension");
@@ -90,6 +91,21 @@ void gemm(const torch::Tensor& A, const torch::Tensor& B, torch::Tensor& C, bool
   g.beta = static_cast<float>(beta);
   g.allow_split_k = allow_split_k;
   g.status = status_ptr(A);
+  if (wait_flags.has_value()) {
+    TORCH_CHECK(wait_flags->is_cuda() && wait_flags->scalar_type() == torch::kInt32 && wait_flags->is_contiguous(),
+                "wait_flags must be a contiguous CUDA int32 tensor");
+    g.wait_flags = wait_flags->data_ptr<int>();
+    g.wait_count = static_cast<int>(wait_flags->numel());
+    g.wait_value = static_cast<int>(wait_value);
+  }
+  if (gather_src != 0) {
+    TORCH_CHECK(gather_counter.has_value() && gather_counter->scalar_type() == torch::kInt32, "gather needs a counter");
+    TORCH_CHECK(B.is_contiguous() && B.dim() == 2, "gathered B operand must be a contiguous matrix");
+    g.gather_src = reinterpret_cast<const void*>(static_cast<uintptr_t>(gather_src));
+    g.gather_bytes = B.numel() * 2;
+    g.gather_counter = gather_counter->data_ptr<int>();
+    g.gather_base = static_cast<int>(gather_base);
+  }
   const char* err = nc::gemm_bf16(g, at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(err == nullptr, err);
 }
@@ -105,7 +121,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogue", pybind11::arg("A"), pybind11::arg("B"),
         pybind11::arg("C"), pybind11::arg("a_mn") = false, pybind11::arg("b_mn") = false, pybind11::arg("epi") = 0,
         pybind11::arg("R") = pybind11::none(), pybind11::arg("C2") = pybind11::none(), pybind11::arg("alpha") = 1.0,
-        pybind11::arg("beta") = 0.0, pybind11::arg("allow_split_k") = true);
+        pybind11::arg("beta") = 0.0, pybind11::arg("allow_split_k") = true,
+        pybind11::arg("wait_flags") = pybind11::none(), pybind11::arg("wait_value") = 0,
+        pybind11::arg("gather_src") = 0, pybind11::arg("gather_counter") = pybind11::none(),
+        pybind11::arg("gather_base") = 0);
   m.def("read_status", &read_status, "first bounded-wait failure recorded on the device (0 = none); synchronizes");
   m.def("reset_status", &reset_status);
   m.def("status_tensor", [](int64_t d) { return status_tensor(static_cast<int>(d)); });

@@ -1,0 +1,46 @@
+// Host launchers of the data-parallel communication kernels (comm.cu). All of them work on symmetric
+// buffers: every rank allocated the same layout, `PeerPtrs` holds the address of that buffer on each
+// rank (peer addresses are NVLink peer mappings; entry [rank] is the local buffer).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace nc {
+
+constexpr int kMaxRanks = 8;
+
+struct PeerPtrs {
+  void* p[kMaxRanks];
+};
+
+struct Segment {
+  long long offset;  // elements from the start of the flat buffer
+  long long count;   // elements (multiple of 4)
+};
+
+// Publish `value` into slot `slot` of every rank's flag array: flags[slot * world + my_rank] = value.
+void comm_signal(const PeerPtrs& flags, int world, int my_rank, int slot, int value, cudaStream_t s);
+
+// Spin (bounded) until flags[slot * world + r] >= value for every r; records kErrWaitPeer on expiry.
+void comm_wait(const int* local_flags, int world, int slot, int value, int* status, cudaStream_t s);
+
+// Gradient reduce-scatter by peer loads: for every element of this rank's segments,
+//   out[e] = scale * sum_{r = 0..world-1} grads[r][e]   (fixed rank order)
+// written in place into the local gradient buffer, plus the sum of squares of the result accumulated
+// into `sumsq` (double). Waits first until every rank has published `value` in `slot`.
+void comm_reduce_pull(const PeerPtrs& grads, int world, int my_rank, const Segment* segs_dev, int nsegs,
+                      long long total, float scale, const int* local_flags, int slot, int value, double* sumsq,
+                      int* status, int ctas, cudaStream_t s);
+
+// AdamW on this rank's slice, writing the updated bf16 values into every rank's parameter buffer
+// (values.p[r] + value_offset): the all-gather is the update's store.
+void comm_adamw_push(float* master, const PeerPtrs& values, long long value_offset, int world, const float* grad,
+                     float* m, float* v, long long n, float lr, float beta1, float beta2, float eps,
+                     float weight_decay, int step, const float* grad_scale, cudaStream_t s);
+
+// Muon's last stage (cautious decay + update) for one matrix, pushing the bf16 result to every rank.
+void comm_muon_apply_push(float* master, const PeerPtrs& values, long long value_offset, int world,
+                          const __nv_bfloat16* xb, const float* scale0, const float* line_scale,
+                          bool lines_are_rows, int rows, int cols, float lr, float weight_decay, cudaStream_t s);
+
+}  // namespace nc

@@ -1,0 +1,76 @@
+// Tensor-level wrappers of the communication kernels. Peer buffers are passed as lists of raw device
+// addresses (one per rank, as handed out by the symmetric-memory rendezvous).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "comm.h"
+
+namespace {
+
+using torch::Tensor;
+inline cudaStream_t cur() { return at::cuda::getCurrentCUDAStream(); }
+
+nc::PeerPtrs to_peers(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(!ptrs.empty() && ptrs.size() <= nc::kMaxRanks, "between 1 and 8 ranks are supported");
+  nc::PeerPtrs p;
+  for (int i = 0; i < nc::kMaxRanks; ++i) p.p[i] = nullptr;
+  for (size_t i = 0; i < ptrs.size(); ++i) p.p[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(ptrs[i]));
+  return p;
+}
+
+void comm_signal(const std::vector<int64_t>& flag_ptrs, int64_t my_rank, int64_t slot, int64_t value) {
+  nc::comm_signal(to_peers(flag_ptrs), static_cast<int>(flag_ptrs.size()), my_rank, slot, value, cur());
+}
+
+void comm_wait(const Tensor& flags, int64_t world, int64_t slot, int64_t value, Tensor status) {
+  const c10::cuda::CUDAGuard g(flags.device());
+  nc::comm_wait(flags.data_ptr<int>(), world, slot, value, status.data_ptr<int>(), cur());
+}
+
+// segs: int64 [nsegs, 2] (offset, count) on the device
+void comm_reduce_pull(const std::vector<int64_t>& grad_ptrs, int64_t my_rank, const Tensor& segs, int64_t total,
+                      double scale, const Tensor& flags, int64_t slot, int64_t value, Tensor sumsq, Tensor status,
+                      int64_t ctas) {
+  const c10::cuda::CUDAGuard g(flags.device());
+  TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == torch::kInt64 && segs.is_contiguous() && segs.size(1) == 2,
+              "segs must be an int64 [n, 2] CUDA tensor");
+  static_assert(sizeof(nc::Segment) == 16, "Segment layout");
+  nc::comm_reduce_pull(to_peers(grad_ptrs), static_cast<int>(grad_ptrs.size()), my_rank,
+                       reinterpret_cast<const nc::Segment*>(segs.data_ptr<int64_t>()), segs.size(0), total, scale,
+                       flags.data_ptr<int>(), slot, value, sumsq.data_ptr<double>(), status.data_ptr<int>(), ctas,
+                       cur());
+}
+
+void comm_adamw_push(Tensor& master, const std::vector<int64_t>& value_ptrs, int64_t value_offset, const Tensor& grad,
+                     Tensor& m, Tensor& v, double lr, double beta1, double beta2, double eps, double weight_decay,
+                     int64_t step, const c10::optional<Tensor>& grad_scale) {
+  const c10::cuda::CUDAGuard g(master.device());
+  TORCH_CHECK(master.is_contiguous() && grad.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw_push");
+  nc::comm_adamw_push(master.data_ptr<float>(), to_peers(value_ptrs), value_offset,
+                      static_cast<int>(value_ptrs.size()), grad.data_ptr<float>(), m.data_ptr<float>(),
+                      v.data_ptr<float>(), master.numel(), lr, beta1, beta2, eps, weight_decay, step,
+                      grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, cur());
+}
+
+void comm_muon_apply_push(Tensor& master, const std::vector<int64_t>& value_ptrs, int64_t value_offset,
+                          const Tensor& xb, const Tensor& scale0, const Tensor& line_scale, bool lines_are_rows,
+                          double lr, double wd) {
+  const c10::cuda::CUDAGuard g(master.device());
+  TORCH_CHECK(master.dim() == 2 && master.is_contiguous() && xb.is_contiguous() && master.size(1) % 2 == 0,
+              "muon_apply_push");
+  nc::comm_muon_apply_push(master.data_ptr<float>(), to_peers(value_ptrs), value_offset,
+                           static_cast<int>(value_ptrs.size()), reinterpret_cast<const __nv_bfloat16*>(xb.data_ptr()),
+                           scale0.data_ptr<float>(), line_scale.data_ptr<float>(), lines_are_rows, master.size(0),
+                           master.size(1), lr, wd, cur());
+}
+
+}  // namespace
+
+void register_comm(pybind11::module_& m) {
+  m.def("comm_signal", &comm_signal);
+  m.def("comm_wait", &comm_wait);
+  m.def("comm_reduce_pull", &comm_reduce_pull);
+  m.def("comm_adamw_push", &comm_adamw_push);
+  m.def("comm_muon_apply_push", &comm_muon_apply_push);
+}

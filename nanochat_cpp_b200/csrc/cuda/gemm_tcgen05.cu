@@ -59,6 +59,13 @@ struct KernelParams {
   long long ldr, strideR;
   float alpha, beta;
   int* status;
+  const int* wait_flags;
+  int wait_count, wait_value;
+  const uint4* gather_src;
+  uint4* gather_dst;
+  long long gather_vecs;
+  int* gather_counter;
+  int gather_base;
 };
 
 struct Unit {
@@ -128,12 +135,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (p.gather_src != nullptr) {
+    // All-gather fused into the consuming GEMM: every CTA pulls its slice of the weight from the owner's
+    // memory with plain peer loads and stores it at the local address the tensor map points to.
+    const long long per = (p.gather_vecs + gridDim.x - 1) / gridDim.x;
+    const long long v0 = static_cast<long long>(blockIdx.x) * per;
+    const long long v1 = min(p.gather_vecs, v0 + per);
+    for (long long i = v0 + threadIdx.x; i < v1; i += NUM_THREADS) p.gather_dst[i] = p.gather_src[i];
+    __threadfence();
+    asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores before async-proxy (TMA) loads
+    __syncthreads();
+    if (threadIdx.x == 0) atomicAdd(p.gather_counter, 1);
+  }
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if (p.gather_src != nullptr) {
+        const unsigned long long t0 = globaltimer_ns();
+        const int want = p.gather_base + static_cast<int>(gridDim.x);
+        while (ok && ld_acquire_sys(p.gather_counter) - want < 0) {
+          if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+            *abort_flag = 1;
+            if (p.status != nullptr) atomicCAS(p.status, 0, kErrWaitOther);
+            ok = false;
+          }
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
+      if (ok && p.wait_flags != nullptr && !wait_flags_bounded(p.wait_flags, p.wait_count, p.wait_value, p.status)) {
+        *abort_flag = 1;
+        ok = false;
+      }
       for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
         const Unit u = decode_unit(p, unit);
         for (int kb = u.kb0; kb < u.kb1; ++kb) {
@@ -419,6 +455,14 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   kp.R = static_cast<const __nv_bfloat16*>(a.R), kp.ldr = a.ldr, kp.strideR = a.strideR;
   kp.alpha = a.alpha, kp.beta = a.beta;
   kp.status = a.status;
+  kp.wait_flags = a.wait_flags, kp.wait_count = a.wait_count, kp.wait_value = a.wait_value;
+  kp.gather_src = static_cast<const uint4*>(a.gather_src);
+  kp.gather_dst = static_cast<uint4*>(const_cast<void*>(a.B));
+  kp.gather_vecs = a.gather_bytes / 16;
+  kp.gather_counter = a.gather_counter;
+  kp.gather_base = a.gather_base;
+  if (a.gather_src != nullptr && (a.gather_counter == nullptr || (a.gather_bytes % 16) != 0))
+    return "gemm_bf16: gather needs a counter and a byte count that is a multiple of 16";
   if (f32 && splits > 1 && a.beta == 0.0f) {
     // red.add needs a zeroed destination
     if (a.ldc == a.N && a.batch == 1) {

@@ -32,6 +32,19 @@ struct GemmArgs {
   int epi = kEpiBf16;
   bool allow_split_k = true;  // kEpiF32 only: split K across CTAs when there are fewer tiles than SMs
   int* status = nullptr;      // device status word (see ptx.cuh error codes); may be null
+  // Data-parallel hooks for the B operand (the weight), both optional:
+  //  * wait_flags: the TMA producer does not touch B before wait_flags[i] >= wait_value for all i < wait_count
+  //    (owners publish these flags after pushing updated weights into this rank's parameter buffer);
+  //  * gather_src: B is first copied from `gather_src` (a peer mapping of the owner's copy) into its local
+  //    address by all CTAs (plain peer loads), then a grid-wide counter releases the TMA producers. The
+  //    tensor map always points at local memory. gather_counter must count up monotonically across calls:
+  //    pass the value it will have reached when every CTA of this launch has arrived (kernel adds grid each call).
+  const int* wait_flags = nullptr;
+  int wait_count = 0, wait_value = 0;
+  const void* gather_src = nullptr;
+  long long gather_bytes = 0;
+  int* gather_counter = nullptr;
+  int gather_base = 0;  // counter value before this launch
 };
 
 // Returns nullptr on success or a static error string.

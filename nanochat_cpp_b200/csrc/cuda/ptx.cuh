@@ -95,6 +95,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// ---------------------------------------------------------------- cross-GPU flags
+constexpr unsigned long long kPeerWaitBudgetNs = 20000000000ull;  // 20 s: a peer may be a whole step behind
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Wait until flags[i] >= value for i in [0, count). Returns false (status <- kErrWaitPeer) on expiry.
+__device__ __forceinline__ bool wait_flags_bounded(const int* flags, int count, int value, int* status) {
+  const unsigned long long t0 = globaltimer_ns();
+  for (int r = 0; r < count; ++r) {
+    unsigned spins = 0;
+    while (ld_acquire_sys(flags + r) < value) {
+      if ((++spins & 0xff) == 0) {
+        if (globaltimer_ns() - t0 > kPeerWaitBudgetNs) {
+          if (status != nullptr) atomicCAS(status, 0, kErrWaitPeer);
+          return false;
+        }
+        __nanosleep(200);
+      }
+    }
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -36,12 +36,12 @@ from .params import ParamStore, init_weights
 
 class GPT:
     def __init__(self, cfg: Config, device="cpu", dtype: torch.dtype = torch.bfloat16, seed: int = 0,
-                 init: bool = True, head_chunk_rows: int = 8192):
+                 init: bool = True, head_chunk_rows: int = 8192, allocator=None):
         cfg.validate()
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype
-        self.params = ParamStore(cfg, self.device, dtype)
+        self.params = ParamStore(cfg, self.device, dtype, allocator=allocator)
         if init:
             init_weights(self.params, seed)
         self.head_chunk_rows = head_chunk_rows

@@ -79,7 +79,9 @@ class ParamStore:
     """Flat buffers plus named views. `value` aliases `master` when the compute dtype is fp32."""
 
     def __init__(self, cfg: Config, device, dtype: torch.dtype = torch.bfloat16,
-                 grad_dtype: torch.dtype = torch.float32):
+                 grad_dtype: torch.dtype = torch.float32, allocator=None):
+        """`allocator(numel, dtype) -> zeroed 1-D tensor` lets the data-parallel engine place the gradient
+        and the compute copy in symmetric (peer-mapped) memory."""
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype
@@ -87,9 +89,9 @@ class ParamStore:
         last = self.specs[-1]
         self.total = last.offset + ((last.count + ALIGN - 1) // ALIGN) * ALIGN
         self.master = torch.zeros(self.total, dtype=torch.float32, device=self.device)
-        self.value = self.master if dtype == torch.float32 else torch.zeros(
-            self.total, dtype=dtype, device=self.device)
-        self.grad = torch.zeros(self.total, dtype=grad_dtype, device=self.device)
+        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
+        self.value = self.master if dtype == torch.float32 else alloc(self.total, dtype)
+        self.grad = alloc(self.total, grad_dtype)
         self.by_name: Dict[str, ParamSpec] = {s.name: s for s in self.specs}
         self._v: Dict[str, torch.Tensor] = {}
         self._g: Dict[str, torch.Tensor] = {}

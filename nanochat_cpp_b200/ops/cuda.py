@@ -76,22 +76,38 @@ def check_status(device=None) -> None:
 # ---------------------------------------------------------------------------
 # GEMMs
 # ---------------------------------------------------------------------------
+# Data-parallel hook: (flag tensor, value) that the next forward GEMM must wait for inside the kernel before
+# its TMA producer touches the weight operand (owners publish the flags after pushing updated weights).
+_pending_weight_wait = None
+
+
+def set_weight_wait(flags, value) -> None:
+    global _pending_weight_wait
+    _pending_weight_wait = (flags, int(value))
+
+
 def gemm(a, b, *, a_mn=False, b_mn=False, epi=EPI_BF16, out=None, r=None, out2=None, alpha=1.0, beta=0.0,
-         split_k=True):
+         split_k=True, wait_flags=None, wait_value=0, gather_src=0, gather_counter=None, gather_base=0):
     """out = epilogue(A x B^T). See csrc/cuda/bindings.cpp for operand orders."""
     m = a.shape[-1] if a_mn else a.shape[-2]
     n = b.shape[-1] if b_mn else b.shape[-2]
     if out is None:
         shape = (*a.shape[:-2], m, n)
         out = torch.empty(shape, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
-    _C.gemm(a, b, out, a_mn, b_mn, epi, r, out2, alpha, beta, split_k)
+    _C.gemm(a, b, out, a_mn, b_mn, epi, r, out2, alpha, beta, split_k, wait_flags, wait_value, gather_src,
+            gather_counter, gather_base)
     return out
 
 
 def linear_fwd(x, w, *, out=None, residual=None):
+    global _pending_weight_wait
+    kw = {}
+    if _pending_weight_wait is not None:
+        kw = dict(wait_flags=_pending_weight_wait[0], wait_value=_pending_weight_wait[1])
+        _pending_weight_wait = None
     if residual is not None:
-        return gemm(x, w, epi=EPI_BF16_RES, r=residual, out=out, alpha=1.0, beta=1.0)
-    return gemm(x, w, out=out)
+        return gemm(x, w, epi=EPI_BF16_RES, r=residual, out=out, alpha=1.0, beta=1.0, **kw)
+    return gemm(x, w, out=out, **kw)
 
 
 def linear_relu2_fwd(x, w):

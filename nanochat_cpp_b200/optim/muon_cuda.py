@@ -58,7 +58,9 @@ class MuonGroupState:
 def muon_group_step(grads: List[torch.Tensor], masters: List[torch.Tensor], values: List[Optional[torch.Tensor]],
                     buf1: List[torch.Tensor], buf2: List[torch.Tensor], scratch: MuonGroupState, *, lr: float,
                     momentum: float, beta2: float, weight_decay: float, ns_steps: int,
-                    grad_scale: Optional[torch.Tensor]) -> None:
+                    grad_scale: Optional[torch.Tensor], apply_fn=None) -> None:
+    """`apply_fn(p, master, X_p, scale_p, line_scale_p, lines_are_rows, lr, wd)` replaces the final update
+    launch (the data-parallel engine uses it to push the new parameters to every rank)."""
     from ..ops import cuda as K
     C = K._C
     P = len(grads)
@@ -95,4 +97,7 @@ def muon_group_step(grads: List[torch.Tensor], masters: List[torch.Tensor], valu
     line_scale = (step_size * (v_norm / denom)).contiguous()
     scale = scale.contiguous()
     for p in range(P):
-        C.muon_apply(masters[p], values[p], X[p], scale[p], line_scale[p], reduce_cols, lr, weight_decay)
+        if apply_fn is not None:
+            apply_fn(p, masters[p], X[p], scale[p], line_scale[p], reduce_cols, lr, weight_decay)
+        else:
+            C.muon_apply(masters[p], values[p], X[p], scale[p], line_scale[p], reduce_cols, lr, weight_decay)

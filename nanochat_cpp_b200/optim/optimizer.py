@@ -115,6 +115,7 @@ class Optimizer:
                     self.state[s.name] = dict(buf1=torch.zeros(s.shape, dtype=torch.float32, device=dev),
                                               buf2=torch.zeros(lines, dtype=torch.float32, device=dev))
         self._muon_scratch = {}
+        self.pusher = None   # data-parallel engine: pushes updated parameters to every rank (parallel.fused)
         self.lr_multiplier_override: float = -1.0
         self.last_grad_norm: Optional[torch.Tensor] = None
         self.step_count = 0
@@ -156,10 +157,17 @@ class Optimizer:
                 if b <= a:
                     continue
                 lo, hi = s.offset + a, s.offset + b
+                if self.pusher is not None:
+                    self.pusher.adamw_push(st.master[lo:hi], lo, st.grad[lo:hi], stt["m"].view(-1), stt["v"].view(-1),
+                                           lr=g.lr * lrm, beta1=g.beta1, beta2=g.beta2, eps=g.eps,
+                                           weight_decay=g.weight_decay, step=step, grad_scale=clip_scale)
+                    continue
                 ops.adamw_update(st.master[lo:hi], None if st.value is st.master else st.value[lo:hi],
                                  st.grad[lo:hi], stt["m"].view(-1), stt["v"].view(-1), lr=g.lr * lrm,
                                  beta1=g.beta1, beta2=g.beta2, eps=g.eps, weight_decay=g.weight_decay, step=step,
                                  grad_scale=clip_scale)
+        if self.pusher is not None:
+            self.pusher.after_adamw(step)
         momentum = self.scheduler.muon_momentum(step)
         wd = self.scheduler.weight_decay(step)
         use_kernels = st.device.type == "cuda" and ops.get_mode() == "kernels" and st.value is not st.master
@@ -176,7 +184,8 @@ class Optimizer:
                                 [st.v(s.name) for s in mine], [self.state[s.name]["buf1"] for s in mine],
                                 [self.state[s.name]["buf2"] for s in mine], self._muon_scratch[key],
                                 lr=g.lr * lrm, momentum=momentum, beta2=cfg.muon_beta2, weight_decay=wd,
-                                ns_steps=cfg.muon_ns_steps, grad_scale=clip_scale)
+                                ns_steps=cfg.muon_ns_steps, grad_scale=clip_scale,
+                                apply_fn=None if self.pusher is None else self.pusher.make_muon_apply(mine))
                 continue
             grads = torch.stack([st.g(s.name) for s in mine])
             master = torch.stack([st.m(s.name) for s in mine])
@@ -189,6 +198,10 @@ class Optimizer:
                 st.m(s.name).copy_(master[k])
                 if st.value is not st.master:
                     st.v(s.name).copy_(master[k])
+                if self.pusher is not None:
+                    self.pusher.push_span(s.offset, s.count)
                 self.state[s.name]["buf1"].copy_(buf1[k])
                 self.state[s.name]["buf2"].copy_(buf2[k])
+        if self.pusher is not None:
+            self.pusher.after_muon(step)
         self.step_count = step

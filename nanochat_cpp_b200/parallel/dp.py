@@ -51,10 +51,16 @@ def adamw_slice(spec: ParamSpec, rank: int, world: int) -> Tuple[int, int]:
 
 
 class DataParallel:
-    def __init__(self, rank: int, world_size: int, transport: str = "nccl", group=None):
+    def __init__(self, rank: int, world_size: int, transport: str = "nccl", group=None, device=None):
         self.rank, self.world_size = rank, world_size
         self.transport = transport
         self.group = group
+        self.fused = None
+        if transport == "fused":
+            from .fused import FusedTransport
+            self.fused = FusedTransport(rank, world_size, device, group)
+        elif transport != "nccl":
+            raise ValueError(f"unknown data-parallel transport {transport!r}")
         self.model = None
         self.optimizer = None
         self.owners: Dict[str, int] = {}
@@ -73,15 +79,46 @@ class DataParallel:
         """True for parameters this rank updates (its Muon matrices, and its slice of every AdamW tensor)."""
         return self.owners[spec.name] in (-1, self.rank)
 
+    def allocator(self):
+        """Allocator for the parameter store (symmetric memory for the fused transport, else None)."""
+        return None if self.fused is None else self.fused.allocator
+
     def attach(self, model, optimizer) -> None:
         self.model, self.optimizer = model, optimizer
         store = model.params
         if self.world_size > 1:  # every rank must start from identical weights
             dist.broadcast(store.master, src=0, group=self.group)
             store.sync_compute()
+        if self.fused is not None:
+            from .fused import Pusher
+            f = self.fused
+            f.build_buckets(store, self.owners, self.slices)
+            optimizer.pusher = Pusher(f)
+            L = store.cfg.num_layers
+            model.on_layer_grads_ready = lambda i: self._bucket_ready(i)
+            model.on_head_grads_ready = lambda: self._bucket_ready(L)
+            model.on_embed_grads_ready = lambda: self._bucket_ready(L + 1)
+            self._step = 0
+            torch.cuda.synchronize()
+            if self.world_size > 1:
+                dist.barrier(group=self.group)
 
-    def begin_step(self) -> None:
-        pass
+    def _bucket_ready(self, b: int) -> None:
+        if self._last_micro:
+            self.fused.reduce_bucket(b, self._step)
+
+    def begin_step(self, step: int = 0) -> None:
+        if self.fused is None:
+            return
+        self._step = step
+        f = self.fused
+        if step > 1:
+            # parameters updated by the previous step: embeddings and scalars are needed first (tiny wait kernel);
+            # the matrices are waited for inside the first GEMM that reads a weight
+            f.wait(f.slot_adamw, step - 1)
+            from ..ops import cuda as K
+            K.set_weight_wait(f.flag_view(f.slot_muon), step - 1)
+        f.begin_reduction()
 
     def set_last_micro(self, last: bool) -> None:
         self._last_micro = last
@@ -90,6 +127,11 @@ class DataParallel:
     def finish_step(self, step: int) -> None:
         store = self.model.params
         opt = self.optimizer
+        if self.fused is not None:
+            norm, clip = self.fused.global_grad_norm(opt.config.clip)
+            opt.last_grad_norm = norm
+            opt.step(step, clip_scale=clip)
+            return
         if self.world_size > 1:
             dist.all_reduce(store.grad, op=dist.ReduceOp.SUM, group=self.group)
         from .. import ops

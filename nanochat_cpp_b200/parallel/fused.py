@@ -1,0 +1,185 @@
+"""Fused data-parallel transport: reduce-scatter by peer loads + owner update that pushes parameters.
+
+One step, per rank (see csrc/cuda/comm.cu for the kernels):
+
+  backward ──► layer i done ──► signal(slot i)            (compute stream, after the bucket's last wgrad)
+                              └► reduce_pull(bucket i)     (comm stream: waits for slot i of ALL ranks, then
+                                                            loads this rank's segments from every peer,
+                                                            sums, scales, stores locally, adds to sumsq)
+  all buckets reduced ──► all-reduce of one double (grad norm) ──► clip scale
+  AdamW slices: update + push bf16 to every rank ──► signal(slot A)
+  Muon matrices: Newton-Schulz, update + push bf16 to every rank ──► signal(slot M)
+  next forward: embeddings wait for slot A (tiny kernel); the first QKV GEMM's TMA producer waits for slot M
+  inside the GEMM kernel (no all-gather collective, no barrier).
+
+The buffers that peers touch (flat fp32 gradient, flat bf16 parameters, flag words) live in symmetric
+memory obtained from `torch.distributed._symmetric_memory` (plumbing only: allocation + address exchange).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+class SymmetricBuffer:
+    """A tensor that exists at the same size on every rank, with the peer addresses of all copies."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device, group):
+        import torch.distributed._symmetric_memory as symm
+        self.tensor = symm.empty(numel, dtype=dtype, device=device)
+        self.tensor.zero_()
+        self.handle = symm.rendezvous(self.tensor, group)
+        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+
+
+class FusedTransport:
+    def __init__(self, rank: int, world: int, device, group=None):
+        self.rank, self.world = rank, world
+        self.device = torch.device(device)
+        self.group = group if group is not None else dist.group.WORLD
+        self.buffers: List[SymmetricBuffer] = []
+        self.grad: Optional[SymmetricBuffer] = None
+        self.value: Optional[SymmetricBuffer] = None
+        self.flags: Optional[SymmetricBuffer] = None
+        self.comm_stream = torch.cuda.Stream(device=self.device)
+        self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.buckets: List[dict] = []
+        self.num_slots = 0
+        self.reduce_ctas = 32
+
+    # ------------------------------------------------------------------ allocation
+    def allocator(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        buf = SymmetricBuffer(numel, dtype, self.device, self.group)
+        self.buffers.append(buf)
+        if dtype == torch.float32 and self.grad is None:
+            self.grad = buf
+        elif dtype == torch.bfloat16 and self.value is None:
+            self.value = buf
+        return buf.tensor
+
+    # ------------------------------------------------------------------ buckets
+    def build_buckets(self, store, owners: Dict[str, int], slices: Dict[str, Tuple[int, int]]) -> None:
+        """Bucket b < L: everything whose gradient is final when layer b's backward is done (its matrices and
+        its value embedding); bucket L: LM head; bucket L+1: token embedding and the scalars."""
+        cfg = store.cfg
+        L = cfg.num_layers
+        per: List[List[Tuple[int, int]]] = [[] for _ in range(L + 2)]
+        for s in store.specs:
+            if s.kind == "lm_head":
+                b = L
+            elif s.kind in ("matrix", "value_embed"):
+                b = s.layer
+            else:
+                b = L + 1
+            o = owners[s.name]
+            if o == self.rank:
+                seg = (s.offset, (s.count + 3) // 4 * 4)
+            elif o == -1:
+                a, e = slices[s.name]
+                if e <= a:
+                    continue
+                seg = (s.offset + a, (e - a + 3) // 4 * 4)
+            else:
+                continue
+            per[b].append(seg)
+        self.buckets = []
+        for b, segs in enumerate(per):
+            segs.sort()
+            total = sum(c for _, c in segs)
+            t = torch.tensor(segs if segs else [[0, 0]], dtype=torch.int64, device=self.device).reshape(-1, 2)
+            self.buckets.append(dict(segs=t, total=total, n=len(segs)))
+        self.slot_adamw = L + 2
+        self.slot_muon = L + 3
+        self.num_slots = L + 4
+        self.flags = SymmetricBuffer(self.num_slots * self.world, torch.int32, self.device, self.group)
+
+    # ------------------------------------------------------------------ step pieces
+    def signal(self, slot: int, value: int) -> None:
+        from ..ops import cuda as K
+        K._C.comm_signal(self.flags.ptrs, self.rank, slot, value)
+
+    def reduce_bucket(self, b: int, step: int, scale: float = 1.0) -> None:
+        """Publish "bucket b is final on this rank" on the current stream and enqueue this rank's share of the
+        reduction on the communication stream."""
+        from ..ops import cuda as K
+        self.signal(b, step)
+        bk = self.buckets[b]
+        if bk["total"] == 0:
+            return
+        with torch.cuda.stream(self.comm_stream):
+            K._C.comm_reduce_pull(self.grad.ptrs, self.rank, bk["segs"], bk["total"], scale, self.flags.tensor, b,
+                                  step, self.sumsq, K._C.status_tensor(self.device.index), self.reduce_ctas)
+
+    def begin_reduction(self) -> None:
+        with torch.cuda.stream(self.comm_stream):
+            self.sumsq.zero_()
+        # the reduction kernels must not start before this step's zero_() of sumsq, nor before earlier work on
+        # the compute stream that they are ordered after by flags only
+        self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+
+    def global_grad_norm(self, clip: float):
+        """Joins the communication stream, all-reduces the squared norm and returns (norm, clip_scale)."""
+        torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        total = self.sumsq.clone()
+        if self.world > 1:
+            dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group)
+        norm = total.sqrt().float()[0]
+        if clip and clip > 0:
+            scale = torch.where(norm > clip, clip / norm.clamp_min(1e-30), torch.ones_like(norm))
+        else:
+            scale = torch.ones_like(norm)
+        return norm, scale
+
+    def wait(self, slot: int, value: int) -> None:
+        from ..ops import cuda as K
+        K._C.comm_wait(self.flags.tensor, self.world, slot, value, K._C.status_tensor(self.device.index))
+
+    def flag_view(self, slot: int) -> torch.Tensor:
+        return self.flags.tensor[slot * self.world:(slot + 1) * self.world]
+
+    # ------------------------------------------------------------------ pushing updates
+    def adamw_push(self, master, offset: int, grad, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale):
+        from ..ops import cuda as K
+        gs = grad_scale.reshape(1) if isinstance(grad_scale, torch.Tensor) else None
+        K._C.comm_adamw_push(master, self.value.ptrs, offset, grad, m, v, lr, beta1, beta2, eps, weight_decay, step, gs)
+
+    def muon_apply_push(self, master, offset: int, xb, scale0, line_scale, lines_are_rows: bool, lr: float, wd: float):
+        from ..ops import cuda as K
+        K._C.comm_muon_apply_push(master, self.value.ptrs, offset, xb, scale0, line_scale, lines_are_rows, lr, wd)
+
+    def push_span(self, offset: int, count: int) -> None:
+        """Copy a (small) span of this rank's parameter buffer to every peer with ordinary peer copies."""
+        local = self.value.tensor[offset:offset + count]
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            peer = self.value.handle.get_buffer(r, (self.value.tensor.numel(),), self.value.tensor.dtype)
+            peer[offset:offset + count].copy_(local)
+
+
+class Pusher:
+    """Adapter handed to the Optimizer: owner updates write straight into every rank's parameters."""
+
+    def __init__(self, transport: FusedTransport):
+        self.t = transport
+
+    def adamw_push(self, master, offset, grad, m, v, **kw):
+        self.t.adamw_push(master, offset, grad, m, v, **kw)
+
+    def after_adamw(self, step: int) -> None:
+        self.t.signal(self.t.slot_adamw, step)
+
+    def make_muon_apply(self, specs):
+        t = self.t
+
+        def apply(p, master, xb, scale0, line_scale, lines_are_rows, lr, wd):
+            t.muon_apply_push(master, specs[p].offset, xb, scale0, line_scale, lines_are_rows, lr, wd)
+        return apply
+
+    def push_span(self, offset: int, count: int) -> None:
+        self.t.push_span(offset, count)
+
+    def after_muon(self, step: int) -> None:
+        self.t.signal(self.t.slot_muon, step)

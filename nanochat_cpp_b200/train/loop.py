@@ -46,7 +46,8 @@ class Trainer:
         self.cfg, self.tc = cfg, tc
         self.device = torch.device(device)
         dtype = torch.bfloat16 if tc.dtype == "bf16" else torch.float32
-        self.model = model or GPT(cfg, self.device, dtype, seed=tc.seed, head_chunk_rows=tc.head_chunk_rows)
+        self.model = model or GPT(cfg, self.device, dtype, seed=tc.seed, head_chunk_rows=tc.head_chunk_rows,
+                                  allocator=None if dp is None else dp.allocator())
         if tc.sched.num_iterations == 0:
             tc.sched.num_iterations = tc.num_iterations
         self.dp = dp
@@ -69,7 +70,7 @@ class Trainer:
         accum = len(micro_batches)
         scale = 1.0 / (accum * self.world)
         if self.dp is not None:
-            self.dp.begin_step()
+            self.dp.begin_step(self.step_count + 1)
         m.zero_grad()
         total = None
         for k, (tokens, targets) in enumerate(micro_batches):

@@ -1,0 +1,57 @@
+"""Data parallelism on real GPUs: the fused peer-memory transport must give the same parameters as the NCCL
+baseline (and both equal single-rank training on the global batch up to bf16 noise). Needs >= 2 GPUs."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, transport, out):
+    import torch.distributed as dist
+    from nanochat_cpp_b200.config import Config
+    from nanochat_cpp_b200.parallel.dp import DataParallel
+    from nanochat_cpp_b200.train import TrainConfig, Trainer
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    cfg = Config(num_layers=4, num_heads=4, num_kv_heads=2, hidden_dim=512, seq_len=256, vocab_size=1000,
+                 padded_vocab_size=1024, window_pattern="SSSL", short_window_override=128)
+    tc = TrainConfig(batch=2, grad_accum=2, num_iterations=6, seed=9)
+    tr = Trainer(cfg, tc, device=dev, dp=DataParallel(rank, world, transport=transport, device=dev))
+    g = torch.Generator().manual_seed(3)
+    data = torch.randint(0, 200, (6, world, 2, 2, cfg.seq_len + 1), generator=g)
+    for step in range(6):
+        mb = [(data[step, rank, a, :, :-1].to(dev), data[step, rank, a, :, 1:].to(dev)) for a in range(2)]
+        loss = tr.train_step(mb)
+    torch.cuda.synchronize()
+    from nanochat_cpp_b200.ops import cuda as K
+    K.check_status()
+    if rank == 0:
+        torch.save({"value": tr.model.params.value.float().cpu(), "loss": float(loss)}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_transport_matches_nccl(tmp_path):
+    import torch.multiprocessing as mp
+    outs = {}
+    for transport in ("nccl", "fused"):
+        out = str(tmp_path / f"{transport}.pt")
+        mp.spawn(_worker, args=(2, _free_port(), transport, out), nprocs=2, join=True)
+        outs[transport] = torch.load(out)
+    a, b = outs["nccl"]["value"], outs["fused"]["value"]
+    assert abs(outs["nccl"]["loss"] - outs["fused"]["loss"]) < 5e-2
+    rel = float((a - b).norm() / (a.norm() + 1e-12))
+    assert rel < 2e-2, rel
