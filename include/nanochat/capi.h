@@ -1,0 +1,228 @@
+/* Flat C ABI of the host runtime and the CPU engine (libnanochat_core.so).
+ *
+ * Names, struct layouts and conventions follow the reference's include/nanochat/capi.h so that a client
+ * written against it links unchanged: status code + thread-local error string, opaque handles, caller-owned
+ * output buffers. Functions that exist only here are prefixed `ncb_`. */
+#ifndef NANOCHAT_CAPI_H_
+#define NANOCHAT_CAPI_H_
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { NANOCHAT_STATUS_OK = 0, NANOCHAT_STATUS_ERROR = 1 } nanochat_status;
+
+typedef struct nanochat_model nanochat_model;
+typedef struct nanochat_optim nanochat_optim;
+typedef struct nanochat_loader nanochat_loader;
+typedef struct nanochat_tokenizer nanochat_tokenizer;
+typedef struct nanochat_checkpoint nanochat_checkpoint;
+
+typedef struct {
+  int num_layers, num_heads, num_kv_heads, hidden_dim, seq_len, vocab_size, padded_vocab_size;
+  float rope_base;
+  const char* window_pattern;
+  int value_embedding;
+} nanochat_config;
+
+typedef struct {
+  int64_t total, transformer_matrices, lm_head, embeddings, scalars;
+  double flops_per_token;
+} nanochat_params;
+
+typedef struct {
+  int device_index, compute_major, compute_minor;
+  int64_t total_memory_bytes;
+  const char* device_name;
+} nanochat_device;
+
+typedef struct {
+  const char* name;
+  void* value;
+  void* grad;
+  int64_t count;
+  int rows, cols;
+} nanochat_param;
+
+typedef struct {
+  int position;
+  const int* ids;
+  int count;
+} nanochat_focus;
+
+typedef struct {
+  const float* nll;
+  const int* argmax;
+  const float* focus_logits;
+} nanochat_score_result;
+
+typedef struct {
+  int num_samples, max_tokens;
+  float temperature;
+  int top_k;
+  uint64_t seed;
+  int stop_id, bos_id;
+  const int* stop_ids;
+} nanochat_generate_params;
+
+typedef struct {
+  int count;
+  const int* tokens;
+  const uint8_t* mask;
+  const int* lengths;
+  const int* offsets;
+} nanochat_sequences;
+
+typedef struct {
+  int num_prompts, prompt_len;
+  const int* row_stops;
+  nanochat_generate_params params;
+} nanochat_generate_multi_params;
+
+typedef struct {
+  float unembedding_lr, embedding_lr, matrix_lr, scalar_lr, weight_decay;
+  int muon_ns_steps;
+  float muon_beta2, adam_eps, clip;
+  int num_iterations, warmup_steps;
+  float warmdown_ratio, final_lr_frac, weight_decay_base;
+  float muon_momentum_warmup_steps, muon_momentum_start, muon_momentum_peak, muon_momentum_final;
+} nanochat_optim_config;
+
+size_t nanochat_optim_config_size(void);
+nanochat_status nanochat_init(void);
+const char* nanochat_last_error(void);
+const char* nanochat_version(void);
+const char* nanochat_backend(void);
+int nanochat_compute_type_size(void);
+void nanochat_device_info(nanochat_device* out);
+int nanochat_device_count(void);
+int nanochat_device_at(int ordinal, nanochat_device* out);
+
+nanochat_status nanochat_params_get(const nanochat_config* config, nanochat_params* out);
+nanochat_status nanochat_optim_config_preset(const char* name, nanochat_optim_config* out);
+
+/* ---- CPU engine ---------------------------------------------------------------------------------- */
+nanochat_model* nanochat_model_create(const nanochat_config* config, uint64_t seed);
+void nanochat_model_free(nanochat_model* model);
+float nanochat_forward_loss(nanochat_model* model, const int* tokens, const int* targets, int batch, int seq);
+void nanochat_backward(nanochat_model* model);
+void nanochat_backward_weighted(nanochat_model* model, const float* row_weights, float scale);
+void nanochat_backward_accumulate(nanochat_model* model, float scale);
+float nanochat_train_step(nanochat_model* model, nanochat_optim* optimizer, const int* tokens, const int* targets,
+                          int batch, int seq);
+float nanochat_rl_step(nanochat_model* model, nanochat_optim* optimizer, const int* tokens, const int* targets,
+                       const float* advantages, int batch, int seq, int num_passes, int examples_per_rank, int step);
+void nanochat_zero_grad(nanochat_model* model);
+int nanochat_param_count(nanochat_model* model);
+int nanochat_param_info(nanochat_model* model, int index, nanochat_param* out);
+int64_t nanochat_param_read(nanochat_model* model, int index, int grad, int64_t offset, int64_t count, void* data);
+int64_t nanochat_param_write(nanochat_model* model, int index, int grad, int64_t offset, int64_t count,
+                             const void* data);
+void nanochat_save(nanochat_model* model, const char* path);
+void nanochat_load(nanochat_model* model, const char* path);
+nanochat_optim* nanochat_optim_create(nanochat_model* model, const nanochat_optim_config* config);
+void nanochat_optim_step(nanochat_optim* optimizer, int step);
+float nanochat_optim_grad_norm(nanochat_optim* optimizer);
+void nanochat_optim_free(nanochat_optim* optimizer);
+void nanochat_score_batch(nanochat_model* model, const int* tokens, int batch, int seq, const int* lengths,
+                          const nanochat_focus* focus, nanochat_score_result* out);
+void nanochat_generate(nanochat_model* model, const int* prompt, int length, const nanochat_generate_params* params,
+                       nanochat_sequences* out);
+void nanochat_generate_multi(nanochat_model* model, const int* prompts, const nanochat_generate_multi_params* params,
+                             nanochat_sequences* out);
+float nanochat_eval_bpb(nanochat_model* model, nanochat_loader* loader, int steps);
+
+/* ---- checkpoints ---------------------------------------------------------------------------------- */
+typedef struct nanochat_record {
+  const char* name;
+  int32_t dtype;
+  int32_t ndim;
+  const int64_t* dims;
+  const void* data;
+  int64_t bytes;
+  int64_t attribute_count;
+  const struct nanochat_record* attributes;
+} nanochat_record;
+
+typedef enum { NANOCHAT_STAGE_BASE = 0, NANOCHAT_STAGE_SFT = 1, NANOCHAT_STAGE_RL = 2 } nanochat_stage;
+typedef enum { NANOCHAT_PRECISION_FP32 = 0, NANOCHAT_PRECISION_BF16 = 1, NANOCHAT_PRECISION_FP8 = 2 } nanochat_precision;
+
+typedef struct {
+  int32_t schema;
+  int32_t stage;
+  int64_t step;
+  int64_t world_size;
+  int32_t precision;
+  const char* config_json;
+  const char* tokenizer_id;
+  const char* git_revision;
+  const char* created_utc;
+  const char* const* notes;
+  int32_t note_count;
+} nanochat_checkpoint_metadata;
+
+nanochat_status nanochat_checkpoint_dtype(int32_t index, const char** name, int32_t* code, int32_t* size);
+nanochat_status nanochat_checkpoint_write(const char* path, const nanochat_record* records, int64_t record_count,
+                                          const nanochat_record* optimizer, int64_t optimizer_count);
+nanochat_status nanochat_checkpoint_read(const char* path, nanochat_checkpoint** owner,
+                                         const nanochat_record** records, int64_t* record_count,
+                                         const nanochat_record** optimizer, int64_t* optimizer_count);
+void nanochat_checkpoint_free(nanochat_checkpoint* owner);
+nanochat_status nanochat_checkpoint_metadata_read(const char* path, nanochat_checkpoint** owner,
+                                                  nanochat_checkpoint_metadata* out);
+int32_t nanochat_checkpoint_metadata_stage(const nanochat_checkpoint_metadata* meta);
+int64_t nanochat_checkpoint_metadata_step(const nanochat_checkpoint_metadata* meta);
+int64_t nanochat_checkpoint_metadata_world_size(const nanochat_checkpoint_metadata* meta);
+const char* nanochat_checkpoint_metadata_config_json(const nanochat_checkpoint_metadata* meta);
+/* Same as nanochat_checkpoint_write, with the metadata block of the file given explicitly (JSON config as
+ * produced by nanochat_checkpoint_metadata_config_json). */
+nanochat_status ncb_checkpoint_write_meta(const char* path, const nanochat_record* records, int64_t record_count,
+                                          const nanochat_record* optimizer, int64_t optimizer_count,
+                                          const nanochat_config* config, int32_t stage, int64_t step,
+                                          int64_t world_size, int32_t precision, const char* tokenizer_id,
+                                          const char* notes);
+
+/* ---- data ------------------------------------------------------------------------------------------ */
+nanochat_loader* nanochat_loader_create(const char** parquet, int count, const char* text_column,
+                                        nanochat_tokenizer* tokenizer, int batch, int seq, uint64_t seed,
+                                        int tokenizer_threads, size_t document_buffer);
+int nanochat_loader_next(nanochat_loader* loader, int* tokens, int* targets);
+const uint8_t* nanochat_loader_token_bytes(nanochat_loader* loader, int* vocab);
+void nanochat_loader_free(nanochat_loader* loader);
+/* Loaders over other sources: token documents given directly (offsets has count + 1 entries), a text file with
+ * one document per line, or a synthetic Zipf(s) stream. rank/world select every world-th document. */
+nanochat_loader* ncb_loader_from_documents(const int* tokens, const int64_t* offsets, int64_t count, int batch,
+                                           int seq, size_t document_buffer, int rank, int world);
+nanochat_loader* ncb_loader_from_text(const char* path, nanochat_tokenizer* tokenizer, int batch, int seq,
+                                      size_t document_buffer, int rank, int world);
+nanochat_loader* ncb_loader_zipf(int vocab, int doc_len, double s, uint64_t seed, int batch, int seq,
+                                 size_t document_buffer);
+nanochat_status ncb_loader_save_cursor(nanochat_loader* loader, const char* path);
+nanochat_status ncb_loader_load_cursor(nanochat_loader* loader, const char* path);
+uint64_t ncb_loader_epoch(nanochat_loader* loader);
+
+nanochat_tokenizer* nanochat_tokenizer_load(const char* path);
+int nanochat_encode(nanochat_tokenizer* tokenizer, const char* text, int* out, int capacity);
+int nanochat_decode(nanochat_tokenizer* tokenizer, const int* ids, int count, char* out, int capacity);
+void nanochat_tokenizer_free(nanochat_tokenizer* tokenizer);
+int ncb_tokenizer_vocab_size(nanochat_tokenizer* tokenizer);
+int ncb_tokenizer_special_id(nanochat_tokenizer* tokenizer, const char* name);
+int ncb_encode_n(nanochat_tokenizer* tokenizer, const char* text, int64_t length, int prepend, int append, int* out,
+                 int capacity);
+nanochat_status ncb_tokenizer_save(nanochat_tokenizer* tokenizer, const char* path);
+/* Trains a tokenizer on a text file (one document per line) or one parquet column. */
+nanochat_tokenizer* ncb_tokenizer_train(const char* text_path, const char* parquet_path, const char* text_column,
+                                        int vocab_size, int64_t doc_cap, int64_t max_chars);
+/* Splits text with the fixed pattern; writes piece end offsets (bytes). Returns the number of pieces. */
+int ncb_split_pattern(const char* text, int64_t length, int64_t* ends, int capacity);
+/* Reads one string column of a parquet file; returns the row count and fills offsets/bytes when given. */
+int64_t ncb_parquet_read(const char* path, const char* column, char* bytes, int64_t byte_capacity, int64_t* offsets,
+                         int64_t offset_capacity, int64_t* total_bytes);
+int ncb_sample_token(const float* logits, int vocab, float temperature, int top_k, uint64_t seed, uint64_t row,
+                     uint64_t step);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NANOCHAT_CAPI_H_ */

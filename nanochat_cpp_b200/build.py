@@ -74,6 +74,22 @@ def _compile_many(jobs) -> List[str]:
     return objs
 
 
+def _prune(keep: List[str], prefix: str) -> None:
+    """Drop cached objects (and their logs) of sources that have since changed."""
+    keep_set = set(keep)
+    for path in glob.glob(os.path.join(BUILD_DIR, "*.o")):
+        base = os.path.basename(path)
+        is_host = base.startswith("host_")
+        if (prefix == "host_") != is_host:
+            continue
+        if path not in keep_set:
+            for victim in (path, path + ".log"):
+                try:
+                    os.remove(victim)
+                except OSError:
+                    pass
+
+
 def build_extension(verbose: bool = False) -> str:
     """Compile every CUDA source for sm_100a and link the PyTorch extension."""
     import torch
@@ -104,6 +120,7 @@ def build_extension(verbose: bool = False) -> str:
         obj = os.path.join(BUILD_DIR, os.path.basename(src) + "." + tag + ".o")
         jobs.append((src, obj, ["g++"] + CXX_FLAGS + defs + inc + ["-c", src, "-o", obj]))
     objs = _compile_many(jobs)
+    _prune(objs, prefix="")
     stamp = os.path.join(BUILD_DIR, "ext.stamp")
     key = _hash(objs, "link")
     if os.path.exists(EXT_PATH) and os.path.exists(stamp) and open(stamp).read() == key:
@@ -136,6 +153,7 @@ def build_core(verbose: bool = False) -> str:
         obj = os.path.join(BUILD_DIR, "host_" + os.path.basename(src) + "." + tag + ".o")
         jobs.append((src, obj, ["g++"] + HOST_FLAGS + inc + ["-c", src, "-o", obj]))
     objs = _compile_many(jobs)
+    _prune(objs, prefix="host_")
     stamp = os.path.join(BUILD_DIR, "core.stamp")
     key = _hash(objs, "link-core")
     if os.path.exists(CORE_PATH) and os.path.exists(stamp) and open(stamp).read() == key:

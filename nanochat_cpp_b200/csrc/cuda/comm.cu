@@ -37,35 +37,72 @@ __global__ void wait_kernel(const int* flags, int world, int slot, int value, in
   if (threadIdx.x == 0) wait_flags(flags, world, slot, value, status);
 }
 
+constexpr int kReduceUnroll = 4;
+constexpr int kMaxSegs = 64;
+
 __global__ void __launch_bounds__(256) reduce_pull_kernel(PeerPtrs grads, int world, int my_rank,
                                                           const Segment* __restrict__ segs, int nsegs,
                                                           long long total, float scale, const int* flags, int slot,
                                                           int value, double* sumsq, int* status) {
   __shared__ int ok_sh;
   __shared__ double red[8];
-  if (threadIdx.x == 0) ok_sh = wait_flags(flags, world, slot, value, status) ? 1 : 0;
+  __shared__ long long seg_first[kMaxSegs + 1];  // first vector index of every segment in the concatenated space
+  __shared__ long long seg_off[kMaxSegs];
+  if (threadIdx.x == 0) {
+    ok_sh = wait_flags(flags, world, slot, value, status) ? 1 : 0;
+    long long acc = 0;
+    for (int i = 0; i < nsegs; ++i) {
+      seg_first[i] = acc;
+      seg_off[i] = segs[i].offset;
+      acc += segs[i].count / 4;
+    }
+    seg_first[nsegs] = acc;
+  }
   __syncthreads();
   if (!ok_sh) return;
   double acc = 0.0;
   const long long nvec = total / 4;
-  int seg = 0;
-  long long seg_begin = 0;  // first vector index of `seg` in the concatenated space
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    while (seg < nsegs - 1 && i >= seg_begin + segs[seg].count / 4) {
-      seg_begin += segs[seg].count / 4;
-      ++seg;
+  const long long threads = static_cast<long long>(gridDim.x) * blockDim.x;
+  float* mine = static_cast<float*>(grads.p[my_rank]);
+  // kReduceUnroll independent 16-byte peer loads per rank are in flight per thread: NVLink latency is hidden by
+  // memory-level parallelism, not by occupancy
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nvec;
+       i0 += threads * kReduceUnroll) {
+    long long e[kReduceUnroll];
+    float4 sum[kReduceUnroll];
+#pragma unroll
+    for (int u = 0; u < kReduceUnroll; ++u) {
+      const long long i = i0 + u * threads;
+      e[u] = -1;
+      sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < nvec) {
+        int lo = 0, hi = nsegs - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (seg_first[mid] <= i) lo = mid; else hi = mid - 1;
+        }
+        e[u] = seg_off[lo] + (i - seg_first[lo]) * 4;
+      }
     }
-    const long long e = segs[seg].offset + (i - seg_begin) * 4;
-    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
     for (int r = 0; r < world; ++r) {
-      const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[r]) + e);
-      sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+      const float* src = static_cast<const float*>(grads.p[r]);
+      float4 v[kReduceUnroll];
+#pragma unroll
+      for (int u = 0; u < kReduceUnroll; ++u)
+        v[u] = e[u] >= 0 ? *reinterpret_cast<const float4*>(src + e[u]) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < kReduceUnroll; ++u) {
+        sum[u].x += v[u].x, sum[u].y += v[u].y, sum[u].z += v[u].z, sum[u].w += v[u].w;
+      }
     }
-    sum.x *= scale, sum.y *= scale, sum.z *= scale, sum.w *= scale;
-    *reinterpret_cast<float4*>(static_cast<float*>(grads.p[my_rank]) + e) = sum;
-    acc += static_cast<double>(sum.x * sum.x + sum.y * sum.y) + static_cast<double>(sum.z * sum.z + sum.w * sum.w);
+#pragma unroll
+    for (int u = 0; u < kReduceUnroll; ++u) {
+      if (e[u] < 0) continue;
+      float4 q = sum[u];
+      q.x *= scale, q.y *= scale, q.z *= scale, q.w *= scale;
+      *reinterpret_cast<float4*>(mine + e[u]) = q;
+      acc += static_cast<double>(q.x * q.x + q.y * q.y) + static_cast<double>(q.z * q.z + q.w * q.w);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -178,7 +215,7 @@ void comm_wait(const int* local_flags, int world, int slot, int value, int* stat
 void comm_reduce_pull(const PeerPtrs& grads, int world, int my_rank, const Segment* segs_dev, int nsegs,
                       long long total, float scale, const int* local_flags, int slot, int value, double* sumsq,
                       int* status, int ctas, cudaStream_t s) {
-  if (total <= 0 || nsegs <= 0) return;
+  if (total <= 0 || nsegs <= 0 || nsegs > kMaxSegs) return;
   reduce_pull_kernel<<<ctas, 256, 0, s>>>(grads, world, my_rank, segs_dev, nsegs, total, scale, local_flags, slot,
                                           value, sumsq, status);
 }

@@ -47,7 +47,7 @@ class FusedTransport:
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
         self.buckets: List[dict] = []
         self.num_slots = 0
-        self.reduce_ctas = 32
+        self.reduce_ctas = 148 * 2
 
     # ------------------------------------------------------------------ allocation
     def allocator(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
