@@ -35,6 +35,7 @@ void comm_reduce_pull(const std::vector<int64_t>& grad_ptrs, int64_t my_rank, co
   const c10::cuda::CUDAGuard g(flags.device());
   TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == torch::kInt64 && segs.is_contiguous() && segs.size(1) == 2,
               "segs must be an int64 [n, 2] CUDA tensor");
+  TORCH_CHECK(segs.size(0) <= 64, "reduce_pull takes at most 64 segments per launch");
   static_assert(sizeof(nc::Segment) == 16, "Segment layout");
   nc::comm_reduce_pull(to_peers(grad_ptrs), static_cast<int>(grad_ptrs.size()), my_rank,
                        reinterpret_cast<const nc::Segment*>(segs.data_ptr<int64_t>()), segs.size(0), total, scale,

@@ -1,0 +1,29 @@
+// Host interface of the paged-KV inference kernels (decode.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace nc {
+
+struct DecodeArgs {
+  int B = 0, H = 0, KV = 0, D = 0;
+  const __nv_bfloat16* q = nullptr;       // [B, H, D], prepared (normed, rotated, scaled)
+  const __nv_bfloat16* k_pool = nullptr;  // [pages, page_size, KV, D]
+  const __nv_bfloat16* v_pool = nullptr;
+  const int* page_table = nullptr;        // [B, max_pages]
+  int max_pages = 0, page_size = 16;
+  const int* seq_lens = nullptr;          // [B], including the token being decoded
+  int window_left = -1;
+  float scale = 1.0f;
+  __nv_bfloat16* out = nullptr;           // [B, H, D]
+};
+
+// Rows k_new / v_new ([B*T, row_elems], leading dimensions k_ld / v_ld) go to absolute positions positions[B*T]
+// (negative = skip) of their sequence's pages.
+void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_table, int max_pages,
+               const int* positions, const __nv_bfloat16* k_new, long long k_ld, const __nv_bfloat16* v_new,
+               long long v_ld, int B, int T, int page_size, int row_elems, cudaStream_t s);
+
+const char* paged_decode_attention(const DecodeArgs& args, cudaStream_t s);
+
+}  // namespace nc

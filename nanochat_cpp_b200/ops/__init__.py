@@ -120,11 +120,12 @@ _NAMES = [
     "backout_fwd", "backout_bwd", "blend_norm_fwd", "blend_bwd", "qk_prep_fwd", "qk_prep_bwd",
     "attention_fwd", "attention_bwd", "value_gate_fwd", "value_gate_bwd", "smear_fwd", "smear_bwd",
     "embedding_fwd", "embedding_bwd", "classifier_fwd_bwd", "adamw_update", "muon_update",
-    "grad_norm_and_clip",
+    "grad_norm_and_clip", "kv_append", "paged_decode_attention",
 ]
 for _n in _NAMES:
     globals()[_n] = _dispatch(_n)
 
 build_rope = ref.build_rope
+paged_gather = ref.paged_gather
 
 __all__ = _NAMES + ["profile", "OpProfile", "build_rope", "ref", "set_mode", "get_mode", "cuda_module"]

@@ -344,6 +344,21 @@ def adamw_update(master, value, grad, m, v, *, lr, beta1, beta2, eps, weight_dec
 muon_update = ref.muon_update
 
 
+# ---------------------------------------------------------------------------
+# Paged KV cache
+# ---------------------------------------------------------------------------
+def kv_append(k_pool, v_pool, page_table, positions, k_new, v_new):
+    _C.kv_append(k_pool, v_pool, page_table, positions.contiguous(), k_new, v_new)
+
+
+def paged_decode_attention(q, k_pool, v_pool, page_table, seq_lens, window_left=-1, scale=None):
+    import math
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    return _C.paged_decode_attention(q.contiguous(), k_pool, v_pool, page_table, seq_lens, int(window_left),
+                                     float(scale))
+
+
 def __getattr__(name):
     # Operators without a kernel are an error on a GPU, not a fallback.
     raise AttributeError(f"ops.cuda has no operator {name!r}")

@@ -500,3 +500,56 @@ def grad_norm_and_clip(grads, clip):
     else:
         scale = torch.ones_like(norm)
     return norm, scale
+
+
+# --------------------------------------------------------------------------
+# Paged KV cache (inference). Pools are [num_pages, page_size, KV, D]; page_table [B, max_pages] int32
+# --------------------------------------------------------------------------
+def kv_append(k_pool, v_pool, page_table, positions, k_new, v_new):
+    """Write rows k_new/v_new [B, T, KV, D] at absolute positions `positions` [B, T] (int32; < 0 = skip)."""
+    page_size = k_pool.shape[1]
+    B, T = positions.shape
+    pos = positions.long()
+    valid = pos >= 0
+    pos_c = pos.clamp_min(0)
+    page = torch.gather(page_table.long(), 1, pos_c // page_size)
+    slot = pos_c % page_size
+    kp = k_pool.view(-1, *k_pool.shape[2:])
+    vp = v_pool.view(-1, *v_pool.shape[2:])
+    flat = (page * page_size + slot)[valid]
+    kp[flat] = k_new[valid].to(kp.dtype)
+    vp[flat] = v_new[valid].to(vp.dtype)
+
+
+def paged_gather(pool, page_table, length):
+    """Contiguous [B, length, KV, D] view of the first `length` positions of every sequence."""
+    page_size = pool.shape[1]
+    n_pages = (length + page_size - 1) // page_size
+    idx = page_table[:, :n_pages].long()
+    out = pool[idx]  # [B, n_pages, page, KV, D]
+    B = idx.shape[0]
+    return out.reshape(B, n_pages * page_size, *pool.shape[2:])[:, :length]
+
+
+def paged_decode_attention(q, k_pool, v_pool, page_table, seq_lens, window_left=-1, scale=None):
+    """One new query per sequence. q [B, H, D]; the query of sequence b sits at position seq_lens[b] - 1 and
+    sees keys j <= that position with position - j <= window_left. Returns [B, H, D]."""
+    B, H, D = q.shape
+    KV = k_pool.shape[2]
+    group = H // KV
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    max_len = int(seq_lens.max().item())
+    k = paged_gather(k_pool, page_table, max_len).float()  # [B, S, KV, D]
+    v = paged_gather(v_pool, page_table, max_len).float()
+    k = k.repeat_interleave(group, dim=2)
+    v = v.repeat_interleave(group, dim=2)
+    s = torch.einsum("bhd,bshd->bhs", q.float(), k) * scale
+    j = torch.arange(max_len, device=q.device)[None, :]
+    qpos = (seq_lens.long() - 1)[:, None]
+    ok = j <= qpos
+    if window_left is not None and window_left >= 0:
+        ok = ok & ((qpos - j) <= window_left)
+    s = s.masked_fill(~ok[:, None, :], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("bhs,bshd->bhd", p, v).to(q.dtype)

@@ -90,6 +90,9 @@ class FusedTransport:
             total = sum(c for _, c in segs)
             t = torch.tensor(segs if segs else [[0, 0]], dtype=torch.int64, device=self.device).reshape(-1, 2)
             self.buckets.append(dict(segs=t, total=total, n=len(segs)))
+        if max(bk["n"] for bk in self.buckets) > 64:
+            raise ValueError("a reduction bucket has more than 64 segments (the kernel's segment table)")
+        self._events = [torch.cuda.Event() for _ in self.buckets]
         self.slot_adamw = L + 2
         self.slot_muon = L + 3
         self.num_slots = L + 4
@@ -108,7 +111,15 @@ class FusedTransport:
         bk = self.buckets[b]
         if bk["total"] == 0:
             return
+        # The reduction must not become resident before this rank's own backward has reached the bucket: its
+        # CTAs spin on the peers' flags, and a spinning grid that starts early can keep the backward kernels of
+        # BOTH ranks off the SMs (each waits for a signal that sits behind the other's blocked backward).
+        # Ordered after the local signal, a waiting reduction only ever waits for a peer that is behind and
+        # whose own reductions can all complete, so some rank always makes progress.
+        ev = self._events[b]
+        ev.record(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ev)
             K._C.comm_reduce_pull(self.grad.ptrs, self.rank, bk["segs"], bk["total"], scale, self.flags.tensor, b,
                                   step, self.sumsq, K._C.status_tensor(self.device.index), self.reduce_ctas)
 
