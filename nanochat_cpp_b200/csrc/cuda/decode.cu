@@ -4,8 +4,8 @@
 // The reference decodes one row at a time over a contiguous cache and runs the attention through batched
 // cuBLAS products (src/generate.cc:266-412, backends/cuda/kernels/attention_dispatch.h:38-48). Decode attention
 // is bandwidth-bound (every cached key and value is read once per step), so this kernel streams K and V pages
-// with 16-byte loads and keeps the online softmax in fp32 registers: one CTA per (sequence, kv head), the query
-// heads of the group share the K / V traffic.
+// with 16-byte loads and keeps the online softmax in fp32 registers: CTAs cover (key split, kv head, sequence),
+// the query heads of a group share the K / V traffic, and a small combine kernel merges the key splits.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>
@@ -43,94 +43,187 @@ __global__ void __launch_bounds__(256) kv_append_kernel(__nv_bfloat16* __restric
   }
 }
 
-constexpr int kChunk = 64;  // keys per step
+constexpr int kDecodeWarps = 4;
+constexpr int kDecodeUnroll = 4;
 
-// grid (KV heads, B); block = D threads (one output dimension per thread); the group's heads loop inside.
+__device__ __forceinline__ void unpack8(const uint4& r, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+
+// grid (splits, KV heads, B), 128 threads. A key row (D bf16) is read by D/8 lanes with one 16-byte load each, so a
+// warp covers 32/(D/8) keys per load instruction and every thread keeps kDecodeUnroll K and V loads in flight. Each
+// lane group runs its own online softmax over the keys it sees (fp32, base-2); the groups of the CTA are merged
+// through shared memory at the end. With more than one split the CTA stores its unnormalised partial sums and the
+// combine kernel finishes; with one split it writes the output row itself.
 template <int D, int G>
-__global__ void __launch_bounds__(D) paged_decode_kernel(const __nv_bfloat16* __restrict__ q,  // [B, H, D]
-                                                         const __nv_bfloat16* __restrict__ k_pool,
-                                                         const __nv_bfloat16* __restrict__ v_pool,
-                                                         const int* __restrict__ page_table, int max_pages,
-                                                         const int* __restrict__ seq_lens, int H, int KV,
-                                                         int page_size, int window_left, float scale_log2,
-                                                         __nv_bfloat16* __restrict__ out) {
-  __shared__ float q_s[G][D];
-  __shared__ float p_s[G][kChunk];
-  __shared__ __nv_bfloat16 k_s[kChunk][D + 8];  // +8 keeps rows 16-byte aligned and off the same bank
-  const int kvh = blockIdx.x, b = blockIdx.y;
-  const int t = threadIdx.x;
+__global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+    const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
+    const int* __restrict__ seq_lens, int H, int KV, int page_size, int window_left, float scale_log2, int splits,
+    float* __restrict__ part_acc, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out) {
+  constexpr int LPK = D / 8;        // lanes per key
+  constexpr int KPW = 32 / LPK;     // keys per warp per load
+  constexpr int GROUPS = kDecodeWarps * KPW;
+  __shared__ float sm_m[G][GROUPS], sm_l[G][GROUPS];
+  __shared__ float sm_acc[G][GROUPS][D];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int len = seq_lens[b];
   if (len <= 0) return;
   const int qpos = len - 1;
   const int first = window_left >= 0 ? max(0, qpos - window_left) : 0;
-  for (int g = 0; g < G; ++g)
-    q_s[g][t] = __bfloat162float(q[(static_cast<long long>(b) * H + kvh * G + g) * D + t]) * scale_log2;
-  float m[G], l[G], acc[G];
+  const int n = qpos - first + 1;
+  const int per = (n + splits - 1) / splits;
+  const int k0 = first + split * per;
+  const int k1 = min(k0 + per, qpos + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPK, part = lane % LPK;
+  const int group = warp * KPW + sub;
+
+  float qf[G][8];
 #pragma unroll
-  for (int g = 0; g < G; ++g) m[g] = -CUDART_INF_F, l[g] = 0.0f, acc[g] = 0.0f;
-  const long long row = static_cast<long long>(KV) * D;  // elements per (page slot)
-  for (int c0 = (first / kChunk) * kChunk; c0 <= qpos; c0 += kChunk) {
-    __syncthreads();
-    // stage the K chunk: thread t copies 16-byte pieces of key rows
-    for (int i = t; i < kChunk * (D / 8); i += D) {
-      const int j = i / (D / 8), part = i % (D / 8);
-      const int key = c0 + j;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (key <= qpos) {
-        const int page = page_table[b * max_pages + key / page_size];
-        v = *reinterpret_cast<const uint4*>(k_pool + (static_cast<long long>(page) * page_size + key % page_size) * row +
-                                            kvh * D + part * 8);
+  for (int g = 0; g < G; ++g) {
+    const uint4 r = *reinterpret_cast<const uint4*>(q + (static_cast<long long>(b) * H + kvh * G + g) * D + part * 8);
+    unpack8(r, qf[g]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qf[g][i] *= scale_log2;
+  }
+  float m[G], l[G], acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -CUDART_INF_F, l[g] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[g][i] = 0.0f;
+  }
+  const long long row = static_cast<long long>(KV) * D;
+  const int* table = page_table + static_cast<long long>(b) * max_pages;
+  for (int kb = k0; kb < k1; kb += GROUPS * kDecodeUnroll) {  // uniform over the CTA: the shuffles below are full-warp
+    uint4 kr[kDecodeUnroll], vr[kDecodeUnroll];
+    bool ok[kDecodeUnroll];
+#pragma unroll
+    for (int u = 0; u < kDecodeUnroll; ++u) {
+      const int key = kb + u * GROUPS + group;
+      ok[u] = key < k1;
+      kr[u] = make_uint4(0, 0, 0, 0), vr[u] = make_uint4(0, 0, 0, 0);
+      if (ok[u]) {
+        const int page = table[key / page_size];
+        const long long off = (static_cast<long long>(page) * page_size + key % page_size) * row + kvh * D + part * 8;
+        kr[u] = *reinterpret_cast<const uint4*>(k_pool + off);
+        vr[u] = *reinterpret_cast<const uint4*>(v_pool + off);
       }
-      *reinterpret_cast<uint4*>(&k_s[j][part * 8]) = v;
     }
-    __syncthreads();
-    // scores: thread t < kChunk handles key c0 + t for every head of the group
-    if (t < kChunk) {
-      const int key = c0 + t;
-      const bool ok = key <= qpos && key >= first;
+    float sc[kDecodeUnroll][G];
+#pragma unroll
+    for (int u = 0; u < kDecodeUnroll; ++u) {
+      float kf[8];
+      unpack8(kr[u], kf);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        float s = 0.0f;
-#pragma unroll 8
-        for (int d = 0; d < D; ++d) s += q_s[g][d] * __bfloat162float(k_s[t][d]);
-        p_s[g][t] = ok ? s : -CUDART_INF_F;
+        float d = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d = fmaf(qf[g][i], kf[i], d);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        sc[u][g] = ok[u] ? d : -CUDART_INF_F;
       }
     }
-    __syncthreads();
-    // online softmax (every thread recomputes the chunk statistics: 64 values) and the V accumulation
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      float cm = m[g];
-      for (int j = 0; j < kChunk; ++j) cm = fmaxf(cm, p_s[g][j]);
-      const float alpha = m[g] == -CUDART_INF_F ? 0.0f : exp2f(m[g] - cm);
-      float a = acc[g] * alpha, ls = l[g] * alpha;
-      for (int j = 0; j < kChunk; ++j) {
-        const int key = c0 + j;
-        if (key > qpos) break;
-        const float pj = exp2f(p_s[g][j] - cm);
-        if (pj == 0.0f) continue;
-        const int page = page_table[b * max_pages + key / page_size];
-        const float vv = __bfloat162float(
-            v_pool[(static_cast<long long>(page) * page_size + key % page_size) * row + kvh * D + t]);
-        a += pj * vv;
-        ls += pj;
+      float mx = m[g];
+#pragma unroll
+      for (int u = 0; u < kDecodeUnroll; ++u) mx = fmaxf(mx, sc[u][g]);
+      if (mx == -CUDART_INF_F) continue;
+      const float alpha = exp2f(m[g] - mx);  // 0 when m is still -inf
+      l[g] *= alpha;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[g][i] *= alpha;
+      m[g] = mx;
+    }
+#pragma unroll
+    for (int u = 0; u < kDecodeUnroll; ++u) {
+      float vf[8];
+      unpack8(vr[u], vf);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float p = sc[u][g] == -CUDART_INF_F ? 0.0f : exp2f(sc[u][g] - m[g]);
+        l[g] += p;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i]);
       }
-      acc[g] = a, l[g] = ls, m[g] = cm;
     }
   }
+  // merge the lane groups
 #pragma unroll
-  for (int g = 0; g < G; ++g)
-    out[(static_cast<long long>(b) * H + kvh * G + g) * D + t] = __float2bfloat16_rn(acc[g] / l[g]);
+  for (int g = 0; g < G; ++g) {
+    if (part == 0) sm_m[g][group] = m[g], sm_l[g][group] = l[g];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm_acc[g][group][part * 8 + i] = acc[g][i];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += kDecodeWarps * 32) {
+    const int g = idx / D, d = idx % D;
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < GROUPS; ++j) mx = fmaxf(mx, sm_m[g][j]);
+    float a = 0.0f, ls = 0.0f;
+    if (mx != -CUDART_INF_F) {
+#pragma unroll
+      for (int j = 0; j < GROUPS; ++j) {
+        const float w = exp2f(sm_m[g][j] - mx);
+        a = fmaf(w, sm_acc[g][j][d], a);
+        ls = fmaf(w, sm_l[g][j], ls);
+      }
+    }
+    const long long head = static_cast<long long>(b) * H + kvh * G + g;
+    if (splits == 1) {
+      out[head * D + d] = __float2bfloat16_rn(ls > 0.0f ? a / ls : 0.0f);
+    } else {
+      part_acc[(head * splits + split) * D + d] = a;
+      if (d == 0) {
+        part_ml[(head * splits + split) * 2] = mx;
+        part_ml[(head * splits + split) * 2 + 1] = ls;
+      }
+    }
+  }
+}
+
+// grid (H, B), D threads: out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+template <int D>
+__global__ void __launch_bounds__(D) decode_combine_kernel(const float* __restrict__ part_acc,
+                                                           const float* __restrict__ part_ml,
+                                                           const int* __restrict__ seq_lens, int H, int splits,
+                                                           __nv_bfloat16* __restrict__ out) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  if (seq_lens[b] <= 0) return;
+  const long long head = static_cast<long long>(b) * H + h;
+  float mx = -CUDART_INF_F;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(head * splits + s) * 2]);
+  float a = 0.0f, ls = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(head * splits + s) * 2];
+    if (ms == -CUDART_INF_F) continue;
+    const float w = exp2f(ms - mx);
+    a = fmaf(w, part_acc[(head * splits + s) * D + d], a);
+    ls = fmaf(w, part_ml[(head * splits + s) * 2 + 1], ls);
+  }
+  out[head * D + d] = __float2bfloat16_rn(ls > 0.0f ? a / ls : 0.0f);
 }
 
 template <int D>
 const char* launch_decode(const DecodeArgs& a, cudaStream_t s) {
-  const dim3 grid(a.KV, a.B);
+  const int splits = a.splits < 1 ? 1 : a.splits;
+  if (splits > 1 && (a.part_acc == nullptr || a.part_ml == nullptr)) return "paged_decode_attention: no split scratch";
+  const dim3 grid(splits, a.KV, a.B);
   const int G = a.H / a.KV;
   const float sl2 = a.scale * 1.4426950408889634f;
-#define NC_DECODE(GV)                                                                                          \
-  paged_decode_kernel<D, GV><<<grid, D, 0, s>>>(a.q, a.k_pool, a.v_pool, a.page_table, a.max_pages, a.seq_lens, \
-                                                a.H, a.KV, a.page_size, a.window_left, sl2, a.out)
+#define NC_DECODE(GV)                                                                                                \
+  paged_decode_kernel<D, GV><<<grid, kDecodeWarps * 32, 0, s>>>(a.q, a.k_pool, a.v_pool, a.page_table, a.max_pages, \
+                                                                a.seq_lens, a.H, a.KV, a.page_size, a.window_left,  \
+                                                                sl2, splits, a.part_acc, a.part_ml, a.out)
   switch (G) {
     case 1: NC_DECODE(1); break;
     case 2: NC_DECODE(2); break;
@@ -139,6 +232,8 @@ const char* launch_decode(const DecodeArgs& a, cudaStream_t s) {
     default: return "paged_decode_attention: group size must be 1, 2, 4 or 8";
   }
 #undef NC_DECODE
+  if (splits > 1)
+    decode_combine_kernel<D><<<dim3(a.H, a.B), D, 0, s>>>(a.part_acc, a.part_ml, a.seq_lens, a.H, splits, a.out);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
@@ -152,6 +247,15 @@ void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_tab
   if (total <= 0) return;
   kv_append_kernel<<<(total + 7) / 8, 256, 0, s>>>(k_pool, v_pool, page_table, max_pages, positions, k_new, k_ld,
                                                    v_new, v_ld, T, total, page_size, row_elems);
+}
+
+int decode_splits(int B, int KV, int max_keys) {
+  const int target = 148 * 4;  // four 128-thread CTAs per SM keep enough loads in flight
+  int splits = (target + B * KV - 1) / (B * KV);
+  const int by_len = (max_keys + 255) / 256;  // at least 256 keys per split
+  if (splits > by_len) splits = by_len;
+  if (splits > 32) splits = 32;
+  return splits < 1 ? 1 : splits;
 }
 
 const char* paged_decode_attention(const DecodeArgs& a, cudaStream_t s) {

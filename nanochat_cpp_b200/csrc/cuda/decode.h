@@ -16,7 +16,15 @@ struct DecodeArgs {
   int window_left = -1;
   float scale = 1.0f;
   __nv_bfloat16* out = nullptr;           // [B, H, D]
+  // Key splits per (sequence, kv head). With splits > 1 the kernel needs scratch: part_acc [B, H, splits, D] and
+  // part_ml [B, H, splits, 2] floats.
+  int splits = 1;
+  float* part_acc = nullptr;
+  float* part_ml = nullptr;
 };
+
+// Key splits that fill the GPU for B sequences of at most `max_keys` attended keys.
+int decode_splits(int B, int KV, int max_keys);
 
 // Rows k_new / v_new ([B*T, row_elems], leading dimensions k_ld / v_ld) go to absolute positions positions[B*T]
 // (negative = skip) of their sequence's pages.

@@ -47,6 +47,17 @@ Tensor paged_decode_attention(const Tensor& q, const Tensor& k_pool, const Tenso
   a.window_left = static_cast<int>(window_left);
   a.scale = static_cast<float>(scale);
   a.out = bp(out);
+  int max_keys = a.max_pages * a.page_size;
+  if (window_left >= 0 && window_left + 1 < max_keys) max_keys = static_cast<int>(window_left) + 1;
+  a.splits = nc::decode_splits(a.B, a.KV, max_keys);
+  Tensor part_acc, part_ml;
+  if (a.splits > 1) {
+    const auto f32 = q.options().dtype(torch::kFloat32);
+    part_acc = torch::empty({a.B, a.H, a.splits, a.D}, f32);
+    part_ml = torch::empty({a.B, a.H, a.splits, 2}, f32);
+    a.part_acc = part_acc.data_ptr<float>();
+    a.part_ml = part_ml.data_ptr<float>();
+  }
   const char* err = nc::paged_decode_attention(a, at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(err == nullptr, err);
   return out;
