@@ -21,6 +21,12 @@ from ..models import GPT
 from ..optim import Optimizer
 
 STAGES = {"base": 0, "sft": 1, "rl": 2}
+# AdamW group names as they appear in record names (reference src/optim.cc:75-90)
+RECORD_KIND = {"wte": "embedding", "value_embed": "value_embedding"}
+
+
+def _kind(g) -> str:
+    return RECORD_KIND.get(g.kind, g.kind)
 
 
 def _np(t: torch.Tensor) -> np.ndarray:
@@ -47,7 +53,7 @@ def _gather_state(opt: Optimizer, dp) -> Dict[str, np.ndarray]:
         if not g.params:
             continue
         for key in ("m", "v"):
-            out[f"adamw.{g.kind}.{key}"] = np.concatenate([_np(full_adamw(s, key)) for s in g.params])
+            out[f"adamw.{_kind(g)}.{key}"] = np.concatenate([_np(full_adamw(s, key)) for s in g.params])
     for g in opt.muon_groups:
         lines = g.rows if g.rows >= g.cols else g.cols
         b1, b2 = [], []
@@ -158,7 +164,7 @@ def load_checkpoint(path: str, model: Optional[GPT] = None, optimizer: Optional[
     if model is None:
         model = GPT(infer_config(records, meta), device, dtype, init=False)
     elif strict_config and meta["config"].get("container_version", 1) == 1:
-        want = config_from_metadata(meta)
+        want = infer_config(records, meta)
         got = model.cfg
         for k in ("num_layers", "num_heads", "num_kv_heads", "hidden_dim", "vocab_size", "padded_vocab_size"):
             if getattr(want, k) != getattr(got, k):
@@ -179,7 +185,7 @@ def _restore_state(opt: Optimizer, recs: Dict[str, torch.Tensor]) -> None:
     dev = opt.store.device
     for g in opt.adamw_groups:
         for key in ("m", "v"):
-            name = f"adamw.{g.kind}.{key}"
+            name = f"adamw.{_kind(g)}.{key}"
             if name not in recs:
                 continue
             flat = recs[name].reshape(-1)
@@ -191,11 +197,14 @@ def _restore_state(opt: Optimizer, recs: Dict[str, torch.Tensor]) -> None:
                 off += s.count
     for g in opt.muon_groups:
         n1, n2 = f"muon.{g.rows}x{g.cols}.buf1", f"muon.{g.rows}x{g.cols}.buf2"
+        P = len(g.params)
+        b1 = recs[n1].reshape(P, g.rows, g.cols) if n1 in recs else None
+        b2 = recs[n2].reshape(P, -1) if n2 in recs else None
         for k, s in enumerate(g.params):
             if s.name in opt.state:
-                if n1 in recs:
-                    opt.state[s.name]["buf1"].copy_(recs[n1][k].to(dev))
-                if n2 in recs:
-                    opt.state[s.name]["buf2"].copy_(recs[n2][k].to(dev))
+                if b1 is not None:
+                    opt.state[s.name]["buf1"].copy_(b1[k].to(dev))
+                if b2 is not None:
+                    opt.state[s.name]["buf2"].copy_(b2[k].to(dev))
     if "optimizer/step" in recs:
         opt.step_count = int(recs["optimizer/step"].reshape(-1)[0].item())
