@@ -89,6 +89,124 @@ class Trainer:
     def tokens_per_step(self) -> int:
         return self.tc.batch * self.cfg.seq_len * self.tc.grad_accum * self.world
 
+    # ------------------------------------------------------------------ the loop
+    def _rank0(self) -> bool:
+        return self.dp is None or self.dp.rank == 0
+
+    def _stage(self, loader):
+        """`grad_accum` micro-batches from the loader through pinned host buffers to the device."""
+        B, T = self.tc.batch, self.cfg.seq_len
+        if not hasattr(self, "_pinned"):
+            pin = self.device.type == "cuda"
+            self._pinned = [(torch.empty((B, T), dtype=torch.int32, pin_memory=pin),
+                             torch.empty((B, T), dtype=torch.int32, pin_memory=pin))
+                            for _ in range(self.tc.grad_accum)]
+        out = []
+        for tok_h, tgt_h in self._pinned:
+            loader.next_into(tok_h.numpy(), tgt_h.numpy())
+            out.append((tok_h.to(self.device, non_blocking=True).long(),
+                        tgt_h.to(self.device, non_blocking=True).long()))
+        return out
+
+    def resume(self, path: str, loader=None) -> int:
+        """Restores weights, optimizer state and step (and the loader position from `<path>.cursor`)."""
+        import os
+        from .checkpointer import load_checkpoint
+        _, meta = load_checkpoint(path, self.model, self.optimizer)
+        self.step_count = int(meta.get("step", 0))
+        self.optimizer.step_count = self.step_count
+        if loader is not None and os.path.exists(path + ".cursor"):
+            loader.load_cursor(path + ".cursor")
+        return self.step_count      # every rank reads the same canonical file, so no broadcast is needed
+
+    def save(self, path: str, loader=None, stage: str = "base") -> None:
+        from .checkpointer import save_checkpoint
+        save_checkpoint(path, self.model, self.optimizer, step=self.step_count, stage=stage, dp=self.dp,
+                        loader=loader if self._rank0() else None)
+
+    def run(self, train_loader, val_loader=None, token_bytes=None, metrics_dir: str = "", out=None) -> dict:
+        """The training loop of the reference (`src/train.cc:726-945`): steps `step_count+1 .. num_iterations`, a log
+        line every `log_every` steps (and on the last), validation bits per byte every `eval_every`, a checkpoint
+        every `save_every` and at the end. Returns the summary that is also written to `summary.json`."""
+        import json
+        import os
+        import sys
+        from ..eval import eval_bpb
+        tc = self.tc
+        out = out or sys.stdout
+        log_f = open(tc.log, "a") if tc.log and self._rank0() else None
+        met_f = None
+        if metrics_dir and self._rank0():
+            os.makedirs(metrics_dir, exist_ok=True)
+            met_f = open(os.path.join(metrics_dir, "metrics.jsonl"), "a")
+
+        def emit(line: str) -> None:
+            if self._rank0():
+                print(line, file=out, flush=True)
+                if log_f:
+                    log_f.write(line + "\n")
+                    log_f.flush()
+
+        peaks = perf.measured_peaks()
+        fpt = perf.flops_per_token(self.cfg)
+        muon_flops = perf.muon_flops_per_step(self.cfg, tc.optim.muon_ns_steps)
+        tokens_step = self.tokens_per_step()
+        cuda = self.device.type == "cuda"
+        t_log = time.perf_counter()
+        steps_since = 0
+        data_ms = 0.0
+        last = {}
+        losses = []
+        first = self.step_count + 1
+        for step in range(first, tc.num_iterations + 1):
+            t0 = time.perf_counter()
+            micro = self._stage(train_loader)
+            data_ms += (time.perf_counter() - t0) * 1e3
+            loss = self.train_step(micro)
+            steps_since += 1
+            final = step == tc.num_iterations
+            eval_ms = 0.0
+            bpb = None
+            if val_loader is not None and tc.eval_every > 0 and (step % tc.eval_every == 0 or final):
+                te = time.perf_counter()
+                bpb = eval_bpb(self.model, val_loader, tc.eval_steps, token_bytes)
+                eval_ms = (time.perf_counter() - te) * 1e3
+                emit(f"[nanochat] step {step} val_bpb {bpb:.6f}")
+            if (tc.log_every > 0 and step % tc.log_every == 0) or final:
+                if cuda:
+                    torch.cuda.synchronize(self.device)
+                now = time.perf_counter()
+                step_ms = ((now - t_log) * 1e3 - eval_ms) / max(steps_since, 1)
+                tok_s = tokens_step / (step_ms / 1e3)
+                lv = float(loss)
+                gn = self.optimizer.grad_norm()
+                lr = self.optimizer.scheduler.lr_multiplier(step)
+                mfu_v = perf.mfu(tok_s / self.world, self.cfg, peaks["bf16_tflops_sustained"])
+                last = dict(step=step, loss=lv, lr=lr, grad_norm=gn, tok_s=tok_s, mfu=mfu_v,
+                            model_tflops=tok_s * fpt / 1e12, optim_tflops=muon_flops / (step_ms / 1e3) / 1e12,
+                            step_ms=step_ms, data_ms=data_ms / max(steps_since, 1), eval_ms=eval_ms)
+                if bpb is not None:
+                    last["val_bpb"] = bpb
+                losses.append(lv)
+                emit(format_log_line(step, lv, lr, gn, tok_s, mfu_v, last["model_tflops"], last["optim_tflops"],
+                                     step_ms, last["data_ms"], eval_ms=eval_ms))
+                if met_f:
+                    met_f.write(json.dumps(last) + "\n")
+                    met_f.flush()
+                t_log, steps_since, data_ms = time.perf_counter(), 0, 0.0
+            if tc.checkpoint and ((tc.save_every > 0 and step % tc.save_every == 0) or final):
+                self.save(tc.checkpoint, train_loader)
+                emit(f"[nanochat] saved {tc.checkpoint} at step {step}")
+        summary = dict(final_step=self.step_count, final_loss=losses[-1] if losses else None, world_size=self.world,
+                       tokens_per_step=tokens_step, last=last)
+        if metrics_dir and self._rank0():
+            with open(os.path.join(metrics_dir, "summary.json"), "w") as f:
+                json.dump(summary, f, indent=1)
+        for f in (log_f, met_f):
+            if f:
+                f.close()
+        return summary
+
 
 def format_log_line(step: int, loss: float, lr: float, grad_norm: float, tok_s: float, mfu_v: float,
                     model_tflops: float, optim_tflops: float, step_ms: float, data_ms: float = 0.0,
