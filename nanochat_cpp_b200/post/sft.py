@@ -92,8 +92,10 @@ class SftStepLog:
 @torch.no_grad()
 def run_sft(model: GPT, optimizer: Optimizer, shard: SftShard, cfg: SftConfig, *,
             val_shard: Optional[SftShard] = None, token_bytes: Optional[np.ndarray] = None,
-            on_step: Optional[Callable[[SftStepLog], None]] = None, log=sys.stderr) -> List[SftStepLog]:
+            on_step: Optional[Callable[[SftStepLog], None]] = None, log="stderr") -> List[SftStepLog]:
     dev = model.device
+    if log == "stderr":
+        log = sys.stderr
     first = max(cfg.first_step, 1)
     target = max(first - 1 + cfg.num_iterations, cfg.num_iterations)
     cursor, epoch, consumed, progress = 0, 1, 0, 0.0
