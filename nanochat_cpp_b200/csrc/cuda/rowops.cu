@@ -293,6 +293,47 @@ __global__ void __launch_bounds__(kThreads) qk_prep_fwd_kernel(const bf16* __res
   const float* cp = cosT + static_cast<long long>(pos) * half;
   const float* sp = sinT + static_cast<long long>(pos) * half;
   const float inv_d = 1.0f / static_cast<float>(D);
+  // head_dim 128: eight lanes share a head (16-byte loads of both halves), four heads per warp at a time
+  if (D == 128 && ((reinterpret_cast<uintptr_t>(row_in) | reinterpret_cast<uintptr_t>(row_out)) & 15) == 0 &&
+      ((reinterpret_cast<uintptr_t>(cp) | reinterpret_cast<uintptr_t>(sp)) & 15) == 0) {
+    const int sub = lane >> 3, j = lane & 7;
+    float c[8], sn[8];
+    *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cp + 8 * j);
+    *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cp + 8 * j + 4);
+    *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sp + 8 * j);
+    *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sp + 8 * j + 4);
+#pragma unroll 2
+    for (int h0 = 0; h0 < heads; h0 += 4) {
+      const int h = h0 + sub;
+      const bool act = h < heads;
+      V8 a, b;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a.f[e] = 0.f, b.f[e] = 0.f;
+      if (act) {
+        a = ld8(row_in + h * 128 + 8 * j);
+        b = ld8(row_in + h * 128 + 64 + 8 * j);
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += a.f[e] * a.f[e] + b.f[e] * b.f[e];
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      const float r = 1.0f / sqrtf(ss * inv_d + eps);
+      if (act) {
+        V8 y1, y2;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float x1 = b2f(f2b(a.f[e] * r)), x2 = b2f(f2b(b.f[e] * r));
+          y1.f[e] = (x1 * c[e] + x2 * sn[e]) * scale;
+          y2.f[e] = (-x1 * sn[e] + x2 * c[e]) * scale;
+        }
+        st8(row_out + h * 128 + 8 * j, y1);
+        st8(row_out + h * 128 + 64 + 8 * j, y2);
+      }
+    }
+    return;
+  }
   const bool vec = (half % 2 == 0) && half <= 64 && (reinterpret_cast<uintptr_t>(cp) & 7) == 0 &&
                    (reinterpret_cast<uintptr_t>(sp) & 7) == 0 &&
                    ((reinterpret_cast<uintptr_t>(row_in) | reinterpret_cast<uintptr_t>(row_out)) & 3) == 0 && (D % 2 == 0);
@@ -364,6 +405,56 @@ __global__ void __launch_bounds__(kThreads) qk_prep_bwd_kernel(const bf16* __res
   const float* cp = cosT + static_cast<long long>(pos) * half;
   const float* sp = sinT + static_cast<long long>(pos) * half;
   const float inv_d = 1.0f / static_cast<float>(D);
+  if (D == 128 && ((reinterpret_cast<uintptr_t>(row_x) | reinterpret_cast<uintptr_t>(row_g) |
+                    reinterpret_cast<uintptr_t>(row_o)) & 15) == 0 &&
+      ((reinterpret_cast<uintptr_t>(cp) | reinterpret_cast<uintptr_t>(sp)) & 15) == 0) {
+    const int sub = lane >> 3, j = lane & 7;
+    float c[8], sn[8];
+    *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cp + 8 * j);
+    *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cp + 8 * j + 4);
+    *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sp + 8 * j);
+    *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sp + 8 * j + 4);
+#pragma unroll 2
+    for (int h0 = 0; h0 < heads; h0 += 4) {
+      const int h = h0 + sub;
+      const bool act = h < heads;
+      V8 x1, x2, g1, g2;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x1.f[e] = 0.f, x2.f[e] = 0.f, g1.f[e] = 0.f, g2.f[e] = 0.f;
+      if (act) {
+        x1 = ld8(row_x + h * 128 + 8 * j);
+        x2 = ld8(row_x + h * 128 + 64 + 8 * j);
+        g1 = ld8(row_g + h * 128 + 8 * j);
+        g2 = ld8(row_g + h * 128 + 64 + 8 * j);
+      }
+      float n1[8], n2[8], ss = 0.f, dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        n1[e] = scale * (g1.f[e] * c[e] - g2.f[e] * sn[e]);
+        n2[e] = scale * (g1.f[e] * sn[e] + g2.f[e] * c[e]);
+        ss += x1.f[e] * x1.f[e] + x2.f[e] * x2.f[e];
+        dot += x1.f[e] * n1[e] + x2.f[e] * n2[e];
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      }
+      const float r = 1.0f / sqrtf(ss * inv_d + eps);
+      const float coeff = r * r * r * dot * inv_d;
+      if (act) {
+        V8 o1, o2;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          o1.f[e] = r * n1[e] - coeff * x1.f[e];
+          o2.f[e] = r * n2[e] - coeff * x2.f[e];
+        }
+        st8(row_o + h * 128 + 8 * j, o1);
+        st8(row_o + h * 128 + 64 + 8 * j, o2);
+      }
+    }
+    return;
+  }
   const bool vec = (half % 2 == 0) && half <= 64 && (reinterpret_cast<uintptr_t>(cp) & 7) == 0 &&
                    (reinterpret_cast<uintptr_t>(sp) & 7) == 0 && (D % 2 == 0) &&
                    ((reinterpret_cast<uintptr_t>(row_x) | reinterpret_cast<uintptr_t>(row_g) |
@@ -709,6 +800,104 @@ __global__ void __launch_bounds__(256) classifier_kernel(bf16* __restrict__ logi
   }
 }
 
+// One CTA per row with the row's logits kept in shared memory between the two sweeps, so a chunk of logits is
+// read from HBM once and written once. The soft cap bounds every logit to [-cap, cap], which makes the running
+// maximum unnecessary: exp(z - cap) cannot overflow and its sum over any vocabulary stays far above the fp32
+// denormal range. tanh is the single-instruction approximation (relative error 2^-11, four times finer than the
+// bf16 rounding of its input). Per element: tanh + ex2 in each sweep.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr int kClsThreads = 512;
+
+__global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
+    bf16* __restrict__ logits, long long ld, const int* __restrict__ targets, float* __restrict__ losses,
+    const float* __restrict__ row_scale, const float* __restrict__ dlogit_scale, int vocab, int padded,
+    float softcap, int ignore_index, bool want_grad) {
+  extern __shared__ __align__(16) unsigned char cls_smem[];
+  bf16* row_s = reinterpret_cast<bf16*>(cls_smem);
+  __shared__ float sh[32];
+  const int row = blockIdx.x;
+  bf16* lp = logits + static_cast<long long>(row) * ld;
+  const int target = targets[row];
+  if (target == ignore_index) {
+    if (threadIdx.x == 0) losses[row] = 0.0f;
+    if (want_grad) {
+      for (int i = threadIdx.x * 8; i < padded; i += kClsThreads * 8)
+        *reinterpret_cast<uint4*>(lp + i) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+  const float inv_cap = 1.0f / softcap;
+  const float c2 = softcap * 1.4426950408889634f;  // cap * log2(e): exp(z - cap) = 2^(c2 * (t - 1))
+  float l = 0.0f;
+  // four 16-byte loads per thread are issued before any of them is used: 32 KB in flight per CTA
+  constexpr int kBatch = 4;
+  for (int i0 = threadIdx.x * 8; i0 < vocab; i0 += kClsThreads * 8 * kBatch) {
+    uint4 raw[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int i = i0 + u * kClsThreads * 8;
+      raw[u] = i < vocab ? __ldcs(reinterpret_cast<const uint4*>(lp + i)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int i = i0 + u * kClsThreads * 8;
+      if (i >= vocab) break;
+      if (want_grad) *reinterpret_cast<uint4*>(row_s + i) = raw[u];
+      const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float t0 = tanh_fast(__uint_as_float(w[e] << 16) * inv_cap);
+        const float t1 = tanh_fast(__uint_as_float(w[e] & 0xffff0000u) * inv_cap);
+        l += ex2_fast(fmaf(c2, t0, -c2)) + ex2_fast(fmaf(c2, t1, -c2));
+      }
+    }
+  }
+  const float lsum = block_sum(l, sh);
+  const bool in_range = target >= 0 && target < vocab;
+  if (threadIdx.x == 0) {
+    const float tz = in_range ? softcap * tanh_fast(b2f(lp[target]) * inv_cap) : 0.0f;
+    losses[row] = logf(lsum) + softcap - tz;
+  }
+  if (!want_grad) return;  // block_sum ended with a barrier: every thread's part of the row is in shared memory
+  const float inv = 1.0f / lsum;
+  const float scale = *dlogit_scale;
+  const float rs = row_scale ? row_scale[row] : 1.0f;
+  for (int i = threadIdx.x * 8; i < padded; i += kClsThreads * 8) {
+    uint4 outv = make_uint4(0, 0, 0, 0);
+    if (i < vocab) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(row_s + i);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float t0 = tanh_fast(__uint_as_float(w[e] << 16) * inv_cap);
+        const float t1 = tanh_fast(__uint_as_float(w[e] & 0xffff0000u) * inv_cap);
+        const float p0 = ex2_fast(fmaf(c2, t0, -c2)) * inv;
+        const float p1 = ex2_fast(fmaf(c2, t1, -c2)) * inv;
+        const float h0 = (i + 2 * e == target) ? 1.0f : 0.0f;
+        const float h1 = (i + 2 * e + 1 == target) ? 1.0f : 0.0f;
+        // rounded once before the loss scale, as the two-pass definition does
+        const float g0 = b2f(f2b((p0 - h0) * (1.0f - t0 * t0) * rs)) * scale;
+        const float g1 = b2f(f2b((p1 - h1) * (1.0f - t1 * t1) * rs)) * scale;
+        const __nv_bfloat162 pk = __floats2bfloat162_rn(g0, g1);
+        o[e] = *reinterpret_cast<const uint32_t*>(&pk);
+      }
+      outv = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    *reinterpret_cast<uint4*>(lp + i) = outv;
+  }
+}
+
 // ------------------------------------------------------------------ gradient norm
 __global__ void __launch_bounds__(256) sumsq_kernel(const float* __restrict__ g, long long n, double* out) {
   __shared__ double shd[8];
@@ -836,6 +1025,14 @@ void classifier_fwd_bwd(bf16* logits, long long ld, const int* targets, float* l
                         const float* dlogit_scale, int rows, int vocab, int padded, float softcap, int ignore_index,
                         bool want_grad, cudaStream_t s) {
   if (rows <= 0) return;
+  const size_t row_bytes = static_cast<size_t>(padded) * sizeof(bf16);
+  const bool vec = vocab % 8 == 0 && padded % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  if (vec && row_bytes <= 200 * 1024) {
+    cudaFuncSetAttribute(classifier_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    classifier_smem_kernel<<<rows, kClsThreads, want_grad ? row_bytes : 0, s>>>(
+        logits, ld, targets, losses, row_scale, dlogit_scale, vocab, padded, softcap, ignore_index, want_grad);
+    return;
+  }
   classifier_kernel<<<rows, 256, 0, s>>>(logits, ld, targets, losses, row_scale, dlogit_scale, rows, vocab, padded,
                                          softcap, ignore_index, want_grad);
 }

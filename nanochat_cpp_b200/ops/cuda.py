@@ -66,7 +66,9 @@ EPI_BF16, EPI_BF16_RES, EPI_RELU2, EPI_DRELU2, EPI_F32 = 0, 1, 2, 3, 4
 
 def check_status(device=None) -> None:
     """Raise if any kernel recorded a bounded-wait failure. Synchronizes the device."""
-    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    dev = None if device is None else torch.device(device).index
+    if dev is None:
+        dev = torch.cuda.current_device()
     code = _C.read_status(dev)
     if code != 0:
         _C.reset_status(dev)
