@@ -95,91 +95,116 @@ __device__ __forceinline__ Unit decode_unit(const KernelParams& p, int unit) {
   return u;
 }
 
+// One 32-column chunk of a thread's accumulator row through the fused epilogue EPI to global memory.
+// `rv` holds the thread's 32 residual / pre-activation values (bf16) for the epilogues that read R.
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_t (&r)[32], const uint4 (&rv)[4],
+                                            int col0, long long crow) {
+  if (EPI == kEpiF32) {
+    float* crow_p = reinterpret_cast<float*>(p.C) + crow + col0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (col0 + j * 4 >= p.N) break;
+      float4 v = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                             __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+      float4* dst = reinterpret_cast<float4*>(crow_p + j * 4);
+      if (p.splits > 1) {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z),
+                     "f"(v.w)
+                     : "memory");
+      } else {
+        if (p.beta != 0.0f) {
+          const float4 o = *dst;
+          v.x += p.beta * o.x;
+          v.y += p.beta * o.y;
+          v.z += p.beta * o.z;
+          v.w += p.beta * o.w;
+        }
+        *dst = v;
+      }
+    }
+    return;
+  }
+  __nv_bfloat16* crow_p = reinterpret_cast<__nv_bfloat16*>(p.C) + crow + col0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (col0 + j * 8 >= p.N) break;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
+    const uint32_t rw[4] = {rv[j].x, rv[j].y, rv[j].z, rv[j].w};
+    if (EPI == kEpiBf16) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] *= p.alpha;
+    } else if (EPI == kEpiBf16Res) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        f[2 * e] = p.alpha * f[2 * e] + p.beta * bf16_lo(rw[e]);
+        f[2 * e + 1] = p.alpha * f[2 * e + 1] + p.beta * bf16_hi(rw[e]);
+      }
+    } else if (EPI == kEpiDRelu2) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        f[2 * e] *= 2.0f * fmaxf(bf16_lo(rw[e]), 0.0f);
+        f[2 * e + 1] *= 2.0f * fmaxf(bf16_hi(rw[e]), 0.0f);
+      }
+    }
+    uint4 out;
+    out.x = pack_bf16(f[0], f[1]);
+    out.y = pack_bf16(f[2], f[3]);
+    out.z = pack_bf16(f[4], f[5]);
+    out.w = pack_bf16(f[6], f[7]);
+    *reinterpret_cast<uint4*>(crow_p + j * 8) = out;
+    if (EPI == kEpiRelu2) {
+      // act = relu(pre)^2 computed from the rounded pre-activation, as a separate pass would.
+      const uint32_t ow[4] = {out.x, out.y, out.z, out.w};
+      uint32_t aw[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float lo = fmaxf(bf16_lo(ow[e]), 0.0f);
+        const float hi = fmaxf(bf16_hi(ow[e]), 0.0f);
+        aw[e] = pack_bf16(lo * lo, hi * hi);
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0 + j * 8) =
+          make_uint4(aw[0], aw[1], aw[2], aw[3]);
+    }
+  }
+}
+
+template <int EPI>
+__device__ __forceinline__ void load_residual(const KernelParams& p, uint4 (&rv)[4], int col0, long long rrow,
+                                              bool row_ok) {
+  if (EPI != kEpiBf16Res && EPI != kEpiDRelu2) return;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    rv[j] = (row_ok && col0 + j * 8 < p.N) ? *reinterpret_cast<const uint4*>(p.R + rrow + col0 + j * 8)
+                                           : make_uint4(0, 0, 0, 0);
+  }
+}
+
 // Epilogue of one warp: its 32 accumulator rows x BN columns from TMEM (`taddr` = lane quadrant and first
 // column), through the fused epilogue EPI, to global memory. `crow` / `rrow` are the element offsets of the
-// thread's row in C and R.
+// thread's row in C and R. The TMEM read and the residual load of chunk c+1 are in flight while chunk c is
+// converted and stored.
 template <int EPI>
 __device__ __forceinline__ void store_tile(const KernelParams& p, uint32_t taddr, int n_base, bool row_ok,
                                            long long crow, long long rrow) {
+  uint32_t r0[32], r1[32];
+  uint4 q0[4], q1[4];
+  tmem_ld_32x32(taddr, r0);
+  load_residual<EPI>(p, q0, n_base, rrow, row_ok);
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
-    uint32_t r[32];
-    tmem_ld_32x32(taddr + c * 32, r);
+  for (int c = 0; c < BN / 32; c += 2) {
     tmem_ld_wait();
-    const int col0 = n_base + c * 32;
-    if (!row_ok || col0 >= p.N) continue;
-    if (EPI == kEpiF32) {
-      float* crow_p = reinterpret_cast<float*>(p.C) + crow + col0;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (col0 + j * 4 >= p.N) break;
-        float4 v = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
-                               __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
-        float4* dst = reinterpret_cast<float4*>(crow_p + j * 4);
-        if (p.splits > 1) {
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z),
-                       "f"(v.w)
-                       : "memory");
-        } else {
-          if (p.beta != 0.0f) {
-            const float4 o = *dst;
-            v.x += p.beta * o.x;
-            v.y += p.beta * o.y;
-            v.z += p.beta * o.z;
-            v.w += p.beta * o.w;
-          }
-          *dst = v;
-        }
-      }
-    } else {
-      __nv_bfloat16* crow_p = reinterpret_cast<__nv_bfloat16*>(p.C) + crow + col0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (col0 + j * 8 >= p.N) break;
-        float f[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
-        uint4 out, out2;
-        if (EPI == kEpiBf16) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] *= p.alpha;
-        } else if (EPI == kEpiBf16Res) {
-          const uint4 rv = *reinterpret_cast<const uint4*>(p.R + rrow + col0 + j * 8);
-          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            f[2 * e] = p.alpha * f[2 * e] + p.beta * bf16_lo(rw[e]);
-            f[2 * e + 1] = p.alpha * f[2 * e + 1] + p.beta * bf16_hi(rw[e]);
-          }
-        } else if (EPI == kEpiDRelu2) {
-          const uint4 rv = *reinterpret_cast<const uint4*>(p.R + rrow + col0 + j * 8);
-          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            f[2 * e] *= 2.0f * fmaxf(bf16_lo(rw[e]), 0.0f);
-            f[2 * e + 1] *= 2.0f * fmaxf(bf16_hi(rw[e]), 0.0f);
-          }
-        }
-        out.x = pack_bf16(f[0], f[1]);
-        out.y = pack_bf16(f[2], f[3]);
-        out.z = pack_bf16(f[4], f[5]);
-        out.w = pack_bf16(f[6], f[7]);
-        *reinterpret_cast<uint4*>(crow_p + j * 8) = out;
-        if (EPI == kEpiRelu2) {
-          // act = relu(pre)^2 computed from the rounded pre-activation, as a separate pass would.
-          const uint32_t ow[4] = {out.x, out.y, out.z, out.w};
-          uint32_t aw[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float lo = fmaxf(bf16_lo(ow[e]), 0.0f);
-            const float hi = fmaxf(bf16_hi(ow[e]), 0.0f);
-            aw[e] = pack_bf16(lo * lo, hi * hi);
-          }
-          out2 = make_uint4(aw[0], aw[1], aw[2], aw[3]);
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0 + j * 8) = out2;
-        }
-      }
+    tmem_ld_32x32(taddr + (c + 1) * 32, r1);
+    load_residual<EPI>(p, q1, n_base + (c + 1) * 32, rrow, row_ok);
+    if (row_ok && n_base + c * 32 < p.N) store_chunk<EPI>(p, r0, q0, n_base + c * 32, crow);
+    tmem_ld_wait();
+    if (c + 2 < BN / 32) {
+      tmem_ld_32x32(taddr + (c + 2) * 32, r0);
+      load_residual<EPI>(p, q0, n_base + (c + 2) * 32, rrow, row_ok);
     }
+    if (row_ok && n_base + (c + 1) * 32 < p.N) store_chunk<EPI>(p, r1, q1, n_base + (c + 1) * 32, crow);
   }
 }
 
