@@ -195,7 +195,14 @@ class DataLoader:
 
     @classmethod
     def from_parquet(cls, paths: Sequence[str], tokenizer: Tokenizer, batch: int, seq: int, text_column: str = "text",
-                     buffer_docs: int = 1000, seed: int = 0, tokenizer_threads: int = 4) -> "DataLoader":
+                     buffer_docs: int = 1000, seed: int = 0, tokenizer_threads: int = 4, rank: int = 0,
+                     world: int = 1) -> "DataLoader":
+        """With `world > 1` document i goes to rank i % world (reference src/data.cc:823-880)."""
+        if world > 1:
+            bos = tokenizer.bos_id
+            docs = [tokenizer.encode(t.decode("utf-8", "replace"), prepend=bos)
+                    for p in paths for t in read_parquet_strings(p, text_column)]
+            return cls.from_documents(docs, batch, seq, buffer_docs, rank, world)
         arr = (C.c_char_p * len(paths))(*[p.encode() for p in paths])
         return cls(lib().nanochat_loader_create(arr, len(paths), text_column.encode(), tokenizer._h, batch, seq, seed,
                                                 tokenizer_threads, buffer_docs), batch, seq, keep=tokenizer)

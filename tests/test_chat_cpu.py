@@ -1,0 +1,123 @@
+"""Chat template, SFT packer, calculator tool and tasks against the reference's fixtures."""
+import json
+import os
+
+import numpy as np
+import torch
+
+from nanochat_cpp_b200 import api
+from nanochat_cpp_b200.chat import (ARC, GSM8K, MMLU, ChatEngine, PackedRowStream, TaskMixture, evaluate_task,
+                                    pack_rows, render_conversation, render_for_completion, use_calculator)
+
+
+def _json_fixture(path):
+    blob = open(path, "rb").read()
+    assert blob[:8] == b"NANCHAT1"
+    return json.loads(blob[12:])
+
+
+def test_completion_prompts_match_fixture(data_dir):
+    fx = _json_fixture(os.path.join(data_dir, "chat_fixture.bin"))
+    tok = api.Tokenizer.load(os.path.join(data_dir, "loader_tokenizer.nctoken"))
+    for case in fx["cases"]:
+        assert render_for_completion(case["conversation"], tok) == case["prompt_ids"], case["name"]
+        ids, mask = render_conversation(case["conversation"], tok)
+        assert ids[:len(case["prompt_ids"])] == case["prompt_ids"] and len(ids) == len(mask) and mask[0] == 0
+
+
+class _PieceTokenizer:
+    """The fixture's tokenizer: whole strings map to fixed id lists."""
+
+    def __init__(self, table, specials):
+        self.table, self.sp = table, specials
+
+    def encode(self, text):
+        return list(self.table[text])
+
+    def encode_special(self, name):
+        return self.sp.get(name, -1)
+
+    def get_bos_token_id(self):
+        return self.sp["<|bos|>"]
+
+
+def test_render_mixture_and_packing_match_fixture(data_dir):
+    fx = _json_fixture(os.path.join(data_dir, "sft_pack_fixture.bin"))
+    names = ["<|bos|>", "<|user_start|>", "<|user_end|>", "<|assistant_start|>", "<|assistant_end|>",
+             "<|python_start|>", "<|python_end|>", "<|output_start|>", "<|output_end|>"]
+    sp = fx["tokenizer"].get("specials") or {n: i for i, n in enumerate(names)}
+    tok = _PieceTokenizer(fx["tokenizer"]["pieces"], sp)
+    convs = fx["conversations"]
+    for conv, want in zip(convs, fx["render"]):
+        ids, mask = render_conversation(conv, tok, max_tokens=fx["settings"]["render_max_tokens"])
+        assert ids == want["ids"] and mask == want["mask"], conv.get("name")
+    st = fx["settings"]
+    n = st["conversations"]
+    tokens, targets = pack_rows(convs[:n], tok, st["seq_len"], buffer_size=st["buffer_size"],
+                                render_max_tokens=st["render_max_tokens"], rank=st["rank"],
+                                world_size=st["world_size"])
+    assert tokens[:st["rows"]].tolist() == fx["pack"]["inputs"]
+    assert targets[:st["rows"]].tolist() == fx["pack"]["targets"]
+    for key in ("mixture", "validation_mixture"):
+        mix = TaskMixture([list(range(t["length"])) for t in fx[key]["tasks"]], seed=fx[key]["seed"])
+        assert [list(p) for p in mix.index_map] == fx[key]["order"] and len(mix) == fx[key]["conversations"]
+
+
+def test_calculator():
+    assert use_calculator("8 * 5") == "40" and use_calculator("1,000 + 24") == "1024"
+    assert use_calculator("7 / 2") == "3.5" and use_calculator("2 ** 8") is None
+    assert use_calculator("'strawberry'.count('r')") == "3"
+    assert use_calculator("__import__('os')") is None and use_calculator("open('x')") is None
+
+
+def test_tool_use_and_tasks(data_dir):
+    tok = api.Tokenizer.load(os.path.join(data_dir, "loader_tokenizer.nctoken"))
+    cfg = api.Config(num_layers=2, num_heads=2, hidden_dim=64, seq_len=128, vocab_size=tok.vocab_size,
+                     head_dim=32, window_pattern="L")
+    model = api.Model(cfg, device="cpu", seed=5)
+    eng = ChatEngine(model, tok)
+    sp = eng.sp
+    # make the model's "samples" a scripted tool call by forcing through the same hook the engine uses
+    script = [sp["<|python_start|>"], *tok.encode("6*7"), sp["<|python_end|>"]]
+    prompt = render_for_completion({"messages": [{"role": "user", "content": "6*7?"},
+                                                 {"role": "assistant", "content": ""}]}, tok)
+    from nanochat_cpp_b200.inference import GenerateParams, generate_multi
+    inner = {}
+
+    def hook(r, tokens):
+        k = len(tokens) - len(prompt)
+        if k < len(script):
+            return script[k]
+        return inner["forced"](r, tokens)
+
+    # reuse the engine's own state machine for everything after the scripted call
+    rows = None
+    orig = generate_multi
+
+    def run():
+        import nanochat_cpp_b200.inference as inf
+        real = inf.generate_multi
+
+        def patched(engine, prompts, params, forced=None):
+            inner["forced"] = forced
+            return real(engine, prompts, params, forced=hook)
+        inf.generate_multi = patched
+        try:
+            return eng.generate(prompt, max_tokens=len(script) + 6, temperature=0.0)
+        finally:
+            inf.generate_multi = real
+    tokens, mask = run()[0]
+    tail = tokens[len(prompt) + len(script):]
+    want = [sp["<|output_start|>"], *tok.encode("42"), sp["<|output_end|>"]]
+    assert tail[:len(want)] == want and mask[len(prompt) + len(script):][:len(want)] == [0] * len(want)
+    # tasks
+    mm = MMLU([{"question": "1+1?", "choices": ["1", "2", "3", "4"], "answer": 1, "subject": "math"}] * 3)
+    assert mm[0]["messages"][0]["content"].startswith("Multiple Choice question: 1+1?\n- 1=A\n- 2=B")
+    rep = evaluate_task(mm, model, tok, batch=2)
+    assert rep["total"] == 3 and 0.0 <= rep["accuracy"] <= 1.0
+    arc = ARC([{"question": "sky?", "choices": {"text": ["blue", "red"], "label": ["A", "B"]}, "answerKey": "A"}])
+    assert arc.evaluate(arc[0], "A") and not arc.evaluate(arc[0], "B")
+    g = GSM8K([{"question": "5 boxes of 8?", "answer": "8 * 5 = <<8*5=40>>40\n#### 40"}])
+    parts = g[0]["messages"][1]["content"]
+    assert [p["type"] for p in parts] == ["text", "python", "python_output", "text"] and parts[1]["text"] == "8*5"
+    assert g.evaluate(g[0], "so #### 40") and not g.evaluate(g[0], "#### 41") and g.reward(g[0], "#### 40") == 1.0
