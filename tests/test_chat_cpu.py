@@ -121,3 +121,45 @@ def test_tool_use_and_tasks(data_dir):
     parts = g[0]["messages"][1]["content"]
     assert [p["type"] for p in parts] == ["text", "python", "python_output", "text"] and parts[1]["text"] == "8*5"
     assert g.evaluate(g[0], "so #### 40") and not g.evaluate(g[0], "#### 41") and g.reward(g[0], "#### 40") == 1.0
+
+
+def test_rl_loop_in_process_and_over_pipes(data_dir, tmp_path):
+    from nanochat_cpp_b200.optim import Optimizer
+    from nanochat_cpp_b200.post import RlWorker
+    from nanochat_cpp_b200.post.rl_loop import InProcessWorker, PipeWorker, run
+    tok = api.Tokenizer.load(os.path.join(data_dir, "loader_tokenizer.nctoken"))
+    cfg = api.Config(num_layers=2, num_heads=2, hidden_dim=64, seq_len=64, vocab_size=tok.vocab_size, head_dim=32,
+                     window_pattern="L")
+    model = api.Model(cfg, device="cpu", seed=5)
+    task = GSM8K([{"question": "2+2?", "answer": "#### 4"}, {"question": "3+3?", "answer": "#### 6"}])
+
+    class LengthReward:     # a reward with variance on a random model: longer replies score higher
+        def reward(self, conv, text):
+            return float(len(text))
+    convs = [task[0], task[1]]
+    before = model.gpt.params.master.clone()
+    ck = str(tmp_path / "rl.ckpt")
+    rep = run(InProcessWorker(RlWorker(model.gpt, Optimizer(model.gpt.params))), LengthReward(), convs, tok,
+              num_samples=3, steps=2, max_tokens=6, seed=1, checkpoint=ck)
+    assert len(rep.losses) == 2 and all(np.isfinite(rep.losses)) and os.path.exists(ck)
+    assert not torch.equal(before, model.gpt.params.master)
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    w = PipeWorker.spawn(api.model_flags(cfg), checkpoint=ck, device="cpu", env=env)
+    try:
+        rep2 = run(w, LengthReward(), convs, tok, num_samples=2, steps=1, max_tokens=4, seed=2)
+    finally:
+        w.close()
+    assert len(rep2.losses) == 1 and np.isfinite(rep2.losses[0])
+
+
+def test_pipeline_tiny_profile(data_dir, tmp_path):
+    from nanochat_cpp_b200.pipeline import run_pipeline
+    convs = [{"messages": [{"role": "user", "content": "Say hello."}, {"role": "assistant", "content": "Hello!"}]},
+             {"messages": [{"role": "user", "content": "2+2?"}, {"role": "assistant", "content": "#### 4"}]}] * 3
+    task = GSM8K([{"question": "2+2?", "answer": "#### 4"}])
+    rep = run_pipeline("tiny", str(tmp_path), os.path.join(data_dir, "loader_tokenizer.nctoken"),
+                       train_parquet=[os.path.join(data_dir, "text.parquet")], sft_conversations=convs,
+                       rl_task=task, rl_conversations=[task[0]], device="cpu")
+    assert rep.base["final_step"] == 8 and rep.sft["steps"] == 4 and rep.rl["steps"] == 1
+    assert np.isfinite(rep.eval["val_bpb"]) and rep.eval["checkpoint"].endswith("rl.ckpt")
+    assert os.path.exists(tmp_path / "pipeline.json")
