@@ -1,0 +1,280 @@
+// C ABI of the CPU engine: model, optimizer, scoring, generation, evaluation (reference
+// include/nanochat/capi.h:377-439, 571-617). Errors are reported through nanochat_last_error(); functions that
+// return a value return NaN / 0 / null on failure.
+#include <cmath>
+#include <cstring>
+#include <limits>
+
+#include "capi_internal.h"
+#include "engine.h"
+
+struct nanochat_model {
+  std::unique_ptr<ncb::CpuModel> model;
+  // storage that results handed to the caller point into; valid until the next call on the same model
+  std::vector<std::vector<float>> score_nll, score_focus;
+  std::vector<std::vector<int>> score_argmax;
+  std::vector<int> seq_tokens, seq_lengths, seq_offsets;
+  std::vector<std::uint8_t> seq_mask;
+};
+struct nanochat_optim {
+  std::unique_ptr<ncb::CpuOptimizer> opt;
+  nanochat_model* model = nullptr;
+  int steps_done = 0;  // for nanochat_train_step, which does not take a step number
+};
+
+namespace {
+
+const float kNaN = std::numeric_limits<float>::quiet_NaN();
+
+template <typename F>
+auto Guard(F&& f, decltype(f()) fallback) -> decltype(f()) {
+  try {
+    return f();
+  } catch (const std::exception& e) {
+    ncb_set_error(e.what());
+    return fallback;
+  }
+}
+
+void FillSequences(nanochat_model* m, const std::vector<ncb::GeneratedRow>& rows, nanochat_sequences* out) {
+  m->seq_tokens.clear(), m->seq_mask.clear(), m->seq_lengths.clear(), m->seq_offsets.clear();
+  for (const auto& r : rows) {
+    m->seq_offsets.push_back(static_cast<int>(m->seq_tokens.size()));
+    m->seq_lengths.push_back(static_cast<int>(r.tokens.size()));
+    m->seq_tokens.insert(m->seq_tokens.end(), r.tokens.begin(), r.tokens.end());
+    m->seq_mask.insert(m->seq_mask.end(), r.mask.begin(), r.mask.end());
+  }
+  out->count = static_cast<int>(rows.size());
+  out->tokens = m->seq_tokens.data();
+  out->mask = m->seq_mask.data();
+  out->lengths = m->seq_lengths.data();
+  out->offsets = m->seq_offsets.data();
+}
+
+ncb::GenerateOptions ToOptions(const nanochat_generate_params& p) {
+  ncb::GenerateOptions o;
+  o.num_samples = p.num_samples > 0 ? p.num_samples : 1;
+  o.max_tokens = p.max_tokens;
+  o.temperature = p.temperature;
+  o.top_k = p.top_k;
+  o.seed = p.seed;
+  o.stop_id = p.stop_id;
+  o.bos_id = p.bos_id;
+  if (p.stop_ids != nullptr) o.stop_ids.assign(p.stop_ids, p.stop_ids + o.num_samples);
+  return o;
+}
+
+}  // namespace
+
+extern "C" {
+
+nanochat_model* nanochat_model_create(const nanochat_config* config, uint64_t seed) {
+  if (config == nullptr) {
+    ncb_set_error("nanochat_model_create: config is null");
+    return nullptr;
+  }
+  ncb::EngineConfig cfg;
+  static_cast<ncb::ModelConfig&>(cfg) = ncb_to_model_config(*config);
+  std::string err;
+  if (!cfg.Validate(&err)) {
+    ncb_set_error("nanochat_model_create: " + err);
+    return nullptr;
+  }
+  return Guard([&]() {
+    auto* m = new nanochat_model();
+    m->model = std::make_unique<ncb::CpuModel>(cfg);
+    m->model->InitWeights(seed);
+    return m;
+  }, static_cast<nanochat_model*>(nullptr));
+}
+void nanochat_model_free(nanochat_model* model) { delete model; }
+
+float nanochat_forward_loss(nanochat_model* model, const int* tokens, const int* targets, int batch, int seq) {
+  if (model == nullptr || tokens == nullptr || targets == nullptr || batch <= 0 || seq <= 0) return kNaN;
+  return Guard([&]() { return model->model->ForwardLoss(tokens, targets, batch, seq); }, kNaN);
+}
+void nanochat_backward(nanochat_model* model) {
+  if (model != nullptr) Guard([&]() { return model->model->Backward(1.0f), 0; }, 0);
+}
+void nanochat_backward_accumulate(nanochat_model* model, float scale) {
+  if (model != nullptr) Guard([&]() { return model->model->Backward(scale), 0; }, 0);
+}
+void nanochat_backward_weighted(nanochat_model* model, const float* row_weights, float scale) {
+  if (model != nullptr) Guard([&]() { return model->model->Backward(scale, row_weights), 0; }, 0);
+}
+void nanochat_zero_grad(nanochat_model* model) {
+  if (model != nullptr) model->model->ZeroGrad();
+}
+float nanochat_train_step(nanochat_model* model, nanochat_optim* optimizer, const int* tokens, const int* targets,
+                          int batch, int seq) {
+  if (model == nullptr) return kNaN;
+  return Guard([&]() {
+    model->model->ZeroGrad();
+    const float loss = model->model->ForwardLoss(tokens, targets, batch, seq);
+    model->model->Backward(1.0f);
+    if (optimizer != nullptr) optimizer->opt->Step(++optimizer->steps_done);
+    return loss;
+  }, kNaN);
+}
+float nanochat_rl_step(nanochat_model* model, nanochat_optim* optimizer, const int* tokens, const int* targets,
+                       const float* advantages, int batch, int seq, int num_passes, int examples_per_rank, int step) {
+  if (model == nullptr || tokens == nullptr || targets == nullptr || advantages == nullptr || batch <= 0 || seq <= 0 ||
+      num_passes <= 0 || examples_per_rank <= 0) {
+    ncb_set_error("nanochat_rl_step: invalid argument");
+    return kNaN;
+  }
+  return Guard([&]() {
+    return ncb::RlStep(model->model.get(), optimizer ? optimizer->opt.get() : nullptr, tokens, targets, advantages, batch,
+                       seq, num_passes, examples_per_rank, step);
+  }, kNaN);
+}
+
+int nanochat_param_count(nanochat_model* model) {
+  return model == nullptr ? 0 : static_cast<int>(model->model->params().size());
+}
+int nanochat_param_info(nanochat_model* model, int index, nanochat_param* out) {
+  if (model == nullptr || out == nullptr || index < 0 || index >= nanochat_param_count(model)) return 0;
+  const ncb::CpuParam& p = model->model->params()[static_cast<std::size_t>(index)];
+  out->name = p.name.c_str();
+  out->value = model->model->value(p);
+  out->grad = model->model->grad(p);
+  out->count = static_cast<int64_t>(p.count);
+  out->rows = p.rows, out->cols = p.cols;
+  return 1;
+}
+int64_t nanochat_param_read(nanochat_model* model, int index, int grad, int64_t offset, int64_t count, void* data) {
+  if (model == nullptr || data == nullptr || index < 0 || index >= nanochat_param_count(model)) return 0;
+  const ncb::CpuParam& p = model->model->params()[static_cast<std::size_t>(index)];
+  if (offset < 0 || offset >= static_cast<int64_t>(p.count)) return 0;
+  const int64_t n = std::min<int64_t>(count, static_cast<int64_t>(p.count) - offset);
+  const float* src = (grad ? model->model->grad(p) : model->model->value(p)) + offset;
+  std::memcpy(data, src, static_cast<std::size_t>(n) * sizeof(float));
+  return n;
+}
+int64_t nanochat_param_write(nanochat_model* model, int index, int grad, int64_t offset, int64_t count,
+                             const void* data) {
+  if (model == nullptr || data == nullptr || index < 0 || index >= nanochat_param_count(model)) return 0;
+  const ncb::CpuParam& p = model->model->params()[static_cast<std::size_t>(index)];
+  if (offset < 0 || offset >= static_cast<int64_t>(p.count)) return 0;
+  const int64_t n = std::min<int64_t>(count, static_cast<int64_t>(p.count) - offset);
+  float* dst = (grad ? model->model->grad(p) : model->model->value(p)) + offset;
+  std::memcpy(dst, data, static_cast<std::size_t>(n) * sizeof(float));
+  return n;
+}
+void nanochat_save(nanochat_model* model, const char* path) {
+  std::string err;
+  if (model == nullptr || path == nullptr || !model->model->Save(path, &err)) ncb_set_error("nanochat_save: " + err);
+}
+void nanochat_load(nanochat_model* model, const char* path) {
+  std::string err;
+  if (model == nullptr || path == nullptr || !model->model->Load(path, &err)) ncb_set_error("nanochat_load: " + err);
+}
+
+nanochat_optim* nanochat_optim_create(nanochat_model* model, const nanochat_optim_config* c) {
+  if (model == nullptr || c == nullptr) return nullptr;
+  ncb::OptimConfig o;
+  o.unembedding_lr = c->unembedding_lr, o.embedding_lr = c->embedding_lr, o.matrix_lr = c->matrix_lr;
+  o.scalar_lr = c->scalar_lr, o.weight_decay = c->weight_decay, o.muon_ns_steps = c->muon_ns_steps;
+  o.muon_beta2 = c->muon_beta2, o.adam_eps = c->adam_eps, o.clip = c->clip;
+  o.num_iterations = c->num_iterations, o.warmup_steps = c->warmup_steps, o.warmdown_ratio = c->warmdown_ratio;
+  o.final_lr_frac = c->final_lr_frac, o.weight_decay_base = c->weight_decay_base;
+  o.muon_momentum_warmup_steps = c->muon_momentum_warmup_steps, o.muon_momentum_start = c->muon_momentum_start;
+  o.muon_momentum_peak = c->muon_momentum_peak, o.muon_momentum_final = c->muon_momentum_final;
+  auto* h = new nanochat_optim();
+  h->opt = std::make_unique<ncb::CpuOptimizer>(model->model.get(), o);
+  h->model = model;
+  return h;
+}
+void nanochat_optim_step(nanochat_optim* optimizer, int step) {
+  if (optimizer == nullptr) return;
+  Guard([&]() { return optimizer->opt->Step(step), 0; }, 0);
+  optimizer->steps_done = step;
+}
+float nanochat_optim_grad_norm(nanochat_optim* optimizer) { return optimizer ? optimizer->opt->grad_norm() : 0.0f; }
+void nanochat_optim_free(nanochat_optim* optimizer) { delete optimizer; }
+
+void nanochat_score_batch(nanochat_model* model, const int* tokens, int batch, int seq, const int* lengths,
+                          const nanochat_focus* focus, nanochat_score_result* out) {
+  if (model == nullptr || tokens == nullptr || out == nullptr || batch <= 0 || seq <= 0) return;
+  Guard([&]() {
+    std::vector<ncb::FocusRequest> req;
+    if (focus != nullptr) {
+      req.resize(static_cast<std::size_t>(batch));
+      for (int b = 0; b < batch; ++b) {
+        req[b].position = focus[b].position;
+        if (focus[b].ids != nullptr && focus[b].count > 0) req[b].ids.assign(focus[b].ids, focus[b].ids + focus[b].count);
+        if (req[b].ids.empty()) req[b].position = -1;
+      }
+    }
+    auto rows = ncb::ScoreBatch(model->model.get(), tokens, batch, seq, lengths, focus ? req.data() : nullptr);
+    model->score_nll.resize(rows.size()), model->score_argmax.resize(rows.size()), model->score_focus.resize(rows.size());
+    for (std::size_t b = 0; b < rows.size(); ++b) {
+      model->score_nll[b] = std::move(rows[b].nll);
+      model->score_argmax[b] = std::move(rows[b].argmax);
+      model->score_focus[b] = std::move(rows[b].focus_logits);
+      out[b].nll = model->score_nll[b].data();
+      out[b].argmax = model->score_argmax[b].data();
+      out[b].focus_logits = model->score_focus[b].empty() ? nullptr : model->score_focus[b].data();
+    }
+    return 0;
+  }, 0);
+}
+
+void nanochat_generate(nanochat_model* model, const int* prompt, int length, const nanochat_generate_params* params,
+                       nanochat_sequences* out) {
+  if (model == nullptr || prompt == nullptr || params == nullptr || out == nullptr || length <= 0) return;
+  Guard([&]() {
+    FillSequences(model, ncb::GenerateBatch(model->model.get(), prompt, length, ToOptions(*params)), out);
+    return 0;
+  }, 0);
+}
+
+void nanochat_generate_multi(nanochat_model* model, const int* prompts, const nanochat_generate_multi_params* params,
+                             nanochat_sequences* out) {
+  if (model == nullptr || prompts == nullptr || params == nullptr || out == nullptr || params->num_prompts <= 0 ||
+      params->prompt_len <= 0)
+    return;
+  Guard([&]() {
+    std::vector<ncb::GeneratedRow> all;
+    ncb::GenerateOptions base = ToOptions(params->params);
+    const int S = base.num_samples;
+    for (int p = 0; p < params->num_prompts; ++p) {
+      ncb::GenerateOptions o = base;
+      if (params->row_stops != nullptr) o.stop_ids.assign(params->row_stops + p * S, params->row_stops + (p + 1) * S);
+      auto rows = ncb::GenerateBatch(model->model.get(), prompts + static_cast<std::size_t>(p) * params->prompt_len,
+                                     params->prompt_len, o, p * S);
+      for (auto& r : rows) all.push_back(std::move(r));
+    }
+    FillSequences(model, all, out);
+    return 0;
+  }, 0);
+}
+
+float nanochat_eval_bpb(nanochat_model* model, nanochat_loader* loader, int steps) {
+  const float inf = std::numeric_limits<float>::infinity();
+  if (model == nullptr || loader == nullptr || steps <= 0 || loader->batch <= 0 || loader->seq <= 0) return inf;
+  return Guard([&]() {
+    const std::size_t rows = static_cast<std::size_t>(loader->batch) * loader->seq;
+    std::vector<int> tokens(rows), targets(rows);
+    int vocab = 0;
+    const uint8_t* bytes = nanochat_loader_token_bytes(loader, &vocab);
+    double nats = 0.0;
+    long long total = 0;
+    for (int s = 0; s < steps; ++s) {
+      if (!nanochat_loader_next(loader, tokens.data(), targets.data())) break;
+      model->model->ForwardLoss(tokens.data(), targets.data(), loader->batch, loader->seq);
+      const std::vector<float>& losses = model->model->losses();
+      for (std::size_t i = 0; i < rows; ++i) {
+        const int t = targets[i];
+        if (t < 0) continue;
+        const int b = bytes != nullptr ? (t < vocab ? bytes[t] : 0) : 1;
+        if (b <= 0) continue;
+        nats += losses[i];
+        total += b;
+      }
+    }
+    return total == 0 ? inf : static_cast<float>(nats / (std::log(2.0) * static_cast<double>(total)));
+  }, inf);
+}
+
+}  // extern "C"
