@@ -112,7 +112,7 @@ def build_extension(verbose: bool = False) -> str:
     inc += ["-I", os.path.join(cuda_home, "include"), "-I", sysconfig.get_paths()["include"], "-I", CSRC_CUDA]
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI) if hasattr(torch._C, "_GLIBCXX_USE_CXX11_ABI") else 1
     defs = ["-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={abi}"]
-    for part in ("rowops", "attention", "optim", "comm", "decode"):
+    for part in ("rowops", "attention", "optim", "comm", "decode", "fp8"):
         if os.path.exists(os.path.join(CSRC_CUDA, part + "_bind.cpp")):
             defs.append("-DNC_HAVE_" + part.upper())
     for src in cpp_sources:

@@ -117,6 +117,7 @@ void register_attention(pybind11::module_& m);
 void register_optim(pybind11::module_& m);
 void register_comm(pybind11::module_& m);
 void register_decode(pybind11::module_& m);
+void register_fp8(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogue", pybind11::arg("A"), pybind11::arg("B"),
@@ -143,5 +144,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #endif
 #ifdef NC_HAVE_DECODE
   register_decode(m);
+#endif
+#ifdef NC_HAVE_FP8
+  register_fp8(m);
 #endif
 }

@@ -33,8 +33,9 @@ __global__ void signal_kernel(PeerPtrs flags, int world, int my_rank, int slot, 
   }
 }
 
-__global__ void wait_kernel(const int* flags, int world, int slot, int value, int* status) {
-  if (threadIdx.x == 0) wait_flags(flags, world, slot, value, status);
+__global__ void wait_kernel(const int* flags, int world, int slot, int value, int* status,
+                            unsigned long long budget_ns) {
+  if (threadIdx.x == 0) wait_flags_bounded(flags + slot * world, world, value, status, budget_ns);
 }
 
 constexpr int kReduceUnroll = 4;
@@ -209,8 +210,10 @@ inline int grid_for(long long n, int per_thread, int cap) {
 void comm_signal(const PeerPtrs& flags, int world, int my_rank, int slot, int value, cudaStream_t s) {
   signal_kernel<<<1, 32, 0, s>>>(flags, world, my_rank, slot, value);
 }
-void comm_wait(const int* local_flags, int world, int slot, int value, int* status, cudaStream_t s) {
-  wait_kernel<<<1, 32, 0, s>>>(local_flags, world, slot, value, status);
+void comm_wait(const int* local_flags, int world, int slot, int value, int* status, cudaStream_t s, int budget_ms) {
+  const unsigned long long budget = budget_ms > 0 ? static_cast<unsigned long long>(budget_ms) * 1000000ull
+                                                  : kPeerWaitBudgetNs;
+  wait_kernel<<<1, 32, 0, s>>>(local_flags, world, slot, value, status, budget);
 }
 void comm_reduce_pull(const PeerPtrs& grads, int world, int my_rank, const Segment* segs_dev, int nsegs,
                       long long total, float scale, const int* local_flags, int slot, int value, double* sumsq,

@@ -22,7 +22,10 @@ struct Segment {
 void comm_signal(const PeerPtrs& flags, int world, int my_rank, int slot, int value, cudaStream_t s);
 
 // Spin (bounded) until flags[slot * world + r] >= value for every r; records kErrWaitPeer on expiry.
-void comm_wait(const int* local_flags, int world, int slot, int value, int* status, cudaStream_t s);
+// `budget_ms` <= 0: the default peer-wait budget (20 s). On expiry the status word becomes kErrWaitPeer and the
+// kernel returns; the context stays usable.
+void comm_wait(const int* local_flags, int world, int slot, int value, int* status, cudaStream_t s,
+               int budget_ms = 0);
 
 // Gradient reduce-scatter by peer loads: for every element of this rank's segments,
 //   out[e] = scale * sum_{r = 0..world-1} grads[r][e]   (fixed rank order)

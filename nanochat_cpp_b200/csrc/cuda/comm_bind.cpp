@@ -23,9 +23,9 @@ void comm_signal(const std::vector<int64_t>& flag_ptrs, int64_t my_rank, int64_t
   nc::comm_signal(to_peers(flag_ptrs), static_cast<int>(flag_ptrs.size()), my_rank, slot, value, cur());
 }
 
-void comm_wait(const Tensor& flags, int64_t world, int64_t slot, int64_t value, Tensor status) {
+void comm_wait(const Tensor& flags, int64_t world, int64_t slot, int64_t value, Tensor status, int64_t budget_ms) {
   const c10::cuda::CUDAGuard g(flags.device());
-  nc::comm_wait(flags.data_ptr<int>(), world, slot, value, status.data_ptr<int>(), cur());
+  nc::comm_wait(flags.data_ptr<int>(), world, slot, value, status.data_ptr<int>(), cur(), static_cast<int>(budget_ms));
 }
 
 // segs: int64 [nsegs, 2] (offset, count) on the device
@@ -70,7 +70,8 @@ void comm_muon_apply_push(Tensor& master, const std::vector<int64_t>& value_ptrs
 
 void register_comm(pybind11::module_& m) {
   m.def("comm_signal", &comm_signal);
-  m.def("comm_wait", &comm_wait);
+  m.def("comm_wait", &comm_wait, pybind11::arg("flags"), pybind11::arg("world"), pybind11::arg("slot"),
+        pybind11::arg("value"), pybind11::arg("status"), pybind11::arg("budget_ms") = 0);
   m.def("comm_reduce_pull", &comm_reduce_pull);
   m.def("comm_adamw_push", &comm_adamw_push);
   m.def("comm_muon_apply_push", &comm_muon_apply_push);

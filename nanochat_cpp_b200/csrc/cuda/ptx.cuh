@@ -107,13 +107,14 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Wait until flags[i] >= value for i in [0, count). Returns false (status <- kErrWaitPeer) on expiry.
-__device__ __forceinline__ bool wait_flags_bounded(const int* flags, int count, int value, int* status) {
+__device__ __forceinline__ bool wait_flags_bounded(const int* flags, int count, int value, int* status,
+                                                   unsigned long long budget_ns = kPeerWaitBudgetNs) {
   const unsigned long long t0 = globaltimer_ns();
   for (int r = 0; r < count; ++r) {
     unsigned spins = 0;
     while (ld_acquire_sys(flags + r) < value) {
       if ((++spins & 0xff) == 0) {
-        if (globaltimer_ns() - t0 > kPeerWaitBudgetNs) {
+        if (globaltimer_ns() - t0 > budget_ns) {
           if (status != nullptr) atomicCAS(status, 0, kErrWaitPeer);
           return false;
         }

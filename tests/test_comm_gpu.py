@@ -95,3 +95,25 @@ def test_gemm_waits_for_flags_and_gathers_weight():
     out3 = K.gemm(x, w_local, gather_src=w_owner.data_ptr(), gather_counter=counter, gather_base=base)
     assert (out3.float() - 2 * want).abs().max() <= 2e-2 * 2 * want.abs().max()
     K.check_status()
+
+
+def test_wait_that_runs_out_reports_status_and_context_survives():
+    """A flag that nothing sets: the wait gives up after its budget, records the peer-wait code in the status
+    word, and the next kernels on the same context run normally."""
+    import time
+    K = _K()
+    dev = torch.device("cuda")
+    K.check_status()
+    flags = torch.zeros(8, dtype=torch.int32, device=dev)
+    t0 = time.perf_counter()
+    K._C.comm_wait(flags, 2, 1, 5, K._C.status_tensor(dev.index), 300)       # 0.3 s budget
+    torch.cuda.synchronize()
+    assert 0.25 < time.perf_counter() - t0 < 5.0
+    with pytest.raises(RuntimeError, match="status code 5"):
+        K.check_status()
+    K.check_status()                                                           # the word was cleared
+    a = torch.randn(256, 256, device=dev).to(torch.bfloat16)
+    assert torch.isfinite(K.gemm(a, a).float()).all()
+    flags.fill_(5)
+    K._C.comm_wait(flags, 2, 1, 5, K._C.status_tensor(dev.index), 300)        # a satisfied wait returns at once
+    K.check_status()
