@@ -1,0 +1,45 @@
+"""Block-scaled fp8 GEMM against this package's bf16 GEMM and cuBLAS bf16 on the d26 / d20 linear shapes.
+
+    python -m nanochat_cpp_b200.bench.fp8_bench
+
+Times (CUDA events, 3 warm-ups, L2 flushed between iterations) the GEMM alone and the GEMM plus the activation
+quantization that a forward pass needs (weights are quantized once per optimizer step, not per call).
+"""
+from __future__ import annotations
+
+import json
+
+import torch
+
+from ..ops import cuda as K
+from ..ops import fp8
+from .timing import time_cuda
+
+SHAPES = [("d26.qkv", 32768, 4992, 1664), ("d26.fc", 32768, 6656, 1664), ("d26.mlp_proj", 32768, 1664, 6656),
+          ("d20.qkv", 65536, 3840, 1280), ("d20.fc", 65536, 5120, 1280), ("d20.mlp_proj", 65536, 1280, 5120)]
+
+
+def main():
+    for name, M, N, Kd in SHAPES:
+        Np = (N + 127) // 128 * 128
+        x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(Np, Kd, device="cuda") * 0.02).to(torch.bfloat16)
+        wq, sw = fp8.quantize_blocks(w)
+        wq = wq[:N].contiguous()
+        xq, sx = fp8.quantize_rows(x)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t_fp8 = time_cuda(lambda: fp8.fp8_gemm(xq, sx, wq, sw, out))["median_ms"]
+        t_q = time_cuda(lambda: fp8.quantize_rows(x))["median_ms"]
+        t_bf16 = time_cuda(lambda: K.gemm(x, w[:N], out=out))["median_ms"]
+        t_lib = time_cuda(lambda: torch.matmul(x, w[:N].t(), out=out))["median_ms"]
+        flops = 2.0 * M * N * Kd
+        print(json.dumps(dict(name=name, m=M, n=N, k=Kd, fp8_ms=round(t_fp8, 4), quantize_ms=round(t_q, 4),
+                              bf16_ms=round(t_bf16, 4), cublas_bf16_ms=round(t_lib, 4),
+                              fp8_tflops=round(flops / t_fp8 / 1e9, 1), bf16_tflops=round(flops / t_bf16 / 1e9, 1),
+                              speedup_gemm=round(t_bf16 / t_fp8, 3),
+                              speedup_with_quantize=round(t_bf16 / (t_fp8 + t_q), 3))))
+    K.check_status()
+
+
+if __name__ == "__main__":
+    main()

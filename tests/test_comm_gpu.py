@@ -102,7 +102,7 @@ def test_wait_that_runs_out_reports_status_and_context_survives():
     word, and the next kernels on the same context run normally."""
     import time
     K = _K()
-    dev = torch.device("cuda")
+    dev = torch.device("cuda", torch.cuda.current_device())
     K.check_status()
     flags = torch.zeros(8, dtype=torch.int32, device=dev)
     t0 = time.perf_counter()

@@ -13,14 +13,22 @@ def test_quantizers_match_definition():
     x = (torch.randn(300, 512, device="cuda", generator=g) * 3).to(torch.bfloat16)
     x[5] = 0                                     # an all-zero row keeps scale 1
     x[7, 130] = 1000.0                           # an outlier stays inside its own 128-block
+    def same(q, s, qr, sr):
+        # scales agree to an ulp of the division; codes agree except where that ulp moves a value across a
+        # rounding boundary (rare, and then by one code)
+        assert torch.allclose(s, sr, rtol=3e-7, atol=0)
+        a, b = q.view(torch.float8_e4m3fn).float(), qr.float()
+        differ = a != b
+        assert differ.float().mean().item() < 2e-3
+        assert ((a - b).abs()[differ] <= 0.126 * b.abs()[differ].clamp_min(2 ** -6)).all()
+
     q, s = fp8.quantize_rows(x)
-    qr, sr = fp8.ref_quantize_rows(x)
-    assert torch.equal(s, sr)
-    assert torch.equal(q.view(torch.float8_e4m3fn).float(), qr.float())
+    same(q, s, *fp8.ref_quantize_rows(x))
+    assert float(s[0, 5]) == 1.0 and (q[5] == 0).all()                      # the all-zero row
+    assert float(s[1, 7]) == pytest.approx(1000.0 / 448.0, rel=1e-6) and float(s[0, 7]) < 0.1
     w = (torch.randn(256, 384, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
     q, s = fp8.quantize_blocks(w)
-    qr, sr = fp8.ref_quantize_blocks(w)
-    assert torch.equal(s, sr) and torch.equal(q.view(torch.float8_e4m3fn).float(), qr.float())
+    same(q, s, *fp8.ref_quantize_blocks(w))
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 640, 512), (1024, 1280, 1280), (257, 136, 384)])
