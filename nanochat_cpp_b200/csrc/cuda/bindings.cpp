@@ -6,6 +6,8 @@
 #include <map>
 #include <string>
 
+#include <cstdlib>
+
 #include "gemm_tcgen05.h"
 
 namespace {
@@ -105,6 +107,19 @@ void gemm(const torch::Tensor& A, const torch::Tensor& B, torch::Tensor& C, bool
     g.gather_bytes = B.numel() * 2;
     g.gather_counter = gather_counter->data_ptr<int>();
     g.gather_base = static_cast<int>(gather_base);
+  }
+  // decode-shaped products take the cluster split-K kernel
+  static const bool skinny_enabled = [] {
+    const char* e = std::getenv("NANOCHAT_GEMM_SKINNY");
+    return e == nullptr || e[0] != '0';
+  }();
+  const bool plain = g.epi == nc::kEpiBf16 && g.alpha == 1.0f;
+  const bool res = g.epi == nc::kEpiBf16Res && g.alpha == 1.0f && g.beta == 1.0f;
+  if (skinny_enabled && g.M <= 64 && g.N >= 128 && g.N <= 16384 && !a_mn && !b_mn && g.batch == 1 &&
+      (plain || res || g.epi == nc::kEpiRelu2) && g.wait_flags == nullptr && g.gather_src == nullptr) {
+    const char* err = nc::gemm_skinny(g, at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(err == nullptr, err);
+    return;
   }
   const char* err = nc::gemm_bf16(g, at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(err == nullptr, err);

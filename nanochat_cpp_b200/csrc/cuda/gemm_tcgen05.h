@@ -49,5 +49,8 @@ struct GemmArgs {
 
 // Returns nullptr on success or a static error string.
 const char* gemm_bf16(const GemmArgs& args, cudaStream_t stream);
+// Decode-shaped products (M <= 64, K-major operands, batch 1, epilogues bf16 / bf16+residual / relu^2): weight rows
+// on the MMA's M side, K split over a thread-block cluster (gemm_skinny.cu).
+const char* gemm_skinny(const GemmArgs& args, cudaStream_t stream);
 
 }  // namespace nc

@@ -94,3 +94,22 @@ def test_batched():
     y = K.gemm(a2, X, b_mn=True, epi=K.EPI_BF16_RES, r=X, alpha=1.0, beta=3.0)
     _close(y, a2.float() @ X.float() + 3.0 * X.float())
     K.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 1280, 1280), (64, 3840, 1280), (7, 1280, 5120), (64, 65536, 1280),
+                                   (33, 520, 192), (1, 128, 64)])
+def test_skinny_decode_gemm(M, N, K):
+    """Small-M products (cluster split-K kernel): plain, residual and relu^2 epilogues."""
+    from nanochat_cpp_b200.ops import cuda as Kmod
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    r = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    want = x.float() @ w.float().t()
+    tol = 2e-2 * want.abs().max()
+    assert (Kmod.linear_fwd(x, w).float() - want).abs().max() <= tol
+    assert (Kmod.linear_fwd(x, w, residual=r).float() - (want + r.float())).abs().max() <= tol + 2e-2 * r.abs().max()
+    pre, act = Kmod.linear_relu2_fwd(x, w)
+    assert (pre.float() - want).abs().max() <= tol
+    assert torch.equal(act, torch.relu(pre.float()).square().to(torch.bfloat16))
+    Kmod.check_status()
