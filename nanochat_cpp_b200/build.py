@@ -32,7 +32,7 @@ CORE_PATH = os.path.join(HERE, "libnanochat_core.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 CXX_FLAGS = ["-O2", "-fPIC", "-std=c++17", "-Wall", "-Wno-unused-function"]
-HOST_FLAGS = ["-O2", "-fPIC", "-std=c++20", "-Wall", "-Wextra", "-pthread"]
+HOST_FLAGS = ["-O3", "-fPIC", "-std=c++20", "-Wall", "-Wextra", "-pthread", "-fopenmp"]
 
 
 def _nvcc() -> str:
@@ -158,7 +158,7 @@ def build_core(verbose: bool = False) -> str:
     key = _hash(objs, "link-core")
     if os.path.exists(CORE_PATH) and os.path.exists(stamp) and open(stamp).read() == key:
         return CORE_PATH
-    _run(["g++", "-shared", "-pthread", "-o", CORE_PATH] + objs, os.path.join(BUILD_DIR, "link_core.log"))
+    _run(["g++", "-shared", "-pthread", "-fopenmp", "-o", CORE_PATH] + objs, os.path.join(BUILD_DIR, "link_core.log"))
     with open(stamp, "w") as f:
         f.write(key)
     if verbose:
