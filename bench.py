@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--batch", type=int, default=32, help="sequences per GPU per step")
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-batch (0 = whole batch)")
     ap.add_argument("--transport", default=os.environ.get("NANOCHAT_DP_TRANSPORT", "auto"))
+    ap.add_argument("--fp8", action="store_true", help="block-scaled E4M3 forward products for QKV and MLP up-projection")
     return ap.parse_args()
 
 
@@ -135,7 +136,7 @@ def main():
     cfg = preset(args.preset)
     micro = args.micro_batch or args.batch
     accum = args.batch // micro
-    tc = TrainConfig(batch=micro, grad_accum=accum, num_iterations=1000, seed=1234)
+    tc = TrainConfig(batch=micro, grad_accum=accum, num_iterations=1000, seed=1234, fp8=args.fp8)
     tc.sched.warmup_steps = 0
     trainer = Trainer(cfg, tc, device=dev, dp=dp)
     from nanochat_cpp_b200.ops import cuda as K
@@ -218,7 +219,8 @@ def main():
             "metric": "train_tokens_per_sec", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": round(value / PUBLISHED_TOK_S, 3),
-            "dtype": "bf16", "data": "synthetic Zipf(1.1) token ids, random-init weights", "impl": "ours",
+            "dtype": "fp8-e4m3(qkv,fc fwd)+bf16" if args.fp8 else "bf16",
+            "data": "synthetic Zipf(1.1) token ids, random-init weights", "impl": "ours",
             "mfu_of_measured_sustained": round(value * fl_tok / world / (peaks["bf16_tflops_sustained"] * 1e12), 4),
             "model_tflops_per_gpu": round(value * fl_tok / world / 1e12, 1),
             "config": {"model": args.preset, "layers": cfg.num_layers, "hidden": cfg.hidden_dim,

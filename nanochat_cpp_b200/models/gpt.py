@@ -36,7 +36,10 @@ from .params import ParamStore, init_weights
 
 class GPT:
     def __init__(self, cfg: Config, device="cpu", dtype: torch.dtype = torch.bfloat16, seed: int = 0,
-                 init: bool = True, head_chunk_rows: int = 8192, allocator=None):
+                 init: bool = True, head_chunk_rows: int = 8192, allocator=None, fp8: bool = False):
+        """`fp8`: run the forward QKV and MLP up-projection products in block-scaled E4M3 (1x128 activation scales,
+        128x128 weight scales, bf16 out); attention, norms, the projections with fused residuals, the LM head and
+        the whole backward stay in bf16. Call `refresh_fp8()` after every optimizer step."""
         cfg.validate()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -50,6 +53,27 @@ class GPT:
         self.on_layer_grads_ready: Optional[Callable[[int], None]] = None
         self.on_head_grads_ready: Optional[Callable[[], None]] = None
         self.on_embed_grads_ready: Optional[Callable[[], None]] = None
+        self.fp8 = bool(fp8) and self.device.type == "cuda"
+        self._fp8_w: Dict[str, object] = {}
+        if self.fp8:
+            self.refresh_fp8()
+
+    def refresh_fp8(self) -> None:
+        """Re-quantize the fp8 weight copies from the bf16 compute copy (after an optimizer step)."""
+        if not self.fp8:
+            return
+        from ..ops import fp8 as F8
+        cfg = self.cfg
+        for i in range(cfg.num_layers):
+            wqkv = self.params.qkv_view(i)
+            fc = self._w(i, "mlp.c_fc")
+            for key, w in ((f"qkv{i}", wqkv), (f"fc{i}", fc)):
+                if w is None or w.shape[0] % 128 or w.shape[1] % 128:
+                    continue
+                if key in self._fp8_w:
+                    self._fp8_w[key].refresh(w)
+                else:
+                    self._fp8_w[key] = F8.Fp8Weight(w)
 
     # ------------------------------------------------------------------
     def rope(self, seq: int):
@@ -85,7 +109,17 @@ class GPT:
         M = B * T
         xr, h, rstd1 = ops.blend_norm_fwd(x, x0, self._lam("resid_lambdas", i), self._lam("x0_lambdas", i))
         wqkv = P.qkv_view(i)
-        if wqkv is not None:
+        hq = None
+        if self.fp8 and (f"qkv{i}" in self._fp8_w):
+            from ..ops import fp8 as F8
+            hq = F8.quantize_rows(h)
+        if hq is not None:
+            w8 = self._fp8_w[f"qkv{i}"]
+            qkv = F8.fp8_gemm(hq[0], hq[1], w8.q, w8.s)
+            q_pre = qkv[:, : cfg.query_dim]
+            k_pre = qkv[:, cfg.query_dim: cfg.query_dim + cfg.kv_dim]
+            v = qkv[:, cfg.query_dim + cfg.kv_dim:]
+        elif wqkv is not None:
             qkv = ops.linear_fwd(h, wqkv)
             q_pre = qkv[:, : cfg.query_dim]
             k_pre = qkv[:, cfg.query_dim: cfg.query_dim + cfg.kv_dim]
@@ -103,7 +137,11 @@ class GPT:
         attn, lse = ops.attention_fwd(q, k, v4, cfg.window_left(i))
         x_mid = ops.linear_fwd(attn.view(M, H * D), self._w(i, "attn.c_proj"), residual=xr)
         h2, rstd2 = ops.rmsnorm_fwd(x_mid)
-        pre, act = ops.linear_relu2_fwd(h2, self._w(i, "mlp.c_fc"))
+        if self.fp8 and (f"fc{i}" in self._fp8_w):
+            from ..ops import fp8 as F8
+            pre, act = F8.linear_fwd_fp8(h2, self._fp8_w[f"fc{i}"], relu2=True)
+        else:
+            pre, act = ops.linear_relu2_fwd(h2, self._w(i, "mlp.c_fc"))
         x_out = ops.linear_fwd(act, self._w(i, "mlp.c_proj"), residual=x_mid)
         if save is not None:
             save["layers"].append(dict(x=x, xr=xr, rstd1=rstd1, q_pre=q_pre, k_pre=k_pre, q=q, k=k, v=v4,

@@ -35,6 +35,7 @@ class TrainConfig:
     log: str = ""
     dtype: str = "bf16"
     head_chunk_rows: int = 8192
+    fp8: bool = False
     optim: OptimizerConfig = field(default_factory=OptimizerConfig)
     sched: SchedulerConfig = field(default_factory=SchedulerConfig)
 
@@ -47,7 +48,7 @@ class Trainer:
         self.device = torch.device(device)
         dtype = torch.bfloat16 if tc.dtype == "bf16" else torch.float32
         self.model = model or GPT(cfg, self.device, dtype, seed=tc.seed, head_chunk_rows=tc.head_chunk_rows,
-                                  allocator=None if dp is None else dp.allocator())
+                                  allocator=None if dp is None else dp.allocator(), fp8=tc.fp8)
         if tc.sched.num_iterations == 0:
             tc.sched.num_iterations = tc.num_iterations
         self.dp = dp
@@ -83,6 +84,13 @@ class Trainer:
             self.dp.finish_step(self.step_count)
         else:
             self.optimizer.step(self.step_count)
+        if m.fp8:
+            if self.dp is not None and getattr(self.dp, "fused", None) is not None:
+                # owners push the new bf16 weights asynchronously: wait (on the stream) for this step's pushes
+                f = self.dp.fused
+                f.wait(f.slot_adamw, self.step_count)
+                f.wait(f.slot_muon, self.step_count)
+            m.refresh_fp8()
         self.last_loss = total / accum
         return self.last_loss
 

@@ -51,3 +51,35 @@ def test_fp8_gemm_matches_dequantized_product(M, N, K):
     fp8.fp8_gemm(xq, sx, wq, sw, pre, act)
     assert torch.equal(pre, out) and torch.equal(act, torch.relu(out.float()).square().to(torch.bfloat16))
     Kmod.check_status()
+
+
+def test_model_forward_in_fp8_tracks_bf16_and_trains():
+    from nanochat_cpp_b200.config import Config
+    from nanochat_cpp_b200.models import GPT
+    from nanochat_cpp_b200.optim import Optimizer
+    cfg = Config(num_layers=2, num_heads=2, num_kv_heads=2, hidden_dim=256, seq_len=256, vocab_size=512,
+                 padded_vocab_size=512, window_pattern="SL", short_window_override=128)
+    a = GPT(cfg, "cuda", torch.bfloat16, seed=3)
+    b = GPT(cfg, "cuda", torch.bfloat16, seed=3, fp8=True)
+    assert len(b._fp8_w) == 4
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for m in (a, b):                      # non-zero projections so that the fp8 products matter
+        gg = torch.Generator().manual_seed(1)
+        for s in m.params.specs:
+            if s.name.endswith("c_proj.weight"):
+                m.params.m(s.name).copy_((torch.randn(s.shape, generator=gg) * 0.02).cuda())
+        m.params.sync_compute()
+    b.refresh_fp8()
+    tok = torch.randint(0, 512, (4, 256), device="cuda", generator=g)
+    tgt = torch.roll(tok, -1, 1)
+    la, lb = float(a.forward_loss(tok, tgt)), float(b.forward_loss(tok, tgt))
+    assert abs(la - lb) < 2e-2 * abs(la)
+    opt = Optimizer(b.params)
+    first = None
+    for step in range(1, 6):
+        b.zero_grad()
+        loss = float(b.forward_backward(tok, tgt))
+        opt.step(step)
+        b.refresh_fp8()
+        first = loss if first is None else first
+    assert loss < first
