@@ -44,6 +44,11 @@ enum class DType : std::uint32_t { kFp32 = 0, kBf16 = 1, kInt8 = 2, kFp8E4M3 = 4
 std::size_t DTypeSize(DType t);
 std::uint16_t FloatToBf16(float v);  // round to nearest even
 float Bf16ToFloat(std::uint16_t v);
+// fp8 codecs (fp8.cc): saturating round-to-nearest-even; E4M3 max 448 (no infinities), E5M2 max 57344
+std::uint8_t FloatToE4M3(float v);
+float E4M3ToFloat(std::uint8_t c);
+std::uint8_t FloatToE5M2(float v);
+float E5M2ToFloat(std::uint8_t c);
 
 struct TensorAttribute {
   std::string name;

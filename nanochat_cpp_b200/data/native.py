@@ -351,3 +351,20 @@ def read_parquet_strings(path: str, column: str = "text") -> List[bytes]:
 def sample_token(logits: np.ndarray, temperature: float, top_k: int, seed: int, row: int = 0, step: int = 0) -> int:
     arr = np.ascontiguousarray(logits, dtype=np.float32)
     return lib().ncb_sample_token(arr.ctypes.data, arr.size, temperature, top_k, seed, row, step)
+
+
+def fp8_encode(values, fmt: str = "e4m3") -> np.ndarray:
+    """Saturating round-to-nearest-even fp8 codes (uint8) of `values`; `fmt` is "e4m3" or "e5m2"."""
+    v = np.ascontiguousarray(np.asarray(values, dtype=np.float32).reshape(-1))
+    out = np.empty(v.size, dtype=np.uint8)
+    lib().ncb_fp8_encode(v.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), C.c_longlong(v.size),
+                         0 if fmt == "e4m3" else 1)
+    return out.reshape(np.asarray(values).shape)
+
+
+def fp8_decode(codes, fmt: str = "e4m3") -> np.ndarray:
+    c = np.ascontiguousarray(np.asarray(codes, dtype=np.uint8).reshape(-1))
+    out = np.empty(c.size, dtype=np.float32)
+    lib().ncb_fp8_decode(c.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), C.c_longlong(c.size),
+                         0 if fmt == "e4m3" else 1)
+    return out.reshape(np.asarray(codes).shape)

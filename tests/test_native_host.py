@@ -178,3 +178,38 @@ def test_sampler():
     draws = {native.sample_token(logits, 1.0, 2, 7, row=r) for r in range(64)}
     assert draws <= {1, 3} and len(draws) == 2
     assert native.sample_token(logits, 1.0, 2, 7, row=3, step=2) == native.sample_token(logits, 1.0, 2, 7, row=3, step=2)
+
+
+def test_fp8_host_codecs_match_torch():
+    import torch
+    from nanochat_cpp_b200.data.native import fp8_decode, fp8_encode
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(5000).astype(np.float32) * s for s in (1e-3, 0.1, 1, 30, 500, 1e5)] +
+                       [np.array([0.0, -0.0, 448, 449, -1e9, 2 ** -9, 2 ** -10, 3 * 2 ** -10], dtype=np.float32)])
+    for fmt, dt, mx in (("e4m3", torch.float8_e4m3fn, 448.0), ("e5m2", torch.float8_e5m2, 57344.0)):
+        codes = fp8_encode(x, fmt)
+        want = torch.from_numpy(np.clip(x, -mx, mx)).to(dt).float().numpy()
+        assert np.array_equal(fp8_decode(codes, fmt), want)
+
+
+def test_spec_profile_and_plan():
+    import pytest
+    from nanochat_cpp_b200.plan import ModelSpec, SpecError, build_plan, device_profiles, profile_for
+    spec = ModelSpec.default()
+    cfg = spec.to_config()
+    assert (cfg.num_layers, cfg.hidden_dim, cfg.window_pattern, cfg.value_embedding) == (12, 768, "SSSL", True)
+    assert [cfg.window_left(i) >= 0 for i in range(12)] == [b["attention"] == "sliding_window" for b in spec.blocks]
+    profs = device_profiles()
+    assert profile_for("NVIDIA B200").device == "b200" and profile_for("Xeon").device == "cpu"
+    plan = build_plan(spec, profs["b200"])
+    assert all(r.choice == "kernel" for r in plan.rows) and "fused families" in plan.line()
+    cpu_plan = build_plan(spec, profs["cpu"], precision="fp32")
+    assert all(r.choice == "composition" for r in cpu_plan.rows)
+    assert {r.family for r in build_plan(spec, profs["b200"], graph="decode").rows} >= {"decode_attention"}
+    with pytest.raises(SpecError):
+        build_plan(spec, profs["cpu"], precision="bf16")
+    bad = dict(spec_version=1, name="x", dimensions=dict(num_heads=2, hidden_dim=64), blocks=[dict(norm="layer_norm")])
+    with pytest.raises(SpecError, match="layer_norm"):
+        ModelSpec.from_json(bad)
+    with pytest.raises(SpecError, match="unknown spec keys"):
+        ModelSpec.from_json(dict(bad, colour="red"))
