@@ -22,6 +22,11 @@ struct AttnArgs {
   const void* dO = nullptr;
   long long do_stride_b = 0, do_stride_t = 0, do_stride_h = 0;
   float* delta = nullptr;  // [B, H, Tq] scratch: rowsum(dO * O)
+  // Optional scratch for dS^T [B, H, ds_tk, ds_tq] bf16 (ds_tk = Tk rounded up to 128, ds_tq = Tq rounded up to
+  // 128). When given, the dK/dV kernel stores the dS tiles it computes and dQ = dS K runs as a banded GEMM over
+  // them (attention_dq.cu) instead of recomputing scores and probabilities.
+  void* dS = nullptr;
+  long long ds_tk = 0, ds_tq = 0;
   void *dQ = nullptr, *dK = nullptr, *dV = nullptr;
   long long dq_stride_b = 0, dq_stride_t = 0, dq_stride_h = 0;
   long long dk_stride_b = 0, dk_stride_t = 0, dk_stride_h = 0;
@@ -34,5 +39,7 @@ const char* attention_fwd(const AttnArgs& args, cudaStream_t stream);
 // two query tiles per CTA, running output in TMEM with lazy rescaling (the default)
 const char* attention_fwd2(const AttnArgs& args, cudaStream_t stream);
 const char* attention_bwd(const AttnArgs& args, cudaStream_t stream);
+// dQ from stored dS^T (used by attention_bwd when AttnArgs::dS is set)
+const char* attention_dq_from_ds(const AttnArgs& args, cudaStream_t stream);
 
 }  // namespace nc

@@ -56,7 +56,7 @@ std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor
 
 void attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse,
                    const Tensor& d_o, Tensor& dq, Tensor& dk, Tensor& dv, int64_t window_left, double scale,
-                   int64_t q_offset, Tensor status) {
+                   int64_t q_offset, Tensor status, const c10::optional<Tensor>& ds_scratch) {
   const c10::cuda::CUDAGuard guard(q.device());
   nc::AttnArgs a;
   fill_common(a, q, k, v, window_left, scale, q_offset);
@@ -79,6 +79,16 @@ void attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
   a.dk_stride_b = dk.stride(0), a.dk_stride_t = dk.stride(1), a.dk_stride_h = dk.stride(2);
   a.dv_stride_b = dv.stride(0), a.dv_stride_t = dv.stride(1), a.dv_stride_h = dv.stride(2);
   a.status = status.data_ptr<int>();
+  if (ds_scratch.has_value()) {
+    // [B, H, Tk padded to 128, Tq padded to 128] bf16, contiguous
+    const Tensor& ds = *ds_scratch;
+    TORCH_CHECK(ds.dim() == 4 && ds.is_contiguous() && ds.scalar_type() == torch::kBFloat16 && ds.size(0) == a.B &&
+                    ds.size(1) == a.H && ds.size(2) % 128 == 0 && ds.size(3) % 128 == 0 && ds.size(2) >= a.Tk &&
+                    ds.size(3) >= a.Tq,
+                "ds_scratch must be a contiguous bf16 [B, H, Tk128, Tq128] tensor");
+    a.dS = ds.data_ptr();
+    a.ds_tk = ds.size(2), a.ds_tq = ds.size(3);
+  }
   const char* err = nc::attention_bwd(a, at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(err == nullptr, err);
 }
@@ -87,5 +97,8 @@ void attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
 
 void register_attention(pybind11::module_& m) {
   m.def("attention_fwd", &attention_fwd);
-  m.def("attention_bwd", &attention_bwd);
+  m.def("attention_bwd", &attention_bwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"),
+        pybind11::arg("lse"), pybind11::arg("d_o"), pybind11::arg("dq"), pybind11::arg("dk"), pybind11::arg("dv"),
+        pybind11::arg("window_left"), pybind11::arg("scale"), pybind11::arg("q_offset"), pybind11::arg("status"),
+        pybind11::arg("ds_scratch") = c10::optional<Tensor>());
 }

@@ -60,6 +60,8 @@ struct BwdParams {
   __nv_bfloat16* out2;  //    | dV
   long long o1_stride_b, o1_stride_t, o1_stride_h;
   long long o2_stride_b, o2_stride_t, o2_stride_h;
+  __nv_bfloat16* ds_out;       // DKV mode, optional: dS^T [B, H, ds_tk, ds_tq]
+  long long ds_tk, ds_tq;
   int* status;
 };
 
@@ -350,6 +352,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
           pk_ds[e / 2] = pack_bf16(dsv[0], dsv[1]);
           if (MODE == kModeDKV) pk_p[e / 2] = pack_bf16(pv[0], pv[1]);
         }
+        if (MODE == kModeDKV && p.ds_out != nullptr) {
+          // this thread's 32 consecutive query columns of key row prow (in bounds: the scratch is padded)
+          __nv_bfloat16* dsp = p.ds_out +
+                               ((static_cast<long long>(b) * p.H + (kvh * group + g)) * p.ds_tk + prow) * p.ds_tq + s0 +
+                               c32 * 32;
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq)
+            *reinterpret_cast<uint4*>(dsp + gq * 8) =
+                make_uint4(pk_ds[4 * gq], pk_ds[4 * gq + 1], pk_ds[4 * gq + 2], pk_ds[4 * gq + 3]);
+        }
 #pragma unroll
         for (int gq = 0; gq < 4; ++gq) {
           const int gran = (c32 * 4 + gq) ^ (row & 7);
@@ -493,6 +505,10 @@ const char* attention_bwd(const AttnArgs& a, cudaStream_t stream) {
   p.lse = a.lse;
   p.delta = a.delta;
   p.status = a.status;
+  p.ds_out = static_cast<__nv_bfloat16*>(a.dS);
+  p.ds_tk = a.ds_tk, p.ds_tq = a.ds_tq;
+  if (a.dS != nullptr && (a.ds_tk < (a.Tk + 127) / 128 * 128 || a.ds_tq < (a.Tq + 127) / 128 * 128 || a.ds_tq % 8))
+    return "attention_bwd: dS scratch is too small";
   const char* err;
   // dK, dV
   p.out1 = static_cast<__nv_bfloat16*>(a.dK);
@@ -503,7 +519,9 @@ const char* attention_bwd(const AttnArgs& a, cudaStream_t stream) {
   err = a.D == 128 ? launch_bwd<128, kModeDKV>(k128, v128, q64, do64, p, grid_kv, stream)
                    : launch_bwd<64, kModeDKV>(k128, v128, q64, do64, p, grid_kv, stream);
   if (err) return err;
+  if (a.dS != nullptr) return attention_dq_from_ds(a, stream);
   // dQ
+  p.ds_out = nullptr;
   p.out1 = static_cast<__nv_bfloat16*>(a.dQ);
   p.o1_stride_b = a.dq_stride_b, p.o1_stride_t = a.dq_stride_t, p.o1_stride_h = a.dq_stride_h;
   p.out2 = nullptr;

@@ -316,6 +316,29 @@ def attention_fwd(q, k, v, window_left=-1, scale=None, q_offset=None, variant=2)
     return o, lse
 
 
+_ds_scratch = {}
+_DS_LIMIT_BYTES = int(float(os.environ.get("NANOCHAT_ATTN_DS_GB", "6")) * (1 << 30))
+
+
+def _ds_workspace(q, k):
+    """Scratch for dS^T [B, H, Tk128, Tq128] (bf16), one per device and shape, reused by every layer. None when it
+    would exceed NANOCHAT_ATTN_DS_GB (default 6): the backward then recomputes dS for dQ instead of storing it."""
+    B, Tq, H, _ = q.shape
+    Tk = k.shape[1]
+    shape = (B, H, (Tk + 127) // 128 * 128, (Tq + 127) // 128 * 128)
+    nbytes = 2 * shape[0] * shape[1] * shape[2] * shape[3]
+    if nbytes > _DS_LIMIT_BYTES or _DS_LIMIT_BYTES <= 0:
+        return None
+    key = (q.device.index, shape)
+    ws = _ds_scratch.get(key)
+    if ws is None:
+        if len(_ds_scratch) > 4:
+            _ds_scratch.clear()
+        ws = torch.empty(shape, dtype=torch.bfloat16, device=q.device)
+        _ds_scratch[key] = ws
+    return ws
+
+
 def attention_bwd(q, k, v, o, lse, do, window_left=-1, scale=None, q_offset=None, out=None):
     """`out` may give (dq, dk, dv) destination views (e.g. column slices of one [M, 3C] buffer)."""
     import math
@@ -329,7 +352,7 @@ def attention_bwd(q, k, v, o, lse, do, window_left=-1, scale=None, q_offset=None
     if dv is None:
         dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
     _C.attention_bwd(q, k, v, o, lse, do, dq, dk, dv, int(window_left), float(scale),
-                     -1 if q_offset is None else int(q_offset), _status(q))
+                     -1 if q_offset is None else int(q_offset), _status(q), _ds_workspace(q, k))
     return dq, dk, dv
 
 
