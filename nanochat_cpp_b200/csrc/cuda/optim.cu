@@ -125,6 +125,125 @@ __global__ void __launch_bounds__(256) muon_apply_kernel(float* __restrict__ mas
   }
 }
 
+// ---- batched forms: one launch per shape group (grid.y = matrix), 16-byte accesses --------------------------
+// Stage 1 over P matrices given by pointer tables (gradients and momentum buffers live in different places).
+__global__ void __launch_bounds__(256) muon_nesterov_batched_kernel(const long long* __restrict__ grad_ptrs,
+                                                                    const long long* __restrict__ buf1_ptrs,
+                                                                    float* __restrict__ x, float* __restrict__ row_sumsq,
+                                                                    int rows, int cols, float mu,
+                                                                    const float* grad_scale) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int p = blockIdx.y, lane = threadIdx.x & 31;
+  const float gs = grad_scale ? *grad_scale : 1.0f;
+  const long long off = static_cast<long long>(row) * cols;
+  const float4* g4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grad_ptrs[p]) + off);
+  float4* b4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(buf1_ptrs[p]) + off);
+  float4* x4 = reinterpret_cast<float4*>(x + (static_cast<long long>(p) * rows + row) * cols);
+  float ss = 0.0f;
+  for (int c = lane; c < cols / 4; c += 32) {
+    const float4 g = g4[c];
+    float4 b = b4[c];
+    float4 xv;
+    b.x += (1.0f - mu) * (g.x * gs - b.x), xv.x = (1.0f - mu) * g.x * gs + mu * b.x;
+    b.y += (1.0f - mu) * (g.y * gs - b.y), xv.y = (1.0f - mu) * g.y * gs + mu * b.y;
+    b.z += (1.0f - mu) * (g.z * gs - b.z), xv.z = (1.0f - mu) * g.z * gs + mu * b.z;
+    b.w += (1.0f - mu) * (g.w * gs - b.w), xv.w = (1.0f - mu) * g.w * gs + mu * b.w;
+    b4[c] = b;
+    x4[c] = xv;
+    ss += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) row_sumsq[static_cast<long long>(p) * rows + row] = ss;
+}
+
+__global__ void __launch_bounds__(256) muon_scale_rows_batched_kernel(const float* __restrict__ x,
+                                                                      const float* __restrict__ row_scale,
+                                                                      const float* __restrict__ all_scale,
+                                                                      __nv_bfloat16* __restrict__ out, int rows,
+                                                                      int cols) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int p = blockIdx.y, lane = threadIdx.x & 31;
+  const long long r = static_cast<long long>(p) * rows + row;
+  const float s = row_scale[r] * all_scale[p];
+  const float4* x4 = reinterpret_cast<const float4*>(x + r * cols);
+  uint2* o2 = reinterpret_cast<uint2*>(out + r * cols);
+  for (int c = lane; c < cols / 4; c += 32) {
+    const float4 v = x4[c];
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * s, v.y * s), hi = __floats2bfloat162_rn(v.z * s, v.w * s);
+    o2[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+  }
+}
+
+// Sum of squares along rows (reduce_cols: out[p, row]) or along columns (out[p, col]) of bf16 X [P, rows, cols].
+__global__ void __launch_bounds__(256) muon_line_sumsq_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              float* __restrict__ out, int rows, int cols,
+                                                              bool reduce_cols) {
+  const int p = blockIdx.y;
+  const __nv_bfloat16* xp = x + static_cast<long long>(p) * rows * cols;
+  if (reduce_cols) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint4* r4 = reinterpret_cast<const uint4*>(xp + static_cast<long long>(row) * cols);
+    float ss = 0.0f;
+    for (int c = lane; c < cols / 8; c += 32) {
+      const uint4 u = r4[c];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float a = __uint_as_float(w[e] << 16), b = __uint_as_float(w[e] & 0xffff0000u);
+        ss += a * a + b * b;
+      }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) out[static_cast<long long>(p) * rows + row] = ss;
+  } else {
+    // thread = pair of columns; rows are split over blockIdx.z-free loop (rows <= a few thousand)
+    const int c2 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c2 >= cols / 2) return;
+    float s0 = 0.0f, s1 = 0.0f;
+    for (int r = 0; r < rows; ++r) {
+      const uint32_t w = reinterpret_cast<const uint32_t*>(xp + static_cast<long long>(r) * cols)[c2];
+      const float a = __uint_as_float(w << 16), b = __uint_as_float(w & 0xffff0000u);
+      s0 += a * a, s1 += b * b;
+    }
+    out[static_cast<long long>(p) * cols + 2 * c2] = s0;
+    out[static_cast<long long>(p) * cols + 2 * c2 + 1] = s1;
+  }
+}
+
+__global__ void __launch_bounds__(256) muon_apply_batched_kernel(const long long* __restrict__ master_ptrs,
+                                                                 const long long* __restrict__ value_ptrs,
+                                                                 const __nv_bfloat16* __restrict__ xb,
+                                                                 const float* __restrict__ scale0,
+                                                                 const float* __restrict__ line_scale,
+                                                                 bool lines_are_rows, int rows, int cols, float lr,
+                                                                 float wd) {
+  const int p = blockIdx.y;
+  float* master = reinterpret_cast<float*>(master_ptrs[p]);
+  __nv_bfloat16* value = value_ptrs ? reinterpret_cast<__nv_bfloat16*>(value_ptrs[p]) : nullptr;
+  const __nv_bfloat16* xp = xb + static_cast<long long>(p) * rows * cols;
+  const int lines = lines_are_rows ? rows : cols;
+  const float* ls = line_scale + static_cast<long long>(p) * lines;
+  const float s0 = scale0[p];
+  const long long n2 = static_cast<long long>(rows) * cols / 2;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n2;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * 2;
+    const int r = static_cast<int>(e / cols), c = static_cast<int>(e - static_cast<long long>(r) * cols);
+    const uint32_t w = reinterpret_cast<const uint32_t*>(xp)[i];
+    const float x0 = __uint_as_float(w << 16) * s0 * ls[lines_are_rows ? r : c];
+    const float x1 = __uint_as_float(w & 0xffff0000u) * s0 * ls[lines_are_rows ? r : c + 1];
+    float2 pm = reinterpret_cast<float2*>(master)[i];
+    pm.x = pm.x - lr * x0 - ((x0 * pm.x >= 0.0f) ? lr * wd * pm.x : 0.0f);
+    pm.y = pm.y - lr * x1 - ((x1 * pm.y >= 0.0f) ? lr * wd * pm.y : 0.0f);
+    reinterpret_cast<float2*>(master)[i] = pm;
+    if (value != nullptr) reinterpret_cast<__nv_bfloat162*>(value)[i] = __floats2bfloat162_rn(pm.x, pm.y);
+  }
+}
+
 __global__ void __launch_bounds__(256) relu2_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                                     long long n) {
   const long long nv = n / 8;
@@ -211,6 +330,36 @@ void relu2_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, cudaStrea
 void cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s) {
   if (n <= 0) return;
   cast_kernel<<<grid_for(n, 4), 256, 0, s>>>(x, y, n);
+}
+
+void muon_nesterov_batched(const long long* grad_ptrs, const long long* buf1_ptrs, float* x, float* row_sumsq, int P,
+                           int rows, int cols, float momentum, const float* grad_scale, cudaStream_t s) {
+  if (P <= 0 || rows <= 0) return;
+  muon_nesterov_batched_kernel<<<dim3((rows + 7) / 8, P), 256, 0, s>>>(grad_ptrs, buf1_ptrs, x, row_sumsq, rows, cols,
+                                                                      momentum, grad_scale);
+}
+void muon_scale_rows_batched(const float* x, const float* row_scale, const float* all_scale, __nv_bfloat16* out, int P,
+                             int rows, int cols, cudaStream_t s) {
+  if (P <= 0 || rows <= 0) return;
+  muon_scale_rows_batched_kernel<<<dim3((rows + 7) / 8, P), 256, 0, s>>>(x, row_scale, all_scale, out, rows, cols);
+}
+void muon_line_sumsq(const __nv_bfloat16* x, float* out, int P, int rows, int cols, bool reduce_cols, cudaStream_t s) {
+  if (P <= 0 || rows <= 0) return;
+  if (reduce_cols) {
+    muon_line_sumsq_kernel<<<dim3((rows + 7) / 8, P), 256, 0, s>>>(x, out, rows, cols, true);
+  } else {
+    muon_line_sumsq_kernel<<<dim3((cols / 2 + 255) / 256, P), 256, 0, s>>>(x, out, rows, cols, false);
+  }
+}
+void muon_apply_batched(const long long* master_ptrs, const long long* value_ptrs, const __nv_bfloat16* xb,
+                        const float* scale0, const float* line_scale, bool lines_are_rows, int P, int rows, int cols,
+                        float lr, float weight_decay, cudaStream_t s) {
+  if (P <= 0 || rows <= 0) return;
+  const long long n2 = static_cast<long long>(rows) * cols / 2;
+  long long blocks = (n2 + 255) / 256;
+  if (blocks > 296) blocks = 296;
+  muon_apply_batched_kernel<<<dim3(static_cast<unsigned>(blocks), P), 256, 0, s>>>(
+      master_ptrs, value_ptrs, xb, scale0, line_scale, lines_are_rows, rows, cols, lr, weight_decay);
 }
 
 }  // namespace nc

@@ -22,6 +22,16 @@ void muon_scale_rows(const float* x, const float* row_scale, const float* all_sc
 void muon_apply(float* master, __nv_bfloat16* value, const __nv_bfloat16* xb, const float* scale0,
                 const float* line_scale, bool lines_are_rows, int rows, int cols, float lr, float weight_decay,
                 cudaStream_t s);
+// Batched forms over the P matrices [rows, cols] of a shape group (cols a multiple of 8). Pointer tables are device
+// arrays of P addresses; x, row_sumsq, xb, scale0, line_scale are stacked [P, ...] tensors.
+void muon_nesterov_batched(const long long* grad_ptrs, const long long* buf1_ptrs, float* x, float* row_sumsq, int P,
+                           int rows, int cols, float momentum, const float* grad_scale, cudaStream_t s);
+void muon_scale_rows_batched(const float* x, const float* row_scale, const float* all_scale, __nv_bfloat16* out, int P,
+                             int rows, int cols, cudaStream_t s);
+void muon_line_sumsq(const __nv_bfloat16* x, float* out, int P, int rows, int cols, bool reduce_cols, cudaStream_t s);
+void muon_apply_batched(const long long* master_ptrs, const long long* value_ptrs, const __nv_bfloat16* xb,
+                        const float* scale0, const float* line_scale, bool lines_are_rows, int P, int rows, int cols,
+                        float lr, float weight_decay, cudaStream_t s);
 // relu(x)^2 elementwise (bf16)
 void relu2_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, cudaStream_t s);
 // bf16 <- fp32 cast of a span

@@ -68,6 +68,45 @@ void cast_f32_bf16(const Tensor& x, Tensor& y) {
 
 void register_optim(pybind11::module_& m) {
   m.def("adamw_update", &adamw_update);
+  m.def("muon_nesterov_batched", [](const Tensor& grad_ptrs, const Tensor& buf1_ptrs, Tensor& x, Tensor& row_ss,
+                                    double momentum, const c10::optional<Tensor>& grad_scale) {
+    const c10::cuda::CUDAGuard g(x.device());
+    TORCH_CHECK(x.dim() == 3 && x.is_contiguous() && x.size(2) % 8 == 0 && grad_ptrs.scalar_type() == torch::kInt64 &&
+                    grad_ptrs.numel() == x.size(0) && buf1_ptrs.numel() == x.size(0), "muon_nesterov_batched");
+    nc::muon_nesterov_batched(reinterpret_cast<const long long*>(grad_ptrs.data_ptr<int64_t>()),
+                              reinterpret_cast<const long long*>(buf1_ptrs.data_ptr<int64_t>()), x.data_ptr<float>(),
+                              row_ss.data_ptr<float>(), x.size(0), x.size(1), x.size(2), momentum,
+                              grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr,
+                              at::cuda::getCurrentCUDAStream());
+  });
+  m.def("muon_scale_rows_batched", [](const Tensor& x, const Tensor& row_scale, const Tensor& all_scale, Tensor& out) {
+    const c10::cuda::CUDAGuard g(x.device());
+    TORCH_CHECK(x.dim() == 3 && x.is_contiguous() && out.is_contiguous() && row_scale.is_contiguous() &&
+                    all_scale.is_contiguous() && x.size(2) % 8 == 0, "muon_scale_rows_batched");
+    nc::muon_scale_rows_batched(x.data_ptr<float>(), row_scale.data_ptr<float>(), all_scale.data_ptr<float>(), bptr(out),
+                                x.size(0), x.size(1), x.size(2), at::cuda::getCurrentCUDAStream());
+  });
+  m.def("muon_line_sumsq", [](const Tensor& x, bool reduce_cols) {
+    const c10::cuda::CUDAGuard g(x.device());
+    TORCH_CHECK(x.dim() == 3 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16 && x.size(2) % 8 == 0,
+                "muon_line_sumsq");
+    Tensor out = torch::empty({x.size(0), reduce_cols ? x.size(1) : x.size(2)}, x.options().dtype(torch::kFloat32));
+    nc::muon_line_sumsq(bptr(x), out.data_ptr<float>(), x.size(0), x.size(1), x.size(2), reduce_cols,
+                        at::cuda::getCurrentCUDAStream());
+    return out;
+  });
+  m.def("muon_apply_batched", [](const Tensor& master_ptrs, const c10::optional<Tensor>& value_ptrs, const Tensor& xb,
+                                 const Tensor& scale0, const Tensor& line_scale, bool lines_are_rows, double lr,
+                                 double wd) {
+    const c10::cuda::CUDAGuard g(xb.device());
+    TORCH_CHECK(xb.dim() == 3 && xb.is_contiguous() && scale0.is_contiguous() && line_scale.is_contiguous() &&
+                    master_ptrs.numel() == xb.size(0), "muon_apply_batched");
+    nc::muon_apply_batched(reinterpret_cast<const long long*>(master_ptrs.data_ptr<int64_t>()),
+                           value_ptrs.has_value() ? reinterpret_cast<const long long*>(value_ptrs->data_ptr<int64_t>())
+                                                  : nullptr,
+                           bptr(xb), scale0.data_ptr<float>(), line_scale.data_ptr<float>(), lines_are_rows, xb.size(0),
+                           xb.size(1), xb.size(2), lr, wd, at::cuda::getCurrentCUDAStream());
+  });
   m.def("muon_nesterov", &muon_nesterov);
   m.def("muon_scale_rows", &muon_scale_rows);
   m.def("muon_apply", &muon_apply);

@@ -52,6 +52,16 @@ class MuonGroupState:
         self.x32 = torch.empty(P, rows, cols, dtype=torch.float32, device=device)
         self.X = torch.empty(P, rows, cols, dtype=torch.bfloat16, device=device)
         self.row_ss = torch.empty(P, rows, dtype=torch.float32, device=device)
+        self._tables = {}
+
+    def table(self, key: str, tensors) -> torch.Tensor:
+        """Device array of the tensors' addresses, cached as long as the addresses stay the same."""
+        ptrs = tuple(t.data_ptr() for t in tensors)
+        hit = self._tables.get(key)
+        if hit is None or hit[0] != ptrs:
+            hit = (ptrs, torch.tensor(ptrs, dtype=torch.int64, device=self.x32.device))
+            self._tables[key] = hit
+        return hit[1]
 
 
 @torch.no_grad()
@@ -67,8 +77,13 @@ def muon_group_step(grads: List[torch.Tensor], masters: List[torch.Tensor], valu
     rows, cols = masters[0].shape
     reduce_cols = rows >= cols
     gs = None if grad_scale is None else grad_scale.reshape(1)
-    for p in range(P):
-        C.muon_nesterov(grads[p], buf1[p], scratch.x32[p], scratch.row_ss[p], momentum, gs)
+    batched = cols % 8 == 0 and all(t.is_contiguous() for t in grads) and all(t.is_contiguous() for t in buf1)
+    if batched:
+        C.muon_nesterov_batched(scratch.table("g", grads), scratch.table("b1", buf1), scratch.x32[:P],
+                                scratch.row_ss[:P], momentum, gs)
+    else:
+        for p in range(P):
+            C.muon_nesterov(grads[p], buf1[p], scratch.x32[p], scratch.row_ss[p], momentum, gs)
     row_ss = scratch.row_ss[:P]
     frob = torch.sqrt(row_ss.sum(-1, keepdim=True))
     target = frob / math.sqrt(float(rows))
@@ -77,25 +92,35 @@ def muon_group_step(grads: List[torch.Tensor], masters: List[torch.Tensor], valu
     frob2 = torch.sqrt((row_ss * row_scale * row_scale).sum(-1))
     all_scale = 1.0 / (frob2 * 1.01 + 1e-6)
     row_scale = row_scale.contiguous()
-    for p in range(P):
-        C.muon_scale_rows(scratch.x32[p], row_scale[p], all_scale[p:p + 1], scratch.X[p])
+    if batched:
+        C.muon_scale_rows_batched(scratch.x32[:P], row_scale, all_scale.contiguous(), scratch.X[:P])
+    else:
+        for p in range(P):
+            C.muon_scale_rows(scratch.x32[p], row_scale[p], all_scale[p:p + 1], scratch.X[p])
     X = polar_express_bf16(scratch.X[:P], ns_steps)
     red = -1 if reduce_cols else -2
     line_len = cols if reduce_cols else rows
-    line_ss = X.float().square().sum(red)                       # [P, lines]
+    if batched and X.is_contiguous():
+        line_ss = C.muon_line_sumsq(X, reduce_cols)             # [P, lines]
+    else:
+        line_ss = X.float().square().sum(red)
     frob_post = torch.sqrt(line_ss.sum(-1, keepdim=True))
     scale = math.sqrt(float(min(rows, cols))) / frob_post.clamp_min(1e-6)   # [P, 1]
     v_mean = line_ss * (scale * scale) / float(line_len)
     v_norm = torch.sqrt(v_mean.sum(-1, keepdim=True) * float(line_len))
     b2 = torch.stack(buf2)
     b2.add_((1.0 - beta2) * (v_mean - b2))
-    for p in range(P):
-        buf2[p].copy_(b2[p])
+    torch._foreach_copy_(list(buf2), list(b2.unbind(0)))
     step_size = torch.rsqrt(b2.clamp_min(1e-10))
     sum_scaled = (v_mean * float(line_len) * step_size * step_size).sum(-1, keepdim=True)
     denom = torch.sqrt(sum_scaled).clamp_min(1e-10)
     line_scale = (step_size * (v_norm / denom)).contiguous()
     scale = scale.contiguous()
+    if apply_fn is None and batched and X.is_contiguous() and all(m.is_contiguous() for m in masters):
+        vt = scratch.table("v", values) if all(v is not None for v in values) else None
+        C.muon_apply_batched(scratch.table("m", masters), vt, X, scale.reshape(-1), line_scale, reduce_cols, lr,
+                             weight_decay)
+        return
     for p in range(P):
         if apply_fn is not None:
             apply_fn(p, masters[p], X[p], scale[p], line_scale[p], reduce_cols, lr, weight_decay)
