@@ -62,6 +62,7 @@ __global__ void __launch_bounds__(256) reduce_pull_kernel(PeerPtrs grads, int wo
   __syncthreads();
   if (!ok_sh) return;
   double acc = 0.0;
+  float acc_f = 0.0f;   // squares are added in fp32 and folded into the fp64 sum once per loop trip (16 terms)
   const long long nvec = total / 4;
   const long long threads = static_cast<long long>(gridDim.x) * blockDim.x;
   float* mine = static_cast<float*>(grads.p[my_rank]);
@@ -102,8 +103,10 @@ __global__ void __launch_bounds__(256) reduce_pull_kernel(PeerPtrs grads, int wo
       float4 q = sum[u];
       q.x *= scale, q.y *= scale, q.z *= scale, q.w *= scale;
       *reinterpret_cast<float4*>(mine + e[u]) = q;
-      acc += static_cast<double>(q.x * q.x + q.y * q.y) + static_cast<double>(q.z * q.z + q.w * q.w);
+      acc_f += q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
     }
+    acc += static_cast<double>(acc_f);
+    acc_f = 0.0f;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);

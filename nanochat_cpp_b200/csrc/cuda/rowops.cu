@@ -899,14 +899,29 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
 }
 
 // ------------------------------------------------------------------ gradient norm
+// Sum of squares of an fp32 span in fp64. Each thread squares and adds 64 values in fp32 (four independent 16-byte
+// loads in flight, partial sums of at most 16 terms each) before it touches the fp64 accumulator: the conversion
+// and the double add are rare enough that the kernel runs at memory speed.
 __global__ void __launch_bounds__(256) sumsq_kernel(const float* __restrict__ g, long long n, double* out) {
   __shared__ double shd[8];
   double acc = 0.0;
   const long long nv = n / 4;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float4 v = reinterpret_cast<const float4*>(g)[i];
-    acc += static_cast<double>(v.x * v.x + v.y * v.y) + static_cast<double>(v.z * v.z + v.w * v.w);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const float4* g4 = reinterpret_cast<const float4*>(g);
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nv; i0 += stride * 16) {
+    float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long i = i0 + (r * 4 + u) * stride;
+        v[u] = i < nv ? g4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) part[u] += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+    }
+    acc += static_cast<double>(part[0] + part[1]) + static_cast<double>(part[2] + part[3]);
   }
   if (blockIdx.x == 0) {
     for (long long i = nv * 4 + threadIdx.x; i < n; i += blockDim.x) acc += static_cast<double>(g[i]) * g[i];

@@ -46,12 +46,14 @@ def cuda_module():
 
 
 def _first_tensor(args, kwargs):
-    for a in args:
+    """The tensor that decides where an operator runs; looks inside list / tuple arguments too (gradient lists)."""
+    for a in list(args) + list(kwargs.values()):
         if isinstance(a, torch.Tensor):
             return a
-    for a in kwargs.values():
-        if isinstance(a, torch.Tensor):
-            return a
+        if isinstance(a, (list, tuple)):
+            for b in a:
+                if isinstance(b, torch.Tensor):
+                    return b
     return None
 
 
