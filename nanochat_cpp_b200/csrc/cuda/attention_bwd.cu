@@ -11,7 +11,7 @@
 // ring, and run per secondary tile
 //      T1 = X1 * Y1^T   (scores, or scores transposed)        tcgen05.mma -> TMEM, double buffered
 //      T2 = X2 * Y2^T   (dP, or dP transposed)                tcgen05.mma -> TMEM, double buffered
-//      p  = exp2(T1 * c - lse),  ds = p * (T2 - delta) * scale  by 256 threads (two per TMEM lane)
+//      p  = exp2(T1 * c - lse),  ds = p * (T2 - delta) * scale  by 8 (dQ) or 16 (dK,dV) warps       
 //      acc1 += ds * Y1  (dQ += dS K   |  dK += dS^T Q)        A = ds from shared memory,
 //      acc2 += p  * Y2  (             |  dV += P^T dO)        B = the SAME shared-memory tile re-read
 //                                                             through an MN-major descriptor
@@ -29,8 +29,15 @@ namespace {
 
 constexpr int BP = 128;  // primary rows per CTA (TMEM lanes)
 constexpr int BS = 64;   // secondary rows per step
-constexpr int NUM_COMPUTE_WARPS = 8;  // two warps per TMEM lane quadrant, each takes half of the columns
-constexpr int NUM_THREADS = 64 + NUM_COMPUTE_WARPS * 32;
+// Compute warps: a multiple of four (one per TMEM lane quadrant); the warps of a quadrant split the 64 columns of
+// a score tile. The dK/dV sweep is bound by the latency of its per-element chain (TMEM load, exp2, pack, stores),
+// not by issue slots, so it runs four warps per scheduler; the dQ sweep keeps two.
+template <int MODE>
+struct BwdWarps {
+  static constexpr int kCompute = MODE == 1 ? 16 : 8;
+  static constexpr int kThreads = 64 + kCompute * 32;
+  static constexpr int kCols = 64 / (kCompute / 4);  // score-tile columns per warp
+};
 constexpr int YSTAGES = 3;
 
 enum { kModeDQ = 0, kModeDKV = 1 };
@@ -73,13 +80,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // tmX1/tmY1 and tmX2/tmY2: DQ mode -> X = (Q, dO), Y = (K, V); DKV mode -> X = (K, V), Y = (Q, dO).
 template <int D, int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(BwdWarps<MODE>::kThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                      const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
-                     const BwdParams p) {
+                     const __grid_constant__ CUtensorMap tmDS, const BwdParams p) {
   using L = BwdSmem<D, MODE>;
   constexpr int DC = D / 64;
   constexpr int NW = L::kNW;
+  constexpr int NUM_COMPUTE_WARPS = BwdWarps<MODE>::kCompute;
+  constexpr int CW = BwdWarps<MODE>::kCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
@@ -125,6 +134,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   }
   const int n_sub = max(0, s_hi - s_lo + 1);
   const int n_iters = MODE == kModeDQ ? n_sub : n_sub * group;
+  // dK/dV sweep with a dS^T scratch: each finished dS tile leaves shared memory as one TMA store (its swizzled
+  // K-major layout is the store's box layout), and a tile buffer is free again when the MMAs that read it have
+  // completed AND the store has read it: two arrivals on w_empty.
+  const bool store_ds = MODE == kModeDKV && p.ds_out != nullptr;
 
   if (threadIdx.x == 0) {
     mbar_init(x_full, 1);
@@ -136,7 +149,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       mbar_init(&t_full[i], 1);
       mbar_init(&t_empty[i], NUM_COMPUTE_WARPS);
       mbar_init(&w_full[i], NUM_COMPUTE_WARPS);
-      mbar_init(&w_empty[i], 1);
+      mbar_init(&w_empty[i], store_ds ? 2 : 1);
       mbar_init(&stats_full[i], NUM_COMPUTE_WARPS * 32);
     }
     mbar_init(acc_full, 1);
@@ -228,6 +241,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         const uint32_t tph = (it >> 1) & 1;
         if (!mbar_wait(&w_full[tb], tph, abort_flag, p.status, kErrWaitOther)) return false;
         tc_fence_after();
+        if (store_ds) {
+          const int g = it / n_sub;
+          const int s0 = (s_lo + it % n_sub) * BS;
+          tma_store_4d(&tmDS, smem + L::kOffW + tb * NW * L::kW, s0, p0, kvh * group + g, b);
+          tma_store_commit();
+        }
         const uint64_t dw = w_desc0 + static_cast<uint64_t>(tb * ((NW * L::kW) >> 4));
         const uint64_t dy1 = ymn_desc0 + static_cast<uint64_t>(yst * ((2 * L::kY) >> 4));
         const uint64_t dy2 = dy1 + static_cast<uint64_t>(L::kY >> 4);
@@ -254,15 +273,20 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       for (int it = 0; it < n_iters && ok; ++it) {
         ok = issue_acc(it);
         if (ok && it + 2 < n_iters) ok = issue_t(it + 2);
+        if (ok && store_ds) {
+          tma_store_wait_read<0>();
+          mbar_arrive(&w_empty[it & 1]);
+        }
       }
       if (ok) mma_commit(acc_full);
+      tma_store_wait<0>();
     }
   } else {
     // -------------------------------------------------------------- compute warps
     const int qd = warp & 3;
     const int row = qd * 32 + lane;  // primary row inside the tile
-    const int tid128 = (warp - 2) * 32 + lane;  // 0..255
-    const int ch = (warp - 2) >> 2;              // column half of this warp
+    const int tid128 = (warp - 2) * 32 + lane;  // index among the compute threads
+    const int ch = (warp - 2) >> 2;              // which CW-column slice of the tile this warp takes
     const uint32_t lane_sel = static_cast<uint32_t>(qd * 32) << 16;
     const int prow = p0 + row;
     const float kLog2e = 1.4426950408889634f;
@@ -317,24 +341,29 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       if (!mbar_wait(&w_empty[tb], tph ^ 1, abort_flag, p.status, kErrWaitOther)) { ok = false; break; }
       uint8_t* sW = smem + L::kOffW + tb * NW * L::kW + row * 128;
       {
-        const int c32 = ch;
-        uint32_t t1[32], t2[32];
-        tmem_ld_32x32(tmem_T1 + tb * BS + c32 * 32 + lane_sel, t1);
-        tmem_ld_32x32(tmem_T2 + tb * BS + c32 * 32 + lane_sel, t2);
+        const int c0 = ch * CW;  // first column of this warp
+        uint32_t t1[CW], t2[CW];
+        if constexpr (CW == 32) {
+          tmem_ld_32x32(tmem_T1 + tb * BS + c0 + lane_sel, t1);
+          tmem_ld_32x32(tmem_T2 + tb * BS + c0 + lane_sel, t2);
+        } else {
+          tmem_ld_32x16(tmem_T1 + tb * BS + c0 + lane_sel, t1);
+          tmem_ld_32x16(tmem_T2 + tb * BS + c0 + lane_sel, t2);
+        }
         tmem_ld_wait();
-        uint32_t pk_ds[16], pk_p[16];
+        uint32_t pk_ds[CW / 2], pk_p[CW / 2];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
+        for (int e = 0; e < CW; e += 2) {
           float pv[2], dsv[2];
           float lse_pair[2] = {0.0f, 0.0f}, delta_pair[2] = {0.0f, 0.0f};
           if (MODE == kModeDKV) {
-            const float2 a = *reinterpret_cast<const float2*>(st_lse + c32 * 32 + e);
-            const float2 d2 = *reinterpret_cast<const float2*>(st_delta + c32 * 32 + e);
+            const float2 a = *reinterpret_cast<const float2*>(st_lse + c0 + e);
+            const float2 d2 = *reinterpret_cast<const float2*>(st_delta + c0 + e);
             lse_pair[0] = a.x, lse_pair[1] = a.y, delta_pair[0] = d2.x, delta_pair[1] = d2.y;
           }
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int col = c32 * 32 + e + u;
+            const int col = c0 + e + u;
             const float lse2 = MODE == kModeDQ ? my_lse2 : lse_pair[u];
             const float dl = MODE == kModeDQ ? my_delta : delta_pair[u];
             float pe = fast_exp2(__uint_as_float(t1[e + u]) * p.scale_log2 - lse2);
@@ -352,19 +381,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
           pk_ds[e / 2] = pack_bf16(dsv[0], dsv[1]);
           if (MODE == kModeDKV) pk_p[e / 2] = pack_bf16(pv[0], pv[1]);
         }
-        if (MODE == kModeDKV && p.ds_out != nullptr) {
-          // this thread's 32 consecutive query columns of key row prow (in bounds: the scratch is padded)
-          __nv_bfloat16* dsp = p.ds_out +
-                               ((static_cast<long long>(b) * p.H + (kvh * group + g)) * p.ds_tk + prow) * p.ds_tq + s0 +
-                               c32 * 32;
 #pragma unroll
-          for (int gq = 0; gq < 4; ++gq)
-            *reinterpret_cast<uint4*>(dsp + gq * 8) =
-                make_uint4(pk_ds[4 * gq], pk_ds[4 * gq + 1], pk_ds[4 * gq + 2], pk_ds[4 * gq + 3]);
-        }
-#pragma unroll
-        for (int gq = 0; gq < 4; ++gq) {
-          const int gran = (c32 * 4 + gq) ^ (row & 7);
+        for (int gq = 0; gq < CW / 8; ++gq) {
+          const int gran = (ch * (CW / 8) + gq) ^ (row & 7);
           *reinterpret_cast<uint4*>(sW + gran * 16) =
               make_uint4(pk_ds[4 * gq], pk_ds[4 * gq + 1], pk_ds[4 * gq + 2], pk_ds[4 * gq + 3]);
           if (MODE == kModeDKV)
@@ -396,24 +415,28 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         const long long sh = which == 0 ? p.o1_stride_h : p.o2_stride_h;
         __nv_bfloat16* op = base + b * sb + static_cast<long long>(prow) * stt + static_cast<long long>(hp) * sh;
         const uint32_t tacc = which == 0 ? tmem_A1 : tmem_A2;
+        // the warps of a quadrant split the D accumulator columns; chunks of EW columns
+        constexpr int EC = D / (NUM_COMPUTE_WARPS / 4);
+        constexpr int EW = EC >= 32 ? 32 : 16;
 #pragma unroll 1
-        for (int c = ch * (D / 64); c < (ch + 1) * (D / 64); ++c) {
-          uint32_t r[32];
+        for (int c = ch * EC; c < (ch + 1) * EC; c += EW) {
+          uint32_t r[EW];
           if (have) {
-            tmem_ld_32x32(tacc + c * 32 + lane_sel, r);
+            if constexpr (EW == 32) tmem_ld_32x32(tacc + c + lane_sel, r);
+            else tmem_ld_32x16(tacc + c + lane_sel, r);
             tmem_ld_wait();
           } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) r[e] = 0u;
+            for (int e = 0; e < EW; ++e) r[e] = 0u;
           }
           if (row_ok) {
 #pragma unroll
-            for (int gq = 0; gq < 4; ++gq) {
+            for (int gq = 0; gq < EW / 8; ++gq) {
               uint32_t w[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e)
                 w[e] = pack_bf16(__uint_as_float(r[gq * 8 + e * 2]), __uint_as_float(r[gq * 8 + e * 2 + 1]));
-              *reinterpret_cast<uint4*>(op + c * 32 + gq * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(op + c + gq * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
         }
@@ -457,7 +480,7 @@ __global__ void __launch_bounds__(256) attention_delta_kernel(const __nv_bfloat1
 
 template <int D, int MODE>
 const char* launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& y1, const CUtensorMap& y2,
-                       const BwdParams& p, dim3 grid, cudaStream_t stream) {
+                       const CUtensorMap& ds, const BwdParams& p, dim3 grid, cudaStream_t stream) {
   using L = BwdSmem<D, MODE>;
   static bool cfg = false;
   if (!cfg) {
@@ -466,7 +489,7 @@ const char* launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUten
     if (e != cudaSuccess) return cudaGetErrorString(e);
     cfg = true;
   }
-  attention_bwd_kernel<D, MODE><<<grid, NUM_THREADS, L::kTotal, stream>>>(x1, x2, y1, y2, p);
+  attention_bwd_kernel<D, MODE><<<grid, BwdWarps<MODE>::kThreads, L::kTotal, stream>>>(x1, x2, y1, y2, ds, p);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
@@ -509,6 +532,13 @@ const char* attention_bwd(const AttnArgs& a, cudaStream_t stream) {
   p.ds_tk = a.ds_tk, p.ds_tq = a.ds_tq;
   if (a.dS != nullptr && (a.ds_tk < (a.Tk + 127) / 128 * 128 || a.ds_tq < (a.Tq + 127) / 128 * 128 || a.ds_tq % 8))
     return "attention_bwd: dS scratch is too small";
+  CUtensorMap ds_map = q64;  // placeholder when there is no scratch (never dereferenced then)
+  if (a.dS != nullptr) {
+    const long long dd[4] = {a.ds_tq, a.ds_tk, a.H, a.B};
+    const long long sd[3] = {a.ds_tq, a.ds_tq * a.ds_tk, a.ds_tq * a.ds_tk * a.H};
+    const int boxd[4] = {BS, BP, 1, 1};
+    if (!make_tmap_bf16_4d(&ds_map, a.dS, dd, sd, boxd)) return "attention_bwd: dS tensor map construction failed";
+  }
   const char* err;
   // dK, dV
   p.out1 = static_cast<__nv_bfloat16*>(a.dK);
@@ -516,8 +546,8 @@ const char* attention_bwd(const AttnArgs& a, cudaStream_t stream) {
   p.out2 = static_cast<__nv_bfloat16*>(a.dV);
   p.o2_stride_b = a.dv_stride_b, p.o2_stride_t = a.dv_stride_t, p.o2_stride_h = a.dv_stride_h;
   const dim3 grid_kv((a.Tk + BP - 1) / BP, a.KVH, a.B);
-  err = a.D == 128 ? launch_bwd<128, kModeDKV>(k128, v128, q64, do64, p, grid_kv, stream)
-                   : launch_bwd<64, kModeDKV>(k128, v128, q64, do64, p, grid_kv, stream);
+  err = a.D == 128 ? launch_bwd<128, kModeDKV>(k128, v128, q64, do64, ds_map, p, grid_kv, stream)
+                   : launch_bwd<64, kModeDKV>(k128, v128, q64, do64, ds_map, p, grid_kv, stream);
   if (err) return err;
   if (a.dS != nullptr) return attention_dq_from_ds(a, stream);
   // dQ
@@ -526,8 +556,8 @@ const char* attention_bwd(const AttnArgs& a, cudaStream_t stream) {
   p.o1_stride_b = a.dq_stride_b, p.o1_stride_t = a.dq_stride_t, p.o1_stride_h = a.dq_stride_h;
   p.out2 = nullptr;
   const dim3 grid_q((a.Tq + BP - 1) / BP, a.H, a.B);
-  err = a.D == 128 ? launch_bwd<128, kModeDQ>(q128, do128, k64, v64, p, grid_q, stream)
-                   : launch_bwd<64, kModeDQ>(q128, do128, k64, v64, p, grid_q, stream);
+  err = a.D == 128 ? launch_bwd<128, kModeDQ>(q128, do128, k64, v64, ds_map, p, grid_q, stream)
+                   : launch_bwd<64, kModeDQ>(q128, do128, k64, v64, ds_map, p, grid_q, stream);
   return err;
 }
 
