@@ -222,6 +222,91 @@ int64_t ncb_parquet_read(const char* path, const char* column, char* bytes, int6
 int ncb_sample_token(const float* logits, int vocab, float temperature, int top_k, uint64_t seed, uint64_t row,
                      uint64_t step);
 
+
+/* ---- in-process mesh runtime (CPU engine): one model replica per mesh position, gradients summed with a ring
+ * all-reduce inside the process, one optimizer step per replica; names and layouts follow the reference. */
+typedef struct nanochat_mesh nanochat_mesh;
+typedef struct nanochat_runtime nanochat_runtime;
+nanochat_mesh* nanochat_mesh_create(const int* indices, int count); /* count < 1 becomes 1; null = 0, 1, ... */
+void nanochat_mesh_free(nanochat_mesh* mesh);
+int nanochat_mesh_size(nanochat_mesh* mesh);
+/* `batch`: global batch in sequences (a multiple of mesh size * grad_accum); `seq` 0 selects config.seq_len. */
+nanochat_runtime* nanochat_runtime_create(const nanochat_mesh* mesh, const nanochat_config* config,
+                                          const nanochat_optim_config* optim, int batch, int grad_accum, int seq,
+                                          uint64_t seed);
+void nanochat_runtime_free(nanochat_runtime* runtime);
+int nanochat_runtime_world_size(nanochat_runtime* runtime);
+/* One step over batch * seq row-major ids; returns the global mean loss, 0 on error. */
+float nanochat_runtime_train_step(nanochat_runtime* runtime, const int* tokens, const int* targets);
+typedef struct {
+  int device_count;
+  const float* loss; /* device_count per-replica losses; valid until the next step */
+  float grad_norm;
+  float step_seconds;
+} nanochat_metrics;
+nanochat_status nanochat_runtime_metrics(nanochat_runtime* runtime, nanochat_metrics* out);
+int nanochat_runtime_param_count(nanochat_runtime* runtime, int replica);
+int nanochat_runtime_param_info(nanochat_runtime* runtime, int replica, int index, nanochat_param* out);
+int64_t nanochat_runtime_param_read(nanochat_runtime* runtime, int replica, int index, int grad, int64_t offset,
+                                    int64_t count, void* data);
+/* FNV-1a 64 over the fp32 bytes of every parameter of the replica. */
+nanochat_status nanochat_runtime_param_digest(nanochat_runtime* runtime, int replica, uint64_t* out);
+void nanochat_runtime_save(nanochat_runtime* runtime, const char* path);         /* replica 0, optimizer + step */
+void nanochat_runtime_load(nanochat_runtime* runtime, const char* path);         /* every replica */
+void nanochat_runtime_load_weights(nanochat_runtime* runtime, const char* path); /* parameters only */
+int nanochat_runtime_step(nanochat_runtime* runtime);
+/* Failure-detection test hook: the next step's first ring message from replica `from` is dropped and every
+ * receive of the reduce is bounded by `timeout_ms`; the step then fails with an error instead of hanging. */
+void ncb_runtime_inject_drop(nanochat_runtime* runtime, int from, int timeout_ms);
+
+typedef struct {
+  const char* const* parquet;
+  int parquet_count;
+  const char* tokenizer_path;
+  const char* packed_rows_path; /* an NCSFT001 shard; empty selects parquet */
+  uint64_t data_seed;
+} nanochat_mesh_data_config;
+typedef struct {
+  int batch, grad_accum, seq;
+  uint64_t seed;
+  int num_iterations, log_every, save_every, resume;
+} nanochat_mesh_run_config;
+typedef struct {
+  const char* out_dir;
+  const char* checkpoint_path; /* empty selects out_dir/checkpoint.ckpt */
+} nanochat_mesh_output_config;
+typedef struct {
+  nanochat_config model;
+  const nanochat_mesh* mesh;
+  const char* preset; /* "default" or "track3"; ignored when `optimizer` is given */
+  const nanochat_optim_config* optimizer;
+  const char* warm_start_path;
+  double flops_per_token; /* 0: the model estimate */
+  double peak_flops;      /* 0: MFU is reported as 0 */
+  nanochat_mesh_data_config data;
+  nanochat_mesh_run_config run;
+  nanochat_mesh_output_config output;
+} nanochat_mesh_train_config;
+typedef struct {
+  int steps;
+  int interrupted;
+  double mean_loss;
+  double steady_mfu;
+  char checkpoint[4096];
+} nanochat_mesh_train_summary;
+/* Runs one job: metrics.jsonl, summary.json and the checkpoint under out_dir; SIGINT stops it with a checkpoint.
+ * Returns the last loss, 0 on error. */
+float nanochat_mesh_train_run(const nanochat_mesh_train_config* config, nanochat_mesh_train_summary* out);
+
+/* ---- host collectives (TCP over 127.0.0.1 between CPU ranks; an in-process ring for tests) */
+typedef struct ncb_tcp ncb_tcp;
+ncb_tcp* ncb_tcp_create(int rank, int world);
+int ncb_tcp_port(ncb_tcp* transport);
+nanochat_status ncb_tcp_connect(ncb_tcp* transport, const int* ports, int count, int timeout_ms);
+nanochat_status ncb_tcp_all_reduce_sum(ncb_tcp* transport, float* data, int64_t count, int timeout_ms);
+void ncb_tcp_free(ncb_tcp* transport);
+nanochat_status ncb_memory_ring_all_reduce(float* data, int world, int64_t count, int drop_from, int timeout_ms);
+
 #ifdef __cplusplus
 }
 #endif

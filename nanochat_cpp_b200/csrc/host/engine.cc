@@ -705,6 +705,127 @@ bool CpuModel::Load(const std::string& path, std::string* error) {
   return true;
 }
 
+bool CpuModel::SaveWithOptimizer(const std::string& path, const CpuOptimizer& opt, std::uint64_t step,
+                                 std::uint32_t world_size, std::string* error) const {
+  Checkpoint ck;
+  static_cast<ModelConfig&>(ck.metadata.config) = cfg_;
+  ck.metadata.step = step;
+  ck.metadata.world_size = world_size;
+  for (const auto& p : params_) {
+    TensorRecord r;
+    r.name = p.name, r.dtype = DType::kFp32, r.shape = p.shape;
+    r.data.resize(p.count * 4);
+    std::memcpy(r.data.data(), value_.data() + p.offset, p.count * 4);
+    ck.tensors.push_back(std::move(r));
+  }
+  opt.ExportState(&ck.optimizer_state);
+  TensorRecord st;
+  st.name = "optimizer/step", st.dtype = DType::kFp32, st.shape = {1};
+  const float stepf = static_cast<float>(step);
+  st.data.resize(4);
+  std::memcpy(st.data.data(), &stepf, 4);
+  ck.optimizer_state.push_back(std::move(st));
+  return ck.Save(path, error);
+}
+
+bool CpuModel::LoadWithOptimizer(const std::string& path, CpuOptimizer* opt, std::uint64_t* step, std::string* error) {
+  if (!Load(path, error)) return false;
+  if (opt == nullptr && step == nullptr) return true;
+  Checkpoint ck;
+  if (!ck.Load(path, true, error)) return false;
+  if (step != nullptr) *step = ck.metadata.step;
+  return opt == nullptr || opt->ImportState(ck.optimizer_state, error);
+}
+
+namespace {
+const char* KindRecordName(ParamKind k) {
+  switch (k) {
+    case ParamKind::kLmHead: return "lm_head";
+    case ParamKind::kWte: return "embedding";
+    case ParamKind::kValueEmbed: return "value_embedding";
+    case ParamKind::kResid: return "resid";
+    case ParamKind::kX0: return "x0";
+    case ParamKind::kSmear: return "smear";
+    default: return "matrix";
+  }
+}
+TensorRecord FloatRecord(const std::string& name, std::vector<std::int64_t> shape, const std::vector<const std::vector<float>*>& parts) {
+  TensorRecord r;
+  r.name = name, r.dtype = DType::kFp32, r.shape = std::move(shape);
+  std::size_t total = 0;
+  for (const auto* p : parts) total += p->size();
+  r.data.resize(total * 4);
+  std::size_t off = 0;
+  for (const auto* p : parts) {
+    std::memcpy(r.data.data() + off, p->data(), p->size() * 4);
+    off += p->size() * 4;
+  }
+  return r;
+}
+bool Scatter(const TensorRecord* r, std::vector<std::vector<float>>* parts, const std::string& name, std::string* error) {
+  if (r == nullptr) return true;  // an absent record keeps the fresh state
+  std::size_t total = 0;
+  for (const auto& p : *parts) total += p.size();
+  if (r->dtype != DType::kFp32 || r->data.size() != total * 4) {
+    if (error) *error = "optimizer record " + name + " has the wrong size or dtype";
+    return false;
+  }
+  std::size_t off = 0;
+  for (auto& p : *parts) {
+    std::memcpy(p.data(), r->data.data() + off, p.size() * 4);
+    off += p.size() * 4;
+  }
+  return true;
+}
+}  // namespace
+
+void CpuOptimizer::ExportState(std::vector<TensorRecord>* out) const {
+  for (const auto& g : adam_) {
+    if (g.params.empty()) continue;
+    std::vector<const std::vector<float>*> m, v;
+    std::int64_t total = 0;
+    for (std::size_t k = 0; k < g.params.size(); ++k) {
+      m.push_back(&g.m[k]);
+      v.push_back(&g.v[k]);
+      total += static_cast<std::int64_t>(g.m[k].size());
+    }
+    const std::string base = std::string("adamw.") + KindRecordName(g.kind);
+    out->push_back(FloatRecord(base + ".m", {total}, m));
+    out->push_back(FloatRecord(base + ".v", {total}, v));
+  }
+  for (const auto& g : muon_) {
+    std::vector<const std::vector<float>*> b1, b2;
+    for (std::size_t k = 0; k < g.params.size(); ++k) {
+      b1.push_back(&g.buf1[k]);
+      b2.push_back(&g.buf2[k]);
+    }
+    const std::string base = "muon." + std::to_string(g.rows) + "x" + std::to_string(g.cols);
+    const std::int64_t n = static_cast<std::int64_t>(g.params.size());
+    out->push_back(FloatRecord(base + ".buf1", {n, g.rows, g.cols}, b1));
+    out->push_back(FloatRecord(base + ".buf2", {n, std::max(g.rows, g.cols)}, b2));
+  }
+}
+
+bool CpuOptimizer::ImportState(const std::vector<TensorRecord>& records, std::string* error) {
+  auto find = [&](const std::string& name) -> const TensorRecord* {
+    for (const auto& r : records)
+      if (r.name == name) return &r;
+    return nullptr;
+  };
+  for (auto& g : adam_) {
+    if (g.params.empty()) continue;
+    const std::string base = std::string("adamw.") + KindRecordName(g.kind);
+    if (!Scatter(find(base + ".m"), &g.m, base + ".m", error)) return false;
+    if (!Scatter(find(base + ".v"), &g.v, base + ".v", error)) return false;
+  }
+  for (auto& g : muon_) {
+    const std::string base = "muon." + std::to_string(g.rows) + "x" + std::to_string(g.cols);
+    if (!Scatter(find(base + ".buf1"), &g.buf1, base + ".buf1", error)) return false;
+    if (!Scatter(find(base + ".buf2"), &g.buf2, base + ".buf2", error)) return false;
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------------------------------------- inference
 // Contiguous cache: per layer prepared keys and gated values [max_seq, kv_dim], plus the normalised embedding of the
 // last token (the smear of the next token mixes it in) - the layout of the reference's KvCacheImpl

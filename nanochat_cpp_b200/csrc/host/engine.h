@@ -65,6 +65,11 @@ class CpuModel {
 
   bool Save(const std::string& path, std::string* error) const;
   bool Load(const std::string& path, std::string* error);
+  // The same container with the optimizer records and the step beside the parameters (a resumable checkpoint).
+  bool SaveWithOptimizer(const std::string& path, const class CpuOptimizer& opt, std::uint64_t step,
+                         std::uint32_t world_size, std::string* error) const;
+  // `opt` may be null (weights only: a warm start keeps fresh optimizer state). `step` receives the stored step.
+  bool LoadWithOptimizer(const std::string& path, class CpuOptimizer* opt, std::uint64_t* step, std::string* error);
 
   // Inference with a contiguous KV cache, one sequence at a time (soft-capped logits over the real vocabulary).
   std::unique_ptr<KvCache> NewCache(int max_seq) const;
@@ -101,6 +106,10 @@ class CpuOptimizer {
   void Step(int step);  // 1-based
   float grad_norm() const { return grad_norm_; }
   const OptimConfig& config() const { return cfg_; }
+  // Optimizer records in the checkpoint's naming: `adamw.<kind>.{m,v}` (the parameters of a kind concatenated),
+  // `muon.<rows>x<cols>.{buf1,buf2}` (stacked over the group), all fp32.
+  void ExportState(std::vector<TensorRecord>* out) const;
+  bool ImportState(const std::vector<TensorRecord>& records, std::string* error);
 
  private:
   struct AdamGroup {
