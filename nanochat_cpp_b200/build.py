@@ -138,6 +138,9 @@ def build_extension(verbose: bool = False) -> str:
     return EXT_PATH
 
 
+CLI_PATH = os.path.join(HERE, "nanochat_cli")
+
+
 def build_core(verbose: bool = False) -> str:
     """Compile the host runtime (no CUDA, no torch)."""
     os.makedirs(BUILD_DIR, exist_ok=True)
@@ -163,7 +166,27 @@ def build_core(verbose: bool = False) -> str:
         f.write(key)
     if verbose:
         print("built", CORE_PATH)
+    build_cli(verbose)
     return CORE_PATH
+
+
+def build_cli(verbose: bool = False) -> str:
+    """The native command line (links only the host runtime; finds it beside itself through $ORIGIN)."""
+    src = os.path.join(CSRC_HOST, "cli", "nanochat_cli.cc")
+    if not os.path.exists(src) or not os.path.exists(CORE_PATH):
+        return ""
+    stamp = os.path.join(BUILD_DIR, "cli.stamp")
+    key = _hash([src, CORE_PATH, os.path.join(os.path.dirname(HERE), "include", "nanochat", "capi.h")], "cli")
+    if os.path.exists(CLI_PATH) and os.path.exists(stamp) and open(stamp).read() == key:
+        return CLI_PATH
+    _run(["g++", "-std=c++20", "-O2", "-I", os.path.join(os.path.dirname(HERE), "include"), src, "-o", CLI_PATH,
+          "-L", HERE, "-lnanochat_core", "-Wl,-rpath,$ORIGIN", "-pthread", "-fopenmp"],
+         os.path.join(BUILD_DIR, "link_cli.log"))
+    with open(stamp, "w") as f:
+        f.write(key)
+    if verbose:
+        print("built", CLI_PATH)
+    return CLI_PATH
 
 
 def build_all(verbose: bool = False) -> None:

@@ -214,6 +214,22 @@ float nanochat_mesh_train_run(const nanochat_mesh_train_config* c, nanochat_mesh
   return last;
 }
 
+nanochat_status nanochat_params_get(const nanochat_config* config, nanochat_params* out) {
+  ncb::EngineConfig c;
+  if (out == nullptr || !ToEngine(config, &c, "nanochat_params_get")) return NANOCHAT_STATUS_ERROR;
+  const int64_t L = c.num_layers, C = c.hidden_dim, V = c.padded_vocab_size;
+  int64_t value_layers = 0;
+  for (int i = 0; i < c.num_layers; ++i) value_layers += c.has_value_embedding(i) ? 1 : 0;
+  out->lm_head = V * C;
+  out->embeddings = V * C + value_layers * V * c.kv_dim();
+  out->transformer_matrices = L * (C * c.query_dim() + 2 * C * c.kv_dim() + C * C + 2 * C * c.mlp_dim()) +
+                              value_layers * c.num_kv_heads * 12;  // value gates read 12 channels
+  out->scalars = 2 * L + 24 + 2;  // residual / x0 lambdas, the smear gate (24 channels), smear and backout lambdas
+  out->total = out->lm_head + out->embeddings + out->transformer_matrices + out->scalars;
+  out->flops_per_token = ncb::EstimateFlopsPerToken(c);
+  return NANOCHAT_STATUS_OK;
+}
+
 // --- collectives over TCP for multi-process CPU jobs (the ports travel through the caller) ------------------
 struct ncb_tcp {
   std::unique_ptr<ncb::TcpTransport> t;

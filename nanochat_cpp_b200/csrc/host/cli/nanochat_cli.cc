@@ -1,0 +1,314 @@
+// nanochat_cli: a native command line over the C ABI (include/nanochat/capi.h) for hosts without Python or a GPU.
+// It runs the CPU engine: `train` (the in-process mesh driver), `generate`, `eval` (bits per byte), `tok_train`,
+// `params`. Flag names follow the Python entry point (`python -m nanochat_cpp_b200.cli`), which follows the
+// reference's `nanochat_cli` (src/train_command.cc:27-61, src/generate_command.cc:37-50, src/eval_command.cc:42-54).
+// The GPU path is driven from Python; this binary links only libnanochat_core.
+//
+// Environment contract of the reference's binaries (include/nanochat/sandbox.h): they refuse to start outside their
+// sandbox. Here the check is opt-in: with NANOCHAT_SANDBOX_ENFORCE=1 the binary exits unless NANOCHAT_SANDBOX names
+// a profile; otherwise the variable is only echoed in `--version`.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "nanochat/capi.h"
+
+namespace {
+
+struct Args {
+  std::map<std::string, std::vector<std::string>> values;
+  bool Has(const std::string& k) const { return values.count(k) != 0; }
+  std::string Str(const std::string& k, const std::string& d = "") const {
+    auto it = values.find(k);
+    return it == values.end() || it->second.empty() ? d : it->second.back();
+  }
+  long long Int(const std::string& k, long long d) const { return Has(k) ? std::atoll(Str(k).c_str()) : d; }
+  double Num(const std::string& k, double d) const { return Has(k) ? std::atof(Str(k).c_str()) : d; }
+  const std::vector<std::string>& All(const std::string& k) const {
+    static const std::vector<std::string> none;
+    auto it = values.find(k);
+    return it == values.end() ? none : it->second;
+  }
+};
+
+// `--key value`, `--key=value`, bare `--flag` (value "1"); a key may repeat.
+Args Parse(int argc, char** argv, int first) {
+  Args a;
+  for (int i = first; i < argc; ++i) {
+    std::string s = argv[i];
+    if (s.rfind("--", 0) != 0) {
+      a.values["_"].push_back(s);
+      continue;
+    }
+    s = s.substr(2);
+    const auto eq = s.find('=');
+    if (eq != std::string::npos) {
+      a.values[s.substr(0, eq)].push_back(s.substr(eq + 1));
+    } else if (i + 1 < argc && std::strncmp(argv[i + 1], "--", 2) != 0) {
+      a.values[s].push_back(argv[++i]);
+    } else {
+      a.values[s].push_back("1");
+    }
+  }
+  return a;
+}
+
+int Fail(const char* what) {
+  const char* e = nanochat_last_error();
+  std::fprintf(stderr, "nanochat_cli: %s%s%s\n", what, e && *e ? ": " : "", e ? e : "");
+  return 1;
+}
+
+// Model flags; `--preset-model` picks a named shape, `--depth N` derives hidden = 64 N rounded up to 128 per head.
+std::string g_pattern;
+nanochat_config ModelFromArgs(const Args& a) {
+  nanochat_config c{};
+  c.num_layers = 12, c.num_heads = 6, c.hidden_dim = 768, c.seq_len = 2048, c.vocab_size = 32768;
+  const std::string preset = a.Str("preset-model");
+  if (preset == "tiny") c.num_layers = 2, c.num_heads = 2, c.hidden_dim = 64, c.seq_len = 64, c.vocab_size = 512;
+  else if (preset == "d12") c.num_layers = 12, c.num_heads = 6, c.hidden_dim = 768, c.vocab_size = 65536;
+  else if (preset == "d20") c.num_layers = 20, c.num_heads = 10, c.hidden_dim = 1280, c.vocab_size = 65536;
+  else if (preset == "d26") c.num_layers = 26, c.num_heads = 13, c.hidden_dim = 1664, c.vocab_size = 65536;
+  if (a.Has("depth")) {
+    const int d = static_cast<int>(a.Int("depth", 12));
+    c.num_layers = d;
+    c.hidden_dim = (d * 64 + 127) / 128 * 128;
+    c.num_heads = c.hidden_dim / 128;
+  }
+  c.num_layers = static_cast<int>(a.Int("layers", c.num_layers));
+  c.num_heads = static_cast<int>(a.Int("heads", c.num_heads));
+  c.hidden_dim = static_cast<int>(a.Int("hidden", c.hidden_dim));
+  c.seq_len = static_cast<int>(a.Int("seq", c.seq_len));
+  c.vocab_size = static_cast<int>(a.Int("vocab", c.vocab_size));
+  c.num_kv_heads = static_cast<int>(a.Int("kv-heads", 0));
+  if (c.num_kv_heads <= 0) c.num_kv_heads = c.num_heads;
+  c.padded_vocab_size = static_cast<int>(a.Int("padded-vocab", 0));
+  if (c.padded_vocab_size <= 0) c.padded_vocab_size = (c.vocab_size + 63) / 64 * 64;
+  c.rope_base = static_cast<float>(a.Num("rope-base", 100000.0));
+  g_pattern = a.Str("window-pattern", "SSSL");
+  c.window_pattern = g_pattern.c_str();
+  c.value_embedding = a.Has("no-value-embedding") ? 0 : 1;
+  return c;
+}
+
+bool OptimFromArgs(const Args& a, nanochat_optim_config* o) {
+  if (nanochat_optim_config_preset(a.Str("preset", "default").c_str(), o) != NANOCHAT_STATUS_OK) return false;
+  o->embedding_lr = static_cast<float>(a.Num("embedding-lr", o->embedding_lr));
+  o->unembedding_lr = static_cast<float>(a.Num("unembedding-lr", o->unembedding_lr));
+  o->matrix_lr = static_cast<float>(a.Num("matrix-lr", o->matrix_lr));
+  o->scalar_lr = static_cast<float>(a.Num("scalar-lr", o->scalar_lr));
+  o->weight_decay = static_cast<float>(a.Num("weight-decay", o->weight_decay));
+  o->weight_decay_base = static_cast<float>(a.Num("weight-decay-base", o->weight_decay_base));
+  o->clip = static_cast<float>(a.Num("clip", o->clip));
+  o->adam_eps = static_cast<float>(a.Num("adam-eps", o->adam_eps));
+  o->muon_ns_steps = static_cast<int>(a.Int("muon-ns-steps", o->muon_ns_steps));
+  o->muon_beta2 = static_cast<float>(a.Num("muon-beta2", o->muon_beta2));
+  o->warmup_steps = static_cast<int>(a.Int("warmup-steps", o->warmup_steps));
+  o->warmdown_ratio = static_cast<float>(a.Num("warmdown-ratio", o->warmdown_ratio));
+  o->final_lr_frac = static_cast<float>(a.Num("final-lr-frac", o->final_lr_frac));
+  o->muon_momentum_warmup_steps = static_cast<float>(a.Num("muon-momentum-warmup-steps", o->muon_momentum_warmup_steps));
+  o->muon_momentum_start = static_cast<float>(a.Num("muon-momentum-start", o->muon_momentum_start));
+  o->muon_momentum_peak = static_cast<float>(a.Num("muon-momentum-peak", o->muon_momentum_peak));
+  o->muon_momentum_final = static_cast<float>(a.Num("muon-momentum-final", o->muon_momentum_final));
+  o->num_iterations = static_cast<int>(a.Int("num-iterations", 100));
+  return true;
+}
+
+int CmdTrain(const Args& a) {
+  nanochat_mesh_train_config c{};
+  c.model = ModelFromArgs(a);
+  nanochat_optim_config optim;
+  if (!OptimFromArgs(a, &optim)) return Fail("train");
+  c.optimizer = &optim;
+  nanochat_mesh* mesh = nanochat_mesh_create(nullptr, static_cast<int>(a.Int("world-size", 1)));
+  c.mesh = mesh;
+  std::vector<const char*> parquet;
+  for (const std::string& p : a.All("train-parquet")) parquet.push_back(p.c_str());
+  c.data.parquet = parquet.data();
+  c.data.parquet_count = static_cast<int>(parquet.size());
+  const std::string tok = a.Str("tokenizer"), rows = a.Str("rows"), warm = a.Str("warm-start");
+  const std::string out_dir = a.Str("out-dir", "."), ckpt = a.Str("checkpoint");
+  c.data.tokenizer_path = tok.c_str();
+  c.data.packed_rows_path = rows.c_str();
+  c.warm_start_path = warm.c_str();
+  c.run.batch = static_cast<int>(a.Int("batch", 8));
+  c.run.grad_accum = static_cast<int>(a.Int("grad-accum", 1));
+  c.run.seq = static_cast<int>(a.Int("train-seq", 0));
+  c.run.seed = static_cast<uint64_t>(a.Int("seed", 42));
+  c.run.num_iterations = static_cast<int>(a.Int("num-iterations", 100));
+  c.run.log_every = static_cast<int>(a.Int("log-every", 10));
+  c.run.save_every = static_cast<int>(a.Int("save-every", 0));
+  c.run.resume = a.Has("resume") ? 1 : 0;
+  c.peak_flops = a.Num("peak-flops", 0.0);
+  c.output.out_dir = out_dir.c_str();
+  c.output.checkpoint_path = ckpt.c_str();
+  nanochat_mesh_train_summary s{};
+  const float last = nanochat_mesh_train_run(&c, &s);
+  nanochat_mesh_free(mesh);
+  if (s.steps == 0 && last == 0.0f) return Fail("train");
+  std::printf("[nanochat] %d steps%s, mean loss %.6f, last loss %.6f, checkpoint %s\n", s.steps,
+              s.interrupted ? " (interrupted)" : "", s.mean_loss, last, s.checkpoint);
+  return 0;
+}
+
+nanochat_model* LoadModel(const Args& a, nanochat_config* cfg) {
+  *cfg = ModelFromArgs(a);
+  nanochat_model* m = nanochat_model_create(cfg, static_cast<uint64_t>(a.Int("seed", 42)));
+  if (m != nullptr && a.Has("model")) {
+    nanochat_load(m, a.Str("model").c_str());
+    const char* e = nanochat_last_error();
+    if (e != nullptr && *e) {
+      nanochat_model_free(m);
+      return nullptr;
+    }
+  }
+  return m;
+}
+
+int CmdGenerate(const Args& a) {
+  nanochat_config cfg;
+  nanochat_model* m = LoadModel(a, &cfg);
+  if (m == nullptr) return Fail("generate");
+  nanochat_tokenizer* tok = a.Has("tokenizer") ? nanochat_tokenizer_load(a.Str("tokenizer").c_str()) : nullptr;
+  std::vector<int> prompt;
+  if (a.Has("tokens")) {
+    const std::string s = a.Str("tokens");
+    for (std::size_t i = 0; i < s.size();) {
+      std::size_t j = s.find(',', i);
+      if (j == std::string::npos) j = s.size();
+      prompt.push_back(std::atoi(s.substr(i, j - i).c_str()));
+      i = j + 1;
+    }
+  } else if (tok != nullptr) {
+    const std::string text = a.Str("prompt");
+    prompt.resize(text.size() + 8);
+    const int n = nanochat_encode(tok, text.c_str(), prompt.data(), static_cast<int>(prompt.size()));
+    prompt.resize(static_cast<std::size_t>(n > 0 ? n : 0));
+    const int bos = ncb_tokenizer_special_id(tok, "<|bos|>");
+    if (bos >= 0) prompt.insert(prompt.begin(), bos);
+  }
+  if (prompt.empty()) {
+    std::fprintf(stderr, "nanochat_cli generate: give --tokens a,b,c or --tokenizer with --prompt\n");
+    return 2;
+  }
+  nanochat_generate_params p{};
+  p.num_samples = static_cast<int>(a.Int("num-samples", 1));
+  p.max_tokens = static_cast<int>(a.Int("max-tokens", 32));
+  p.temperature = static_cast<float>(a.Num("temperature", 0.0));
+  p.top_k = static_cast<int>(a.Int("top-k", 0));
+  p.seed = static_cast<uint64_t>(a.Int("seed", 42));
+  p.stop_id = static_cast<int>(a.Int("stop-id", -1));
+  p.bos_id = static_cast<int>(a.Int("bos-id", -1));
+  nanochat_sequences out{};
+  nanochat_generate(m, prompt.data(), static_cast<int>(prompt.size()), &p, &out);
+  for (int r = 0; r < out.count; ++r) {
+    const int* row = out.tokens + out.offsets[r];
+    const int len = out.lengths[r];
+    if (tok != nullptr) {
+      std::vector<char> text(static_cast<std::size_t>(len) * 16 + 16);
+      const int n = nanochat_decode(tok, row, len, text.data(), static_cast<int>(text.size()));
+      std::printf("%.*s\n", n > 0 ? n : 0, text.data());
+    } else {
+      for (int i = 0; i < len; ++i) std::printf("%s%d", i ? "," : "", row[i]);
+      std::printf("\n");
+    }
+  }
+  if (tok) nanochat_tokenizer_free(tok);
+  nanochat_model_free(m);
+  return 0;
+}
+
+int CmdEval(const Args& a) {
+  nanochat_config cfg;
+  nanochat_model* m = LoadModel(a, &cfg);
+  if (m == nullptr) return Fail("eval");
+  nanochat_tokenizer* tok = nanochat_tokenizer_load(a.Str("tokenizer").c_str());
+  if (tok == nullptr) return Fail("eval: tokenizer");
+  std::vector<const char*> parquet;
+  for (const std::string& p : a.All("val-parquet")) parquet.push_back(p.c_str());
+  const int batch = static_cast<int>(a.Int("batch", 8)), seq = static_cast<int>(a.Int("eval-seq", cfg.seq_len));
+  nanochat_loader* loader = nanochat_loader_create(parquet.data(), static_cast<int>(parquet.size()),
+                                                   a.Str("text-column", "text").c_str(), tok, batch, seq, 0, 1,
+                                                   static_cast<size_t>(a.Int("buffer-docs", 1000)));
+  if (loader == nullptr) return Fail("eval: loader");
+  const float bpb = nanochat_eval_bpb(m, loader, static_cast<int>(a.Int("steps", 10)));
+  std::printf("val_bpb %.6f\n", bpb);
+  nanochat_loader_free(loader);
+  nanochat_tokenizer_free(tok);
+  nanochat_model_free(m);
+  return 0;
+}
+
+int CmdTokTrain(const Args& a) {
+  nanochat_tokenizer* tok = ncb_tokenizer_train(a.Has("text") ? a.Str("text").c_str() : nullptr,
+                                                a.Has("parquet") ? a.Str("parquet").c_str() : nullptr,
+                                                a.Str("text-column", "text").c_str(),
+                                                static_cast<int>(a.Int("vocab", 32768)), a.Int("doc-cap", 10000),
+                                                a.Int("max-chars", 10000000000ll));
+  if (tok == nullptr) return Fail("tok_train");
+  const nanochat_status st = ncb_tokenizer_save(tok, a.Str("out", "tokenizer.nctoken").c_str());
+  std::printf("vocab %d -> %s\n", ncb_tokenizer_vocab_size(tok), a.Str("out", "tokenizer.nctoken").c_str());
+  nanochat_tokenizer_free(tok);
+  return st == NANOCHAT_STATUS_OK ? 0 : Fail("tok_train: save");
+}
+
+int CmdParams(const Args& a) {
+  nanochat_config cfg = ModelFromArgs(a);
+  nanochat_params p{};
+  if (nanochat_params_get(&cfg, &p) != NANOCHAT_STATUS_OK) return Fail("params");
+  std::printf("{\"total\": %lld, \"transformer_matrices\": %lld, \"lm_head\": %lld, \"embeddings\": %lld, "
+              "\"scalars\": %lld, \"flops_per_token\": %.0f}\n",
+              static_cast<long long>(p.total), static_cast<long long>(p.transformer_matrices),
+              static_cast<long long>(p.lm_head), static_cast<long long>(p.embeddings),
+              static_cast<long long>(p.scalars), p.flops_per_token);
+  return 0;
+}
+
+void Usage() {
+  std::printf(
+      "nanochat_cli <command> [--flag value ...]     (native CPU engine; the GPU path is `python -m nanochat_cpp_b200.cli`)\n"
+      "  train      --train-parquet P.. --tokenizer T | --rows shard.nchsft   [--world-size N --batch B --grad-accum A\n"
+      "             --num-iterations K --log-every L --save-every S --out-dir D --checkpoint C --resume --warm-start W\n"
+      "             --preset track3 + optimizer / schedule / model flags]\n"
+      "  generate   --model C [--tokenizer T --prompt TEXT | --tokens a,b,c] --max-tokens N --num-samples S\n"
+      "             --temperature X --top-k K --seed Z --stop-id I\n"
+      "  eval       --model C --val-parquet P.. --tokenizer T --steps N --batch B\n"
+      "  tok_train  --text F | --parquet P  --vocab V --out tokenizer.nctoken\n"
+      "  params     model flags -> parameter counts and FLOPs per token (JSON)\n"
+      "model flags: --preset-model tiny|d12|d20|d26 | --depth N | --layers --heads --kv-heads --hidden --seq --vocab\n"
+      "             --padded-vocab --rope-base --window-pattern --no-value-embedding\n");
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  const char* sandbox = std::getenv("NANOCHAT_SANDBOX");
+  const char* enforce = std::getenv("NANOCHAT_SANDBOX_ENFORCE");
+  if (enforce != nullptr && std::strcmp(enforce, "1") == 0 && (sandbox == nullptr || !*sandbox)) {
+    std::fprintf(stderr, "nanochat_cli: NANOCHAT_SANDBOX is not set and NANOCHAT_SANDBOX_ENFORCE=1; refusing to start\n");
+    return 3;
+  }
+  if (argc < 2 || std::strcmp(argv[1], "help") == 0 || std::strcmp(argv[1], "--help") == 0) {
+    Usage();
+    return argc < 2 ? 2 : 0;
+  }
+  const std::string cmd = argv[1];
+  if (cmd == "--version" || cmd == "version") {
+    std::printf("nanochat_cli %s (backend %s, sandbox %s)\n", nanochat_version(), nanochat_backend(),
+                sandbox != nullptr && *sandbox ? sandbox : "none");
+    return 0;
+  }
+  if (nanochat_init() != NANOCHAT_STATUS_OK) return Fail("init");
+  const Args a = Parse(argc, argv, 2);
+  if (cmd == "train") return CmdTrain(a);
+  if (cmd == "generate") return CmdGenerate(a);
+  if (cmd == "eval") return CmdEval(a);
+  if (cmd == "tok_train") return CmdTokTrain(a);
+  if (cmd == "params") return CmdParams(a);
+  std::fprintf(stderr, "nanochat_cli: unknown command '%s'\n", cmd.c_str());
+  Usage();
+  return 2;
+}
