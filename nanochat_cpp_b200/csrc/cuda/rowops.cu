@@ -693,6 +693,47 @@ __global__ void __launch_bounds__(kThreads) embedding_bwd_kernel(const int* __re
   }
 }
 
+// Deterministic variant: the token ids arrive stably sorted (`perm[j]` = original row of sorted position j). The
+// warp at the head of a run of equal ids sums the run's rows in ascending row order in fp32 registers and is the
+// only writer of that table row, so the result does not depend on scheduling (the atomic kernel above adds in
+// arrival order). The reference's embedding backward is deterministic too, one thread per (row of the table,
+// column) scanning all tokens (backends/cuda/kernels/embedding.cu); this keeps that property at O(tokens) work.
+__global__ void __launch_bounds__(kThreads) embedding_bwd_sorted_kernel(const int* __restrict__ sorted_ids,
+                                                                        const int* __restrict__ perm,
+                                                                        const bf16* __restrict__ dout, long long ld,
+                                                                        float* __restrict__ dtable, int tokens,
+                                                                        int dim) {
+  const int i = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (i >= tokens) return;
+  const int id = sorted_ids[i];
+  if (i > 0 && sorted_ids[i - 1] == id) return;  // not the head of its run
+  const int lane = threadIdx.x & 31;
+  float* dst = dtable + static_cast<long long>(id) * dim;
+  const bool vec = dim % 8 == 0 && ld % 8 == 0 && aligned16(dout) && aligned16(dst);
+  if (vec) {
+    for (int c0 = lane * 8; c0 < dim; c0 += 256) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = i; j < tokens && sorted_ids[j] == id; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(dout + static_cast<long long>(perm[j]) * ld + c0);
+        const bf16* h = reinterpret_cast<const bf16*>(&v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += b2f(h[k]);
+      }
+      float4* d4 = reinterpret_cast<float4*>(dst + c0);
+      float4 lo = d4[0], hi = d4[1];
+      lo.x += acc[0], lo.y += acc[1], lo.z += acc[2], lo.w += acc[3];
+      hi.x += acc[4], hi.y += acc[5], hi.z += acc[6], hi.w += acc[7];
+      d4[0] = lo, d4[1] = hi;
+    }
+  } else {
+    for (int c = lane; c < dim; c += 32) {
+      float acc = 0.f;
+      for (int j = i; j < tokens && sorted_ids[j] == id; ++j) acc += b2f(dout[static_cast<long long>(perm[j]) * ld + c]);
+      dst[c] += acc;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ softcap + cross entropy (+ backward, in place)
 __device__ __forceinline__ float tanh_acc(float x) {
   // 1 - 2/(exp(2x)+1): accurate to a few ulp and saturates cleanly for large |x|
@@ -1035,6 +1076,12 @@ void embedding_fwd(const int* ids, const bf16* table, bf16* out, int tokens, int
 void embedding_bwd(const int* ids, const bf16* dout, long long ld, float* dtable, int tokens, int dim, cudaStream_t s) {
   if (tokens <= 0) return;
   embedding_bwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(ids, dout, ld, dtable, tokens, dim);
+}
+void embedding_bwd_sorted(const int* sorted_ids, const int* perm, const bf16* dout, long long ld, float* dtable,
+                          int tokens, int dim, cudaStream_t s) {
+  if (tokens <= 0) return;
+  embedding_bwd_sorted_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(sorted_ids, perm, dout, ld, dtable, tokens,
+                                                                           dim);
 }
 void classifier_fwd_bwd(bf16* logits, long long ld, const int* targets, float* losses, const float* row_scale,
                         const float* dlogit_scale, int rows, int vocab, int padded, float softcap, int ignore_index,

@@ -54,6 +54,9 @@ void smear_bwd(const bf16* emb, const bf16* gate_w, const float* lam, const floa
 void embedding_fwd(const int* ids, const bf16* table, bf16* out, int tokens, int dim, cudaStream_t s);
 // dtable[ids[t]] += dout[t] (fp32 accumulate, vector red.global.add)
 void embedding_bwd(const int* ids, const bf16* dout, long long ld, float* dtable, int tokens, int dim, cudaStream_t s);
+// Same sum with a fixed order: `sorted_ids` stably sorted, `perm` the original row of each sorted position.
+void embedding_bwd_sorted(const int* sorted_ids, const int* perm, const bf16* dout, long long ld, float* dtable,
+                          int tokens, int dim, cudaStream_t s);
 
 // Softcap + cross entropy over [rows, padded] bf16 logits, in place: logits are overwritten by dlogits when
 // `want_grad`. dlogit_scale is a device scalar. losses[row] = 0 on ignored rows.

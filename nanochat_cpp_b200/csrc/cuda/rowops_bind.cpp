@@ -213,6 +213,18 @@ void embedding_bwd(const Tensor& ids, const Tensor& dout, Tensor& dtable) {
   nc::embedding_bwd(ids.data_ptr<int>(), bp(dout), dout.stride(0), dtable.data_ptr<float>(), ids.numel(),
                     dtable.size(1), cur());
 }
+void embedding_bwd_sorted(const Tensor& sorted_ids, const Tensor& perm, const Tensor& dout, Tensor& dtable) {
+  chk(sorted_ids, torch::kInt32, "sorted_ids");
+  chk(perm, torch::kInt32, "perm");
+  chk_rows(dout, "dout");
+  chk(dtable, torch::kFloat32, "dtable");
+  TORCH_CHECK(dtable.is_contiguous() && sorted_ids.is_contiguous() && perm.is_contiguous() &&
+                  perm.numel() == sorted_ids.numel() && dout.size(0) == sorted_ids.numel(),
+              "embedding_bwd_sorted");
+  const c10::cuda::CUDAGuard g(dout.device());
+  nc::embedding_bwd_sorted(sorted_ids.data_ptr<int>(), perm.data_ptr<int>(), bp(dout), dout.stride(0),
+                           dtable.data_ptr<float>(), sorted_ids.numel(), dtable.size(1), cur());
+}
 
 // In place: `logits` becomes dlogits when want_grad. Returns per-row losses.
 Tensor classifier_fwd_bwd(Tensor& logits, const Tensor& targets, int64_t vocab, const c10::optional<Tensor>& dscale,
@@ -276,6 +288,7 @@ void register_rowops(pybind11::module_& m) {
   m.def("smear_bwd", &smear_bwd);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
+  m.def("embedding_bwd_sorted", &embedding_bwd_sorted);
   m.def("classifier_fwd_bwd", &classifier_fwd_bwd);
   m.def("grad_norm_clip", &grad_norm_clip);
   m.def("sumsq_into", &sumsq_into);

@@ -20,7 +20,8 @@ constexpr std::size_t kAlign = 64;
 // The three products below carry the model's FLOPs. Inner loops are written so that the compiler vectorizes them
 // (float lanes, folded into a double every 256 elements, which keeps the 1e-5 agreement with the fp64-accumulating
 // oracle), are cloned for AVX2+FMA / AVX-512 with run-time dispatch, and rows are spread over OpenMP threads.
-#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__) && !defined(__SANITIZE_THREAD__) && \
+    !defined(__SANITIZE_ADDRESS__)  // ifunc resolvers run before a sanitizer runtime is up
 #define NCB_SIMD_CLONES __attribute__((target_clones("avx512f", "avx2,fma", "default")))
 #else
 #define NCB_SIMD_CLONES

@@ -54,6 +54,9 @@ class GPT:
         self.on_head_grads_ready: Optional[Callable[[], None]] = None
         self.on_embed_grads_ready: Optional[Callable[[], None]] = None
         self.fp8 = bool(fp8) and self.device.type == "cuda"
+        # bitwise-reproducible embedding gradients (sorted, single-writer sums instead of atomics)
+        import os as _os
+        self.deterministic_embedding = _os.environ.get("NANOCHAT_DETERMINISTIC", "0") == "1"
         self._fp8_w: Dict[str, object] = {}
         if self.fp8:
             self.refresh_fp8()
@@ -236,6 +239,7 @@ class GPT:
         M = B * T
         tok = tokens.reshape(-1).to(torch.int32)
         tgt = targets.reshape(-1).to(torch.int32)
+        order = ops.embedding_order(tok) if self.deterministic_embedding else None
         save: dict = {"layers": []}
         xn = self._trunk(tok, B, T, save)
         valid = (tgt != -1).sum().clamp_min(1).float()
@@ -292,7 +296,7 @@ class GPT:
             if cfg.has_value_embedding(i):
                 dve, dh12, dgw = ops.value_gate_bwd(h, s["ve"], self._w(i, "attn.ve_gate"), s["gate"], dv2, D)
                 self._g(i, "attn.ve_gate").add_(dgw)
-                ops.embedding_bwd(tok, dve, P.g(f"value_embeds.{i}.weight"))
+                ops.embedding_bwd(tok, dve, P.g(f"value_embeds.{i}.weight"), order=order)
                 del dve
             gqkv = P.qkv_view(i, "g")
             wqkv = P.qkv_view(i)
@@ -326,7 +330,7 @@ class GPT:
         P.g("smear_gate.weight").view(-1).add_(dgw)
         P.g("smear_lambda").add_(dlam)
         de_raw = ops.rmsnorm_bwd(save["emb_raw"], de, save["rstd_e"])
-        ops.embedding_bwd(tok, de_raw, P.g("transformer.wte.weight"))
+        ops.embedding_bwd(tok, de_raw, P.g("transformer.wte.weight"), order=order)
         if self.on_embed_grads_ready is not None:
             self.on_embed_grads_ready()
         self._saved = None

@@ -121,7 +121,7 @@ _NAMES = [
     "linear_wgrad_relu2", "rmsnorm_fwd", "rmsnorm_apply", "rmsnorm_bwd", "add", "add_cols", "concat_qkv",
     "backout_fwd", "backout_bwd", "blend_norm_fwd", "blend_bwd", "qk_prep_fwd", "qk_prep_bwd",
     "attention_fwd", "attention_bwd", "value_gate_fwd", "value_gate_bwd", "smear_fwd", "smear_bwd",
-    "embedding_fwd", "embedding_bwd", "classifier_fwd_bwd", "adamw_update", "muon_update",
+    "embedding_fwd", "embedding_bwd", "embedding_order", "classifier_fwd_bwd", "adamw_update", "muon_update",
     "grad_norm_and_clip", "kv_append", "paged_decode_attention",
 ]
 for _n in _NAMES:

@@ -259,8 +259,20 @@ def embedding_fwd(ids, table):
     return _C.embedding_fwd(ids.reshape(-1).contiguous(), table)
 
 
-def embedding_bwd(ids, dout, dtable):
-    _C.embedding_bwd(ids.reshape(-1).contiguous(), dout, dtable)
+def embedding_order(ids):
+    """(sorted ids, original row of each sorted position) of a stable sort: the fixed summation order of the
+    deterministic embedding backward. Computed once per micro-batch and shared by every table of the step."""
+    s, perm = torch.sort(ids.reshape(-1), stable=True)
+    return s.to(torch.int32).contiguous(), perm.to(torch.int32).contiguous()
+
+
+def embedding_bwd(ids, dout, dtable, order=None):
+    """dtable[ids[m]] += dout[m]. With `order` (from `embedding_order`) the sum runs in a fixed order with one writer
+    per table row (bitwise reproducible); without it rows are added with vector atomics in arrival order."""
+    if order is not None:
+        _C.embedding_bwd_sorted(order[0], order[1], dout, dtable)
+    else:
+        _C.embedding_bwd(ids.reshape(-1).contiguous(), dout, dtable)
     return dtable
 
 

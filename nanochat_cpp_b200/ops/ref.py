@@ -366,7 +366,12 @@ def embedding_fwd(ids, table):
     return table.index_select(0, ids.reshape(-1).long())
 
 
-def embedding_bwd(ids, dout, dtable):
+def embedding_order(ids):
+    s, perm = torch.sort(ids.reshape(-1), stable=True)
+    return s.to(torch.int32), perm.to(torch.int32)
+
+
+def embedding_bwd(ids, dout, dtable, order=None):
     dtable.index_add_(0, ids.reshape(-1).long(), dout.to(dtable.dtype))
     return dtable
 

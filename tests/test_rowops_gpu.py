@@ -161,3 +161,29 @@ def test_grad_norm():
     assert abs(scale.item() - 1.0 / g.double().norm().item()) < 1e-6
     norm2, scale2 = K.grad_norm_and_clip([g[:1000], g[1000:]], 0.0)
     assert abs(norm2.item() - norm.item()) < 1e-2 and scale2.item() == 1.0
+
+
+@pytest.mark.parametrize("tokens,vocab,dim", [(4096, 97, 1280), (1000, 5000, 100), (513, 3, 64)])
+def test_embedding_bwd_sorted_is_exact_and_reproducible(tokens, vocab, dim):
+    """The sorted single-writer scatter: equal to the fp32 index_add, and the same bits on every run."""
+    K = _K()
+    torch.manual_seed(tokens + vocab)
+    ids = torch.randint(0, vocab, (tokens,), device="cuda", dtype=torch.int32)
+    ids[: tokens // 3] = 1  # one very frequent token
+    g = _r(tokens, dim)
+    order = K.embedding_order(ids)
+    assert torch.equal(order[0].long(), ids.long()[order[1].long()])
+    outs = []
+    for _ in range(3):
+        dt = torch.ones(vocab, dim, device="cuda", dtype=torch.float32)
+        K.embedding_bwd(ids, g, dt, order=order)
+        outs.append(dt)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    want = ref.embedding_bwd(ids, g, torch.ones(vocab, dim, device="cuda", dtype=torch.float64)).float()
+    torch.testing.assert_close(outs[0], want, rtol=1e-5, atol=1e-4)
+    # a strided view (a column slice of a wider buffer) takes the same path
+    wide = _r(tokens, dim + 64)
+    dt = torch.zeros(vocab, dim, device="cuda", dtype=torch.float32)
+    K.embedding_bwd(ids, wide[:, :dim], dt, order=order)
+    want = ref.embedding_bwd(ids, wide[:, :dim], torch.zeros(vocab, dim, device="cuda", dtype=torch.float64)).float()
+    torch.testing.assert_close(dt, want, rtol=1e-5, atol=1e-4)
