@@ -53,6 +53,7 @@ class GPT:
         self.on_layer_grads_ready: Optional[Callable[[int], None]] = None
         self.on_head_grads_ready: Optional[Callable[[], None]] = None
         self.on_embed_grads_ready: Optional[Callable[[], None]] = None
+        self.phase_event = None  # a CUDA event recorded between the forward trunk and the head / backward
         self.fp8 = bool(fp8) and self.device.type == "cuda"
         # bitwise-reproducible embedding gradients (sorted, single-writer sums instead of atomics)
         import os as _os
@@ -242,6 +243,8 @@ class GPT:
         order = ops.embedding_order(tok) if self.deterministic_embedding else None
         save: dict = {"layers": []}
         xn = self._trunk(tok, B, T, save)
+        if self.phase_event is not None:  # end of the forward trunk (the head runs forward and backward fused)
+            self.phase_event.record()
         valid = (tgt != -1).sum().clamp_min(1).float()
         denom = valid if divisor is None else torch.full_like(valid, float(divisor))
         dscale = (grad_scale / denom)

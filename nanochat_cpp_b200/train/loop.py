@@ -62,6 +62,8 @@ class Trainer:
             dp.attach(self.model, self.optimizer)
         self.step_count = 0
         self.last_loss: Optional[torch.Tensor] = None
+        self.time_phases = False      # set for one step by the loop on logging steps
+        self._phase_events = None
 
     @torch.no_grad()
     def train_step(self, micro_batches: Sequence[Tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor:
@@ -70,6 +72,13 @@ class Trainer:
         m = self.model
         accum = len(micro_batches)
         scale = 1.0 / (accum * self.world)
+        timed = self.time_phases and self.device.type == "cuda"
+        ev = None
+        if timed:  # phase timers of a logging step: events only, nothing is synchronised here
+            ev = {k: torch.cuda.Event(enable_timing=True) for k in ("start", "bwd_end", "end")}
+            ev["fwd_end"] = [torch.cuda.Event(enable_timing=True) for _ in range(accum)]
+            ev["micro"] = [torch.cuda.Event(enable_timing=True) for _ in range(accum)]
+            ev["start"].record()
         if self.dp is not None:
             self.dp.begin_step(self.step_count + 1)
         m.zero_grad()
@@ -77,13 +86,22 @@ class Trainer:
         for k, (tokens, targets) in enumerate(micro_batches):
             if self.dp is not None:
                 self.dp.set_last_micro(k == accum - 1)
+            if timed:
+                ev["micro"][k].record()
+                m.phase_event = ev["fwd_end"][k]
             loss = m.forward_backward(tokens, targets, grad_scale=scale)
             total = loss if total is None else total + loss
+        m.phase_event = None
+        if timed:
+            ev["bwd_end"].record()
         self.step_count += 1
         if self.dp is not None:
             self.dp.finish_step(self.step_count)
         else:
             self.optimizer.step(self.step_count)
+        if timed:
+            ev["end"].record()
+            self._phase_events = ev
         if m.fp8:
             if self.dp is not None and getattr(self.dp, "fused", None) is not None:
                 # owners push the new bf16 weights asynchronously: wait (on the stream) for this step's pushes
@@ -93,6 +111,20 @@ class Trainer:
             m.refresh_fp8()
         self.last_loss = total / accum
         return self.last_loss
+
+    def phase_times(self) -> dict:
+        """fwd / bwd / opt milliseconds of the last step run with `time_phases` (after a device synchronise). `opt`
+        is the optimizer step including, under data parallelism, whatever gradient synchronisation is still
+        outstanding after the last backward kernel (`sync` is reported inside it: the fused transport has no
+        separate phase)."""
+        ev = self._phase_events
+        if ev is None:
+            return {"fwd_ms": 0.0, "bwd_ms": 0.0, "sync_ms": 0.0, "opt_ms": 0.0}
+        accum = len(ev["micro"])
+        fwd = sum(ev["micro"][k].elapsed_time(ev["fwd_end"][k]) for k in range(accum))
+        whole = ev["start"].elapsed_time(ev["bwd_end"])
+        return {"fwd_ms": fwd, "bwd_ms": max(0.0, whole - fwd), "sync_ms": 0.0,
+                "opt_ms": ev["bwd_end"].elapsed_time(ev["end"])}
 
     def tokens_per_step(self) -> int:
         return self.tc.batch * self.cfg.seq_len * self.tc.grad_accum * self.world
@@ -170,9 +202,10 @@ class Trainer:
             t0 = time.perf_counter()
             micro = self._stage(train_loader)
             data_ms += (time.perf_counter() - t0) * 1e3
+            final = step == tc.num_iterations
+            self.time_phases = (tc.log_every > 0 and step % tc.log_every == 0) or final
             loss = self.train_step(micro)
             steps_since += 1
-            final = step == tc.num_iterations
             eval_ms = 0.0
             bpb = None
             if val_loader is not None and tc.eval_every > 0 and (step % tc.eval_every == 0 or final):
@@ -190,14 +223,16 @@ class Trainer:
                 gn = self.optimizer.grad_norm()
                 lr = self.optimizer.scheduler.lr_multiplier(step)
                 mfu_v = perf.mfu(tok_s / self.world, self.cfg, peaks["bf16_tflops_sustained"])
+                phases = self.phase_times() if cuda else {"fwd_ms": 0.0, "bwd_ms": 0.0, "sync_ms": 0.0, "opt_ms": 0.0}
                 last = dict(step=step, loss=lv, lr=lr, grad_norm=gn, tok_s=tok_s, mfu=mfu_v,
                             model_tflops=tok_s * fpt / 1e12, optim_tflops=muon_flops / (step_ms / 1e3) / 1e12,
-                            step_ms=step_ms, data_ms=data_ms / max(steps_since, 1), eval_ms=eval_ms)
+                            step_ms=step_ms, data_ms=data_ms / max(steps_since, 1), eval_ms=eval_ms, **phases)
                 if bpb is not None:
                     last["val_bpb"] = bpb
                 losses.append(lv)
                 emit(format_log_line(step, lv, lr, gn, tok_s, mfu_v, last["model_tflops"], last["optim_tflops"],
-                                     step_ms, last["data_ms"], eval_ms=eval_ms))
+                                     step_ms, last["data_ms"], fwd_ms=phases["fwd_ms"], bwd_ms=phases["bwd_ms"],
+                                     sync_ms=phases["sync_ms"], opt_ms=phases["opt_ms"], eval_ms=eval_ms))
                 if met_f:
                     met_f.write(json.dumps(last) + "\n")
                     met_f.flush()
