@@ -298,6 +298,19 @@ typedef struct {
  * Returns the last loss, 0 on error. */
 float nanochat_mesh_train_run(const nanochat_mesh_train_config* config, nanochat_mesh_train_summary* out);
 
+/* Sliding window (tokens to the left) of `S` layers for every model created afterwards; 0 = ceil(seq/4/128)*128. */
+void ncb_set_short_window(int tokens);
+
+/* ---- performance model: analytic roofline of one training step as `nanochat.roofline.v3` JSON (or a text table).
+ * `device`: b200 | h100 | t4 | cpu; measured_* > 0 override the B200 peaks. Returns the text length, negative on error. */
+int64_t ncb_roofline(const nanochat_config* config, const char* device, const char* precision, int batch, int grad_accum,
+                     int world_size, int64_t total_tokens, double link_gbps, double latency_us, double overlap,
+                     int muon_ns_steps, double measured_bf16_tflops, double measured_hbm_gbs, int as_table, char* out,
+                     int64_t capacity);
+double ncb_muon_flops_per_step(const nanochat_config* config, int ns_steps);
+double ncb_prefill_flops(const nanochat_config* config, int prompt_tokens);
+double ncb_decode_flops_per_token(const nanochat_config* config, int context_tokens);
+
 /* ---- host collectives (TCP over 127.0.0.1 between CPU ranks; an in-process ring for tests) */
 typedef struct ncb_tcp ncb_tcp;
 ncb_tcp* ncb_tcp_create(int rank, int world);

@@ -25,6 +25,9 @@ struct nanochat_checkpoint {
 };
 
 void ncb_set_error(const std::string& msg);
+// Process-wide override of the sliding window of `S` layers (0: ceil(seq/4/128)*128), applied to every model the
+// C ABI creates afterwards; `nanochat_config` keeps the reference's layout and has no field for it.
+int& ncb_short_window_override();
 
 inline ncb::ModelConfig ncb_to_model_config(const nanochat_config& c) {
   ncb::ModelConfig m;

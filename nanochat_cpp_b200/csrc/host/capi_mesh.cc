@@ -7,6 +7,7 @@
 
 #include "capi_internal.h"
 #include "mesh.h"
+#include "perf.h"
 
 struct nanochat_mesh {
   ncb::MeshSpec spec;
@@ -36,6 +37,7 @@ bool ToEngine(const nanochat_config* config, ncb::EngineConfig* cfg, const char*
     return false;
   }
   static_cast<ncb::ModelConfig&>(*cfg) = ncb_to_model_config(*config);
+  cfg->short_window_override = ncb_short_window_override();
   std::string err;
   if (!cfg->Validate(&err)) {
     ncb_set_error(std::string(who) + ": " + err);
@@ -56,7 +58,14 @@ bool Try(const char* who, F&& f) {
 
 }  // namespace
 
+int& ncb_short_window_override() {
+  static int value = 0;
+  return value;
+}
+
 extern "C" {
+
+void ncb_set_short_window(int tokens) { ncb_short_window_override() = tokens > 0 ? tokens : 0; }
 
 nanochat_mesh* nanochat_mesh_create(const int* indices, int count) {
   auto* m = new nanochat_mesh();
@@ -217,17 +226,52 @@ float nanochat_mesh_train_run(const nanochat_mesh_train_config* c, nanochat_mesh
 nanochat_status nanochat_params_get(const nanochat_config* config, nanochat_params* out) {
   ncb::EngineConfig c;
   if (out == nullptr || !ToEngine(config, &c, "nanochat_params_get")) return NANOCHAT_STATUS_ERROR;
-  const int64_t L = c.num_layers, C = c.hidden_dim, V = c.padded_vocab_size;
-  int64_t value_layers = 0;
-  for (int i = 0; i < c.num_layers; ++i) value_layers += c.has_value_embedding(i) ? 1 : 0;
-  out->lm_head = V * C;
-  out->embeddings = V * C + value_layers * V * c.kv_dim();
-  out->transformer_matrices = L * (C * c.query_dim() + 2 * C * c.kv_dim() + C * C + 2 * C * c.mlp_dim()) +
-                              value_layers * c.num_kv_heads * 12;  // value gates read 12 channels
-  out->scalars = 2 * L + 24 + 2;  // residual / x0 lambdas, the smear gate (24 channels), smear and backout lambdas
-  out->total = out->lm_head + out->embeddings + out->transformer_matrices + out->scalars;
-  out->flops_per_token = ncb::EstimateFlopsPerToken(c);
+  const ncb::ParamCounts p = ncb::CountParams(c);
+  out->total = p.total, out->transformer_matrices = p.transformer_matrices, out->lm_head = p.lm_head;
+  out->embeddings = p.embeddings, out->scalars = p.scalars;
+  out->flops_per_token = ncb::FlopsPerToken(c);
   return NANOCHAT_STATUS_OK;
+}
+
+// The analytic roofline as `nanochat.roofline.v3` JSON (or the text table with `as_table`). Returns the length
+// needed (without the terminator); the text is truncated to `capacity - 1`. Negative on error.
+int64_t ncb_roofline(const nanochat_config* config, const char* device, const char* precision, int batch, int grad_accum,
+                     int world_size, int64_t total_tokens, double link_gbps, double latency_us, double overlap,
+                     int muon_ns_steps, double measured_bf16_tflops, double measured_hbm_gbs, int as_table, char* out,
+                     int64_t capacity) {
+  ncb::EngineConfig c;
+  if (!ToEngine(config, &c, "ncb_roofline")) return -1;
+  ncb::RooflinePlan plan;
+  plan.device = device != nullptr ? device : "b200";
+  plan.precision = precision != nullptr ? precision : "bf16";
+  plan.batch = batch, plan.grad_accum = grad_accum, plan.world_size = world_size, plan.total_tokens = total_tokens;
+  plan.link_gbps = link_gbps, plan.latency_us = latency_us, plan.overlap = overlap, plan.muon_ns_steps = muon_ns_steps;
+  plan.measured_bf16_tflops = measured_bf16_tflops, plan.measured_hbm_gbs = measured_hbm_gbs;
+  ncb::RooflineEstimate e;
+  std::string err;
+  if (!ncb::EstimatePerformance(c, plan, &e, &err)) {
+    ncb_set_error("ncb_roofline: " + err);
+    return -1;
+  }
+  const std::string text = as_table ? ncb::RooflineTable(e) : ncb::RooflineJson(e);
+  if (out != nullptr && capacity > 0) {
+    const std::size_t n = std::min<std::size_t>(text.size(), static_cast<std::size_t>(capacity - 1));
+    std::memcpy(out, text.data(), n);
+    out[n] = 0;
+  }
+  return static_cast<int64_t>(text.size());
+}
+double ncb_muon_flops_per_step(const nanochat_config* config, int ns_steps) {
+  ncb::EngineConfig c;
+  return ToEngine(config, &c, "ncb_muon_flops_per_step") ? ncb::MuonFlopsPerStep(c, ns_steps) : 0.0;
+}
+double ncb_prefill_flops(const nanochat_config* config, int prompt_tokens) {
+  ncb::EngineConfig c;
+  return ToEngine(config, &c, "ncb_prefill_flops") ? ncb::PrefillFlops(c, prompt_tokens) : 0.0;
+}
+double ncb_decode_flops_per_token(const nanochat_config* config, int context_tokens) {
+  ncb::EngineConfig c;
+  return ToEngine(config, &c, "ncb_decode_flops_per_token") ? ncb::DecodeFlopsPerToken(c, context_tokens) : 0.0;
 }
 
 // --- collectives over TCP for multi-process CPU jobs (the ports travel through the caller) ------------------

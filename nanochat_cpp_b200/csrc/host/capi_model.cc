@@ -75,6 +75,7 @@ nanochat_model* nanochat_model_create(const nanochat_config* config, uint64_t se
   }
   ncb::EngineConfig cfg;
   static_cast<ncb::ModelConfig&>(cfg) = ncb_to_model_config(*config);
+  cfg.short_window_override = ncb_short_window_override();
   std::string err;
   if (!cfg.Validate(&err)) {
     ncb_set_error("nanochat_model_create: " + err);

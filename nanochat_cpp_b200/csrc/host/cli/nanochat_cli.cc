@@ -1,6 +1,6 @@
 // nanochat_cli: a native command line over the C ABI (include/nanochat/capi.h) for hosts without Python or a GPU.
 // It runs the CPU engine: `train` (the in-process mesh driver), `generate`, `eval` (bits per byte), `tok_train`,
-// `params`. Flag names follow the Python entry point (`python -m nanochat_cpp_b200.cli`), which follows the
+// `params`, `roofline`. Flag names follow the Python entry point (`python -m nanochat_cpp_b200.cli`), which follows the
 // reference's `nanochat_cli` (src/train_command.cc:27-61, src/generate_command.cc:37-50, src/eval_command.cc:42-54).
 // The GPU path is driven from Python; this binary links only libnanochat_core.
 //
@@ -69,7 +69,7 @@ nanochat_config ModelFromArgs(const Args& a) {
   c.num_layers = 12, c.num_heads = 6, c.hidden_dim = 768, c.seq_len = 2048, c.vocab_size = 32768;
   const std::string preset = a.Str("preset-model");
   if (preset == "tiny") c.num_layers = 2, c.num_heads = 2, c.hidden_dim = 64, c.seq_len = 64, c.vocab_size = 512;
-  else if (preset == "d12") c.num_layers = 12, c.num_heads = 6, c.hidden_dim = 768, c.vocab_size = 65536;
+  else if (preset == "d12") c.num_layers = 12, c.num_heads = 6, c.hidden_dim = 768, c.vocab_size = 32768;
   else if (preset == "d20") c.num_layers = 20, c.num_heads = 10, c.hidden_dim = 1280, c.vocab_size = 65536;
   else if (preset == "d26") c.num_layers = 26, c.num_heads = 13, c.hidden_dim = 1664, c.vocab_size = 65536;
   if (a.Has("depth")) {
@@ -91,6 +91,9 @@ nanochat_config ModelFromArgs(const Args& a) {
   g_pattern = a.Str("window-pattern", "SSSL");
   c.window_pattern = g_pattern.c_str();
   c.value_embedding = a.Has("no-value-embedding") ? 0 : 1;
+  // the d12/d20/d26 presets are the benchmark shapes: 1024-token sliding window at seq 2048
+  const bool bench_shape = preset == "d12" || preset == "d20" || preset == "d26";
+  ncb_set_short_window(static_cast<int>(a.Int("short-window", bench_shape ? 1024 : 0)));
   return c;
 }
 
@@ -267,6 +270,21 @@ int CmdParams(const Args& a) {
   return 0;
 }
 
+int CmdRoofline(const Args& a) {
+  nanochat_config cfg = ModelFromArgs(a);
+  std::vector<char> text(1 << 16);
+  const int64_t n = ncb_roofline(&cfg, a.Str("device", "b200").c_str(), a.Str("precision", "bf16").c_str(),
+                                 static_cast<int>(a.Int("batch", 32)), static_cast<int>(a.Int("grad-accum", 1)),
+                                 static_cast<int>(a.Int("devices", 1)), a.Int("tokens", 0), a.Num("link-gbps", 0.0),
+                                 a.Num("latency-us", 5.0), a.Num("overlap", 0.0),
+                                 static_cast<int>(a.Int("muon-ns-steps", 5)), a.Num("bf16-tflops", 0.0),
+                                 a.Num("hbm-gbs", 0.0), a.Has("json") ? 0 : 1, text.data(),
+                                 static_cast<int64_t>(text.size()));
+  if (n < 0) return Fail("roofline");
+  std::printf("%s%s", text.data(), a.Has("json") ? "\n" : "");
+  return 0;
+}
+
 void Usage() {
   std::printf(
       "nanochat_cli <command> [--flag value ...]     (native CPU engine; the GPU path is `python -m nanochat_cpp_b200.cli`)\n"
@@ -278,8 +296,10 @@ void Usage() {
       "  eval       --model C --val-parquet P.. --tokenizer T --steps N --batch B\n"
       "  tok_train  --text F | --parquet P  --vocab V --out tokenizer.nctoken\n"
       "  params     model flags -> parameter counts and FLOPs per token (JSON)\n"
+      "  roofline   --device b200|h100|t4|cpu --precision bf16|fp8|fp32 --batch B --grad-accum A --devices N --tokens T\n"
+      "             --link-gbps G --latency-us U --overlap F --muon-ns-steps K [--bf16-tflops X --hbm-gbs Y] [--json]\n"
       "model flags: --preset-model tiny|d12|d20|d26 | --depth N | --layers --heads --kv-heads --hidden --seq --vocab\n"
-      "             --padded-vocab --rope-base --window-pattern --no-value-embedding\n");
+      "             --padded-vocab --rope-base --window-pattern --short-window --no-value-embedding\n");
 }
 
 }  // namespace
@@ -308,6 +328,7 @@ int main(int argc, char** argv) {
   if (cmd == "eval") return CmdEval(a);
   if (cmd == "tok_train") return CmdTokTrain(a);
   if (cmd == "params") return CmdParams(a);
+  if (cmd == "roofline") return CmdRoofline(a);
   std::fprintf(stderr, "nanochat_cli: unknown command '%s'\n", cmd.c_str());
   Usage();
   return 2;

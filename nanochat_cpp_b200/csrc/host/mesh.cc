@@ -1,5 +1,7 @@
 #include "mesh.h"
 
+#include "perf.h"
+
 #include <glob.h>
 #include <sys/stat.h>
 
@@ -129,18 +131,7 @@ bool MeshRuntime::LoadWeights(const std::string& path, std::string* error) {
 }
 
 // ------------------------------------------------------------------------------------------------ driver
-double EstimateFlopsPerToken(const EngineConfig& cfg) {
-  const double C = cfg.hidden_dim;
-  const double per_layer = C * cfg.query_dim() + 2.0 * C * cfg.kv_dim() + cfg.query_dim() * C + 2.0 * C * cfg.mlp_dim();
-  double matmul = cfg.num_layers * per_layer + static_cast<double>(cfg.padded_vocab_size) * C;
-  double attn = 0.0;
-  for (int i = 0; i < cfg.num_layers; ++i) {
-    const int w = cfg.window_left(i);
-    const double visible = w < 0 ? cfg.seq_len : std::min(cfg.seq_len, w + 1);
-    attn += 12.0 * cfg.num_heads * cfg.head_dim() * visible;
-  }
-  return 6.0 * matmul + attn;
-}
+double EstimateFlopsPerToken(const EngineConfig& cfg) { return FlopsPerToken(cfg); }
 
 namespace {
 

@@ -69,3 +69,26 @@ def test_train_resume_generate(cli, tmp_path):
     assert list(rows[0][0]) == ids
     r = run(cli, "train", "--preset-model", "tiny", "--rows", str(tmp_path / "missing"), "--out-dir", out)
     assert r.returncode == 1 and "nanochat_cli" in r.stderr
+
+
+def test_native_roofline_matches_python_model(cli):
+    """The native performance model and the Python one are the same arithmetic: row by row agreement."""
+    from nanochat_cpp_b200.config import preset
+    from nanochat_cpp_b200.perf import roofline as rf
+    from nanochat_cpp_b200.train import mfu
+    peaks = mfu.measured_peaks()
+    for device, world in (("b200", 8), ("h100", 1)):
+        r = run(cli, "roofline", "--preset-model", "d20", "--device", device, "--devices", str(world), "--batch", "32",
+                "--bf16-tflops", repr(peaks["bf16_tflops_sustained"]), "--hbm-gbs", repr(peaks["hbm_gbs"]), "--json")
+        assert r.returncode == 0, r.stderr
+        native = json.loads(r.stdout)
+        assert native["schema"] == "nanochat.roofline.v3"
+        want = json.loads(rf.report_json(rf.estimate(preset("d20"), rf.RooflinePlan(device=device, world_size=world))))
+        assert [x["name"] + x["phase"] for x in native["rows"]] == [x["name"] + x["phase"] for x in want["rows"]]
+        for a, b in zip(native["rows"], want["rows"]):
+            for k in ("flops", "bytes", "bound_seconds", "mfu"):
+                assert abs(a[k] - b[k]) <= 1e-9 * max(1.0, abs(b[k])), (a["name"], k)
+            assert a["limit"] == b["limit"]
+        for k in ("step_seconds", "tokens_per_second", "model_mfu", "sync_seconds", "optimizer_flops"):
+            assert abs(native[k] - want[k]) <= 1e-9 * max(1.0, abs(want[k])), k
+    assert "step bound" in run(cli, "roofline", "--preset-model", "d12").stdout
