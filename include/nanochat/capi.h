@@ -311,6 +311,11 @@ double ncb_muon_flops_per_step(const nanochat_config* config, int ns_steps);
 double ncb_prefill_flops(const nanochat_config* config, int prompt_tokens);
 double ncb_decode_flops_per_token(const nanochat_config* config, int context_tokens);
 
+/* One rank of a multi-process CPU data-parallel job (TCP ring over 127.0.0.1, rendezvous on `port`): the same
+ * config as the mesh driver, `run.batch` is the per-rank micro-batch, `mesh` is ignored. Rank 0 writes the artifacts. */
+float ncb_dist_train_run(const nanochat_mesh_train_config* config, int rank, int world, int port, int timeout_ms,
+                         nanochat_mesh_train_summary* out);
+
 /* ---- host collectives (TCP over 127.0.0.1 between CPU ranks; an in-process ring for tests) */
 typedef struct ncb_tcp ncb_tcp;
 ncb_tcp* ncb_tcp_create(int rank, int world);

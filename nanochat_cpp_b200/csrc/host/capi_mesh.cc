@@ -180,7 +180,23 @@ void ncb_runtime_inject_drop(nanochat_runtime* runtime, int from, int timeout_ms
   runtime->rt->InjectDrop(from);
 }
 
+static float RunTrain(const nanochat_mesh_train_config* c, nanochat_mesh_train_summary* out, const ncb::DistConfig* dist);
+
 float nanochat_mesh_train_run(const nanochat_mesh_train_config* c, nanochat_mesh_train_summary* out) {
+  return RunTrain(c, out, nullptr);
+}
+
+// One rank of a multi-process CPU data-parallel job: `config->run.batch` is the per-rank micro-batch, the mesh
+// field is ignored, ranks meet on 127.0.0.1:`port`; rank 0 writes the checkpoint, metrics.jsonl and summary.json.
+float ncb_dist_train_run(const nanochat_mesh_train_config* c, int rank, int world, int port, int timeout_ms,
+                         nanochat_mesh_train_summary* out) {
+  ncb::DistConfig d;
+  d.rank = rank, d.world = world, d.port = port;
+  if (timeout_ms > 0) d.timeout_ms = timeout_ms;
+  return RunTrain(c, out, &d);
+}
+
+static float RunTrain(const nanochat_mesh_train_config* c, nanochat_mesh_train_summary* out, const ncb::DistConfig* dist) {
   if (c == nullptr) {
     ncb_set_error("nanochat_mesh_train_run: config is null");
     return 0.0f;
@@ -211,7 +227,7 @@ float nanochat_mesh_train_run(const nanochat_mesh_train_config* c, nanochat_mesh
   std::string err;
   float last = 0.0f;
   Try("nanochat_mesh_train_run", [&] {
-    last = ncb::RunMeshTrain(cfg, &s, &err);
+    last = dist != nullptr ? ncb::RunDistributedTrain(cfg, *dist, &s, &err) : ncb::RunMeshTrain(cfg, &s, &err);
     return true;
   });
   if (!err.empty()) ncb_set_error("nanochat_mesh_train_run: " + err);

@@ -10,9 +10,13 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <csignal>
 #include <map>
 #include <string>
 #include <vector>
+
+#include <sys/wait.h>
+#include <unistd.h>
 
 #include "nanochat/capi.h"
 
@@ -126,7 +130,7 @@ int CmdTrain(const Args& a) {
   nanochat_optim_config optim;
   if (!OptimFromArgs(a, &optim)) return Fail("train");
   c.optimizer = &optim;
-  nanochat_mesh* mesh = nanochat_mesh_create(nullptr, static_cast<int>(a.Int("world-size", 1)));
+  nanochat_mesh* mesh = nanochat_mesh_create(nullptr, static_cast<int>(a.Int("mesh", 1)));
   c.mesh = mesh;
   std::vector<const char*> parquet;
   for (const std::string& p : a.All("train-parquet")) parquet.push_back(p.c_str());
@@ -149,8 +153,18 @@ int CmdTrain(const Args& a) {
   c.output.out_dir = out_dir.c_str();
   c.output.checkpoint_path = ckpt.c_str();
   nanochat_mesh_train_summary s{};
-  const float last = nanochat_mesh_train_run(&c, &s);
+  // multi-process data parallelism: flags or the launcher's environment (NANOCHAT_RANK / _WORLD_SIZE / _MASTER_PORT)
+  auto env_int = [](const char* name, long long d) {
+    const char* v = std::getenv(name);
+    return v != nullptr && *v ? std::atoll(v) : d;
+  };
+  const int world = static_cast<int>(a.Int("world-size", env_int("NANOCHAT_WORLD_SIZE", 1)));
+  const int rank = static_cast<int>(a.Int("rank", env_int("NANOCHAT_RANK", 0)));
+  const int port = static_cast<int>(a.Int("port", env_int("NANOCHAT_MASTER_PORT", 29500)));
+  const float last = world > 1 ? ncb_dist_train_run(&c, rank, world, port, static_cast<int>(a.Int("timeout-ms", 0)), &s)
+                               : nanochat_mesh_train_run(&c, &s);
   nanochat_mesh_free(mesh);
+  if (world > 1 && rank != 0) return (s.steps == 0 && last == 0.0f) ? Fail("train") : 0;
   if (s.steps == 0 && last == 0.0f) return Fail("train");
   std::printf("[nanochat] %d steps%s, mean loss %.6f, last loss %.6f, checkpoint %s\n", s.steps,
               s.interrupted ? " (interrupted)" : "", s.mean_loss, last, s.checkpoint);
@@ -285,16 +299,69 @@ int CmdRoofline(const Args& a) {
   return 0;
 }
 
+// `dist --world-size N [--port P] -- <command> [flags]`: one child process per rank with NANOCHAT_RANK,
+// NANOCHAT_WORLD_SIZE, NANOCHAT_MASTER_ADDR and NANOCHAT_MASTER_PORT set (the reference launcher's contract,
+// python/nanochat_cpp/cli.py:827-945), rank 0 first. If a rank fails the others are terminated.
+int CmdDist(int argc, char** argv) {
+  int split = -1;
+  for (int i = 2; i < argc; ++i)
+    if (std::strcmp(argv[i], "--") == 0) {
+      split = i;
+      break;
+    }
+  if (split < 0 || split + 1 >= argc) {
+    std::fprintf(stderr, "nanochat_cli dist: usage: dist --world-size N [--port P] -- <command> [flags]\n");
+    return 2;
+  }
+  const Args a = Parse(split, argv, 2);
+  const int world = static_cast<int>(a.Int("world-size", 2));
+  const std::string port = a.Str("port", "29500");
+  std::vector<pid_t> kids;
+  for (int r = 0; r < world; ++r) {
+    const pid_t pid = ::fork();
+    if (pid == 0) {
+      ::setenv("NANOCHAT_RANK", std::to_string(r).c_str(), 1);
+      ::setenv("NANOCHAT_WORLD_SIZE", std::to_string(world).c_str(), 1);
+      ::setenv("NANOCHAT_MASTER_ADDR", "127.0.0.1", 1);
+      ::setenv("NANOCHAT_MASTER_PORT", port.c_str(), 1);
+      std::vector<char*> child = {argv[0]};
+      for (int i = split + 1; i < argc; ++i) child.push_back(argv[i]);
+      child.push_back(nullptr);
+      ::execv("/proc/self/exe", child.data());
+      std::perror("nanochat_cli dist: exec");
+      ::_exit(127);
+    }
+    if (pid < 0) return Fail("dist: fork");
+    kids.push_back(pid);
+    if (r == 0) ::usleep(200000);  // rank 0 opens the rendezvous port first
+  }
+  int worst = 0;
+  for (std::size_t left = kids.size(); left > 0; --left) {
+    int status = 0;
+    const pid_t done = ::wait(&status);
+    if (done < 0) break;
+    const int rc = WIFEXITED(status) ? WEXITSTATUS(status) : 128 + WTERMSIG(status);
+    if (rc != 0 && worst == 0) {
+      worst = rc;
+      for (pid_t k : kids)
+        if (k != done) ::kill(k, SIGTERM);  // exact PIDs of the children this launcher started
+    }
+  }
+  return worst;
+}
+
 void Usage() {
   std::printf(
       "nanochat_cli <command> [--flag value ...]     (native CPU engine; the GPU path is `python -m nanochat_cpp_b200.cli`)\n"
-      "  train      --train-parquet P.. --tokenizer T | --rows shard.nchsft   [--world-size N --batch B --grad-accum A\n"
+      "  train      --train-parquet P.. --tokenizer T | --rows shard.nchsft   [--mesh N (replicas in this process) | --rank R\n"
+      "             --world-size W --port P (one process per rank; or `dist`)] [--batch B --grad-accum A\n"
       "             --num-iterations K --log-every L --save-every S --out-dir D --checkpoint C --resume --warm-start W\n"
       "             --preset track3 + optimizer / schedule / model flags]\n"
       "  generate   --model C [--tokenizer T --prompt TEXT | --tokens a,b,c] --max-tokens N --num-samples S\n"
       "             --temperature X --top-k K --seed Z --stop-id I\n"
       "  eval       --model C --val-parquet P.. --tokenizer T --steps N --batch B\n"
       "  tok_train  --text F | --parquet P  --vocab V --out tokenizer.nctoken\n"
+      "  dist       --world-size N [--port P] -- train ...      one process per rank over the TCP ring\n"
       "  params     model flags -> parameter counts and FLOPs per token (JSON)\n"
       "  roofline   --device b200|h100|t4|cpu --precision bf16|fp8|fp32 --batch B --grad-accum A --devices N --tokens T\n"
       "             --link-gbps G --latency-us U --overlap F --muon-ns-steps K [--bf16-tflops X --hbm-gbs Y] [--json]\n"
@@ -321,6 +388,7 @@ int main(int argc, char** argv) {
                 sandbox != nullptr && *sandbox ? sandbox : "none");
     return 0;
   }
+  if (cmd == "dist") return CmdDist(argc, argv);
   if (nanochat_init() != NANOCHAT_STATUS_OK) return Fail("init");
   const Args a = Parse(argc, argv, 2);
   if (cmd == "train") return CmdTrain(a);

@@ -245,6 +245,77 @@ bool TcpTransport::Recv(int from, void* data, std::size_t bytes, int timeout_ms)
   return true;
 }
 
+// ------------------------------------------------------------------------------------------ rendezvous
+bool RendezvousAndConnect(TcpTransport* t, int master_port, int timeout_ms) {
+  const int world = t->world(), rank = t->rank();
+  std::vector<int> ports(world, 0);
+  ports[rank] = t->port();
+  if (world == 1) return t->Connect(ports, timeout_ms);
+  sockaddr_in addr{};
+  addr.sin_family = AF_INET;
+  addr.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+  addr.sin_port = htons(static_cast<std::uint16_t>(master_port));
+  if (rank == 0) {
+    const int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+    int one = 1;
+    ::setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+    if (fd < 0 || ::bind(fd, reinterpret_cast<sockaddr*>(&addr), sizeof(addr)) != 0 || ::listen(fd, world) != 0) {
+      t->set_error("rendezvous: cannot listen on 127.0.0.1:" + std::to_string(master_port));
+      if (fd >= 0) ::close(fd);
+      return false;
+    }
+    std::vector<int> peers;
+    bool ok = true;
+    for (int k = 1; k < world && ok; ++k) {
+      pollfd pf{fd, POLLIN, 0};
+      if (::poll(&pf, 1, timeout_ms) <= 0) {
+        t->set_error("rendezvous: " + std::to_string(world - k) + " rank(s) did not join");
+        ok = false;
+        break;
+      }
+      const int c = ::accept(fd, nullptr, nullptr);
+      std::uint32_t hello[2] = {0, 0};
+      if (c < 0 || !ReadAll(c, hello, sizeof(hello), timeout_ms) || hello[0] == 0 || hello[0] >= static_cast<std::uint32_t>(world) ||
+          ports[hello[0]] != 0) {
+        t->set_error("rendezvous: bad hello");
+        if (c >= 0) ::close(c);
+        ok = false;
+        break;
+      }
+      ports[hello[0]] = static_cast<int>(hello[1]);
+      peers.push_back(c);
+    }
+    std::vector<std::uint32_t> table(ports.begin(), ports.end());
+    for (int c : peers) {
+      if (ok) ok = WriteAll(c, table.data(), table.size() * 4);
+      ::close(c);
+    }
+    ::close(fd);
+    if (!ok) return false;
+  } else {
+    const int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    bool connected = false;
+    while (std::chrono::steady_clock::now() < deadline) {
+      if (::connect(fd, reinterpret_cast<sockaddr*>(&addr), sizeof(addr)) == 0) {
+        connected = true;
+        break;
+      }
+      std::this_thread::sleep_for(std::chrono::milliseconds(50));
+    }
+    const std::uint32_t hello[2] = {static_cast<std::uint32_t>(rank), static_cast<std::uint32_t>(t->port())};
+    std::vector<std::uint32_t> table(world);
+    const bool ok = connected && WriteAll(fd, hello, sizeof(hello)) && ReadAll(fd, table.data(), table.size() * 4, timeout_ms);
+    ::close(fd);
+    if (!ok) {
+      t->set_error("rendezvous: rank 0 did not answer on 127.0.0.1:" + std::to_string(master_port));
+      return false;
+    }
+    for (int r = 0; r < world; ++r) ports[r] = static_cast<int>(table[r]);
+  }
+  return t->Connect(ports, timeout_ms);
+}
+
 // ------------------------------------------------------------------------------------------ collectives
 bool RingAllReduceSum(Transport* t, float* data, std::size_t count, int timeout_ms) {
   const int n = t->world(), r = t->rank();

@@ -71,6 +71,7 @@ class TcpTransport : public Transport {
   int world() const override { return world_; }
   bool Send(int to, const void* data, std::size_t bytes) override;
   bool Recv(int from, void* data, std::size_t bytes, int timeout_ms) override;
+  void set_error(const std::string& e) { error_ = e; }
 
  private:
   struct Out {
@@ -86,6 +87,12 @@ class TcpTransport : public Transport {
   std::atomic<bool> stop_{false}, failed_{false};
   std::thread sender_;
 };
+
+// Control-plane rendezvous of a multi-process job on one host: rank 0 listens on `master_port`, every other rank
+// reports the ephemeral port of its transport, rank 0 answers with the whole table, and all ranks connect
+// (the reference exchanges its ring ports the same way through `Rendezvous::ExchangeBytes`, src/rendezvous.cc:145).
+// Returns false with `t->error()` set when a rank does not show up within `timeout_ms`.
+bool RendezvousAndConnect(TcpTransport* t, int master_port, int timeout_ms);
 
 // Sum all-reduce of `count` floats in place: reduce-scatter then all-gather around the ring, chunk =
 // ceil(count / world), the last chunks may be short or empty. Every rank ends with bit-identical data (each

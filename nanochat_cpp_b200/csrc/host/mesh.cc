@@ -153,8 +153,10 @@ std::vector<std::string> ExpandGlobs(const std::vector<std::string>& patterns) {
 // Batches of the run: either the document loader over parquet text, or rows of a packed shard in file order.
 class BatchSource {
  public:
-  bool Open(const MeshTrainConfig& c, int seq, std::string* error) {
-    batch_ = c.batch, seq_ = seq;
+  // `rows`: sequences this process consumes per step; with `world` > 1 the documents (parquet) are dealt to the
+  // ranks round-robin and packed rows are dealt in blocks of `rows` per rank inside each global step.
+  bool Open(const MeshTrainConfig& c, int seq, int rows, int rank, int world, std::string* error) {
+    batch_ = rows, seq_ = seq, rank_ = rank, world_ = world;
     if (!c.packed_rows_path.empty()) {
       std::string magic;
       std::vector<FixtureRecord> recs;
@@ -187,7 +189,9 @@ class BatchSource {
       if (error) *error = "no documents: check the parquet paths";
       return false;
     }
-    loader_ = std::make_unique<DataLoader>(VectorSource(std::move(docs)), c.batch, seq, 1000, 2, 1);
+    std::unique_ptr<DocumentSource> src = VectorSource(std::move(docs));
+    if (world > 1) src = ShardSource(std::move(src), rank, world);
+    loader_ = std::make_unique<DataLoader>(std::move(src), rows, seq, 1000, 2, 1);
     return true;
   }
   void Next(int* tokens, int* targets) {
@@ -195,22 +199,24 @@ class BatchSource {
       loader_->Next(tokens, targets);
       return;
     }
-    for (int b = 0; b < batch_; ++b, cursor_ = (cursor_ + 1) % rows_) {
-      std::memcpy(tokens + static_cast<std::size_t>(b) * seq_, tokens_.data() + cursor_ * seq_, seq_ * 4);
-      std::memcpy(targets + static_cast<std::size_t>(b) * seq_, targets_.data() + cursor_ * seq_, seq_ * 4);
+    for (int b = 0; b < batch_; ++b) {
+      const std::size_t row = (cursor_ + static_cast<std::size_t>(rank_) * batch_ + b) % rows_;
+      std::memcpy(tokens + static_cast<std::size_t>(b) * seq_, tokens_.data() + row * seq_, seq_ * 4);
+      std::memcpy(targets + static_cast<std::size_t>(b) * seq_, targets_.data() + row * seq_, seq_ * 4);
     }
+    cursor_ = (cursor_ + static_cast<std::size_t>(world_) * batch_) % rows_;
   }
   void Skip(int steps) {  // a resume replays the loader to the stored step
     if (loader_) {
       std::vector<int> a(static_cast<std::size_t>(batch_) * seq_), b(a.size());
       for (int i = 0; i < steps; ++i) loader_->Next(a.data(), b.data());
     } else if (rows_) {
-      cursor_ = (static_cast<std::size_t>(steps) * batch_) % rows_;
+      cursor_ = (static_cast<std::size_t>(steps) * batch_ * world_) % rows_;
     }
   }
 
  private:
-  int batch_ = 0, seq_ = 0;
+  int batch_ = 0, seq_ = 0, rank_ = 0, world_ = 1;
   std::unique_ptr<Tokenizer> tokenizer_;
   std::unique_ptr<DataLoader> loader_;
   std::vector<int> tokens_, targets_;
@@ -235,7 +241,7 @@ float RunMeshTrain(const MeshTrainConfig& c, MeshTrainSummary* out, std::string*
   if (!rt.ok()) return 0.0f;
   if (!c.warm_start_path.empty() && !rt.LoadWeights(c.warm_start_path, error)) return 0.0f;
   BatchSource data;
-  if (!data.Open(c, seq, error)) return 0.0f;
+  if (!data.Open(c, seq, c.batch, 0, 1, error)) return 0.0f;
   if (c.resume && FileExists(ckpt)) {
     if (!rt.Load(ckpt, error)) return 0.0f;
     data.Skip(rt.step());
@@ -298,6 +304,118 @@ float RunMeshTrain(const MeshTrainConfig& c, MeshTrainSummary* out, std::string*
                  s.steps, rt.step(), s.interrupted ? "true" : "false", s.mean_loss, last, s.steady_mfu, rt.world(),
                  tokens_per_step, ckpt.c_str());
     std::fclose(f);
+  }
+  if (out) *out = s;
+  return last;
+}
+
+float RunDistributedTrain(const MeshTrainConfig& c, const DistConfig& d, MeshTrainSummary* out, std::string* error) {
+  const int seq = c.seq > 0 ? c.seq : c.model.seq_len;
+  const int world = std::max(1, d.world), accum = std::max(1, c.grad_accum);
+  if (d.rank < 0 || d.rank >= world || c.batch <= 0 || seq > c.model.seq_len) {
+    if (error) *error = "bad rank, batch or sequence length";
+    return 0.0f;
+  }
+  const bool writer = d.rank == 0;
+  std::string out_dir = c.out_dir.empty() ? "." : c.out_dir;
+  if (writer) ::mkdir(out_dir.c_str(), 0755);
+  const std::string ckpt = c.checkpoint_path.empty() ? out_dir + "/checkpoint.ckpt" : c.checkpoint_path;
+  TcpTransport link(d.rank, world);
+  if (!RendezvousAndConnect(&link, d.port, d.timeout_ms)) {
+    if (error) *error = link.error();
+    return 0.0f;
+  }
+  OptimConfig optim = c.optim;
+  if (optim.num_iterations == 0) optim.num_iterations = c.num_iterations;
+  CpuModel model(c.model);
+  model.InitWeights(c.seed);
+  CpuOptimizer opt(&model, optim);
+  if (!c.warm_start_path.empty() && !model.Load(c.warm_start_path, error)) return 0.0f;
+  BatchSource data;
+  if (!data.Open(c, seq, c.batch * accum, d.rank, world, error)) return 0.0f;
+  int step0 = 0;
+  if (c.resume && FileExists(ckpt)) {  // every rank reads the one canonical file
+    std::uint64_t st = 0;
+    if (!model.LoadWithOptimizer(ckpt, &opt, &st, error)) return 0.0f;
+    step0 = static_cast<int>(st);
+    data.Skip(step0);
+  }
+  std::FILE* metrics = writer ? std::fopen((out_dir + "/metrics.jsonl").c_str(), c.resume ? "a" : "w") : nullptr;
+  const double fpt = c.flops_per_token > 0 ? c.flops_per_token : EstimateFlopsPerToken(c.model);
+  const double tokens_per_step = static_cast<double>(c.batch) * accum * world * seq;
+  const float scale = 1.0f / static_cast<float>(accum * world);
+  g_interrupted = 0;
+  auto previous = std::signal(SIGINT, OnSigint);
+  std::vector<int> tokens(static_cast<std::size_t>(c.batch) * accum * seq), targets(tokens.size());
+  double loss_sum = 0.0, mfu_sum = 0.0;
+  int steps = 0, mfu_steps = 0, step = step0;
+  float last = 0.0f;
+  bool failed = false;
+  while (step < c.num_iterations && !failed) {
+    const auto t0 = std::chrono::steady_clock::now();
+    data.Next(tokens.data(), targets.data());
+    model.ZeroGrad();
+    double loss = 0.0;
+    for (int m = 0; m < accum; ++m) {
+      const std::size_t off = static_cast<std::size_t>(m) * c.batch * seq;
+      loss += model.ForwardLoss(tokens.data() + off, targets.data() + off, c.batch, seq);
+      model.Backward(scale);
+    }
+    // the loss and the stop request travel with the gradients: two extra floats at the end of the reduced vector
+    std::vector<float>& g = model.grads();
+    const std::size_t n = g.size();
+    g.push_back(static_cast<float>(loss / accum));
+    g.push_back(g_interrupted ? 1.0f : 0.0f);
+    const bool reduced = RingAllReduceSum(&link, g.data(), g.size(), d.timeout_ms);
+    const float mean_loss = g[n] / world;
+    const bool stop = g[n + 1] > 0.0f;
+    g.resize(n);
+    if (!reduced) {
+      if (error) *error = "watchdog: rank " + std::to_string(d.rank) + ": " + link.error();
+      failed = true;
+      break;
+    }
+    ++step;
+    opt.Step(step);
+    last = mean_loss;
+    const float secs = std::chrono::duration<float>(std::chrono::steady_clock::now() - t0).count();
+    const double tok_s = tokens_per_step / std::max(1e-9f, secs);
+    const double mfu = c.peak_flops > 0 ? tok_s * fpt / (c.peak_flops * world) : 0.0;
+    ++steps;
+    loss_sum += last;
+    if (steps > 1) mfu_sum += mfu, ++mfu_steps;
+    if (metrics) {
+      std::fprintf(metrics, "{\"step\": %d, \"loss\": %.6f, \"grad_norm\": %.6f, \"step_seconds\": %.6f, \"tok_s\": %.1f, \"mfu\": %.6f}\n",
+                   step, last, opt.grad_norm(), secs, tok_s, mfu);
+      std::fflush(metrics);
+    }
+    if (writer && (steps == 1 || step == c.num_iterations || (c.log_every > 0 && step % c.log_every == 0)))
+      std::printf("step %6d | loss %.6f | grad_norm %.4f | tok/s %.0f | mfu %.4f | step_ms %.2f\n", step, last,
+                  opt.grad_norm(), tok_s, mfu, secs * 1e3);
+    if (stop) break;  // every rank saw the same flag, so all leave after the same step
+    if (writer && c.save_every > 0 && step % c.save_every == 0 && step != c.num_iterations &&
+        !model.SaveWithOptimizer(ckpt, opt, static_cast<std::uint64_t>(step), static_cast<std::uint32_t>(world), error))
+      failed = true;
+  }
+  std::signal(SIGINT, previous);
+  if (metrics) std::fclose(metrics);
+  if (failed) return 0.0f;
+  if (writer && !model.SaveWithOptimizer(ckpt, opt, static_cast<std::uint64_t>(step), static_cast<std::uint32_t>(world), error))
+    return 0.0f;
+  MeshTrainSummary s;
+  s.steps = steps;
+  s.interrupted = step < c.num_iterations;
+  s.mean_loss = steps ? loss_sum / steps : 0.0;
+  s.steady_mfu = mfu_steps ? mfu_sum / mfu_steps : 0.0;
+  s.checkpoint = ckpt;
+  if (writer) {
+    if (std::FILE* f = std::fopen((out_dir + "/summary.json").c_str(), "w")) {
+      std::fprintf(f, "{\"steps\": %d, \"final_step\": %d, \"interrupted\": %s, \"mean_loss\": %.6f, \"final_loss\": %.6f, "
+                      "\"steady_mfu\": %.6f, \"world_size\": %d, \"tokens_per_step\": %.0f, \"checkpoint\": \"%s\"}\n",
+                   s.steps, step, s.interrupted ? "true" : "false", s.mean_loss, last, s.steady_mfu, world,
+                   tokens_per_step, ckpt.c_str());
+      std::fclose(f);
+    }
   }
   if (out) *out = s;
   return last;

@@ -94,6 +94,16 @@ struct MeshTrainSummary {
 // resume; stops cleanly (with a checkpoint) on SIGINT. Returns the last loss, 0 on error.
 float RunMeshTrain(const MeshTrainConfig& config, MeshTrainSummary* out, std::string* error);
 
+// One rank of a multi-process data-parallel CPU job (the reference's `nanochat_cli train --rank R --world-size W`,
+// src/train.cc:628-724: backward scaled by 1 / (grad_accum * world), gradients summed over the ranks, every rank
+// takes the same optimizer step; rank 0 writes the checkpoint and the metrics). `config.batch` is the per-rank
+// micro-batch here. Ranks meet through `RendezvousAndConnect` on 127.0.0.1:`port` and reduce with the TCP ring.
+struct DistConfig {
+  int rank = 0, world = 1, port = 29500, timeout_ms = 600000;
+};
+float RunDistributedTrain(const MeshTrainConfig& config, const DistConfig& dist, MeshTrainSummary* out,
+                          std::string* error);
+
 // 6 * matmul parameters + 12 * layers * heads * head_dim * mean visible keys (the usual estimate).
 double EstimateFlopsPerToken(const EngineConfig& cfg);
 

@@ -47,7 +47,7 @@ def test_train_resume_generate(cli, tmp_path):
     shard = str(tmp_path / "rows.nchsft")
     save_sft_shard(shard, SftShard(tok[:, :-1].copy(), tok[:, 1:].copy()))
     out = str(tmp_path / "run")
-    common = ["--preset-model", "tiny", "--rows", shard, "--batch", "4", "--world-size", "2", "--out-dir", out]
+    common = ["--preset-model", "tiny", "--rows", shard, "--batch", "4", "--mesh", "2", "--out-dir", out]
     r = run(cli, "train", *common, "--num-iterations", "2")
     assert r.returncode == 0, r.stderr
     assert "2 steps" in r.stdout
@@ -92,3 +92,31 @@ def test_native_roofline_matches_python_model(cli):
         for k in ("step_seconds", "tokens_per_second", "model_mfu", "sync_seconds", "optimizer_flops"):
             assert abs(native[k] - want[k]) <= 1e-9 * max(1.0, abs(want[k])), k
     assert "step bound" in run(cli, "roofline", "--preset-model", "d12").stdout
+
+
+def test_dist_launcher_matches_the_in_process_mesh(cli, tmp_path):
+    """Two processes over the TCP ring end with the same weights as two mesh replicas inside one process."""
+    rng = np.random.default_rng(1)
+    tok = rng.integers(0, 512, size=(16, 65), dtype=np.int32)
+    shard = str(tmp_path / "rows.nchsft")
+    save_sft_shard(shard, SftShard(tok[:, :-1].copy(), tok[:, 1:].copy()))
+    common = ["--preset-model", "tiny", "--rows", shard, "--num-iterations", "3", "--log-every", "1"]
+    out_d, out_m = str(tmp_path / "dist"), str(tmp_path / "mesh")
+    port = str(20000 + os.getpid() % 20000)
+    r = run(cli, "dist", "--world-size", "2", "--port", port, "--", "train", *common, "--batch", "2", "--out-dir", out_d)
+    assert r.returncode == 0, (r.stdout, r.stderr)
+    assert r.stdout.count("step      3 |") == 1          # only rank 0 logs
+    r = run(cli, "train", *common, "--batch", "4", "--mesh", "2", "--out-dir", out_m)
+    assert r.returncode == 0, r.stderr
+    cfg = Config(num_layers=2, num_heads=2, num_kv_heads=2, hidden_dim=64, seq_len=64, vocab_size=512,
+                 padded_vocab_size=512)
+    a, b = CpuModel(cfg, seed=0), CpuModel(cfg, seed=1)
+    a.load(os.path.join(out_d, "checkpoint.ckpt"))
+    b.load(os.path.join(out_m, "checkpoint.ckpt"))
+    for name in a.names():
+        assert np.array_equal(a.read(name), b.read(name)), name
+    assert json.load(open(os.path.join(out_d, "summary.json")))["world_size"] == 2
+    # a rank that never joins: the launcher reports the failure instead of hanging
+    r = run(cli, "train", *common, "--batch", "2", "--rank", "1", "--world-size", "2", "--port", port, "--timeout-ms",
+            "500", "--out-dir", out_d)
+    assert r.returncode == 1 and "rendezvous" in r.stderr
