@@ -54,6 +54,12 @@ class GPT:
         self.on_head_grads_ready: Optional[Callable[[], None]] = None
         self.on_embed_grads_ready: Optional[Callable[[], None]] = None
         self.phase_event = None  # a CUDA event recorded between the forward trunk and the head / backward
+        # Weight-gradient products are off the critical path of the backward (nothing in the backward reads them),
+        # so they run on a second stream: a persistent GEMM CTA per SM leaves most thread slots free, and the
+        # memory-bound row kernels of the critical path run beside it instead of after it.
+        import os as _os2
+        self._wgrad_stream = (torch.cuda.Stream(self.device) if self.device.type == "cuda" and
+                              _os2.environ.get("NANOCHAT_WGRAD_STREAM", "0") == "1" else None)
         self.fp8 = bool(fp8) and self.device.type == "cuda"
         # bitwise-reproducible embedding gradients (sorted, single-writer sums instead of atomics)
         import os as _os
@@ -61,6 +67,27 @@ class GPT:
         self._fp8_w: Dict[str, object] = {}
         if self.fp8:
             self.refresh_fp8()
+
+    def _off_path(self, fn, *inputs) -> None:
+        """Runs `fn` (a weight-gradient product reading `inputs`) on the side stream, after everything issued so far."""
+        side = self._wgrad_stream
+        if side is None:
+            fn()
+            return
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            fn()
+        for t in inputs:
+            t.record_stream(side)  # the allocator must not hand the block out again before the side stream is done
+
+    def _join_side(self, event=None) -> None:
+        """The current stream waits for the side stream (or for `event` recorded on it)."""
+        if self._wgrad_stream is not None:
+            cur = torch.cuda.current_stream(self.device)
+            if event is not None:
+                cur.wait_event(event)
+            else:
+                cur.wait_stream(self._wgrad_stream)
 
     def refresh_fp8(self) -> None:
         """Re-quantize the fp8 weight copies from the bf16 compute copy (after an optimizer step)."""
@@ -264,23 +291,24 @@ class GPT:
         dx0 = None
         cos, sin = save["cos"], save["sin"]
         H, KV, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        pending = None
         for i in reversed(range(cfg.num_layers)):
             s = save["layers"][i]
             if i == cfg.backout_layer:
                 dx = ops.add(dx, dxb)
                 dxb = None
             # MLP
-            ops.linear_wgrad_relu2(dx, s["pre"], self._g(i, "mlp.c_proj"))
+            self._off_path(lambda: ops.linear_wgrad_relu2(dx, s["pre"], self._g(i, "mlp.c_proj")), dx, s["pre"])
             dpre = ops.linear_dgrad_relu2(dx, self._w(i, "mlp.c_proj"), s["pre"])
             h2 = ops.rmsnorm_apply(s["x_mid"], s["rstd2"])
-            ops.linear_wgrad(dpre, h2, self._g(i, "mlp.c_fc"))
+            self._off_path(lambda: ops.linear_wgrad(dpre, h2, self._g(i, "mlp.c_fc")), dpre, h2)
             dh2 = ops.linear_dgrad(dpre, self._w(i, "mlp.c_fc"))
             del dpre, h2
             dx_mid = ops.rmsnorm_bwd(s["x_mid"], dh2, s["rstd2"], residual=dx)
             del dh2
             # attention output projection
             attn2 = s["attn"].view(M, H * D)
-            ops.linear_wgrad(dx_mid, attn2, self._g(i, "attn.c_proj"))
+            self._off_path(lambda: ops.linear_wgrad(dx_mid, attn2, self._g(i, "attn.c_proj")), dx_mid, attn2)
             dattn = ops.linear_dgrad(dx_mid, self._w(i, "attn.c_proj"))
             qd, kd = cfg.query_dim, cfg.kv_dim
             dqkv = torch.empty(M, qd + 2 * kd, dtype=dx_mid.dtype, device=dx_mid.device)
@@ -304,12 +332,14 @@ class GPT:
             gqkv = P.qkv_view(i, "g")
             wqkv = P.qkv_view(i)
             if gqkv is not None:
-                ops.linear_wgrad(dqkv, h, gqkv)
+                self._off_path(lambda: ops.linear_wgrad(dqkv, h, gqkv), dqkv, h)
                 dh = ops.linear_dgrad(dqkv, wqkv)
             else:
-                ops.linear_wgrad(dqkv[:, :qd], h, self._g(i, "attn.c_q"))
-                ops.linear_wgrad(dqkv[:, qd:qd + kd], h, self._g(i, "attn.c_k"))
-                ops.linear_wgrad(dqkv[:, qd + kd:], h, self._g(i, "attn.c_v"))
+                def _three():
+                    ops.linear_wgrad(dqkv[:, :qd], h, self._g(i, "attn.c_q"))
+                    ops.linear_wgrad(dqkv[:, qd:qd + kd], h, self._g(i, "attn.c_k"))
+                    ops.linear_wgrad(dqkv[:, qd + kd:], h, self._g(i, "attn.c_v"))
+                self._off_path(_three, dqkv, h)
                 dh = ops.linear_dgrad(dqkv[:, :qd], self._w(i, "attn.c_q"))
                 dh = ops.linear_dgrad(dqkv[:, qd:qd + kd], self._w(i, "attn.c_k"), residual=dh)
                 dh = ops.linear_dgrad(dqkv[:, qd + kd:], self._w(i, "attn.c_v"), residual=dh)
@@ -325,7 +355,16 @@ class GPT:
             del dxr
             save["layers"][i] = None
             if self.on_layer_grads_ready is not None:
-                self.on_layer_grads_ready(i)
+                # a layer is announced one layer late, once its side-stream products are known to be complete,
+                # so the wait never stalls the critical path
+                if pending is not None:
+                    self._join_side(pending[1])
+                    self.on_layer_grads_ready(pending[0])
+                done = self._wgrad_stream.record_event() if self._wgrad_stream is not None else None
+                pending = (i, done)
+        if pending is not None:
+            self._join_side(pending[1])
+            self.on_layer_grads_ready(pending[0])
         # ---- embedding side --------------------------------------------
         dx0 = ops.add(dx0, dx)
         de, dgw, dlam = ops.smear_bwd(save["emb"], P.v("smear_gate.weight"), self._lam("smear_lambda"),
@@ -334,6 +373,7 @@ class GPT:
         P.g("smear_lambda").add_(dlam)
         de_raw = ops.rmsnorm_bwd(save["emb_raw"], de, save["rstd_e"])
         ops.embedding_bwd(tok, de_raw, P.g("transformer.wte.weight"), order=order)
+        self._join_side()
         if self.on_embed_grads_ready is not None:
             self.on_embed_grads_ready()
         self._saved = None
