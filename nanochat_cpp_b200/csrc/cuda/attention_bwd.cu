@@ -89,6 +89,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   constexpr int NW = L::kNW;
   constexpr int NUM_COMPUTE_WARPS = BwdWarps<MODE>::kCompute;
   constexpr int CW = BwdWarps<MODE>::kCols;
+  // dK/dV sweep: the probabilities never touch shared memory. Each warp packs its 16 columns of P to bf16 and
+  // stores them back over the first 8 of its own 16 score columns in TMEM; the dV product then takes its A operand
+  // from TMEM (one K=16 slice per warp column group). The score buffer is rewritten by the score MMA two tiles
+  // later, which the MMA thread issues after the accumulate MMAs that read P, and MMAs run in issue order.
+  constexpr bool P_IN_TMEM = MODE == kModeDKV && CW == 16;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
@@ -259,8 +264,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         if (MODE == kModeDKV) {
 #pragma unroll
           for (int k = 0; k < BS / 16; ++k) {
-            mma_f16_ss(tmem_A2, dw + static_cast<uint64_t>((L::kW + k * 32) >> 4),
-                       dy2 + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_a, (it > 0 || k > 0) ? 1u : 0u);
+            if constexpr (P_IN_TMEM)
+              mma_f16_ts(tmem_A2, tmem_T1 + tb * BS + k * 16, dy2 + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_a,
+                         (it > 0 || k > 0) ? 1u : 0u);
+            else
+              mma_f16_ss(tmem_A2, dw + static_cast<uint64_t>((L::kW + k * 32) >> 4),
+                         dy2 + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_a, (it > 0 || k > 0) ? 1u : 0u);
           }
         }
         mma_commit(&y_empty[yst]);
@@ -386,9 +395,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
           const int gran = (ch * (CW / 8) + gq) ^ (row & 7);
           *reinterpret_cast<uint4*>(sW + gran * 16) =
               make_uint4(pk_ds[4 * gq], pk_ds[4 * gq + 1], pk_ds[4 * gq + 2], pk_ds[4 * gq + 3]);
-          if (MODE == kModeDKV)
+          if (MODE == kModeDKV && !P_IN_TMEM)
             *reinterpret_cast<uint4*>(sW + L::kW + gran * 16) =
                 make_uint4(pk_p[4 * gq], pk_p[4 * gq + 1], pk_p[4 * gq + 2], pk_p[4 * gq + 3]);
+        }
+        if constexpr (P_IN_TMEM) {
+          tmem_st_32x8(tmem_T1 + tb * BS + c0 + lane_sel, pk_p);
+          tmem_st_wait();
         }
       }
       tc_fence_before();

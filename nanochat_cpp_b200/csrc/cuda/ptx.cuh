@@ -268,6 +268,13 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 
+// Store 32 lanes x 8 32-bit columns (16 packed bf16 per lane: one K=16 slice of a TMEM A operand).
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor, SWIZZLE_128B, version 1 (Blackwell). Offsets in bytes.
 //   K-major  operand: rows of 128 B (64 bf16 along K); 8-row groups `sbo` apart (1024 B); lbo unused.

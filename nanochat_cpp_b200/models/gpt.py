@@ -59,7 +59,7 @@ class GPT:
         # memory-bound row kernels of the critical path run beside it instead of after it.
         import os as _os2
         self._wgrad_stream = (torch.cuda.Stream(self.device) if self.device.type == "cuda" and
-                              _os2.environ.get("NANOCHAT_WGRAD_STREAM", "0") == "1" else None)
+                              _os2.environ.get("NANOCHAT_WGRAD_STREAM", "1") != "0" else None)
         self.fp8 = bool(fp8) and self.device.type == "cuda"
         # bitwise-reproducible embedding gradients (sorted, single-writer sums instead of atomics)
         import os as _os
