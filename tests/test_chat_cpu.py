@@ -163,3 +163,34 @@ def test_pipeline_tiny_profile(data_dir, tmp_path):
     assert rep.base["final_step"] == 8 and rep.sft["steps"] == 4 and rep.rl["steps"] == 1
     assert np.isfinite(rep.eval["val_bpb"]) and rep.eval["checkpoint"].endswith("rl.ckpt")
     assert os.path.exists(tmp_path / "pipeline.json")
+
+
+def test_chat_evaluator_isolation_and_core_means(data_dir, tmp_path):
+    from nanochat_cpp_b200.chat import (ALL_TASKS, BASELINES, ChatEvaluator, TaskReport, centered_mean, directory_loader)
+    tok = api.Tokenizer.load(os.path.join(data_dir, "loader_tokenizer.nctoken"))
+    cfg = api.Config(num_layers=2, num_heads=2, hidden_dim=64, seq_len=128, vocab_size=tok.vocab_size,
+                     head_dim=32, window_pattern="L")
+    model = api.Model(cfg, device="cpu", seed=5)
+    arc_rows = [{"question": "sky?", "choices": {"text": ["blue", "red"], "label": ["A", "B"]}, "answerKey": "A"}] * 4
+    mmlu_rows = [{"question": "1+1?", "choices": ["1", "2", "3", "4"], "answer": 1, "subject": "math"}] * 3
+    for name, rows in (("ARC-Easy", arc_rows), ("ARC-Challenge", arc_rows[:2]), ("MMLU", mmlu_rows)):
+        with open(tmp_path / f"{name}.jsonl", "w") as f:
+            f.write("\n".join(json.dumps(r) for r in rows))
+    ev = ChatEvaluator(model, tok, task_loader=directory_loader(str(tmp_path)), score_batch=2)
+    one = ev.task("MMLU", max_problems=2)
+    assert one.total == 2 and one.baseline == 0.25 and 0.0 <= one.accuracy <= 1.0 and not one.skipped
+    rep = ev.run()                                  # GSM8K and HumanEval have no data: isolated, not fatal
+    assert [r.name for r in rep.tasks] == list(ALL_TASKS)
+    skipped = {r.name for r in rep.tasks if r.skipped}
+    assert skipped == {"GSM8K", "HumanEval"} and all("FileNotFoundError" in r.error for r in rep.tasks if r.skipped)
+    assert rep.chat_core is None                    # a skipped task voids the overall mean
+    cat = [r for r in rep.tasks if not r.skipped]
+    want = sum((r.accuracy - 0.25) / 0.75 for r in cat) / 3
+    assert abs(rep.categorical_core - want) < 1e-12
+    import pytest
+    with pytest.raises(ValueError):
+        ev.task("nonsense")
+    with pytest.raises(FileNotFoundError):
+        ev.task("GSM8K")
+    full = [TaskReport(n, 1, 2, 0.5, BASELINES[n]) for n in ALL_TASKS]
+    assert abs(centered_mean(full, ALL_TASKS) - (3 * (0.25 / 0.75) + 2 * 0.5) / 5) < 1e-12
