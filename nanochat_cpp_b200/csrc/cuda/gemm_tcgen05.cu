@@ -143,10 +143,13 @@ __device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_
         f[2 * e + 1] = p.alpha * f[2 * e + 1] + p.beta * bf16_hi(rw[e]);
       }
     } else if (EPI == kEpiDRelu2) {
+      // d(pre) = d(act) * 2 relu(pre). The side operand is either the saved pre-activation (beta == 0) or the saved
+      // activation act = relu(pre)^2 (beta != 0), from which relu(pre) = sqrt(act).
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        f[2 * e] *= 2.0f * fmaxf(bf16_lo(rw[e]), 0.0f);
-        f[2 * e + 1] *= 2.0f * fmaxf(bf16_hi(rw[e]), 0.0f);
+        const float lo = fmaxf(bf16_lo(rw[e]), 0.0f), hi = fmaxf(bf16_hi(rw[e]), 0.0f);
+        f[2 * e] *= 2.0f * (p.beta != 0.0f ? sqrtf(lo) : lo);
+        f[2 * e + 1] *= 2.0f * (p.beta != 0.0f ? sqrtf(hi) : hi);
       }
     }
     uint4 out;
@@ -154,7 +157,8 @@ __device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_
     out.y = pack_bf16(f[2], f[3]);
     out.z = pack_bf16(f[4], f[5]);
     out.w = pack_bf16(f[6], f[7]);
-    *reinterpret_cast<uint4*>(crow_p + j * 8) = out;
+    // relu2 with C2 == C: only the activation is kept (the backward then works from the activation alone)
+    if (EPI != kEpiRelu2 || p.C != p.C2) *reinterpret_cast<uint4*>(crow_p + j * 8) = out;
     if (EPI == kEpiRelu2) {
       // act = relu(pre)^2 computed from the rounded pre-activation, as a separate pass would.
       const uint32_t ow[4] = {out.x, out.y, out.z, out.w};

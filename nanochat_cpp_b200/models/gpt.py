@@ -172,12 +172,12 @@ class GPT:
             from ..ops import fp8 as F8
             pre, act = F8.linear_fwd_fp8(h2, self._fp8_w[f"fc{i}"], relu2=True)
         else:
-            pre, act = ops.linear_relu2_fwd(h2, self._w(i, "mlp.c_fc"))
+            pre, act = None, ops.linear_relu2_act_fwd(h2, self._w(i, "mlp.c_fc"))
         x_out = ops.linear_fwd(act, self._w(i, "mlp.c_proj"), residual=x_mid)
         if save is not None:
             save["layers"].append(dict(x=x, xr=xr, rstd1=rstd1, q_pre=q_pre, k_pre=k_pre, q=q, k=k, v=v4,
                                        ve=ve, gate=gate, attn=attn, lse=lse, x_mid=x_mid, rstd2=rstd2,
-                                       pre=pre))
+                                       pre=pre, act=act if pre is None else None))
         return x_out
 
     def _trunk(self, tokens, B, T, save):
@@ -298,8 +298,12 @@ class GPT:
                 dx = ops.add(dx, dxb)
                 dxb = None
             # MLP
-            self._off_path(lambda: ops.linear_wgrad_relu2(dx, s["pre"], self._g(i, "mlp.c_proj")), dx, s["pre"])
-            dpre = ops.linear_dgrad_relu2(dx, self._w(i, "mlp.c_proj"), s["pre"])
+            if s["act"] is not None:  # the activation was saved instead of the pre-activation: nothing to recompute
+                self._off_path(lambda: ops.linear_wgrad(dx, s["act"], self._g(i, "mlp.c_proj")), dx, s["act"])
+                dpre = ops.linear_dgrad_relu2_act(dx, self._w(i, "mlp.c_proj"), s["act"])
+            else:
+                self._off_path(lambda: ops.linear_wgrad_relu2(dx, s["pre"], self._g(i, "mlp.c_proj")), dx, s["pre"])
+                dpre = ops.linear_dgrad_relu2(dx, self._w(i, "mlp.c_proj"), s["pre"])
             h2 = ops.rmsnorm_apply(s["x_mid"], s["rstd2"])
             self._off_path(lambda: ops.linear_wgrad(dpre, h2, self._g(i, "mlp.c_fc")), dpre, h2)
             dh2 = ops.linear_dgrad(dpre, self._w(i, "mlp.c_fc"))

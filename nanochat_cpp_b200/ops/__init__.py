@@ -117,7 +117,7 @@ def _dispatch(name: str) -> Callable:
 
 
 _NAMES = [
-    "linear_fwd", "linear_relu2_fwd", "linear_dgrad", "linear_dgrad_relu2", "linear_wgrad",
+    "linear_fwd", "linear_relu2_fwd", "linear_relu2_act_fwd", "linear_dgrad_relu2_act", "linear_dgrad", "linear_dgrad_relu2", "linear_wgrad",
     "linear_wgrad_relu2", "rmsnorm_fwd", "rmsnorm_apply", "rmsnorm_bwd", "add", "add_cols", "concat_qkv",
     "backout_fwd", "backout_bwd", "blend_norm_fwd", "blend_bwd", "qk_prep_fwd", "qk_prep_bwd",
     "attention_fwd", "attention_bwd", "value_gate_fwd", "value_gate_bwd", "smear_fwd", "smear_bwd",

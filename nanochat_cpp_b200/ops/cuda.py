@@ -119,6 +119,18 @@ def linear_relu2_fwd(x, w):
     return pre, act
 
 
+def linear_relu2_act_fwd(x, w):
+    """act = relu(x @ w^T)^2 only: the pre-activation is never written (its backward uses sqrt(act))."""
+    act = torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)
+    gemm(x, w, epi=EPI_RELU2, out=act, out2=act)
+    return act
+
+
+def linear_dgrad_relu2_act(dy, w, act):
+    """d(pre) = (dy @ w) * 2 sqrt(act), the backward of act = relu(pre)^2 written in terms of act."""
+    return gemm(dy, w, b_mn=True, epi=EPI_DRELU2, r=act, beta=1.0)
+
+
 def linear_dgrad(dy, w, *, residual=None):
     # dx[M,K] = dy[M,N] @ w[N,K]: B operand is w read MN-major (its K index is contiguous)
     if residual is not None:

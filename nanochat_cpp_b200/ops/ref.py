@@ -50,6 +50,17 @@ def linear_relu2_fwd(x, w):
     return pre, act
 
 
+def linear_relu2_act_fwd(x, w):
+    """act = relu(pre)^2 with pre = x @ w^T rounded to the compute dtype first (as `linear_relu2_fwd`)."""
+    return linear_relu2_fwd(x, w)[1]
+
+
+def linear_dgrad_relu2_act(dy, w, act):
+    """d(pre) = (dy @ w) * 2 sqrt(act): relu(pre) recovered from the saved activation."""
+    dact = torch.matmul(dy, w).float()
+    return (dact * 2.0 * torch.sqrt(act.float().clamp_min(0.0))).to(dy.dtype)
+
+
 def linear_dgrad(dy, w, *, residual=None):
     dx = torch.matmul(dy, w)
     if residual is not None:

@@ -17,7 +17,8 @@ from .roofline import RooflinePlan, estimate
 
 # operator of the step profile -> (roofline family prefix, phase)
 JOIN = {
-    "linear_fwd": ("gemm_", "forward"), "linear_relu2_fwd": ("gemm_mlp_fc", "forward"),
+    "linear_fwd": ("gemm_", "forward"), "linear_relu2_fwd": ("gemm_mlp_fc", "forward"), "linear_relu2_act_fwd": ("gemm_mlp_fc", "forward"),
+    "linear_dgrad_relu2_act": ("gemm_mlp_proj", "backward"),
     "linear_dgrad": ("gemm_", "backward"), "linear_wgrad": ("gemm_", "backward"),
     "linear_dgrad_relu2": ("gemm_mlp_proj", "backward"), "linear_wgrad_relu2": ("gemm_mlp_proj", "backward"),
     "attention_fwd": ("attention", "forward"), "attention_bwd": ("attention", "backward"),

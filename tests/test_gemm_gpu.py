@@ -113,3 +113,24 @@ def test_skinny_decode_gemm(M, N, K):
     assert (pre.float() - want).abs().max() <= tol
     assert torch.equal(act, torch.relu(pre.float()).square().to(torch.bfloat16))
     Kmod.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 256), (300, 520, 192), (8, 256, 128)])
+def test_relu2_from_the_saved_activation(M, N, K):
+    """MLP with only act = relu(pre)^2 saved: forward without the pre-activation, backward through sqrt(act)."""
+    from nanochat_cpp_b200.ops import cuda as Kmod, ref
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    pre, act_two = Kmod.linear_relu2_fwd(x, w)
+    act = Kmod.linear_relu2_act_fwd(x, w)
+    assert torch.equal(act, act_two)                       # same epilogue, the pre store is just skipped
+    dy = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w2 = (torch.randn(K, N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)   # c_proj: [out=K, in=N]
+    got = Kmod.linear_dgrad_relu2_act(dy, w2, act).float()
+    want = ref.linear_dgrad_relu2_act(dy.float(), w2.float(), act.float())
+    assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+    # and it agrees with the derivative taken from the pre-activation (sqrt of a bf16 square loses < 1 bf16 ulp)
+    from_pre = Kmod.linear_dgrad_relu2(dy, w2, pre).float()
+    assert (got - from_pre).abs().max() <= 2e-2 * want.abs().max()
+    Kmod.check_status()
