@@ -29,6 +29,11 @@ constexpr int BKV = 64;    // keys per step
 constexpr int KVSTAGES = 3;
 constexpr int NUM_THREADS = 64 + NQ * 128;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
+// The probabilities stay in tensor memory: each thread packs its row of P to bf16 and stores it over the first 32
+// of the 64 score columns it has just read; the P V product takes its A operand from there. The score buffer is
+// next written by the score MMA two key tiles later, which the MMA thread issues after this tile's P V product,
+// and MMAs run in issue order, so no extra barrier is needed. Shared memory carries only Q, K and V.
+constexpr bool kPInTmem = true;
 
 template <int D>
 struct Fwd2Smem {
@@ -230,8 +235,12 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const uint32_t to = tmem_O(x);
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k) {
-            mma_f16_ss(to, dp + static_cast<uint64_t>((k * 32) >> 4), dv + static_cast<uint64_t>((k * 16 * 128) >> 4),
-                       idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+            if constexpr (kPInTmem)
+              mma_f16_ts(to, tmem_S(x, i & 1) + k * 8, dv + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_o,
+                         (i > 0 || k > 0) ? 1u : 0u);
+            else
+              mma_f16_ss(to, dp + static_cast<uint64_t>((k * 32) >> 4), dv + static_cast<uint64_t>((k * 16 * 128) >> 4),
+                         idesc_o, (i > 0 || k > 0) ? 1u : 0u);
           }
           mma_commit(p_empty(x, i & 1));
           mma_commit(o_done(x));
@@ -329,15 +338,21 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         packed[e / 2] = pk;
       }
       l_run += l_tile;
-      if (!mbar_wait(p_empty(x, sb), ph ^ 1, abort_flag, p.status, kErrWaitOther)) { ok = false; break; }
-      uint8_t* sP = smem + L::kOffP + (x * 2 + sb) * L::kP + row * 128;
+      if constexpr (kPInTmem) {
+        tmem_st_32x32(tmem_S(x, sb) + lane_sel, packed);
+        tmem_st_wait();
+        tc_fence_before();
+      } else {
+        if (!mbar_wait(p_empty(x, sb), ph ^ 1, abort_flag, p.status, kErrWaitOther)) { ok = false; break; }
+        uint8_t* sP = smem + L::kOffP + (x * 2 + sb) * L::kP + row * 128;
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        const int gran = g ^ (row & 7);
-        *reinterpret_cast<uint4*>(sP + gran * 16) =
-            make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+        for (int g = 0; g < 8; ++g) {
+          const int gran = g ^ (row & 7);
+          *reinterpret_cast<uint4*>(sP + gran * 16) =
+              make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+        }
+        fence_async_shared();
       }
-      fence_async_shared();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(x, sb));
     }

@@ -181,7 +181,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const long long ci = static_cast<long long>(m) * p.ldc + n;
         if (p.epi == kEpiBf16Res) v += __bfloat162float(p.R[static_cast<long long>(m) * p.ldr + n]);
         const __nv_bfloat16 o = __float2bfloat16_rn(v);
-        p.C[ci] = o;
+        if (p.epi != kEpiRelu2 || p.C != p.C2) p.C[ci] = o;  // C2 == C: only the activation is kept
         if (p.epi == kEpiRelu2) {
           const float a = fmaxf(__bfloat162float(o), 0.0f);
           p.C2[ci] = __float2bfloat16_rn(a * a);

@@ -97,6 +97,13 @@ __device__ __forceinline__ Unit decode_unit(const KernelParams& p, int unit) {
 
 // One 32-column chunk of a thread's accumulator row through the fused epilogue EPI to global memory.
 // `rv` holds the thread's 32 residual / pre-activation values (bf16) for the epilogues that read R.
+// One MUFU instruction; the result feeds a bf16 rounding, so the approximation error (about 1 fp32 ulp) is invisible.
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int EPI>
 __device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_t (&r)[32], const uint4 (&rv)[4],
                                             int col0, long long crow) {
@@ -145,11 +152,12 @@ __device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_
     } else if (EPI == kEpiDRelu2) {
       // d(pre) = d(act) * 2 relu(pre). The side operand is either the saved pre-activation (beta == 0) or the saved
       // activation act = relu(pre)^2 (beta != 0), from which relu(pre) = sqrt(act).
+      const bool from_act = p.beta != 0.0f;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float lo = fmaxf(bf16_lo(rw[e]), 0.0f), hi = fmaxf(bf16_hi(rw[e]), 0.0f);
-        f[2 * e] *= 2.0f * (p.beta != 0.0f ? sqrtf(lo) : lo);
-        f[2 * e + 1] *= 2.0f * (p.beta != 0.0f ? sqrtf(hi) : hi);
+        f[2 * e] *= 2.0f * (from_act ? sqrt_approx(lo) : lo);
+        f[2 * e + 1] *= 2.0f * (from_act ? sqrt_approx(hi) : hi);
       }
     }
     uint4 out;

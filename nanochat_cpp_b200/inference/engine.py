@@ -133,7 +133,7 @@ class InferenceEngine:
                 attn, _ = ops.attention_fwd(q, kk.contiguous(), vv.contiguous(), wl, q_offset=t0)
             x_mid = ops.linear_fwd(attn.reshape(M, H * D), m._w(i, "attn.c_proj"), residual=xr)
             h2, _ = ops.rmsnorm_fwd(x_mid)
-            _, act = ops.linear_relu2_fwd(h2, m._w(i, "mlp.c_fc"))
+            act = ops.linear_relu2_act_fwd(h2, m._w(i, "mlp.c_fc"))
             x = ops.linear_fwd(act, m._w(i, "mlp.c_proj"), residual=x_mid)
             if i == cfg.backout_layer:
                 x_backout = x

@@ -53,6 +53,11 @@ class GPT:
         self.on_layer_grads_ready: Optional[Callable[[int], None]] = None
         self.on_head_grads_ready: Optional[Callable[[], None]] = None
         self.on_embed_grads_ready: Optional[Callable[[], None]] = None
+        import os as _os3
+        # False: rebuild the normalised activations in the backward (saves memory)
+        self.keep_normed = _os3.environ.get("NANOCHAT_KEEP_NORMED", "1") != "0"
+        # True: the MLP keeps act = relu(pre)^2 only; False: keeps pre and rebuilds act for the weight gradient
+        self.mlp_keep_act = _os3.environ.get("NANOCHAT_MLP_KEEP_ACT", "1") != "0"
         self.phase_event = None  # a CUDA event recorded between the forward trunk and the head / backward
         # Weight-gradient products are off the critical path of the backward (nothing in the backward reads them),
         # so they run on a second stream: a persistent GEMM CTA per SM leaves most thread slots free, and the
@@ -172,12 +177,18 @@ class GPT:
             from ..ops import fp8 as F8
             pre, act = F8.linear_fwd_fp8(h2, self._fp8_w[f"fc{i}"], relu2=True)
         else:
-            pre, act = None, ops.linear_relu2_act_fwd(h2, self._w(i, "mlp.c_fc"))
+            if self.mlp_keep_act:
+                pre, act = None, ops.linear_relu2_act_fwd(h2, self._w(i, "mlp.c_fc"))
+            else:
+                pre, act = ops.linear_relu2_fwd(h2, self._w(i, "mlp.c_fc"))
         x_out = ops.linear_fwd(act, self._w(i, "mlp.c_proj"), residual=x_mid)
         if save is not None:
             save["layers"].append(dict(x=x, xr=xr, rstd1=rstd1, q_pre=q_pre, k_pre=k_pre, q=q, k=k, v=v4,
                                        ve=ve, gate=gate, attn=attn, lse=lse, x_mid=x_mid, rstd2=rstd2,
-                                       pre=pre, act=act if pre is None else None))
+                                       pre=pre, act=act if pre is None else None,
+                                       # the normalised inputs of the QKV and MLP products are kept for their weight
+                                       # gradients (2 x M x hidden per layer) instead of being rebuilt from x and rstd
+                                       h=h if self.keep_normed else None, h2=h2 if self.keep_normed else None))
         return x_out
 
     def _trunk(self, tokens, B, T, save):
@@ -304,7 +315,7 @@ class GPT:
             else:
                 self._off_path(lambda: ops.linear_wgrad_relu2(dx, s["pre"], self._g(i, "mlp.c_proj")), dx, s["pre"])
                 dpre = ops.linear_dgrad_relu2(dx, self._w(i, "mlp.c_proj"), s["pre"])
-            h2 = ops.rmsnorm_apply(s["x_mid"], s["rstd2"])
+            h2 = s["h2"] if s["h2"] is not None else ops.rmsnorm_apply(s["x_mid"], s["rstd2"])
             self._off_path(lambda: ops.linear_wgrad(dpre, h2, self._g(i, "mlp.c_fc")), dpre, h2)
             dh2 = ops.linear_dgrad(dpre, self._w(i, "mlp.c_fc"))
             del dpre, h2
@@ -325,7 +336,7 @@ class GPT:
             ops.qk_prep_bwd(_heads(s["q_pre"], B, T, H, D), _heads(s["k_pre"], B, T, KV, D), dq, dk, cos, sin,
                             out_q=_heads(dqkv[:, :qd], B, T, H, D), out_k=_heads(dqkv[:, qd:qd + kd], B, T, KV, D))
             del dq, dk, dqk
-            h = ops.rmsnorm_apply(s["xr"], s["rstd1"])
+            h = s["h"] if s["h"] is not None else ops.rmsnorm_apply(s["xr"], s["rstd1"])
             dv2 = dqkv[:, qd + kd:]
             dh12 = None
             if cfg.has_value_embedding(i):
