@@ -859,6 +859,10 @@ __device__ __forceinline__ float ex2_fast(float x) {
 
 constexpr int kClsThreads = 512;
 
+// STAGE: the row is parked in shared memory between the two passes (one CTA per SM for a 64K-entry row). Without it
+// the second pass reads the row again through L2, where the first pass left it, and several CTAs share an SM, so one
+// CTA's exponentials overlap another's loads and stores.
+template <bool STAGE>
 __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
     bf16* __restrict__ logits, long long ld, const int* __restrict__ targets, float* __restrict__ losses,
     const float* __restrict__ row_scale, const float* __restrict__ dlogit_scale, int vocab, int padded,
@@ -887,13 +891,15 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const int i = i0 + u * kClsThreads * 8;
-      raw[u] = i < vocab ? __ldcs(reinterpret_cast<const uint4*>(lp + i)) : make_uint4(0, 0, 0, 0);
+      raw[u] = i >= vocab ? make_uint4(0, 0, 0, 0)
+                          : STAGE ? __ldcs(reinterpret_cast<const uint4*>(lp + i))
+                                  : *reinterpret_cast<const uint4*>(lp + i);
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const int i = i0 + u * kClsThreads * 8;
       if (i >= vocab) break;
-      if (want_grad) *reinterpret_cast<uint4*>(row_s + i) = raw[u];
+      if (STAGE && want_grad) *reinterpret_cast<uint4*>(row_s + i) = raw[u];
       const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -916,7 +922,7 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
   for (int i = threadIdx.x * 8; i < padded; i += kClsThreads * 8) {
     uint4 outv = make_uint4(0, 0, 0, 0);
     if (i < vocab) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(row_s + i);
+      const uint4 raw = STAGE ? *reinterpret_cast<const uint4*>(row_s + i) : *reinterpret_cast<const uint4*>(lp + i);
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
       uint32_t o[4];
 #pragma unroll
@@ -1089,9 +1095,18 @@ void classifier_fwd_bwd(bf16* logits, long long ld, const int* targets, float* l
   if (rows <= 0) return;
   const size_t row_bytes = static_cast<size_t>(padded) * sizeof(bf16);
   const bool vec = vocab % 8 == 0 && padded % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  static const bool stage = [] {
+    const char* e = getenv("NANOCHAT_CLS_STAGE");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (vec && !stage) {
+    classifier_smem_kernel<false><<<rows, kClsThreads, 0, s>>>(logits, ld, targets, losses, row_scale, dlogit_scale,
+                                                               vocab, padded, softcap, ignore_index, want_grad);
+    return;
+  }
   if (vec && row_bytes <= 200 * 1024) {
-    cudaFuncSetAttribute(classifier_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    classifier_smem_kernel<<<rows, kClsThreads, want_grad ? row_bytes : 0, s>>>(
+    cudaFuncSetAttribute(classifier_smem_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    classifier_smem_kernel<true><<<rows, kClsThreads, want_grad ? row_bytes : 0, s>>>(
         logits, ld, targets, losses, row_scale, dlogit_scale, vocab, padded, softcap, ignore_index, want_grad);
     return;
   }
