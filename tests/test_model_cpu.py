@@ -61,3 +61,25 @@ def test_grad_accumulates_and_scales():
     g1 = m.params.grad.clone()
     m.forward_backward(tokens, targets, grad_scale=0.5)
     assert torch.allclose(m.params.grad, 2 * g1, rtol=1e-5, atol=1e-7)
+
+
+def test_backward_memory_modes_agree(monkeypatch):
+    """Keeping act / the normalised activations and rebuilding them in the backward give the same gradients."""
+    import torch
+    from nanochat_cpp_b200.config import Config
+    from nanochat_cpp_b200.models import GPT
+    cfg = Config(num_layers=2, num_heads=2, num_kv_heads=2, hidden_dim=64, seq_len=32, vocab_size=96,
+                 padded_vocab_size=128, window_pattern="SL")
+    tok = torch.randint(0, cfg.vocab_size, (2, cfg.seq_len + 1), generator=torch.Generator().manual_seed(0))
+    grads = []
+    for keep_act, keep_normed in ((True, True), (False, False)):
+        m = GPT(cfg, "cpu", torch.float32, seed=4)
+        for spec in m.params.specs:
+            m.params.m(spec.name).add_(0.02 * torch.randn(spec.shape, generator=torch.Generator().manual_seed(7)))
+        m.params.sync_compute()
+        m.mlp_keep_act, m.keep_normed = keep_act, keep_normed
+        m.zero_grad()
+        loss = m.forward_backward(tok[:, :-1], tok[:, 1:])
+        grads.append((float(loss), m.params.grad.clone()))
+    assert grads[0][0] == grads[1][0]
+    torch.testing.assert_close(grads[0][1], grads[1][1], rtol=1e-4, atol=1e-6)
