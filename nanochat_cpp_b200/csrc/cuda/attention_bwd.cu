@@ -17,6 +17,8 @@
 //                                                             through an MN-major descriptor
 // so nothing is transposed in memory and the probabilities are recomputed, never stored.
 #include <cuda.h>
+
+#include <algorithm>
 #include <cuda_bf16.h>
 
 #include "attention.h"
@@ -491,6 +493,56 @@ __global__ void __launch_bounds__(256) attention_delta_kernel(const __nv_bfloat1
   if (lane == 0) delta[(static_cast<long long>(b) * H + h) * T + t] = acc;
 }
 
+// The same sum with 16-byte loads: D / 8 lanes share a row, a warp covers 32 / (D / 8) rows per pass and keeps four
+// passes (eight loads per thread) in flight, so the kernel runs at memory speed (it reads O and dO once).
+template <int D>
+__global__ void __launch_bounds__(256) attention_delta_vec_kernel(const __nv_bfloat16* __restrict__ O, long long osb,
+                                                                  long long ost, long long osh,
+                                                                  const __nv_bfloat16* __restrict__ dO, long long dsb,
+                                                                  long long dst, long long dsh,
+                                                                  float* __restrict__ delta, int B, int H, int T) {
+  constexpr int LPR = D / 8;     // lanes per row
+  constexpr int RPW = 32 / LPR;  // rows per warp and pass
+  constexpr int UNROLL = 4;
+  const int lane = threadIdx.x & 31, sub = lane / LPR, li = lane % LPR;
+  const long long n = static_cast<long long>(B) * T * H;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const long long step = static_cast<long long>(gridDim.x) * 8 * RPW * UNROLL;
+  for (long long base = warp_global * RPW * UNROLL; base < n; base += step) {
+    uint4 a[UNROLL], g[UNROLL];
+    long long out[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long r = base + u * RPW + sub;
+      out[u] = -1;
+      a[u] = g[u] = make_uint4(0, 0, 0, 0);
+      if (r < n) {
+        const int h = static_cast<int>(r % H);
+        const long long bt = r / H;
+        const int t = static_cast<int>(bt % T);
+        const long long b = bt / T;
+        a[u] = *reinterpret_cast<const uint4*>(O + b * osb + static_cast<long long>(t) * ost +
+                                               static_cast<long long>(h) * osh + li * 8);
+        g[u] = *reinterpret_cast<const uint4*>(dO + b * dsb + static_cast<long long>(t) * dst +
+                                               static_cast<long long>(h) * dsh + li * 8);
+        out[u] = (b * H + h) * T + t;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, gw[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+      float acc = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        acc += __uint_as_float(aw[e] << 16) * __uint_as_float(gw[e] << 16) +
+               __uint_as_float(aw[e] & 0xffff0000u) * __uint_as_float(gw[e] & 0xffff0000u);
+#pragma unroll
+      for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (li == 0 && out[u] >= 0) delta[out[u]] = acc;
+    }
+  }
+}
+
 template <int D, int MODE>
 const char* launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& y1, const CUtensorMap& y2,
                        const CUtensorMap& ds, const BwdParams& p, dim3 grid, cudaStream_t stream) {
@@ -514,10 +566,26 @@ const char* attention_bwd(const AttnArgs& a, cudaStream_t stream) {
   if (a.H % a.KVH) return "attention_bwd: heads must be a multiple of kv heads";
   {
     const long long n = static_cast<long long>(a.B) * a.Tq * a.H;
-    attention_delta_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(a.O), a.o_stride_b, a.o_stride_t, a.o_stride_h,
-        static_cast<const __nv_bfloat16*>(a.dO), a.do_stride_b, a.do_stride_t, a.do_stride_h, a.delta, a.B, a.H, a.Tq,
-        a.D);
+    const __nv_bfloat16* o = static_cast<const __nv_bfloat16*>(a.O);
+    const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(a.dO);
+    auto mult8 = [](long long v) { return v % 8 == 0; };
+    const bool vec = ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(g)) & 15) == 0 &&
+                     mult8(a.o_stride_b) && mult8(a.o_stride_t) && mult8(a.o_stride_h) && mult8(a.do_stride_b) &&
+                     mult8(a.do_stride_t) && mult8(a.do_stride_h);
+    const long long rows_per_cta = 8 * (32 / (a.D / 8)) * 4;
+    const unsigned ctas = static_cast<unsigned>(std::min<long long>((n + rows_per_cta - 1) / rows_per_cta, 148 * 16));
+    if (vec && a.D == 128)
+      attention_delta_vec_kernel<128><<<ctas, 256, 0, stream>>>(o, a.o_stride_b, a.o_stride_t, a.o_stride_h, g,
+                                                                 a.do_stride_b, a.do_stride_t, a.do_stride_h, a.delta,
+                                                                 a.B, a.H, a.Tq);
+    else if (vec && a.D == 64)
+      attention_delta_vec_kernel<64><<<ctas, 256, 0, stream>>>(o, a.o_stride_b, a.o_stride_t, a.o_stride_h, g,
+                                                                a.do_stride_b, a.do_stride_t, a.do_stride_h, a.delta, a.B,
+                                                                a.H, a.Tq);
+    else
+      attention_delta_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(
+          o, a.o_stride_b, a.o_stride_t, a.o_stride_h, g, a.do_stride_b, a.do_stride_t, a.do_stride_h, a.delta, a.B,
+          a.H, a.Tq, a.D);
   }
   CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64;
   const long long dq[4] = {a.D, a.H, a.Tq, a.B};
