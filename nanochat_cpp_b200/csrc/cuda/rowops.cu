@@ -52,7 +52,7 @@ __device__ __forceinline__ void st8(bf16* p, const V8& v) {
 }
 __device__ __forceinline__ float b2f(bf16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ bf16 f2b(float v) { return __float2bfloat16_rn(v); }
-__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+__host__ __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
 __device__ __forceinline__ float block_sum(float v, float* sh) {
@@ -583,6 +583,95 @@ __global__ void __launch_bounds__(kThreads) value_gate_bwd_kernel(
   for (int i = threadIdx.x; i < KV * kGateCh; i += blockDim.x) atomicAdd(&dgw[i], sh_dgw[i]);
 }
 
+// 16-byte versions (D a multiple of 8 up to 128, aligned rows): a half-warp owns one (token, kv head) pair, each of
+// its lanes one 8-element slice of the head, so a warp moves two heads per pass with every lane loading 16 bytes.
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(kThreads) value_gate_fwd_vec_kernel(const bf16* __restrict__ h, long long ldh,
+                                                                      const bf16* __restrict__ ve,
+                                                                      const bf16* __restrict__ gw, bf16* __restrict__ v,
+                                                                      long long ldv, bf16* __restrict__ gate,
+                                                                      int tokens, int KV, int D) {
+  const int lane = threadIdx.x & 31, li = lane & 15;
+  const long long pair = (static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5)) * 2 + (lane >> 4);
+  const bool valid = pair < static_cast<long long>(tokens) * KV;
+  const int tok = valid ? static_cast<int>(pair / KV) : 0, kh = valid ? static_cast<int>(pair % KV) : 0;
+  float pre = 0.0f;
+  if (valid && li < kGateCh) pre = b2f(h[static_cast<long long>(tok) * ldh + li]) * b2f(gw[kh * kGateCh + li]);
+  pre = half_warp_sum(pre);
+  const float g = 3.0f / (1.0f + __expf(-pre));
+  if (!valid) return;
+  if (li == 0) gate[static_cast<long long>(tok) * KV + kh] = f2b(g);
+  const int d = li * 8;
+  if (d >= D) return;
+  bf16* vp = v + static_cast<long long>(tok) * ldv + kh * D + d;
+  const uint4 ev = *reinterpret_cast<const uint4*>(ve + (static_cast<long long>(tok) * KV + kh) * D + d);
+  const uint4 vv = *reinterpret_cast<const uint4*>(vp);
+  const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float lo = __uint_as_float(vw[e] << 16) + g * __uint_as_float(ew[e] << 16);
+    const float hi = __uint_as_float(vw[e] & 0xffff0000u) + g * __uint_as_float(ew[e] & 0xffff0000u);
+    const __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+    o[e] = *reinterpret_cast<const uint32_t*>(&pk);
+  }
+  *reinterpret_cast<uint4*>(vp) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__global__ void __launch_bounds__(kThreads) value_gate_bwd_vec_kernel(
+    const bf16* __restrict__ h, long long ldh, const bf16* __restrict__ ve, const bf16* __restrict__ gw,
+    const bf16* __restrict__ gate, const bf16* __restrict__ dv, long long lddv, bf16* __restrict__ dve,
+    float* __restrict__ dh12, float* __restrict__ dgw, int tokens, int KV, int D) {
+  extern __shared__ float sh_dgw[];  // KV*12
+  for (int i = threadIdx.x; i < KV * kGateCh; i += blockDim.x) sh_dgw[i] = 0.0f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, li = lane & 15, half = lane >> 4;
+  const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (tok < tokens) {
+    float dh_acc = 0.0f;  // lane li < 12 of each half accumulates its heads' part of dh12[tok, li]
+    const float hj = li < kGateCh ? b2f(h[static_cast<long long>(tok) * ldh + li]) : 0.0f;
+    const int d = li * 8;
+    for (int kh0 = 0; kh0 < KV; kh0 += 2) {
+      const int kh = kh0 + half;
+      const bool live = kh < KV;
+      float dg = 0.0f, g = 0.0f;
+      if (live) {
+        g = b2f(gate[static_cast<long long>(tok) * KV + kh]);
+        if (d < D) {
+          const uint4 dvv = *reinterpret_cast<const uint4*>(dv + static_cast<long long>(tok) * lddv + kh * D + d);
+          const uint4 ev = *reinterpret_cast<const uint4*>(ve + (static_cast<long long>(tok) * KV + kh) * D + d);
+          const uint32_t dw[4] = {dvv.x, dvv.y, dvv.z, dvv.w}, ew[4] = {ev.x, ev.y, ev.z, ev.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float d0 = __uint_as_float(dw[e] << 16), d1 = __uint_as_float(dw[e] & 0xffff0000u);
+            dg += d0 * __uint_as_float(ew[e] << 16) + d1 * __uint_as_float(ew[e] & 0xffff0000u);
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(g * d0, g * d1);
+            o[e] = *reinterpret_cast<const uint32_t*>(&pk);
+          }
+          *reinterpret_cast<uint4*>(dve + (static_cast<long long>(tok) * KV + kh) * D + d) =
+              make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+      dg = half_warp_sum(dg);
+      const float dpre = dg * g * (1.0f - g * (1.0f / 3.0f));
+      if (live && li < kGateCh) {
+        atomicAdd(&sh_dgw[kh * kGateCh + li], dpre * hj);
+        dh_acc += dpre * b2f(gw[kh * kGateCh + li]);
+      }
+    }
+    dh_acc += __shfl_xor_sync(0xffffffffu, dh_acc, 16);  // the two halves handled alternate heads
+    if (lane < kGateCh) dh12[static_cast<long long>(tok) * kGateCh + lane] = dh_acc;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < KV * kGateCh; i += blockDim.x) atomicAdd(&dgw[i], sh_dgw[i]);
+}
+
 // ------------------------------------------------------------------ smear
 constexpr int kSmearCh = 24;
 __global__ void __launch_bounds__(kThreads) smear_fwd_kernel(const bf16* __restrict__ emb,
@@ -1056,11 +1145,21 @@ void value_gate_fwd(const bf16* h, long long ldh, const bf16* ve, const bf16* ga
                     bf16* gate, int tokens, int KV, int D, cudaStream_t s) {
   const long long n = static_cast<long long>(tokens) * KV;
   if (n <= 0) return;
+  if (D % 8 == 0 && D <= 128 && ldv % 8 == 0 && aligned16(v) && aligned16(ve)) {
+    value_gate_fwd_vec_kernel<<<blocks_for_rows((n + 1) / 2), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens,
+                                                                                KV, D);
+    return;
+  }
   value_gate_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens, KV, D);
 }
 void value_gate_bwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, const bf16* gate, const bf16* dv,
                     long long lddv, bf16* dve, float* dh12, float* dgw, int tokens, int KV, int D, cudaStream_t s) {
   if (tokens <= 0) return;
+  if (D % 8 == 0 && D <= 128 && lddv % 8 == 0 && aligned16(dv) && aligned16(ve) && aligned16(dve)) {
+    value_gate_bwd_vec_kernel<<<blocks_for_rows(tokens), kThreads, KV * kGateCh * sizeof(float), s>>>(
+        h, ldh, ve, gate_w, gate, dv, lddv, dve, dh12, dgw, tokens, KV, D);
+    return;
+  }
   value_gate_bwd_kernel<<<blocks_for_rows(tokens), kThreads, KV * kGateCh * sizeof(float), s>>>(
       h, ldh, ve, gate_w, gate, dv, lddv, dve, dh12, dgw, tokens, KV, D);
 }
