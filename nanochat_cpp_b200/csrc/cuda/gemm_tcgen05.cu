@@ -47,7 +47,8 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64-wide MN chunk of an MN-major
 constexpr int GROUP_M = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kEpiStageBytes = 32 * 64;  // one epilogue warp's staging tile (32 rows x 32 bf16)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 4 * kEpiStageBytes;
 
 struct KernelParams {
   int M, N, K;
@@ -104,10 +105,44 @@ __device__ __forceinline__ float sqrt_approx(float x) {
   return y;
 }
 
+// bf16 outputs leave through a warp-private shared-memory tile: a thread owns one accumulator row (a TMEM lane), so
+// storing straight from registers would scatter 16 bytes to each of 32 rows per instruction (32 half-filled
+// sectors). The warp writes its 32 rows x 64 bytes to shared memory (granules swizzled against bank conflicts) and
+// reads them back so that four lanes cover the 64 contiguous bytes of one row: 16 full sectors per instruction.
+struct EpiWarp {
+  uint8_t* stage;       // 32 rows x 64 bytes, private to the warp
+  int lane;
+  int rows_valid;       // rows of this warp's 32 that exist (M edge)
+  long long crow0;      // element offset of the warp's first row in C (and C2)
+};
+
+__device__ __forceinline__ void emit_rows(const KernelParams& p, const EpiWarp& w, __nv_bfloat16* base, int col0,
+                                          const uint4 (&out)[4], bool own_row_ok) {
+  const int r = w.lane;
+  if (own_row_ok) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(w.stage + r * 64 + ((j ^ ((r >> 1) & 3)) << 4)) = out[j];
+  }
+  __syncwarp();
+  const int g = w.lane & 3;
+  const bool col_ok = col0 + g * 8 < p.N;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int rr = it * 8 + (w.lane >> 2);
+    if (col_ok && rr < w.rows_valid) {
+      const uint4 v = *reinterpret_cast<const uint4*>(w.stage + rr * 64 + ((g ^ ((rr >> 1) & 3)) << 4));
+      *reinterpret_cast<uint4*>(base + w.crow0 + static_cast<long long>(rr) * p.ldc + col0 + g * 8) = v;
+    }
+  }
+  __syncwarp();
+}
+
 template <int EPI>
 __device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_t (&r)[32], const uint4 (&rv)[4],
-                                            int col0, long long crow) {
+                                            int col0, long long crow, const EpiWarp& w, bool row_ok) {
   if (EPI == kEpiF32) {
+    if (!row_ok) return;
     float* crow_p = reinterpret_cast<float*>(p.C) + crow + col0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -132,10 +167,9 @@ __device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_
     }
     return;
   }
-  __nv_bfloat16* crow_p = reinterpret_cast<__nv_bfloat16*>(p.C) + crow + col0;
+  uint4 outs[4], acts[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    if (col0 + j * 8 >= p.N) break;
     float f[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
@@ -165,8 +199,7 @@ __device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_
     out.y = pack_bf16(f[2], f[3]);
     out.z = pack_bf16(f[4], f[5]);
     out.w = pack_bf16(f[6], f[7]);
-    // relu2 with C2 == C: only the activation is kept (the backward then works from the activation alone)
-    if (EPI != kEpiRelu2 || p.C != p.C2) *reinterpret_cast<uint4*>(crow_p + j * 8) = out;
+    outs[j] = out;
     if (EPI == kEpiRelu2) {
       // act = relu(pre)^2 computed from the rounded pre-activation, as a separate pass would.
       const uint32_t ow[4] = {out.x, out.y, out.z, out.w};
@@ -177,10 +210,12 @@ __device__ __forceinline__ void store_chunk(const KernelParams& p, const uint32_
         const float hi = fmaxf(bf16_hi(ow[e]), 0.0f);
         aw[e] = pack_bf16(lo * lo, hi * hi);
       }
-      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0 + j * 8) =
-          make_uint4(aw[0], aw[1], aw[2], aw[3]);
+      acts[j] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
     }
   }
+  // relu2 with C2 == C: only the activation is kept (the backward then works from the activation alone)
+  if (EPI != kEpiRelu2 || p.C != p.C2) emit_rows(p, w, reinterpret_cast<__nv_bfloat16*>(p.C), col0, outs, row_ok);
+  if (EPI == kEpiRelu2) emit_rows(p, w, reinterpret_cast<__nv_bfloat16*>(p.C2), col0, acts, row_ok);
 }
 
 template <int EPI>
@@ -200,7 +235,7 @@ __device__ __forceinline__ void load_residual(const KernelParams& p, uint4 (&rv)
 // converted and stored.
 template <int EPI>
 __device__ __forceinline__ void store_tile(const KernelParams& p, uint32_t taddr, int n_base, bool row_ok,
-                                           long long crow, long long rrow) {
+                                           long long crow, long long rrow, const EpiWarp& w) {
   uint32_t r0[32], r1[32];
   uint4 q0[4], q1[4];
   tmem_ld_32x32(taddr, r0);
@@ -210,13 +245,13 @@ __device__ __forceinline__ void store_tile(const KernelParams& p, uint32_t taddr
     tmem_ld_wait();
     tmem_ld_32x32(taddr + (c + 1) * 32, r1);
     load_residual<EPI>(p, q1, n_base + (c + 1) * 32, rrow, row_ok);
-    if (row_ok && n_base + c * 32 < p.N) store_chunk<EPI>(p, r0, q0, n_base + c * 32, crow);
+    if (n_base + c * 32 < p.N) store_chunk<EPI>(p, r0, q0, n_base + c * 32, crow, w, row_ok);
     tmem_ld_wait();
     if (c + 2 < BN / 32) {
       tmem_ld_32x32(taddr + (c + 2) * 32, r0);
       load_residual<EPI>(p, q0, n_base + (c + 2) * 32, rrow, row_ok);
     }
-    if (row_ok && n_base + (c + 1) * 32 < p.N) store_chunk<EPI>(p, r1, q1, n_base + (c + 1) * 32, crow);
+    if (n_base + (c + 1) * 32 < p.N) store_chunk<EPI>(p, r1, q1, n_base + (c + 1) * 32, crow, w, row_ok);
   }
 }
 
@@ -394,7 +429,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool row_ok = row < p.M;
       const long long crow = static_cast<long long>(u.b) * p.strideC + static_cast<long long>(row) * p.ldc;
       const long long rrow = static_cast<long long>(u.b) * p.strideR + static_cast<long long>(row) * p.ldr;
-      store_tile<EPI>(p, tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16), u.n_blk * BN, row_ok, crow, rrow);
+      EpiWarp w;
+      w.stage = smem + STAGES * STAGE_BYTES + 256 + q * kEpiStageBytes;
+      w.lane = lane;
+      w.rows_valid = min(32, p.M - (row - lane));
+      w.crow0 = crow - static_cast<long long>(lane) * p.ldc;
+      store_tile<EPI>(p, tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16), u.n_blk * BN, row_ok, crow, rrow, w);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -424,7 +464,7 @@ constexpr int P_STAGES = 6;
 constexpr int P_A_BYTES = BM * BK * 2;         // 16 KiB
 constexpr int P_B_BYTES = (BN / 2) * BK * 2;   // 16 KiB: this CTA's half of the 256-wide B tile
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256 + 4 * kEpiStageBytes;
 
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -582,7 +622,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool row_ok = row < p.M;
       const long long crow = static_cast<long long>(u.b) * p.strideC + static_cast<long long>(row) * p.ldc;
       const long long rrow = static_cast<long long>(u.b) * p.strideR + static_cast<long long>(row) * p.ldr;
-      store_tile<EPI>(p, tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16), u.n_blk * BN, row_ok, crow, rrow);
+      EpiWarp w;
+      w.stage = smem + P_STAGES * P_STAGE_BYTES + 256 + q * kEpiStageBytes;
+      w.lane = lane;
+      w.rows_valid = min(32, p.M - (row - lane));
+      w.crow0 = crow - static_cast<long long>(lane) * p.ldc;
+      store_tile<EPI>(p, tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16), u.n_blk * BN, row_ok, crow, rrow, w);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc == 0 ? leader_empty0 : leader_empty1);
