@@ -36,7 +36,7 @@ from .params import ParamStore, init_weights
 
 class GPT:
     def __init__(self, cfg: Config, device="cpu", dtype: torch.dtype = torch.bfloat16, seed: int = 0,
-                 init: bool = True, head_chunk_rows: int = 8192, allocator=None, fp8: bool = False):
+                 init: bool = True, head_chunk_rows: int = 11264, allocator=None, fp8: bool = False):
         """`fp8`: run the forward QKV and MLP up-projection products in block-scaled E4M3 (1x128 activation scales,
         128x128 weight scales, bf16 out); attention, norms, the projections with fused residuals, the LM head and
         the whole backward stay in bf16. Call `refresh_fp8()` after every optimizer step."""
@@ -47,7 +47,10 @@ class GPT:
         self.params = ParamStore(cfg, self.device, dtype, allocator=allocator)
         if init:
             init_weights(self.params, seed)
-        self.head_chunk_rows = head_chunk_rows
+        import os as _os0
+        # rows of logits alive at once. 11264 = 44 x 256: with the 1280-wide dgrad output (5 column tiles) a chunk is
+        # 220 tile pairs, 2.97 rounds over 74 CTA pairs; 8192 gave 160 = 2.16 rounds, a third of the last one idle.
+        self.head_chunk_rows = int(_os0.environ.get("NANOCHAT_HEAD_CHUNK_ROWS", head_chunk_rows))
         self._rope: Dict[int, tuple] = {}
         self._saved: Optional[dict] = None
         self.on_layer_grads_ready: Optional[Callable[[int], None]] = None

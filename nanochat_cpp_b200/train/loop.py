@@ -34,7 +34,7 @@ class TrainConfig:
     resume: str = ""
     log: str = ""
     dtype: str = "bf16"
-    head_chunk_rows: int = 8192
+    head_chunk_rows: int = 11264
     fp8: bool = False
     optim: OptimizerConfig = field(default_factory=OptimizerConfig)
     sched: SchedulerConfig = field(default_factory=SchedulerConfig)
