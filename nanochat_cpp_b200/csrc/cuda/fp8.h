@@ -30,4 +30,28 @@ struct Fp8GemmArgs {
 // Returns nullptr on success or a static error string.
 const char* gemm_fp8_blockscaled(const Fp8GemmArgs& args, cudaStream_t stream);
 
+// ---- MXFP8 (fp8_mx.cu): E4M3 operands, one UE8M0 (power-of-two) scale per row and 32 K elements, applied by
+// tcgen05.mma kind::mxf8f6f4.block_scale; the whole K extent accumulates in tensor memory.
+// Scales are stored as 512-byte atoms (128 rows x 4 scales, byte (r % 32) * 16 + (r / 32) * 4 + k32), rows grouped
+// by GEMM tile: atom = ((r / tile_rows) * (K / 128) + kb) * ceil(tile_rows / 128) + (r % tile_rows) / 128.
+// tile_rows is 128 for the A operand and mxfp8_tile_n(N) for the B operand.
+int mxfp8_tile_n(int N);
+long long mxfp8_scale_bytes(int R, int K, int tile_rows);
+// K % 128 == 0, ldx % 8 == 0. Returns nullptr on success or a static error string.
+const char* quantize_mxfp8(const __nv_bfloat16* x, long long ldx, uint8_t* xq, uint8_t* sf, int R, int K, int tile_rows,
+                           cudaStream_t s);
+
+struct MxGemmArgs {
+  const uint8_t* A = nullptr;    // [M, K] e4m3, row-major
+  const uint8_t* B = nullptr;    // [N, K] e4m3, row-major
+  const uint8_t* sfa = nullptr;  // atoms of A, tile_rows = 128
+  const uint8_t* sfb = nullptr;  // atoms of B, tile_rows = mxfp8_tile_n(N)
+  int M = 0, N = 0, K = 0;
+  __nv_bfloat16* C = nullptr;    // [M, N]
+  long long ldc = 0;
+  __nv_bfloat16* C2 = nullptr;   // optional second output relu(C)^2 (same layout); C2 == C keeps only the activation
+  int* status = nullptr;
+};
+const char* gemm_mxfp8(const MxGemmArgs& args, cudaStream_t stream);
+
 }  // namespace nc

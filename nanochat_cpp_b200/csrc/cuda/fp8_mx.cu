@@ -1,0 +1,429 @@
+// MXFP8 GEMM for sm_100a: E4M3 operands with one power-of-two scale (UE8M0) per 32 consecutive K elements of every
+// row, applied by the tensor core itself (tcgen05.mma kind::mxf8f6f4.block_scale), and its quantizer.
+//
+// The reference scales fp8 operands per tensor and calls cublasLt (backends/cuda/kernels/fp8.cu:39-80,
+// backends/cuda/gemm.cu:553-690). The two-level kernel in fp8.cu applies fp32 block scales on the CUDA cores and
+// is bound by that promotion. Here the scales travel with the operands into tensor memory, the whole K extent
+// accumulates in TMEM, and the epilogue is the plain bf16 one, so the product runs at the fp8 tensor rate.
+//
+// Scale layout ("atoms"). The scales of 128 rows x 128 K elements (128 x 4 bytes) form one 512-byte atom in the
+// order tcgen05.cp.32x128b.warpx4 expects: byte (r % 32) * 16 + (r / 32) * 4 + k32. Rows are grouped by GEMM tile
+// (`tile_rows` = 128 for the activations, the kernel's BN for the weights) so that the atoms of one tile and one
+// 128-deep K block are contiguous: atom index = ((r / tile_rows) * (K / 128) + kb) * atoms_per_tile + (r % tile_rows) / 128.
+//
+//   warp 0       producer: TMA tiles of A (128 x 128 B) and B (BN x 128 B), bulk copies of their scale atoms
+//   warp 1       TMEM allocation; per K block: tcgen05.cp of the atoms into TMEM, 4 MMAs of K = 32 (scale id 0..3)
+//   warps 2..9   epilogue: TMEM -> registers -> bf16 -> warp-private shared-memory transpose -> 64-byte row segments
+//                (optionally relu(x)^2 as a second output), overlapped with the next tile (two accumulators)
+#include "fp8.h"
+
+#include <cuda.h>
+#include <cuda_fp8.h>
+
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace nc {
+
+namespace {
+
+__device__ __forceinline__ uint8_t mx_to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+// One half-warp per (row, 128-wide K block): a thread owns 8 consecutive elements, four threads share a scale.
+// Rows in [R, R_pad) only get the neutral scale byte 127 (2^0); their data is never read (TMA zero-fills).
+__global__ void __launch_bounds__(256) quantize_mx_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                          uint8_t* __restrict__ xq, uint8_t* __restrict__ sf, int R,
+                                                          int R_pad, int K, int tile_rows, int atoms_per_tile) {
+  const int kbs = K / 128;
+  const long long unit = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 4;
+  if (unit >= static_cast<long long>(R_pad) * kbs) return;
+  const int row = static_cast<int>(unit / kbs), kb = static_cast<int>(unit % kbs);
+  const int l16 = threadIdx.x & 15;
+  // (R_pad * kbs is even, so both half-warps of a warp are in range together and the shuffles below are uniform)
+  float v[8];
+  float amax = 0.0f;
+  if (row < R) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * ldx + kb * 128 + l16 * 8);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = bf16_lo(w[i]);
+      v[2 * i + 1] = bf16_hi(w[i]);
+      amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    }
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  // smallest power of two >= amax / 448: biased exponent of s, plus one when s is not itself a power of two
+  const uint32_t bits = __float_as_uint(amax * (1.0f / 448.0f));
+  uint32_t eb = (bits >> 23) + ((bits & 0x7fffffu) ? 1u : 0u);
+  eb = amax > 0.0f ? min(max(eb, 1u), 253u) : 127u;
+  if (row < R) {
+    const float inv = __uint_as_float((254u - eb) << 23);
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      lo |= static_cast<uint32_t>(mx_to_e4m3(v[e] * inv)) << (8 * e);
+      hi |= static_cast<uint32_t>(mx_to_e4m3(v[4 + e] * inv)) << (8 * e);
+    }
+    *reinterpret_cast<uint2*>(xq + static_cast<long long>(row) * K + kb * 128 + l16 * 8) = make_uint2(lo, hi);
+  }
+  // the four scale bytes of this (row, K block) sit in lanes 0, 4, 8, 12 of the half-warp
+  const int base = threadIdx.x & 16;
+  const uint32_t b0 = __shfl_sync(0xffffffffu, eb, base), b1 = __shfl_sync(0xffffffffu, eb, base + 4);
+  const uint32_t b2 = __shfl_sync(0xffffffffu, eb, base + 8), b3 = __shfl_sync(0xffffffffu, eb, base + 12);
+  if (l16 == 0) {
+    const int tile = row / tile_rows, rt = row % tile_rows;
+    const long long atom = (static_cast<long long>(tile) * kbs + kb) * atoms_per_tile + rt / 128;
+    const int r = rt % 128;
+    *reinterpret_cast<uint32_t*>(sf + atom * 512 + (r % 32) * 16 + (r / 32) * 4) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+constexpr int BM = 128, BK = 128;             // BK in elements = bytes
+constexpr int UMMA_K = 32;
+constexpr int A_BYTES = BM * BK;
+constexpr int SFA_BYTES = 512, SFB_BYTES = 1024;   // one atom for the 128 A rows, two for the B rows
+constexpr int SF_BYTES = SFA_BYTES + SFB_BYTES;
+constexpr int EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
+constexpr int TMEM_COLS = 512;
+constexpr int SF_SLOTS = 4, SF_SLOT_COLS = 16;     // scale columns rotate over four slots behind the accumulators
+constexpr int kEpiStageBytes = 32 * 64;            // one warp's 32 rows x 32 bf16 on the way out
+
+template <int BN>
+struct MxCfg {
+  static_assert(BN % 32 == 0 && BN > 128 && 2 * BN + SF_SLOTS * SF_SLOT_COLS <= TMEM_COLS, "tile width");
+  static constexpr int B_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;          // a multiple of 1024 (SWIZZLE_128B tiles)
+  static constexpr int STAGES = BN <= 192 ? 5 : 4;
+  static constexpr int H0 = ((BN / 32 + 1) / 2) * 32;             // columns of the first epilogue half
+  static constexpr int SF_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
+  static constexpr int EPI_OFF = BAR_OFF + 256;
+  static constexpr int SMEM_BYTES = EPI_OFF + EPI_WARPS * kEpiStageBytes + 1024;
+  static constexpr int SF_COL0 = 2 * BN;
+};
+
+struct MxParams {
+  int M, N, K, m_blocks, n_blocks, k_blocks;
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  __nv_bfloat16* C;
+  __nv_bfloat16* C2;
+  long long ldc;
+  int* status;
+};
+
+// kind::mxf8f6f4 with E4M3 operands (format 0), UE8M0 scales, both operands K-major. The scale ids (which of the
+// four bytes of a TMEM scale column this K = 32 step uses) are OR-ed in per instruction.
+__host__ __device__ constexpr uint32_t make_idesc_mx_e4m3(int m, int n) {
+  return (1u << 23) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+__device__ __forceinline__ uint32_t with_sf_id(uint32_t idesc, uint32_t id) { return idesc | (id << 29) | (id << 4); }
+
+__device__ __forceinline__ void mma_mxf8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+
+// 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated into all four lane quadrants.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// Unswizzled K-major descriptor of one scale atom: 8-row groups of 16-byte rows, 128 bytes apart.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <int BN, bool RELU2>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const MxParams p) {
+  using Cfg = MxCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sf_smem = smem + Cfg::SF_OFF;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_units = p.m_blocks * p.n_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], EPI_WARPS);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
+        const uint8_t* sfa = p.sfa + static_cast<long long>(m_blk) * p.k_blocks * SFA_BYTES;
+        const uint8_t* sfb = p.sfb + static_cast<long long>(n_blk) * p.k_blocks * SFB_BYTES;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrWaitEmpty)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* ss = sf_smem + stage * SF_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES + SF_BYTES);
+          tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
+          tma_load_2d(sa + A_BYTES, &tmB, &full_bar[stage], kb * BK, n_blk * BN);
+          bulk_load(ss, sfa + static_cast<long long>(kb) * SFA_BYTES, SFA_BYTES, &full_bar[stage]);
+          bulk_load(ss + SFA_BYTES, sfb + static_cast<long long>(kb) * SFB_BYTES, SFB_BYTES, &full_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {   // give the copies in flight time to land before the CTA's shared memory goes away
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_mx_e4m3(BM, BN);
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
+      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem) + A_BYTES, 16, 1024);
+      int stage = 0, buf = 0, slot = 0;
+      uint32_t phase = 0, aphase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, abort_flag, p.status, kErrWaitTmemEmpty)) break;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrWaitFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t ss = smem_u32(sf_smem + stage * SF_BYTES);
+          const uint32_t tsfa = tmem_base + Cfg::SF_COL0 + slot * SF_SLOT_COLS, tsfb = tsfa + 4;
+          tmem_cp_32x128b_warpx4(tsfa, make_sf_desc(ss));
+          tmem_cp_32x128b_warpx4(tsfb, make_sf_desc(ss + SFA_BYTES));
+          tmem_cp_32x128b_warpx4(tsfb + 4, make_sf_desc(ss + SFA_BYTES + 512));
+          const uint64_t da = a_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
+          const uint64_t db = b_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)   // 32 one-byte elements = 32 bytes = 2 descriptor units per step
+            mma_mxf8_ss(tmem_base + buf * BN, da + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
+                        with_sf_id(idesc, k), tsfa, tsfb, (kb | k) ? 1u : 0u);
+          mma_commit(&empty_bar[stage]);
+          if (kb == p.k_blocks - 1) mma_commit(&acc_full[buf]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+          slot = (slot + 1) & (SF_SLOTS - 1);
+        }
+        if (++buf == 2) {
+          buf = 0;
+          aphase ^= 1;
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    const int col_first = half ? Cfg::H0 : 0;
+    constexpr int MAX_GROUPS = Cfg::H0 / 32;
+    const int groups = (half ? BN - Cfg::H0 : Cfg::H0) / 32;
+    uint8_t* stage_buf = smem + Cfg::EPI_OFF + (warp - 2) * kEpiStageBytes;
+    const int g4 = lane & 3;
+    int buf = 0;
+    uint32_t aphase = 0;
+    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+      const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
+      const int row0 = m_blk * BM + q * 32;
+      const bool row_ok = row0 + lane < p.M;
+      const int rows_valid = min(32, p.M - row0);
+      if (!mbar_wait(&acc_full[buf], aphase, abort_flag, p.status, kErrWaitTmemFull)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + buf * BN + col_first + (static_cast<uint32_t>(q * 32) << 16);
+      // The thread owns one accumulator row. A group of 32 columns becomes 64 bytes of bf16, goes through a
+      // warp-private swizzled tile and leaves as full 64-byte row segments (four lanes per row).
+      auto emit = [&](__nv_bfloat16* base, const uint4 (&v)[4], int c0) {
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v[j];
+        }
+        __syncwarp();
+        const bool col_ok = c0 + g4 * 8 < p.N;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int rr = it * 8 + (lane >> 2);
+          if (col_ok && rr < rows_valid)
+            *reinterpret_cast<uint4*>(base + static_cast<long long>(row0 + rr) * p.ldc + c0 + g4 * 8) =
+                *reinterpret_cast<const uint4*>(stage_buf + rr * 64 + ((g4 ^ ((rr >> 1) & 3)) << 4));
+        }
+        __syncwarp();
+      };
+      uint32_t r[2][32];
+      tmem_ld_32x32(taddr, r[0]);
+#pragma unroll
+      for (int g = 0; g < MAX_GROUPS; ++g) {
+        if (g >= groups) break;
+        tmem_ld_wait();
+        if (g + 1 < groups) {
+          tmem_ld_32x32(taddr + (g + 1) * 32, r[(g + 1) & 1]);
+        } else {   // everything of this accumulator is in registers: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        const int c0 = n_blk * BN + col_first + g * 32;
+        if (c0 >= p.N) continue;
+        const uint32_t(&acc)[32] = r[g & 1];
+        uint4 outs[4], acts[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t* a8 = acc + j * 8;
+          outs[j].x = pack_bf16(__uint_as_float(a8[0]), __uint_as_float(a8[1]));
+          outs[j].y = pack_bf16(__uint_as_float(a8[2]), __uint_as_float(a8[3]));
+          outs[j].z = pack_bf16(__uint_as_float(a8[4]), __uint_as_float(a8[5]));
+          outs[j].w = pack_bf16(__uint_as_float(a8[6]), __uint_as_float(a8[7]));
+          if (RELU2) {
+            const uint32_t ow[4] = {outs[j].x, outs[j].y, outs[j].z, outs[j].w};
+            uint32_t aw[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float lo = fmaxf(bf16_lo(ow[e]), 0.0f), hi = fmaxf(bf16_hi(ow[e]), 0.0f);
+              aw[e] = pack_bf16(lo * lo, hi * hi);
+            }
+            acts[j] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+          }
+        }
+        if (!RELU2 || p.C != p.C2) emit(p.C, outs, c0);
+        if (RELU2) emit(p.C2, acts, c0);
+      }
+      if (++buf == 2) {
+        buf = 0;
+        aphase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, bool RELU2>
+cudaError_t launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const MxParams& p, int grid, cudaStream_t stream) {
+  // set on every launch: the attribute belongs to the current device's copy of the function
+  const cudaError_t e = cudaFuncSetAttribute(gemm_mxfp8_kernel<BN, RELU2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             MxCfg<BN>::SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  gemm_mxfp8_kernel<BN, RELU2><<<grid, NUM_THREADS, MxCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int mxfp8_tile_n(int N) {
+  const int pad192 = (N + 191) / 192 * 192, pad224 = (N + 223) / 224 * 224;
+  return pad192 < pad224 ? 192 : 224;
+}
+
+long long mxfp8_scale_bytes(int R, int K, int tile_rows) {
+  const long long tiles = (R + tile_rows - 1) / tile_rows, atoms = (tile_rows + 127) / 128;
+  return tiles * atoms * (K / 128) * 512;
+}
+
+const char* quantize_mxfp8(const __nv_bfloat16* x, long long ldx, uint8_t* xq, uint8_t* sf, int R, int K, int tile_rows,
+                           cudaStream_t s) {
+  if (R <= 0 || K <= 0) return nullptr;
+  if (K % 128 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return "quantize_mxfp8: K % 128, ld % 8 and 16-byte rows";
+  if (tile_rows != 128 && tile_rows != 192 && tile_rows != 224) return "quantize_mxfp8: tile_rows must be 128, 192 or 224";
+  const int tiles = (R + tile_rows - 1) / tile_rows, atoms = (tile_rows + 127) / 128;
+  const int R_pad = tiles * tile_rows;
+  const long long units = static_cast<long long>(R_pad) * (K / 128);
+  quantize_mx_kernel<<<static_cast<unsigned>((units + 15) / 16), 256, 0, s>>>(x, ldx, xq, sf, R, R_pad, K, tile_rows, atoms);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+const char* gemm_mxfp8(const MxGemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0) return nullptr;
+  if (a.K % 128) return "gemm_mxfp8: K must be a multiple of 128";
+  if (a.N % 8 || a.ldc % 8) return "gemm_mxfp8: N and ldc must allow 16-byte stores";
+  if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) | reinterpret_cast<uintptr_t>(a.sfa) |
+       reinterpret_cast<uintptr_t>(a.sfb) | reinterpret_cast<uintptr_t>(a.C) | reinterpret_cast<uintptr_t>(a.C2)) & 15)
+    return "gemm_mxfp8: misaligned operand";
+  const int bn = mxfp8_tile_n(a.N);
+  CUtensorMap ta, tb;
+  if (!make_tmap_u8_2d(&ta, a.A, a.K, a.M, a.K, BK, BM) || !make_tmap_u8_2d(&tb, a.B, a.K, a.N, a.K, BK, bn))
+    return "gemm_mxfp8: cuTensorMapEncodeTiled failed";
+  MxParams p;
+  p.M = a.M, p.N = a.N, p.K = a.K;
+  p.m_blocks = (a.M + BM - 1) / BM, p.n_blocks = (a.N + bn - 1) / bn, p.k_blocks = a.K / BK;
+  p.sfa = a.sfa, p.sfb = a.sfb;
+  p.C = a.C, p.C2 = a.C2, p.ldc = a.ldc, p.status = a.status;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int units = p.m_blocks * p.n_blocks;
+  const int grid = units < sms ? units : sms;
+  cudaError_t e;
+  if (bn == 192)
+    e = a.C2 ? launch_mx<192, true>(ta, tb, p, grid, stream) : launch_mx<192, false>(ta, tb, p, grid, stream);
+  else
+    e = a.C2 ? launch_mx<224, true>(ta, tb, p, grid, stream) : launch_mx<224, false>(ta, tb, p, grid, stream);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+}  // namespace nc

@@ -90,3 +90,90 @@ def linear_fwd_fp8(x: torch.Tensor, w: Fp8Weight, relu2: bool = False):
         fp8_gemm(xq, sx, w.q, w.s, pre, act)
         return pre, act
     return fp8_gemm(xq, sx, w.q, w.s)
+
+
+# ================================================================================================ MXFP8
+# E4M3 values with one power-of-two scale (UE8M0 byte, value 2^(b - 127)) per row and 32 consecutive K elements.
+# The tensor core applies the scales itself (tcgen05.mma kind::mxf8f6f4.block_scale, `csrc/cuda/fp8_mx.cu`), so
+# the whole K extent accumulates in tensor memory and no promotion pass on the CUDA cores is needed.
+MX_BLOCK = 32
+
+
+def ref_mx_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """x [R, K] -> (q float8_e4m3fn [R, K], biased exponents uint8 [R, K/32]).
+
+    The scale of a block is the smallest power of two >= amax / 448 (exponent byte 127 for an all-zero block).
+    """
+    R, K = x.shape
+    xb = x.float().view(R, K // MX_BLOCK, MX_BLOCK)
+    amax = xb.abs().amax(-1)
+    bits = (amax * (1.0 / E4M3_MAX)).view(torch.int32)
+    eb = (bits >> 23) + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    eb = torch.where(amax > 0, eb.clamp(1, 253), torch.full_like(eb, 127))
+    inv = ((254 - eb) << 23).view(torch.float32)
+    q = (xb * inv.unsqueeze(-1)).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q.view(R, K), eb.to(torch.uint8)
+
+
+def ref_mx_dequantize(q: torch.Tensor, eb: torch.Tensor) -> torch.Tensor:
+    R, K = q.shape
+    scale = torch.exp2(eb.float() - 127.0)
+    return (q.float().view(R, K // MX_BLOCK, MX_BLOCK) * scale.unsqueeze(-1)).view(R, K)
+
+
+def mx_scales_from_atoms(sf: torch.Tensor, R: int, K: int, tile_rows: int) -> torch.Tensor:
+    """Undo the kernel's scale layout: atoms uint8 -> biased exponents uint8 [R, K/32] (for tests and debugging).
+
+    One 512-byte atom holds 128 rows x 4 scales at byte (r % 32) * 16 + (r // 32) * 4 + k32; atoms are ordered
+    [row tile][128-deep K block][128-row group inside the tile].
+    """
+    kbs = K // 128
+    atoms_per_tile = (tile_rows + 127) // 128
+    tiles = (R + tile_rows - 1) // tile_rows
+    a = sf.view(tiles, kbs, atoms_per_tile, 32, 4, 4)            # [tile, kb, atom, r % 32, r // 32, k32]
+    a = a.permute(0, 2, 4, 3, 1, 5).reshape(tiles, atoms_per_tile * 128, kbs * 4)
+    return a[:, :tile_rows].reshape(tiles * tile_rows, kbs * 4)[:R].contiguous()
+
+
+def mx_tile_n(n: int) -> int:
+    """Width of the GEMM's B tile for an output of n columns; the scale atoms of a weight are grouped by it."""
+    from . import cuda as K
+    return int(K._C.fp8_mx_tile_n(n))
+
+
+def mx_quantize(x: torch.Tensor, tile_rows: int = 128):
+    """bf16 [R, K] -> (uint8 e4m3 [R, K], scale atoms uint8). tile_rows: 128 for activations, mx_tile_n(N) for weights."""
+    from . import cuda as K
+    q, sf = K._C.fp8_mx_quantize(x, tile_rows)
+    return q, sf
+
+
+def mx_gemm(xq, sfx, wq, sfw, out: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None):
+    """bf16 [M, N] = xq [M, K] x wq [N, K]^T with both operands' scales applied by the MMA; `out2` receives
+    relu(out)^2 (pass out2 = out to keep only the activation)."""
+    from . import cuda as K
+    if out is None:
+        out = torch.empty((xq.shape[0], wq.shape[0]), dtype=torch.bfloat16, device=xq.device)
+    K._C.fp8_mx_gemm(xq, sfx, wq, sfw, out, out2, K._C.status_tensor(xq.device.index))
+    return out
+
+
+class MxWeight:
+    """A weight [N, K] kept as MXFP8 (values + scale atoms grouped by the GEMM's B tile); refresh after every update."""
+
+    def __init__(self, w: torch.Tensor):
+        self.tile_n = mx_tile_n(w.shape[0])
+        self.q, self.s = mx_quantize(w, self.tile_n)
+
+    def refresh(self, w: torch.Tensor) -> None:
+        self.q, self.s = mx_quantize(w, self.tile_n)
+
+
+def linear_fwd_mx(x: torch.Tensor, w: MxWeight, relu2: bool = False):
+    xq, sx = mx_quantize(x, 128)
+    if relu2:
+        pre = torch.empty((x.shape[0], w.q.shape[0]), dtype=torch.bfloat16, device=x.device)
+        act = torch.empty_like(pre)
+        mx_gemm(xq, sx, w.q, w.s, pre, act)
+        return pre, act
+    return mx_gemm(xq, sx, w.q, w.s)

@@ -83,3 +83,49 @@ def test_model_forward_in_fp8_tracks_bf16_and_trains():
         b.refresh_fp8()
         first = loss if first is None else first
     assert loss < first
+
+
+# ------------------------------------------------------------------------------------------------ MXFP8
+def test_mx_quantizer_matches_definition_bit_for_bit():
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = (torch.randn(300, 512, device="cuda", generator=g) * 3).to(torch.bfloat16)
+    x[5] = 0                                     # all-zero blocks keep the neutral exponent 127
+    x[7, 130] = 1000.0                           # an outlier only coarsens its own 32-block
+    x[9, :32] = 448.0                            # amax / 448 is exactly a power of two: no round-up
+    for tile_rows in (128, 192, 224):
+        q, sf = fp8.mx_quantize(x, tile_rows)
+        qr, ebr = fp8.ref_mx_quantize(x)
+        eb = fp8.mx_scales_from_atoms(sf, 300, 512, tile_rows)
+        assert torch.equal(eb, ebr)
+        assert torch.equal(q.view(torch.float8_e4m3fn).float(), qr.float())
+    assert (ebr[5] == 127).all() and int(ebr[9, 0]) == 127
+    assert int(ebr[7, 130 // 32]) == 127 + 2 and int(ebr[7, 0]) < 127     # 1000 / 448 -> 2^2
+    back = fp8.ref_mx_dequantize(qr, ebr)
+    assert (back - x.float()).abs().max() <= 0.0715 * x.float().abs().max()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 192, 128), (128, 224, 128), (300, 640, 512), (1024, 1280, 1280),
+                                   (257, 136, 384), (2048, 3840, 1280), (515, 5120, 256)])
+def test_mx_gemm_matches_dequantized_product(M, N, K):
+    from nanochat_cpp_b200.ops import cuda as Kmod
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    x[:, K // 2:] *= 37.0                         # scales differ along K: every scale byte of a column matters
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    w[N // 3:] *= 0.01                            # and along N
+    xq, sx = fp8.mx_quantize(x, 128)
+    wq, sw = fp8.mx_quantize(w, fp8.mx_tile_n(N))
+    out = fp8.mx_gemm(xq, sx, wq, sw)
+    xd = fp8.ref_mx_dequantize(*fp8.ref_mx_quantize(x))
+    wd = fp8.ref_mx_dequantize(*fp8.ref_mx_quantize(w))
+    want = xd @ wd.t()
+    assert (out.float() - want).abs().max() <= 1e-2 * want.abs().max()
+    exact = x.float() @ w.float().t()
+    assert (out.float() - exact).abs().max() <= 8e-2 * exact.abs().max()
+    pre, act = torch.empty_like(out), torch.empty_like(out)
+    fp8.mx_gemm(xq, sx, wq, sw, pre, act)
+    assert torch.equal(pre, out) and torch.equal(act, torch.relu(out.float()).square().to(torch.bfloat16))
+    only_act = torch.empty_like(out)
+    fp8.mx_gemm(xq, sx, wq, sw, only_act, only_act)
+    assert torch.equal(only_act, act)
+    Kmod.check_status()
