@@ -39,7 +39,9 @@ def parse():
     ap.add_argument("--batch", type=int, default=32, help="sequences per GPU per step")
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-batch (0 = whole batch)")
     ap.add_argument("--transport", default=os.environ.get("NANOCHAT_DP_TRANSPORT", "auto"))
-    ap.add_argument("--fp8", action="store_true", help="block-scaled E4M3 forward products for QKV and MLP up-projection")
+    ap.add_argument("--fp8", nargs="?", const="mx", default=None, choices=["mx", "block"],
+                    help="E4M3 forward products for QKV and MLP up-projection: mx = MXFP8 scales inside the MMA, "
+                         "block = fp32 block scales promoted on the CUDA cores (not the headline: that is bf16)")
     return ap.parse_args()
 
 
@@ -219,7 +221,7 @@ def main():
             "metric": "train_tokens_per_sec", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": round(value / PUBLISHED_TOK_S, 3),
-            "dtype": "fp8-e4m3(qkv,fc fwd)+bf16" if args.fp8 else "bf16",
+            "dtype": f"fp8-e4m3-{args.fp8}(qkv,fc fwd)+bf16" if args.fp8 else "bf16",
             "data": "synthetic Zipf(1.1) token ids, random-init weights", "impl": "ours",
             "mfu_of_measured_sustained": round(value * fl_tok / world / (peaks["bf16_tflops_sustained"] * 1e12), 4),
             "model_tflops_per_gpu": round(value * fl_tok / world / 1e12, 1),

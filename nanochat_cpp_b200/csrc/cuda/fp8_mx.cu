@@ -31,54 +31,66 @@ __device__ __forceinline__ uint8_t mx_to_e4m3(float v) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
 
-// One half-warp per (row, 128-wide K block): a thread owns 8 consecutive elements, four threads share a scale.
+// One half-warp per two consecutive (row, 128-wide K block) units: a thread owns 8 consecutive elements of each,
+// four threads share a scale; both 16-byte loads are issued before either unit is processed.
 // Rows in [R, R_pad) only get the neutral scale byte 127 (2^0); their data is never read (TMA zero-fills).
+// R_pad * (K / 128) is even, so a half-warp's two units are in range together and a warp's shuffles are uniform.
 __global__ void __launch_bounds__(256) quantize_mx_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                           uint8_t* __restrict__ xq, uint8_t* __restrict__ sf, int R,
                                                           int R_pad, int K, int tile_rows, int atoms_per_tile) {
   const int kbs = K / 128;
-  const long long unit = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 4;
-  if (unit >= static_cast<long long>(R_pad) * kbs) return;
-  const int row = static_cast<int>(unit / kbs), kb = static_cast<int>(unit % kbs);
+  const long long total = static_cast<long long>(R_pad) * kbs;
+  const long long unit0 = ((static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 4) * 2;
   const int l16 = threadIdx.x & 15;
-  // (R_pad * kbs is even, so both half-warps of a warp are in range together and the shuffles below are uniform)
-  float v[8];
-  float amax = 0.0f;
-  if (row < R) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * ldx + kb * 128 + l16 * 8);
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  const int base = threadIdx.x & 16;
+  const bool in_range = unit0 < total;
+  int row[2], kb[2];
+  uint4 raw[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const long long unit = in_range ? unit0 + u : 0;
+    row[u] = static_cast<int>(unit / kbs), kb[u] = static_cast<int>(unit % kbs);
+    raw[u] = make_uint4(0, 0, 0, 0);
+    if (in_range && row[u] < R)
+      raw[u] = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row[u]) * ldx + kb[u] * 128 + l16 * 8);
+  }
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+    float v[8];
+    float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       v[2 * i] = bf16_lo(w[i]);
       v[2 * i + 1] = bf16_hi(w[i]);
       amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
     }
-  }
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  // smallest power of two >= amax / 448: biased exponent of s, plus one when s is not itself a power of two
-  const uint32_t bits = __float_as_uint(amax * (1.0f / 448.0f));
-  uint32_t eb = (bits >> 23) + ((bits & 0x7fffffu) ? 1u : 0u);
-  eb = amax > 0.0f ? min(max(eb, 1u), 253u) : 127u;
-  if (row < R) {
-    const float inv = __uint_as_float((254u - eb) << 23);
-    uint32_t lo = 0, hi = 0;
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // smallest power of two >= amax / 448: biased exponent of s, plus one when s is not itself a power of two
+    const uint32_t bits = __float_as_uint(amax * (1.0f / 448.0f));
+    uint32_t eb = (bits >> 23) + ((bits & 0x7fffffu) ? 1u : 0u);
+    eb = amax > 0.0f ? min(max(eb, 1u), 253u) : 127u;
+    const bool live = in_range && row[u] < R;
+    if (live) {
+      const float inv = __uint_as_float((254u - eb) << 23);
+      uint32_t lo = 0, hi = 0;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      lo |= static_cast<uint32_t>(mx_to_e4m3(v[e] * inv)) << (8 * e);
-      hi |= static_cast<uint32_t>(mx_to_e4m3(v[4 + e] * inv)) << (8 * e);
+      for (int e = 0; e < 4; ++e) {
+        lo |= static_cast<uint32_t>(mx_to_e4m3(v[e] * inv)) << (8 * e);
+        hi |= static_cast<uint32_t>(mx_to_e4m3(v[4 + e] * inv)) << (8 * e);
+      }
+      *reinterpret_cast<uint2*>(xq + static_cast<long long>(row[u]) * K + kb[u] * 128 + l16 * 8) = make_uint2(lo, hi);
     }
-    *reinterpret_cast<uint2*>(xq + static_cast<long long>(row) * K + kb * 128 + l16 * 8) = make_uint2(lo, hi);
-  }
-  // the four scale bytes of this (row, K block) sit in lanes 0, 4, 8, 12 of the half-warp
-  const int base = threadIdx.x & 16;
-  const uint32_t b0 = __shfl_sync(0xffffffffu, eb, base), b1 = __shfl_sync(0xffffffffu, eb, base + 4);
-  const uint32_t b2 = __shfl_sync(0xffffffffu, eb, base + 8), b3 = __shfl_sync(0xffffffffu, eb, base + 12);
-  if (l16 == 0) {
-    const int tile = row / tile_rows, rt = row % tile_rows;
-    const long long atom = (static_cast<long long>(tile) * kbs + kb) * atoms_per_tile + rt / 128;
-    const int r = rt % 128;
-    *reinterpret_cast<uint32_t*>(sf + atom * 512 + (r % 32) * 16 + (r / 32) * 4) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    // the four scale bytes of this (row, K block) sit in lanes 0, 4, 8, 12 of the half-warp
+    const uint32_t b0 = __shfl_sync(0xffffffffu, eb, base), b1 = __shfl_sync(0xffffffffu, eb, base + 4);
+    const uint32_t b2 = __shfl_sync(0xffffffffu, eb, base + 8), b3 = __shfl_sync(0xffffffffu, eb, base + 12);
+    if (in_range && l16 == 0) {
+      const int tile = row[u] / tile_rows, rt = row[u] % tile_rows;
+      const long long atom = (static_cast<long long>(tile) * kbs + kb[u]) * atoms_per_tile + rt / 128;
+      const int r = rt % 128;
+      *reinterpret_cast<uint32_t*>(sf + atom * 512 + (r % 32) * 16 + (r / 32) * 4) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    }
   }
 }
 
@@ -392,7 +404,7 @@ const char* quantize_mxfp8(const __nv_bfloat16* x, long long ldx, uint8_t* xq, u
   const int tiles = (R + tile_rows - 1) / tile_rows, atoms = (tile_rows + 127) / 128;
   const int R_pad = tiles * tile_rows;
   const long long units = static_cast<long long>(R_pad) * (K / 128);
-  quantize_mx_kernel<<<static_cast<unsigned>((units + 15) / 16), 256, 0, s>>>(x, ldx, xq, sf, R, R_pad, K, tile_rows, atoms);
+  quantize_mx_kernel<<<static_cast<unsigned>((units + 31) / 32), 256, 0, s>>>(x, ldx, xq, sf, R, R_pad, K, tile_rows, atoms);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

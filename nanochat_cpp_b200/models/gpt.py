@@ -36,10 +36,12 @@ from .params import ParamStore, init_weights
 
 class GPT:
     def __init__(self, cfg: Config, device="cpu", dtype: torch.dtype = torch.bfloat16, seed: int = 0,
-                 init: bool = True, head_chunk_rows: int = 11264, allocator=None, fp8: bool = False):
-        """`fp8`: run the forward QKV and MLP up-projection products in block-scaled E4M3 (1x128 activation scales,
-        128x128 weight scales, bf16 out); attention, norms, the projections with fused residuals, the LM head and
-        the whole backward stay in bf16. Call `refresh_fp8()` after every optimizer step."""
+                 init: bool = True, head_chunk_rows: int = 11264, allocator=None, fp8=False):
+        """`fp8`: run the forward QKV and MLP up-projection products in E4M3 with bf16 outputs; attention, norms,
+        the projections with fused residuals, the LM head and the whole backward stay in bf16. "mx" (or True):
+        MXFP8, one power-of-two scale per row and 32 K elements applied inside the MMA. "block": fp32 scales per
+        1x128 activation block and 128x128 weight block, promoted on the CUDA cores. Call `refresh_fp8()` after
+        every optimizer step."""
         cfg.validate()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -68,7 +70,10 @@ class GPT:
         import os as _os2
         self._wgrad_stream = (torch.cuda.Stream(self.device) if self.device.type == "cuda" and
                               _os2.environ.get("NANOCHAT_WGRAD_STREAM", "1") != "0" else None)
+        if fp8 not in (False, None, True, "mx", "block"):
+            raise ValueError(f"fp8 must be False, True, 'mx' or 'block', got {fp8!r}")
         self.fp8 = bool(fp8) and self.device.type == "cuda"
+        self.fp8_mode = ("block" if fp8 == "block" else "mx") if self.fp8 else None
         # bitwise-reproducible embedding gradients (sorted, single-writer sums instead of atomics)
         import os as _os
         self.deterministic_embedding = _os.environ.get("NANOCHAT_DETERMINISTIC", "0") == "1"
@@ -107,12 +112,12 @@ class GPT:
             wqkv = self.params.qkv_view(i)
             fc = self._w(i, "mlp.c_fc")
             for key, w in ((f"qkv{i}", wqkv), (f"fc{i}", fc)):
-                if w is None or w.shape[0] % 128 or w.shape[1] % 128:
+                if w is None or w.shape[1] % 128 or w.shape[0] % (8 if self.fp8_mode == "mx" else 128):
                     continue
                 if key in self._fp8_w:
                     self._fp8_w[key].refresh(w)
                 else:
-                    self._fp8_w[key] = F8.Fp8Weight(w)
+                    self._fp8_w[key] = F8.MxWeight(w) if self.fp8_mode == "mx" else F8.Fp8Weight(w)
 
     # ------------------------------------------------------------------
     def rope(self, seq: int):
@@ -151,10 +156,10 @@ class GPT:
         hq = None
         if self.fp8 and (f"qkv{i}" in self._fp8_w):
             from ..ops import fp8 as F8
-            hq = F8.quantize_rows(h)
+            hq = F8.mx_quantize(h, 128) if self.fp8_mode == "mx" else F8.quantize_rows(h)
         if hq is not None:
             w8 = self._fp8_w[f"qkv{i}"]
-            qkv = F8.fp8_gemm(hq[0], hq[1], w8.q, w8.s)
+            qkv = (F8.mx_gemm if self.fp8_mode == "mx" else F8.fp8_gemm)(hq[0], hq[1], w8.q, w8.s)
             q_pre = qkv[:, : cfg.query_dim]
             k_pre = qkv[:, cfg.query_dim: cfg.query_dim + cfg.kv_dim]
             v = qkv[:, cfg.query_dim + cfg.kv_dim:]
@@ -178,7 +183,16 @@ class GPT:
         h2, rstd2 = ops.rmsnorm_fwd(x_mid)
         if self.fp8 and (f"fc{i}" in self._fp8_w):
             from ..ops import fp8 as F8
-            pre, act = F8.linear_fwd_fp8(h2, self._fp8_w[f"fc{i}"], relu2=True)
+            w8 = self._fp8_w[f"fc{i}"]
+            if self.fp8_mode == "mx" and self.mlp_keep_act:
+                h2q = F8.mx_quantize(h2, 128)
+                act = torch.empty((M, w8.q.shape[0]), dtype=torch.bfloat16, device=h2.device)
+                F8.mx_gemm(h2q[0], h2q[1], w8.q, w8.s, act, act)      # only relu(pre)^2 is stored
+                pre = None
+            elif self.fp8_mode == "mx":
+                pre, act = F8.linear_fwd_mx(h2, w8, relu2=True)
+            else:
+                pre, act = F8.linear_fwd_fp8(h2, w8, relu2=True)
         else:
             if self.mlp_keep_act:
                 pre, act = None, ops.linear_relu2_act_fwd(h2, self._w(i, "mlp.c_fc"))

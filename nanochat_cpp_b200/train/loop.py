@@ -35,7 +35,7 @@ class TrainConfig:
     log: str = ""
     dtype: str = "bf16"
     head_chunk_rows: int = 11264
-    fp8: bool = False
+    fp8: object = False          # False, True / "mx", or "block" (see models.GPT)
     optim: OptimizerConfig = field(default_factory=OptimizerConfig)
     sched: SchedulerConfig = field(default_factory=SchedulerConfig)
 

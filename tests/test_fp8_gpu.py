@@ -53,15 +53,16 @@ def test_fp8_gemm_matches_dequantized_product(M, N, K):
     Kmod.check_status()
 
 
-def test_model_forward_in_fp8_tracks_bf16_and_trains():
+@pytest.mark.parametrize("mode", ["block", "mx"])
+def test_model_forward_in_fp8_tracks_bf16_and_trains(mode):
     from nanochat_cpp_b200.config import Config
     from nanochat_cpp_b200.models import GPT
     from nanochat_cpp_b200.optim import Optimizer
     cfg = Config(num_layers=2, num_heads=2, num_kv_heads=2, hidden_dim=256, seq_len=256, vocab_size=512,
                  padded_vocab_size=512, window_pattern="SL", short_window_override=128)
     a = GPT(cfg, "cuda", torch.bfloat16, seed=3)
-    b = GPT(cfg, "cuda", torch.bfloat16, seed=3, fp8=True)
-    assert len(b._fp8_w) == 4
+    b = GPT(cfg, "cuda", torch.bfloat16, seed=3, fp8=mode)
+    assert len(b._fp8_w) == 4 and b.fp8_mode == mode
     g = torch.Generator(device="cuda").manual_seed(0)
     for m in (a, b):                      # non-zero projections so that the fp8 products matter
         gg = torch.Generator().manual_seed(1)
