@@ -34,13 +34,14 @@ def main():
         mq, ms = fp8.mx_quantize(w[:N].contiguous(), fp8.mx_tile_n(N))
         aq, as_ = fp8.mx_quantize(x, 128)
         t_mx = time_cuda(lambda: fp8.mx_gemm(aq, as_, mq, ms, out))["median_ms"]
+        t_mx1 = time_cuda(lambda: fp8.mx_gemm(aq, as_, mq, ms, out, variant=1))["median_ms"]
         t_mq = time_cuda(lambda: fp8.mx_quantize(x, 128))["median_ms"]
         t_bf16 = time_cuda(lambda: K.gemm(x, w[:N], out=out))["median_ms"]
         t_lib = time_cuda(lambda: torch.matmul(x, w[:N].t(), out=out))["median_ms"]
         flops = 2.0 * M * N * Kd
         print(json.dumps(dict(name=name, m=M, n=N, k=Kd, fp8_ms=round(t_fp8, 4), quantize_ms=round(t_q, 4),
                               bf16_ms=round(t_bf16, 4), cublas_bf16_ms=round(t_lib, 4),
-                              mx_ms=round(t_mx, 4), mx_quantize_ms=round(t_mq, 4),
+                              mx_ms=round(t_mx, 4), mx_single_cta_ms=round(t_mx1, 4), mx_quantize_ms=round(t_mq, 4),
                               mx_tflops=round(flops / t_mx / 1e9, 1), mx_speedup_gemm=round(t_bf16 / t_mx, 3),
                               mx_speedup_with_quantize=round(t_bf16 / (t_mx + t_mq), 3),
                               fp8_tflops=round(flops / t_fp8 / 1e9, 1), bf16_tflops=round(flops / t_bf16 / 1e9, 1),

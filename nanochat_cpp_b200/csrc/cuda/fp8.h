@@ -51,6 +51,7 @@ struct MxGemmArgs {
   long long ldc = 0;
   __nv_bfloat16* C2 = nullptr;   // optional second output relu(C)^2 (same layout); C2 == C keeps only the activation
   int* status = nullptr;
+  int variant = 0;               // 0: CTA pairs (256-row tiles) when M > 128; 1: single CTAs; 2: CTA pairs
 };
 const char* gemm_mxfp8(const MxGemmArgs& args, cudaStream_t stream);
 

@@ -78,7 +78,7 @@ std::vector<Tensor> fp8_mx_quantize(const Tensor& x, int64_t tile_rows) {
 }
 
 void fp8_mx_gemm(const Tensor& aq, const Tensor& sfa, const Tensor& bq, const Tensor& sfb, Tensor& out,
-                 const c10::optional<Tensor>& out2, Tensor status) {
+                 const c10::optional<Tensor>& out2, Tensor status, int64_t variant) {
   const c10::cuda::CUDAGuard g(aq.device());
   TORCH_CHECK(aq.is_contiguous() && bq.is_contiguous() && aq.scalar_type() == torch::kUInt8 &&
                   bq.scalar_type() == torch::kUInt8 && aq.dim() == 2 && bq.dim() == 2 && aq.size(1) == bq.size(1),
@@ -104,6 +104,7 @@ void fp8_mx_gemm(const Tensor& aq, const Tensor& sfa, const Tensor& bq, const Te
     a.C2 = reinterpret_cast<__nv_bfloat16*>(out2->data_ptr());
   }
   a.status = status.data_ptr<int>();
+  a.variant = static_cast<int>(variant);
   const char* err = nc::gemm_mxfp8(a, at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(err == nullptr, err);
 }
@@ -115,6 +116,7 @@ void register_fp8(pybind11::module_& m) {
   m.def("fp8_quantize_blocks", &fp8_quantize_blocks);
   m.def("fp8_gemm", &fp8_gemm);
   m.def("fp8_mx_quantize", &fp8_mx_quantize);
-  m.def("fp8_mx_gemm", &fp8_mx_gemm);
+  m.def("fp8_mx_gemm", &fp8_mx_gemm, pybind11::arg("aq"), pybind11::arg("sfa"), pybind11::arg("bq"), pybind11::arg("sfb"),
+        pybind11::arg("out"), pybind11::arg("out2"), pybind11::arg("status"), pybind11::arg("variant") = 0);
   m.def("fp8_mx_tile_n", [](int64_t n) { return nc::mxfp8_tile_n(static_cast<int>(n)); });
 }

@@ -27,8 +27,9 @@ namespace nc {
 
 namespace {
 
-__device__ __forceinline__ uint8_t mx_to_e4m3(float v) {
-  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+// two values -> two E4M3 bytes (a in bits 0..7, b in bits 8..15), round to nearest even, saturating
+__device__ __forceinline__ uint32_t mx_to_e4m3x2(float a, float b) {
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
 }
 
 // One half-warp per two consecutive (row, 128-wide K block) units: a thread owns 8 consecutive elements of each,
@@ -39,8 +40,8 @@ __global__ void __launch_bounds__(256) quantize_mx_kernel(const __nv_bfloat16* _
                                                           uint8_t* __restrict__ xq, uint8_t* __restrict__ sf, int R,
                                                           int R_pad, int K, int tile_rows, int atoms_per_tile) {
   const int kbs = K / 128;
-  const long long total = static_cast<long long>(R_pad) * kbs;
-  const long long unit0 = ((static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 4) * 2;
+  const uint32_t total = static_cast<uint32_t>(R_pad) * kbs;        // the host checks that this fits 31 bits
+  const uint32_t unit0 = (blockIdx.x * 16u + (threadIdx.x >> 4)) * 2u;
   const int l16 = threadIdx.x & 15;
   const int base = threadIdx.x & 16;
   const bool in_range = unit0 < total;
@@ -48,8 +49,9 @@ __global__ void __launch_bounds__(256) quantize_mx_kernel(const __nv_bfloat16* _
   uint4 raw[2];
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
-    const long long unit = in_range ? unit0 + u : 0;
-    row[u] = static_cast<int>(unit / kbs), kb[u] = static_cast<int>(unit % kbs);
+    const uint32_t unit = in_range ? unit0 + u : 0u;
+    row[u] = static_cast<int>(unit / static_cast<uint32_t>(kbs));
+    kb[u] = static_cast<int>(unit - static_cast<uint32_t>(row[u]) * kbs);
     raw[u] = make_uint4(0, 0, 0, 0);
     if (in_range && row[u] < R)
       raw[u] = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row[u]) * ldx + kb[u] * 128 + l16 * 8);
@@ -74,12 +76,8 @@ __global__ void __launch_bounds__(256) quantize_mx_kernel(const __nv_bfloat16* _
     const bool live = in_range && row[u] < R;
     if (live) {
       const float inv = __uint_as_float((254u - eb) << 23);
-      uint32_t lo = 0, hi = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        lo |= static_cast<uint32_t>(mx_to_e4m3(v[e] * inv)) << (8 * e);
-        hi |= static_cast<uint32_t>(mx_to_e4m3(v[4 + e] * inv)) << (8 * e);
-      }
+      const uint32_t lo = mx_to_e4m3x2(v[0] * inv, v[1] * inv) | (mx_to_e4m3x2(v[2] * inv, v[3] * inv) << 16);
+      const uint32_t hi = mx_to_e4m3x2(v[4] * inv, v[5] * inv) | (mx_to_e4m3x2(v[6] * inv, v[7] * inv) << 16);
       *reinterpret_cast<uint2*>(xq + static_cast<long long>(row[u]) * K + kb[u] * 128 + l16 * 8) = make_uint2(lo, hi);
     }
     // the four scale bytes of this (row, K block) sit in lanes 0, 4, 8, 12 of the half-warp
@@ -168,6 +166,73 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                    smem_u32(dst)),
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
+}
+
+// Epilogue of one 128-row accumulator for one warp: the thread owns row `row0 + lane`; the warp covers the columns
+// [col_first, col_first + 32 * groups) of the tile that starts at output column n0. A group of 32 columns becomes
+// 64 bytes of bf16 per row, goes through a warp-private swizzled tile and leaves as full 64-byte row segments
+// (four lanes per row). `release()` runs once, as soon as the whole accumulator is in registers.
+template <bool RELU2, int MAX_GROUPS, class Release>
+__device__ __forceinline__ void mx_store_tile(const MxParams& p, uint32_t taddr, int row0, int n0, int col_first,
+                                              int groups, uint8_t* stage_buf, int lane, Release release) {
+  const bool row_ok = row0 + lane < p.M;
+  const int rows_valid = min(32, p.M - row0);
+  const int g4 = lane & 3;
+  auto emit = [&](__nv_bfloat16* base, const uint4 (&v)[4], int c0) {
+    if (row_ok) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v[j];
+    }
+    __syncwarp();
+    const bool col_ok = c0 + g4 * 8 < p.N;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int rr = it * 8 + (lane >> 2);
+      if (col_ok && rr < rows_valid)
+        *reinterpret_cast<uint4*>(base + static_cast<long long>(row0 + rr) * p.ldc + c0 + g4 * 8) =
+            *reinterpret_cast<const uint4*>(stage_buf + rr * 64 + ((g4 ^ ((rr >> 1) & 3)) << 4));
+    }
+    __syncwarp();
+  };
+  uint32_t r[2][32];
+  tmem_ld_32x32(taddr + col_first, r[0]);
+#pragma unroll
+  for (int g = 0; g < MAX_GROUPS; ++g) {
+    if (g >= groups) break;
+    tmem_ld_wait();
+    if (g + 1 < groups) {
+      tmem_ld_32x32(taddr + col_first + (g + 1) * 32, r[(g + 1) & 1]);
+    } else {
+      tc_fence_before();
+      __syncwarp();
+      release();
+    }
+    const int c0 = n0 + col_first + g * 32;
+    if (c0 >= p.N) continue;
+    const uint32_t(&acc)[32] = r[g & 1];
+    uint4 outs[4], acts[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t* a8 = acc + j * 8;
+      outs[j].x = pack_bf16(__uint_as_float(a8[0]), __uint_as_float(a8[1]));
+      outs[j].y = pack_bf16(__uint_as_float(a8[2]), __uint_as_float(a8[3]));
+      outs[j].z = pack_bf16(__uint_as_float(a8[4]), __uint_as_float(a8[5]));
+      outs[j].w = pack_bf16(__uint_as_float(a8[6]), __uint_as_float(a8[7]));
+      if (RELU2) {
+        const uint32_t ow[4] = {outs[j].x, outs[j].y, outs[j].z, outs[j].w};
+        uint32_t aw[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = fmaxf(bf16_lo(ow[e]), 0.0f), hi = fmaxf(bf16_hi(ow[e]), 0.0f);
+          aw[e] = pack_bf16(lo * lo, hi * hi);
+        }
+        acts[j] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+      }
+    }
+    if (!RELU2 || p.C != p.C2) emit(p.C, outs, c0);
+    if (RELU2) emit(p.C2, acts, c0);
+  }
 }
 
 template <int BN, bool RELU2>
@@ -288,77 +353,19 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     const int q = warp & 3, half = (warp - 2) >> 2;
     const int col_first = half ? Cfg::H0 : 0;
-    constexpr int MAX_GROUPS = Cfg::H0 / 32;
     const int groups = (half ? BN - Cfg::H0 : Cfg::H0) / 32;
     uint8_t* stage_buf = smem + Cfg::EPI_OFF + (warp - 2) * kEpiStageBytes;
-    const int g4 = lane & 3;
     int buf = 0;
     uint32_t aphase = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
       const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
-      const int row0 = m_blk * BM + q * 32;
-      const bool row_ok = row0 + lane < p.M;
-      const int rows_valid = min(32, p.M - row0);
       if (!mbar_wait(&acc_full[buf], aphase, abort_flag, p.status, kErrWaitTmemFull)) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + buf * BN + col_first + (static_cast<uint32_t>(q * 32) << 16);
-      // The thread owns one accumulator row. A group of 32 columns becomes 64 bytes of bf16, goes through a
-      // warp-private swizzled tile and leaves as full 64-byte row segments (four lanes per row).
-      auto emit = [&](__nv_bfloat16* base, const uint4 (&v)[4], int c0) {
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v[j];
-        }
-        __syncwarp();
-        const bool col_ok = c0 + g4 * 8 < p.N;
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int rr = it * 8 + (lane >> 2);
-          if (col_ok && rr < rows_valid)
-            *reinterpret_cast<uint4*>(base + static_cast<long long>(row0 + rr) * p.ldc + c0 + g4 * 8) =
-                *reinterpret_cast<const uint4*>(stage_buf + rr * 64 + ((g4 ^ ((rr >> 1) & 3)) << 4));
-        }
-        __syncwarp();
-      };
-      uint32_t r[2][32];
-      tmem_ld_32x32(taddr, r[0]);
-#pragma unroll
-      for (int g = 0; g < MAX_GROUPS; ++g) {
-        if (g >= groups) break;
-        tmem_ld_wait();
-        if (g + 1 < groups) {
-          tmem_ld_32x32(taddr + (g + 1) * 32, r[(g + 1) & 1]);
-        } else {   // everything of this accumulator is in registers: hand it back to the MMA warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        }
-        const int c0 = n_blk * BN + col_first + g * 32;
-        if (c0 >= p.N) continue;
-        const uint32_t(&acc)[32] = r[g & 1];
-        uint4 outs[4], acts[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t* a8 = acc + j * 8;
-          outs[j].x = pack_bf16(__uint_as_float(a8[0]), __uint_as_float(a8[1]));
-          outs[j].y = pack_bf16(__uint_as_float(a8[2]), __uint_as_float(a8[3]));
-          outs[j].z = pack_bf16(__uint_as_float(a8[4]), __uint_as_float(a8[5]));
-          outs[j].w = pack_bf16(__uint_as_float(a8[6]), __uint_as_float(a8[7]));
-          if (RELU2) {
-            const uint32_t ow[4] = {outs[j].x, outs[j].y, outs[j].z, outs[j].w};
-            uint32_t aw[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float lo = fmaxf(bf16_lo(ow[e]), 0.0f), hi = fmaxf(bf16_hi(ow[e]), 0.0f);
-              aw[e] = pack_bf16(lo * lo, hi * hi);
-            }
-            acts[j] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
-          }
-        }
-        if (!RELU2 || p.C != p.C2) emit(p.C, outs, c0);
-        if (RELU2) emit(p.C2, acts, c0);
-      }
+      uint64_t* done = &acc_empty[buf];
+      mx_store_tile<RELU2, Cfg::H0 / 32>(p, tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16),
+                                         m_blk * BM + q * 32, n_blk * BN, col_first, groups, stage_buf, lane, [&] {
+                                           if (lane == 0) mbar_arrive(done);   // the MMA warp may refill this buffer
+                                         });
       if (++buf == 2) {
         buf = 0;
         aphase ^= 1;
@@ -372,6 +379,230 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CTA pairs (cta_group::2): two CTAs of a cluster compute one 256 x BN tile. Each holds its 128 rows of A, its half
+// of the B tile (BN / 2 rows), the scale atom of its A rows and the scale atoms of ALL BN columns; the leader issues
+// tcgen05.cp and tcgen05.mma for both. Per output element the pair reads (128 + BN / 2) operand rows from L2
+// instead of (128 + BN): the single-CTA kernel is bound by L2 bandwidth at the fp8 rate, this one is not.
+template <int BN>
+struct MxPairCfg {
+  static constexpr int B_BYTES = (BN / 2) * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static_assert(STAGE_BYTES % 1024 == 0, "SWIZZLE_128B tiles start on 1024-byte boundaries");
+  static constexpr int STAGES = 6;
+  static constexpr int H0 = ((BN / 32 + 1) / 2) * 32;
+  static constexpr int SF_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
+  static constexpr int EPI_OFF = BAR_OFF + 256;
+  static constexpr int SMEM_BYTES = EPI_OFF + EPI_WARPS * kEpiStageBytes + 1024;
+  static constexpr int SF_COL0 = 2 * BN;
+};
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* tmap, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void mma_mxf8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// In both CTAs of the pair: 32 rows x 16 bytes of the CTA's own shared memory -> 4 columns of its own TMEM.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+template <int BN, bool RELU2>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                       const MxParams p) {   // p.m_blocks counts 256-row tiles
+  using Cfg = MxPairCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sf_smem = smem + Cfg::SF_OFF;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();   // 0 = leader
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int total_units = p.m_blocks * p.n_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);    // the leader's arrive.expect_tx; the bytes of both CTAs complete on it
+      mbar_init(&empty_bar[s], 1);   // one commit, delivered to both CTAs
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);   // the epilogue warps of both CTAs (used in the leader only)
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmSFA);
+    tma_prefetch_desc(&tmSFB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // barrier initialisation of both CTAs is visible before any remote arrive or copy
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = pair_id; unit < total_units && ok; unit += num_pairs) {
+        const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
+        const int m0 = m_blk * (2 * BM) + static_cast<int>(rank) * BM;
+        const int n0 = n_blk * BN + static_cast<int>(rank) * (BN / 2);
+        // rows of 256 bytes in the scale arrays: an atom is two rows
+        const int sfa_row0 = (m_blk * 2 + static_cast<int>(rank)) * p.k_blocks * 2;
+        const int sfb_row0 = n_blk * p.k_blocks * 4;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrWaitEmpty)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* ss = sf_smem + stage * SF_BYTES;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * (STAGE_BYTES + SF_BYTES));
+          const uint32_t bar = mapa_u32(&full_bar[stage], 0);
+          tma_load_2d_pair(sa, &tmA, bar, kb * BK, m0);
+          tma_load_2d_pair(sa + A_BYTES, &tmB, bar, kb * BK, n0);
+          tma_load_2d_pair(ss, &tmSFA, bar, 0, sfa_row0 + kb * 2);
+          tma_load_2d_pair(ss + SFA_BYTES, &tmSFB, bar, 0, sfb_row0 + kb * 4);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {   // give the copies in flight time to land before the CTA's shared memory goes away
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_mx_e4m3(2 * BM, BN);
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
+      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem) + A_BYTES, 16, 1024);
+      int stage = 0, buf = 0, slot = 0;
+      uint32_t phase = 0, aphase = 0;
+      bool ok = true;
+      for (int unit = pair_id; unit < total_units && ok; unit += num_pairs) {
+        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, abort_flag, p.status, kErrWaitTmemEmpty)) break;
+        tc_fence_after();
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrWaitFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t ss = smem_u32(sf_smem + stage * SF_BYTES);
+          const uint32_t tsfa = tmem_base + Cfg::SF_COL0 + slot * SF_SLOT_COLS, tsfb = tsfa + 4;
+          tmem_cp_32x128b_warpx4_pair(tsfa, make_sf_desc(ss));
+          tmem_cp_32x128b_warpx4_pair(tsfb, make_sf_desc(ss + SFA_BYTES));
+          tmem_cp_32x128b_warpx4_pair(tsfb + 4, make_sf_desc(ss + SFA_BYTES + 512));
+          const uint64_t da = a_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
+          const uint64_t db = b_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            mma_mxf8_ss_pair(tmem_base + buf * BN, da + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
+                             with_sf_id(idesc, k), tsfa, tsfb, (kb | k) ? 1u : 0u);
+          mma_commit_pair(&empty_bar[stage], 3);   // frees the stage in both CTAs
+          if (kb == p.k_blocks - 1) mma_commit_pair(&acc_full[buf], 3);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+          slot = (slot + 1) & (SF_SLOTS - 1);
+        }
+        if (++buf == 2) {
+          buf = 0;
+          aphase ^= 1;
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    const int col_first = half ? Cfg::H0 : 0;
+    const int groups = (half ? BN - Cfg::H0 : Cfg::H0) / 32;
+    uint8_t* stage_buf = smem + Cfg::EPI_OFF + (warp - 2) * kEpiStageBytes;
+    const uint32_t leader_empty[2] = {mapa_u32(&acc_empty[0], 0), mapa_u32(&acc_empty[1], 0)};
+    int buf = 0;
+    uint32_t aphase = 0;
+    for (int unit = pair_id; unit < total_units; unit += num_pairs) {
+      const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
+      if (!mbar_wait(&acc_full[buf], aphase, abort_flag, p.status, kErrWaitTmemFull)) break;
+      tc_fence_after();
+      const uint32_t done = leader_empty[buf];
+      mx_store_tile<RELU2, Cfg::H0 / 32>(p, tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16),
+                                         m_blk * (2 * BM) + static_cast<int>(rank) * BM + q * 32, n_blk * BN, col_first,
+                                         groups, stage_buf, lane, [&] {
+                                           if (lane == 0) mbar_arrive_cluster(done);
+                                         });
+      if (++buf == 2) {
+        buf = 0;
+        aphase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA frees tensor memory or retires while the other may still use the pair
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, bool RELU2>
+cudaError_t launch_mx_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                           const MxParams& p, int pairs, cudaStream_t stream) {
+  auto kernel = gemm_mxfp8_pair_kernel<BN, RELU2>;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxPairCfg<BN>::SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = MxPairCfg<BN>::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, ta, tb, tsa, tsb, p);
 }
 
 template <int BN, bool RELU2>
@@ -404,6 +635,7 @@ const char* quantize_mxfp8(const __nv_bfloat16* x, long long ldx, uint8_t* xq, u
   const int tiles = (R + tile_rows - 1) / tile_rows, atoms = (tile_rows + 127) / 128;
   const int R_pad = tiles * tile_rows;
   const long long units = static_cast<long long>(R_pad) * (K / 128);
+  if (units >= (1ll << 31)) return "quantize_mxfp8: more than 2^31 row blocks";
   quantize_mx_kernel<<<static_cast<unsigned>((units + 31) / 32), 256, 0, s>>>(x, ldx, xq, sf, R, R_pad, K, tile_rows, atoms);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
@@ -417,24 +649,44 @@ const char* gemm_mxfp8(const MxGemmArgs& a, cudaStream_t stream) {
        reinterpret_cast<uintptr_t>(a.sfb) | reinterpret_cast<uintptr_t>(a.C) | reinterpret_cast<uintptr_t>(a.C2)) & 15)
     return "gemm_mxfp8: misaligned operand";
   const int bn = mxfp8_tile_n(a.N);
-  CUtensorMap ta, tb;
-  if (!make_tmap_u8_2d(&ta, a.A, a.K, a.M, a.K, BK, BM) || !make_tmap_u8_2d(&tb, a.B, a.K, a.N, a.K, BK, bn))
-    return "gemm_mxfp8: cuTensorMapEncodeTiled failed";
+  const bool pair = a.variant == 2 || (a.variant == 0 && a.M > BM);
   MxParams p;
   p.M = a.M, p.N = a.N, p.K = a.K;
-  p.m_blocks = (a.M + BM - 1) / BM, p.n_blocks = (a.N + bn - 1) / bn, p.k_blocks = a.K / BK;
+  p.n_blocks = (a.N + bn - 1) / bn, p.k_blocks = a.K / BK;
   p.sfa = a.sfa, p.sfb = a.sfb;
   p.C = a.C, p.C2 = a.C2, p.ldc = a.ldc, p.status = a.status;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int units = p.m_blocks * p.n_blocks;
-  const int grid = units < sms ? units : sms;
+  CUtensorMap ta, tb;
   cudaError_t e;
-  if (bn == 192)
-    e = a.C2 ? launch_mx<192, true>(ta, tb, p, grid, stream) : launch_mx<192, false>(ta, tb, p, grid, stream);
-  else
-    e = a.C2 ? launch_mx<224, true>(ta, tb, p, grid, stream) : launch_mx<224, false>(ta, tb, p, grid, stream);
+  if (pair) {
+    CUtensorMap tsa, tsb;
+    const long long rows_a = mxfp8_scale_bytes(a.M, a.K, BM) / 256, rows_b = mxfp8_scale_bytes(a.N, a.K, bn) / 256;
+    if (!make_tmap_u8_2d(&ta, a.A, a.K, a.M, a.K, BK, BM) || !make_tmap_u8_2d(&tb, a.B, a.K, a.N, a.K, BK, bn / 2) ||
+        !make_tmap_u8_2d_plain(&tsa, a.sfa, 256, rows_a, 256, 256, 2) ||
+        !make_tmap_u8_2d_plain(&tsb, a.sfb, 256, rows_b, 256, 256, 4))
+      return "gemm_mxfp8: cuTensorMapEncodeTiled failed";
+    p.m_blocks = (a.M + 2 * BM - 1) / (2 * BM);
+    const int units = p.m_blocks * p.n_blocks;
+    const int pairs = units < sms / 2 ? units : sms / 2;
+    if (bn == 192)
+      e = a.C2 ? launch_mx_pair<192, true>(ta, tb, tsa, tsb, p, pairs, stream)
+               : launch_mx_pair<192, false>(ta, tb, tsa, tsb, p, pairs, stream);
+    else
+      e = a.C2 ? launch_mx_pair<224, true>(ta, tb, tsa, tsb, p, pairs, stream)
+               : launch_mx_pair<224, false>(ta, tb, tsa, tsb, p, pairs, stream);
+  } else {
+    if (!make_tmap_u8_2d(&ta, a.A, a.K, a.M, a.K, BK, BM) || !make_tmap_u8_2d(&tb, a.B, a.K, a.N, a.K, BK, bn))
+      return "gemm_mxfp8: cuTensorMapEncodeTiled failed";
+    p.m_blocks = (a.M + BM - 1) / BM;
+    const int units = p.m_blocks * p.n_blocks;
+    const int grid = units < sms ? units : sms;
+    if (bn == 192)
+      e = a.C2 ? launch_mx<192, true>(ta, tb, p, grid, stream) : launch_mx<192, false>(ta, tb, p, grid, stream);
+    else
+      e = a.C2 ? launch_mx<224, true>(ta, tb, p, grid, stream) : launch_mx<224, false>(ta, tb, p, grid, stream);
+  }
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 

@@ -45,13 +45,14 @@ struct KeyHash {
 };
 
 bool encode_cached(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, int rank, const void* ptr,
-                   const long long* dims, const long long* strides, const int* box) {
+                   const long long* dims, const long long* strides, const int* box,
+                   CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   static std::mutex mu;
   static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
   Key key;
   std::memset(&key, 0, sizeof(key));
   key.v[0] = reinterpret_cast<long long>(ptr);
-  key.v[1] = static_cast<long long>(dt) * 16 + rank;
+  key.v[1] = static_cast<long long>(dt) * 16 + rank + static_cast<long long>(swizzle) * 4096;
   for (int i = 0; i < rank; ++i) {
     key.v[2 + i] = dims[i];
     key.v[10 + i] = box[i];
@@ -77,7 +78,7 @@ bool encode_cached(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, int
   }
   for (int i = 0; i < rank - 1; ++i) s[i] = static_cast<cuuint64_t>(strides[i]) * elem_bytes;
   const CUresult r = encode(out, dt, rank, const_cast<void*>(ptr), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   std::lock_guard<std::mutex> lock(mu);
@@ -106,6 +107,15 @@ bool make_tmap_u8_2d(CUtensorMap* out, const void* ptr, long long d0, long long 
   const long long strides[1] = {s1};
   const int box[2] = {box0, box1};
   return encode_cached(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 2, ptr, dims, strides, box);
+}
+
+
+bool make_tmap_u8_2d_plain(CUtensorMap* out, const void* ptr, long long d0, long long d1, long long s1, int box0,
+                           int box1) {
+  const long long dims[2] = {d0, d1};
+  const long long strides[1] = {s1};
+  const int box[2] = {box0, box1};
+  return encode_cached(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 }  // namespace nc

@@ -13,5 +13,8 @@ bool make_tmap_bf16_4d(CUtensorMap* out, const void* ptr, const long long dims[4
                        const int box[4]);
 // 2-D map of 1-byte elements (fp8 operands): {d0 contiguous, d1}, row stride s1 bytes.
 bool make_tmap_u8_2d(CUtensorMap* out, const void* ptr, long long d0, long long d1, long long s1, int box0, int box1);
+// the same without shared-memory swizzling: box rows land back to back (box0 <= 256 bytes)
+bool make_tmap_u8_2d_plain(CUtensorMap* out, const void* ptr, long long d0, long long d1, long long s1, int box0,
+                           int box1);
 
 }  // namespace nc

@@ -148,13 +148,15 @@ def mx_quantize(x: torch.Tensor, tile_rows: int = 128):
     return q, sf
 
 
-def mx_gemm(xq, sfx, wq, sfw, out: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None):
+def mx_gemm(xq, sfx, wq, sfw, out: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None,
+            variant: int = 0):
     """bf16 [M, N] = xq [M, K] x wq [N, K]^T with both operands' scales applied by the MMA; `out2` receives
-    relu(out)^2 (pass out2 = out to keep only the activation)."""
+    relu(out)^2 (pass out2 = out to keep only the activation). variant: 0 = CTA pairs computing 256-row tiles
+    when M > 128, 1 = one CTA per 128-row tile, 2 = CTA pairs."""
     from . import cuda as K
     if out is None:
         out = torch.empty((xq.shape[0], wq.shape[0]), dtype=torch.bfloat16, device=xq.device)
-    K._C.fp8_mx_gemm(xq, sfx, wq, sfw, out, out2, K._C.status_tensor(xq.device.index))
+    K._C.fp8_mx_gemm(xq, sfx, wq, sfw, out, out2, K._C.status_tensor(xq.device.index), variant)
     return out
 
 

@@ -107,7 +107,8 @@ def test_mx_quantizer_matches_definition_bit_for_bit():
 
 @pytest.mark.parametrize("M,N,K", [(128, 192, 128), (128, 224, 128), (300, 640, 512), (1024, 1280, 1280),
                                    (257, 136, 384), (2048, 3840, 1280), (515, 5120, 256)])
-def test_mx_gemm_matches_dequantized_product(M, N, K):
+@pytest.mark.parametrize("variant", [1, 2])          # one CTA per 128-row tile; CTA pairs on 256-row tiles
+def test_mx_gemm_matches_dequantized_product(M, N, K, variant):
     from nanochat_cpp_b200.ops import cuda as Kmod
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
@@ -116,7 +117,7 @@ def test_mx_gemm_matches_dequantized_product(M, N, K):
     w[N // 3:] *= 0.01                            # and along N
     xq, sx = fp8.mx_quantize(x, 128)
     wq, sw = fp8.mx_quantize(w, fp8.mx_tile_n(N))
-    out = fp8.mx_gemm(xq, sx, wq, sw)
+    out = fp8.mx_gemm(xq, sx, wq, sw, variant=variant)
     xd = fp8.ref_mx_dequantize(*fp8.ref_mx_quantize(x))
     wd = fp8.ref_mx_dequantize(*fp8.ref_mx_quantize(w))
     want = xd @ wd.t()
@@ -124,9 +125,9 @@ def test_mx_gemm_matches_dequantized_product(M, N, K):
     exact = x.float() @ w.float().t()
     assert (out.float() - exact).abs().max() <= 8e-2 * exact.abs().max()
     pre, act = torch.empty_like(out), torch.empty_like(out)
-    fp8.mx_gemm(xq, sx, wq, sw, pre, act)
+    fp8.mx_gemm(xq, sx, wq, sw, pre, act, variant=variant)
     assert torch.equal(pre, out) and torch.equal(act, torch.relu(out.float()).square().to(torch.bfloat16))
     only_act = torch.empty_like(out)
-    fp8.mx_gemm(xq, sx, wq, sw, only_act, only_act)
+    fp8.mx_gemm(xq, sx, wq, sw, only_act, only_act, variant=variant)
     assert torch.equal(only_act, act)
     Kmod.check_status()
