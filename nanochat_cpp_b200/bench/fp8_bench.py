@@ -1,7 +1,9 @@
 """Block-scaled fp8 GEMMs (fp32 scales with CUDA-core promotion, and MXFP8 with the scales inside the MMA) against
 this package's bf16 GEMM and cuBLAS bf16 on the d26 / d20 linear shapes.
 
-    python -m nanochat_cpp_b200.bench.fp8_bench
+    python -m nanochat_cpp_b200.bench.fp8_bench [--only d20.qkv] [--rows 16384] [--mx-only]
+
+`--only`, `--rows` and `--mx-only` cut the run down to a few launches of one kernel on a small case (for a profiler).
 
 Times (CUDA events, 3 warm-ups, L2 flushed between iterations) the GEMM alone and the GEMM plus the activation
 quantization that a forward pass needs (weights are quantized once per optimizer step, not per call).
@@ -21,7 +23,27 @@ SHAPES = [("d26.qkv", 32768, 4992, 1664), ("d26.fc", 32768, 6656, 1664), ("d26.m
 
 
 def main():
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, help="one shape name")
+    ap.add_argument("--rows", type=int, default=0, help="override M")
+    ap.add_argument("--mx-only", action="store_true", help="three launches of the MXFP8 GEMM, nothing else timed")
+    args = ap.parse_args()
     for name, M, N, Kd in SHAPES:
+        if args.only and name != args.only:
+            continue
+        M = args.rows or M
+        if args.mx_only:
+            x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
+            w = (torch.randn(N, Kd, device="cuda") * 0.02).to(torch.bfloat16)
+            mq, ms = fp8.mx_quantize(w, fp8.mx_tile_n(N))
+            aq, as_ = fp8.mx_quantize(x, 128)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            for _ in range(3):
+                fp8.mx_gemm(aq, as_, mq, ms, out)
+            torch.cuda.synchronize()
+            print(json.dumps(dict(name=name, m=M, n=N, k=Kd, launches=3)))
+            continue
         Np = (N + 127) // 128 * 128
         x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
         w = (torch.randn(Np, Kd, device="cuda") * 0.02).to(torch.bfloat16)

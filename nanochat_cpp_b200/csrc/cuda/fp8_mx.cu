@@ -126,7 +126,20 @@ struct MxParams {
   __nv_bfloat16* C2;
   long long ldc;
   int* status;
+  int group_m;
 };
+
+// Tile order: groups of `group_m` row tiles sweep all column tiles before the next group starts (rows fastest inside
+// a group), so the CTAs running at one time share a few A row tiles and B column tiles that stay in L2, and every
+// operand is read from DRAM about once. (With rows fastest over the whole matrix, A is re-read once per column tile.)
+__device__ __forceinline__ void mx_decode_unit(const MxParams& p, int unit, int& m_blk, int& n_blk) {
+  const int per_group = p.group_m * p.n_blocks;
+  const int g = unit / per_group, r = unit - g * per_group;
+  const int m_first = g * p.group_m;
+  const int gm = min(p.group_m, p.m_blocks - m_first);
+  n_blk = r / gm;
+  m_blk = m_first + (r - n_blk * gm);
+}
 
 // kind::mxf8f6f4 with E4M3 operands (format 0), UE8M0 scales, both operands K-major. The scale ids (which of the
 // four bytes of a TMEM scale column this K = 32 step uses) are OR-ed in per instruction.
@@ -152,6 +165,13 @@ __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t 
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
+// Ask L2 for a tile some time before a TMA load brings it into shared memory (no shared memory is held meanwhile).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(tmap)),
+               "r"(c0), "r"(c1)
+               : "memory");
+}
+
 // Unswizzled K-major descriptor of one scale atom: 8-row groups of 16-byte rows, 128 bytes apart.
 __device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
   uint64_t d = 0;
@@ -166,6 +186,91 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                    smem_u32(dst)),
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* tmap, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void mma_mxf8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// In both CTAs of the pair: 32 rows x 16 bytes of the CTA's own shared memory -> 4 columns of its own TMEM.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// The MMA-issuing thread's loop over this CTA's (or pair's) tiles and K blocks. The scale atoms of K block i + 1
+// are copied into tensor memory (their own slot of columns) BEFORE the MMAs of K block i are issued, so the copy's
+// latency hides behind those MMAs instead of sitting between two K blocks.
+template <bool PAIR, int BN, int STAGES, int STAGE_BYTES, int SF_COL0>
+__device__ __forceinline__ void mx_mma_loop(const MxParams& p, int my_units, uint8_t* smem, uint8_t* sf_smem,
+                                            uint64_t* full_bar, uint64_t* empty_bar, uint64_t* acc_full,
+                                            uint64_t* acc_empty, uint32_t tmem_base, volatile int* abort_flag) {
+  constexpr uint32_t idesc = make_idesc_mx_e4m3(PAIR ? 2 * BM : BM, BN);
+  const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
+  const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem) + A_BYTES, 16, 1024);
+  const int items = my_units * p.k_blocks;
+  auto copy_scales = [&](int st, uint32_t ph, int sl) -> bool {
+    if (!mbar_wait(&full_bar[st], ph, abort_flag, p.status, kErrWaitFull)) return false;
+    tc_fence_after();
+    const uint32_t ss = smem_u32(sf_smem + st * SF_BYTES);
+    const uint32_t tsfa = tmem_base + SF_COL0 + sl * SF_SLOT_COLS, tsfb = tsfa + 4;
+    if (PAIR) {
+      tmem_cp_32x128b_warpx4_pair(tsfa, make_sf_desc(ss));
+      tmem_cp_32x128b_warpx4_pair(tsfb, make_sf_desc(ss + SFA_BYTES));
+      tmem_cp_32x128b_warpx4_pair(tsfb + 4, make_sf_desc(ss + SFA_BYTES + 512));
+    } else {
+      tmem_cp_32x128b_warpx4(tsfa, make_sf_desc(ss));
+      tmem_cp_32x128b_warpx4(tsfb, make_sf_desc(ss + SFA_BYTES));
+      tmem_cp_32x128b_warpx4(tsfb + 4, make_sf_desc(ss + SFA_BYTES + 512));
+    }
+    return true;
+  };
+  int stage = 0, slot = 0, buf = 0, kb = 0;
+  uint32_t phase = 0, aphase = 0;
+  if (items > 0 && !copy_scales(0, 0, 0)) return;
+  for (int i = 0; i < items; ++i) {
+    int nstage = stage + 1;
+    uint32_t nphase = phase;
+    if (nstage == STAGES) nstage = 0, nphase ^= 1;
+    const int nslot = (slot + 1) & (SF_SLOTS - 1);
+    if (kb == 0) {
+      if (!mbar_wait(&acc_empty[buf], aphase ^ 1, abort_flag, p.status, kErrWaitTmemEmpty)) return;
+      tc_fence_after();
+    }
+    if (i + 1 < items && !copy_scales(nstage, nphase, nslot)) return;
+    const uint32_t tsfa = tmem_base + SF_COL0 + slot * SF_SLOT_COLS, tsfb = tsfa + 4;
+    const uint64_t da = a_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
+    const uint64_t db = b_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
+#pragma unroll
+    for (int k = 0; k < BK / UMMA_K; ++k) {   // 32 one-byte elements = 32 bytes = 2 descriptor units per step
+      if (PAIR)
+        mma_mxf8_ss_pair(tmem_base + buf * BN, da + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
+                         with_sf_id(idesc, k), tsfa, tsfb, (kb | k) ? 1u : 0u);
+      else
+        mma_mxf8_ss(tmem_base + buf * BN, da + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
+                    with_sf_id(idesc, k), tsfa, tsfb, (kb | k) ? 1u : 0u);
+    }
+    if (PAIR) mma_commit_pair(&empty_bar[stage], 3); else mma_commit(&empty_bar[stage]);
+    if (++kb == p.k_blocks) {
+      kb = 0;
+      if (PAIR) mma_commit_pair(&acc_full[buf], 3); else mma_commit(&acc_full[buf]);
+      if (++buf == 2) buf = 0, aphase ^= 1;
+    }
+    stage = nstage, phase = nphase, slot = nslot;
+  }
 }
 
 // Epilogue of one 128-row accumulator for one warp: the thread owns row `row0 + lane`; the warp covers the columns
@@ -283,7 +388,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
-        const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
+        int m_blk, n_blk;
+      mx_decode_unit(p, unit, m_blk, n_blk);
         const uint8_t* sfa = p.sfa + static_cast<long long>(m_blk) * p.k_blocks * SFA_BYTES;
         const uint8_t* sfb = p.sfb + static_cast<long long>(n_blk) * p.k_blocks * SFB_BYTES;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -311,44 +417,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_mx_e4m3(BM, BN);
-      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
-      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem) + A_BYTES, 16, 1024);
-      int stage = 0, buf = 0, slot = 0;
-      uint32_t phase = 0, aphase = 0;
-      bool ok = true;
-      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
-        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, abort_flag, p.status, kErrWaitTmemEmpty)) break;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrWaitFull)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t ss = smem_u32(sf_smem + stage * SF_BYTES);
-          const uint32_t tsfa = tmem_base + Cfg::SF_COL0 + slot * SF_SLOT_COLS, tsfb = tsfa + 4;
-          tmem_cp_32x128b_warpx4(tsfa, make_sf_desc(ss));
-          tmem_cp_32x128b_warpx4(tsfb, make_sf_desc(ss + SFA_BYTES));
-          tmem_cp_32x128b_warpx4(tsfb + 4, make_sf_desc(ss + SFA_BYTES + 512));
-          const uint64_t da = a_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
-          const uint64_t db = b_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)   // 32 one-byte elements = 32 bytes = 2 descriptor units per step
-            mma_mxf8_ss(tmem_base + buf * BN, da + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
-                        with_sf_id(idesc, k), tsfa, tsfb, (kb | k) ? 1u : 0u);
-          mma_commit(&empty_bar[stage]);
-          if (kb == p.k_blocks - 1) mma_commit(&acc_full[buf]);
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-          slot = (slot + 1) & (SF_SLOTS - 1);
-        }
-        if (++buf == 2) {
-          buf = 0;
-          aphase ^= 1;
-        }
-      }
+      const int my_units = blockIdx.x < total_units ? (total_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      mx_mma_loop<false, BN, STAGES, STAGE_BYTES, Cfg::SF_COL0>(p, my_units, smem, sf_smem, full_bar, empty_bar, acc_full,
+                                                                acc_empty, tmem_base, abort_flag);
     }
   } else {
     const int q = warp & 3, half = (warp - 2) >> 2;
@@ -358,7 +429,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int buf = 0;
     uint32_t aphase = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
-      const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
+      int m_blk, n_blk;
+      mx_decode_unit(p, unit, m_blk, n_blk);
       if (!mbar_wait(&acc_full[buf], aphase, abort_flag, p.status, kErrWaitTmemFull)) break;
       tc_fence_after();
       uint64_t* done = &acc_empty[buf];
@@ -399,29 +471,6 @@ struct MxPairCfg {
   static constexpr int SMEM_BYTES = EPI_OFF + EPI_WARPS * kEpiStageBytes + 1024;
   static constexpr int SF_COL0 = 2 * BN;
 };
-
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* tmap, uint32_t bar_cluster_addr, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
-      "[%2];" ::"r"(smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void mma_mxf8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %6, 0;\n"
-      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
-      : "memory");
-}
-// In both CTAs of the pair: 32 rows x 16 bytes of the CTA's own shared memory -> 4 columns of its own TMEM.
-__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
 
 template <int BN, bool RELU2>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -478,12 +527,21 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       for (int unit = pair_id; unit < total_units && ok; unit += num_pairs) {
-        const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
+        int m_blk, n_blk;
+      mx_decode_unit(p, unit, m_blk, n_blk);
         const int m0 = m_blk * (2 * BM) + static_cast<int>(rank) * BM;
         const int n0 = n_blk * BN + static_cast<int>(rank) * (BN / 2);
         // rows of 256 bytes in the scale arrays: an atom is two rows
         const int sfa_row0 = (m_blk * 2 + static_cast<int>(rank)) * p.k_blocks * 2;
         const int sfb_row0 = n_blk * p.k_blocks * 4;
+        const bool has_next = unit + num_pairs < total_units;
+        int m0_next = 0, n0_next = 0;
+        if (has_next) {
+          int mn, nn;
+          mx_decode_unit(p, unit + num_pairs, mn, nn);
+          m0_next = mn * (2 * BM) + static_cast<int>(rank) * BM;
+          n0_next = nn * BN + static_cast<int>(rank) * (BN / 2);
+        }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrWaitEmpty)) {
             ok = false;
@@ -497,6 +555,10 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           tma_load_2d_pair(sa + A_BYTES, &tmB, bar, kb * BK, n0);
           tma_load_2d_pair(ss, &tmSFA, bar, 0, sfa_row0 + kb * 2);
           tma_load_2d_pair(ss + SFA_BYTES, &tmSFB, bar, 0, sfb_row0 + kb * 4);
+          if (has_next) {   // the same K block of the pair's next tile: in L2 one whole tile ahead of its load
+            tma_prefetch_l2_2d(&tmA, kb * BK, m0_next);
+            tma_prefetch_l2_2d(&tmB, kb * BK, n0_next);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -510,45 +572,9 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_mx_e4m3(2 * BM, BN);
-      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
-      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem) + A_BYTES, 16, 1024);
-      int stage = 0, buf = 0, slot = 0;
-      uint32_t phase = 0, aphase = 0;
-      bool ok = true;
-      for (int unit = pair_id; unit < total_units && ok; unit += num_pairs) {
-        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, abort_flag, p.status, kErrWaitTmemEmpty)) break;
-        tc_fence_after();
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrWaitFull)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t ss = smem_u32(sf_smem + stage * SF_BYTES);
-          const uint32_t tsfa = tmem_base + Cfg::SF_COL0 + slot * SF_SLOT_COLS, tsfb = tsfa + 4;
-          tmem_cp_32x128b_warpx4_pair(tsfa, make_sf_desc(ss));
-          tmem_cp_32x128b_warpx4_pair(tsfb, make_sf_desc(ss + SFA_BYTES));
-          tmem_cp_32x128b_warpx4_pair(tsfb + 4, make_sf_desc(ss + SFA_BYTES + 512));
-          const uint64_t da = a_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
-          const uint64_t db = b_desc0 + static_cast<uint64_t>(stage * (STAGE_BYTES >> 4));
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            mma_mxf8_ss_pair(tmem_base + buf * BN, da + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
-                             with_sf_id(idesc, k), tsfa, tsfb, (kb | k) ? 1u : 0u);
-          mma_commit_pair(&empty_bar[stage], 3);   // frees the stage in both CTAs
-          if (kb == p.k_blocks - 1) mma_commit_pair(&acc_full[buf], 3);
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-          slot = (slot + 1) & (SF_SLOTS - 1);
-        }
-        if (++buf == 2) {
-          buf = 0;
-          aphase ^= 1;
-        }
-      }
+      const int my_units = pair_id < total_units ? (total_units - pair_id + num_pairs - 1) / num_pairs : 0;
+      mx_mma_loop<true, BN, STAGES, STAGE_BYTES, Cfg::SF_COL0>(p, my_units, smem, sf_smem, full_bar, empty_bar, acc_full,
+                                                               acc_empty, tmem_base, abort_flag);
     }
   } else {
     const int q = warp & 3, half = (warp - 2) >> 2;
@@ -559,7 +585,8 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     int buf = 0;
     uint32_t aphase = 0;
     for (int unit = pair_id; unit < total_units; unit += num_pairs) {
-      const int m_blk = unit % p.m_blocks, n_blk = unit / p.m_blocks;
+      int m_blk, n_blk;
+      mx_decode_unit(p, unit, m_blk, n_blk);
       if (!mbar_wait(&acc_full[buf], aphase, abort_flag, p.status, kErrWaitTmemFull)) break;
       tc_fence_after();
       const uint32_t done = leader_empty[buf];
@@ -668,6 +695,7 @@ const char* gemm_mxfp8(const MxGemmArgs& a, cudaStream_t stream) {
         !make_tmap_u8_2d_plain(&tsb, a.sfb, 256, rows_b, 256, 256, 4))
       return "gemm_mxfp8: cuTensorMapEncodeTiled failed";
     p.m_blocks = (a.M + 2 * BM - 1) / (2 * BM);
+    p.group_m = 8;
     const int units = p.m_blocks * p.n_blocks;
     const int pairs = units < sms / 2 ? units : sms / 2;
     if (bn == 192)
@@ -680,6 +708,7 @@ const char* gemm_mxfp8(const MxGemmArgs& a, cudaStream_t stream) {
     if (!make_tmap_u8_2d(&ta, a.A, a.K, a.M, a.K, BK, BM) || !make_tmap_u8_2d(&tb, a.B, a.K, a.N, a.K, BK, bn))
       return "gemm_mxfp8: cuTensorMapEncodeTiled failed";
     p.m_blocks = (a.M + BM - 1) / BM;
+    p.group_m = 16;
     const int units = p.m_blocks * p.n_blocks;
     const int grid = units < sms ? units : sms;
     if (bn == 192)
