@@ -43,6 +43,15 @@ def run_hardware_gate(device) -> Tuple[bool, List[Dict]]:
     K.linear_wgrad(dy, x, acc_k)
     ref.linear_wgrad(dy, x, acc_r)
     check("gemm.wgrad", _rel(acc_k, acc_r), 2e-2)
+    # fp8: the quantizer bit for bit, then the block-scaled product on three shapes (ragged M, both tile widths)
+    xq = rn(300, 512) * 4
+    qk_, ek_ = K.quantize_fp8(xq)
+    qr_, er_ = ref.quantize_fp8(xq)
+    check("fp8.quantize.codes", float((qk_.float() != qr_.float()).float().mean()), 0.0)
+    check("fp8.quantize.scales", float((ek_ != er_).float().mean()), 0.0)
+    for m_, n_, k_ in ((512, 640, 384), (257, 3840, 256), (1024, 1280, 1280)):
+        a_, b_ = rn(m_, k_), rn(n_, k_)
+        check(f"fp8.scaled_gemm.{m_}x{n_}x{k_}", _rel(K.gemm_scaled_fp8(a_, b_), ref.gemm_scaled_fp8(a_, b_)), 2e-2)
     # attention forward / backward, GQA + window
     B, T, H, KV, D = 2, 384, 4, 2, 128
     q, k, v, do = rn(B, T, H, D), rn(B, T, KV, D), rn(B, T, KV, D), rn(B, T, H, D)

@@ -122,7 +122,7 @@ _NAMES = [
     "backout_fwd", "backout_bwd", "blend_norm_fwd", "blend_bwd", "qk_prep_fwd", "qk_prep_bwd",
     "attention_fwd", "attention_bwd", "value_gate_fwd", "value_gate_bwd", "smear_fwd", "smear_bwd",
     "embedding_fwd", "embedding_bwd", "embedding_order", "classifier_fwd_bwd", "adamw_update", "muon_update",
-    "grad_norm_and_clip", "kv_append", "paged_decode_attention",
+    "grad_norm_and_clip", "kv_append", "paged_decode_attention", "quantize_fp8", "gemm_scaled_fp8",
 ]
 for _n in _NAMES:
     globals()[_n] = _dispatch(_n)

@@ -119,6 +119,26 @@ def linear_relu2_fwd(x, w):
     return pre, act
 
 
+def quantize_fp8(x):
+    """MXFP8 quantizer kernel; returns the same pair as the definition (the kernel's scale atoms are unpacked)."""
+    from . import fp8 as F8
+    q, sf = F8.mx_quantize(x, 128)
+    return q.view(torch.float8_e4m3fn), F8.mx_scales_from_atoms(sf, x.shape[0], x.shape[1], 128)
+
+
+def gemm_scaled_fp8(x, w, relu2: bool = False):
+    """Quantize both operands to MXFP8 and multiply with tcgen05.mma block scaling (`csrc/cuda/fp8_mx.cu`)."""
+    from . import fp8 as F8
+    xq, sx = F8.mx_quantize(x, 128)
+    wq, sw = F8.mx_quantize(w, F8.mx_tile_n(w.shape[0]))
+    if relu2:
+        y = torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)
+        act = torch.empty_like(y)
+        F8.mx_gemm(xq, sx, wq, sw, y, act)
+        return y, act
+    return F8.mx_gemm(xq, sx, wq, sw)
+
+
 def linear_relu2_act_fwd(x, w):
     """act = relu(x @ w^T)^2 only: the pre-activation is never written (its backward uses sqrt(act))."""
     act = torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)

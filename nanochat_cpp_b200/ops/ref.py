@@ -50,6 +50,24 @@ def linear_relu2_fwd(x, w):
     return pre, act
 
 
+def quantize_fp8(x):
+    """MXFP8 of x [R, K] (K % 32 == 0): (E4M3 values as float8_e4m3fn [R, K], biased power-of-two exponents uint8
+    [R, K/32]); the value of element (r, k) is q[r, k] * 2^(e[r, k // 32] - 127). The seam's QuantizeFp8
+    (reference: include/nanochat/kernels.h:138-175, per-tensor scale there)."""
+    from .fp8 import ref_mx_quantize
+    return ref_mx_quantize(x)
+
+
+def gemm_scaled_fp8(x, w, relu2: bool = False):
+    """y = Q(x) @ Q(w)^T in the compute dtype, Q = MXFP8 quantize-dequantize; with `relu2` returns (y, relu(y)^2).
+    The seam's QuantizeFp8 + GemmScaledFp8 composition (reference: src/ops.cc:551-706, fp8 linear forward)."""
+    from .fp8 import ref_mx_dequantize, ref_mx_quantize
+    y = (ref_mx_dequantize(*ref_mx_quantize(x)) @ ref_mx_dequantize(*ref_mx_quantize(w)).t()).to(x.dtype)
+    if relu2:
+        return y, torch.relu(y.float()).square().to(x.dtype)
+    return y
+
+
 def linear_relu2_act_fwd(x, w):
     """act = relu(pre)^2 with pre = x @ w^T rounded to the compute dtype first (as `linear_relu2_fwd`)."""
     return linear_relu2_fwd(x, w)[1]

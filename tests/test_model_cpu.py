@@ -83,3 +83,21 @@ def test_backward_memory_modes_agree(monkeypatch):
         grads.append((float(loss), m.params.grad.clone()))
     assert grads[0][0] == grads[1][0]
     torch.testing.assert_close(grads[0][1], grads[1][1], rtol=1e-4, atol=1e-6)
+
+
+def test_fp8_seam_operators_on_cpu():
+    """The seam's fp8 entries run their definition on CPU tensors: codes and exponents of the MXFP8 quantizer, and
+    a scaled product that tracks the bf16 product to fp8 accuracy."""
+    import torch
+    from nanochat_cpp_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(48, 128, generator=g).to(torch.bfloat16)
+    w = (torch.randn(40, 128, generator=g) * 0.1).to(torch.bfloat16)
+    q, e = ops.quantize_fp8(x)
+    assert q.dtype == torch.float8_e4m3fn and e.shape == (48, 4) and e.dtype == torch.uint8
+    back = q.float().view(48, 4, 32) * torch.exp2(e.float() - 127).unsqueeze(-1)
+    assert (back.view(48, 128) - x.float()).abs().max() <= 0.0715 * x.float().abs().max()
+    y, act = ops.gemm_scaled_fp8(x, w, relu2=True)
+    exact = x.float() @ w.float().t()
+    assert (y.float() - exact).abs().max() <= 8e-2 * exact.abs().max()
+    assert torch.equal(act, torch.relu(y.float()).square().to(torch.bfloat16))
