@@ -673,6 +673,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     _rl_parsers(sub)
     _perf_parsers(sub)
     _misc_parsers(sub)
+    from . import tools_cli
+    tools_cli.register(sub)
     a = ap.parse_args(argv)
     return int(a.fn(a) or 0)
 

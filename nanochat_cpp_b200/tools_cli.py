@@ -1,0 +1,187 @@
+"""Workflow sub-commands of the command line: build, test, check, devices, doctor, verify, bench, profile, attain.
+
+The reference's `tools/nanochat` front end offers the same verbs around Bazel, a sandbox and a GPU queue
+(python/nanochat_cpp/cli.py: build, test, check, devices, doctor, verify, bench, profile, attain). Here they run in
+the calling process or as one child `python -m ...`: the extension is built by nvcc in-tree, tests are pytest tiers
+(`cpu` = everything not marked gpu, `gpu` = the rest), and benchmarks are the modules under `nanochat_cpp_b200.bench`.
+"""
+from __future__ import annotations
+
+import importlib
+import json
+import os
+import shutil
+import subprocess
+import sys
+from typing import Dict, List
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+BENCHES: Dict[str, str] = {
+    "gemm": "gemm_bench", "attention": "attn_bench", "optimizer": "optim_bench", "rows": "row_bench",
+    "fp8": "fp8_bench", "decode": "decode_bench", "comm": "dp_comm_bench", "cpu": "cpu_config",
+}
+
+
+def cmd_build(a) -> int:
+    """Compile every CUDA source for sm_100a and the host runtime, link them in-tree, import the result."""
+    from . import build as b
+    b.build_all(verbose=not a.quiet)
+    importlib.import_module("nanochat_cpp_b200")
+    print(json.dumps({"extension": b.EXT_PATH, "exists": os.path.exists(b.EXT_PATH)}))
+    return 0 if os.path.exists(b.EXT_PATH) else 1
+
+
+def _pytest(tier: str, extra: List[str]) -> int:
+    marker = {"cpu": "not gpu", "gpu": "gpu"}[tier]
+    cmd = [sys.executable, "-m", "pytest", os.path.join(ROOT, "tests"), "-q", "-m", marker] + extra
+    return subprocess.call(cmd, cwd=ROOT)
+
+
+def cmd_test(a) -> int:
+    """One test tier: `cpu` needs no GPU (multi-process paths use gloo), `gpu` needs one B200."""
+    return _pytest(a.tier, a.rest)
+
+
+def cmd_check(a) -> int:
+    """Build, then the CPU tier, then (when a GPU is present) the hardware gate: what a change must pass."""
+    rc = cmd_build(a)
+    if rc:
+        return rc
+    rc = _pytest("cpu", ["-x"])
+    if rc:
+        return rc
+    import torch
+    return cmd_verify(a) if torch.cuda.is_available() else 0
+
+
+def device_table() -> List[dict]:
+    """CPU entry first, then one entry per visible GPU (name, SMs, memory, compute capability, peer access)."""
+    import torch
+    out = [{"index": -1, "kind": "cpu", "name": "host", "threads": os.cpu_count()}]
+    if torch.cuda.is_available():
+        n = torch.cuda.device_count()
+        for i in range(n):
+            p = torch.cuda.get_device_properties(i)
+            peers = [j for j in range(n) if j != i and torch.cuda.can_device_access_peer(i, j)]
+            out.append({"index": i, "kind": "cuda", "name": p.name, "sms": p.multi_processor_count,
+                        "memory_gib": round(p.total_memory / 2 ** 30, 1), "cc": f"{p.major}.{p.minor}",
+                        "native": (p.major, p.minor) == (10, 0), "peers": peers})
+    return out
+
+
+def cmd_devices(a) -> int:
+    for d in device_table():
+        print(json.dumps(d))
+    return 0
+
+
+def doctor_report() -> dict:
+    """What the framework needs and whether it is there: interpreter, torch, CUDA toolchain, the built extension and
+    host library, collective backends, measured peaks."""
+    import torch
+    from . import build as b
+    rep = {
+        "python": sys.version.split()[0],
+        "torch": torch.__version__,
+        "torch_cuda": torch.version.cuda,
+        "gpu_visible": torch.cuda.is_available(),
+        "nvcc": shutil.which("nvcc") or (os.path.exists("/usr/local/cuda/bin/nvcc") and "/usr/local/cuda/bin/nvcc") or None,
+        "extension_built": os.path.exists(b.EXT_PATH),
+        "host_library_built": os.path.exists(os.path.join(os.path.dirname(b.EXT_PATH), "libnanochat_core.so")),
+        "native_cli_built": os.path.exists(os.path.join(os.path.dirname(b.EXT_PATH), "nanochat_cli")),
+        "nccl": bool(torch.distributed.is_available() and torch.distributed.is_nccl_available()),
+        "gloo": bool(torch.distributed.is_available() and torch.distributed.is_gloo_available()),
+        "measured_peaks": os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")),
+    }
+    if rep["gpu_visible"]:
+        cc = torch.cuda.get_device_capability(0)
+        rep["gpu0"] = torch.cuda.get_device_name(0)
+        rep["gpu0_is_sm100"] = cc == (10, 0)
+    problems = []
+    if not rep["extension_built"]:
+        problems.append("CUDA extension not built: run `build`")
+    if not rep["host_library_built"]:
+        problems.append("host runtime library not built: run `build`")
+    if rep["nvcc"] is None:
+        problems.append("nvcc not found: the extension cannot be rebuilt here")
+    if rep["gpu_visible"] and not rep.get("gpu0_is_sm100", False):
+        problems.append("GPU 0 is not sm_100: the kernels are compiled for sm_100a only")
+    rep["problems"] = problems
+    return rep
+
+
+def cmd_doctor(a) -> int:
+    rep = doctor_report()
+    print(json.dumps(rep, indent=1))
+    return 1 if rep["problems"] and a.strict else 0
+
+
+def cmd_verify(a) -> int:
+    """The start-up correctness gate on GPU `--device` (kernels against the PyTorch definitions)."""
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"ok": False, "error": "no GPU visible"}))
+        return 1
+    from .hwgate import run_hardware_gate
+    ok, report = run_hardware_gate(getattr(a, "device", "cuda:0") or "cuda:0")
+    for r in report:
+        print(json.dumps(r))
+    print(json.dumps({"ok": ok, "checks": len(report)}))
+    return 0 if ok else 1
+
+
+def cmd_bench(a) -> int:
+    """`bench list`, `bench step [bench.py flags]` (the headline training step) or `bench <name> [flags]`."""
+    if a.name == "list":
+        print(json.dumps({"step": "bench.py (d20 training step, tokens/s)",
+                          **{k: f"nanochat_cpp_b200.bench.{v}" for k, v in BENCHES.items()}}, indent=1))
+        return 0
+    if a.name == "step":
+        return subprocess.call([sys.executable, os.path.join(ROOT, "bench.py")] + a.rest, cwd=ROOT)
+    if a.name not in BENCHES:
+        print(f"bench: unknown benchmark {a.name!r}; try `bench list`", file=sys.stderr)
+        return 2
+    return subprocess.call([sys.executable, "-m", f"nanochat_cpp_b200.bench.{BENCHES[a.name]}"] + a.rest, cwd=ROOT)
+
+
+def cmd_profile(a) -> int:
+    """Per-operator device time of one training step (CUDA events around every operator)."""
+    return subprocess.call([sys.executable, "-m", "nanochat_cpp_b200.bench.step_profile"] + a.rest, cwd=ROOT)
+
+
+def cmd_attain(a) -> int:
+    """Measured phase times against the roofline model (fraction of the attainable time per phase)."""
+    return subprocess.call([sys.executable, "-m", "nanochat_cpp_b200.perf.attain"] + a.rest, cwd=ROOT)
+
+
+def register(sub) -> None:
+    import argparse
+    ap = sub.add_parser("build", help="compile the CUDA extension and the host runtime in-tree")
+    ap.add_argument("--quiet", action="store_true")
+    ap.set_defaults(fn=cmd_build)
+    ap = sub.add_parser("test", help="run a test tier")
+    ap.add_argument("tier", choices=["cpu", "gpu"])
+    ap.add_argument("rest", nargs=argparse.REMAINDER, help="extra pytest arguments")
+    ap.set_defaults(fn=cmd_test)
+    ap = sub.add_parser("check", help="build + CPU tier (+ hardware gate when a GPU is present)")
+    ap.add_argument("--quiet", action="store_true")
+    ap.set_defaults(fn=cmd_check)
+    ap = sub.add_parser("devices", help="list the CPU and the visible GPUs")
+    ap.set_defaults(fn=cmd_devices)
+    ap = sub.add_parser("doctor", help="environment report")
+    ap.add_argument("--strict", action="store_true", help="exit 1 when a problem is listed")
+    ap.set_defaults(fn=cmd_doctor)
+    ap = sub.add_parser("verify", help="hardware correctness gate")
+    ap.add_argument("--device", default="cuda:0")
+    ap.set_defaults(fn=cmd_verify)
+    ap = sub.add_parser("bench", help="run a benchmark: list | step | " + " | ".join(BENCHES))
+    ap.add_argument("name")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_bench)
+    ap = sub.add_parser("profile", help="per-operator step profile")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_profile)
+    ap = sub.add_parser("attain", help="attainment report against the roofline model")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_attain)

@@ -82,3 +82,26 @@ def test_rl_worker_pipe_and_tokenizer_training(tmp_path):
     from nanochat_cpp_b200.data.native import Tokenizer
     t = Tokenizer.load(out)
     assert t.decode(t.encode("the lazy fox")) == "the lazy fox"
+
+
+def test_workflow_commands_devices_doctor_bench_list(capsys):
+    """The workflow verbs exist on the command line; `devices` lists the host first, `doctor` reports the build
+    state without failing, `bench list` names every benchmark module and an unknown name is an error."""
+    import importlib
+    import json
+    from nanochat_cpp_b200 import cli, tools_cli
+    assert cli.main(["devices"]) == 0
+    first = json.loads(capsys.readouterr().out.splitlines()[0])
+    assert first["kind"] == "cpu" and first["index"] == -1
+    assert cli.main(["doctor"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["extension_built"] and rep["host_library_built"] and rep["gloo"] and isinstance(rep["problems"], list)
+    assert cli.main(["bench", "list"]) == 0
+    listed = json.loads(capsys.readouterr().out)
+    assert set(tools_cli.BENCHES) | {"step"} == set(listed)
+    for mod in tools_cli.BENCHES.values():
+        assert importlib.util.find_spec(f"nanochat_cpp_b200.bench.{mod}") is not None
+    assert cli.main(["bench", "no-such-benchmark"]) == 2
+    capsys.readouterr()
+    assert cli.main(["verify"]) in (0, 1)          # 1 with a clear message when no GPU is visible
+    assert "ok" in json.loads(capsys.readouterr().out.splitlines()[-1])
