@@ -1,7 +1,7 @@
 """Block-scaled fp8 GEMMs (fp32 scales with CUDA-core promotion, and MXFP8 with the scales inside the MMA) against
 this package's bf16 GEMM and cuBLAS bf16 on the d26 / d20 linear shapes.
 
-    python -m nanochat_cpp_b200.bench.fp8_bench [--only d20.qkv] [--rows 16384] [--mx-only]
+    python -m nanochat_cpp_b200.bench.fp8_bench [--only d20.qkv] [--rows 16384] [--mx-only | --sustained]
 
 `--only`, `--rows` and `--mx-only` cut the run down to a few launches of one kernel on a small case (for a profiler).
 
@@ -22,17 +22,60 @@ SHAPES = [("d26.qkv", 32768, 4992, 1664), ("d26.fc", 32768, 6656, 1664), ("d26.m
           ("d20.qkv", 65536, 3840, 1280), ("d20.fc", 65536, 5120, 1280), ("d20.mlp_proj", 65536, 1280, 5120)]
 
 
+def sustained(fn, label: str, flops: float, secs: float = 3.0) -> dict:
+    """Back-to-back launches for `secs` seconds with the SM clock and board power sampled every 100 ms: what the
+    kernel delivers once the power cap has settled (a burst of ten launches runs at a higher clock)."""
+    import statistics
+    import subprocess
+    import time
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    smi = subprocess.Popen(["nvidia-smi", "--query-gpu=clocks.sm,power.draw,clocks_event_reasons.sw_power_cap",
+                            "--format=csv,noheader,nounits", "-lms", "100", "-i", str(torch.cuda.current_device())],
+                           stdout=subprocess.PIPE, text=True)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t0 = 0, time.time()
+    a.record()
+    while time.time() - t0 < secs:
+        for _ in range(50):
+            fn()
+        n += 50
+        torch.cuda.synchronize()
+    b.record()
+    torch.cuda.synchronize()
+    smi.terminate()
+    rows = [l.split(",") for l in smi.stdout.read().strip().splitlines()[3:] if l.count(",") == 2]
+    ms = a.elapsed_time(b) / n
+    return dict(kernel=label, ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1),
+                sm_mhz_median=statistics.median(float(r[0]) for r in rows) if rows else None,
+                power_w_median=statistics.median(float(r[1]) for r in rows) if rows else None,
+                power_cap_active_samples=sum(r[2].strip() == "Active" for r in rows), samples=len(rows))
+
+
 def main():
     import argparse
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None, help="one shape name")
     ap.add_argument("--rows", type=int, default=0, help="override M")
     ap.add_argument("--mx-only", action="store_true", help="three launches of the MXFP8 GEMM, nothing else timed")
+    ap.add_argument("--sustained", action="store_true",
+                    help="3-second loops of the MXFP8 and bf16 GEMMs with clock and power sampling")
     args = ap.parse_args()
     for name, M, N, Kd in SHAPES:
         if args.only and name != args.only:
             continue
         M = args.rows or M
+        if args.sustained:
+            x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
+            w = (torch.randn(N, Kd, device="cuda") * 0.02).to(torch.bfloat16)
+            mq, ms = fp8.mx_quantize(w, fp8.mx_tile_n(N))
+            aq, as_ = fp8.mx_quantize(x, 128)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            fl = 2.0 * M * N * Kd
+            print(json.dumps(dict(name=name, **sustained(lambda: fp8.mx_gemm(aq, as_, mq, ms, out), "mxfp8", fl))))
+            print(json.dumps(dict(name=name, **sustained(lambda: K.gemm(x, w, out=out), "bf16", fl))))
+            continue
         if args.mx_only:
             x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
             w = (torch.randn(N, Kd, device="cuda") * 0.02).to(torch.bfloat16)

@@ -463,13 +463,14 @@ struct MxPairCfg {
   static constexpr int B_BYTES = (BN / 2) * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static_assert(STAGE_BYTES % 1024 == 0, "SWIZZLE_128B tiles start on 1024-byte boundaries");
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = BN <= 192 ? 7 : 6;                // as many as fit in 227 KB
   static constexpr int H0 = ((BN / 32 + 1) / 2) * 32;
   static constexpr int SF_OFF = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
   static constexpr int EPI_OFF = BAR_OFF + 256;
   static constexpr int SMEM_BYTES = EPI_OFF + EPI_WARPS * kEpiStageBytes + 1024;
   static constexpr int SF_COL0 = 2 * BN;
+  static_assert(SMEM_BYTES <= 232448, "shared memory per CTA");
 };
 
 template <int BN, bool RELU2>
