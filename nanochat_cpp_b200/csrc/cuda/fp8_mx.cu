@@ -20,17 +20,13 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#include "mx_quant.cuh"
 #include "ptx.cuh"
 #include "tmap.h"
 
 namespace nc {
 
 namespace {
-
-// two values -> two E4M3 bytes (a in bits 0..7, b in bits 8..15), round to nearest even, saturating
-__device__ __forceinline__ uint32_t mx_to_e4m3x2(float a, float b) {
-  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
-}
 
 // One half-warp per two consecutive (row, 128-wide K block) units: a thread owns 8 consecutive elements of each,
 // four threads share a scale; both 16-byte loads are issued before either unit is processed.
@@ -69,16 +65,11 @@ __global__ void __launch_bounds__(256) quantize_mx_kernel(const __nv_bfloat16* _
     }
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    // smallest power of two >= amax / 448: biased exponent of s, plus one when s is not itself a power of two
-    const uint32_t bits = __float_as_uint(amax * (1.0f / 448.0f));
-    uint32_t eb = (bits >> 23) + ((bits & 0x7fffffu) ? 1u : 0u);
-    eb = amax > 0.0f ? min(max(eb, 1u), 253u) : 127u;
+    const uint32_t eb = mx_block_exponent(amax);
     const bool live = in_range && row[u] < R;
     if (live) {
-      const float inv = __uint_as_float((254u - eb) << 23);
-      const uint32_t lo = mx_to_e4m3x2(v[0] * inv, v[1] * inv) | (mx_to_e4m3x2(v[2] * inv, v[3] * inv) << 16);
-      const uint32_t hi = mx_to_e4m3x2(v[4] * inv, v[5] * inv) | (mx_to_e4m3x2(v[6] * inv, v[7] * inv) << 16);
-      *reinterpret_cast<uint2*>(xq + static_cast<long long>(row[u]) * K + kb[u] * 128 + l16 * 8) = make_uint2(lo, hi);
+      *reinterpret_cast<uint2*>(xq + static_cast<long long>(row[u]) * K + kb[u] * 128 + l16 * 8) =
+          mx_pack8(v, mx_inverse_scale(eb));
     }
     // the four scale bytes of this (row, K block) sit in lanes 0, 4, 8, 12 of the half-warp
     const uint32_t b0 = __shfl_sync(0xffffffffu, eb, base), b1 = __shfl_sync(0xffffffffu, eb, base + 4);
@@ -86,8 +77,7 @@ __global__ void __launch_bounds__(256) quantize_mx_kernel(const __nv_bfloat16* _
     if (in_range && l16 == 0) {
       const int tile = row[u] / tile_rows, rt = row[u] % tile_rows;
       const long long atom = (static_cast<long long>(tile) * kbs + kb[u]) * atoms_per_tile + rt / 128;
-      const int r = rt % 128;
-      *reinterpret_cast<uint32_t*>(sf + atom * 512 + (r % 32) * 16 + (r / 32) * 4) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+      *reinterpret_cast<uint32_t*>(sf + atom * 512 + mx_atom_offset(rt % 128)) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
     }
   }
 }

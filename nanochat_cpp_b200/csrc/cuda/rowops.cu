@@ -7,6 +7,8 @@
 // kernel, and the classifier forward and backward are one sweep over a logits chunk.
 #include "rowops.h"
 
+#include "mx_quant.cuh"
+
 #include <math_constants.h>
 
 namespace nc {
@@ -78,7 +80,8 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const bf16* __restric
                                                            const bf16* __restrict__ x0, const float* lam_r,
                                                            const float* lam_0, bf16* __restrict__ xr,
                                                            bf16* __restrict__ y, float* __restrict__ rstd, int rows,
-                                                           int dim, float eps) {
+                                                           int dim, float eps, uint8_t* __restrict__ yq = nullptr,
+                                                           uint8_t* __restrict__ sf = nullptr) {
   const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -127,7 +130,41 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const bf16* __restric
   }
   if (MODE == 2) __syncwarp();
   const bf16* src = (MODE == 2) ? xrp : xp;
-  if (vec) {
+  if (yq != nullptr) {
+    // MXFP8 copy of the output beside the bf16 one (host guarantees the vector path and dim % 128 == 0): the four
+    // lanes of a 32-element block agree on its power-of-two scale, the bf16-rounded values are encoded as E4M3, and
+    // the scale bytes go straight into the 512-byte atoms the GEMM copies into tensor memory (128-row groups).
+    // The trip count is the same for every lane, so the shuffles stay warp-uniform when dim % 256 == 128.
+    const int kbs = dim >> 7;
+    for (int base = 0; base < dim; base += 256) {
+      const int i = base + lane * 8;
+      const bool act = i < dim;
+      float f[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+      float amax = 0.0f;
+      if (act) {
+        V8 v = ld8(src + i);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v.f[e] *= r;
+        st8(yp + i, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          f[e] = b2f(f2b(v.f[e]));
+          amax = fmaxf(amax, fabsf(f[e]));
+        }
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint32_t eb = mx_block_exponent(amax);
+      if (act) *reinterpret_cast<uint2*>(yq + static_cast<long long>(row) * dim + i) = mx_pack8(f, mx_inverse_scale(eb));
+      const int first = lane & 16;
+      const uint32_t b0 = __shfl_sync(0xffffffffu, eb, first), b1 = __shfl_sync(0xffffffffu, eb, first + 4);
+      const uint32_t b2 = __shfl_sync(0xffffffffu, eb, first + 8), b3 = __shfl_sync(0xffffffffu, eb, first + 12);
+      if (act && (lane & 15) == 0) {
+        const long long atom = static_cast<long long>(row >> 7) * kbs + (i >> 7);
+        *reinterpret_cast<uint32_t*>(sf + atom * 512 + mx_atom_offset(row & 127)) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+      }
+    }
+  } else if (vec) {
     for (int i = lane * 8; i < dim; i += 256) {
       V8 v = ld8(src + i);
 #pragma unroll
@@ -1089,10 +1126,11 @@ inline int flat_grid(long long n) {
 }  // namespace
 
 // ------------------------------------------------------------------ launchers
-void rmsnorm_fwd(const bf16* x, long long ldx, bf16* y, float* rstd, int rows, int dim, float eps, cudaStream_t s) {
+void rmsnorm_fwd(const bf16* x, long long ldx, bf16* y, float* rstd, int rows, int dim, float eps, cudaStream_t s,
+                 uint8_t* yq, uint8_t* sf) {
   if (rows <= 0) return;
   rmsnorm_kernel<0><<<blocks_for_rows(rows), kThreads, 0, s>>>(x, ldx, nullptr, nullptr, nullptr, nullptr, y, rstd,
-                                                               rows, dim, eps);
+                                                               rows, dim, eps, yq, sf);
 }
 void rmsnorm_apply(const bf16* x, long long ldx, const float* rstd, bf16* y, int rows, int dim, cudaStream_t s) {
   if (rows <= 0) return;
@@ -1105,9 +1143,10 @@ void rmsnorm_bwd(const bf16* x, const bf16* dy, const float* rstd, const bf16* r
   rmsnorm_bwd_kernel<<<blocks_for_rows(rows), kThreads, 0, s>>>(x, dy, rstd, residual, dx, rows, dim);
 }
 void blend_norm_fwd(const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* xr, bf16* h,
-                    float* rstd, int rows, int dim, float eps, cudaStream_t s) {
+                    float* rstd, int rows, int dim, float eps, cudaStream_t s, uint8_t* hq, uint8_t* sf) {
   if (rows <= 0) return;
-  rmsnorm_kernel<2><<<blocks_for_rows(rows), kThreads, 0, s>>>(x, dim, x0, lam_r, lam_0, xr, h, rstd, rows, dim, eps);
+  rmsnorm_kernel<2><<<blocks_for_rows(rows), kThreads, 0, s>>>(x, dim, x0, lam_r, lam_0, xr, h, rstd, rows, dim, eps, hq,
+                                                               sf);
 }
 void blend_bwd(const bf16* dxr, const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* dx,
                bf16* dx0, bool accumulate_dx0, float* dlam2, long long n, cudaStream_t s) {

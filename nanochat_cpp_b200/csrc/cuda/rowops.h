@@ -11,14 +11,18 @@ namespace nc {
 using bf16 = __nv_bfloat16;
 
 // y = x * rsqrt(mean(x^2) + eps); rstd saved per row.
-void rmsnorm_fwd(const bf16* x, long long ldx, bf16* y, float* rstd, int rows, int dim, float eps, cudaStream_t s);
+// With `yq` and `sf` the kernel also writes y as MXFP8 (E4M3 codes [rows, dim] + scale atoms for 128-row tiles, the
+// layout of fp8.h); needs dim % 128 == 0 and 16-byte aligned rows.
+void rmsnorm_fwd(const bf16* x, long long ldx, bf16* y, float* rstd, int rows, int dim, float eps, cudaStream_t s,
+                 uint8_t* yq = nullptr, uint8_t* sf = nullptr);
 void rmsnorm_apply(const bf16* x, long long ldx, const float* rstd, bf16* y, int rows, int dim, cudaStream_t s);
 // dx = rstd*dy - rstd^3 * mean(x*dy) * x (+ residual)
 void rmsnorm_bwd(const bf16* x, const bf16* dy, const float* rstd, const bf16* residual, bf16* dx, int rows, int dim,
                  cudaStream_t s);
 // xr = lam_r*x + lam_0*x0 ; h = rmsnorm(xr)
 void blend_norm_fwd(const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* xr, bf16* h,
-                    float* rstd, int rows, int dim, float eps, cudaStream_t s);
+                    float* rstd, int rows, int dim, float eps, cudaStream_t s, uint8_t* hq = nullptr,
+                    uint8_t* sf = nullptr);
 // dx = lam_r*dxr ; dx0 (+)= lam_0*dxr ; dlam[0] += <dxr,x> ; dlam[1] += <dxr,x0>
 void blend_bwd(const bf16* dxr, const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* dx,
                bf16* dx0, bool accumulate_dx0, float* dlam2, long long n, cudaStream_t s);

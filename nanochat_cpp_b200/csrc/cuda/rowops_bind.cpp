@@ -38,6 +38,45 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, double eps) {
   nc::rmsnorm_fwd(bp(x), x.stride(0), bpm(y), rstd.data_ptr<float>(), x.size(0), x.size(1), eps, cur());
   return {y, rstd};
 }
+// MXFP8 companions: the same kernels also emit the output as E4M3 codes + scale atoms (128-row tiles).
+bool mx_ok(const Tensor& x) {
+  return x.size(1) % 128 == 0 && x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0;
+}
+Tensor mx_atoms(const Tensor& x) {
+  const int64_t tiles = (x.size(0) + 127) / 128;
+  return torch::empty({tiles * (x.size(1) / 128) * 512}, x.options().dtype(torch::kUInt8));
+}
+std::vector<Tensor> rmsnorm_fwd_mx(const Tensor& x, double eps) {
+  chk_rows(x, "x");
+  TORCH_CHECK(mx_ok(x), "rmsnorm_fwd_mx: dim % 128 == 0 and 16-byte aligned rows");
+  const c10::cuda::CUDAGuard g(x.device());
+  Tensor y = torch::empty({x.size(0), x.size(1)}, x.options());
+  Tensor rstd = f32_empty(x, {x.size(0)});
+  Tensor yq = torch::empty({x.size(0), x.size(1)}, x.options().dtype(torch::kUInt8));
+  Tensor sf = mx_atoms(x);
+  nc::rmsnorm_fwd(bp(x), x.stride(0), bpm(y), rstd.data_ptr<float>(), x.size(0), x.size(1), eps, cur(),
+                  yq.data_ptr<uint8_t>(), sf.data_ptr<uint8_t>());
+  return {y, rstd, yq, sf};
+}
+std::vector<Tensor> blend_norm_fwd_mx(const Tensor& x, const Tensor& x0, const Tensor& lam_r, const Tensor& lam_0,
+                                      double eps) {
+  chk_rows(x, "x");
+  chk_rows(x0, "x0");
+  chk(lam_r, torch::kFloat32, "lam_r");
+  chk(lam_0, torch::kFloat32, "lam_0");
+  TORCH_CHECK(x.is_contiguous() && x0.is_contiguous() && x.sizes() == x0.sizes() && mx_ok(x) && mx_ok(x0),
+              "blend_mx: bad inputs");
+  const c10::cuda::CUDAGuard g(x.device());
+  Tensor xr = torch::empty_like(x), h = torch::empty_like(x);
+  Tensor rstd = f32_empty(x, {x.size(0)});
+  Tensor hq = torch::empty({x.size(0), x.size(1)}, x.options().dtype(torch::kUInt8));
+  Tensor sf = mx_atoms(x);
+  nc::blend_norm_fwd(bp(x), bp(x0), lam_r.data_ptr<float>(), lam_0.data_ptr<float>(), bpm(xr), bpm(h),
+                     rstd.data_ptr<float>(), x.size(0), x.size(1), eps, cur(), hq.data_ptr<uint8_t>(),
+                     sf.data_ptr<uint8_t>());
+  return {xr, h, rstd, hq, sf};
+}
+
 Tensor rmsnorm_apply(const Tensor& x, const Tensor& rstd) {
   chk_rows(x, "x");
   chk(rstd, torch::kFloat32, "rstd");
@@ -275,6 +314,8 @@ void register_rowops(pybind11::module_& m) {
   m.def("rmsnorm_apply", &rmsnorm_apply);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("blend_norm_fwd", &blend_norm_fwd);
+  m.def("rmsnorm_fwd_mx", &rmsnorm_fwd_mx);
+  m.def("blend_norm_fwd_mx", &blend_norm_fwd_mx);
   m.def("blend_bwd", &blend_bwd);
   m.def("backout_fwd", &backout_fwd);
   m.def("backout_bwd", &backout_bwd);

@@ -151,10 +151,18 @@ class GPT:
         cfg, P = self.cfg, self.params
         H, KV, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         M = B * T
-        xr, h, rstd1 = ops.blend_norm_fwd(x, x0, self._lam("resid_lambdas", i), self._lam("x0_lambdas", i))
         wqkv = P.qkv_view(i)
         hq = None
-        if self.fp8 and (f"qkv{i}" in self._fp8_w):
+        fuse_q = self.fp8_mode == "mx" and cfg.hidden_dim % 128 == 0 and ops.get_mode() == "kernels"
+        if fuse_q and (f"qkv{i}" in self._fp8_w):
+            from ..ops import fp8 as F8
+            # the norm kernel writes h a second time as MXFP8: no separate quantizer pass
+            xr, h, rstd1, hq0, hq1 = ops.cuda_module().blend_norm_fwd_mx(x, x0, self._lam("resid_lambdas", i),
+                                                                        self._lam("x0_lambdas", i))
+            hq = (hq0, hq1)
+        else:
+            xr, h, rstd1 = ops.blend_norm_fwd(x, x0, self._lam("resid_lambdas", i), self._lam("x0_lambdas", i))
+        if hq is None and self.fp8 and (f"qkv{i}" in self._fp8_w):
             from ..ops import fp8 as F8
             hq = F8.mx_quantize(h, 128) if self.fp8_mode == "mx" else F8.quantize_rows(h)
         if hq is not None:
@@ -180,17 +188,25 @@ class GPT:
         v4 = _heads(v, B, T, KV, D)
         attn, lse = ops.attention_fwd(q, k, v4, cfg.window_left(i))
         x_mid = ops.linear_fwd(attn.view(M, H * D), self._w(i, "attn.c_proj"), residual=xr)
-        h2, rstd2 = ops.rmsnorm_fwd(x_mid)
+        h2q = None
+        if fuse_q and (f"fc{i}" in self._fp8_w):
+            h2, rstd2, q0, q1 = ops.cuda_module().rmsnorm_fwd_mx(x_mid)
+            h2q = (q0, q1)
+        else:
+            h2, rstd2 = ops.rmsnorm_fwd(x_mid)
         if self.fp8 and (f"fc{i}" in self._fp8_w):
             from ..ops import fp8 as F8
             w8 = self._fp8_w[f"fc{i}"]
             if self.fp8_mode == "mx" and self.mlp_keep_act:
-                h2q = F8.mx_quantize(h2, 128)
+                h2q = h2q if h2q is not None else F8.mx_quantize(h2, 128)
                 act = torch.empty((M, w8.q.shape[0]), dtype=torch.bfloat16, device=h2.device)
                 F8.mx_gemm(h2q[0], h2q[1], w8.q, w8.s, act, act)      # only relu(pre)^2 is stored
                 pre = None
             elif self.fp8_mode == "mx":
-                pre, act = F8.linear_fwd_mx(h2, w8, relu2=True)
+                h2q = h2q if h2q is not None else F8.mx_quantize(h2, 128)
+                pre = torch.empty((M, w8.q.shape[0]), dtype=torch.bfloat16, device=h2.device)
+                act = torch.empty_like(pre)
+                F8.mx_gemm(h2q[0], h2q[1], w8.q, w8.s, pre, act)
             else:
                 pre, act = F8.linear_fwd_fp8(h2, w8, relu2=True)
         else:

@@ -183,6 +183,19 @@ def rmsnorm_fwd(x, eps=RMS_EPS):
     return y, rstd
 
 
+def rmsnorm_fwd_mx(x, eps=RMS_EPS):
+    """rmsnorm that also writes its output as MXFP8: (y, rstd, y_e4m3 uint8 [M, K], scale atoms for 128-row tiles).
+    The codes and scales equal `fp8.mx_quantize(y, 128)`; the separate pass over y is saved."""
+    y, rstd, yq, sf = _C.rmsnorm_fwd_mx(x, eps)
+    return y, rstd, yq, sf
+
+
+def blend_norm_fwd_mx(x, x0, lam_r, lam_0, eps=RMS_EPS):
+    """blend + rmsnorm that also writes h as MXFP8: (xr, h, rstd, h_e4m3, scale atoms)."""
+    xr, h, rstd, hq, sf = _C.blend_norm_fwd_mx(x, x0, lam_r, lam_0, eps)
+    return xr, h, rstd, hq, sf
+
+
 def rmsnorm_apply(x, rstd):
     return _C.rmsnorm_apply(x, rstd)
 

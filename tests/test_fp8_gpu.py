@@ -131,3 +131,31 @@ def test_mx_gemm_matches_dequantized_product(M, N, K, variant):
     fp8.mx_gemm(xq, sx, wq, sw, only_act, only_act, variant=variant)
     assert torch.equal(only_act, act)
     Kmod.check_status()
+
+
+@pytest.mark.parametrize("M,K", [(300, 512), (64, 384), (1025, 1280)])
+def test_norm_kernels_emit_the_same_mxfp8_as_the_quantizer(M, K):
+    """rmsnorm / blend+rmsnorm with the fused MXFP8 output: bf16 results identical to the plain kernels, codes and
+    scales identical to quantizing that bf16 output in a separate pass (K % 256 == 128 covers the half-idle warp)."""
+    from nanochat_cpp_b200.ops import cuda as Kmod
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 2).to(torch.bfloat16)
+    x0 = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    y, rstd = Kmod.rmsnorm_fwd(x)
+    y2, rstd2, yq, sf = Kmod.rmsnorm_fwd_mx(x)
+    assert torch.equal(y, y2) and torch.equal(rstd, rstd2)
+    q_ref, sf_ref = fp8.mx_quantize(y, 128)
+    assert torch.equal(yq, q_ref)
+    assert torch.equal(fp8.mx_scales_from_atoms(sf, M, K, 128), fp8.mx_scales_from_atoms(sf_ref, M, K, 128))
+    lr = torch.tensor([0.9], device="cuda")
+    l0 = torch.tensor([0.2], device="cuda")
+    xr, h, r1 = Kmod.blend_norm_fwd(x, x0, lr, l0)
+    xr2, h2, r2, hq, sfh = Kmod.blend_norm_fwd_mx(x, x0, lr, l0)
+    assert torch.equal(xr, xr2) and torch.equal(h, h2) and torch.equal(r1, r2)
+    q_ref, sf_ref = fp8.mx_quantize(h, 128)
+    assert torch.equal(hq, q_ref)
+    assert torch.equal(fp8.mx_scales_from_atoms(sfh, M, K, 128), fp8.mx_scales_from_atoms(sf_ref, M, K, 128))
+    w = (torch.randn(256, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wq, sw = fp8.mx_quantize(w, fp8.mx_tile_n(256))
+    assert torch.equal(fp8.mx_gemm(hq, sfh, wq, sw), fp8.mx_gemm(q_ref, sf_ref, wq, sw))
+    Kmod.check_status()
