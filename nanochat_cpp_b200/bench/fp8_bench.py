@@ -75,6 +75,7 @@ def main():
             fl = 2.0 * M * N * Kd
             print(json.dumps(dict(name=name, **sustained(lambda: fp8.mx_gemm(aq, as_, mq, ms, out), "mxfp8", fl))))
             print(json.dumps(dict(name=name, **sustained(lambda: K.gemm(x, w, out=out), "bf16", fl))))
+            print(json.dumps(dict(name=name, **sustained(lambda: torch.matmul(x, w.t(), out=out), "cublas_bf16", fl))))
             continue
         if args.mx_only:
             x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
