@@ -174,12 +174,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (warp >= 2 && split == 0) {
     const int n = n0 + wrow;
     if (n < p.N) {
+      // The residual may be the output itself (x += ...), so the compiler cannot move a residual load above the
+      // store of the row before it: loaded inside the store loop, the 64 loads run one memory latency after the
+      // other (tens of microseconds). All of them are issued here, before the first store.
+      if (p.epi == kEpiBf16Res) {
+        __nv_bfloat16 res[TX];
+#pragma unroll
+        for (int m = 0; m < TX; ++m)
+          res[m] = m < p.M ? p.R[static_cast<long long>(m) * p.ldr + n] : __float2bfloat16_rn(0.0f);
+#pragma unroll
+        for (int m = 0; m < TX; ++m) acc[m] += __bfloat162float(res[m]);
+      }
 #pragma unroll
       for (int m = 0; m < TX; ++m) {   // fully unrolled: acc[] stays in registers
         if (m >= p.M) break;
-        float v = acc[m];
+        const float v = acc[m];
         const long long ci = static_cast<long long>(m) * p.ldc + n;
-        if (p.epi == kEpiBf16Res) v += __bfloat162float(p.R[static_cast<long long>(m) * p.ldr + n]);
         const __nv_bfloat16 o = __float2bfloat16_rn(v);
         if (p.epi != kEpiRelu2 || p.C != p.C2) p.C[ci] = o;  // C2 == C: only the activation is kept
         if (p.epi == kEpiRelu2) {
