@@ -101,9 +101,9 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
   }
   const long long row = static_cast<long long>(KV) * D;
   const int* table = page_table + static_cast<long long>(b) * max_pages;
-  for (int kb = k0; kb < k1; kb += GROUPS * kDecodeUnroll) {  // uniform over the CTA: the shuffles below are full-warp
-    uint4 kr[kDecodeUnroll], vr[kDecodeUnroll];
-    bool ok[kDecodeUnroll];
+  // Software pipeline: the K and V rows of the next batch of keys (and the page-table entries their addresses need)
+  // are requested before the current batch is reduced, so loads stay in flight during the arithmetic.
+  auto fetch = [&](int kb, uint4 (&kr)[kDecodeUnroll], uint4 (&vr)[kDecodeUnroll], bool (&ok)[kDecodeUnroll]) {
 #pragma unroll
     for (int u = 0; u < kDecodeUnroll; ++u) {
       const int key = kb + u * GROUPS + group;
@@ -116,6 +116,14 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
         vr[u] = *reinterpret_cast<const uint4*>(v_pool + off);
       }
     }
+  };
+  uint4 kr[kDecodeUnroll], vr[kDecodeUnroll];
+  bool ok[kDecodeUnroll];
+  fetch(k0, kr, vr, ok);
+  for (int kb = k0; kb < k1; kb += GROUPS * kDecodeUnroll) {  // uniform over the CTA: the shuffles below are full-warp
+    uint4 kr_next[kDecodeUnroll], vr_next[kDecodeUnroll];
+    bool ok_next[kDecodeUnroll];
+    fetch(kb + GROUPS * kDecodeUnroll, kr_next, vr_next, ok_next);   // past k1 every key is masked: no load is issued
     float sc[kDecodeUnroll][G];
 #pragma unroll
     for (int u = 0; u < kDecodeUnroll; ++u) {
@@ -155,6 +163,8 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
         for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i]);
       }
     }
+#pragma unroll
+    for (int u = 0; u < kDecodeUnroll; ++u) kr[u] = kr_next[u], vr[u] = vr_next[u], ok[u] = ok_next[u];
   }
   // merge the lane groups
 #pragma unroll
