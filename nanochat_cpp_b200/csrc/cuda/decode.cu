@@ -54,6 +54,13 @@ __device__ __forceinline__ void unpack8(const uint4& r, float* f) {
     f[2 * i] = t.x, f[2 * i + 1] = t.y;
   }
 }
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 r;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return r;
+}
 
 // grid (splits, KV heads, B), 128 threads. A key row (D bf16) is read by D/8 lanes with one 16-byte load each, so a
 // warp covers 32/(D/8) keys per load instruction and every thread keeps kDecodeUnroll K and V loads in flight. Each
@@ -65,7 +72,8 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
     const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
     const int* __restrict__ seq_lens, int H, int KV, int page_size, int window_left, float scale_log2, int splits,
-    float* __restrict__ part_acc, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out) {
+    float* __restrict__ part_acc, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+    long long q_stride_b) {
   constexpr int LPK = D / 8;        // lanes per key
   constexpr int KPW = 32 / LPK;     // keys per warp per load
   constexpr int GROUPS = kDecodeWarps * KPW;
@@ -87,7 +95,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
   float qf[G][8];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const uint4 r = *reinterpret_cast<const uint4*>(q + (static_cast<long long>(b) * H + kvh * G + g) * D + part * 8);
+    const uint4 r = *reinterpret_cast<const uint4*>(q + b * q_stride_b + (kvh * G + g) * D + part * 8);
     unpack8(r, qf[g]);
 #pragma unroll
     for (int i = 0; i < 8; ++i) qf[g][i] *= scale_log2;
@@ -233,7 +241,9 @@ const char* launch_decode(const DecodeArgs& a, cudaStream_t s) {
 #define NC_DECODE(GV)                                                                                                \
   paged_decode_kernel<D, GV><<<grid, kDecodeWarps * 32, 0, s>>>(a.q, a.k_pool, a.v_pool, a.page_table, a.max_pages, \
                                                                 a.seq_lens, a.H, a.KV, a.page_size, a.window_left,  \
-                                                                sl2, splits, a.part_acc, a.part_ml, a.out)
+                                                                sl2, splits, a.part_acc, a.part_ml, a.out,          \
+                                                                a.q_stride_b > 0 ? a.q_stride_b                     \
+                                                                                 : static_cast<long long>(a.H) * D)
   switch (G) {
     case 1: NC_DECODE(1); break;
     case 2: NC_DECODE(2); break;
@@ -250,6 +260,71 @@ const char* launch_decode(const DecodeArgs& a, cudaStream_t s) {
 
 }  // namespace
 
+// Decode prologue in one launch (head_dim 128, one new token per sequence): for the token's fused QKV row,
+// q and k heads get head RMSNorm -> RoPE at the token's position -> scale (the arithmetic of the training kernel
+// qk_prep_fwd, rounding points included); q goes to a dense [B, H, D] buffer, k straight into its page of the
+// cache, and the value row (which may come from another buffer: the value gate writes its own) is copied into its
+// page as well. One warp per (token, four heads) plus one warp per token for the value row; eight lanes share a head.
+__global__ void __launch_bounds__(256) decode_prep_append_kernel(
+    const __nv_bfloat16* __restrict__ qk, long long ld_qk, const __nv_bfloat16* __restrict__ v, long long ld_v,
+    const float* __restrict__ cosT, const float* __restrict__ sinT, const int* __restrict__ positions,
+    const int* __restrict__ page_table, int max_pages, int page_size, __nv_bfloat16* __restrict__ q_out,
+    __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int tokens, int H, int KV, float eps,
+    float scale) {
+  constexpr int D = 128;
+  const int groups = (H + KV + 3) / 4;                  // head groups of the q / k part
+  const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (unit >= tokens * (groups + 1)) return;
+  const int tok = unit / (groups + 1), grp = unit % (groups + 1);
+  const int lane = threadIdx.x & 31;
+  const int pos = positions[tok];
+  if (pos < 0) return;
+  const int page = page_table[static_cast<long long>(tok) * max_pages + pos / page_size];
+  const long long cache_row = (static_cast<long long>(page) * page_size + pos % page_size) * KV * D;
+  if (grp == groups) {   // value row -> cache
+    const uint4* src = reinterpret_cast<const uint4*>(v + static_cast<long long>(tok) * ld_v);
+    uint4* dst = reinterpret_cast<uint4*>(v_pool + cache_row);
+    for (int i = lane; i < KV * D / 8; i += 32) dst[i] = src[i];
+    return;
+  }
+  const int sub = lane >> 3, j = lane & 7;
+  const int h = grp * 4 + sub;
+  const bool act = h < H + KV;
+  const float* cp = cosT + static_cast<long long>(pos) * (D / 2);
+  const float* sp = sinT + static_cast<long long>(pos) * (D / 2);
+  float c[8], sn[8];
+  *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cp + 8 * j);
+  *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cp + 8 * j + 4);
+  *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sp + 8 * j);
+  *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sp + 8 * j + 4);
+  const __nv_bfloat16* row_in = qk + static_cast<long long>(tok) * ld_qk;
+  float a[8], b[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) a[e] = 0.f, b[e] = 0.f;
+  if (act) {
+    unpack8(*reinterpret_cast<const uint4*>(row_in + h * D + 8 * j), a);
+    unpack8(*reinterpret_cast<const uint4*>(row_in + h * D + 64 + 8 * j), b);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += a[e] * a[e] + b[e] * b[e];
+  ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  const float r = 1.0f / sqrtf(ss * (1.0f / static_cast<float>(D)) + eps);
+  if (!act) return;
+  float y1[8], y2[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float x1 = __bfloat162float(__float2bfloat16_rn(a[e] * r)), x2 = __bfloat162float(__float2bfloat16_rn(b[e] * r));
+    y1[e] = (x1 * c[e] + x2 * sn[e]) * scale;
+    y2[e] = (-x1 * sn[e] + x2 * c[e]) * scale;
+  }
+  __nv_bfloat16* dst = h < H ? q_out + (static_cast<long long>(tok) * H + h) * D : k_pool + cache_row + (h - H) * D;
+  *reinterpret_cast<uint4*>(dst + 8 * j) = pack8(y1);
+  *reinterpret_cast<uint4*>(dst + 64 + 8 * j) = pack8(y2);
+}
+
 void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_table, int max_pages,
                const int* positions, const __nv_bfloat16* k_new, long long k_ld, const __nv_bfloat16* v_new,
                long long v_ld, int B, int T, int page_size, int row_elems, cudaStream_t s) {
@@ -257,6 +332,26 @@ void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_tab
   if (total <= 0) return;
   kv_append_kernel<<<(total + 7) / 8, 256, 0, s>>>(k_pool, v_pool, page_table, max_pages, positions, k_new, k_ld,
                                                    v_new, v_ld, T, total, page_size, row_elems);
+}
+
+const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const __nv_bfloat16* v, long long ld_v,
+                               const float* cosT, const float* sinT, const int* positions, const int* page_table,
+                               int max_pages, int page_size, __nv_bfloat16* q_out, __nv_bfloat16* k_pool,
+                               __nv_bfloat16* v_pool, int tokens, int H, int KV, int D, float eps, float scale,
+                               cudaStream_t s) {
+  if (tokens <= 0) return nullptr;
+  if (D != 128) return "decode_prep_append: head_dim must be 128";
+  if (ld_qk % 8 || ld_v % 8 ||
+      ((reinterpret_cast<uintptr_t>(qk) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(q_out) |
+        reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) | reinterpret_cast<uintptr_t>(cosT) |
+        reinterpret_cast<uintptr_t>(sinT)) & 15))
+    return "decode_prep_append: rows must be 16-byte aligned";
+  const int units = tokens * ((H + KV + 3) / 4 + 1);
+  decode_prep_append_kernel<<<(units + 7) / 8, 256, 0, s>>>(qk, ld_qk, v, ld_v, cosT, sinT, positions, page_table,
+                                                            max_pages, page_size, q_out, k_pool, v_pool, tokens, H, KV,
+                                                            eps, scale);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
 int decode_splits(int B, int KV, int max_keys) {

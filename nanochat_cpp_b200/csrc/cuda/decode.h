@@ -8,6 +8,7 @@ namespace nc {
 struct DecodeArgs {
   int B = 0, H = 0, KV = 0, D = 0;
   const __nv_bfloat16* q = nullptr;       // [B, H, D], prepared (normed, rotated, scaled)
+  long long q_stride_b = 0;               // elements between sequences in q (0: H * D, contiguous); 16-byte multiples
   const __nv_bfloat16* k_pool = nullptr;  // [pages, page_size, KV, D]
   const __nv_bfloat16* v_pool = nullptr;
   const int* page_table = nullptr;        // [B, max_pages]
@@ -31,6 +32,15 @@ int decode_splits(int B, int KV, int max_keys);
 void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_table, int max_pages,
                const int* positions, const __nv_bfloat16* k_new, long long k_ld, const __nv_bfloat16* v_new,
                long long v_ld, int B, int T, int page_size, int row_elems, cudaStream_t s);
+
+// Decode prologue in one launch (head_dim 128): q / k heads of the fused row `qk` ([tokens, >= (H + KV) * D], q heads
+// first) get head RMSNorm -> RoPE at positions[tok] -> scale; q goes to q_out [tokens, H, D], k and the value row
+// v ([tokens, KV * D]) go into the token's page of the pools. One token per sequence (page_table row = token).
+const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const __nv_bfloat16* v, long long ld_v,
+                               const float* cosT, const float* sinT, const int* positions, const int* page_table,
+                               int max_pages, int page_size, __nv_bfloat16* q_out, __nv_bfloat16* k_pool,
+                               __nv_bfloat16* v_pool, int tokens, int H, int KV, int D, float eps, float scale,
+                               cudaStream_t s);
 
 const char* paged_decode_attention(const DecodeArgs& args, cudaStream_t s);
 

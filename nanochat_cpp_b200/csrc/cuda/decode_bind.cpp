@@ -31,13 +31,47 @@ void kv_append(Tensor& k_pool, Tensor& v_pool, const Tensor& page_table, const T
                 k_pool.size(1), row, at::cuda::getCurrentCUDAStream());
 }
 
+// qk: [B, >= (H + KV) * D] rows of the fused projection (q heads first), v: [B, KV * D] rows (any row stride);
+// cos / sin: fp32 [positions, D / 2]; positions: int32 [B]. Returns q prepared, dense [B, H, D].
+Tensor decode_prep_append(const Tensor& qk, const Tensor& v, const Tensor& cos, const Tensor& sin,
+                          const Tensor& positions, Tensor& k_pool, Tensor& v_pool, const Tensor& page_table, int64_t H,
+                          double eps, double scale) {
+  const c10::cuda::CUDAGuard g(qk.device());
+  TORCH_CHECK(k_pool.is_contiguous() && v_pool.is_contiguous() && k_pool.dim() == 4, "pools must be [P, page, KV, D]");
+  const int KV = k_pool.size(2), D = k_pool.size(3), B = qk.size(0);
+  TORCH_CHECK(qk.dim() == 2 && qk.scalar_type() == torch::kBFloat16 && qk.stride(1) == 1 && qk.size(1) >= (H + KV) * D,
+              "qk must be bf16 rows holding the q and k heads");
+  TORCH_CHECK(v.dim() == 2 && v.scalar_type() == torch::kBFloat16 && v.stride(1) == 1 && v.size(0) == B &&
+                  v.size(1) == KV * D,
+              "v must be bf16 [B, KV * D]");
+  TORCH_CHECK(cos.scalar_type() == torch::kFloat32 && sin.scalar_type() == torch::kFloat32 && cos.is_contiguous() &&
+                  sin.is_contiguous() && cos.size(-1) == D / 2,
+              "cos / sin must be fp32 [positions, D / 2]");
+  TORCH_CHECK(positions.scalar_type() == torch::kInt32 && positions.is_contiguous() && positions.numel() == B,
+              "positions must be int32 [B]");
+  TORCH_CHECK(page_table.scalar_type() == torch::kInt32 && page_table.is_contiguous() && page_table.size(0) == B,
+              "page_table must be int32 [B, max_pages]");
+  Tensor q_out = torch::empty({B, H, D}, qk.options());
+  const char* err = nc::decode_prep_append(bp(qk), qk.stride(0), bp(v), v.stride(0), cos.data_ptr<float>(),
+                                           sin.data_ptr<float>(), positions.data_ptr<int>(), page_table.data_ptr<int>(),
+                                           page_table.size(1), k_pool.size(1), bp(q_out), bp(k_pool), bp(v_pool), B,
+                                           static_cast<int>(H), KV, D, static_cast<float>(eps), static_cast<float>(scale),
+                                           at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(err == nullptr, err);
+  return q_out;
+}
+
 Tensor paged_decode_attention(const Tensor& q, const Tensor& k_pool, const Tensor& v_pool, const Tensor& page_table,
                               const Tensor& seq_lens, int64_t window_left, double scale) {
   const c10::cuda::CUDAGuard g(q.device());
-  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && q.scalar_type() == torch::kBFloat16, "q must be bf16 [B, H, D]");
+  // q may be a slice of a wider row (the q half of the fused q/k preparation output): heads and channels dense
+  TORCH_CHECK(q.dim() == 3 && q.scalar_type() == torch::kBFloat16 && q.stride(2) == 1 && q.stride(1) == q.size(2) &&
+                  q.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(q.data_ptr()) & 15) == 0,
+              "q must be bf16 [B, H, D] with dense heads and 16-byte aligned rows");
   TORCH_CHECK(seq_lens.scalar_type() == torch::kInt32 && seq_lens.is_contiguous(), "seq_lens must be int32");
-  Tensor out = torch::empty_like(q);
+  Tensor out = torch::empty({q.size(0), q.size(1), q.size(2)}, q.options());
   nc::DecodeArgs a;
+  a.q_stride_b = q.stride(0);
   a.B = q.size(0), a.H = q.size(1), a.D = q.size(2), a.KV = k_pool.size(2);
   a.q = bp(q), a.k_pool = bp(k_pool), a.v_pool = bp(v_pool);
   a.page_table = page_table.data_ptr<int>();
@@ -67,5 +101,6 @@ Tensor paged_decode_attention(const Tensor& q, const Tensor& k_pool, const Tenso
 
 void register_decode(pybind11::module_& m) {
   m.def("kv_append", &kv_append);
+  m.def("decode_prep_append", &decode_prep_append);
   m.def("paged_decode_attention", &paged_decode_attention);
 }

@@ -98,6 +98,9 @@ class InferenceEngine:
             cos_all, sin_all = self._rope(t0 + T)
             cos, sin = cos_all[t0:t0 + T], sin_all[t0:t0 + T]
         new_lens = cache.seq_lens + T
+        fused_prologue = (decode and self.device.type == "cuda" and ops.get_mode() == "kernels" and D == 128
+                          and cache.page_table.shape[0] == B)
+        pos_flat = pos.reshape(-1).contiguous()
         x = x0
         x_backout = None
         for i in range(cfg.num_layers):
@@ -114,6 +117,20 @@ class InferenceEngine:
             if cfg.has_value_embedding(i):
                 ve = ops.embedding_fwd(tok, P.v(f"value_embeds.{i}.weight"))
                 v, _ = ops.value_gate_fwd(h, ve, m._w(i, "attn.ve_gate"), v, D)
+            wl = cfg.window_left(i)
+            if fused_prologue and wqkv is not None:
+                # one launch: q / k preparation, k and v appended to their pages; q comes back dense
+                q3 = ops.cuda_module().decode_prep_append(qkv, v, cos_all, sin_all, pos_flat, cache.k[i], cache.v[i],
+                                                          cache.page_table, H)
+                attn = ops.paged_decode_attention(q3, cache.k[i], cache.v[i], cache.page_table, new_lens,
+                                                  wl).view(B, 1, H, D)
+                x_mid = ops.linear_fwd(attn.reshape(M, H * D), m._w(i, "attn.c_proj"), residual=xr)
+                h2, _ = ops.rmsnorm_fwd(x_mid)
+                act = ops.linear_relu2_act_fwd(h2, m._w(i, "mlp.c_fc"))
+                x = ops.linear_fwd(act, m._w(i, "mlp.c_proj"), residual=x_mid)
+                if i == cfg.backout_layer:
+                    x_backout = x
+                continue
             q4, k4 = _heads(q_pre, B, T, H, D), _heads(k_pre, B, T, KV, D)
             if decode and self.device.type == "cuda" and ops.get_mode() == "kernels":
                 q, k = ops.cuda_module().qk_prep_fwd(q4, k4, cos_all, sin_all, positions=pos.reshape(-1).contiguous())
@@ -121,9 +138,8 @@ class InferenceEngine:
                 q, k = ops.qk_prep_fwd(q4, k4, cos, sin)
             v4 = _heads(v, B, T, KV, D)
             ops.kv_append(cache.k[i], cache.v[i], cache.page_table, pos, k, v4)
-            wl = cfg.window_left(i)
             if decode:
-                attn = ops.paged_decode_attention(q.reshape(B, H, D), cache.k[i], cache.v[i], cache.page_table,
+                attn = ops.paged_decode_attention(q[:, 0], cache.k[i], cache.v[i], cache.page_table,
                                                   new_lens, wl).view(B, 1, H, D)
             elif t0 == 0:
                 attn, _ = ops.attention_fwd(q, k, v4, wl)

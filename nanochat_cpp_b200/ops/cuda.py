@@ -433,12 +433,20 @@ def kv_append(k_pool, v_pool, page_table, positions, k_new, v_new):
     _C.kv_append(k_pool, v_pool, page_table, positions.contiguous(), k_new, v_new)
 
 
+def decode_prep_append(qk_rows, v_rows, cos, sin, positions, k_pool, v_pool, page_table, num_heads,
+                       eps=RMS_EPS, scale=QK_SCALE):
+    """Decode prologue in one launch (head_dim 128, one token per sequence): `qk_prep_fwd` of the q and k heads of the
+    fused projection rows, k and the value rows appended to the paged cache. Returns q [B, H, D]."""
+    return _C.decode_prep_append(qk_rows, v_rows, cos, sin, positions, k_pool, v_pool, page_table, num_heads, eps, scale)
+
+
 def paged_decode_attention(q, k_pool, v_pool, page_table, seq_lens, window_left=-1, scale=None):
     import math
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    return _C.paged_decode_attention(q.contiguous(), k_pool, v_pool, page_table, seq_lens, int(window_left),
-                                     float(scale))
+    if not (q.stride(2) == 1 and q.stride(1) == q.shape[2] and q.stride(0) % 8 == 0):
+        q = q.contiguous()             # the kernel takes any 16-byte aligned stride between sequences
+    return _C.paged_decode_attention(q, k_pool, v_pool, page_table, seq_lens, int(window_left), float(scale))
 
 
 def __getattr__(name):

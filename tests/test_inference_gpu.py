@@ -71,3 +71,32 @@ def test_engine_matches_torch_ops_and_graph_replay():
     lg_k2 = eager.decode(cache, nxt)
     assert (lg_k - lg_t).abs().max() < 0.15 and (lg_k2 - lg_t2).abs().max() < 0.15
     _K().check_status()
+
+
+@pytest.mark.parametrize("H,KV", [(10, 10), (4, 2), (3, 1)])
+def test_decode_prologue_matches_qk_prep_and_kv_append(H, KV):
+    """The one-launch decode prologue writes exactly what `qk_prep_fwd` + `kv_append` write: q dense, k and v in the
+    token's page; untouched cache rows stay as they were."""
+    K = _K()
+    D, B, page, max_pages = 128, 5, 16, 6
+    g = torch.Generator(device="cuda").manual_seed(H * 7 + KV)
+    width = (H + 2 * KV) * D
+    qkv = torch.randn(B, width + 64, device="cuda", generator=g).to(torch.bfloat16)[:, :width]     # padded row stride
+    v_own = torch.randn(B, KV * D, device="cuda", generator=g).to(torch.bfloat16)                 # a separate v buffer
+    cos, sin = ops.build_rope(page * max_pages, D, 10000.0, torch.device("cuda"))
+    pos = torch.tensor([0, 17, 31, 64, 95], device="cuda", dtype=torch.int32)
+    table = torch.randperm(B * max_pages, device="cuda", generator=g).to(torch.int32).view(B, max_pages)
+    for v_rows in (qkv[:, (H + KV) * D:], v_own):
+        k_a = torch.randn(B * max_pages, page, KV, D, device="cuda", generator=g).to(torch.bfloat16)
+        v_a = torch.randn_like(k_a)
+        k_b, v_b = k_a.clone(), v_a.clone()
+        q4 = qkv[:, : H * D].as_strided((B, 1, H, D), (qkv.stride(0), qkv.stride(0), D, 1))
+        k4 = qkv[:, H * D:(H + KV) * D].as_strided((B, 1, KV, D), (qkv.stride(0), qkv.stride(0), D, 1),
+                                                   qkv.storage_offset() + H * D)
+        q_ref, k_ref = K.qk_prep_fwd(q4, k4, cos, sin, positions=pos)
+        v4 = v_rows.as_strided((B, 1, KV, D), (v_rows.stride(0), v_rows.stride(0), D, 1), v_rows.storage_offset())
+        K.kv_append(k_a, v_a, table, pos.view(B, 1), k_ref, v4)
+        q_new = K.decode_prep_append(qkv, v_rows, cos, sin, pos, k_b, v_b, table, H)
+        assert torch.equal(q_new, q_ref.reshape(B, H, D))
+        assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+    K.check_status()
