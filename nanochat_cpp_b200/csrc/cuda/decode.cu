@@ -334,6 +334,24 @@ void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_tab
                                                    v_new, v_ld, T, total, page_size, row_elems);
 }
 
+// fp32 out[r, c] = cap * tanh(logits[r, c] / cap) for c < vocab: the head's soft cap, one pass over the bf16 logits
+// (two elements per thread; the same float operations as the elementwise definition).
+__global__ void __launch_bounds__(256) softcap_logits_kernel(const __nv_bfloat16* __restrict__ lg, long long ld,
+                                                             float* __restrict__ out, int rows, int vocab, float cap) {
+  const long long i = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) * 2;
+  const int r = static_cast<int>(i / vocab), c = static_cast<int>(i % vocab);
+  if (r >= rows) return;
+  const __nv_bfloat16* src = lg + static_cast<long long>(r) * ld + c;
+  float* dst = out + static_cast<long long>(r) * vocab + c;
+  dst[0] = cap * tanhf(__bfloat162float(src[0]) / cap);
+  if (c + 1 < vocab) dst[1] = cap * tanhf(__bfloat162float(src[1]) / cap);
+}
+void softcap_logits(const __nv_bfloat16* lg, long long ld, float* out, int rows, int vocab, float cap, cudaStream_t s) {
+  if (rows <= 0 || vocab <= 0) return;
+  const long long pairs = (static_cast<long long>(rows) * vocab + 1) / 2;   // vocab even: pairs never straddle rows
+  softcap_logits_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, s>>>(lg, ld, out, rows, vocab, cap);
+}
+
 const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const __nv_bfloat16* v, long long ld_v,
                                const float* cosT, const float* sinT, const int* positions, const int* page_table,
                                int max_pages, int page_size, __nv_bfloat16* q_out, __nv_bfloat16* k_pool,

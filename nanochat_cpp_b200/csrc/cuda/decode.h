@@ -42,6 +42,9 @@ const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const _
                                __nv_bfloat16* v_pool, int tokens, int H, int KV, int D, float eps, float scale,
                                cudaStream_t s);
 
+// out fp32 [rows, vocab] = cap * tanh(logits[:, :vocab] / cap); logits bf16 rows with leading dimension ld; vocab even.
+void softcap_logits(const __nv_bfloat16* logits, long long ld, float* out, int rows, int vocab, float cap, cudaStream_t s);
+
 const char* paged_decode_attention(const DecodeArgs& args, cudaStream_t s);
 
 }  // namespace nc

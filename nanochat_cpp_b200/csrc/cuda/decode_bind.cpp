@@ -61,6 +61,17 @@ Tensor decode_prep_append(const Tensor& qk, const Tensor& v, const Tensor& cos, 
   return q_out;
 }
 
+Tensor softcap_logits(const Tensor& logits, int64_t vocab, double cap) {
+  const c10::cuda::CUDAGuard g(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == torch::kBFloat16 && logits.stride(1) == 1 &&
+                  vocab <= logits.size(1) && vocab % 2 == 0,
+              "softcap_logits: bf16 [rows, >= vocab], even vocab");
+  Tensor out = torch::empty({logits.size(0), vocab}, logits.options().dtype(torch::kFloat32));
+  nc::softcap_logits(bp(logits), logits.stride(0), out.data_ptr<float>(), logits.size(0), static_cast<int>(vocab),
+                     static_cast<float>(cap), at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
 Tensor paged_decode_attention(const Tensor& q, const Tensor& k_pool, const Tensor& v_pool, const Tensor& page_table,
                               const Tensor& seq_lens, int64_t window_left, double scale) {
   const c10::cuda::CUDAGuard g(q.device());
@@ -102,5 +113,6 @@ Tensor paged_decode_attention(const Tensor& q, const Tensor& k_pool, const Tenso
 void register_decode(pybind11::module_& m) {
   m.def("kv_append", &kv_append);
   m.def("decode_prep_append", &decode_prep_append);
+  m.def("softcap_logits", &softcap_logits);
   m.def("paged_decode_attention", &paged_decode_attention);
 }

@@ -568,7 +568,7 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_kernel(const bf16* __
                                                                   const bf16* __restrict__ ve,
                                                                   const bf16* __restrict__ gw, bf16* __restrict__ v,
                                                                   long long ldv, bf16* __restrict__ gate, int tokens,
-                                                                  int KV, int D) {
+                                                                  int KV, int D, const int* __restrict__ ids) {
   const long long wid = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   if (wid >= static_cast<long long>(tokens) * KV) return;
   const int lane = threadIdx.x & 31;
@@ -579,7 +579,7 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_kernel(const bf16* __
   const float g = 3.0f / (1.0f + __expf(-pre));
   if (lane == 0) gate[static_cast<long long>(tok) * KV + kh] = f2b(g);
   bf16* vp = v + static_cast<long long>(tok) * ldv + kh * D;
-  const bf16* ep = ve + (static_cast<long long>(tok) * KV + kh) * D;
+  const bf16* ep = ve + (static_cast<long long>(ids ? ids[tok] : tok) * KV + kh) * D;
   for (int d = lane; d < D; d += 32) vp[d] = f2b(b2f(vp[d]) + g * b2f(ep[d]));
 }
 
@@ -632,7 +632,8 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_vec_kernel(const bf16
                                                                       const bf16* __restrict__ ve,
                                                                       const bf16* __restrict__ gw, bf16* __restrict__ v,
                                                                       long long ldv, bf16* __restrict__ gate,
-                                                                      int tokens, int KV, int D) {
+                                                                      int tokens, int KV, int D,
+                                                                      const int* __restrict__ ids) {
   const int lane = threadIdx.x & 31, li = lane & 15;
   const long long pair = (static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   const bool valid = pair < static_cast<long long>(tokens) * KV;
@@ -646,7 +647,8 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_vec_kernel(const bf16
   const int d = li * 8;
   if (d >= D) return;
   bf16* vp = v + static_cast<long long>(tok) * ldv + kh * D + d;
-  const uint4 ev = *reinterpret_cast<const uint4*>(ve + (static_cast<long long>(tok) * KV + kh) * D + d);
+  // with `ids` the embedding rows are gathered from the table on the fly (decode: no separate gather pass)
+  const uint4 ev = *reinterpret_cast<const uint4*>(ve + (static_cast<long long>(ids ? ids[tok] : tok) * KV + kh) * D + d);
   const uint4 vv = *reinterpret_cast<const uint4*>(vp);
   const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
   uint32_t o[4];
@@ -1181,15 +1183,15 @@ void qk_prep_bwd(const bf16* pre, long long ld_pre, const bf16* grad, long long 
                                                              seq, heads, D, eps, scale);
 }
 void value_gate_fwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, bf16* v, long long ldv,
-                    bf16* gate, int tokens, int KV, int D, cudaStream_t s) {
+                    bf16* gate, int tokens, int KV, int D, cudaStream_t s, const int* ids) {
   const long long n = static_cast<long long>(tokens) * KV;
   if (n <= 0) return;
   if (D % 8 == 0 && D <= 128 && ldv % 8 == 0 && aligned16(v) && aligned16(ve)) {
     value_gate_fwd_vec_kernel<<<blocks_for_rows((n + 1) / 2), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens,
-                                                                                KV, D);
+                                                                                KV, D, ids);
     return;
   }
-  value_gate_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens, KV, D);
+  value_gate_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens, KV, D, ids);
 }
 void value_gate_bwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, const bf16* gate, const bf16* dv,
                     long long lddv, bf16* dve, float* dh12, float* dgw, int tokens, int KV, int D, cudaStream_t s) {

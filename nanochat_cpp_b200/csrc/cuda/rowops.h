@@ -45,7 +45,8 @@ void qk_prep_bwd(const bf16* pre, long long ld_pre, const bf16* grad, long long 
 
 // v += 3*sigmoid(h[:, :12] . w[kh]) * ve  (in place on v); gate saved as bf16 [tokens, KV]
 void value_gate_fwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, bf16* v, long long ldv,
-                    bf16* gate, int tokens, int KV, int D, cudaStream_t s);
+                    bf16* gate, int tokens, int KV, int D, cudaStream_t s,
+                    const int* ids = nullptr);   // ids: `ve` is an embedding table [vocab, KV * D], row ids[tok] is used
 void value_gate_bwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, const bf16* gate, const bf16* dv,
                     long long lddv, bf16* dve, float* dh12, float* dgw, int tokens, int KV, int D, cudaStream_t s);
 

@@ -196,6 +196,22 @@ Tensor value_gate_fwd(const Tensor& h, const Tensor& ve, const Tensor& gate_w, T
   nc::value_gate_fwd(bp(h), h.stride(0), bp(ve), bp(gate_w), bpm(v), v.stride(0), bpm(gate), h.size(0), KV, D, cur());
   return gate;
 }
+// Same with the value-embedding rows gathered inside the kernel: table [vocab, KV * D], ids int32 [tokens].
+Tensor value_gate_fwd_gather(const Tensor& h, const Tensor& ids, const Tensor& table, const Tensor& gate_w, Tensor& v,
+                             int64_t D) {
+  chk_rows(h, "h");
+  chk_rows(v, "v");
+  TORCH_CHECK(table.is_contiguous() && gate_w.is_contiguous() && table.scalar_type() == torch::kBFloat16 &&
+                  ids.scalar_type() == torch::kInt32 && ids.is_contiguous() && ids.numel() == h.size(0),
+              "value_gate_fwd_gather");
+  const c10::cuda::CUDAGuard g(h.device());
+  const int KV = gate_w.size(0);
+  TORCH_CHECK(table.size(1) == KV * D, "value_gate_fwd_gather: table width");
+  Tensor gate = torch::empty({h.size(0), KV}, h.options());
+  nc::value_gate_fwd(bp(h), h.stride(0), bp(table), bp(gate_w), bpm(v), v.stride(0), bpm(gate), h.size(0), KV, D, cur(),
+                     ids.data_ptr<int>());
+  return gate;
+}
 std::vector<Tensor> value_gate_bwd(const Tensor& h, const Tensor& ve, const Tensor& gate_w, const Tensor& gate,
                                    const Tensor& dv, int64_t D) {
   chk_rows(h, "h");
@@ -325,6 +341,7 @@ void register_rowops(pybind11::module_& m) {
   m.def("qk_prep_bwd_one", &qk_prep_bwd_one);
   m.def("value_gate_fwd", &value_gate_fwd);
   m.def("value_gate_bwd", &value_gate_bwd);
+  m.def("value_gate_fwd_gather", &value_gate_fwd_gather);
   m.def("smear_fwd", &smear_fwd);
   m.def("smear_bwd", &smear_bwd);
   m.def("embedding_fwd", &embedding_fwd);

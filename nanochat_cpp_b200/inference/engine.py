@@ -115,8 +115,12 @@ class InferenceEngine:
                 k_pre = ops.linear_fwd(h, m._w(i, "attn.c_k"))
                 v = ops.linear_fwd(h, m._w(i, "attn.c_v"))
             if cfg.has_value_embedding(i):
-                ve = ops.embedding_fwd(tok, P.v(f"value_embeds.{i}.weight"))
-                v, _ = ops.value_gate_fwd(h, ve, m._w(i, "attn.ve_gate"), v, D)
+                if fused_prologue:      # the gate kernel reads the embedding rows straight from the table
+                    v, _ = ops.cuda_module().value_gate_fwd_gather(h, tok, P.v(f"value_embeds.{i}.weight"),
+                                                                   m._w(i, "attn.ve_gate"), v, D)
+                else:
+                    ve = ops.embedding_fwd(tok, P.v(f"value_embeds.{i}.weight"))
+                    v, _ = ops.value_gate_fwd(h, ve, m._w(i, "attn.ve_gate"), v, D)
             wl = cfg.window_left(i)
             if fused_prologue and wqkv is not None:
                 # one launch: q / k preparation, k and v appended to their pages; q comes back dense
@@ -162,6 +166,8 @@ class InferenceEngine:
     def _logits(self, xn_rows: torch.Tensor) -> torch.Tensor:
         """Soft-capped logits over the real vocabulary, fp32."""
         lg = ops.linear_fwd(xn_rows.contiguous(), self.model.params.v("lm_head.weight"))
+        if lg.is_cuda and ops.get_mode() == "kernels" and self.cfg.vocab_size % 2 == 0:
+            return ops.cuda_module().softcap_logits(lg, self.cfg.vocab_size, LOGIT_SOFTCAP)
         z = lg[:, : self.cfg.vocab_size].float()
         return LOGIT_SOFTCAP * torch.tanh(z / LOGIT_SOFTCAP)
 

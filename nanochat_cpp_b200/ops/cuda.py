@@ -285,6 +285,12 @@ def value_gate_fwd(h, ve, gate_w, v, head_dim):
     return v, gate
 
 
+def value_gate_fwd_gather(h, ids, table, gate_w, v, head_dim):
+    """`value_gate_fwd(h, table[ids], ...)` without materialising the gathered rows (decode)."""
+    gate = _C.value_gate_fwd_gather(h, ids, table, gate_w.contiguous(), v, head_dim)   # v updated in place
+    return v, gate
+
+
 def value_gate_bwd(h, ve, gate_w, gate, dv, head_dim):
     dve, dh12, dgw = _C.value_gate_bwd(h, ve, gate_w.contiguous(), gate, dv, head_dim)
     return dve, dh12, dgw
@@ -431,6 +437,11 @@ muon_update = ref.muon_update
 # ---------------------------------------------------------------------------
 def kv_append(k_pool, v_pool, page_table, positions, k_new, v_new):
     _C.kv_append(k_pool, v_pool, page_table, positions.contiguous(), k_new, v_new)
+
+
+def softcap_logits(logits_bf16, vocab, cap):
+    """fp32 cap * tanh(logits[:, :vocab] / cap) in one pass over the bf16 logits."""
+    return _C.softcap_logits(logits_bf16, int(vocab), float(cap))
 
 
 def decode_prep_append(qk_rows, v_rows, cos, sin, positions, k_pool, v_pool, page_table, num_heads,

@@ -100,3 +100,24 @@ def test_decode_prologue_matches_qk_prep_and_kv_append(H, KV):
         assert torch.equal(q_new, q_ref.reshape(B, H, D))
         assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
     K.check_status()
+
+
+def test_gather_fused_value_gate_and_softcap_match_their_compositions():
+    K = _K()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    B, KV, D, hidden, vocab = 7, 2, 128, 512, 1000
+    h = torch.randn(B, hidden, device="cuda", generator=g).to(torch.bfloat16)
+    table = torch.randn(vocab, KV * D, device="cuda", generator=g).to(torch.bfloat16)
+    gw = (torch.randn(KV, 12, device="cuda", generator=g) * 0.3).to(torch.bfloat16)
+    ids = torch.randint(0, vocab, (B,), device="cuda", generator=g).to(torch.int32)
+    wide = torch.randn(B, 3 * KV * D, device="cuda", generator=g).to(torch.bfloat16)
+    v_a, v_b = wide.clone()[:, KV * D: 2 * KV * D], wide.clone()[:, KV * D: 2 * KV * D]      # strided rows
+    _, gate_a = K.value_gate_fwd(h, K.embedding_fwd(ids, table), gw, v_a, D)
+    _, gate_b = K.value_gate_fwd_gather(h, ids, table, gw, v_b, D)
+    assert torch.equal(v_a, v_b) and torch.equal(gate_a, gate_b)
+    lg = (torch.randn(B, 1024, device="cuda", generator=g) * 20).to(torch.bfloat16)
+    want = 15.0 * torch.tanh(lg[:, :vocab].float() / 15.0)
+    got = K.softcap_logits(lg, vocab, 15.0)
+    assert got.dtype == torch.float32 and got.shape == (B, vocab)
+    assert (got - want).abs().max() <= 2e-5
+    K.check_status()
