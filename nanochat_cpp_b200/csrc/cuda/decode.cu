@@ -79,6 +79,8 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
   constexpr int GROUPS = kDecodeWarps * KPW;
   __shared__ float sm_m[G][GROUPS], sm_l[G][GROUPS];
   __shared__ float sm_acc[G][GROUPS][D];
+  // the projection GEMM behind this kernel (programmatic serialization) may set itself up while keys are streamed
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int len = seq_lens[b];
   if (len <= 0) return;

@@ -95,6 +95,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in the
+// stream is still running; `pdl_wait` returns once that kernel has completed and its writes are visible, so
+// everything before it (barrier init, TMEM allocation, descriptor prefetch) overlaps the predecessor's tail.
+// `pdl_launch_dependents` lets the next kernel in the stream start its own preamble early. Both are no-ops for
+// kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- cross-GPU flags
 constexpr unsigned long long kPeerWaitBudgetNs = 20000000000ull;  // 20 s: a peer may be a whole step behind
 

@@ -82,6 +82,8 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const bf16* __restric
                                                            bf16* __restrict__ y, float* __restrict__ rstd, int rows,
                                                            int dim, float eps, uint8_t* __restrict__ yq = nullptr,
                                                            uint8_t* __restrict__ sf = nullptr) {
+  // a GEMM launched behind this kernel with programmatic serialization may set itself up while the rows are normed
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
