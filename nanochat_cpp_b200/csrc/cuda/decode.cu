@@ -13,7 +13,17 @@
 
 #include "decode.h"
 
+#include <atomic>
+
+#include "pdl_launch.h"
+
 namespace nc {
+
+namespace {
+std::atomic<bool> g_pdl{false};
+}
+bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed); }
+void set_pdl_enabled(bool on) { g_pdl.store(on, std::memory_order_relaxed); }
 
 namespace {
 
@@ -81,6 +91,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
   __shared__ float sm_acc[G][GROUPS][D];
   // the projection GEMM behind this kernel (programmatic serialization) may set itself up while keys are streamed
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // q and the appended K / V row come from the kernel before
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int len = seq_lens[b];
   if (len <= 0) return;
@@ -241,11 +252,9 @@ const char* launch_decode(const DecodeArgs& a, cudaStream_t s) {
   const int G = a.H / a.KV;
   const float sl2 = a.scale * 1.4426950408889634f;
 #define NC_DECODE(GV)                                                                                                \
-  paged_decode_kernel<D, GV><<<grid, kDecodeWarps * 32, 0, s>>>(a.q, a.k_pool, a.v_pool, a.page_table, a.max_pages, \
-                                                                a.seq_lens, a.H, a.KV, a.page_size, a.window_left,  \
-                                                                sl2, splits, a.part_acc, a.part_ml, a.out,          \
-                                                                a.q_stride_b > 0 ? a.q_stride_b                     \
-                                                                                 : static_cast<long long>(a.H) * D)
+  launch_maybe_pdl(paged_decode_kernel<D, GV>, grid, dim3(kDecodeWarps * 32), 0, s, a.q, a.k_pool, a.v_pool,          \
+                   a.page_table, a.max_pages, a.seq_lens, a.H, a.KV, a.page_size, a.window_left, sl2, splits,        \
+                   a.part_acc, a.part_ml, a.out, a.q_stride_b > 0 ? a.q_stride_b : static_cast<long long>(a.H) * D)
   switch (G) {
     case 1: NC_DECODE(1); break;
     case 2: NC_DECODE(2); break;
@@ -274,6 +283,8 @@ __global__ void __launch_bounds__(256) decode_prep_append_kernel(
     __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int tokens, int H, int KV, float eps,
     float scale) {
   constexpr int D = 128;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // the fused projection row comes from the kernel before
   const int groups = (H + KV + 3) / 4;                  // head groups of the q / k part
   const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (unit >= tokens * (groups + 1)) return;
@@ -367,10 +378,9 @@ const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const _
         reinterpret_cast<uintptr_t>(sinT)) & 15))
     return "decode_prep_append: rows must be 16-byte aligned";
   const int units = tokens * ((H + KV + 3) / 4 + 1);
-  decode_prep_append_kernel<<<(units + 7) / 8, 256, 0, s>>>(qk, ld_qk, v, ld_v, cosT, sinT, positions, page_table,
-                                                            max_pages, page_size, q_out, k_pool, v_pool, tokens, H, KV,
-                                                            eps, scale);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_maybe_pdl(decode_prep_append_kernel, dim3((units + 7) / 8), dim3(256), 0, s, qk, ld_qk, v,
+                                         ld_v, cosT, sinT, positions, page_table, max_pages, page_size, q_out, k_pool,
+                                         v_pool, tokens, H, KV, eps, scale);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 

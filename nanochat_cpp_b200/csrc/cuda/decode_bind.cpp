@@ -4,6 +4,7 @@
 #include <torch/extension.h>
 
 #include "decode.h"
+#include "pdl_launch.h"
 
 namespace {
 
@@ -114,5 +115,7 @@ void register_decode(pybind11::module_& m) {
   m.def("kv_append", &kv_append);
   m.def("decode_prep_append", &decode_prep_append);
   m.def("softcap_logits", &softcap_logits);
+  m.def("set_pdl_enabled", [](bool on) { nc::set_pdl_enabled(on); });
+  m.def("pdl_enabled", []() { return nc::pdl_enabled(); });
   m.def("paged_decode_attention", &paged_decode_attention);
 }

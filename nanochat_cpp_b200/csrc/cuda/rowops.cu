@@ -8,6 +8,7 @@
 #include "rowops.h"
 
 #include "mx_quant.cuh"
+#include "pdl_launch.h"
 
 #include <math_constants.h>
 
@@ -84,6 +85,7 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const bf16* __restric
                                                            uint8_t* __restrict__ sf = nullptr) {
   // a GEMM launched behind this kernel with programmatic serialization may set itself up while the rows are normed
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialization
   const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -636,6 +638,8 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_vec_kernel(const bf16
                                                                       long long ldv, bf16* __restrict__ gate,
                                                                       int tokens, int KV, int D,
                                                                       const int* __restrict__ ids) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialization
   const int lane = threadIdx.x & 31, li = lane & 15;
   const long long pair = (static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   const bool valid = pair < static_cast<long long>(tokens) * KV;
@@ -1133,8 +1137,8 @@ inline int flat_grid(long long n) {
 void rmsnorm_fwd(const bf16* x, long long ldx, bf16* y, float* rstd, int rows, int dim, float eps, cudaStream_t s,
                  uint8_t* yq, uint8_t* sf) {
   if (rows <= 0) return;
-  rmsnorm_kernel<0><<<blocks_for_rows(rows), kThreads, 0, s>>>(x, ldx, nullptr, nullptr, nullptr, nullptr, y, rstd,
-                                                               rows, dim, eps, yq, sf);
+  launch_maybe_pdl(rmsnorm_kernel<0>, dim3(blocks_for_rows(rows)), dim3(kThreads), 0, s, x, ldx, nullptr, nullptr, nullptr,
+                   nullptr, y, rstd, rows, dim, eps, yq, sf);
 }
 void rmsnorm_apply(const bf16* x, long long ldx, const float* rstd, bf16* y, int rows, int dim, cudaStream_t s) {
   if (rows <= 0) return;
@@ -1149,8 +1153,8 @@ void rmsnorm_bwd(const bf16* x, const bf16* dy, const float* rstd, const bf16* r
 void blend_norm_fwd(const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* xr, bf16* h,
                     float* rstd, int rows, int dim, float eps, cudaStream_t s, uint8_t* hq, uint8_t* sf) {
   if (rows <= 0) return;
-  rmsnorm_kernel<2><<<blocks_for_rows(rows), kThreads, 0, s>>>(x, dim, x0, lam_r, lam_0, xr, h, rstd, rows, dim, eps, hq,
-                                                               sf);
+  launch_maybe_pdl(rmsnorm_kernel<2>, dim3(blocks_for_rows(rows)), dim3(kThreads), 0, s, x, static_cast<long long>(dim),
+                   x0, lam_r, lam_0, xr, h, rstd, rows, dim, eps, hq, sf);
 }
 void blend_bwd(const bf16* dxr, const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* dx,
                bf16* dx0, bool accumulate_dx0, float* dlam2, long long n, cudaStream_t s) {
@@ -1189,8 +1193,8 @@ void value_gate_fwd(const bf16* h, long long ldh, const bf16* ve, const bf16* ga
   const long long n = static_cast<long long>(tokens) * KV;
   if (n <= 0) return;
   if (D % 8 == 0 && D <= 128 && ldv % 8 == 0 && aligned16(v) && aligned16(ve)) {
-    value_gate_fwd_vec_kernel<<<blocks_for_rows((n + 1) / 2), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens,
-                                                                                KV, D, ids);
+    launch_maybe_pdl(value_gate_fwd_vec_kernel, dim3(blocks_for_rows((n + 1) / 2)), dim3(kThreads), 0, s, h, ldh, ve,
+                     gate_w, v, ldv, gate, tokens, KV, D, ids);
     return;
   }
   value_gate_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens, KV, D, ids);

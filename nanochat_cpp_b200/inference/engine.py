@@ -184,8 +184,15 @@ class InferenceEngine:
     @torch.no_grad()
     def decode(self, cache: PagedKVCache, tokens: torch.Tensor) -> torch.Tensor:
         """tokens [B]: one new token per sequence. Returns logits [B, vocab]."""
-        xn = self._forward(cache, tokens.view(-1, 1), decode=True)
-        return self._logits(xn)
+        pdl = self.device.type == "cuda" and ops.get_mode() == "kernels"
+        if pdl:     # the step's small kernels are launched so that each is resident before the one before it ends
+            ops.cuda_module()._C.set_pdl_enabled(True)
+        try:
+            xn = self._forward(cache, tokens.view(-1, 1), decode=True)
+            return self._logits(xn)
+        finally:
+            if pdl:
+                ops.cuda_module()._C.set_pdl_enabled(False)
 
     # ------------------------------------------------------------------ CUDA-graph decode
     @torch.no_grad()
