@@ -16,6 +16,7 @@
 #include <cstdlib>
 
 #include "gemm_tcgen05.h"
+#include "pdl_launch.h"
 #include "ptx.cuh"
 #include "tmap.h"
 
@@ -41,6 +42,7 @@ struct SkinnyParams {
   long long ldc, ldr;
   int epi;
   int* status;
+  int early_w;   // weight tiles may be requested before the previous kernel of the stream has finished
 };
 
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
@@ -90,15 +92,28 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // everything above overlapped the tail of the previous kernel; its outputs (x, the residual) are read below
+  // Everything above overlapped the tail of the previous kernel; its outputs (x, the residual) are read below, after
+  // pdl_wait. With `early_w` (decode: the weights are not written by anything in the step) the producer also requests
+  // the weight tiles of its first ring-full of K blocks before waiting, so most of the weight stream of a short K
+  // overlaps the previous kernel as well; the x tiles of those stages follow after the wait, on the same barriers.
+  int early = 0;
+  if (warp == 0 && lane == 0 && p.early_w) {
+    early = min(STAGES, my_kbs);
+    for (int i = 0; i < early; ++i) {
+      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+      tma_load_3d(smem + i * STAGE_BYTES, &tmW, &full_bar[i], (kb0 + i) * BK, n0, 0);
+    }
+  }
   pdl_wait();
   pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int i = 0; i < early; ++i)
+        tma_load_3d(smem + i * STAGE_BYTES + W_BYTES, &tmX, &full_bar[i], (kb0 + i) * BK, 0, 0);
+      int stage = early == STAGES ? 0 : early;
+      uint32_t phase = early == STAGES ? 1 : 0;
+      for (int kb = kb0 + early; kb < kb1; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrWaitEmpty)) break;
         uint8_t* sw = smem + stage * STAGE_BYTES;
         mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
@@ -242,6 +257,7 @@ const char* gemm_skinny(const GemmArgs& a, cudaStream_t stream) {
   p.C = static_cast<__nv_bfloat16*>(a.C), p.C2 = static_cast<__nv_bfloat16*>(a.C2);
   p.R = static_cast<const __nv_bfloat16*>(a.R);
   p.ldc = a.ldc, p.ldr = a.ldr, p.epi = a.epi, p.status = a.status;
+  p.early_w = pdl_enabled() ? 1 : 0;   // the inference engine turns this on around a decode step (static weights)
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
