@@ -44,8 +44,9 @@ def main():
     cache = eng.new_cache(args.prompts, args.prompt_len + args.new_tokens + 1)
     # warm-up (also builds tensor maps and the decode graph)
     logits = eng.prefill(cache, prompts)
+    nxt = logits.argmax(-1)
     for _ in range(3):
-        logits = eng.decode_graphed(cache, logits.argmax(-1))
+        nxt = eng.decode_graphed(cache, nxt, greedy=True)
     torch.cuda.synchronize()
     cache.reset()
     if world > 1:
@@ -62,8 +63,7 @@ def main():
     for _ in range(args.new_tokens):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        logits = eng.decode_graphed(cache, nxt)
-        nxt = logits.argmax(-1)
+        nxt = eng.decode_graphed(cache, nxt, greedy=True)     # next token ids straight from the step (greedy)
         b.record()
         b.synchronize()
         lat.append(a.elapsed_time(b))

@@ -365,6 +365,47 @@ void softcap_logits(const __nv_bfloat16* lg, long long ld, float* out, int rows,
   softcap_logits_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, s>>>(lg, ld, out, rows, vocab, cap);
 }
 
+// out[r] = index of the largest of logits[r, 0 .. vocab): greedy decoding straight from the bf16 logits (the soft
+// cap is monotonic, so the fp32 capped copy is not needed). Ties go to the lowest index, as in the definition.
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* __restrict__ lg, long long ld, int vocab,
+                                                          long long* __restrict__ out) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const __nv_bfloat16* row = lg + static_cast<long long>(blockIdx.x) * ld;
+  float best = -CUDART_INF_F;
+  int arg = 0x7fffffff;
+  const bool vec = (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(lg) & 15) == 0);
+  const int vend = vec ? (vocab / 8) * 8 : 0;
+  for (int c = threadIdx.x * 8; c < vend; c += 256 * 8) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(row + c), f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (f[e] > best) best = f[e], arg = c + e;   // ascending scan: the first of equal values stays
+  }
+  for (int c = vend + threadIdx.x; c < vocab; c += 256) {
+    const float v = __bfloat162float(row[c]);
+    if (v > best || (v == best && c < arg)) best = v, arg = c;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+    if (ov > best || (ov == best && oi < arg)) best = ov, arg = oi;
+  }
+  if ((threadIdx.x & 31) == 0) sv[threadIdx.x >> 5] = best, si[threadIdx.x >> 5] = arg;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < arg)) best = sv[w], arg = si[w];
+    out[blockIdx.x] = arg == 0x7fffffff ? 0 : arg;   // a row of NaNs or -inf: index 0
+  }
+}
+void argmax_rows(const __nv_bfloat16* lg, long long ld, long long* out, int rows, int vocab, cudaStream_t s) {
+  if (rows <= 0 || vocab <= 0) return;
+  argmax_rows_kernel<<<rows, 256, 0, s>>>(lg, ld, vocab, out);
+}
+
 const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const __nv_bfloat16* v, long long ld_v,
                                const float* cosT, const float* sinT, const int* positions, const int* page_table,
                                int max_pages, int page_size, __nv_bfloat16* q_out, __nv_bfloat16* k_pool,

@@ -45,6 +45,9 @@ const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const _
 // out fp32 [rows, vocab] = cap * tanh(logits[:, :vocab] / cap); logits bf16 rows with leading dimension ld; vocab even.
 void softcap_logits(const __nv_bfloat16* logits, long long ld, float* out, int rows, int vocab, float cap, cudaStream_t s);
 
+// out[r] = argmax over logits[r, 0 .. vocab) (lowest index among equal values); logits bf16 rows, leading dimension ld.
+void argmax_rows(const __nv_bfloat16* logits, long long ld, long long* out, int rows, int vocab, cudaStream_t s);
+
 const char* paged_decode_attention(const DecodeArgs& args, cudaStream_t s);
 
 }  // namespace nc

@@ -73,6 +73,17 @@ Tensor softcap_logits(const Tensor& logits, int64_t vocab, double cap) {
   return out;
 }
 
+Tensor argmax_rows(const Tensor& logits, int64_t vocab) {
+  const c10::cuda::CUDAGuard g(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == torch::kBFloat16 && logits.stride(1) == 1 &&
+                  vocab <= logits.size(1) && vocab > 0,
+              "argmax_rows: bf16 [rows, >= vocab]");
+  Tensor out = torch::empty({logits.size(0)}, logits.options().dtype(torch::kInt64));
+  nc::argmax_rows(bp(logits), logits.stride(0), reinterpret_cast<long long*>(out.data_ptr<int64_t>()), logits.size(0),
+                  static_cast<int>(vocab), at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
 Tensor paged_decode_attention(const Tensor& q, const Tensor& k_pool, const Tensor& v_pool, const Tensor& page_table,
                               const Tensor& seq_lens, int64_t window_left, double scale) {
   const c10::cuda::CUDAGuard g(q.device());
@@ -115,6 +126,7 @@ void register_decode(pybind11::module_& m) {
   m.def("kv_append", &kv_append);
   m.def("decode_prep_append", &decode_prep_append);
   m.def("softcap_logits", &softcap_logits);
+  m.def("argmax_rows", &argmax_rows);
   m.def("set_pdl_enabled", [](bool on) { nc::set_pdl_enabled(on); });
   m.def("pdl_enabled", []() { return nc::pdl_enabled(); });
   m.def("paged_decode_attention", &paged_decode_attention);

@@ -163,6 +163,14 @@ class InferenceEngine:
         xn, _ = ops.rmsnorm_fwd(x_pre)
         return xn
 
+    def _greedy(self, xn_rows: torch.Tensor) -> torch.Tensor:
+        """Token ids of the largest logit per row (int64). The soft cap is monotonic, so on the kernel path the
+        arg-max is taken over the bf16 logits directly and the fp32 capped copy is never made."""
+        lg = ops.linear_fwd(xn_rows.contiguous(), self.model.params.v("lm_head.weight"))
+        if lg.is_cuda and ops.get_mode() == "kernels":
+            return ops.cuda_module().argmax_rows(lg, self.cfg.vocab_size)
+        return lg[:, : self.cfg.vocab_size].float().argmax(dim=-1)
+
     def _logits(self, xn_rows: torch.Tensor) -> torch.Tensor:
         """Soft-capped logits over the real vocabulary, fp32."""
         lg = ops.linear_fwd(xn_rows.contiguous(), self.model.params.v("lm_head.weight"))
@@ -182,26 +190,27 @@ class InferenceEngine:
         return self._logits(xn.view(B, T, -1)[:, -1])
 
     @torch.no_grad()
-    def decode(self, cache: PagedKVCache, tokens: torch.Tensor) -> torch.Tensor:
-        """tokens [B]: one new token per sequence. Returns logits [B, vocab]."""
+    def decode(self, cache: PagedKVCache, tokens: torch.Tensor, greedy: bool = False) -> torch.Tensor:
+        """tokens [B]: one new token per sequence. Returns logits [B, vocab], or with `greedy` the next token ids
+        [B] (int64) without materialising the logits in fp32."""
         pdl = self.device.type == "cuda" and ops.get_mode() == "kernels"
         if pdl:     # the step's small kernels are launched so that each is resident before the one before it ends
             ops.cuda_module()._C.set_pdl_enabled(True)
         try:
             xn = self._forward(cache, tokens.view(-1, 1), decode=True)
-            return self._logits(xn)
+            return self._greedy(xn) if greedy else self._logits(xn)
         finally:
             if pdl:
                 ops.cuda_module()._C.set_pdl_enabled(False)
 
     # ------------------------------------------------------------------ CUDA-graph decode
     @torch.no_grad()
-    def decode_graphed(self, cache: PagedKVCache, tokens: torch.Tensor) -> torch.Tensor:
+    def decode_graphed(self, cache: PagedKVCache, tokens: torch.Tensor, greedy: bool = False) -> torch.Tensor:
         """Same as `decode`; the step is captured once per (cache, batch) and replayed. Falls back to the eager
         step when capture is not possible."""
         if not self.use_cuda_graph:
-            return self.decode(cache, tokens)
-        key = (id(cache), tokens.shape[0])
+            return self.decode(cache, tokens, greedy)
+        key = (id(cache), tokens.shape[0], bool(greedy))
         if self._graph_key != key:
             self._graph = None
             self._graph_key = key
@@ -212,14 +221,14 @@ class InferenceEngine:
                 s = torch.cuda.Stream()
                 s.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(s):
-                    self.decode(cache, self._static_tok)
+                    self.decode(cache, self._static_tok, greedy)
                 torch.cuda.current_stream().wait_stream(s)
                 cache.seq_lens.copy_(lens)
                 cache.prev_emb.copy_(prev)
                 cache.has_prev = had
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
-                    self._static_out = self.decode(cache, self._static_tok)
+                    self._static_out = self.decode(cache, self._static_tok, greedy)
                 cache.seq_lens.copy_(lens)
                 cache.prev_emb.copy_(prev)
                 cache.has_prev = had
@@ -228,7 +237,7 @@ class InferenceEngine:
                 self._graph = None
                 self.use_cuda_graph = False
                 torch.cuda.synchronize()
-                return self.decode(cache, tokens)
+                return self.decode(cache, tokens, greedy)
         self._static_tok.copy_(tokens)
         self._graph.replay()
         cache.has_prev = True
@@ -299,8 +308,11 @@ def generate_multi(engine: InferenceEngine, prompts: torch.Tensor, params: Gener
     row_ids = torch.arange(rows, device=dev)
     stops = {s for s in (params.stop_id, params.bos_id, *params.stop_ids) if s is not None and s >= 0}
     stop_t = torch.tensor(sorted(stops), device=dev, dtype=torch.int64) if stops else None
+    # greedy decoding without forced tokens never needs the logits after the prefill: the step returns token ids
+    greedy_ids = (not params.temperature > 0.0) and forced is None
+    pred = None
     for step in range(params.max_tokens):
-        nxt = sample(logits, params.temperature, params.top_k, params.seed, row_ids, step)
+        nxt = pred if pred is not None else sample(logits, params.temperature, params.top_k, params.seed, row_ids, step)
         was_forced = [False] * rows
         if forced is not None:
             host = nxt.tolist()
@@ -322,7 +334,10 @@ def generate_multi(engine: InferenceEngine, prompts: torch.Tensor, params: Gener
                 out[r].mask.append(0 if was_forced[r] else 1)
         if step + 1 == params.max_tokens:
             break
-        logits = engine.decode_graphed(cache, nxt) if forced is None else engine.decode(cache, nxt)
+        if greedy_ids:
+            pred = engine.decode_graphed(cache, nxt, greedy=True)
+        else:
+            logits = engine.decode_graphed(cache, nxt) if forced is None else engine.decode(cache, nxt)
     return out
 
 

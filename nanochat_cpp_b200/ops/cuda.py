@@ -444,6 +444,11 @@ def softcap_logits(logits_bf16, vocab, cap):
     return _C.softcap_logits(logits_bf16, int(vocab), float(cap))
 
 
+def argmax_rows(logits_bf16, vocab):
+    """int64 [rows]: argmax over logits[:, :vocab] (lowest index among equal values)."""
+    return _C.argmax_rows(logits_bf16, int(vocab))
+
+
 def decode_prep_append(qk_rows, v_rows, cos, sin, positions, k_pool, v_pool, page_table, num_heads,
                        eps=RMS_EPS, scale=QK_SCALE):
     """Decode prologue in one launch (head_dim 128, one token per sequence): `qk_prep_fwd` of the q and k heads of the

@@ -121,3 +121,16 @@ def test_gather_fused_value_gate_and_softcap_match_their_compositions():
     assert got.dtype == torch.float32 and got.shape == (B, vocab)
     assert (got - want).abs().max() <= 2e-5
     K.check_status()
+
+
+def test_argmax_rows_takes_the_first_of_equal_maxima():
+    K = _K()
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for rows, width, vocab in ((5, 1024, 1000), (3, 72, 65), (64, 4096, 4096)):
+        lg = torch.randn(rows, width, device="cuda", generator=g).to(torch.bfloat16)
+        lg[0, 7] = lg[0, vocab - 1] = 50.0                       # a tie: the lower index wins
+        lg[1, vocab:] = 99.0                                     # padding columns are ignored
+        got = K.argmax_rows(lg, vocab)
+        want = lg[:, :vocab].float().argmax(dim=-1)
+        assert got.dtype == torch.int64 and torch.equal(got, want) and int(got[0]) == 7
+    K.check_status()
