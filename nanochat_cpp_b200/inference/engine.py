@@ -89,17 +89,19 @@ class InferenceEngine:
         cache.prev_emb.copy_(emb.view(B, T, -1)[:, -1])
         # absolute positions of the new tokens
         pos = cache.seq_lens[:, None] + torch.arange(T, device=self.device, dtype=torch.int32)[None, :]
+        kernel_decode = decode and self.device.type == "cuda" and ops.get_mode() == "kernels"
         if decode:
             cos_all, sin_all = self._rope(cache.max_seq)
-            cos, sin = cos_all[pos.long()], sin_all[pos.long()]           # [B, 1, D/2] gathered per sequence
+            cos = sin = None
+            if not kernel_decode:      # the kernels index the tables by position themselves
+                cos, sin = cos_all[pos.long()], sin_all[pos.long()]       # [B, 1, D/2] gathered per sequence
             t0 = None
         else:
             t0 = int(cache.seq_lens[0].item())
             cos_all, sin_all = self._rope(t0 + T)
             cos, sin = cos_all[t0:t0 + T], sin_all[t0:t0 + T]
         new_lens = cache.seq_lens + T
-        fused_prologue = (decode and self.device.type == "cuda" and ops.get_mode() == "kernels" and D == 128
-                          and cache.page_table.shape[0] == B)
+        fused_prologue = kernel_decode and D == 128 and cache.page_table.shape[0] == B
         pos_flat = pos.reshape(-1).contiguous()
         x = x0
         x_backout = None
@@ -136,7 +138,7 @@ class InferenceEngine:
                     x_backout = x
                 continue
             q4, k4 = _heads(q_pre, B, T, H, D), _heads(k_pre, B, T, KV, D)
-            if decode and self.device.type == "cuda" and ops.get_mode() == "kernels":
+            if kernel_decode:
                 q, k = ops.cuda_module().qk_prep_fwd(q4, k4, cos_all, sin_all, positions=pos.reshape(-1).contiguous())
             else:
                 q, k = ops.qk_prep_fwd(q4, k4, cos, sin)
