@@ -627,6 +627,8 @@ def _misc_parsers(sub):
     ap = sub.add_parser("dist", help="launch one process per GPU: dist --world-size N -- <sub-command ...>")
     ap.add_argument("--world-size", type=int, required=True)
     ap.add_argument("--master-port", type=int, default=29500)
+    ap.add_argument("--max-restarts", type=int, default=0,
+                    help="start the group again after a failure, resuming from --checkpoint when it exists")
     ap.add_argument("rest", nargs=argparse.REMAINDER)
     ap.set_defaults(fn=cmd_dist)
 
@@ -642,24 +644,24 @@ def cmd_tok_train(a) -> int:
 
 def cmd_dist(a) -> int:
     """Rank 0 first, then the others (the reference's launcher order, python/nanochat_cpp/cli.py:827-945); the
-    children get both the torch and the NANOCHAT_* environment contract and one GPU each."""
+    children get both the torch and the NANOCHAT_* environment contract and one GPU each. The first rank that fails
+    stops the group; with `--max-restarts N` the group is started again (from `--checkpoint` when it exists)."""
+    from .parallel import launcher
     rest = [x for x in a.rest if x != "--"]
     if not rest:
         print("dist: nothing to launch", file=sys.stderr)
         return 2
-    procs = []
-    for r in range(a.world_size):
-        env = dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(a.world_size),
-                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(a.master_port), NANOCHAT_RANK=str(r),
-                   NANOCHAT_WORLD_SIZE=str(a.world_size), NANOCHAT_MASTER_ADDR="127.0.0.1",
-                   NANOCHAT_MASTER_PORT=str(a.master_port))
-        procs.append(subprocess.Popen([sys.executable, "-m", "nanochat_cpp_b200.cli"] + rest, env=env))
-        if r == 0:
-            time.sleep(0.5)
-    rc = 0
-    for p in procs:
-        rc = p.wait() or rc
-    return rc
+    envs = launcher.rank_environments(a.world_size, a.master_port)
+
+    def commands(attempt: int):
+        argv = launcher.with_resume(rest, attempt)
+        return [[sys.executable, "-m", "nanochat_cpp_b200.cli"] + argv for _ in range(a.world_size)]
+
+    res = launcher.run_group(commands, envs, max_restarts=a.max_restarts)
+    if res.returncode != 0:
+        print(f"[nanochat] dist: rank {res.failed_rank} failed with exit code {res.returncode} "
+              f"after {res.starts} start(s); the other ranks were stopped", file=sys.stderr)
+    return res.returncode
 
 
 def main(argv: Optional[List[str]] = None) -> int:

@@ -113,3 +113,36 @@ def test_collective_with_a_silent_peer_ends_with_an_error_not_a_hang():
     for p in procs:
         p.join(timeout=60)
     assert got[1] == "silent" and got[0].startswith("collective_error:")
+
+
+def test_launcher_stops_the_group_when_a_rank_fails_and_restarts_it(tmp_path):
+    """Process-group supervision with plain Python children: the failing rank's exit code comes back, a rank that
+    would run for a minute is stopped within seconds, a group that fails once succeeds on its second start, and a
+    restart adds --resume for an existing checkpoint."""
+    import sys
+    import time
+    from nanochat_cpp_b200.parallel import launcher
+    py = sys.executable
+    envs = launcher.rank_environments(2, 29671)
+    assert envs[1]["RANK"] == "1" and envs[1]["NANOCHAT_WORLD_SIZE"] == "2" and envs[0]["MASTER_ADDR"] == "127.0.0.1"
+    slow = [py, "-c", "import time; time.sleep(60)"]
+    bad = [py, "-c", "import os, sys; sys.exit(3 if os.environ['RANK'] == '1' else 0)"]
+    t0 = time.monotonic()
+    res = launcher.run_group_once([slow, bad], envs, grace_s=2.0, first_rank_head_start_s=0.1)
+    assert res.returncode == 3 and res.failed_rank == 1 and time.monotonic() - t0 < 20
+    assert res.exit_codes[0] not in (None, 0)                      # rank 0 was stopped, not left running
+    # a rank that never finishes: the deadline stops the group
+    res = launcher.run_group_once([slow, slow], envs, grace_s=2.0, first_rank_head_start_s=0.1, timeout_s=1.0)
+    assert res.returncode == 124 and res.failed_rank is None
+    # fails on the first start, succeeds on the second (a marker file plays the checkpoint)
+    marker = tmp_path / "ckpt"
+    flaky = [py, "-c", f"import os, sys; p = {str(marker)!r}; ok = os.path.exists(p); open(p, 'w').close(); "
+                       "sys.exit(0 if ok else 5)"]
+    starts = []
+    res = launcher.run_group(lambda attempt: (starts.append(attempt) or [flaky, [py, "-c", "pass"]]), envs,
+                             max_restarts=2, grace_s=2.0, first_rank_head_start_s=0.1)
+    assert res.returncode == 0 and res.starts == 2 and starts == [0, 1]
+    argv = ["train", "--checkpoint", str(marker), "--batch", "4"]
+    assert launcher.with_resume(argv, 0) == argv
+    assert launcher.with_resume(argv, 1) == argv + ["--resume", str(marker)]
+    assert launcher.with_resume(argv + ["--resume", "x"], 1) == argv + ["--resume", "x"]
