@@ -1,4 +1,5 @@
-"""Workflow sub-commands of the command line: build, test, check, devices, doctor, verify, bench, profile, attain.
+"""Workflow sub-commands of the command line: build, test, check, devices, doctor, verify, bench, profile, attain,
+seam, prune.
 
 The reference's `tools/nanochat` front end offers the same verbs around Bazel, a sandbox and a GPU queue
 (python/nanochat_cpp/cli.py: build, test, check, devices, doctor, verify, bench, profile, attain). Here they run in
@@ -155,6 +156,59 @@ def cmd_attain(a) -> int:
     return subprocess.call([sys.executable, "-m", "nanochat_cpp_b200.perf.attain"] + a.rest, cwd=ROOT)
 
 
+def seam_table() -> List[dict]:
+    """Every operator of the seam with where it is implemented: the PyTorch definition and, when the extension is
+    built, the sm_100a kernel (the reference's `seam` verb lists kernels.h entry points per backend)."""
+    from . import ops
+    try:
+        cuda_mod = ops.cuda_module()
+    except Exception:                      # extension not built: definitions only
+        cuda_mod = None
+    rows = []
+    for name in ops._NAMES:
+        has_kernel = False
+        if cuda_mod is not None:
+            try:
+                has_kernel = callable(getattr(cuda_mod, name))
+            except AttributeError:
+                has_kernel = False
+        rows.append({"operator": name, "definition": hasattr(ops.ref, name), "kernel": has_kernel})
+    return rows
+
+
+def cmd_seam(a) -> int:
+    rows = seam_table()
+    for r in rows:
+        print(json.dumps(r))
+    missing = [r["operator"] for r in rows if not r["definition"]]
+    return 1 if missing else 0
+
+
+def prune_checkpoints(directory: str, keep: int, pattern: str = "*.ckpt") -> List[str]:
+    """Delete all but the `keep` newest checkpoints matching `pattern` in `directory`, with their cursor sidecars
+    (files that start with the checkpoint's name). Returns the deleted paths."""
+    import glob
+    paths = sorted(glob.glob(os.path.join(directory, pattern)), key=os.path.getmtime, reverse=True)
+    removed = []
+    for path in paths[max(0, keep):]:
+        for victim in [path] + [q for q in glob.glob(path + "*") if q != path]:
+            os.remove(victim)
+            removed.append(victim)
+    return removed
+
+
+def cmd_prune(a) -> int:
+    """Remove stale native build objects (those no current source hashes to) and, with --checkpoints, old checkpoints."""
+    from . import build as b
+    before = set(os.listdir(b.BUILD_DIR)) if os.path.isdir(b.BUILD_DIR) else set()
+    if a.build:
+        b.build_all(verbose=False)         # compiling nothing new; its prune step drops objects of changed sources
+    after = set(os.listdir(b.BUILD_DIR)) if os.path.isdir(b.BUILD_DIR) else set()
+    removed = prune_checkpoints(a.checkpoints, a.keep) if a.checkpoints else []
+    print(json.dumps({"build_objects_removed": len(before - after), "checkpoints_removed": removed}))
+    return 0
+
+
 def register(sub) -> None:
     import argparse
     ap = sub.add_parser("build", help="compile the CUDA extension and the host runtime in-tree")
@@ -182,6 +236,13 @@ def register(sub) -> None:
     ap = sub.add_parser("profile", help="per-operator step profile")
     ap.add_argument("rest", nargs=argparse.REMAINDER)
     ap.set_defaults(fn=cmd_profile)
+    ap = sub.add_parser("seam", help="operators of the seam and where each is implemented")
+    ap.set_defaults(fn=cmd_seam)
+    ap = sub.add_parser("prune", help="drop stale build objects and old checkpoints")
+    ap.add_argument("--build", action="store_true", help="prune the native build cache")
+    ap.add_argument("--checkpoints", default="", help="directory of *.ckpt files")
+    ap.add_argument("--keep", type=int, default=3)
+    ap.set_defaults(fn=cmd_prune)
     ap = sub.add_parser("attain", help="attainment report against the roofline model")
     ap.add_argument("rest", nargs=argparse.REMAINDER)
     ap.set_defaults(fn=cmd_attain)

@@ -105,3 +105,24 @@ def test_workflow_commands_devices_doctor_bench_list(capsys):
     capsys.readouterr()
     assert cli.main(["verify"]) in (0, 1)          # 1 with a clear message when no GPU is visible
     assert "ok" in json.loads(capsys.readouterr().out.splitlines()[-1])
+
+
+def test_seam_and_prune_commands(tmp_path, capsys):
+    import json
+    import os
+    import time
+    from nanochat_cpp_b200 import cli, ops, tools_cli
+    assert cli.main(["seam"]) == 0
+    rows = [json.loads(l) for l in capsys.readouterr().out.splitlines()]
+    assert [r["operator"] for r in rows] == list(ops._NAMES) and all(r["definition"] for r in rows)
+    assert all(r["kernel"] for r in rows)          # the built extension has a kernel for every operator of the seam
+    for i in range(5):
+        p = tmp_path / f"step{i}.ckpt"
+        p.write_bytes(b"x")
+        (tmp_path / f"step{i}.ckpt.cursor").write_bytes(b"y")
+        os.utime(p, (time.time() + i, time.time() + i))
+    removed = tools_cli.prune_checkpoints(str(tmp_path), keep=2)
+    left = sorted(os.listdir(tmp_path))
+    assert left == ["step3.ckpt", "step3.ckpt.cursor", "step4.ckpt", "step4.ckpt.cursor"] and len(removed) == 6
+    assert cli.main(["prune", "--checkpoints", str(tmp_path), "--keep", "1"]) == 0
+    assert sorted(os.listdir(tmp_path)) == ["step4.ckpt", "step4.ckpt.cursor"]
