@@ -37,8 +37,11 @@ def main():
     ap.add_argument("--only", default="")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--variant", type=int, default=2)
+    ap.add_argument("--report", default="", help="write a nanochat.bench.v3 document here")
     args = ap.parse_args()
     out = open(args.json, "w") if args.json else None
+    from .report import BenchReport
+    report = BenchReport().use_device_peak("bf16")
     for name, B, T, H, KV, D, window, ref_f, ref_b in SHAPES:
         if args.only and args.only != name:
             continue
@@ -60,6 +63,13 @@ def main():
         print(json.dumps(row), flush=True)
         if out:
             out.write(json.dumps(row) + "\n")
+        shape = f"B={B} T={T} H={H} KV={KV} D={D} window={window}"
+        report.add("attention_fwd:" + name, shape, tf["median_ms"], f_flops / tf["median_ms"] / 1e6,
+                   iterations=args.iters, family="attention", phase="fwd")
+        report.add("attention_bwd:" + name, shape, tb["median_ms"], b_flops / tb["median_ms"] / 1e6,
+                   iterations=args.iters, family="attention", phase="bwd")
+    if args.report:
+        report.write(args.report)
     K.check_status()
 
 

@@ -3,7 +3,10 @@
 Counterpart of the reference's `gemm_benchmark` (docs/performance.md:167-203). Prints one JSON line per
 shape with both timings, TFLOP/s and the fraction of the measured cuBLAS peak.
 
-    python -m nanochat_cpp_b200.bench.gemm_bench --preset d20 [--tokens 65536] [--json out.jsonl]
+    python -m nanochat_cpp_b200.bench.gemm_bench --preset d20 [--tokens 65536] [--json out.jsonl] [--report out.json]
+
+`--report` also writes one `nanochat.bench.v3` document (family "linear", phase fwd / dgrad / wgrad, MFU against the
+measured cuBLAS burst rate).
 """
 from __future__ import annotations
 
@@ -40,6 +43,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=65536)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default="")
+    ap.add_argument("--report", default="", help="write a nanochat.bench.v3 document here")
     ap.add_argument("--only", default="", help="run a single row, e.g. fc.fwd")
     ap.add_argument("--no-lib", action="store_true", help="skip the cuBLAS timing")
     args = ap.parse_args()
@@ -51,6 +55,8 @@ def main():
         peaks = json.load(open(p))
     peak = float(peaks.get("bf16_tflops", 1590.0))
     out = open(args.json, "w") if args.json else None
+    from .report import BenchReport
+    report = BenchReport().use_device_peak("bf16")
     dev = "cuda"
     for name, kind, m, n, k in shapes_for(cfg, args.tokens):
         if args.only and args.only != name:
@@ -84,6 +90,11 @@ def main():
         print(json.dumps(row), flush=True)
         if out:
             out.write(json.dumps(row) + "\n")
+        report.add("gemm:" + name, f"M={m} N={n} K={k}", t_ours["median_ms"], fl / t_ours["median_ms"] / 1e6,
+                   iterations=args.iters, family="linear", phase=kind)
+    if args.report:
+        report.extras["preset"] = args.preset
+        report.write(args.report)
     K.check_status()
 
 
