@@ -11,10 +11,15 @@
 // (`tile_rows` = 128 for the activations, the kernel's BN for the weights) so that the atoms of one tile and one
 // 128-deep K block are contiguous: atom index = ((r / tile_rows) * (K / 128) + kb) * atoms_per_tile + (r % tile_rows) / 128.
 //
-//   warp 0       producer: TMA tiles of A (128 x 128 B) and B (BN x 128 B), bulk copies of their scale atoms
-//   warp 1       TMEM allocation; per K block: tcgen05.cp of the atoms into TMEM, 4 MMAs of K = 32 (scale id 0..3)
+//   warp 0       producer: TMA tiles of A (128 x 128 B) and B (BN x 128 B), copies of their scale atoms
+//   warp 1       TMEM allocation; per K block: tcgen05.cp of the atoms into TMEM (one K block ahead of their MMAs,
+//                four rotating column slots behind the accumulators), 4 MMAs of K = 32 (scale id 0..3)
 //   warps 2..9   epilogue: TMEM -> registers -> bf16 -> warp-private shared-memory transpose -> 64-byte row segments
 //                (optionally relu(x)^2 as a second output), overlapped with the next tile (two accumulators)
+// Two kernels share these roles: one CTA per 128 x BN tile, and (the default for M > 128) CTA pairs computing
+// 256 x BN tiles with tcgen05.mma.cta_group::2, where each CTA loads its 128 rows of A, half of the B tile and the
+// scale atoms, and the leader issues the copies and the MMAs for both. BN is 192 or 224 (two accumulators plus the
+// scale columns must fit the 512 TMEM columns); tiles are visited in groups of row tiles so that operands stay in L2.
 #include "fp8.h"
 
 #include <cuda.h>
