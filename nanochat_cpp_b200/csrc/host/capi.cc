@@ -329,6 +329,66 @@ nanochat_status nanochat_checkpoint_read(const char* path, nanochat_checkpoint**
 }
 void nanochat_checkpoint_free(nanochat_checkpoint* owner) { delete owner; }
 
+// ---- record files -------------------------------------------------------------------------------------------
+struct ncb_record_file {
+  std::vector<ncb::FixtureRecord> recs;
+  std::vector<std::vector<int64_t>> dims;
+  std::vector<nanochat_record> out;
+};
+
+nanochat_status ncb_record_file_read(const char* path, ncb_record_file** owner, char magic[9],
+                                     const nanochat_record** records, int64_t* record_count) {
+  if (owner == nullptr || path == nullptr) return NANOCHAT_STATUS_ERROR;
+  auto h = std::make_unique<ncb_record_file>();
+  std::string mg, err;
+  if (!ncb::ReadRecordFile(path, &mg, &h->recs, &err)) {
+    ncb_set_error(err.empty() ? std::string("cannot read record file ") + path : err);
+    return NANOCHAT_STATUS_ERROR;
+  }
+  if (magic != nullptr) {
+    std::memset(magic, 0, 9);
+    std::memcpy(magic, mg.data(), mg.size() < 8 ? mg.size() : 8);
+  }
+  h->dims.resize(h->recs.size());
+  h->out.resize(h->recs.size());
+  for (size_t i = 0; i < h->recs.size(); ++i) {
+    const ncb::FixtureRecord& r = h->recs[i];
+    h->dims[i].assign(r.dims.begin(), r.dims.end());
+    nanochat_record& o = h->out[i];
+    o = nanochat_record{};
+    o.name = r.name.c_str();
+    o.dtype = r.dtype;
+    o.ndim = static_cast<int32_t>(r.dims.size());
+    o.dims = h->dims[i].data();
+    o.data = r.data.data();
+    o.bytes = static_cast<int64_t>(r.data.size());
+  }
+  if (records != nullptr) *records = h->out.data();
+  if (record_count != nullptr) *record_count = static_cast<int64_t>(h->out.size());
+  *owner = h.release();
+  return NANOCHAT_STATUS_OK;
+}
+void ncb_record_file_free(ncb_record_file* owner) { delete owner; }
+
+nanochat_status ncb_record_file_write(const char* path, const char* magic, const nanochat_record* records,
+                                      int64_t record_count) {
+  if (path == nullptr || magic == nullptr || (records == nullptr && record_count > 0)) return NANOCHAT_STATUS_ERROR;
+  std::vector<ncb::FixtureRecord> recs(static_cast<size_t>(record_count));
+  for (int64_t i = 0; i < record_count; ++i) {
+    const nanochat_record& r = records[i];
+    recs[i].name = r.name != nullptr ? r.name : "";
+    recs[i].dtype = static_cast<std::uint8_t>(r.dtype);
+    for (int d = 0; d < r.ndim; ++d) recs[i].dims.push_back(static_cast<std::uint64_t>(r.dims[d]));
+    const auto* bytes = static_cast<const std::uint8_t*>(r.data);
+    if (bytes != nullptr && r.bytes > 0) recs[i].data.assign(bytes, bytes + r.bytes);
+  }
+  if (!ncb::WriteRecordFile(path, magic, recs)) {
+    ncb_set_error(std::string("cannot write record file ") + path);
+    return NANOCHAT_STATUS_ERROR;
+  }
+  return NANOCHAT_STATUS_OK;
+}
+
 nanochat_status nanochat_checkpoint_metadata_read(const char* path, nanochat_checkpoint** owner,
                                                   nanochat_checkpoint_metadata* out) {
   if (owner == nullptr || out == nullptr) return NANOCHAT_STATUS_ERROR;

@@ -1,6 +1,6 @@
 // nanochat_cli: a native command line over the C ABI (include/nanochat/capi.h) for hosts without Python or a GPU.
-// It runs the CPU engine: `train` (the in-process mesh driver), `generate`, `eval` (bits per byte), `tok_train`,
-// `params`, `roofline`. Flag names follow the Python entry point (`python -m nanochat_cpp_b200.cli`), which follows the
+// It runs the CPU engine: `train` (the in-process mesh driver), `generate`, `eval` (bits per byte), `score` (fixtures),
+// `tok_train`, `params`, `roofline`. Flag names follow the Python entry point (`python -m nanochat_cpp_b200.cli`), which follows the
 // reference's `nanochat_cli` (src/train_command.cc:27-61, src/generate_command.cc:37-50, src/eval_command.cc:42-54).
 // The GPU path is driven from Python; this binary links only libnanochat_core.
 //
@@ -259,6 +259,131 @@ int CmdEval(const Args& a) {
   return 0;
 }
 
+// score: per-position nll / argmax and the logits of focus ids over a NANOEVL1 fixture (input/tokens [B, T] int32,
+// input/lengths [B], optional input/focus_positions / focus_offsets / focus_ids). The model is `--model CKPT`, or the
+// one the fixture carries (config/* and param/* records), or a fresh one from the model flags. Results are printed
+// per row, or written as a NANOEVL1 record file with `--out` (reference: src/score_command.cc).
+const nanochat_record* FindRecord(const nanochat_record* recs, int64_t n, const std::string& name) {
+  for (int64_t i = 0; i < n; ++i)
+    if (name == recs[i].name) return &recs[i];
+  return nullptr;
+}
+
+int CmdScore(const Args& a) {
+  if (!a.Has("fixture")) {
+    std::fprintf(stderr, "nanochat_cli score: --fixture is required\n");
+    return 2;
+  }
+  ncb_record_file* owner = nullptr;
+  const nanochat_record* recs = nullptr;
+  int64_t n = 0;
+  char magic[9];
+  if (ncb_record_file_read(a.Str("fixture").c_str(), &owner, magic, &recs, &n) != NANOCHAT_STATUS_OK) return Fail("score");
+  auto int_at = [&](const std::string& name, long long d) {
+    const nanochat_record* r = FindRecord(recs, n, name);
+    if (r == nullptr || r->bytes < 4) return d;
+    return r->dtype == 3 ? static_cast<long long>(*static_cast<const int64_t*>(r->data))
+                         : static_cast<long long>(*static_cast<const int32_t*>(r->data));
+  };
+  nanochat_config cfg;
+  nanochat_model* m = nullptr;
+  const bool carried = !a.Has("model") && FindRecord(recs, n, "config/layers") != nullptr;
+  std::string pattern;
+  if (carried) {
+    cfg = nanochat_config{};
+    cfg.num_layers = static_cast<int>(int_at("config/layers", 0)), cfg.num_heads = static_cast<int>(int_at("config/heads", 0));
+    cfg.num_kv_heads = static_cast<int>(int_at("config/kv_heads", cfg.num_heads));
+    cfg.hidden_dim = static_cast<int>(int_at("config/embd", 0)), cfg.seq_len = static_cast<int>(int_at("config/seq", 0));
+    cfg.vocab_size = static_cast<int>(int_at("config/vocab", 0));
+    cfg.padded_vocab_size = static_cast<int>(int_at("config/padded_vocab", cfg.vocab_size));
+    cfg.rope_base = 100000.0f;
+    if (const nanochat_record* wp = FindRecord(recs, n, "config/window_pattern"))
+      pattern.assign(static_cast<const char*>(wp->data), static_cast<size_t>(wp->bytes));
+    if (pattern.empty()) pattern = "SSSL";
+    cfg.window_pattern = pattern.c_str();
+    cfg.value_embedding = 1;
+    ncb_set_short_window(0);
+    m = nanochat_model_create(&cfg, 0);
+    if (m == nullptr) return Fail("score: model");
+    const int count = nanochat_param_count(m);
+    for (int i = 0; i < count; ++i) {
+      nanochat_param info{};
+      nanochat_param_info(m, i, &info);
+      const nanochat_record* r = FindRecord(recs, n, std::string("param/") + info.name);
+      if (r == nullptr || r->dtype != 0 || r->bytes != info.count * 4) {
+        std::fprintf(stderr, "nanochat_cli score: the fixture has no fp32 record param/%s of %lld values\n", info.name,
+                     static_cast<long long>(info.count));
+        return 1;
+      }
+      nanochat_param_write(m, i, 0, 0, info.count, r->data);
+    }
+  } else {
+    m = LoadModel(a, &cfg);
+    if (m == nullptr) return Fail("score: model");
+  }
+  const nanochat_record* tok = FindRecord(recs, n, "input/tokens");
+  const nanochat_record* len = FindRecord(recs, n, "input/lengths");
+  if (tok == nullptr || len == nullptr || tok->ndim != 2 || tok->dtype != 1 || len->dtype != 1) {
+    std::fprintf(stderr, "nanochat_cli score: input/tokens [B, T] and input/lengths [B] (int32) are required\n");
+    return 1;
+  }
+  const int B = static_cast<int>(tok->dims[0]), T = static_cast<int>(tok->dims[1]);
+  const int* lengths = static_cast<const int*>(len->data);
+  std::vector<nanochat_focus> focus;
+  const nanochat_record* fp = FindRecord(recs, n, "input/focus_positions");
+  const nanochat_record* fo = FindRecord(recs, n, "input/focus_offsets");
+  const nanochat_record* fi = FindRecord(recs, n, "input/focus_ids");
+  if (fp != nullptr && fo != nullptr && fi != nullptr) {
+    const int* pos = static_cast<const int*>(fp->data);
+    const int* off = static_cast<const int*>(fo->data);
+    const int* ids = static_cast<const int*>(fi->data);
+    focus.resize(static_cast<size_t>(B));
+    for (int b = 0; b < B; ++b) {
+      focus[b].position = pos[b];
+      focus[b].ids = ids + off[b];
+      focus[b].count = pos[b] >= 0 ? off[b + 1] - off[b] : 0;
+    }
+  }
+  std::vector<nanochat_score_result> res(static_cast<size_t>(B));
+  nanochat_score_batch(m, static_cast<const int*>(tok->data), B, T, lengths, focus.empty() ? nullptr : focus.data(),
+                       res.data());
+  const char* e = nanochat_last_error();
+  if (e != nullptr && *e) return Fail("score");
+  std::vector<float> nll(static_cast<size_t>(B) * T), flog;
+  std::vector<int32_t> amax(static_cast<size_t>(B) * T), offs(1, 0);
+  for (int b = 0; b < B; ++b) {
+    for (int t = 0; t < T; ++t) nll[static_cast<size_t>(b) * T + t] = res[b].nll[t], amax[static_cast<size_t>(b) * T + t] = res[b].argmax[t];
+    const int fc = focus.empty() ? 0 : focus[b].count;
+    for (int j = 0; j < fc; ++j) flog.push_back(res[b].focus_logits[j]);
+    offs.push_back(static_cast<int32_t>(flog.size()));
+  }
+  if (a.Has("out")) {
+    const int64_t d_bt[2] = {B, T}, d_off[1] = {B + 1}, d_f[1] = {static_cast<int64_t>(flog.size())};
+    nanochat_record out[4] = {};
+    out[0].name = "result/nll", out[0].dtype = 0, out[0].ndim = 2, out[0].dims = d_bt, out[0].data = nll.data(),
+    out[0].bytes = static_cast<int64_t>(nll.size() * 4);
+    out[1].name = "result/argmax", out[1].dtype = 1, out[1].ndim = 2, out[1].dims = d_bt, out[1].data = amax.data(),
+    out[1].bytes = static_cast<int64_t>(amax.size() * 4);
+    out[2].name = "result/focus_offsets", out[2].dtype = 1, out[2].ndim = 1, out[2].dims = d_off, out[2].data = offs.data(),
+    out[2].bytes = static_cast<int64_t>(offs.size() * 4);
+    out[3].name = "result/focus_logits", out[3].dtype = 0, out[3].ndim = 1, out[3].dims = d_f, out[3].data = flog.data(),
+    out[3].bytes = static_cast<int64_t>(flog.size() * 4);
+    if (ncb_record_file_write(a.Str("out").c_str(), "NANOEVL1", out, 4) != NANOCHAT_STATUS_OK) return Fail("score: out");
+  } else {
+    for (int b = 0; b < B; ++b) {
+      const int cnt = lengths[b] - 1;
+      double mean = 0.0;
+      for (int t = 0; t < cnt; ++t) mean += res[b].nll[t];
+      std::printf("row %d: mean nll %.6f focus [", b, cnt > 0 ? mean / cnt : 0.0);
+      for (int j = offs[b]; j < offs[b + 1]; ++j) std::printf("%s%.6f", j > offs[b] ? ", " : "", flog[j]);
+      std::printf("]\n");
+    }
+  }
+  nanochat_model_free(m);
+  ncb_record_file_free(owner);
+  return 0;
+}
+
 int CmdTokTrain(const Args& a) {
   nanochat_tokenizer* tok = ncb_tokenizer_train(a.Has("text") ? a.Str("text").c_str() : nullptr,
                                                 a.Has("parquet") ? a.Str("parquet").c_str() : nullptr,
@@ -360,6 +485,7 @@ void Usage() {
       "  generate   --model C [--tokenizer T --prompt TEXT | --tokens a,b,c] --max-tokens N --num-samples S\n"
       "             --temperature X --top-k K --seed Z --stop-id I\n"
       "  eval       --model C --val-parquet P.. --tokenizer T --steps N --batch B\n"
+      "  score      --fixture F.bin [--model C] [--out results.bin]   nll / argmax / focus logits over a NANOEVL1 fixture\n"
       "  tok_train  --text F | --parquet P  --vocab V --out tokenizer.nctoken\n"
       "  dist       --world-size N [--port P] -- train ...      one process per rank over the TCP ring\n"
       "  params     model flags -> parameter counts and FLOPs per token (JSON)\n"
@@ -394,6 +520,7 @@ int main(int argc, char** argv) {
   if (cmd == "train") return CmdTrain(a);
   if (cmd == "generate") return CmdGenerate(a);
   if (cmd == "eval") return CmdEval(a);
+  if (cmd == "score") return CmdScore(a);
   if (cmd == "tok_train") return CmdTokTrain(a);
   if (cmd == "params") return CmdParams(a);
   if (cmd == "roofline") return CmdRoofline(a);

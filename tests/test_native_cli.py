@@ -120,3 +120,28 @@ def test_dist_launcher_matches_the_in_process_mesh(cli, tmp_path):
     r = run(cli, "train", *common, "--batch", "2", "--rank", "1", "--world-size", "2", "--port", port, "--timeout-ms",
             "500", "--out-dir", out_d)
     assert r.returncode == 1 and "rendezvous" in r.stderr
+
+
+def test_native_score_matches_the_fixture_results(cli, tmp_path, data_dir):
+    """`nanochat_cli score` builds the model a NANOEVL1 fixture carries, scores its rows and writes (or prints) the
+    results; they match the results recorded in the fixture (per-position nll, argmax, focus logits)."""
+    from nanochat_cpp_b200.data.record_file import read_records
+    fixture = os.path.join(data_dir, "core_eval.bin")
+    out = str(tmp_path / "score.bin")
+    r = run(cli, "score", "--fixture", fixture, "--out", out)
+    assert r.returncode == 0, r.stderr
+    magic, got = read_records(out)
+    _, want = read_records(fixture)
+    assert magic == "NANOEVL1" and list(got) == ["result/nll", "result/argmax", "result/focus_offsets",
+                                                 "result/focus_logits"]
+    assert np.array_equal(np.array(got["result/argmax"])[0, :7], np.array(want["result/argmax"])[0, :7])
+    assert np.allclose(got["result/focus_logits"], want["result/focus_logits"], atol=2e-5)
+    assert np.array_equal(got["result/focus_offsets"], want["result/focus_offsets"])
+    lengths = np.array(want["input/lengths"])
+    for b in range(len(lengths)):                                     # positions before the row's end
+        n = int(lengths[b]) - 1
+        assert np.allclose(np.array(got["result/nll"])[b, :n], np.array(want["result/nll"])[b, :n], atol=2e-5)
+    r = run(cli, "score", "--fixture", fixture)
+    assert r.returncode == 0 and r.stdout.startswith("row 0: mean nll ") and r.stdout.count("\n") == len(lengths)
+    assert run(cli, "score").returncode == 2
+    assert run(cli, "score", "--fixture", str(tmp_path / "missing.bin")).returncode == 1
