@@ -191,6 +191,7 @@ def build_cli(verbose: bool = False) -> str:
 
 def build_all(verbose: bool = False) -> None:
     build_core(verbose)
+    build_cli(verbose)
     build_extension(verbose)
 
 

@@ -1,6 +1,6 @@
 // nanochat_cli: a native command line over the C ABI (include/nanochat/capi.h) for hosts without Python or a GPU.
-// It runs the CPU engine: `train` (the in-process mesh driver), `generate`, `eval` (bits per byte), `score` (fixtures),
-// `tok_train`, `params`, `roofline`. Flag names follow the Python entry point (`python -m nanochat_cpp_b200.cli`), which follows the
+// It runs the CPU engine: `train` (the in-process mesh driver), `generate`, `eval` (bits per byte), `score` and `rl_step`
+// (fixtures), `tok_train`, `params`, `roofline`. Flag names follow the Python entry point (`python -m nanochat_cpp_b200.cli`), which follows the
 // reference's `nanochat_cli` (src/train_command.cc:27-61, src/generate_command.cc:37-50, src/eval_command.cc:42-54).
 // The GPU path is driven from Python; this binary links only libnanochat_core.
 //
@@ -269,6 +269,59 @@ const nanochat_record* FindRecord(const nanochat_record* recs, int64_t n, const 
   return nullptr;
 }
 
+long long RecordInt(const nanochat_record* recs, int64_t n, const std::string& name, long long d) {
+  const nanochat_record* r = FindRecord(recs, n, name);
+  if (r == nullptr || r->bytes < 4) return d;
+  return r->dtype == 3 ? static_cast<long long>(*static_cast<const int64_t*>(r->data))
+                       : static_cast<long long>(*static_cast<const int32_t*>(r->data));
+}
+double RecordNum(const nanochat_record* recs, int64_t n, const std::string& name, double d) {
+  const nanochat_record* r = FindRecord(recs, n, name);
+  if (r == nullptr || r->bytes < 4) return d;
+  if (r->dtype == 0) return *static_cast<const float*>(r->data);
+  if (r->dtype == 2) return *static_cast<const double*>(r->data);
+  return static_cast<double>(RecordInt(recs, n, name, 0));
+}
+
+// The model a fixture carries: config/* records give the shape, param/<name> records (fp32) the weights.
+nanochat_model* ModelFromFixture(const nanochat_record* recs, int64_t n) {
+  static std::string pattern;
+  nanochat_config cfg{};
+  cfg.num_layers = static_cast<int>(RecordInt(recs, n, "config/layers", 0));
+  cfg.num_heads = static_cast<int>(RecordInt(recs, n, "config/heads", 0));
+  cfg.num_kv_heads = static_cast<int>(RecordInt(recs, n, "config/kv_heads", cfg.num_heads));
+  cfg.hidden_dim = static_cast<int>(RecordInt(recs, n, "config/embd", 0));
+  cfg.seq_len = static_cast<int>(RecordInt(recs, n, "config/seq", 0));
+  cfg.vocab_size = static_cast<int>(RecordInt(recs, n, "config/vocab", 0));
+  cfg.padded_vocab_size = static_cast<int>(RecordInt(recs, n, "config/padded_vocab", cfg.vocab_size));
+  cfg.rope_base = 100000.0f;
+  pattern = "SSSL";
+  if (const nanochat_record* wp = FindRecord(recs, n, "config/window_pattern"))
+    if (wp->bytes > 0) pattern.assign(static_cast<const char*>(wp->data), static_cast<size_t>(wp->bytes));
+  cfg.window_pattern = pattern.c_str();
+  cfg.value_embedding = 1;
+  ncb_set_short_window(0);
+  nanochat_model* m = nanochat_model_create(&cfg, 0);
+  if (m == nullptr) {
+    Fail("fixture model");
+    return nullptr;
+  }
+  const int count = nanochat_param_count(m);
+  for (int i = 0; i < count; ++i) {
+    nanochat_param info{};
+    nanochat_param_info(m, i, &info);
+    const nanochat_record* r = FindRecord(recs, n, std::string("param/") + info.name);
+    if (r == nullptr || r->dtype != 0 || r->bytes != info.count * 4) {
+      std::fprintf(stderr, "nanochat_cli: the fixture has no fp32 record param/%s of %lld values\n", info.name,
+                   static_cast<long long>(info.count));
+      nanochat_model_free(m);
+      return nullptr;
+    }
+    nanochat_param_write(m, i, 0, 0, info.count, r->data);
+  }
+  return m;
+}
+
 int CmdScore(const Args& a) {
   if (!a.Has("fixture")) {
     std::fprintf(stderr, "nanochat_cli score: --fixture is required\n");
@@ -279,45 +332,12 @@ int CmdScore(const Args& a) {
   int64_t n = 0;
   char magic[9];
   if (ncb_record_file_read(a.Str("fixture").c_str(), &owner, magic, &recs, &n) != NANOCHAT_STATUS_OK) return Fail("score");
-  auto int_at = [&](const std::string& name, long long d) {
-    const nanochat_record* r = FindRecord(recs, n, name);
-    if (r == nullptr || r->bytes < 4) return d;
-    return r->dtype == 3 ? static_cast<long long>(*static_cast<const int64_t*>(r->data))
-                         : static_cast<long long>(*static_cast<const int32_t*>(r->data));
-  };
-  nanochat_config cfg;
   nanochat_model* m = nullptr;
-  const bool carried = !a.Has("model") && FindRecord(recs, n, "config/layers") != nullptr;
-  std::string pattern;
-  if (carried) {
-    cfg = nanochat_config{};
-    cfg.num_layers = static_cast<int>(int_at("config/layers", 0)), cfg.num_heads = static_cast<int>(int_at("config/heads", 0));
-    cfg.num_kv_heads = static_cast<int>(int_at("config/kv_heads", cfg.num_heads));
-    cfg.hidden_dim = static_cast<int>(int_at("config/embd", 0)), cfg.seq_len = static_cast<int>(int_at("config/seq", 0));
-    cfg.vocab_size = static_cast<int>(int_at("config/vocab", 0));
-    cfg.padded_vocab_size = static_cast<int>(int_at("config/padded_vocab", cfg.vocab_size));
-    cfg.rope_base = 100000.0f;
-    if (const nanochat_record* wp = FindRecord(recs, n, "config/window_pattern"))
-      pattern.assign(static_cast<const char*>(wp->data), static_cast<size_t>(wp->bytes));
-    if (pattern.empty()) pattern = "SSSL";
-    cfg.window_pattern = pattern.c_str();
-    cfg.value_embedding = 1;
-    ncb_set_short_window(0);
-    m = nanochat_model_create(&cfg, 0);
-    if (m == nullptr) return Fail("score: model");
-    const int count = nanochat_param_count(m);
-    for (int i = 0; i < count; ++i) {
-      nanochat_param info{};
-      nanochat_param_info(m, i, &info);
-      const nanochat_record* r = FindRecord(recs, n, std::string("param/") + info.name);
-      if (r == nullptr || r->dtype != 0 || r->bytes != info.count * 4) {
-        std::fprintf(stderr, "nanochat_cli score: the fixture has no fp32 record param/%s of %lld values\n", info.name,
-                     static_cast<long long>(info.count));
-        return 1;
-      }
-      nanochat_param_write(m, i, 0, 0, info.count, r->data);
-    }
+  if (!a.Has("model") && FindRecord(recs, n, "config/layers") != nullptr) {
+    m = ModelFromFixture(recs, n);
+    if (m == nullptr) return 1;
   } else {
+    nanochat_config cfg;
     m = LoadModel(a, &cfg);
     if (m == nullptr) return Fail("score: model");
   }
@@ -379,6 +399,94 @@ int CmdScore(const Args& a) {
       std::printf("]\n");
     }
   }
+  nanochat_model_free(m);
+  ncb_record_file_free(owner);
+  return 0;
+}
+
+// rl_step: replay the policy-gradient steps of a NANOORC1 fixture (model and optimizer settings carried by the
+// fixture; rollout/<k>/tokens, targets [B, T] int32 and advantages [B] fp32 per step) and print, or write with --out,
+// each step's loss and gradient norm and the final parameters (reference: src/rl_step_command.cc).
+int CmdRlStep(const Args& a) {
+  if (!a.Has("fixture")) {
+    std::fprintf(stderr, "nanochat_cli rl_step: --fixture is required\n");
+    return 2;
+  }
+  ncb_record_file* owner = nullptr;
+  const nanochat_record* recs = nullptr;
+  int64_t n = 0;
+  char magic[9];
+  if (ncb_record_file_read(a.Str("fixture").c_str(), &owner, magic, &recs, &n) != NANOCHAT_STATUS_OK) return Fail("rl_step");
+  nanochat_model* m = ModelFromFixture(recs, n);
+  if (m == nullptr) return 1;
+  nanochat_optim_config oc{};
+  auto o = [&](const char* k, double d) { return static_cast<float>(RecordNum(recs, n, std::string("config/opt/") + k, d)); };
+  auto sc = [&](const char* k, double d) { return static_cast<float>(RecordNum(recs, n, std::string("config/sched/") + k, d)); };
+  oc.unembedding_lr = o("unembedding_lr", .004), oc.embedding_lr = o("embedding_lr", .2), oc.matrix_lr = o("matrix_lr", .02);
+  oc.scalar_lr = o("scalar_lr", .5), oc.weight_decay = o("weight_decay", 0.0), oc.clip = o("clip", 0.0);
+  oc.adam_eps = o("adam_eps", 1e-10), oc.muon_ns_steps = static_cast<int>(o("muon_ns_steps", 5)), oc.muon_beta2 = o("muon_beta2", .9);
+  oc.num_iterations = static_cast<int>(sc("num_iterations", 0)), oc.warmup_steps = static_cast<int>(sc("warmup_steps", 0));
+  oc.warmdown_ratio = sc("warmdown_ratio", 0.0), oc.final_lr_frac = sc("final_lr_frac", 0.0);
+  oc.weight_decay_base = sc("weight_decay_base", 0.0), oc.muon_momentum_warmup_steps = sc("muon_momentum_warmup_steps", 0.0);
+  oc.muon_momentum_start = sc("muon_momentum_start", .95), oc.muon_momentum_peak = sc("muon_momentum_peak", .95);
+  oc.muon_momentum_final = sc("muon_momentum_final", .95);
+  nanochat_optim* opt = nanochat_optim_create(m, &oc);
+  if (opt == nullptr) return Fail("rl_step: optimizer");
+  const int steps = static_cast<int>(a.Int("steps", RecordInt(recs, n, "config/steps", 0)));
+  const int passes = static_cast<int>(RecordInt(recs, n, "config/num_passes", 1));
+  const int per = static_cast<int>(RecordInt(recs, n, "config/examples_per_rank", 1));
+  std::vector<float> losses, norms;
+  for (int k = 0; k < steps; ++k) {
+    const std::string base = "rollout/" + std::to_string(k) + "/";
+    const nanochat_record* tok = FindRecord(recs, n, base + "tokens");
+    const nanochat_record* tgt = FindRecord(recs, n, base + "targets");
+    const nanochat_record* adv = FindRecord(recs, n, base + "advantages");
+    if (tok == nullptr || tgt == nullptr || adv == nullptr || tok->ndim != 2) {
+      std::fprintf(stderr, "nanochat_cli rl_step: step %d is missing from the fixture\n", k);
+      return 1;
+    }
+    const float loss = nanochat_rl_step(m, opt, static_cast<const int*>(tok->data), static_cast<const int*>(tgt->data),
+                                        static_cast<const float*>(adv->data), static_cast<int>(tok->dims[0]),
+                                        static_cast<int>(tok->dims[1]), passes, per, k + 1);
+    const char* e = nanochat_last_error();
+    if (e != nullptr && *e) return Fail("rl_step");
+    losses.push_back(loss);
+    norms.push_back(nanochat_optim_grad_norm(opt));
+    std::fprintf(stderr, "rl: step %d loss %.6f grad_norm %.6f\n", k + 1, loss, norms.back());
+  }
+  if (a.Has("out")) {
+    const int count = nanochat_param_count(m);
+    std::vector<std::string> names;
+    std::vector<std::vector<float>> values(static_cast<size_t>(count));
+    std::vector<std::vector<int64_t>> dims;
+    std::vector<nanochat_record> out;
+    names.reserve(static_cast<size_t>(2 * steps + count));
+    dims.reserve(static_cast<size_t>(2 * steps + count));
+    auto push = [&](std::string name, const float* data, std::vector<int64_t> d, int64_t cnt) {
+      names.push_back(std::move(name));
+      dims.push_back(std::move(d));
+      nanochat_record r{};
+      r.name = names.back().c_str(), r.dtype = 0, r.ndim = static_cast<int32_t>(dims.back().size());
+      r.dims = dims.back().data(), r.data = data, r.bytes = cnt * 4;
+      out.push_back(r);
+    };
+    for (int k = 0; k < steps; ++k) {
+      push("step/" + std::to_string(k) + "/loss", &losses[k], {1}, 1);
+      push("step/" + std::to_string(k) + "/grad_norm", &norms[k], {1}, 1);
+    }
+    for (int i = 0; i < count; ++i) {
+      nanochat_param info{};
+      nanochat_param_info(m, i, &info);
+      values[i].resize(static_cast<size_t>(info.count));
+      nanochat_param_read(m, i, 0, 0, info.count, values[i].data());
+      std::vector<int64_t> d = info.cols > 0 ? std::vector<int64_t>{info.rows, info.cols} : std::vector<int64_t>{info.count};
+      push(std::string("param/") + info.name, values[i].data(), d, info.count);
+    }
+    if (ncb_record_file_write(a.Str("out").c_str(), "NANOORC1", out.data(), static_cast<int64_t>(out.size())) !=
+        NANOCHAT_STATUS_OK)
+      return Fail("rl_step: out");
+  }
+  nanochat_optim_free(opt);
   nanochat_model_free(m);
   ncb_record_file_free(owner);
   return 0;
@@ -486,6 +594,7 @@ void Usage() {
       "             --temperature X --top-k K --seed Z --stop-id I\n"
       "  eval       --model C --val-parquet P.. --tokenizer T --steps N --batch B\n"
       "  score      --fixture F.bin [--model C] [--out results.bin]   nll / argmax / focus logits over a NANOEVL1 fixture\n"
+      "  rl_step    --fixture F.bin [--steps N] [--out results.bin]  replay the policy-gradient steps of a NANOORC1 fixture\n"
       "  tok_train  --text F | --parquet P  --vocab V --out tokenizer.nctoken\n"
       "  dist       --world-size N [--port P] -- train ...      one process per rank over the TCP ring\n"
       "  params     model flags -> parameter counts and FLOPs per token (JSON)\n"
@@ -521,6 +630,7 @@ int main(int argc, char** argv) {
   if (cmd == "generate") return CmdGenerate(a);
   if (cmd == "eval") return CmdEval(a);
   if (cmd == "score") return CmdScore(a);
+  if (cmd == "rl_step") return CmdRlStep(a);
   if (cmd == "tok_train") return CmdTokTrain(a);
   if (cmd == "params") return CmdParams(a);
   if (cmd == "roofline") return CmdRoofline(a);

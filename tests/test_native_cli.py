@@ -145,3 +145,26 @@ def test_native_score_matches_the_fixture_results(cli, tmp_path, data_dir):
     assert r.returncode == 0 and r.stdout.startswith("row 0: mean nll ") and r.stdout.count("\n") == len(lengths)
     assert run(cli, "score").returncode == 2
     assert run(cli, "score", "--fixture", str(tmp_path / "missing.bin")).returncode == 1
+
+
+def test_native_rl_step_replays_the_fixture_like_the_python_engine(cli, tmp_path, data_dir):
+    """`nanochat_cli rl_step` (native engine over the C ABI) and the Python replay of the same NANOORC1 fixture agree
+    on every step's loss and gradient norm and on the parameters after the last step."""
+    from nanochat_cpp_b200 import cli as pycli
+    from nanochat_cpp_b200.data.record_file import read_records
+    fixture = os.path.join(data_dir, "rl_parity.bin")
+    out_n, out_p = str(tmp_path / "native.bin"), str(tmp_path / "python.bin")
+    r = run(cli, "rl_step", "--fixture", fixture, "--out", out_n)
+    assert r.returncode == 0 and r.stderr.count("rl: step ") == 3, r.stderr
+    assert pycli.main(["rl_step", "--fixture", fixture, "--out", out_p, "--device", "cpu"]) == 0
+    magic, a = read_records(out_n)
+    _, b = read_records(out_p)
+    assert magic == "NANOORC1"
+    for k in range(3):
+        assert abs(float(a[f"step/{k}/loss"][0]) - float(b[f"step/{k}/loss"][0])) < 2e-5
+        assert abs(float(a[f"step/{k}/grad_norm"][0]) - float(b[f"step/{k}/grad_norm"][0])) < 2e-5
+    params = [k for k in b if k.startswith("param/")]
+    assert params and all(k in a for k in params)
+    for k in params:
+        assert np.allclose(np.array(a[k]).ravel(), np.array(b[k]).ravel(), atol=5e-5), k
+    assert run(cli, "rl_step").returncode == 2
