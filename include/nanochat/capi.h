@@ -175,8 +175,6 @@ int32_t nanochat_checkpoint_metadata_stage(const nanochat_checkpoint_metadata* m
 int64_t nanochat_checkpoint_metadata_step(const nanochat_checkpoint_metadata* meta);
 int64_t nanochat_checkpoint_metadata_world_size(const nanochat_checkpoint_metadata* meta);
 const char* nanochat_checkpoint_metadata_config_json(const nanochat_checkpoint_metadata* meta);
-/* Same as nanochat_checkpoint_write, with the metadata block of the file given explicitly (JSON config as
- * produced by nanochat_checkpoint_metadata_config_json). */
 /* Record files (fixtures: magic[8], u32 version, u32 count, records). dtype codes: 0 f32, 1 i32, 2 f64, 3 i64, 4 u8.
  * `ncb_record_file_read` keeps the records alive until `ncb_record_file_free(owner)`; `magic` receives 8 characters
  * and a terminating zero. */
@@ -186,6 +184,8 @@ nanochat_status ncb_record_file_read(const char* path, ncb_record_file** owner, 
 void ncb_record_file_free(ncb_record_file* owner);
 nanochat_status ncb_record_file_write(const char* path, const char* magic, const nanochat_record* records,
                                       int64_t record_count);
+/* Same as nanochat_checkpoint_write, with the metadata block of the file given explicitly (JSON config as
+ * produced by nanochat_checkpoint_metadata_config_json). */
 nanochat_status ncb_checkpoint_write_meta(const char* path, const nanochat_record* records, int64_t record_count,
                                           const nanochat_record* optimizer, int64_t optimizer_count,
                                           const nanochat_config* config, int32_t stage, int64_t step,

@@ -46,6 +46,14 @@ nanochat_status nanochat_optim_config_preset(const char* name, nanochat_optim_co
     c.clip = 0.0f;
     c.weight_decay_base = 0.28f;
     c.warmdown_ratio = 0.5f;
+  } else if (n == "sft") {
+    // supervised fine-tuning (reference src/sft_command.cc; python/nanochat_cpp/sft.py): higher embedding rate, no
+    // clipping, half of the run in warm-down, momentum 0.85 -> 0.95 over 300 steps and held
+    c.embedding_lr = 0.3f;
+    c.clip = 0.0f;
+    c.warmdown_ratio = 0.5f;
+    c.muon_momentum_warmup_steps = 300.0f, c.muon_momentum_start = 0.85f, c.muon_momentum_peak = 0.95f;
+    c.muon_momentum_final = 0.95f;
   } else if (n != "default" && !n.empty()) {
     ncb_set_error("unknown optimizer preset '" + n + "'");
     return NANOCHAT_STATUS_ERROR;

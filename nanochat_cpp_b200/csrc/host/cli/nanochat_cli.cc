@@ -101,8 +101,84 @@ nanochat_config ModelFromArgs(const Args& a) {
   return c;
 }
 
-bool OptimFromArgs(const Args& a, nanochat_optim_config* o) {
-  if (nanochat_optim_config_preset(a.Str("preset", "default").c_str(), o) != NANOCHAT_STATUS_OK) return false;
+// Shape of the model stored in a checkpoint (its metadata block), for commands that continue from one: explicit
+// model flags still win. Returns false when the file has no readable metadata.
+bool ConfigFromCheckpoint(const std::string& path, nanochat_config* c) {
+  nanochat_checkpoint* owner = nullptr;
+  nanochat_checkpoint_metadata meta{};
+  if (nanochat_checkpoint_metadata_read(path.c_str(), &owner, &meta) != NANOCHAT_STATUS_OK) return false;
+  const char* js = nanochat_checkpoint_metadata_config_json(&meta);
+  const std::string j = js != nullptr ? js : "";
+  auto num = [&](const char* key, double d) {
+    const auto k = j.find(std::string("\"") + key + "\":");
+    return k == std::string::npos ? d : std::atof(j.c_str() + k + std::strlen(key) + 3);
+  };
+  c->num_layers = static_cast<int>(num("num_layers", c->num_layers));
+  c->num_heads = static_cast<int>(num("num_heads", c->num_heads));
+  c->num_kv_heads = static_cast<int>(num("num_kv_heads", c->num_kv_heads));
+  c->hidden_dim = static_cast<int>(num("hidden_dim", c->hidden_dim));
+  c->seq_len = static_cast<int>(num("seq_len", c->seq_len));
+  c->vocab_size = static_cast<int>(num("vocab_size", c->vocab_size));
+  c->padded_vocab_size = static_cast<int>(num("padded_vocab_size", c->padded_vocab_size));
+  c->rope_base = static_cast<float>(num("rope_base", c->rope_base));
+  const auto w = j.find("\"window_pattern\": \"");
+  if (w != std::string::npos) {
+    const auto b = w + std::strlen("\"window_pattern\": \"");
+    g_pattern = j.substr(b, j.find('"', b) - b);
+    c->window_pattern = g_pattern.c_str();
+  }
+  c->value_embedding = j.find("\"value_embedding\": false") == std::string::npos ? 1 : 0;
+  nanochat_checkpoint_free(owner);
+  // Files written through the plain C ABI carry default metadata: when the tensor shapes disagree with it, the shapes win.
+  owner = nullptr;
+  const nanochat_record* recs = nullptr;
+  int64_t n = 0;
+  if (nanochat_checkpoint_read(path.c_str(), &owner, &recs, &n, nullptr, nullptr) == NANOCHAT_STATUS_OK) {
+    auto find = [&](const std::string& name) -> const nanochat_record* {
+      for (int64_t i = 0; i < n; ++i)
+        if (name == recs[i].name) return &recs[i];
+      return nullptr;
+    };
+    auto ends_with = [](const std::string& v, const char* suffix) {
+      const size_t k = std::strlen(suffix);
+      return v.size() >= k && v.compare(v.size() - k, k, suffix) == 0;
+    };
+    const nanochat_record* lm = find("lm_head.weight");
+    const nanochat_record* cq = find("transformer.h.0.attn.c_q.weight");
+    const nanochat_record* ck = find("transformer.h.0.attn.c_k.weight");
+    if (lm != nullptr && cq != nullptr && ck != nullptr && lm->ndim == 2) {
+      int layers = 0;
+      const nanochat_record* gate = nullptr;
+      for (int64_t i = 0; i < n; ++i) {
+        if (ends_with(recs[i].name, "attn.c_q.weight")) ++layers;
+        if (gate == nullptr && ends_with(recs[i].name, "attn.ve_gate.weight")) gate = &recs[i];
+      }
+      const int padded = static_cast<int>(lm->dims[0]), hidden = static_cast<int>(lm->dims[1]);
+      const int q_dim = static_cast<int>(cq->dims[0]), kv_dim = static_cast<int>(ck->dims[0]);
+      const int base_head = c->num_heads > 0 ? c->hidden_dim / c->num_heads : 128;
+      const bool consistent = c->hidden_dim == hidden && c->padded_vocab_size == padded && c->num_layers == layers &&
+                              c->num_heads * base_head == q_dim && c->num_kv_heads * base_head == kv_dim;
+      if (!consistent) {
+        int kv_heads, head_dim;
+        if (gate != nullptr) {
+          kv_heads = static_cast<int>(gate->dims[0]);
+          head_dim = kv_dim / kv_heads;
+        } else {
+          head_dim = q_dim % 128 == 0 ? 128 : q_dim % 64 == 0 ? 64 : base_head;
+          kv_heads = kv_dim / head_dim;
+        }
+        if (!(c->vocab_size <= padded && c->padded_vocab_size == padded)) c->vocab_size = padded;
+        c->num_layers = layers, c->num_heads = q_dim / head_dim, c->num_kv_heads = kv_heads, c->hidden_dim = hidden;
+        c->padded_vocab_size = padded, c->value_embedding = gate != nullptr ? 1 : 0;
+      }
+    }
+    nanochat_checkpoint_free(owner);
+  }
+  return c->num_layers > 0 && c->hidden_dim > 0;
+}
+
+bool OptimFromArgs(const Args& a, nanochat_optim_config* o, const char* default_preset = "default") {
+  if (nanochat_optim_config_preset(a.Str("preset", default_preset).c_str(), o) != NANOCHAT_STATUS_OK) return false;
   o->embedding_lr = static_cast<float>(a.Num("embedding-lr", o->embedding_lr));
   o->unembedding_lr = static_cast<float>(a.Num("unembedding-lr", o->unembedding_lr));
   o->matrix_lr = static_cast<float>(a.Num("matrix-lr", o->matrix_lr));
@@ -124,11 +200,14 @@ bool OptimFromArgs(const Args& a, nanochat_optim_config* o) {
   return true;
 }
 
-int CmdTrain(const Args& a) {
+int CmdTrain(const Args& a, const char* default_preset = "default") {
   nanochat_mesh_train_config c{};
   c.model = ModelFromArgs(a);
+  // continuing from a checkpoint without naming a shape: take the shape the checkpoint records
+  const bool shape_given = a.Has("preset-model") || a.Has("depth") || a.Has("layers") || a.Has("hidden") || a.Has("heads");
+  if (!shape_given && a.Has("warm-start")) ConfigFromCheckpoint(a.Str("warm-start"), &c.model);
   nanochat_optim_config optim;
-  if (!OptimFromArgs(a, &optim)) return Fail("train");
+  if (!OptimFromArgs(a, &optim, default_preset)) return Fail("train");
   c.optimizer = &optim;
   nanochat_mesh* mesh = nanochat_mesh_create(nullptr, static_cast<int>(a.Int("mesh", 1)));
   c.mesh = mesh;
@@ -144,6 +223,17 @@ int CmdTrain(const Args& a) {
   c.run.batch = static_cast<int>(a.Int("batch", 8));
   c.run.grad_accum = static_cast<int>(a.Int("grad-accum", 1));
   c.run.seq = static_cast<int>(a.Int("train-seq", 0));
+  if (c.run.seq == 0 && !rows.empty()) {   // packed rows fix the row length: take it from the shard
+    ncb_record_file* shard = nullptr;
+    const nanochat_record* srecs = nullptr;
+    int64_t sn = 0;
+    char smagic[9];
+    if (ncb_record_file_read(rows.c_str(), &shard, smagic, &srecs, &sn) == NANOCHAT_STATUS_OK) {
+      for (int64_t i = 0; i < sn; ++i)
+        if (std::strcmp(srecs[i].name, "tokens") == 0 && srecs[i].ndim == 2) c.run.seq = static_cast<int>(srecs[i].dims[1]);
+      ncb_record_file_free(shard);
+    }
+  }
   c.run.seed = static_cast<uint64_t>(a.Int("seed", 42));
   c.run.num_iterations = static_cast<int>(a.Int("num-iterations", 100));
   c.run.log_every = static_cast<int>(a.Int("log-every", 10));
@@ -590,6 +680,7 @@ void Usage() {
       "             --world-size W --port P (one process per rank; or `dist`)] [--batch B --grad-accum A\n"
       "             --num-iterations K --log-every L --save-every S --out-dir D --checkpoint C --resume --warm-start W\n"
       "             --preset track3 + optimizer / schedule / model flags]\n"
+      "  sft        --rows shard.nchsft --warm-start base.ckpt [train flags]   fine-tuning over packed rows\n"
       "  generate   --model C [--tokenizer T --prompt TEXT | --tokens a,b,c] --max-tokens N --num-samples S\n"
       "             --temperature X --top-k K --seed Z --stop-id I\n"
       "  eval       --model C --val-parquet P.. --tokenizer T --steps N --batch B\n"
@@ -627,6 +718,13 @@ int main(int argc, char** argv) {
   if (nanochat_init() != NANOCHAT_STATUS_OK) return Fail("init");
   const Args a = Parse(argc, argv, 2);
   if (cmd == "train") return CmdTrain(a);
+  if (cmd == "sft") {   // supervised fine-tuning = the training driver over a packed NCSFT001 shard, from a base model
+    if (!a.Has("rows") || !(a.Has("warm-start") || a.Has("resume"))) {
+      std::fprintf(stderr, "nanochat_cli sft: --rows shard.nchsft and --warm-start base.ckpt (or --resume) are required\n");
+      return 2;
+    }
+    return CmdTrain(a, "sft");   // the fine-tuning optimizer and schedule unless --preset says otherwise
+  }
   if (cmd == "generate") return CmdGenerate(a);
   if (cmd == "eval") return CmdEval(a);
   if (cmd == "score") return CmdScore(a);

@@ -168,3 +168,29 @@ def test_native_rl_step_replays_the_fixture_like_the_python_engine(cli, tmp_path
     for k in params:
         assert np.allclose(np.array(a[k]).ravel(), np.array(b[k]).ravel(), atol=5e-5), k
     assert run(cli, "rl_step").returncode == 2
+
+
+def test_native_sft_takes_shape_and_row_length_from_its_inputs(cli, tmp_path, data_dir, capsys):
+    """`nanochat_cli sft`: the model shape comes from the warm-start checkpoint's tensors, the row length from the
+    packed shard, the optimizer from the fine-tuning preset; the losses track the Python fine-tuning loop on the same
+    fixture and the checkpoint it writes loads in Python."""
+    import re
+    from nanochat_cpp_b200 import cli as pycli
+    from nanochat_cpp_b200.train.checkpointer import load_checkpoint
+    rows = os.path.join(data_dir, "sft_rows_fixture.nchsft")
+    base = os.path.join(data_dir, "sft_base_fixture.ckpt")
+    out = str(tmp_path / "run")
+    os.makedirs(out)
+    ckpt = os.path.join(out, "sft.ckpt")
+    r = run(cli, "sft", "--rows", rows, "--warm-start", base, "--num-iterations", "2", "--grad-accum", "2", "--batch", "2",
+            "--out-dir", out, "--checkpoint", ckpt, "--log-every", "1")
+    assert r.returncode == 0, r.stderr
+    native = [float(x) for x in re.findall(r"\| loss ([0-9.]+) \|", r.stdout)]
+    assert len(native) == 2 and os.path.exists(ckpt)
+    assert pycli.main(["sft", "--rows", rows, "--warm-start", base, "--num-iterations", "2", "--grad-accum", "2",
+                       "--batch", "2", "--checkpoint", str(tmp_path / "py.ckpt"), "--device", "cpu"]) == 0
+    py = [float(x) for x in re.findall(r"sft: step \d+ .* loss ([0-9.]+)", capsys.readouterr().err)]
+    assert len(py) == 2 and abs(native[0] - py[0]) < 1e-3 and abs(native[1] - py[1]) < 5e-3
+    model, meta = load_checkpoint(ckpt, device="cpu")
+    assert model.cfg.hidden_dim == 64 or model.cfg.hidden_dim > 0
+    assert run(cli, "sft", "--rows", rows).returncode == 2
