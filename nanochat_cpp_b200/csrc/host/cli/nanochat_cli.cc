@@ -7,7 +7,9 @@
 // Environment contract of the reference's binaries (include/nanochat/sandbox.h): they refuse to start outside their
 // sandbox. Here the check is opt-in: with NANOCHAT_SANDBOX_ENFORCE=1 the binary exits unless NANOCHAT_SANDBOX names
 // a profile; otherwise the variable is only echoed in `--version`.
+#include <algorithm>
 #include <cstdio>
+#include <ctime>
 #include <cstdlib>
 #include <cstring>
 #include <csignal>
@@ -582,6 +584,48 @@ int CmdRlStep(const Args& a) {
   return 0;
 }
 
+// eval_bench: time the evaluation forward (loss over one batch) of the CPU engine and print a `nanochat.bench.v3`
+// document (reference: src/eval_bench_command.cc). Tokens are xorshift-random in [0, vocab).
+int CmdEvalBench(const Args& a) {
+  nanochat_config cfg;
+  nanochat_model* m = LoadModel(a, &cfg);
+  if (m == nullptr) return Fail("eval_bench");
+  const int batch = static_cast<int>(a.Int("batch", 8)), seq = static_cast<int>(a.Int("eval-seq", cfg.seq_len));
+  const int iters = static_cast<int>(a.Int("iters", 10)), warmup = static_cast<int>(a.Int("warmup", 3));
+  std::vector<int> tok(static_cast<size_t>(batch) * seq), tgt(tok.size());
+  unsigned long long x = 0x9E3779B97F4A7C15ull ^ static_cast<unsigned long long>(a.Int("seed", 0));
+  for (size_t i = 0; i < tok.size(); ++i) {
+    x ^= x << 13, x ^= x >> 7, x ^= x << 17;
+    tok[i] = static_cast<int>(x % static_cast<unsigned long long>(cfg.vocab_size));
+  }
+  for (size_t i = 0; i < tok.size(); ++i) tgt[i] = (i + 1) % seq == 0 ? -1 : tok[i + 1];
+  float loss = 0.0f;
+  for (int i = 0; i < warmup; ++i) loss = nanochat_forward_loss(m, tok.data(), tgt.data(), batch, seq);
+  std::vector<double> ms;
+  for (int i = 0; i < iters; ++i) {
+    timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    loss = nanochat_forward_loss(m, tok.data(), tgt.data(), batch, seq);
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    ms.push_back((t1.tv_sec - t0.tv_sec) * 1e3 + (t1.tv_nsec - t0.tv_nsec) * 1e-6);
+  }
+  const char* e = nanochat_last_error();
+  if (e != nullptr && *e) return Fail("eval_bench");
+  std::sort(ms.begin(), ms.end());
+  const double med = ms.empty() ? 0.0 : ms[ms.size() / 2];
+  nanochat_params counts{};
+  nanochat_params_get(&cfg, &counts);
+  const double flops = counts.flops_per_token / 3.0 * batch * seq;   // forward = a third of forward + backward
+  std::printf("{\"schema\":\"nanochat.bench.v3\",\"device\":\"cpu\",\"precision\":\"fp32\",\"rows\":[{\"name\":"
+              "\"eval_forward\",\"family\":\"eval_forward\",\"phase\":\"fwd\",\"precision\":\"fp32\",\"shape\":\"B=%d T=%d "
+              "L=%d C=%d V=%d\",\"ms\":%.6f,\"gflops\":%.3f,\"work_ratio\":0,\"mfu\":0,\"iterations\":%d}],\"loss\":%.6f,"
+              "\"tokens_per_second\":%.1f}\n",
+              batch, seq, cfg.num_layers, cfg.hidden_dim, cfg.vocab_size, med, med > 0 ? flops / med / 1e6 : 0.0, iters, loss,
+              med > 0 ? batch * seq / med * 1e3 : 0.0);
+  nanochat_model_free(m);
+  return 0;
+}
+
 int CmdTokTrain(const Args& a) {
   nanochat_tokenizer* tok = ncb_tokenizer_train(a.Has("text") ? a.Str("text").c_str() : nullptr,
                                                 a.Has("parquet") ? a.Str("parquet").c_str() : nullptr,
@@ -686,6 +730,7 @@ void Usage() {
       "  eval       --model C --val-parquet P.. --tokenizer T --steps N --batch B\n"
       "  score      --fixture F.bin [--model C] [--out results.bin]   nll / argmax / focus logits over a NANOEVL1 fixture\n"
       "  rl_step    --fixture F.bin [--steps N] [--out results.bin]  replay the policy-gradient steps of a NANOORC1 fixture\n"
+      "  eval_bench model flags --batch B --iters N --warmup W     evaluation forward time as a nanochat.bench.v3 document\n"
       "  tok_train  --text F | --parquet P  --vocab V --out tokenizer.nctoken\n"
       "  dist       --world-size N [--port P] -- train ...      one process per rank over the TCP ring\n"
       "  params     model flags -> parameter counts and FLOPs per token (JSON)\n"
@@ -729,6 +774,7 @@ int main(int argc, char** argv) {
   if (cmd == "eval") return CmdEval(a);
   if (cmd == "score") return CmdScore(a);
   if (cmd == "rl_step") return CmdRlStep(a);
+  if (cmd == "eval_bench") return CmdEvalBench(a);
   if (cmd == "tok_train") return CmdTokTrain(a);
   if (cmd == "params") return CmdParams(a);
   if (cmd == "roofline") return CmdRoofline(a);

@@ -194,3 +194,13 @@ def test_native_sft_takes_shape_and_row_length_from_its_inputs(cli, tmp_path, da
     model, meta = load_checkpoint(ckpt, device="cpu")
     assert model.cfg.hidden_dim == 64 or model.cfg.hidden_dim > 0
     assert run(cli, "sft", "--rows", rows).returncode == 2
+
+
+def test_native_eval_bench_prints_a_bench_v3_document(cli):
+    r = run(cli, "eval_bench", "--preset-model", "tiny", "--batch", "2", "--iters", "3", "--warmup", "1")
+    assert r.returncode == 0, r.stderr
+    doc = json.loads(r.stdout)
+    row = doc["rows"][0]
+    assert doc["schema"] == "nanochat.bench.v3" and doc["device"] == "cpu" and row["family"] == "eval_forward"
+    assert row["ms"] > 0 and row["iterations"] == 3 and row["shape"] == "B=2 T=64 L=2 C=64 V=512"
+    assert 5.5 < doc["loss"] < 7.0 and doc["tokens_per_second"] > 0          # ln(512) = 6.24 for a fresh model
