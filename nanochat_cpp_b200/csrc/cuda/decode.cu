@@ -93,7 +93,8 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // q and the appended K / V row come from the kernel before
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int len = seq_lens[b];
+  // a length beyond what the page table covers is clamped: the table is never indexed out of range
+  const int len = min(seq_lens[b], max_pages * page_size);
   if (len <= 0) return;
   const int qpos = len - 1;
   const int first = window_left >= 0 ? max(0, qpos - window_left) : 0;

@@ -6,6 +6,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <climits>
+#include <cstdint>
 #include <cstdio>
 #include <mutex>
 
@@ -47,6 +49,7 @@ cudaError_t scratch_for_current_device(float** ptr) {
 extern "C" int nc_paged_decode_attention_splits(int B, int KV, int max_pages, int page_size, int window_left) {
   if (B <= 0 || KV <= 0 || max_pages <= 0 || page_size <= 0) return 1;
   long long keys = static_cast<long long>(max_pages) * page_size;
+  if (keys > INT_MAX) keys = INT_MAX;
   if (window_left >= 0 && window_left + 1 < keys) keys = window_left + 1;
   return nc::decode_splits(B, KV, static_cast<int>(keys));
 }
@@ -63,6 +66,22 @@ extern "C" int nc_paged_decode_attention_noalloc(const void* q, const void* k_po
   }
   if (B <= 0 || H <= 0 || KV <= 0 || max_pages <= 0 || page_size <= 0 || H % KV != 0 || (D != 64 && D != 128)) {
     say(message, message_len, "sizes must be positive, H a multiple of KV and D 64 or 128");
+    return NC_DECODE_NOALLOC_BAD_ARGUMENT;
+  }
+  const int group = H / KV;
+  if (group != 1 && group != 2 && group != 4 && group != 8) {
+    say(message, message_len, "the group size H / KV must be 1, 2, 4 or 8");
+    return NC_DECODE_NOALLOC_BAD_ARGUMENT;
+  }
+  if (static_cast<long long>(max_pages) * page_size > INT_MAX) {
+    say(message, message_len, "max_pages * page_size does not fit a 32-bit key index");
+    return NC_DECODE_NOALLOC_BAD_ARGUMENT;
+  }
+  // the kernels read q, K and V rows with 16-byte loads and write the output with 16-byte-aligned rows
+  if (((reinterpret_cast<std::uintptr_t>(q) | reinterpret_cast<std::uintptr_t>(k_pool) |
+        reinterpret_cast<std::uintptr_t>(v_pool) | reinterpret_cast<std::uintptr_t>(out)) & 15u) != 0 ||
+      ((reinterpret_cast<std::uintptr_t>(page_table) | reinterpret_cast<std::uintptr_t>(seq_lens)) & 3u) != 0) {
+    say(message, message_len, "q, k_pool, v_pool and out must be 16-byte aligned; page_table and seq_lens 4-byte aligned");
     return NC_DECODE_NOALLOC_BAD_ARGUMENT;
   }
   if (splits <= 0) splits = nc_paged_decode_attention_splits(B, KV, max_pages, page_size, window_left);

@@ -38,14 +38,20 @@ extern "C" {
 
 enum {
   NC_DECODE_NOALLOC_OK = 0,
-  NC_DECODE_NOALLOC_BAD_ARGUMENT = 1,  // null pointer, unsupported head size or group size, bad counts
+  NC_DECODE_NOALLOC_BAD_ARGUMENT = 1,  // null or misaligned pointer, unsupported head size or group size (H / KV not
+                                       // in {1, 2, 4, 8}), non-positive counts, max_pages * page_size > INT_MAX
   NC_DECODE_NOALLOC_TOO_LARGE = 2,     // the scratch array cannot hold B * H * splits * (D + 2) floats
   NC_DECODE_NOALLOC_CUDA_ERROR = 3,    // set-up or the launch failed; see the message
 };
 
 // q, out:            bf16 [B, H, D], contiguous
 // k_pool, v_pool:    bf16 [pages, page_size, KV, D]
-// page_table:        int32 [B, max_pages]; seq_lens: int32 [B], counting the token that is being decoded
+// page_table:        int32 [B, max_pages]; seq_lens: int32 [B], counting the token that is being decoded. The entry
+//                    point cannot read device memory without a synchronisation, so it does not validate the
+//                    lengths: the kernel clamps a length above max_pages * page_size to that bound (the table is
+//                    never indexed out of range) and skips a sequence whose length is <= 0. Page numbers inside
+//                    the table are the caller's responsibility.
+// q, k_pool, v_pool, out must be 16-byte aligned (the kernels use 16-byte loads and stores).
 // window_left:       keys further back than this are not attended; negative = unlimited
 // splits:            CTAs per (sequence, kv head) along the keys; <= 0 picks the value the tensor-level entry
 //                    point would pick for these sizes

@@ -60,6 +60,7 @@ class InferenceEngine:
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
         self._graph = None
         self._graph_key = None
+        self._graph_cache = None   # strong reference: the captured graph addresses this cache's tensors
 
     # ------------------------------------------------------------------ helpers
     def new_cache(self, batch: int, max_seq: int) -> PagedKVCache:
@@ -212,10 +213,14 @@ class InferenceEngine:
         step when capture is not possible."""
         if not self.use_cuda_graph:
             return self.decode(cache, tokens, greedy)
-        key = (id(cache), tokens.shape[0], bool(greedy))
-        if self._graph_key != key:
+        # The graph bakes in the addresses of this cache's pools, page table, lengths and previous-embedding slot,
+        # so it is valid for this cache object only. The engine keeps the cache alive while the graph exists and
+        # compares by identity: an `id()` can be reused by a new cache once the old one is freed.
+        key = (tokens.shape[0], cache.max_seq, bool(greedy))
+        if self._graph_cache is not cache or self._graph_key != key:
             self._graph = None
             self._graph_key = key
+            self._graph_cache = cache
             try:
                 self._static_tok = tokens.clone()
                 # warm up on a side stream (allocations, tensor-map cache), restoring the cache state afterwards
@@ -237,6 +242,7 @@ class InferenceEngine:
                 self._graph = g
             except Exception:
                 self._graph = None
+                self._graph_cache = None
                 self.use_cuda_graph = False
                 torch.cuda.synchronize()
                 return self.decode(cache, tokens, greedy)

@@ -10,6 +10,8 @@ sidecar `<path>.cursor`.
 """
 from __future__ import annotations
 
+import os
+
 from typing import Dict, Optional
 
 import numpy as np
@@ -105,6 +107,9 @@ def save_checkpoint(path: str, model: GPT, optimizer: Optional[Optimizer] = None
     for s in model.params.specs:
         records.append((s.name, 0, _np(master[s.offset:s.offset + s.count]).reshape(s.shape)))
     precision = 1 if model.dtype == torch.bfloat16 else 0
+    # Both files are written beside their final names and renamed into place, so a run that is stopped in the
+    # middle of a save leaves the previous checkpoint and cursor intact.
+    final_path, path = path, path + ".tmp"
     native.write_checkpoint(path, records, [(k, 0, v) for k, v in opt_records.items()],
                             config=dict(num_layers=cfg.num_layers, num_heads=cfg.num_heads,
                                         num_kv_heads=cfg.num_kv_heads, hidden_dim=cfg.hidden_dim,
@@ -114,7 +119,10 @@ def save_checkpoint(path: str, model: GPT, optimizer: Optional[Optimizer] = None
                             stage=STAGES[stage], step=step, world_size=1 if dp is None else dp.world_size,
                             precision=precision, tokenizer_id=tokenizer_id, notes=notes)
     if loader is not None:
-        loader.save_cursor(path + ".cursor")
+        loader.save_cursor(final_path + ".cursor.tmp")
+    os.replace(path, final_path)
+    if loader is not None:
+        os.replace(final_path + ".cursor.tmp", final_path + ".cursor")
 
 
 def config_from_metadata(meta: dict) -> Config:

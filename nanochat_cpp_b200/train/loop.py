@@ -103,14 +103,20 @@ class Trainer:
             ev["end"].record()
             self._phase_events = ev
         if m.fp8:
-            if self.dp is not None and getattr(self.dp, "fused", None) is not None:
-                # owners push the new bf16 weights asynchronously: wait (on the stream) for this step's pushes
-                f = self.dp.fused
-                f.wait(f.slot_adamw, self.step_count)
-                f.wait(f.slot_muon, self.step_count)
+            self.wait_for_weights()
             m.refresh_fp8()
         self.last_loss = total / accum
         return self.last_loss
+
+    def wait_for_weights(self) -> None:
+        """Under the fused transport the owners push the new bf16 weights into every rank's buffer asynchronously
+        and the next training forward waits for them inside its first GEMM. Anything else that reads the weights
+        right after a step (evaluation, generation, the fp8 re-quantisation, a checkpoint) calls this first: it
+        enqueues, on the compute stream, the bounded waits for this step's pushes."""
+        f = getattr(self.dp, "fused", None) if self.dp is not None else None
+        if f is not None and self.step_count > 0:
+            f.wait(f.slot_adamw, self.step_count)
+            f.wait(f.slot_muon, self.step_count)
 
     def phase_times(self) -> dict:
         """fwd / bwd / opt milliseconds of the last step run with `time_phases` (after a device synchronise). `opt`
@@ -134,19 +140,68 @@ class Trainer:
         return self.dp is None or self.dp.rank == 0
 
     def _stage(self, loader):
-        """`grad_accum` micro-batches from the loader through pinned host buffers to the device."""
+        """`grad_accum` micro-batches from the loader through pinned host buffers to the device.
+
+        The copies are asynchronous and the host may run several steps ahead of the GPU, so the pinned buffers
+        rotate over two sets and each set carries an event recorded after its copies: a set is refilled only once
+        that event has fired, i.e. once the device has read the previous contents."""
         B, T = self.tc.batch, self.cfg.seq_len
+        cuda = self.device.type == "cuda"
         if not hasattr(self, "_pinned"):
-            pin = self.device.type == "cuda"
-            self._pinned = [(torch.empty((B, T), dtype=torch.int32, pin_memory=pin),
-                             torch.empty((B, T), dtype=torch.int32, pin_memory=pin))
-                            for _ in range(self.tc.grad_accum)]
+            self._pinned = [dict(bufs=[(torch.empty((B, T), dtype=torch.int32, pin_memory=cuda),
+                                        torch.empty((B, T), dtype=torch.int32, pin_memory=cuda))
+                                       for _ in range(self.tc.grad_accum)], event=None)
+                            for _ in range(2 if cuda else 1)]
+            self._pinned_next = 0
+        cur = self._pinned[self._pinned_next]
+        self._pinned_next = (self._pinned_next + 1) % len(self._pinned)
+        if cur["event"] is not None:
+            cur["event"].synchronize()
         out = []
-        for tok_h, tgt_h in self._pinned:
+        for tok_h, tgt_h in cur["bufs"]:
             loader.next_into(tok_h.numpy(), tgt_h.numpy())
             out.append((tok_h.to(self.device, non_blocking=True).long(),
                         tgt_h.to(self.device, non_blocking=True).long()))
+        if cuda:
+            cur["event"] = torch.cuda.Event()
+            cur["event"].record()
         return out
+
+    def check_device_status(self) -> None:
+        """Reads the per-device status word that every bounded wait reports through (a kernel that gave up waiting
+        returns early and leaves wrong output behind). Under data parallelism the codes are max-reduced so that every
+        rank raises on the same step; the caller must have synchronised the device. Raising here, before the next
+        checkpoint is written, lets the launcher restart the group from the last good file."""
+        if self.device.type != "cuda":
+            return
+        from .. import ops
+        if ops.get_mode() != "kernels":
+            return
+        K = ops.cuda_module()
+        code = int(K._C.read_status(self.device.index if self.device.index is not None else torch.cuda.current_device()))
+        if self.dp is not None and self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([code], dtype=torch.int32, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            code = int(t.item())
+        if code != 0:
+            K._C.reset_status(self.device.index if self.device.index is not None else torch.cuda.current_device())
+            raise RuntimeError(f"step {self.step_count}: a kernel gave up waiting on some rank (status code {code}); "
+                               "the step's results are not trustworthy, restart from the last checkpoint")
+
+    def _heartbeat(self):
+        """A `parallel.health.Heartbeat` over the process group's store (data-parallel runs only)."""
+        if self.dp is None or self.world <= 1:
+            return None
+        try:
+            import torch.distributed as dist
+            from torch.distributed.distributed_c10d import _get_default_store
+            from ..parallel.health import Heartbeat
+            if not dist.is_initialized():
+                return None
+            return Heartbeat(_get_default_store(), self.dp.rank, self.world, timeout_s=600.0, prefix="train_hb")
+        except Exception:
+            return None
 
     def resume(self, path: str, loader=None) -> int:
         """Restores weights, optimizer state and step (and the loader position from `<path>.cursor`)."""
@@ -198,24 +253,31 @@ class Trainer:
         last = {}
         losses = []
         first = self.step_count + 1
+        hb = self._heartbeat()
         for step in range(first, tc.num_iterations + 1):
             t0 = time.perf_counter()
             micro = self._stage(train_loader)
             data_ms += (time.perf_counter() - t0) * 1e3
             final = step == tc.num_iterations
             self.time_phases = (tc.log_every > 0 and step % tc.log_every == 0) or final
+            if hb is not None:
+                hb.check(step)      # a peer that left or went silent is found before this rank launches the step
             loss = self.train_step(micro)
+            if hb is not None:
+                hb.beat(step)
             steps_since += 1
             eval_ms = 0.0
             bpb = None
             if val_loader is not None and tc.eval_every > 0 and (step % tc.eval_every == 0 or final):
                 te = time.perf_counter()
+                self.wait_for_weights()
                 bpb = eval_bpb(self.model, val_loader, tc.eval_steps, token_bytes)
                 eval_ms = (time.perf_counter() - te) * 1e3
                 emit(f"[nanochat] step {step} val_bpb {bpb:.6f}")
             if (tc.log_every > 0 and step % tc.log_every == 0) or final:
                 if cuda:
                     torch.cuda.synchronize(self.device)
+                    self.check_device_status()
                 now = time.perf_counter()
                 step_ms = ((now - t_log) * 1e3 - eval_ms) / max(steps_since, 1)
                 tok_s = tokens_step / (step_ms / 1e3)
@@ -238,6 +300,9 @@ class Trainer:
                     met_f.flush()
                 t_log, steps_since, data_ms = time.perf_counter(), 0, 0.0
             if tc.checkpoint and ((tc.save_every > 0 and step % tc.save_every == 0) or final):
+                if cuda:
+                    torch.cuda.synchronize(self.device)
+                    self.check_device_status()      # never overwrite a good checkpoint with a failed step's weights
                 self.save(tc.checkpoint, train_loader)
                 emit(f"[nanochat] saved {tc.checkpoint} at step {step}")
         summary = dict(final_step=self.step_count, final_loss=losses[-1] if losses else None, world_size=self.world,

@@ -73,6 +73,30 @@ def test_engine_matches_torch_ops_and_graph_replay():
     _K().check_status()
 
 
+def test_graph_replay_follows_the_cache_across_generate_calls():
+    """Every `generate_multi` call builds a new cache; the engine's captured decode graph must be rebuilt for it
+    (a freed cache's `id()` is reused by the next one). Two calls on one engine, different prompt lengths and the
+    same row count, against an engine that never captures."""
+    cfg = Config(num_layers=4, num_heads=4, num_kv_heads=2, hidden_dim=512, seq_len=256, vocab_size=1000,
+                 padded_vocab_size=1024, window_pattern="SSSL", short_window_override=128)
+    m = GPT(cfg, "cuda", torch.bfloat16, seed=3)
+    g = torch.Generator().manual_seed(1)
+    for s in m.params.specs:
+        if s.name.endswith("c_proj.weight"):
+            m.params.m(s.name).copy_((torch.randn(s.shape, generator=g) * 0.02).cuda())
+    m.params.m("lm_head.weight").copy_((torch.randn(1024, 512, generator=g) * 0.05).cuda())
+    m.params.sync_compute()
+    eng = InferenceEngine(m, use_cuda_graph=True)
+    eager = InferenceEngine(m, use_cuda_graph=False)
+    params = GenerateParams(max_tokens=12)
+    for length in (96, 40, 96, 64):
+        prompts = torch.randint(0, cfg.vocab_size, (3, length), generator=g)
+        got = generate_multi(eng, prompts, params)
+        want = generate_multi(eager, prompts, params)
+        assert [s.tokens for s in got] == [s.tokens for s in want], f"prompt length {length}"
+    _K().check_status()
+
+
 @pytest.mark.parametrize("H,KV", [(10, 10), (4, 2), (3, 1)])
 def test_decode_prologue_matches_qk_prep_and_kv_append(H, KV):
     """The one-launch decode prologue writes exactly what `qk_prep_fwd` + `kv_append` write: q dense, k and v in the

@@ -79,4 +79,35 @@ def test_no_alloc_entry_rejects_oversize_and_bad_arguments():
     rc = lib.nc_paged_decode_attention_noalloc(None, kp.data_ptr(), vp.data_ptr(), table.data_ptr(), sl.data_ptr(),
                                                out.data_ptr(), 2, 4, 2, 128, 4, 16, -1, 1.0, 0, None, msg, len(msg))
     assert rc == 1
+    # a pointer that is not 16-byte aligned, a group size H / KV outside {1, 2, 4, 8}, and a key range beyond
+    # 32 bits are all refused as bad arguments, before set-up and before any launch
+    rc = lib.nc_paged_decode_attention_noalloc(q.data_ptr() + 2, kp.data_ptr(), vp.data_ptr(), table.data_ptr(),
+                                               sl.data_ptr(), out.data_ptr(), 2, 4, 2, 128, 4, 16, -1, 1.0, 0, None,
+                                               msg, len(msg))
+    assert rc == 1 and b"aligned" in msg.value
+    rc = lib.nc_paged_decode_attention_noalloc(q.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(),
+                                               sl.data_ptr(), out.data_ptr(), 2, 6, 2, 128, 4, 16, -1, 1.0, 0, None,
+                                               msg, len(msg))
+    assert rc == 1 and b"group" in msg.value
+    rc = lib.nc_paged_decode_attention_noalloc(q.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(),
+                                               sl.data_ptr(), out.data_ptr(), 2, 4, 2, 128, 1 << 28, 16, -1, 1.0, 0,
+                                               None, msg, len(msg))
+    assert rc == 1 and b"32-bit" in msg.value
     torch.cuda.synchronize()
+
+
+def test_no_alloc_entry_clamps_a_length_beyond_the_page_table():
+    """`seq_lens` lives on the device, so the entry point cannot check it; the kernel clamps instead. A length
+    above max_pages * page_size must give the same answer as the clamped length (and never index past the table)."""
+    K, lib = _lib()
+    B, H, KV, D, max_seq = 2, 4, 2, 128, 64
+    q, kp, vp, table, _ = _case(B, H, KV, D, max_seq, [64, 64], seed=4)
+    ok = torch.tensor([64, 40], device="cuda", dtype=torch.int32)
+    over = torch.tensor([64 + 4096, 40], device="cuda", dtype=torch.int32)
+    a, b = torch.empty_like(q), torch.empty_like(q)
+    for lens, out in ((ok, a), (over, b)):
+        rc, text = _call(lib, q, kp, vp, table, lens, out, -1, D ** -0.5)
+        assert rc == 0, text
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    K.check_status()
