@@ -4,15 +4,20 @@
         -m nanochat_cpp_b200.bench.dp_comm_bench [--preset d20]
 
 Sets up the d20 parameter store in symmetric memory exactly as training does and times, with CUDA events after
-warm-up, each kernel in isolation (every rank has published its flags before the timed launch, so a kernel never
-waits for a peer inside the timed region):
+warm-up and a barrier, each stage in isolation (all ranks start together, so waits for peers are short):
 
-  reduce_pull   every bucket of the step: this rank's shard of the fp32 gradient loaded from all N ranks (N-1 over
-                NVLink), summed, scaled, stored, sum of squares accumulated. Bytes that must cross NVLink per GPU:
-                (N-1) * shard bytes inbound. Roofline time = that / 770 GB/s (measured peer-copy bandwidth).
-  adamw_push    owner AdamW update writing bf16 parameters into all N ranks: (N-1) * 2 bytes/param outbound.
-  muon_push     owner Muon apply writing bf16 matrices into all N ranks.
-  gemm_wait     the first forward GEMM with its in-kernel flag wait against the same GEMM without it.
+  reduce_scatter  every bucket of the step. Default (bf16 by stores): `grad_push` of everything other ranks own into
+                  their receive slots, signal, then `grad_reduce_local` of this rank's shard; bytes that must cross
+                  NVLink per GPU and direction: (N-1)/N * parameters * 2. With `NANOCHAT_DP_REDUCE=pull`: the fp32
+                  pull (`reduce_pull`), (N-1) * shard * 4 bytes inbound.
+  update_and_push the owner's whole optimizer step (AdamW slices and Muon with its Newton-Schulz products), whose
+                  final stores write the bf16 parameters into all N ranks: (N-1) * owned * 2 bytes outbound, and as
+                  many inbound from the other owners. Roofline = max(Newton-Schulz FLOPs at the measured sustained
+                  GEMM rate, AdamW state bytes at the measured copy bandwidth, link bytes / link rate).
+  gemm_wait       the first forward GEMM with its in-kernel flag wait against the same GEMM without it.
+
+Link rate: 900 GB/s per direction per GPU (NVLink 5 nominal, the denominator the benchmark names); the fraction
+against this pool's measured peer-copy rate (770 GB/s) is printed beside it.
 """
 from __future__ import annotations
 
@@ -28,7 +33,8 @@ from ..models import GPT
 from ..optim import Optimizer
 from ..parallel import DataParallel
 
-LINK_GBS = 770.0
+LINK_GBS = 900.0            # nominal per direction per GPU: the roofline denominator
+LINK_GBS_MEASURED = 770.0   # peer copy measured on this pool, for context
 
 
 def _time(fn, stream=None, iters=5, warmup=2):
@@ -67,33 +73,37 @@ def main():
     model.params.grad.normal_(0, 1e-3)
     step = [0]
 
-    # ---- reduce_pull over all buckets
-    def reduce_all():
-        step[0] += 1
-        for b in range(len(f.buckets)):
-            f.signal(b, step[0])
-        torch.cuda.synchronize()
-        dist.barrier()                       # every rank's flags are out before anything is timed
+    # ---- reduce-scatter over all buckets
+    push_mode = f.reduce_mode == "push"
+    status = K._C.status_tensor(dev.index)
 
-    def run_reduce():
-        with torch.cuda.stream(f.comm_stream):
-            for b, bk in enumerate(f.buckets):
-                if bk["total"]:
-                    K._C.comm_reduce_pull(f.grad.ptrs, f.rank, bk["segs"], bk["total"], 1.0, f.flags.tensor, b, step[0],
-                                          f.sumsq, K._C.status_tensor(dev.index), f.reduce_ctas)
+    # The transport's own pipeline, as the training step drives it: every bucket is announced back to back on the
+    # compute stream (as if the whole backward had just finished); pushes, signals and reductions then run on the
+    # transport's streams. Timed from the first announcement to the moment both streams have drained.
     times = []
+    cur = torch.cuda.current_stream()
     for i in range(6):
-        reduce_all()
+        step[0] += 1
+        torch.cuda.synchronize()
+        dist.barrier()
         a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(f.comm_stream)
-        run_reduce()
-        b_.record(f.comm_stream)
+        a.record(cur)
+        f.begin_reduction()
+        for b in range(len(f.buckets)):
+            f.reduce_bucket(b, step[0])
+        cur.wait_stream(f.comm_stream)
+        cur.wait_stream(f.push_stream)
+        b_.record(cur)
         torch.cuda.synchronize()
         if i >= 2:
             times.append(a.elapsed_time(b_))
     reduce_ms = sorted(times)[len(times) // 2]
     shard_elems = sum(bk["total"] for bk in f.buckets)
-    reduce_link_bytes = (world - 1) * shard_elems * 4
+    n_params = model.params.num_params()
+    if push_mode:
+        reduce_link_bytes = int((world - 1) / world * n_params * 2)
+    else:
+        reduce_link_bytes = (world - 1) * shard_elems * 4
 
     # ---- owner updates that push parameters
     K.check_status(dev)
@@ -127,16 +137,25 @@ def main():
     reduce_ms, opt_ms, plain, waited = [float(v) for v in vals]
     K.check_status(dev)
     if rank == 0:
+        from ..train import mfu as perf
+        peaks = perf.measured_peaks()
         red_roof = reduce_link_bytes / (LINK_GBS * 1e9) * 1e3
         push_roof = push_link_bytes / (LINK_GBS * 1e9) * 1e3
+        ns_flops = perf.muon_flops_per_step(cfg, 5) / world
+        ns_ms = ns_flops / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3
+        adamw_ms = owned_adamw * 30.0 / (peaks["hbm_gbs"] * 1e9) * 1e3      # master, grad, m, v read; master, m, v, bf16 written
+        upd_roof = max(push_roof, ns_ms, adamw_ms)
         print(json.dumps(dict(
-            n_gpus=world, model=args.preset, link_gbs_measured_reference=LINK_GBS,
-            reduce_pull=dict(ms=round(reduce_ms, 3), link_bytes_per_gpu=reduce_link_bytes,
-                             achieved_gbs=round(reduce_link_bytes / reduce_ms / 1e6, 1),
-                             roofline_ms=round(red_roof, 3), fraction_of_roofline=round(red_roof / reduce_ms, 3)),
-            owner_update_and_push=dict(ms=round(opt_ms, 3), link_bytes_per_gpu=push_link_bytes,
-                                       push_roofline_ms=round(push_roof, 3),
-                                       note="includes the Newton-Schulz products of the owned matrices"),
+            n_gpus=world, model=args.preset, link_gbs_roofline=LINK_GBS, link_gbs_measured_peer_copy=LINK_GBS_MEASURED,
+            reduce_scatter=dict(mode="bf16 push + local reduce" if push_mode else "fp32 pull", ms=round(reduce_ms, 3),
+                                link_bytes_per_gpu_per_direction=reduce_link_bytes,
+                                achieved_gbs=round(reduce_link_bytes / reduce_ms / 1e6, 1),
+                                roofline_ms=round(red_roof, 3), fraction_of_roofline=round(red_roof / reduce_ms, 3),
+                                fraction_of_measured_link=round(reduce_link_bytes / (LINK_GBS_MEASURED * 1e6) / reduce_ms, 3)),
+            update_and_push=dict(ms=round(opt_ms, 3), link_bytes_per_gpu_per_direction=push_link_bytes,
+                                 link_roofline_ms=round(push_roof, 3), newton_schulz_at_peak_ms=round(ns_ms, 3),
+                                 adamw_hbm_ms=round(adamw_ms, 3), roofline_ms=round(upd_roof, 3),
+                                 fraction_of_roofline=round(upd_roof / opt_ms, 3)),
             gemm_flag_wait=dict(plain_ms=round(plain, 4), with_wait_ms=round(waited, 4),
                                 overhead_us=round((waited - plain) * 1e3, 2)))))
     dist.destroy_process_group()

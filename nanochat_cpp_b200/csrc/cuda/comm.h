@@ -35,6 +35,22 @@ void comm_reduce_pull(const PeerPtrs& grads, int world, int my_rank, const Segme
                       long long total, float scale, const int* local_flags, int slot, int value, double* sumsq,
                       int* status, int ctas, cudaStream_t s);
 
+// Reduce-scatter with bf16 on the wire, first half: the elements of this rank's gradient that other ranks own are
+// scaled, rounded to bf16 and stored into the owners' receive buffers (`recv.p[owner] + my_rank * recv_stride +
+// position`). `segs_dev`: int64 [nsegs, 5] rows (first vector index, source element offset, destination position,
+// destination rank, element count); a vector is 8 elements, `nvec` vectors in all. At most 128 rows per launch.
+void comm_grad_push(const float* grad, const PeerPtrs& recv, long long recv_stride, int my_rank,
+                    const long long* segs_dev, int nsegs, long long nvec, float scale, int ctas, cudaStream_t s);
+
+// Second half, on the owner: waits (bounded) for `value` in `slot` from every rank, then for every owned element
+//   grad[e] = scale * grad[e] + sum_{r != my_rank} recv[r * recv_stride + position]     (fixed rank order, fp32)
+// and accumulates the sum of squares of the result into `sumsq`. `segs_dev`: int64 [nsegs, 4] rows (first vector
+// index, gradient element offset, receive position, element count). At most 64 rows per launch.
+void comm_grad_reduce_local(float* grad, const __nv_bfloat16* recv, long long recv_stride, int world, int my_rank,
+                            const long long* segs_dev, int nsegs, long long nvec, float scale,
+                            const int* local_flags, int slot, int value, double* sumsq, int* status, int ctas,
+                            cudaStream_t s);
+
 // AdamW on this rank's slice, writing the updated bf16 values into every rank's parameter buffer
 // (values.p[r] + value_offset): the all-gather is the update's store.
 void comm_adamw_push(float* master, const PeerPtrs& values, long long value_offset, int world, const float* grad,
@@ -45,5 +61,12 @@ void comm_adamw_push(float* master, const PeerPtrs& values, long long value_offs
 void comm_muon_apply_push(float* master, const PeerPtrs& values, long long value_offset, int world,
                           const __nv_bfloat16* xb, const float* scale0, const float* line_scale,
                           bool lines_are_rows, int rows, int cols, float lr, float weight_decay, cudaStream_t s);
+
+// The same for a whole shape group in one launch (cols % 8 == 0, every value offset a multiple of 8): `master_ptrs`
+// and `value_offsets` are device arrays of P entries.
+void comm_muon_apply_push_batched(const long long* master_ptrs, const long long* value_offsets, const PeerPtrs& values,
+                                  int world, const __nv_bfloat16* xb, const float* scale0, const float* line_scale,
+                                  bool lines_are_rows, int P, int rows, int cols, float lr, float weight_decay,
+                                  cudaStream_t s);
 
 }  // namespace nc

@@ -214,6 +214,80 @@ __global__ void __launch_bounds__(256) muon_line_sumsq_kernel(const __nv_bfloat1
   }
 }
 
+
+// ---- the small per-matrix statistics of Muon, one CTA per matrix --------------------------------------------------
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.0f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) t += red[w];
+  return t;
+}
+
+// Row equilibration and Frobenius normalisation as one row scale (reference backends/cpu/kernels.cc:1667-1700):
+//   row_scale[r] = (||X||_F / sqrt(rows)) / max(||row r||, 1e-6);  all_scale = 1 / (1.01 ||X diag(row_scale)||_F + 1e-6)
+__global__ void __launch_bounds__(256) muon_prescale_kernel(const float* __restrict__ row_ss,
+                                                            float* __restrict__ row_scale,
+                                                            float* __restrict__ all_scale, int rows) {
+  __shared__ float red[8];
+  const int p = blockIdx.x;
+  const float* ss = row_ss + static_cast<long long>(p) * rows;
+  float* out = row_scale + static_cast<long long>(p) * rows;
+  float t = 0.0f;
+  for (int r = threadIdx.x; r < rows; r += 256) t += ss[r];
+  const float frob = sqrtf(block_sum_256(t, red));
+  const float target = frob / sqrtf(static_cast<float>(rows));
+  float t2 = 0.0f;
+  for (int r = threadIdx.x; r < rows; r += 256) {
+    const float v = ss[r];
+    const float sc = target / fmaxf(sqrtf(v), 1e-6f);
+    out[r] = sc;
+    t2 += v * sc * sc;
+  }
+  const float frob2 = sqrtf(block_sum_256(t2, red));
+  if (threadIdx.x == 0) all_scale[p] = 1.0f / (frob2 * 1.01f + 1e-6f);
+}
+
+// Muon+ rescale, NorMuon second moment and per-line step (reference backends/cpu/kernels.cc:1746-1800):
+//   scale = sqrt(min(rows, cols)) / max(||X||_F, 1e-6);  v = line_ss * scale^2 / line_len
+//   buf2 += (1 - beta2)(v - buf2);  step = rsqrt(max(buf2, 1e-10))
+//   line_scale = step * sqrt(sum v * line_len) / max(sqrt(sum v * line_len * step^2), 1e-10)
+__global__ void __launch_bounds__(256) muon_poststats_kernel(const float* __restrict__ line_ss,
+                                                             const long long* __restrict__ buf2_ptrs,
+                                                             float* __restrict__ scale_out,
+                                                             float* __restrict__ line_scale, int lines, int line_len,
+                                                             float target_norm, float beta2) {
+  __shared__ float red[8];
+  const int p = blockIdx.x;
+  const float* ss = line_ss + static_cast<long long>(p) * lines;
+  float* buf2 = reinterpret_cast<float*>(buf2_ptrs[p]);
+  float* out = line_scale + static_cast<long long>(p) * lines;
+  float t = 0.0f;
+  for (int i = threadIdx.x; i < lines; i += 256) t += ss[i];
+  const float frob = sqrtf(block_sum_256(t, red));
+  const float scale = target_norm / fmaxf(frob, 1e-6f);
+  const float len = static_cast<float>(line_len);
+  float tv = 0.0f, ts = 0.0f;
+  for (int i = threadIdx.x; i < lines; i += 256) {
+    const float v = ss[i] * (scale * scale) / len;
+    float b = buf2[i];
+    b += (1.0f - beta2) * (v - b);
+    buf2[i] = b;
+    const float step = rsqrtf(fmaxf(b, 1e-10f));
+    out[i] = step;                       // finished below, once the two sums are known
+    tv += v;
+    ts += v * len * step * step;
+  }
+  const float v_norm = sqrtf(block_sum_256(tv, red) * len);
+  const float denom = fmaxf(sqrtf(block_sum_256(ts, red)), 1e-10f);
+  const float k = v_norm / denom;
+  for (int i = threadIdx.x; i < lines; i += 256) out[i] *= k;
+  if (threadIdx.x == 0) scale_out[p] = scale;
+}
+
 __global__ void __launch_bounds__(256) muon_apply_batched_kernel(const long long* __restrict__ master_ptrs,
                                                                  const long long* __restrict__ value_ptrs,
                                                                  const __nv_bfloat16* __restrict__ xb,
@@ -350,6 +424,15 @@ void muon_line_sumsq(const __nv_bfloat16* x, float* out, int P, int rows, int co
   } else {
     muon_line_sumsq_kernel<<<dim3((cols / 2 + 255) / 256, P), 256, 0, s>>>(x, out, rows, cols, false);
   }
+}
+void muon_prescale(const float* row_ss, float* row_scale, float* all_scale, int P, int rows, cudaStream_t s) {
+  if (P > 0) muon_prescale_kernel<<<P, 256, 0, s>>>(row_ss, row_scale, all_scale, rows);
+}
+void muon_poststats(const float* line_ss, const long long* buf2_ptrs, float* scale_out, float* line_scale, int P,
+                    int lines, int line_len, float target_norm, float beta2, cudaStream_t s) {
+  if (P > 0)
+    muon_poststats_kernel<<<P, 256, 0, s>>>(line_ss, buf2_ptrs, scale_out, line_scale, lines, line_len, target_norm,
+                                            beta2);
 }
 void muon_apply_batched(const long long* master_ptrs, const long long* value_ptrs, const __nv_bfloat16* xb,
                         const float* scale0, const float* line_scale, bool lines_are_rows, int P, int rows, int cols,

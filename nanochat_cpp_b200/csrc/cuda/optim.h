@@ -29,6 +29,12 @@ void muon_nesterov_batched(const long long* grad_ptrs, const long long* buf1_ptr
 void muon_scale_rows_batched(const float* x, const float* row_scale, const float* all_scale, __nv_bfloat16* out, int P,
                              int rows, int cols, cudaStream_t s);
 void muon_line_sumsq(const __nv_bfloat16* x, float* out, int P, int rows, int cols, bool reduce_cols, cudaStream_t s);
+// One CTA per matrix: row_ss [P, rows] -> row_scale [P, rows], all_scale [P] (row equilibration + normalisation).
+void muon_prescale(const float* row_ss, float* row_scale, float* all_scale, int P, int rows, cudaStream_t s);
+// One CTA per matrix: line_ss [P, lines] + NorMuon state (table of per-matrix buf2 addresses) -> scale [P],
+// line_scale [P, lines]; updates buf2 in place. `target_norm` = sqrt(min(rows, cols)).
+void muon_poststats(const float* line_ss, const long long* buf2_ptrs, float* scale_out, float* line_scale, int P,
+                    int lines, int line_len, float target_norm, float beta2, cudaStream_t s);
 void muon_apply_batched(const long long* master_ptrs, const long long* value_ptrs, const __nv_bfloat16* xb,
                         const float* scale0, const float* line_scale, bool lines_are_rows, int P, int rows, int cols,
                         float lr, float weight_decay, cudaStream_t s);

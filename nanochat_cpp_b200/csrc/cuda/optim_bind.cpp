@@ -107,6 +107,23 @@ void register_optim(pybind11::module_& m) {
                            bptr(xb), scale0.data_ptr<float>(), line_scale.data_ptr<float>(), lines_are_rows, xb.size(0),
                            xb.size(1), xb.size(2), lr, wd, at::cuda::getCurrentCUDAStream());
   });
+  m.def("muon_prescale", [](const Tensor& row_ss, Tensor& row_scale, Tensor& all_scale) {
+    const c10::cuda::CUDAGuard g(row_ss.device());
+    TORCH_CHECK(row_ss.dim() == 2 && row_ss.is_contiguous() && row_scale.is_contiguous() && all_scale.is_contiguous() &&
+                    row_scale.numel() == row_ss.numel() && all_scale.numel() == row_ss.size(0), "muon_prescale");
+    nc::muon_prescale(row_ss.data_ptr<float>(), row_scale.data_ptr<float>(), all_scale.data_ptr<float>(),
+                      row_ss.size(0), row_ss.size(1), at::cuda::getCurrentCUDAStream());
+  });
+  m.def("muon_poststats", [](const Tensor& line_ss, const Tensor& buf2_ptrs, Tensor& scale, Tensor& line_scale,
+                             int64_t line_len, double target_norm, double beta2) {
+    const c10::cuda::CUDAGuard g(line_ss.device());
+    TORCH_CHECK(line_ss.dim() == 2 && line_ss.is_contiguous() && line_scale.is_contiguous() &&
+                    line_scale.numel() == line_ss.numel() && scale.numel() == line_ss.size(0) &&
+                    buf2_ptrs.scalar_type() == torch::kInt64 && buf2_ptrs.numel() == line_ss.size(0), "muon_poststats");
+    nc::muon_poststats(line_ss.data_ptr<float>(), reinterpret_cast<const long long*>(buf2_ptrs.data_ptr<int64_t>()),
+                       scale.data_ptr<float>(), line_scale.data_ptr<float>(), line_ss.size(0), line_ss.size(1), line_len,
+                       target_norm, beta2, at::cuda::getCurrentCUDAStream());
+  });
   m.def("muon_nesterov", &muon_nesterov);
   m.def("muon_scale_rows", &muon_scale_rows);
   m.def("muon_apply", &muon_apply);

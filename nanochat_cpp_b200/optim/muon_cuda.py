@@ -5,11 +5,11 @@ Polar Express iterate kept in bf16 between products, as the reference's bf16 CUD
 (docs/model.md:402-416). Per shape group `[P, rows, cols]`:
 
   1. `muon_nesterov`  momentum + Nesterov blend, per-row sum of squares         (1 launch / matrix)
-  2. row equilibration + Frobenius normalisation folded into one row scale      (tiny [P, rows] math)
+  2. `muon_prescale`  row equilibration + Frobenius normalisation as one row scale (1 launch, one CTA / matrix)
   3. `muon_scale_rows` applies it and writes the bf16 iterate                   (1 launch / matrix)
   4. 5 x { A = X X^T (or X^T X), B = b A + c A A, X = a X + B X (or X B) }      (3 batched GEMMs / step,
      residual-add epilogue, no separate axpby passes)
-  5. line sums of squares -> Muon+ rescale, NorMuon second moment and step size ([P, lines] math)
+  5. `muon_line_sumsq` + `muon_poststats`: Muon+ rescale, NorMuon second moment and per-line step (2 launches)
   6. `muon_apply`  cautious decay + update of the fp32 master and bf16 copy     (1 launch / matrix)
 """
 from __future__ import annotations
@@ -52,11 +52,16 @@ class MuonGroupState:
         self.x32 = torch.empty(P, rows, cols, dtype=torch.float32, device=device)
         self.X = torch.empty(P, rows, cols, dtype=torch.bfloat16, device=device)
         self.row_ss = torch.empty(P, rows, dtype=torch.float32, device=device)
+        self.row_scale = torch.empty(P, rows, dtype=torch.float32, device=device)
+        self.all_scale = torch.empty(P, dtype=torch.float32, device=device)
+        lines = rows if rows >= cols else cols
+        self.scale = torch.empty(P, dtype=torch.float32, device=device)
+        self.line_scale = torch.empty(P, lines, dtype=torch.float32, device=device)
         self._tables = {}
 
-    def table(self, key: str, tensors) -> torch.Tensor:
-        """Device array of the tensors' addresses, cached as long as the addresses stay the same."""
-        ptrs = tuple(t.data_ptr() for t in tensors)
+    def table(self, key: str, tensors, values=None) -> torch.Tensor:
+        """Device array of the tensors' addresses (or of the given integers), cached while they stay the same."""
+        ptrs = tuple(values) if values is not None else tuple(t.data_ptr() for t in tensors)
         hit = self._tables.get(key)
         if hit is None or hit[0] != ptrs:
             hit = (ptrs, torch.tensor(ptrs, dtype=torch.int64, device=self.x32.device))
@@ -85,15 +90,10 @@ def muon_group_step(grads: List[torch.Tensor], masters: List[torch.Tensor], valu
         for p in range(P):
             C.muon_nesterov(grads[p], buf1[p], scratch.x32[p], scratch.row_ss[p], momentum, gs)
     row_ss = scratch.row_ss[:P]
-    frob = torch.sqrt(row_ss.sum(-1, keepdim=True))
-    target = frob / math.sqrt(float(rows))
-    row_norm = torch.sqrt(row_ss).clamp_min(1e-6)
-    row_scale = target / row_norm
-    frob2 = torch.sqrt((row_ss * row_scale * row_scale).sum(-1))
-    all_scale = 1.0 / (frob2 * 1.01 + 1e-6)
-    row_scale = row_scale.contiguous()
+    row_scale, all_scale = scratch.row_scale[:P], scratch.all_scale[:P]
+    C.muon_prescale(row_ss, row_scale, all_scale)
     if batched:
-        C.muon_scale_rows_batched(scratch.x32[:P], row_scale, all_scale.contiguous(), scratch.X[:P])
+        C.muon_scale_rows_batched(scratch.x32[:P], row_scale, all_scale, scratch.X[:P])
     else:
         for p in range(P):
             C.muon_scale_rows(scratch.x32[p], row_scale[p], all_scale[p:p + 1], scratch.X[p])
@@ -104,25 +104,19 @@ def muon_group_step(grads: List[torch.Tensor], masters: List[torch.Tensor], valu
         line_ss = C.muon_line_sumsq(X, reduce_cols)             # [P, lines]
     else:
         line_ss = X.float().square().sum(red)
-    frob_post = torch.sqrt(line_ss.sum(-1, keepdim=True))
-    scale = math.sqrt(float(min(rows, cols))) / frob_post.clamp_min(1e-6)   # [P, 1]
-    v_mean = line_ss * (scale * scale) / float(line_len)
-    v_norm = torch.sqrt(v_mean.sum(-1, keepdim=True) * float(line_len))
-    b2 = torch.stack(buf2)
-    b2.add_((1.0 - beta2) * (v_mean - b2))
-    torch._foreach_copy_(list(buf2), list(b2.unbind(0)))
-    step_size = torch.rsqrt(b2.clamp_min(1e-10))
-    sum_scaled = (v_mean * float(line_len) * step_size * step_size).sum(-1, keepdim=True)
-    denom = torch.sqrt(sum_scaled).clamp_min(1e-10)
-    line_scale = (step_size * (v_norm / denom)).contiguous()
-    scale = scale.contiguous()
+    scale, line_scale = scratch.scale[:P], scratch.line_scale[:P]
+    C.muon_poststats(line_ss.contiguous(), scratch.table("b2", buf2), scale, line_scale, line_len,
+                     math.sqrt(float(min(rows, cols))), beta2)
     if apply_fn is None and batched and X.is_contiguous() and all(m.is_contiguous() for m in masters):
         vt = scratch.table("v", values) if all(v is not None for v in values) else None
-        C.muon_apply_batched(scratch.table("m", masters), vt, X, scale.reshape(-1), line_scale, reduce_cols, lr,
-                             weight_decay)
+        C.muon_apply_batched(scratch.table("m", masters), vt, X, scale, line_scale, reduce_cols, lr, weight_decay)
+        return
+    batch_fn = getattr(apply_fn, "batched", None)
+    if batch_fn is not None and batched and X.is_contiguous() and all(m.is_contiguous() for m in masters):
+        batch_fn(scratch, masters, X, scale, line_scale, reduce_cols, lr, weight_decay)     # one launch for the group
         return
     for p in range(P):
         if apply_fn is not None:
-            apply_fn(p, masters[p], X[p], scale[p], line_scale[p], reduce_cols, lr, weight_decay)
+            apply_fn(p, masters[p], X[p], scale[p:p + 1], line_scale[p], reduce_cols, lr, weight_decay)
         else:
-            C.muon_apply(masters[p], values[p], X[p], scale[p], line_scale[p], reduce_cols, lr, weight_decay)
+            C.muon_apply(masters[p], values[p], X[p], scale[p:p + 1], line_scale[p], reduce_cols, lr, weight_decay)

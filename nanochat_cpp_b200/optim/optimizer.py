@@ -17,6 +17,7 @@ contributes to the global norm.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
@@ -148,26 +149,16 @@ class Optimizer:
             self.last_grad_norm = norm
         lrm = self.lr_multiplier_override if self.lr_multiplier_override >= 0.0 \
             else self.scheduler.lr_multiplier(step)
-        for g in self.adamw_groups:
-            for s in g.params:
-                if not self.owned(s):
-                    continue
-                stt = self.state[s.name]
-                a, b = self.adamw_slices.get(s.name, (0, s.count))
-                if b <= a:
-                    continue
-                lo, hi = s.offset + a, s.offset + b
-                if self.pusher is not None:
-                    self.pusher.adamw_push(st.master[lo:hi], lo, st.grad[lo:hi], stt["m"].view(-1), stt["v"].view(-1),
-                                           lr=g.lr * lrm, beta1=g.beta1, beta2=g.beta2, eps=g.eps,
-                                           weight_decay=g.weight_decay, step=step, grad_scale=clip_scale)
-                    continue
-                ops.adamw_update(st.master[lo:hi], None if st.value is st.master else st.value[lo:hi],
-                                 st.grad[lo:hi], stt["m"].view(-1), stt["v"].view(-1), lr=g.lr * lrm,
-                                 beta1=g.beta1, beta2=g.beta2, eps=g.eps, weight_decay=g.weight_decay, step=step,
-                                 grad_scale=clip_scale)
-        if self.pusher is not None:
-            self.pusher.after_adamw(step)
+        # Under the fused data-parallel transport the AdamW slices (bound by HBM and by the NVLink stores of their
+        # pushes) run on a side stream beside Newton-Schulz (bound by the tensor cores); the streams join at the end.
+        side = None
+        if self.pusher is not None and hasattr(self.pusher, "side_stream") and st.device.type == "cuda":
+            side = self.pusher.side_stream()
+            side.wait_stream(torch.cuda.current_stream(st.device))
+        with torch.cuda.stream(side) if side is not None else contextlib.nullcontext():
+            self._adamw_groups_step(step, lrm, clip_scale)
+            if self.pusher is not None:
+                self.pusher.after_adamw(step)
         momentum = self.scheduler.muon_momentum(step)
         wd = self.scheduler.weight_decay(step)
         use_kernels = st.device.type == "cuda" and ops.get_mode() == "kernels" and st.value is not st.master
@@ -204,4 +195,27 @@ class Optimizer:
                 self.state[s.name]["buf2"].copy_(buf2[k])
         if self.pusher is not None:
             self.pusher.after_muon(step)
+        if side is not None:
+            torch.cuda.current_stream(st.device).wait_stream(side)
         self.step_count = step
+
+    def _adamw_groups_step(self, step: int, lrm: float, clip_scale) -> None:
+        st = self.store
+        for g in self.adamw_groups:
+            for s in g.params:
+                if not self.owned(s):
+                    continue
+                stt = self.state[s.name]
+                a, b = self.adamw_slices.get(s.name, (0, s.count))
+                if b <= a:
+                    continue
+                lo, hi = s.offset + a, s.offset + b
+                if self.pusher is not None:
+                    self.pusher.adamw_push(st.master[lo:hi], lo, st.grad[lo:hi], stt["m"].view(-1), stt["v"].view(-1),
+                                           lr=g.lr * lrm, beta1=g.beta1, beta2=g.beta2, eps=g.eps,
+                                           weight_decay=g.weight_decay, step=step, grad_scale=clip_scale)
+                    continue
+                ops.adamw_update(st.master[lo:hi], None if st.value is st.master else st.value[lo:hi],
+                                 st.grad[lo:hi], stt["m"].view(-1), stt["v"].view(-1), lr=g.lr * lrm,
+                                 beta1=g.beta1, beta2=g.beta2, eps=g.eps, weight_decay=g.weight_decay, step=step,
+                                 grad_scale=clip_scale)

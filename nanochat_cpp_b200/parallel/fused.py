@@ -1,11 +1,15 @@
-"""Fused data-parallel transport: reduce-scatter by peer loads + owner update that pushes parameters.
+"""Fused data-parallel transport: bf16 reduce-scatter by peer stores + owner update that pushes parameters.
 
 One step, per rank (see csrc/cuda/comm.cu for the kernels):
 
-  backward ──► layer i done ──► signal(slot i)            (compute stream, after the bucket's last wgrad)
-                              └► reduce_pull(bucket i)     (comm stream: waits for slot i of ALL ranks, then
-                                                            loads this rank's segments from every peer,
-                                                            sums, scales, stores locally, adds to sumsq)
+  backward ──► layer i done ──► grad_push(bucket i)        (push stream: every element another rank owns is
+                                                            rounded to bf16 and stored into that owner's
+                                                            receive slot over NVLink), then signal(slot i)
+                              └► grad_reduce_local(i)      (comm stream: waits for slot i of ALL ranks, then
+                                                            sums its own fp32 values and the N-1 received bf16
+                                                            values in rank order, stores locally, adds to sumsq)
+  (`NANOCHAT_DP_REDUCE=pull` selects the first design instead: signal, then the owner loads its fp32 segments
+   from every peer's gradient buffer - twice the bytes, by loads.)
   all buckets reduced ──► all-reduce of one double (grad norm) ──► clip scale
   AdamW slices: update + push bf16 to every rank ──► signal(slot A)
   Muon matrices: Newton-Schulz, update + push bf16 to every rank ──► signal(slot M)
@@ -34,6 +38,40 @@ class SymmetricBuffer:
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
 
 
+def plan_reduce_scatter(specs, owners: Dict[str, int], world: int, L: int):
+    """Layout of the bf16 reduce-scatter, a pure function of the parameter list (every rank computes the same).
+
+    Returns `(placed, cap)`: `placed[rank][bucket]` lists `(offset, count, position)` for every contiguous run of
+    elements that `rank` owns in `bucket` (offset in the flat gradient buffer, position in the owner's receive
+    space, padded to 8 elements); `cap` is the largest receive space over the ranks. Buckets: b < L is layer b
+    (its matrices and its value embedding), L is the LM head, L + 1 the token embedding and the scalars."""
+    from .dp import adamw_slice
+
+    def bucket_of(s) -> int:
+        return L if s.kind == "lm_head" else s.layer if s.kind in ("matrix", "value_embed") else L + 1
+
+    owned = [[[] for _ in range(L + 2)] for _ in range(world)]
+    for s in specs:
+        o = owners[s.name]
+        for r in range(world):
+            if o == r:
+                owned[r][bucket_of(s)].append((s.offset, s.count))
+            elif o == -1:
+                a, e = adamw_slice(s, r, world)
+                if e > a:
+                    owned[r][bucket_of(s)].append((s.offset + a, e - a))
+    placed = [[[] for _ in range(L + 2)] for _ in range(world)]
+    cap = 0
+    for r in range(world):
+        pos = 0
+        for b in range(L + 2):
+            for off, cnt in sorted(owned[r][b]):
+                placed[r][b].append((off, cnt, pos))
+                pos += (cnt + 7) // 8 * 8
+        cap = max(cap, pos)
+    return placed, cap
+
+
 class FusedTransport:
     def __init__(self, rank: int, world: int, device, group=None):
         self.rank, self.world = rank, world
@@ -44,10 +82,16 @@ class FusedTransport:
         self.value: Optional[SymmetricBuffer] = None
         self.flags: Optional[SymmetricBuffer] = None
         self.comm_stream = torch.cuda.Stream(device=self.device)
+        self.push_stream = torch.cuda.Stream(device=self.device)
+        import os
+        self.reduce_mode = os.environ.get("NANOCHAT_DP_REDUCE", "push")     # push (bf16, stores) | pull (fp32, loads)
+        self.recv: Optional[SymmetricBuffer] = None
+        self.recv_stride = 0
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
         self.buckets: List[dict] = []
         self.num_slots = 0
         self.reduce_ctas = 148 * 2
+        self.push_ctas = 148 * 2
 
     # ------------------------------------------------------------------ allocation
     def allocator(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -92,11 +136,43 @@ class FusedTransport:
             self.buckets.append(dict(segs=t, total=total, n=len(segs)))
         if max(bk["n"] for bk in self.buckets) > 64:
             raise ValueError("a reduction bucket has more than 64 segments (the kernel's segment table)")
+        if self.reduce_mode == "push":
+            self._build_push_tables(store, owners, L)
         self._events = [torch.cuda.Event() for _ in self.buckets]
         self.slot_adamw = L + 2
         self.slot_muon = L + 3
         self.num_slots = L + 4
         self.flags = SymmetricBuffer(self.num_slots * self.world, torch.int32, self.device, self.group)
+
+    def _build_push_tables(self, store, owners: Dict[str, int], L: int) -> None:
+        """Tables of the bf16 reduce-scatter. Every rank computes the ownership of ALL ranks (it is a pure function
+        of the parameter list), lays each owner's elements out bucket by bucket in a receive space (positions
+        padded to 8 elements = one 16-byte bf16 store) and derives: for every bucket, what it must push where, and
+        where its own elements sit. The receive buffer holds one such space per source rank."""
+        placed, cap = plan_reduce_scatter(store.specs, owners, self.world, L)
+        self.recv_stride = cap
+        self.recv = SymmetricBuffer(max(cap, 8) * self.world, torch.bfloat16, self.device, self.group)
+        for b, bk in enumerate(self.buckets):
+            rows, first = [], 0
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                for off, cnt, pos in placed[r][b]:
+                    rows.append([first, off, pos, r, cnt])
+                    first += (cnt + 7) // 8
+            if len(rows) > 128:
+                raise ValueError("a bucket pushes more than 128 segments (the kernel's segment table)")
+            bk["push_rows"] = torch.tensor(rows if rows else [[0, 0, 0, 0, 0]], dtype=torch.int64,
+                                           device=self.device).reshape(-1, 5)
+            bk["push_n"], bk["push_vec"] = len(rows), first
+            rows, first = [], 0
+            for off, cnt, pos in placed[self.rank][b]:
+                rows.append([first, off, pos, cnt])
+                first += (cnt + 7) // 8
+            bk["own_rows"] = torch.tensor(rows if rows else [[0, 0, 0, 0]], dtype=torch.int64,
+                                          device=self.device).reshape(-1, 4)
+            bk["own_n"], bk["own_vec"] = len(rows), first
+        self._events2 = [torch.cuda.Event() for _ in self.buckets]
 
     # ------------------------------------------------------------------ step pieces
     def signal(self, slot: int, value: int) -> None:
@@ -107,8 +183,29 @@ class FusedTransport:
         """Publish "bucket b is final on this rank" on the current stream and enqueue this rank's share of the
         reduction on the communication stream."""
         from ..ops import cuda as K
-        self.signal(b, step)
         bk = self.buckets[b]
+        status = K._C.status_tensor(self.device.index)
+        if self.reduce_mode == "push":
+            # The push never waits for anybody, so it may run as soon as this rank's bucket is final; the local
+            # reduction is ordered after this rank's own push + signal (second event), for the reason given below.
+            ev = self._events[b]
+            ev.record(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.push_stream):
+                self.push_stream.wait_event(ev)
+                if bk["push_n"]:
+                    K._C.comm_grad_push(self.grad.tensor, self.recv.ptrs, self.recv_stride, self.rank, bk["push_rows"],
+                                        bk["push_vec"], scale, self.push_ctas)
+                self.signal(b, step)
+                self._events2[b].record(self.push_stream)
+            if bk["own_n"] == 0:
+                return
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(self._events2[b])
+                K._C.comm_grad_reduce_local(self.grad.tensor, self.recv.tensor, self.recv_stride, self.world, self.rank,
+                                            bk["own_rows"], bk["own_vec"], scale, self.flags.tensor, b, step,
+                                            self.sumsq, status, self.reduce_ctas)
+            return
+        self.signal(b, step)
         if bk["total"] == 0:
             return
         # The reduction must not become resident before this rank's own backward has reached the bucket: its
@@ -121,7 +218,7 @@ class FusedTransport:
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ev)
             K._C.comm_reduce_pull(self.grad.ptrs, self.rank, bk["segs"], bk["total"], scale, self.flags.tensor, b,
-                                  step, self.sumsq, K._C.status_tensor(self.device.index), self.reduce_ctas)
+                                  step, self.sumsq, status, self.reduce_ctas)
 
     def begin_reduction(self) -> None:
         with torch.cuda.stream(self.comm_stream):
@@ -129,10 +226,12 @@ class FusedTransport:
         # the reduction kernels must not start before this step's zero_() of sumsq, nor before earlier work on
         # the compute stream that they are ordered after by flags only
         self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+        self.push_stream.wait_stream(torch.cuda.current_stream(self.device))
 
     def global_grad_norm(self, clip: float):
         """Joins the communication stream, all-reduces the squared norm and returns (norm, clip_scale)."""
         torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        torch.cuda.current_stream(self.device).wait_stream(self.push_stream)
         total = self.sumsq.clone()
         if self.world > 1:
             dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group)
@@ -187,7 +286,19 @@ class Pusher:
 
         def apply(p, master, xb, scale0, line_scale, lines_are_rows, lr, wd):
             t.muon_apply_push(master, specs[p].offset, xb, scale0, line_scale, lines_are_rows, lr, wd)
+
+        def batched(scratch, masters, X, scale, line_scale, lines_are_rows, lr, wd):
+            from ..ops import cuda as K
+            offs = scratch.table("voff", None, values=tuple(s.offset for s in specs))
+            K._C.comm_muon_apply_push_batched(scratch.table("m", masters), offs, t.value.ptrs, X, scale, line_scale,
+                                              lines_are_rows, lr, wd)
+        if all(s.offset % 8 == 0 for s in specs):
+            apply.batched = batched
         return apply
+
+    def side_stream(self):
+        """Stream on which the optimizer may run the AdamW slices while Newton-Schulz runs on the compute stream."""
+        return self.t.comm_stream
 
     def push_span(self, offset: int, count: int) -> None:
         self.t.push_span(offset, count)

@@ -41,6 +41,69 @@ def test_reduce_pull_and_flags():
     K.check_status()
 
 
+def test_bf16_push_reduce_scatter_with_ranks_emulated_on_one_gpu():
+    """grad_push + grad_reduce_local: every "rank" pushes what the others own (bf16, scaled) into their receive
+    slots, flags are published, then every owner reduces locally. Runs odd counts so the partial-vector tails are
+    exercised, and a poisoned receive buffer so an element nobody pushed would show."""
+    K = _K()
+    C = K._C
+    world, n, scale = 4, 1 << 15, 0.5
+    g = torch.Generator(device="cuda").manual_seed(12)
+    grads = [torch.randn(n, device="cuda", generator=g) for _ in range(world)]
+    orig = [t.clone() for t in grads]
+    # owner r holds two runs: a long aligned one and a short odd one
+    runs = {r: [(r * 4096, 4096 - 3 * r), (20000 + r * 40, 37)] for r in range(world)}
+    placed, cap = {}, 0
+    for r in range(world):
+        pos, rows = 0, []
+        for off, cnt in runs[r]:
+            rows.append((off, cnt, pos))
+            pos += (cnt + 7) // 8 * 8
+        placed[r], cap = rows, max(cap, pos)
+    recv = [torch.full((world * cap,), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    rptrs = [t.data_ptr() for t in recv]
+    flags = [torch.zeros(2 * world, dtype=torch.int32, device="cuda") for _ in range(world)]
+    fptrs = [f.data_ptr() for f in flags]
+    status = C.status_tensor(0)
+    for src in range(world):
+        rows, first = [], 0
+        for owner in range(world):
+            if owner == src:
+                continue
+            for off, cnt, pos in placed[owner]:
+                rows.append([first, off, pos, owner, cnt])
+                first += (cnt + 7) // 8
+        C.comm_grad_push(grads[src], rptrs, cap, src, torch.tensor(rows, dtype=torch.int64, device="cuda"), first,
+                         scale, 16)
+        C.comm_signal(fptrs, src, 1, 3)
+    torch.cuda.synchronize()
+    for owner in range(world):
+        rows, first = [], 0
+        for off, cnt, pos in placed[owner]:
+            rows.append([first, off, pos, cnt])
+            first += (cnt + 7) // 8
+        acc = torch.zeros(1, dtype=torch.float64, device="cuda")
+        C.comm_grad_reduce_local(grads[owner], recv[owner], cap, world, owner,
+                                 torch.tensor(rows, dtype=torch.int64, device="cuda"), first, scale, flags[owner], 1, 3,
+                                 acc, status, 8)
+        ss = 0.0
+        for off, cnt, _ in placed[owner]:
+            want = torch.zeros(cnt, device="cuda")
+            for r in range(world):
+                part = orig[r][off:off + cnt] * scale
+                want += part if r == owner else part.to(torch.bfloat16).float()
+            got = grads[owner][off:off + cnt]
+            assert torch.allclose(got, want, rtol=2e-6, atol=1e-7), (owner, off)     # the kernel may fuse scale * own into an FMA
+            ss += float(want.double().square().sum())
+        assert abs(float(acc) - ss) <= 1e-6 * ss
+        # nothing outside the owned runs was touched
+        mask = torch.ones(n, dtype=torch.bool, device="cuda")
+        for off, cnt, _ in placed[owner]:
+            mask[off:off + cnt] = False
+        assert torch.equal(grads[owner][mask], orig[owner][mask])
+    K.check_status()
+
+
 def test_adamw_and_muon_push():
     K = _K()
     C = K._C
