@@ -224,3 +224,86 @@ def main(args, sampler_cls=None) -> int:
     if dist is not None:
         dist.destroy_process_group()
     return 0
+
+
+GEN_RE = re.compile(r"^\[harness\] generate prompts=(\d+) prompt_tokens=(\d+) new_tokens=(\d+) wall_s=([\d.]+)")
+
+
+def main_decode(args, sampler_cls=None) -> int:
+    """Decode benchmark through the reference's own `GenerateMultiPrompt` (src/generate.cc:578-612): one replica per
+    GPU, `--prompts` prompts of `--prompt-len` uniform-random ids, greedy decode of `--new-tokens` tokens each. The
+    reference prefills each prompt at batch 1 and decodes it token by token, sampling on the host, so only the
+    combined time exists: `value` is generated tokens / wall-clock seconds of the whole call (prefill included),
+    max over ranks."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo")
+    reason = ensure_built() if rank == 0 else None
+    if dist is not None:
+        dist.barrier()
+    d = ref_dir()
+    exe = os.path.join(d, "ref_train")
+    rec = None
+    if reason is None:
+        layers, hidden, heads, kv, vocab, seq = PRESETS[args.preset]
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        gpu = visible.split(",")[local_rank] if visible else str(local_rank)
+        env = dict(os.environ)
+        env.update({"CUDA_VISIBLE_DEVICES": gpu, "NANOCHAT_SANDBOX": "bench"})
+        cmd = [exe, "generate", "--layers", str(layers), "--hidden", str(hidden), "--heads", str(heads), "--kv-heads",
+               str(kv), "--vocab", str(vocab), "--padded-vocab", str(vocab), "--seq", str(seq), "--prompts",
+               str(args.prompts), "--prompt-tokens", str(args.prompt_len), "--max-tokens", str(args.new_tokens),
+               "--seed", str(rank)]
+        sampler = None
+        if rank == 0 and sampler_cls is not None:
+            sampler = sampler_cls(int(gpu))
+            sampler.start()
+        try:
+            p = subprocess.run(cmd, cwd=d, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                               timeout=float(os.environ.get("NANOCHAT_REF_TIMEOUT", "780")))
+            out = p.stdout
+        except subprocess.TimeoutExpired as e:
+            out = (e.stdout or b"").decode() if isinstance(e.stdout, bytes) else (e.stdout or "")
+            reason = "reference generate passed its time limit"
+        clocks = sampler.stop() if sampler is not None else {}
+        for line in out.splitlines():
+            m = GEN_RE.match(line)
+            if m:
+                rec = {"new": int(m.group(3)), "wall_s": float(m.group(4)), "clocks": clocks}
+        if rec is None and reason is None:
+            reason = "reference generate printed no result: " + " | ".join(out.strip().splitlines()[-3:])[-300:]
+    wall = rec["wall_s"] if rec else -1.0
+    if dist is not None:
+        import torch
+        t = torch.tensor([wall, 1.0 if reason is not None else 0.0], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        wall = float(t[0])
+        if float(t[1]) > 0 and reason is None:
+            reason = "another rank's reference process failed"
+    if rank == 0:
+        if reason is not None:
+            print(json.dumps({"impl": "reference", "unavailable": reason}))
+        else:
+            total_new = rec["new"] * world
+            print(json.dumps({
+                "metric": "decode_tokens_per_sec", "value": round(total_new / wall, 1), "unit": "tokens/s",
+                "n_gpus": world, "steps": args.new_tokens, "warmup": 1, "ms_per_step": round(wall * 1e3 / args.new_tokens / args.prompts, 4),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "reference",
+                "data": "uniform-random prompt ids, random-init weights",
+                "e2e": {"value": round(total_new / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4,
+                        "d2h_bytes_per_step": PRESETS[args.preset][4] * 4},
+                "gpu_launches": None, "clocks": rec["clocks"],
+                "config": {"model": args.preset, "prompts_per_gpu": args.prompts, "prompt_len": args.prompt_len,
+                           "new_tokens": args.new_tokens, "dtype": "bf16", "sampling": "greedy",
+                           "note": "reference GenerateMultiPrompt: contiguous KV cache, batch-1 prefill and decode per "
+                                   "prompt, host sampling; wall clock of the whole call (prefill included)",
+                           "parallelism": f"{world} replicas"}}))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0

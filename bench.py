@@ -36,6 +36,12 @@ def parse():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="train", choices=["train", "decode"],
+                    help="train: d20 pretraining tokens/s (the headline). decode: batched KV-cache inference on the same "
+                         "architecture, one replica per GPU: prefill tok/s, decode tok/s, p50 per-token latency")
+    ap.add_argument("--prompts", type=int, default=64, help="decode mode: prompts per GPU")
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--preset", default="d20")
     ap.add_argument("--batch", type=int, default=32, help="sequences per GPU per step")
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-batch (0 = whole batch)")
@@ -112,13 +118,30 @@ def run_reference(args):
     its own TrainLoop by baseline/ref_arm.py. Nothing of this repository's package is imported on this path."""
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from baseline import ref_arm
+    if args.mode == "decode":
+        return ref_arm.main_decode(args, ClockSampler)
     return ref_arm.main(args, ClockSampler)
+
+
+def run_decode(args):
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from nanochat_cpp_b200.bench import decode_bench
+    doc = decode_bench.run(args.preset, args.prompts, args.prompt_len, args.new_tokens, sampler_cls=ClockSampler,
+                           warmup=args.warmup)
+    if doc is not None:
+        print(json.dumps(doc))
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        dist.destroy_process_group()
+    return 0
 
 
 def main():
     args = parse()
     if args.impl == "reference":
         return run_reference(args)
+    if args.mode == "decode":
+        return run_decode(args)
 
     import torch
     import torch.distributed as dist

@@ -19,10 +19,18 @@ def _r(*shape, scale=1.0):
 
 
 def _close(a, b, tol, name=""):
+    """Max-normalised bound, then every element: the probabilities and the score gradients pass through bf16 on
+    their way into the second product (2^-9 each, relative to the terms they weight), the result is rounded to
+    bf16 once more, so an element may be off by a few 2^-8 of its own size plus of the tensor's typical size."""
+    from gpu_check import close_elementwise
     a, b = a.float(), b.float()
     err = (a - b).abs().max().item()
     mag = b.abs().max().item() + 1e-6
     assert err <= tol * mag, (name, err, mag)
+    rms = b.square().mean().sqrt().item()
+    grad = name.startswith("d")
+    close_elementwise(a, b, rtol=2.0 ** -5 if grad else 2.0 ** -6, atol=(2.0 ** -5 if grad else 2.0 ** -6) * rms,
+                      name=name, frac=1e-4)
 
 
 CASES = [

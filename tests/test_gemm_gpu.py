@@ -15,10 +15,19 @@ def _rand(*shape, scale=1.0):
 
 
 def _close(got, want, tol=2e-2):
+    """Max-normalised bound, then a bound on every element: two bf16 roundings (2^-7 relative) plus, for elements
+    that cancel towards zero, 2^-8 of the tensor's typical magnitude (fp32 results: accumulation order only)."""
+    from gpu_check import close_elementwise
+    is_bf16 = got.dtype == torch.bfloat16
     got, want = got.float(), want.float()
     err = (got - want).abs().max().item()
     ref = want.abs().max().item() + 1e-6
     assert err <= tol * ref, (err, ref)
+    rms = want.square().mean().sqrt().item()
+    if is_bf16:
+        close_elementwise(got, want, rtol=2.0 ** -7, atol=2.0 ** -8 * rms)
+    else:
+        close_elementwise(got, want, rtol=2.0 ** -12, atol=2.0 ** -12 * rms)
 
 
 SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 1280), (200, 264, 72), (1000, 1288, 328), (64, 8, 16),

@@ -51,16 +51,35 @@ def test_kernels_match_torch_ops():
         ops.set_mode("kernels")
     assert abs(loss_k - loss_t) < 2e-2, (loss_k, loss_t)
     assert abs(eval_k - loss_k) < 2e-2
+    # The yardstick is an fp32 run of the same graph on the same (bf16-representable) weights. Per parameter, the
+    # kernel path may be as far from it as bf16 arithmetic makes the PyTorch-operator path, not further: its error
+    # is bounded by 1.5x that path's error plus 2 % (5 % for the few-element scalars, which are sums of millions of
+    # cancelling terms), and its direction must agree with the fp32 gradient.
+    m32 = GPT(cfg, "cuda", torch.float32, seed=7, head_chunk_rows=256)
+    m32.params.master.copy_(m.params.value.float())
+    m32.params.sync_compute()
+    ops.set_mode("torch")
+    try:
+        m32.zero_grad()
+        loss_32 = m32.forward_backward(tokens, targets).item()
+        g_32 = m32.params.grad.clone()
+    finally:
+        ops.set_mode("kernels")
+    assert abs(loss_k - loss_32) < 1e-2, (loss_k, loss_32)
+    worst = 0.0
     for s in m.params.specs:
+        ref32 = g_32[s.offset:s.offset + s.count].double()
+        if ref32.norm() < 1e-7:
+            continue
         a = g_k[s.offset:s.offset + s.count].double()
         b = g_t[s.offset:s.offset + s.count].double()
-        if b.norm() < 1e-7:
-            continue
-        cos = float((a * b).sum() / (a.norm() * b.norm() + 1e-30))
-        rel = float((a - b).norm() / (b.norm() + 1e-30))
-        # scalar parameters are sums with heavy cancellation: their bf16 noise floor is much higher
-        limit = 0.12 if s.count > 64 else 0.35
-        assert cos > 0.99 and rel < limit, (s.name, cos, rel)
+        rel_k = float((a - ref32).norm() / ref32.norm())
+        rel_t = float((b - ref32).norm() / ref32.norm())
+        cos = float((a * ref32).sum() / (a.norm() * ref32.norm() + 1e-30))
+        slack = 0.02 if s.count > 64 else 0.05
+        assert cos > 0.995 and rel_k <= 1.5 * rel_t + slack, (s.name, cos, rel_k, rel_t)
+        worst = max(worst, rel_k)
+    assert worst < 0.12, worst
 
 
 def test_training_reduces_loss():
