@@ -29,8 +29,8 @@ def test_attention_backward_against_differences_of_the_forward_kernel(B, T, H, K
     # a probe moves one whole head row (D elements): the change in a single score from one element is below the
     # rounding of the bf16 output row it is observed through
     for name, x, gr in (("dq", q, dq), ("dk", k, dk), ("dv", v, dv)):
-        fd_regression(loss, x, gr, delta=2.0 ** -3, probes=64, gen=g, name=f"attention {name}", slope_tol=0.08,
-                      min_corr=0.95, block=D)
+        fd_regression(loss, x, gr, delta=2.0 ** -2, probes=96, gen=g, name=f"attention {name}", slope_tol=0.1,
+                      min_corr=0.93, block=D)
     K.check_status()
 
 
