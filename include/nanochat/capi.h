@@ -317,6 +317,22 @@ int64_t ncb_roofline(const nanochat_config* config, const char* device, const ch
                      int muon_ns_steps, double measured_bf16_tflops, double measured_hbm_gbs, int as_table, char* out,
                      int64_t capacity);
 double ncb_muon_flops_per_step(const nanochat_config* config, int ns_steps);
+
+/* ---- planning layer (host only): model specification + device declaration -> operator plan; training-run plan.
+ * `ncb_plan_json`: `spec_path` is a closed JSON model specification (unknown keys are errors), `caps_path` a device
+ * declaration (`caps/<device>.json`); the result is `nanochat.plan.v1` JSON with one row per operation family
+ * (`kernel` when the device declares the family's capability, else `composition`). A device that lacks a capability
+ * the model requires is an error that names it. `graph`: train | prefill | decode | generate | eval.
+ * `ncb_train_plan_json`: horizon, batch size, learning-rate and weight-decay scaling for a depth (hidden = depth *
+ * aspect_ratio rounded to head_dim); `total_batch_size` -1 asks for the predicted optimum. Both return the text
+ * length (the text is truncated to `capacity - 1`), negative on error. */
+int64_t ncb_plan_json(const char* spec_path, const char* caps_path, const char* precision, const char* graph, char* out,
+                      int64_t capacity);
+nanochat_status ncb_spec_config(const char* spec_path, nanochat_config* out, char* pattern, int pattern_capacity);
+int64_t ncb_train_plan_json(int depth, int aspect_ratio, int head_dim, int seq_len, int vocab_size,
+                            int device_batch_size, const char* window_pattern, int64_t total_batch_size,
+                            int64_t num_iterations, double target_flops, int target_param_data_ratio, char* out,
+                            int64_t capacity);
 double ncb_prefill_flops(const nanochat_config* config, int prompt_tokens);
 double ncb_decode_flops_per_token(const nanochat_config* config, int context_tokens);
 

@@ -8,6 +8,7 @@
 #include "capi_internal.h"
 #include "mesh.h"
 #include "perf.h"
+#include "plan.h"
 
 struct nanochat_mesh {
   ncb::MeshSpec spec;
@@ -277,6 +278,91 @@ int64_t ncb_roofline(const nanochat_config* config, const char* device, const ch
   }
   return static_cast<int64_t>(text.size());
 }
+namespace {
+int64_t CopyOut(const std::string& text, char* out, int64_t capacity) {
+  if (out != nullptr && capacity > 0) {
+    const std::size_t n = std::min<std::size_t>(text.size(), static_cast<std::size_t>(capacity - 1));
+    std::memcpy(out, text.data(), n);
+    out[n] = 0;
+  }
+  return static_cast<int64_t>(text.size());
+}
+bool ReadTextFile(const char* path, std::string* text) {
+  if (path == nullptr) return false;
+  std::FILE* f = std::fopen(path, "rb");
+  if (f == nullptr) return false;
+  char buf[1 << 14];
+  std::size_t n;
+  while ((n = std::fread(buf, 1, sizeof(buf), f)) > 0) text->append(buf, n);
+  std::fclose(f);
+  return true;
+}
+}  // namespace
+
+// The operator plan of a model specification on a device profile as `nanochat.plan.v1` JSON: for every operation
+// family, the fused kernel the device declares or the composition of primitive operators. Both arguments are paths
+// of JSON files. A device that lacks a capability the model requires is an error that names it. Returns the text
+// length, negative on error.
+int64_t ncb_plan_json(const char* spec_path, const char* caps_path, const char* precision, const char* graph, char* out,
+                      int64_t capacity) {
+  std::string spec_text, caps_text, err;
+  if (!ReadTextFile(spec_path, &spec_text) || !ReadTextFile(caps_path, &caps_text)) {
+    ncb_set_error("ncb_plan_json: cannot read the model specification or the device declaration");
+    return -1;
+  }
+  ncb::ModelSpec spec;
+  ncb::DeviceProfile profile;
+  ncb::OperatorPlan plan;
+  if (!ncb::ParseModelSpec(spec_text, &spec, &err) || !ncb::ParseDeviceProfile(caps_text, &profile, &err) ||
+      !ncb::BuildPlan(spec, profile, precision != nullptr ? precision : "bf16", graph != nullptr ? graph : "train", &plan,
+                      &err)) {
+    ncb_set_error("ncb_plan_json: " + err);
+    return -1;
+  }
+  return CopyOut(ncb::PlanJson(plan), out, capacity);
+}
+
+// The model configuration a specification file describes. `out->window_pattern` points into `pattern`, a buffer of
+// the caller (`pattern_capacity` bytes, at least layers + 1).
+nanochat_status ncb_spec_config(const char* spec_path, nanochat_config* out, char* pattern, int pattern_capacity) {
+  std::string text, err;
+  ncb::ModelSpec spec;
+  ncb::EngineConfig c;
+  if (out == nullptr || pattern == nullptr || pattern_capacity <= 0 || !ReadTextFile(spec_path, &text) || !ncb::ParseModelSpec(text, &spec, &err) ||
+      !ncb::SpecToConfig(spec, &c, &err)) {
+    ncb_set_error("ncb_spec_config: " + (err.empty() ? std::string("cannot read the specification") : err));
+    return NANOCHAT_STATUS_ERROR;
+  }
+  out->num_layers = c.num_layers, out->num_heads = c.num_heads, out->num_kv_heads = c.num_kv_heads;
+  out->hidden_dim = c.hidden_dim, out->seq_len = c.seq_len, out->vocab_size = c.vocab_size;
+  out->padded_vocab_size = c.padded_vocab_size, out->rope_base = c.rope_base;
+  std::snprintf(pattern, static_cast<std::size_t>(pattern_capacity), "%s", c.window_pattern.c_str());
+  out->window_pattern = pattern;
+  out->value_embedding = c.value_embedding ? 1 : 0;
+  return NANOCHAT_STATUS_OK;
+}
+
+// The training-run plan (horizon, batch, learning-rate and weight-decay scaling) of a depth as JSON with the keys
+// `counts`, `flops_per_token`, `config`, `inputs`, `plan`. Negative `total_batch_size` asks for the predicted optimum.
+int64_t ncb_train_plan_json(int depth, int aspect_ratio, int head_dim, int seq_len, int vocab_size,
+                            int device_batch_size, const char* window_pattern, int64_t total_batch_size,
+                            int64_t num_iterations, double target_flops, int target_param_data_ratio, char* out,
+                            int64_t capacity) {
+  ncb::TrainPlanInputs in;
+  in.depth = depth, in.aspect_ratio = aspect_ratio, in.head_dim = head_dim, in.seq_len = seq_len;
+  in.vocab_size = vocab_size, in.device_batch_size = device_batch_size;
+  if (window_pattern != nullptr) in.window_pattern = window_pattern;
+  in.total_batch_size = total_batch_size, in.num_iterations = num_iterations, in.target_flops = target_flops;
+  in.target_param_data_ratio = target_param_data_ratio;
+  ncb::TrainPlan plan;
+  std::string err;
+  if (!ncb::ComputeTrainPlan(in, &plan, &err)) {
+    ncb_set_error("ncb_train_plan_json: " + err);
+    return -1;
+  }
+  return CopyOut(ncb::TrainPlanJson(in, plan), out, capacity);
+}
+
 double ncb_muon_flops_per_step(const nanochat_config* config, int ns_steps) {
   ncb::EngineConfig c;
   return ToEngine(config, &c, "ncb_muon_flops_per_step") ? ncb::MuonFlopsPerStep(c, ns_steps) : 0.0;

@@ -666,6 +666,31 @@ int CmdRoofline(const Args& a) {
   return 0;
 }
 
+// `plan --spec <spec.json> --caps <device.json> [--precision bf16] [--graph train]`: the operator plan as JSON.
+int CmdPlan(const Args& a) {
+  std::vector<char> text(1 << 16);
+  const int64_t n = ncb_plan_json(a.Str("spec", "").c_str(), a.Str("caps", "").c_str(), a.Str("precision", "bf16").c_str(),
+                                  a.Str("graph", "train").c_str(), text.data(), static_cast<int64_t>(text.size()));
+  if (n < 0) return Fail("plan");
+  std::printf("%s\n", text.data());
+  return 0;
+}
+
+// `train_plan --depth D --vocab V --device-batch B [--seq T] [--total-batch N] [--num-iterations K] ...`
+int CmdTrainPlan(const Args& a) {
+  std::vector<char> text(1 << 14);
+  const int64_t n = ncb_train_plan_json(
+      static_cast<int>(a.Int("depth", 12)), static_cast<int>(a.Int("aspect-ratio", 64)),
+      static_cast<int>(a.Int("head-dim", 128)), static_cast<int>(a.Int("seq", 2048)),
+      static_cast<int>(a.Int("vocab", 32768)), static_cast<int>(a.Int("device-batch", 32)),
+      a.Str("window-pattern", "SSSL").c_str(), a.Int("total-batch", -1), a.Int("num-iterations", 0),
+      a.Num("target-flops", 0.0), static_cast<int>(a.Int("param-data-ratio", 12)), text.data(),
+      static_cast<int64_t>(text.size()));
+  if (n < 0) return Fail("train_plan");
+  std::printf("%s\n", text.data());
+  return 0;
+}
+
 // `dist --world-size N [--port P] -- <command> [flags]`: one child process per rank with NANOCHAT_RANK,
 // NANOCHAT_WORLD_SIZE, NANOCHAT_MASTER_ADDR and NANOCHAT_MASTER_PORT set (the reference launcher's contract,
 // python/nanochat_cpp/cli.py:827-945), rank 0 first. If a rank fails the others are terminated.
@@ -734,6 +759,8 @@ void Usage() {
       "  tok_train  --text F | --parquet P  --vocab V --out tokenizer.nctoken\n"
       "  dist       --world-size N [--port P] -- train ...      one process per rank over the TCP ring\n"
       "  params     model flags -> parameter counts and FLOPs per token (JSON)\n"
+      "  plan       --spec model.json --caps device.json [--precision bf16] [--graph train|prefill|decode|generate|eval]\n"
+      "  train_plan --depth D --vocab V --device-batch B [--seq T --total-batch N --num-iterations K --target-flops F]\n"
       "  roofline   --device b200|h100|t4|cpu --precision bf16|fp8|fp32 --batch B --grad-accum A --devices N --tokens T\n"
       "             --link-gbps G --latency-us U --overlap F --muon-ns-steps K [--bf16-tflops X --hbm-gbs Y] [--json]\n"
       "model flags: --preset-model tiny|d12|d20|d26 | --depth N | --layers --heads --kv-heads --hidden --seq --vocab\n"
@@ -778,6 +805,8 @@ int main(int argc, char** argv) {
   if (cmd == "tok_train") return CmdTokTrain(a);
   if (cmd == "params") return CmdParams(a);
   if (cmd == "roofline") return CmdRoofline(a);
+  if (cmd == "plan") return CmdPlan(a);
+  if (cmd == "train_plan") return CmdTrainPlan(a);
   std::fprintf(stderr, "nanochat_cli: unknown command '%s'\n", cmd.c_str());
   Usage();
   return 2;

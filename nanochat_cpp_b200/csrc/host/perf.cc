@@ -19,7 +19,12 @@ double ElementBytes(const std::string& p) { return p == "fp32" ? 4.0 : p == "fp8
 std::int64_t NumMatmulParams(const EngineConfig& c) {
   const std::int64_t C = c.hidden_dim;
   const std::int64_t per_layer = c.query_dim() * C + 2 * c.kv_dim() * C + C * C + 2 * C * c.mlp_dim();
-  return c.num_layers * per_layer + static_cast<std::int64_t>(c.padded_vocab_size) * C;
+  std::int64_t value_layers = 0;
+  for (int i = 0; i < c.num_layers; ++i) value_layers += c.has_value_embedding(i) ? 1 : 0;
+  // every linear map of the token stream counts: the block matrices, the LM head, the value gates and the smear
+  // gate (reference src/performance_model.cc:233-249); the embeddings are gathers and do not
+  return c.num_layers * per_layer + static_cast<std::int64_t>(c.padded_vocab_size) * C +
+         value_layers * c.num_kv_heads * kGateChannels + kSmearChannels;
 }
 
 ParamCounts CountParams(const EngineConfig& c) {

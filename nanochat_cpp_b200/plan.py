@@ -176,3 +176,57 @@ def build_plan(spec: ModelSpec, profile: DeviceProfile, precision: str = "bf16",
         rows.append(PlanRow(family, "kernel", kernel) if profile.has(feature)
                     else PlanRow(family, "composition", "PyTorch operators of ops.ref"))
     return Plan(spec.name, profile.device, precision, rows)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Native planning layer (csrc/host/plan.cc, behind the C ABI): the same operator plan computed in C++, and the
+# training-run plan (horizon, batch size, learning-rate and weight-decay scaling for a depth).
+# ---------------------------------------------------------------------------------------------------------
+def _native_text(call) -> str:
+    import ctypes
+    from .data import native
+    lib = native.lib()
+    buf = ctypes.create_string_buffer(1 << 16)
+    n = call(lib, buf, len(buf))
+    if n < 0:
+        lib.nanochat_last_error.restype = ctypes.c_char_p
+        raise SpecError(lib.nanochat_last_error().decode())
+    return buf.value.decode()
+
+
+def build_plan_native(spec_path: Optional[str] = None, caps_path: Optional[str] = None, precision: str = "bf16",
+                      graph: str = "train") -> Plan:
+    """`build_plan` through `ncb_plan_json`: the C++ reader and planner on the same two JSON files."""
+    import ctypes
+    spec_path = spec_path or os.path.join(_HERE, "model_specs", "nanochat-default.json")
+    caps_path = caps_path or os.path.join(_HERE, "caps", "b200.json")
+
+    def call(lib, buf, cap):
+        lib.ncb_plan_json.restype = ctypes.c_int64
+        lib.ncb_plan_json.argtypes = [ctypes.c_char_p] * 4 + [ctypes.c_char_p, ctypes.c_int64]
+        return lib.ncb_plan_json(spec_path.encode(), caps_path.encode(), precision.encode(), graph.encode(), buf, cap)
+    d = json.loads(_native_text(call))
+    return Plan(d["model"], d["device"], d["precision"], [PlanRow(r["family"], r["choice"], r["detail"]) for r in d["rows"]])
+
+
+def compute_plan(depth: int, *, vocab_size: int, device_batch_size: int, aspect_ratio: int = 64, head_dim: int = 128,
+                 seq_len: int = 2048, window_pattern: str = "SSSL", total_batch_size: int = -1, num_iterations: int = 0,
+                 target_flops: float = 0.0, target_param_data_ratio: int = 12) -> dict:
+    """Training-run plan of a depth (reference python/nanochat_cpp/plan.py `compute_plan`, which mirrors upstream
+    `scripts/base_train.py`): the model shape, the parameter counts, and from them the token horizon
+    (`target_param_data_ratio` x scaling parameters), the batch size (power of two nearest to 2^19 x (tokens /
+    tokens at depth 12)^0.383 unless given), the sqrt batch scaling of the learning rates, the weight decay
+    scaled by sqrt(batch ratio) x (depth-12 tokens / tokens), the iteration count and the gradient accumulation.
+    Computed natively (`ncb_train_plan_json`); returns the decoded document (`counts`, `flops_per_token`, `config`,
+    `inputs`, `plan`)."""
+    import ctypes
+
+    def call(lib, buf, cap):
+        lib.ncb_train_plan_json.restype = ctypes.c_int64
+        lib.ncb_train_plan_json.argtypes = [ctypes.c_int] * 6 + [ctypes.c_char_p, ctypes.c_int64, ctypes.c_int64,
+                                                                 ctypes.c_double, ctypes.c_int, ctypes.c_char_p,
+                                                                 ctypes.c_int64]
+        return lib.ncb_train_plan_json(depth, aspect_ratio, head_dim, seq_len, vocab_size, device_batch_size,
+                                       window_pattern.encode(), int(total_batch_size), int(num_iterations),
+                                       float(target_flops), target_param_data_ratio, buf, cap)
+    return json.loads(_native_text(call))

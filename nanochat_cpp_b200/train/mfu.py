@@ -2,7 +2,7 @@
 
 Same counting rules as the reference performance model (`src/performance_model.cc:233-350`):
 flops per token = 6 * matmul parameters + 12 * heads * head_dim * window per layer, where the matmul
-parameters are the block matrices plus the LM head (embeddings are gathers, not matmuls) and the window
+parameters are the block matrices, the LM head and the two kinds of gate (embeddings are gathers, not matmuls) and the window
 of a sliding layer is min(short_window, seq). Muon's Newton-Schulz FLOPs are reported separately and
 never added to the model FLOPs (reference `src/train.cc:917-925`).
 """
@@ -11,13 +11,16 @@ from __future__ import annotations
 import json
 import os
 
-from ..config import Config
+from ..config import SMEAR_CHANNELS, VE_GATE_CHANNELS, Config
 
 
 def num_matmul_params(cfg: Config) -> int:
     C = cfg.hidden_dim
     per_layer = cfg.query_dim * C + 2 * cfg.kv_dim * C + C * C + 2 * C * cfg.mlp_dim
-    return cfg.num_layers * per_layer + cfg.padded_vocab_size * C
+    value_layers = sum(1 for i in range(cfg.num_layers) if cfg.has_value_embedding(i))
+    # the value gates ([kv_heads, 12] each) and the smear gate ([1, 24]) are linear maps of the token stream too
+    return (cfg.num_layers * per_layer + cfg.padded_vocab_size * C + value_layers * cfg.num_kv_heads * VE_GATE_CHANNELS
+            + SMEAR_CHANNELS)
 
 
 def count_params(cfg: Config) -> int:
