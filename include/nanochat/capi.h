@@ -97,6 +97,17 @@ const char* nanochat_backend(void);
 int nanochat_compute_type_size(void);
 void nanochat_device_info(nanochat_device* out);
 int nanochat_device_count(void);
+/* Backend selection at run time (the reference fixes it at link time): "cpu" (default), "cuda" or "cuda:N". The
+ * environment variable NANOCHAT_DEVICE gives the initial choice. After a CUDA device is selected, `nanochat_backend`
+ * answers "cuda", `nanochat_device_count/_at` enumerate the CUDA devices, and every model created afterwards (and
+ * its optimizer, scoring, generation and evaluation calls) runs on that device through the sm_100a kernels of
+ * libnanochat_gpu.so, which must sit beside this library. `nanochat_param_info` then returns null data pointers:
+ * use nanochat_param_read / nanochat_param_write. The in-process mesh runtime stays on the CPU engine. */
+nanochat_status nanochat_select_device(const char* name);
+/* First bounded-wait failure a kernel recorded on the model's device (0 = none; always 0 on the CPU), and the number
+ * of kernel launches the model's engine has issued. */
+int ncb_model_device_status(nanochat_model* model);
+int64_t ncb_model_launch_count(nanochat_model* model);
 int nanochat_device_at(int ordinal, nanochat_device* out);
 
 nanochat_status nanochat_params_get(const nanochat_config* config, nanochat_params* out);

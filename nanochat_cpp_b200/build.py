@@ -6,6 +6,8 @@ Two artefacts, both placed next to this file so that they travel with the source
                    for sm_100a only) plus `csrc/cuda/bindings.cpp`.
 * `libnanochat_core.so` - the host runtime of `csrc/host` (formats, tokenizer, BPE trainer, data
                    loader, parquet reader, C ABI); plain C++20, no CUDA, no torch.
+* `libnanochat_gpu.so` - the same kernels plus the C++ GPU engine of `csrc/gpu` (no torch): what the C ABI and
+                   the native CLI run on when a CUDA device is selected.
 
 `python -m nanochat_cpp_b200.build` builds what is stale. Objects are cached under `_build/`
 keyed by a hash of the source, the headers beside it and the flags.
@@ -80,7 +82,7 @@ def _prune(keep: List[str], prefix: str) -> None:
     for path in glob.glob(os.path.join(BUILD_DIR, "*.o")):
         base = os.path.basename(path)
         is_host = base.startswith("host_")
-        if (prefix == "host_") != is_host:
+        if base.startswith("gpu_") or (prefix == "host_") != is_host:
             continue
         if path not in keep_set:
             for victim in (path, path + ".log"):
@@ -139,6 +141,49 @@ def build_extension(verbose: bool = False) -> str:
 
 
 CLI_PATH = os.path.join(HERE, "nanochat_cli")
+GPU_PATH = os.path.join(HERE, "libnanochat_gpu.so")
+CSRC_GPU = os.path.join(HERE, "csrc", "gpu")
+
+
+def build_gpu_engine(verbose: bool = False) -> str:
+    """`libnanochat_gpu.so`: the sm_100a kernels of csrc/cuda (the same objects the extension links, without any of
+    its PyTorch bindings) and the C++ engine of csrc/gpu that drives them; no torch, no Python. The core library
+    opens it when a CUDA device is selected through the C ABI."""
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    if not os.path.isdir(CSRC_GPU) or not os.path.exists(CORE_PATH):
+        return ""
+    nvcc = _nvcc()
+    cuda_home = os.path.dirname(os.path.dirname(nvcc))
+    headers = (glob.glob(os.path.join(CSRC_CUDA, "*.h")) + glob.glob(os.path.join(CSRC_CUDA, "*.cuh")) +
+               glob.glob(os.path.join(CSRC_HOST, "*.h")) + glob.glob(os.path.join(CSRC_GPU, "*.h")))
+    jobs = []
+    for src in sorted(glob.glob(os.path.join(CSRC_CUDA, "*.cu"))):      # cache shared with the extension
+        tag = _hash([src] + glob.glob(os.path.join(CSRC_CUDA, "*.h")) + glob.glob(os.path.join(CSRC_CUDA, "*.cuh")),
+                    " ".join(NVCC_FLAGS))
+        obj = os.path.join(BUILD_DIR, os.path.basename(src) + "." + tag + ".o")
+        jobs.append((src, obj, [nvcc] + NVCC_FLAGS + ["-I", CSRC_CUDA, "-c", src, "-o", obj]))
+    for src in sorted(glob.glob(os.path.join(CSRC_GPU, "*.cu"))):
+        tag = _hash([src] + headers, " ".join(NVCC_FLAGS))
+        obj = os.path.join(BUILD_DIR, "gpu_" + os.path.basename(src) + "." + tag + ".o")
+        jobs.append((src, obj, [nvcc] + NVCC_FLAGS + ["-I", CSRC_GPU, "-c", src, "-o", obj]))
+    for src in sorted(glob.glob(os.path.join(CSRC_GPU, "*.cc"))):
+        tag = _hash([src] + headers, " ".join(HOST_FLAGS))
+        obj = os.path.join(BUILD_DIR, "gpu_" + os.path.basename(src) + "." + tag + ".o")
+        jobs.append((src, obj, ["g++"] + HOST_FLAGS + ["-I", os.path.join(cuda_home, "include"), "-I", CSRC_GPU, "-I",
+                                                       CSRC_HOST, "-c", src, "-o", obj]))
+    objs = _compile_many(jobs)
+    stamp = os.path.join(BUILD_DIR, "gpu.stamp")
+    key = _hash(objs + [CORE_PATH], "link-gpu")
+    if os.path.exists(GPU_PATH) and os.path.exists(stamp) and open(stamp).read() == key:
+        return GPU_PATH
+    _run(["g++", "-shared", "-pthread", "-fopenmp", "-o", GPU_PATH] + objs +
+         ["-L", HERE, "-lnanochat_core", "-L", os.path.join(cuda_home, "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN",
+          f"-Wl,-rpath,{os.path.join(cuda_home, 'lib64')}"], os.path.join(BUILD_DIR, "link_gpu.log"))
+    with open(stamp, "w") as f:
+        f.write(key)
+    if verbose:
+        print("built", GPU_PATH)
+    return GPU_PATH
 
 
 def build_core(verbose: bool = False) -> str:
@@ -193,6 +238,7 @@ def build_all(verbose: bool = False) -> None:
     build_core(verbose)
     build_cli(verbose)
     build_extension(verbose)
+    build_gpu_engine(verbose)
 
 
 if __name__ == "__main__":

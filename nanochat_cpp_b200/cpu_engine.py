@@ -1,6 +1,8 @@
-"""ctypes binding of the native CPU engine (the model / optimizer / generate / score part of the C ABI in
-`include/nanochat/capi.h`, implemented in `csrc/host/engine.cc`). Useful on machines without a GPU and as an
-oracle that shares no code with the PyTorch path."""
+"""ctypes binding of the native engines behind the C ABI (the model / optimizer / generate / score part of
+`include/nanochat/capi.h`). By default a model lives in the C++ CPU engine (`csrc/host/engine.cc`): useful on
+machines without a GPU and as an oracle that shares no code with the PyTorch path. After `select_device("cuda:0")`
+the same calls create and drive a model in the C++ GPU engine (`csrc/gpu/gpu_engine.cc`, the sm_100a kernels without
+Python or PyTorch in the loop), which is what the native command line and hosts in other languages use."""
 from __future__ import annotations
 
 import ctypes as C
@@ -90,6 +92,24 @@ def _l():
     return L
 
 
+def select_device(name: str = "cpu") -> None:
+    """"cpu", "cuda" or "cuda:N": the engine that models created afterwards live in (process-wide)."""
+    L = _l()
+    L.nanochat_select_device.argtypes = [C.c_char_p]
+    if L.nanochat_select_device(name.encode()) != 0:
+        raise RuntimeError(last_error() or f"cannot select device {name!r}")
+
+
+def backend() -> str:
+    L = _l()
+    L.nanochat_backend.restype = C.c_char_p
+    return L.nanochat_backend().decode()
+
+
+def device_count() -> int:
+    return int(_l().nanochat_device_count())
+
+
 def _i32(a) -> np.ndarray:
     return np.ascontiguousarray(np.asarray(a), dtype=np.int32)
 
@@ -139,6 +159,26 @@ class CpuModel:
     def zero_grad(self) -> None:
         _l().nanochat_zero_grad(self._h)
 
+    def train_step(self, tokens, targets, optimizer: "CpuOptimizer" = None) -> float:
+        """zero_grad + forward + backward (+ one optimizer step): `nanochat_train_step`."""
+        t, g = _i32(tokens), _i32(targets)
+        L = _l()
+        L.nanochat_train_step.restype = C.c_float
+        L.nanochat_train_step.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        return float(L.nanochat_train_step(self._h, optimizer._h if optimizer is not None else None, t.ctypes.data,
+                                           g.ctypes.data, t.shape[0], t.shape[1]))
+
+    def device_status(self) -> int:
+        L = _l()
+        L.ncb_model_device_status.argtypes = [C.c_void_p]
+        return int(L.ncb_model_device_status(self._h))
+
+    def launch_count(self) -> int:
+        L = _l()
+        L.ncb_model_launch_count.restype = C.c_int64
+        L.ncb_model_launch_count.argtypes = [C.c_void_p]
+        return int(L.ncb_model_launch_count(self._h))
+
     def save(self, path: str) -> None:
         _l().nanochat_save(self._h, path.encode())
 
@@ -187,6 +227,9 @@ class CpuModel:
             self._h = None
 
 
+NativeModel = CpuModel      # the same handle drives the GPU engine once a CUDA device is selected
+
+
 class CpuOptimizer:
     def __init__(self, model: CpuModel, **fields):
         c = _OptimC()
@@ -212,3 +255,6 @@ class CpuOptimizer:
         if getattr(self, "_h", None):
             _l().nanochat_optim_free(self._h)
             self._h = None
+
+
+NativeOptimizer = CpuOptimizer

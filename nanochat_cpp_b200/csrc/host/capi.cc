@@ -4,6 +4,10 @@
 #include <cstring>
 #include <sstream>
 
+#include <dlfcn.h>
+
+#include <cstdlib>
+
 #include "capi_internal.h"
 
 namespace {
@@ -12,23 +16,131 @@ thread_local std::string g_last_error;
 
 void ncb_set_error(const std::string& msg) { g_last_error = msg; }
 
+// ---- the GPU engine library, opened on demand ---------------------------------------------------------------------
+namespace {
+ncb_gpu_library g_gpu;
+bool g_gpu_tried = false;
+int g_cuda_device = -2;   // -2: not decided yet (NANOCHAT_DEVICE is read on first use), -1: cpu, >= 0: CUDA ordinal
+std::string g_gpu_error;
+
+std::string OwnDirectory() {
+  Dl_info info;
+  if (dladdr(reinterpret_cast<void*>(&ncb_set_error), &info) == 0 || info.dli_fname == nullptr) return ".";
+  std::string path = info.dli_fname;
+  const std::size_t slash = path.rfind('/');
+  return slash == std::string::npos ? "." : path.substr(0, slash);
+}
+}  // namespace
+
+const ncb_gpu_library* ncb_gpu() {
+  if (!g_gpu_tried) {
+    g_gpu_tried = true;
+    const std::string path = OwnDirectory() + "/libnanochat_gpu.so";
+    void* h = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (h == nullptr) {
+      g_gpu_error = std::string("cannot open ") + path + ": " + dlerror();
+    } else {
+      g_gpu.device_count = reinterpret_cast<ncb::ncb_gpu_device_count_fn>(dlsym(h, "ncb_gpu_device_count"));
+      g_gpu.device_at = reinterpret_cast<ncb::ncb_gpu_device_at_fn>(dlsym(h, "ncb_gpu_device_at"));
+      g_gpu.create = reinterpret_cast<ncb::ncb_gpu_engine_create_fn>(dlsym(h, "ncb_gpu_engine_create"));
+      if (g_gpu.device_count == nullptr || g_gpu.device_at == nullptr || g_gpu.create == nullptr) {
+        g_gpu_error = path + " lacks the engine entry points";
+        g_gpu = ncb_gpu_library();
+      }
+    }
+  }
+  return g_gpu.create != nullptr ? &g_gpu : nullptr;
+}
+
+bool ncb_select_device(const std::string& name, std::string* error) {
+  if (name.empty() || name == "cpu") {
+    g_cuda_device = -1;
+    return true;
+  }
+  if (name.rfind("cuda", 0) != 0) {
+    *error = "unknown device '" + name + "' (cpu, cuda, cuda:N)";
+    return false;
+  }
+  int index = 0;
+  if (name.size() > 4) {
+    if (name[4] != ':' || name.size() == 5) {
+      *error = "unknown device '" + name + "' (cpu, cuda, cuda:N)";
+      return false;
+    }
+    index = std::atoi(name.c_str() + 5);
+  }
+  const ncb_gpu_library* lib = ncb_gpu();
+  if (lib == nullptr) {
+    *error = g_gpu_error.empty() ? "the GPU engine library is not available" : g_gpu_error;
+    return false;
+  }
+  const int n = lib->device_count();
+  if (index < 0 || index >= n) {
+    *error = "CUDA device " + std::to_string(index) + " does not exist (" + std::to_string(n) + " visible)";
+    return false;
+  }
+  g_cuda_device = index;
+  return true;
+}
+
+int ncb_selected_cuda_device() {
+  if (g_cuda_device == -2) {
+    g_cuda_device = -1;
+    const char* env = std::getenv("NANOCHAT_DEVICE");
+    if (env != nullptr && *env) {
+      std::string err;
+      if (!ncb_select_device(env, &err)) ncb_set_error("NANOCHAT_DEVICE: " + err);
+    }
+  }
+  return g_cuda_device;
+}
+
 extern "C" {
 
 size_t nanochat_optim_config_size(void) { return sizeof(nanochat_optim_config); }
 nanochat_status nanochat_init(void) { return NANOCHAT_STATUS_OK; }
 const char* nanochat_last_error(void) { return g_last_error.c_str(); }
 const char* nanochat_version(void) { return "nanochat-b200 0.1.0"; }
-const char* nanochat_backend(void) { return "cpu"; }
-int nanochat_compute_type_size(void) { return 4; }
+const char* nanochat_backend(void) { return ncb_selected_cuda_device() >= 0 ? "cuda" : "cpu"; }
+int nanochat_compute_type_size(void) { return ncb_selected_cuda_device() >= 0 ? 2 : 4; }
 void nanochat_device_info(nanochat_device* out) { nanochat_device_at(0, out); }
-int nanochat_device_count(void) { return 1; }
+
+// Device selection. The reference fixes its backend at link time; here one library serves both, so the backend is
+// a run-time choice: "cpu" (the default), "cuda" or "cuda:N". The environment variable NANOCHAT_DEVICE gives the
+// initial choice. Selecting a CUDA device opens libnanochat_gpu.so (beside this library); models created afterwards
+// live on that device.
+nanochat_status nanochat_select_device(const char* name) {
+  std::string err;
+  if (!ncb_select_device(name != nullptr ? name : "cpu", &err)) {
+    ncb_set_error("nanochat_select_device: " + err);
+    return NANOCHAT_STATUS_ERROR;
+  }
+  return NANOCHAT_STATUS_OK;
+}
+int nanochat_device_count(void) {
+  if (ncb_selected_cuda_device() < 0) return 1;
+  const ncb_gpu_library* lib = ncb_gpu();
+  return lib != nullptr ? lib->device_count() : 0;
+}
 int nanochat_device_at(int ordinal, nanochat_device* out) {
-  if (ordinal != 0 || out == nullptr) return 0;
-  out->device_index = 0;
-  out->compute_major = 0;
-  out->compute_minor = 0;
-  out->total_memory_bytes = 0;
-  out->device_name = "cpu";
+  if (out == nullptr) return 0;
+  if (ncb_selected_cuda_device() < 0) {
+    if (ordinal != 0) return 0;
+    out->device_index = 0;
+    out->compute_major = 0;
+    out->compute_minor = 0;
+    out->total_memory_bytes = 0;
+    out->device_name = "cpu";
+    return 1;
+  }
+  const ncb_gpu_library* lib = ncb_gpu();
+  static thread_local ncb::DeviceDescription d;
+  if (lib == nullptr || !lib->device_at(ordinal, &d)) return 0;
+  out->device_index = d.index;
+  out->compute_major = d.compute_major;
+  out->compute_minor = d.compute_minor;
+  out->total_memory_bytes = static_cast<uint64_t>(d.total_memory_bytes);
+  out->device_name = d.name;
   return 1;
 }
 

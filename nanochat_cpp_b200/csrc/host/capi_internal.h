@@ -6,6 +6,7 @@
 #include <vector>
 
 #include "core.h"
+#include "device_engine.h"
 #include "nanochat/capi.h"
 
 struct nanochat_tokenizer {
@@ -25,6 +26,17 @@ struct nanochat_checkpoint {
 };
 
 void ncb_set_error(const std::string& msg);
+
+// The GPU engine library (libnanochat_gpu.so beside this library), opened on first use; null when it is not there
+// or cannot be loaded. `ncb_selected_cuda_device` is the CUDA ordinal models are created on, or -1 for the CPU.
+struct ncb_gpu_library {
+  ncb::ncb_gpu_device_count_fn device_count = nullptr;
+  ncb::ncb_gpu_device_at_fn device_at = nullptr;
+  ncb::ncb_gpu_engine_create_fn create = nullptr;
+};
+const ncb_gpu_library* ncb_gpu();
+bool ncb_select_device(const std::string& name, std::string* error);
+int ncb_selected_cuda_device();
 // Process-wide override of the sliding window of `S` layers (0: ceil(seq/4/128)*128), applied to every model the
 // C ABI creates afterwards; `nanochat_config` keeps the reference's layout and has no field for it.
 int& ncb_short_window_override();

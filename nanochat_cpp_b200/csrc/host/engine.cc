@@ -963,73 +963,17 @@ void CpuModel::Decode(KvCache* cache, int token, std::vector<float>* logits) { S
 
 std::vector<GeneratedRow> GenerateBatch(CpuModel* model, const int* prompt, int length, const GenerateOptions& opt,
                                         int first_row) {
-  const int rows = std::max(1, opt.num_samples);
-  std::vector<GeneratedRow> out(static_cast<std::size_t>(rows));
-  for (int r = 0; r < rows; ++r) {
-    GeneratedRow& row = out[r];
-    row.tokens.assign(prompt, prompt + length);
-    row.mask.assign(static_cast<std::size_t>(length), 0);
-    auto cache = model->NewCache(length + opt.max_tokens + 1);
-    std::vector<float> logits;
-    model->Prefill(cache.get(), prompt, length, &logits);
-    Rng rng(MixSeed(opt.seed, static_cast<std::uint64_t>(first_row + r)));
-    const int row_stop = r < static_cast<int>(opt.stop_ids.size()) ? opt.stop_ids[r] : -1;
-    for (int step = 0; step < opt.max_tokens; ++step) {
-      const int tok = SampleToken(logits.data(), static_cast<int>(logits.size()), opt.temperature, opt.top_k, &rng);
-      if ((opt.stop_id >= 0 && tok == opt.stop_id) || (opt.bos_id >= 0 && tok == opt.bos_id) ||
-          (row_stop >= 0 && tok == row_stop))
-        break;
-      row.tokens.push_back(tok);
-      row.mask.push_back(1);
-      if (step + 1 == opt.max_tokens) break;
-      model->Decode(cache.get(), tok, &logits);
-    }
-  }
-  return out;
+  return GenerateBatchOn(model, prompt, length, opt, first_row);
 }
 
 std::vector<ScoreRow> ScoreBatch(CpuModel* model, const int* tokens, int batch, int seq, const int* lengths,
                                  const FocusRequest* focus) {
-  const int V = model->config().vocab_size, PV = model->config().padded_vocab_size;
-  std::vector<int> targets(static_cast<std::size_t>(batch) * seq, -1);
-  auto len_of = [&](int b) { return std::min(std::max(lengths ? lengths[b] : seq, 0), seq); };
-  for (int b = 0; b < batch; ++b)
-    for (int p = 0; p + 1 < len_of(b); ++p) targets[static_cast<std::size_t>(b) * seq + p] = tokens[static_cast<std::size_t>(b) * seq + p + 1];
-  model->ForwardLoss(tokens, targets.data(), batch, seq, true);
-  const std::vector<float>& losses = model->losses();
-  const std::vector<float>& logits = model->logits();
-  std::vector<ScoreRow> out(static_cast<std::size_t>(batch));
-  for (int b = 0; b < batch; ++b) {
-    ScoreRow& r = out[b];
-    r.nll.assign(static_cast<std::size_t>(seq), 0.0f);
-    r.argmax.assign(static_cast<std::size_t>(seq), -1);
-    for (int p = 0; p + 1 < len_of(b); ++p) {
-      const std::size_t row = static_cast<std::size_t>(b) * seq + p;
-      r.nll[p] = losses[row];
-      const float* lr = &logits[row * PV];
-      int best = 0;
-      for (int j = 1; j < V; ++j)
-        if (lr[j] > lr[best]) best = j;
-      r.argmax[p] = best;
-    }
-    if (focus != nullptr && focus[b].position >= 0 && focus[b].position < seq) {
-      const float* lr = &logits[(static_cast<std::size_t>(b) * seq + focus[b].position) * PV];
-      for (int id : focus[b].ids) r.focus_logits.push_back(id >= 0 && id < V ? kSoftcap * std::tanh(lr[id] / kSoftcap) : 0.0f);
-    }
-  }
-  return out;
+  return ScoreBatchOn(model, tokens, batch, seq, lengths, focus);
 }
 
 float RlStep(CpuModel* model, CpuOptimizer* opt, const int* tokens, const int* targets, const float* advantages,
              int batch, int seq, int num_passes, int examples_per_rank, int step) {
-  model->ZeroGrad();
-  const float loss = model->ForwardLoss(tokens, targets, batch, seq);
-  const std::int64_t valid = model->valid_targets();
-  if (valid == 0) return loss;
-  const double divisor = static_cast<double>(valid) * num_passes * examples_per_rank;
-  model->Backward(1.0f, advantages, divisor);
-  if (opt != nullptr) opt->Step(step);
-  return loss;
+  return RlStepOn(model, opt, tokens, targets, advantages, batch, seq, num_passes, examples_per_rank, step);
 }
 
 // ---------------------------------------------------------------------------------------------- optimizer
@@ -1174,13 +1118,15 @@ double Frob(const std::vector<float>& x) {
 // decay (reference backends/cpu/kernels.cc:1614-1810).
 void CpuOptimizer::MuonUpdate(MuonGroup* g, std::size_t index, float lr, float momentum, float wd, float grad_scale) {
   const CpuParam& p = *g->params[index];
-  const int rows = g->rows, cols = g->cols;
-  float* w = model_->value(p);
-  const float* gr = model_->grad(p);
-  std::vector<float>& b1 = g->buf1[index];
-  std::vector<float>& b2 = g->buf2[index];
-  std::vector<float> x(p.count);
-  for (std::size_t i = 0; i < p.count; ++i) {
+  MuonUpdateHost(model_->value(p), model_->grad(p), g->buf1[index].data(), g->buf2[index].data(), g->rows, g->cols, lr,
+                 momentum, wd, cfg_.muon_beta2, cfg_.muon_ns_steps, grad_scale);
+}
+
+void MuonUpdateHost(float* w, const float* gr, float* b1, float* b2, int rows, int cols, float lr, float momentum,
+                    float wd, float beta2, int ns_steps, float grad_scale) {
+  const std::size_t count = static_cast<std::size_t>(rows) * cols;
+  std::vector<float> x(count);
+  for (std::size_t i = 0; i < count; ++i) {
     const float gi = gr[i] * grad_scale;
     b1[i] += (1.0f - momentum) * (gi - b1[i]);
     x[i] = (1.0f - momentum) * gi + momentum * b1[i];
@@ -1197,7 +1143,7 @@ void CpuOptimizer::MuonUpdate(MuonGroup* g, std::size_t index, float lr, float m
   for (auto& v : x) v /= (frob * 1.01f + 1e-6f);
   const bool tall = rows > cols;
   std::vector<float> A, A2, B, Y;
-  for (int it = 0; it < std::min(std::max(cfg_.muon_ns_steps, 0), 5); ++it) {
+  for (int it = 0; it < std::min(std::max(ns_steps, 0), 5); ++it) {
     const float ca = static_cast<float>(kPolar[it][0]), cb = static_cast<float>(kPolar[it][1]),
                 cc = static_cast<float>(kPolar[it][2]);
     const std::vector<float> xt = Transpose(x, rows, cols);
@@ -1229,7 +1175,7 @@ void CpuOptimizer::MuonUpdate(MuonGroup* g, std::size_t index, float lr, float m
   std::vector<float> step_size(static_cast<std::size_t>(lines));
   double sum_scaled = 0.0;
   for (int l = 0; l < lines; ++l) {
-    b2[l] += (1.0f - cfg_.muon_beta2) * (v_mean[l] - b2[l]);
+    b2[l] += (1.0f - beta2) * (v_mean[l] - b2[l]);
     step_size[l] = 1.0f / std::sqrt(std::max(b2[l], 1e-10f));
     sum_scaled += static_cast<double>(v_mean[l] * line_len) * step_size[l] * step_size[l];
   }

@@ -160,8 +160,17 @@ struct FocusRequest {
 std::vector<ScoreRow> ScoreBatch(CpuModel* model, const int* tokens, int batch, int seq, const int* lengths,
                                  const FocusRequest* focus);
 
+// Muon for one matrix on the host (momentum + Nesterov, row equilibration, Polar Express, Muon+, NorMuon,
+// cautious decay; reference backends/cpu/kernels.cc:1614-1810). `w` fp32 [rows, cols] is updated in place, `b1`
+// [rows, cols] and `b2` [max(rows, cols) lines] are the two state buffers. Also used by the GPU engine for the few
+// matrices that are too small for its batched kernels (the 12-channel value gates).
+void MuonUpdateHost(float* w, const float* grad, float* b1, float* b2, int rows, int cols, float lr, float momentum,
+                    float wd, float beta2, int ns_steps, float grad_scale);
+
 // One policy-gradient step (reference src/rl.cc): returns the loss; `valid * num_passes * examples_per_rank` divides.
 float RlStep(CpuModel* model, CpuOptimizer* opt, const int* tokens, const int* targets, const float* advantages,
              int batch, int seq, int num_passes, int examples_per_rank, int step);
 
 }  // namespace ncb
+
+#include "engine_drivers.h"
