@@ -108,6 +108,10 @@ nanochat_status nanochat_select_device(const char* name);
  * of kernel launches the model's engine has issued. */
 int ncb_model_device_status(nanochat_model* model);
 int64_t ncb_model_launch_count(nanochat_model* model);
+/* An activation kept by the model's last forward on a CUDA device ("emb", "x0", "xn"; per layer "xr", "h", "qkv", "qk",
+ * "attn", "x_mid", "h2", "act", "x_out"), widened to fp32: for comparing engines stage by stage. Returns the element
+ * count (the copy is truncated to `capacity`), -1 for an unknown name or a model on the CPU. */
+int64_t ncb_model_read_activation(nanochat_model* model, const char* name, int layer, float* dst, int64_t capacity);
 int nanochat_device_at(int ordinal, nanochat_device* out);
 
 nanochat_status nanochat_params_get(const nanochat_config* config, nanochat_params* out);

@@ -173,6 +173,18 @@ class CpuModel:
         L.ncb_model_device_status.argtypes = [C.c_void_p]
         return int(L.ncb_model_device_status(self._h))
 
+    def activation(self, name: str, layer: int = -1) -> np.ndarray:
+        """fp32 copy of an activation the last forward kept on a CUDA device (`ncb_model_read_activation`)."""
+        L = _l()
+        L.ncb_model_read_activation.restype = C.c_int64
+        L.ncb_model_read_activation.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_void_p, C.c_int64]
+        n = L.ncb_model_read_activation(self._h, name.encode(), layer, None, 0)
+        if n < 0:
+            raise KeyError(name)
+        out = np.empty(n, dtype=np.float32)
+        L.ncb_model_read_activation(self._h, name.encode(), layer, out.ctypes.data, n)
+        return out
+
     def launch_count(self) -> int:
         L = _l()
         L.ncb_model_launch_count.restype = C.c_int64
@@ -222,7 +234,7 @@ class CpuModel:
         return out
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and _l is not None:      # module globals may be gone at interpreter exit
             _l().nanochat_model_free(self._h)
             self._h = None
 
@@ -252,7 +264,7 @@ class CpuOptimizer:
                                            t.shape[0], t.shape[1], num_passes, examples_per_rank, step))
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and _l is not None:
             _l().nanochat_optim_free(self._h)
             self._h = None
 

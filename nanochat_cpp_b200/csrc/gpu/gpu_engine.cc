@@ -142,12 +142,55 @@ class GpuEngine final : public DeviceEngine {
   float grad_norm() const override { return grad_norm_; }
   std::int64_t LaunchCount() const override { return launches_; }
 
+  bool ReadActivation(const std::string& name, int layer, std::vector<float>* out) override {
+    Use();
+    const EngineConfig& c = cfg_;
+    const std::size_t m = static_cast<std::size_t>(M_), C = static_cast<std::size_t>(c.hidden_dim);
+    const std::size_t wide = static_cast<std::size_t>(c.query_dim() + 2 * c.kv_dim());
+    const std::size_t hk = static_cast<std::size_t>(c.num_heads + c.num_kv_heads) * c.head_dim();
+    if (name.rfind("value:", 0) == 0) {     // the bf16 compute copy of a parameter
+      const auto it = index_.find(name.substr(6));
+      if (it == index_.end()) return false;
+      const CpuParam& p = params_[it->second];
+      Check(cudaStreamSynchronize(stream_), "sync");
+      std::vector<bf16> raw(p.count);
+      ToHost(raw.data(), value_ + p.offset, p.count * sizeof(bf16), "value read");
+      out->resize(p.count);
+      for (std::size_t i = 0; i < p.count; ++i) (*out)[i] = __bfloat162float(raw[i]);
+      return true;
+    }
+    Buf* b = nullptr;
+    std::size_t n = m * C;
+    if (name == "emb") b = &emb_;
+    else if (name == "x0") b = &x0_;
+    else if (name == "xn") b = &xn_;
+    else if (layer >= 0 && layer < c.num_layers) {
+      LayerBufs& lb = layers_[static_cast<std::size_t>(layer)];
+      if (name == "xr") b = &lb.xr;
+      else if (name == "h") b = &lb.h;
+      else if (name == "qkv") b = &lb.qkv, n = m * wide;
+      else if (name == "qk") b = &lb.qk, n = m * hk;
+      else if (name == "attn") b = &lb.attn, n = m * static_cast<std::size_t>(c.query_dim());
+      else if (name == "x_mid") b = &lb.x_mid;
+      else if (name == "h2") b = &lb.h2;
+      else if (name == "act") b = &lb.act, n = m * static_cast<std::size_t>(c.mlp_dim());
+      else if (name == "x_out") b = &lb.x_out;
+    }
+    if (b == nullptr || b->p == nullptr || b->bytes < n * sizeof(bf16)) return false;
+    Check(cudaStreamSynchronize(stream_), "sync");
+    std::vector<bf16> raw(n);
+    ToHost(raw.data(), b->p, n * sizeof(bf16), "activation read");
+    out->resize(n);
+    for (std::size_t i = 0; i < n; ++i) (*out)[i] = __bfloat162float(raw[i]);
+    return true;
+  }
+
   int Status() override {
     Use();
     Check(cudaStreamSynchronize(stream_), "sync");
     Check(cudaStreamSynchronize(side_), "sync");
     int code = 0;
-    Check(cudaMemcpy(&code, status_, sizeof(int), cudaMemcpyDeviceToHost), "status read");
+    ToHost(&code, status_, sizeof(int), "status read");
     return code;
   }
 
@@ -157,15 +200,14 @@ class GpuEngine final : public DeviceEngine {
     const CpuParam& p = params_.at(index);
     Check(cudaStreamSynchronize(stream_), "sync");
     Check(cudaStreamSynchronize(side_), "sync");
-    Check(cudaMemcpy(dst, (grad ? grad_ : master_) + p.offset + offset, static_cast<std::size_t>(count) * sizeof(float),
-                     cudaMemcpyDeviceToHost), "param read");
+    ToHost(dst, (grad ? grad_ : master_) + p.offset + offset, static_cast<std::size_t>(count) * sizeof(float), "param read");
   }
   void WriteParam(std::size_t index, bool grad, std::int64_t offset, std::int64_t count, const float* src) override {
     Use();
     const CpuParam& p = params_.at(index);
     Check(cudaStreamSynchronize(stream_), "sync");
     float* dst = (grad ? grad_ : master_) + p.offset + offset;
-    Check(cudaMemcpy(dst, src, static_cast<std::size_t>(count) * sizeof(float), cudaMemcpyHostToDevice), "param write");
+    ToDevice(dst, src, static_cast<std::size_t>(count) * sizeof(float), "param write");
     if (!grad) {
       nc::cast_f32_bf16(dst, value_ + p.offset + offset, count, stream_);
       ++launches_;
@@ -303,7 +345,7 @@ class GpuEngine final : public DeviceEngine {
         if (!have_host_clip) {
           float both[2];
           Check(cudaStreamSynchronize(stream_), "sync");
-          Check(cudaMemcpy(both, nc2, sizeof(both), cudaMemcpyDeviceToHost), "clip read");
+          ToHost(both, nc2, sizeof(both), "clip read");
           host_clip = both[1];
           have_host_clip = true;
         }
@@ -314,7 +356,7 @@ class GpuEngine final : public DeviceEngine {
     }
     float both[2];
     Check(cudaStreamSynchronize(stream_), "sync");
-    Check(cudaMemcpy(both, nc2, sizeof(both), cudaMemcpyDeviceToHost), "norm read");
+    ToHost(both, nc2, sizeof(both), "norm read");
     grad_norm_ = both[0];
   }
 
@@ -365,6 +407,17 @@ class GpuEngine final : public DeviceEngine {
 
  private:
   void Use() { Check(cudaSetDevice(device_), "cudaSetDevice"); }
+  // Every copy goes through the engine's own stream. A plain cudaMemcpy is ordered against the legacy default stream
+  // only, and for pageable host memory it may return while the last staged piece is still on its way to the device:
+  // a kernel on this (non-blocking) stream could then read the destination before the data has landed.
+  void ToDevice(void* dst, const void* src, std::size_t bytes, const char* what) {
+    Check(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream_), what);
+    Check(cudaStreamSynchronize(stream_), what);
+  }
+  void ToHost(void* dst, const void* src, std::size_t bytes, const char* what) {
+    Check(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream_), what);
+    Check(cudaStreamSynchronize(stream_), what);
+  }
 
   void BuildParams() {
     const EngineConfig& c = cfg_;
@@ -487,8 +540,8 @@ class GpuEngine final : public DeviceEngine {
       }
     }
     Check(cudaStreamSynchronize(stream_), "sync");
-    Check(cudaMemcpy(cos_.As<float>(c.size()), c.data(), c.size() * sizeof(float), cudaMemcpyHostToDevice), "rope");
-    Check(cudaMemcpy(sin_.As<float>(s.size()), s.data(), s.size() * sizeof(float), cudaMemcpyHostToDevice), "rope");
+    ToDevice(cos_.As<float>(c.size()), c.data(), c.size() * sizeof(float), "rope");
+    ToDevice(sin_.As<float>(s.size()), s.data(), s.size() * sizeof(float), "rope");
     rope_len_ = n;
   }
 
@@ -658,7 +711,7 @@ class GpuEngine final : public DeviceEngine {
       if (keep_logits) {
         host_chunk.resize(static_cast<std::size_t>(rows) * PV);
         Check(cudaStreamSynchronize(stream_), "sync");
-        Check(cudaMemcpy(host_chunk.data(), logits, host_chunk.size() * sizeof(bf16), cudaMemcpyDeviceToHost), "logits");
+        ToHost(host_chunk.data(), logits, host_chunk.size() * sizeof(bf16), "logits");
         float* dst = logits_.data() + static_cast<std::size_t>(a) * PV;
         for (std::size_t j = 0; j < host_chunk.size(); ++j) dst[j] = __bfloat162float(host_chunk[j]);
       }
@@ -899,13 +952,13 @@ class GpuEngine final : public DeviceEngine {
     Check(cudaStreamSynchronize(stream_), "sync");
     for (std::size_t j = 0; j < g->params.size(); ++j) {
       const CpuParam& p = params_[g->params[j]];
-      Check(cudaMemcpy(w.data(), M(p), n * sizeof(float), cudaMemcpyDeviceToHost), "muon host");
-      Check(cudaMemcpy(gr.data(), G(p), n * sizeof(float), cudaMemcpyDeviceToHost), "muon host");
+      ToHost(w.data(), M(p), n * sizeof(float), "muon host");
+      ToHost(gr.data(), G(p), n * sizeof(float), "muon host");
       MuonUpdateHost(w.data(), gr.data(), g->h_buf1[j].data(), g->h_buf2[j].data(), g->rows, g->cols, lr, momentum, wd,
                      ocfg_.muon_beta2, ocfg_.muon_ns_steps, clip);
       for (std::size_t e = 0; e < n; ++e) wb[e] = __float2bfloat16(w[e]);
-      Check(cudaMemcpy(M(p), w.data(), n * sizeof(float), cudaMemcpyHostToDevice), "muon host");
-      Check(cudaMemcpy(V(p), wb.data(), n * sizeof(bf16), cudaMemcpyHostToDevice), "muon host");
+      ToDevice(M(p), w.data(), n * sizeof(float), "muon host");
+      ToDevice(V(p), wb.data(), n * sizeof(bf16), "muon host");
     }
   }
 

@@ -383,6 +383,19 @@ int64_t ncb_model_launch_count(nanochat_model* model) {
   return model != nullptr && model->gpu ? model->gpu->LaunchCount() : 0;
 }
 
+// An activation of the model's last forward on a CUDA device, widened to fp32 (see DeviceEngine::ReadActivation).
+// Returns the element count (the copy is truncated to `capacity`), or -1 for an unknown name or a CPU model.
+int64_t ncb_model_read_activation(nanochat_model* model, const char* name, int layer, float* dst, int64_t capacity) {
+  if (model == nullptr || !model->gpu || name == nullptr) return -1;
+  return Guard([&]() {
+    std::vector<float> v;
+    if (!model->gpu->ReadActivation(name, layer, &v)) return static_cast<int64_t>(-1);
+    if (dst != nullptr && capacity > 0)
+      std::memcpy(dst, v.data(), static_cast<std::size_t>(std::min<int64_t>(capacity, static_cast<int64_t>(v.size()))) * sizeof(float));
+    return static_cast<int64_t>(v.size());
+  }, static_cast<int64_t>(-1));
+}
+
 float nanochat_eval_bpb(nanochat_model* model, nanochat_loader* loader, int steps) {
   const float inf = std::numeric_limits<float>::infinity();
   if (model == nullptr || loader == nullptr || steps <= 0 || loader->batch <= 0 || loader->seq <= 0) return inf;

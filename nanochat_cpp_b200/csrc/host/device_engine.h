@@ -61,6 +61,11 @@ class DeviceEngine {
   virtual void Prefill(DeviceCache* cache, const int* tokens, int count, std::vector<float>* last_logits) = 0;
   virtual void Decode(DeviceCache* cache, int token, std::vector<float>* logits) = 0;
 
+  // An activation the last training-shaped forward kept ("emb", "x0", "xn", or per layer "xr", "h", "qkv", "qk",
+  // "attn", "x_mid", "h2", "act", "x_out"), widened to fp32; for tests that compare engines stage by stage.
+  // Returns false for an unknown name.
+  virtual bool ReadActivation(const std::string& name, int layer, std::vector<float>* out) = 0;
+
   // First bounded-wait failure any kernel recorded on this device (0 = none); synchronises.
   virtual int Status() = 0;
   virtual std::int64_t LaunchCount() const = 0;
