@@ -106,6 +106,9 @@ int nanochat_device_count(void);
 nanochat_status nanochat_select_device(const char* name);
 /* First bounded-wait failure a kernel recorded on the model's device (0 = none; always 0 on the CPU), and the number
  * of kernel launches the model's engine has issued. */
+/* One micro-batch: forward + backward with the gradients accumulated times `scale` (no zeroing, no optimizer step);
+ * on a CUDA device the LM head runs once, fused forward and backward. Returns the micro-batch loss. */
+float ncb_forward_backward(nanochat_model* model, const int* tokens, const int* targets, int batch, int seq, float scale);
 int ncb_model_device_status(nanochat_model* model);
 int64_t ncb_model_launch_count(nanochat_model* model);
 /* An activation kept by the model's last forward on a CUDA device ("emb", "x0", "xn"; per layer "xr", "h", "qkv", "qk",

@@ -165,6 +165,18 @@ float nanochat_train_step(nanochat_model* model, nanochat_optim* optimizer, cons
     return loss;
   }, kNaN);
 }
+// Forward and backward of one micro-batch in one call, gradients accumulated with `scale` (no zeroing, no optimizer
+// step): on a CUDA device the LM head's forward and backward are fused per row chunk, which a separate
+// nanochat_forward_loss + nanochat_backward_accumulate pair has to run twice. Returns the micro-batch loss.
+float ncb_forward_backward(nanochat_model* model, const int* tokens, const int* targets, int batch, int seq, float scale) {
+  if (model == nullptr || tokens == nullptr || targets == nullptr || batch <= 0 || seq <= 0) return kNaN;
+  return Guard([&]() {
+    if (model->gpu) return model->gpu->ForwardBackward(tokens, targets, batch, seq, scale);
+    const float loss = model->model->ForwardLoss(tokens, targets, batch, seq);
+    model->model->Backward(scale);
+    return loss;
+  }, kNaN);
+}
 float nanochat_rl_step(nanochat_model* model, nanochat_optim* optimizer, const int* tokens, const int* targets,
                        const float* advantages, int batch, int seq, int num_passes, int examples_per_rank, int step) {
   if (model == nullptr || tokens == nullptr || targets == nullptr || advantages == nullptr || batch <= 0 || seq <= 0 ||

@@ -8,6 +8,7 @@
 // sandbox. Here the check is opt-in: with NANOCHAT_SANDBOX_ENFORCE=1 the binary exits unless NANOCHAT_SANDBOX names
 // a profile; otherwise the variable is only echoed in `--version`.
 #include <algorithm>
+#include <chrono>
 #include <cstdio>
 #include <ctime>
 #include <cstdlib>
@@ -260,6 +261,87 @@ int CmdTrain(const Args& a, const char* default_preset = "default") {
   if (s.steps == 0 && last == 0.0f) return Fail("train");
   std::printf("[nanochat] %d steps%s, mean loss %.6f, last loss %.6f, checkpoint %s\n", s.steps,
               s.interrupted ? " (interrupted)" : "", s.mean_loss, last, s.checkpoint);
+  return 0;
+}
+
+// `train --device cuda:N`: the training loop on the C++ GPU engine through the C ABI (one process, one GPU). Data:
+// `--train-parquet ... --tokenizer T`, or `--synthetic-zipf S` (Zipf(S) token ids, no files). Each step runs
+// `--grad-accum` micro-batches of `--batch` rows; every `--log-every` steps it prints the reference's log line
+// (src/train.cc:74-101: step | loss | lr | grad_norm | tok/s | mfu | ... | step_ms | ...).
+int CmdTrainDevice(const Args& a) {
+  nanochat_config cfg = ModelFromArgs(a);
+  nanochat_optim_config optim;
+  if (!OptimFromArgs(a, &optim, "default")) return Fail("train");
+  const int batch = static_cast<int>(a.Int("batch", 8)), accum = std::max(1, static_cast<int>(a.Int("grad-accum", 1)));
+  const int seq = static_cast<int>(a.Int("train-seq", cfg.seq_len)), iters = static_cast<int>(a.Int("num-iterations", 100));
+  const int log_every = static_cast<int>(a.Int("log-every", 10));
+  optim.num_iterations = optim.num_iterations > 0 ? optim.num_iterations : iters;
+  nanochat_tokenizer* tok = nullptr;
+  nanochat_loader* loader = nullptr;
+  if (a.Has("synthetic-zipf")) {
+    loader = ncb_loader_zipf(cfg.vocab_size, seq, a.Num("synthetic-zipf", 1.1), static_cast<uint64_t>(a.Int("seed", 42)),
+                             batch, seq, static_cast<size_t>(a.Int("buffer-docs", 1000)));
+  } else {
+    tok = nanochat_tokenizer_load(a.Str("tokenizer").c_str());
+    if (tok == nullptr) return Fail("train: tokenizer");
+    std::vector<const char*> parquet;
+    for (const std::string& p : a.All("train-parquet")) parquet.push_back(p.c_str());
+    loader = nanochat_loader_create(parquet.data(), static_cast<int>(parquet.size()), a.Str("text-column", "text").c_str(),
+                                    tok, batch, seq, static_cast<uint64_t>(a.Int("seed", 42)),
+                                    static_cast<int>(a.Int("tokenizer-threads", 4)),
+                                    static_cast<size_t>(a.Int("buffer-docs", 1000)));
+  }
+  if (loader == nullptr) return Fail("train: loader");
+  nanochat_model* m = nanochat_model_create(&cfg, static_cast<uint64_t>(a.Int("seed", 42)));
+  if (m == nullptr) return Fail("train: model");
+  if (a.Has("warm-start")) nanochat_load(m, a.Str("warm-start").c_str());
+  nanochat_optim* opt = nanochat_optim_create(m, &optim);
+  if (opt == nullptr) return Fail("train: optimizer");
+  nanochat_params counts{};
+  nanochat_params_get(&cfg, &counts);
+  const double peak = a.Num("peak-flops", 0.0);
+  std::vector<int> tokens(static_cast<std::size_t>(batch) * seq), targets(tokens.size());
+  double window_s = 0.0, loss_sum = 0.0, last = 0.0;
+  int window_steps = 0;
+  for (int step = 1; step <= iters; ++step) {
+    const auto t0 = std::chrono::steady_clock::now();
+    double loss = 0.0;
+    nanochat_zero_grad(m);
+    for (int k = 0; k < accum; ++k) {
+      if (!nanochat_loader_next(loader, tokens.data(), targets.data())) break;
+      loss += ncb_forward_backward(m, tokens.data(), targets.data(), batch, seq, 1.0f / static_cast<float>(accum)) / accum;
+    }
+    nanochat_optim_step(opt, step);
+    if (!(loss == loss)) return Fail("train: the loss is not a number");
+    window_s += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    ++window_steps;
+    loss_sum += loss;
+    last = loss;
+    if ((log_every > 0 && step % log_every == 0) || step == iters) {
+      const double step_s = window_s / window_steps, tok_s = static_cast<double>(batch) * seq * accum / step_s;
+      std::printf("step %06d | loss %.6f | lr %.6g | grad_norm %.6g | tok/s %.3f | mfu %.2f%% | model_tflops %.3f | "
+                  "optim_tflops %.3f | step_ms %.3f | data_ms 0.000 | fwd_ms 0.000 | bwd_ms 0.000 | sync_ms 0.000 | "
+                  "opt_ms 0.000 | eval_ms 0.000\n",
+                  step, loss, static_cast<double>(optim.matrix_lr), static_cast<double>(nanochat_optim_grad_norm(opt)),
+                  tok_s, peak > 0 ? 100.0 * tok_s * counts.flops_per_token / peak : 0.0,
+                  tok_s * counts.flops_per_token / 1e12,
+                  ncb_muon_flops_per_step(&cfg, optim.muon_ns_steps) / step_s / 1e12, step_s * 1e3);
+      std::fflush(stdout);
+      window_s = 0.0, window_steps = 0;
+    }
+  }
+  const int status = ncb_model_device_status(m);
+  if (status != 0) {
+    std::fprintf(stderr, "nanochat_cli train: a kernel gave up waiting (status %d); not saving\n", status);
+    return 1;
+  }
+  if (a.Has("checkpoint")) nanochat_save(m, a.Str("checkpoint").c_str());
+  std::printf("[nanochat] %d steps on %s, mean loss %.6f, last loss %.6f, kernel launches %lld\n", iters,
+              nanochat_backend(), loss_sum / std::max(1, iters), last, static_cast<long long>(ncb_model_launch_count(m)));
+  nanochat_optim_free(opt);
+  nanochat_model_free(m);
+  nanochat_loader_free(loader);
+  if (tok != nullptr) nanochat_tokenizer_free(tok);
   return 0;
 }
 
@@ -744,7 +826,9 @@ int CmdDist(int argc, char** argv) {
 
 void Usage() {
   std::printf(
-      "nanochat_cli <command> [--flag value ...]     (native CPU engine; the GPU path is `python -m nanochat_cpp_b200.cli`)\n"
+      "nanochat_cli <command> [--flag value ...] [--device cpu|cuda|cuda:N]\n"
+      "  (native engines: C++ on the CPU, or the sm_100a kernels driven from C++ on a CUDA device; no Python in either)\n"
+      "  train --device cuda:N also takes --synthetic-zipf S (synthetic token ids instead of parquet + tokenizer)\n"
       "  train      --train-parquet P.. --tokenizer T | --rows shard.nchsft   [--mesh N (replicas in this process) | --rank R\n"
       "             --world-size W --port P (one process per rank; or `dist`)] [--batch B --grad-accum A\n"
       "             --num-iterations K --log-every L --save-every S --out-dir D --checkpoint C --resume --warm-start W\n"
@@ -789,6 +873,13 @@ int main(int argc, char** argv) {
   if (cmd == "dist") return CmdDist(argc, argv);
   if (nanochat_init() != NANOCHAT_STATUS_OK) return Fail("init");
   const Args a = Parse(argc, argv, 2);
+  // `--device cpu|cuda|cuda:N` on any command: models live in that engine (NANOCHAT_DEVICE is the default)
+  // (`roofline --device` names a device *profile* instead and is left alone)
+  const bool runs_a_model = cmd == "train" || cmd == "sft" || cmd == "generate" || cmd == "eval" || cmd == "score" ||
+                            cmd == "rl_step" || cmd == "rl_worker" || cmd == "eval_bench";
+  if (runs_a_model && a.Has("device") && nanochat_select_device(a.Str("device").c_str()) != NANOCHAT_STATUS_OK)
+    return Fail("--device");
+  if (cmd == "train" && std::strcmp(nanochat_backend(), "cuda") == 0) return CmdTrainDevice(a);
   if (cmd == "train") return CmdTrain(a);
   if (cmd == "sft") {   // supervised fine-tuning = the training driver over a packed NCSFT001 shard, from a base model
     if (!a.Has("rows") || !(a.Has("warm-start") || a.Has("resume"))) {

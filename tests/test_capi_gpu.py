@@ -129,3 +129,29 @@ def test_generation_and_scoring_run_on_the_device(cuda_backend):
     agree = sum(int(a == b) for a, b in zip(argmax[:63], ref_argmax[:63]))
     assert agree >= 60, agree
     assert native.device_status() == 0
+
+
+def test_native_cli_trains_on_the_device(tmp_path):
+    """`nanochat_cli train --device cuda:0`: one native process, no Python in the loop; the loss on a Zipf stream
+    must fall and the checkpoint it writes must load back into the CPU engine."""
+    import os
+    import re
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "nanochat_cpp_b200", "nanochat_cli")
+    ckpt = str(tmp_path / "gpu.ckpt")
+    out = subprocess.run([exe, "train", "--device", "cuda:0", "--synthetic-zipf", "1.1", "--layers", "4", "--hidden", "512",
+                          "--heads", "4", "--kv-heads", "2", "--seq", "256", "--vocab", "1000", "--padded-vocab", "1024",
+                          "--batch", "8", "--grad-accum", "2", "--num-iterations", "30", "--log-every", "5",
+                          "--checkpoint", ckpt], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-800:]
+    losses = [float(m) for m in re.findall(r"^step \d+ \| loss ([\d.]+)", out.stdout, flags=re.M)]
+    assert len(losses) == 6 and losses[-1] < losses[0] - 0.25, losses
+    assert "on cuda" in out.stdout
+    E.select_device("cpu")
+    cfg = _cfg()
+    host = E.NativeModel(cfg, seed=0)
+    host.load(ckpt)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, 64, (2, cfg.seq_len + 1), generator=g)
+    assert np.isfinite(host.forward_loss(tok[:, :-1].numpy(), tok[:, 1:].numpy()))
