@@ -246,6 +246,11 @@ int ncb_split_pattern(const char* text, int64_t length, int64_t* ends, int capac
 /* Reads one string column of a parquet file; returns the row count and fills offsets/bytes when given. */
 int64_t ncb_parquet_read(const char* path, const char* column, char* bytes, int64_t byte_capacity, int64_t* offsets,
                          int64_t offset_capacity, int64_t* total_bytes);
+/* Sampling with the per-row streams of the native generation loop: row `row_ids[r]` draws from
+ * Rng(MixSeed(seed, row_ids[r])), one draw per sampled position; `draw_index` is the position's index. `logits`:
+ * [rows, vocab] fp32 (soft-capped). Greedy when temperature <= 0. */
+void ncb_sample_rows(const float* logits, int rows, int vocab, float temperature, int top_k, uint64_t seed,
+                     const int64_t* row_ids, int64_t draw_index, int* out);
 int ncb_sample_token(const float* logits, int vocab, float temperature, int top_k, uint64_t seed, uint64_t row,
                      uint64_t step);
 

@@ -570,6 +570,23 @@ int64_t ncb_parquet_read(const char* path, const char* column, char* bytes, int6
   return static_cast<int64_t>(rows.size());
 }
 
+// The sampling streams of generation, for engines that keep their logits elsewhere (the GPU engine of the Python
+// package): row `row_ids[r]` owns the stream Rng(MixSeed(seed, row_ids[r])) and its `draw_index`-th draw picks the
+// token of its `draw_index`-th sampled position, exactly as the native generation loop consumes it
+// (engine_drivers.h GenerateBatchOn; reference src/generate.cc:54, 614-669). `logits` is [rows, vocab] fp32,
+// soft-capped. out[r] receives the token.
+void ncb_sample_rows(const float* logits, int rows, int vocab, float temperature, int top_k, uint64_t seed,
+                     const int64_t* row_ids, int64_t draw_index, int* out) {
+  if (logits == nullptr || out == nullptr || rows <= 0 || vocab <= 0) return;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int r = 0; r < rows; ++r) {
+    ncb::Rng rng(ncb::MixSeed(seed, static_cast<uint64_t>(row_ids != nullptr ? row_ids[r] : r)));
+    if (temperature > 0.0f)
+      for (int64_t k = 0; k < draw_index; ++k) rng.NextU64();
+    out[r] = ncb::SampleToken(logits + static_cast<std::size_t>(r) * vocab, vocab, temperature, top_k, &rng);
+  }
+}
+
 int ncb_sample_token(const float* logits, int vocab, float temperature, int top_k, uint64_t seed, uint64_t row,
                      uint64_t step) {
   ncb::Rng rng(ncb::MixSeed(ncb::MixSeed(seed, row), step));

@@ -6,8 +6,8 @@ every sequence also keeps the normalised embedding of its previous token (the sm
 RoPE tables follow absolute positions and grow on demand; the backout activation is taken after layer L/2;
 the soft-cap is applied to the rows that are sampled from. Differences from the reference are structural only:
 the cache is paged (16-token pages from one pool, a page table per sequence), prefill and decode are batched
-over sequences, the embedding mix and the sampling stay on the device, and on a GPU the decode step can be
-replayed from a CUDA graph.
+over sequences, the embedding mix and greedy selection stay on the device (sampling with a temperature draws from
+the reference's per-row streams in the host runtime), and on a GPU the decode step can be replayed from a CUDA graph.
 """
 from __future__ import annotations
 
@@ -255,28 +255,27 @@ class InferenceEngine:
 # ---------------------------------------------------------------------------------------------------------
 # Sampling on the device
 # ---------------------------------------------------------------------------------------------------------
-def _hash_uniform(seed: int, rows: torch.Tensor, step: int, n: int) -> torch.Tensor:
-    """Counter-based uniforms in (0, 1): one independent stream per (seed, row, step, index)."""
-    dev = rows.device
-    idx = torch.arange(n, device=dev, dtype=torch.int64)[None, :]
-    x = (rows.to(torch.int64)[:, None] * 0x9E3779B1 + idx * 0x85EBCA77 + (step + 1) * 0xC2B2AE3D + seed) & 0xFFFFFFFF
-    for _ in range(2):
-        x = ((x ^ (x >> 16)) * 0x7FEB352D) & 0xFFFFFFFF
-        x = ((x ^ (x >> 15)) * 0x846CA68B) & 0xFFFFFFFF
-        x = x ^ (x >> 16)
-    return (x.float() + 0.5) / 4294967296.0
-
-
 def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, rows: torch.Tensor, step: int):
-    """Greedy for temperature <= 0, else temperature / top-k sampling with the Gumbel-max trick."""
+    """Greedy for temperature <= 0. Otherwise temperature / top-k sampling with the streams of the reference
+    (src/generate.cc:54, 614-669) as the native engine consumes them: row r owns xoshiro256**(MixSeed(seed, r)) and
+    its `step`-th draw picks the `step`-th sampled token by walking the cumulative distribution. The draw itself
+    runs in the host runtime (`ncb_sample_rows`) on a copy of the logits, so a seed gives the same rollout on this
+    engine and on the native ones wherever their logits agree."""
     if not temperature > 0.0:
         return logits.argmax(dim=-1)
-    z = logits / temperature
-    if 0 < top_k < z.shape[-1]:
-        kth = torch.topk(z, top_k, dim=-1).values[:, -1:]
-        z = z.masked_fill(z < kth, float("-inf"))
-    u = _hash_uniform(seed, rows, step, z.shape[-1])
-    return (z - torch.log(-torch.log(u))).argmax(dim=-1)
+    import ctypes
+    import numpy as np
+    from ..data import native
+    L = native.lib()
+    L.ncb_sample_rows.restype = None
+    L.ncb_sample_rows.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int,
+                                  ctypes.c_uint64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+    host = np.ascontiguousarray(logits.detach().float().cpu().numpy())
+    ids = np.ascontiguousarray(rows.detach().cpu().numpy().astype(np.int64))
+    out = np.empty(host.shape[0], dtype=np.int32)
+    L.ncb_sample_rows(host.ctypes.data, host.shape[0], host.shape[1], float(temperature), int(top_k),
+                      ctypes.c_uint64(int(seed) & 0xFFFFFFFFFFFFFFFF), ids.ctypes.data, int(step), out.ctypes.data)
+    return torch.from_numpy(out.astype(np.int64)).to(logits.device)
 
 
 @dataclass
