@@ -15,6 +15,7 @@
 #include <cstring>
 #include <csignal>
 #include <map>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -668,6 +669,170 @@ int CmdRlStep(const Args& a) {
 
 // eval_bench: time the evaluation forward (loss over one batch) of the CPU engine and print a `nanochat.bench.v3`
 // document (reference: src/eval_bench_command.cc). Tokens are xorshift-random in [0, vocab).
+// rl_worker: the persistent policy worker of the RL loop (reference src/rl_worker_command.cc:197-205, protocol
+// src/rl_worker.h). With `--fixture` it replays a recorded run like `rl_step`. Otherwise it loads `--checkpoint`
+// (or builds a model from the model flags), then answers one request per line on stdin with one reply line on stdout:
+//   ping                                                         -> pong ok=1
+//   rollout prompts=<ids,> num_prompts= prompt_len= [num_samples= max_tokens= temperature= top_k= seed= stop_id=
+//           stop_ids=<ids,> bos_id=]                              -> rollout ok=1 ... rows= lengths= masks= tokens=
+//   advantage tokens=<ids,> targets=<ids,> advantages=<floats,> batch= seq= num_passes= examples_per_rank=
+//                                                                -> advantage ok=1 step= loss= grad_norm= valid_targets=
+//   save path=<file>                                             -> save ok=1
+//   quit                                                         -> quit ok=1   (and the worker exits)
+// A request that fails is answered `<kind> ok=0 error=<words_joined_by_underscores>` and the worker stays alive.
+// The same lines are spoken by the Python worker, so the Python RL loop can drive either.
+namespace rlw {
+std::map<std::string, std::string> Fields(const std::vector<std::string>& words) {
+  std::map<std::string, std::string> f;
+  for (std::size_t i = 1; i < words.size(); ++i) {
+    const std::size_t eq = words[i].find('=');
+    if (eq != std::string::npos) f[words[i].substr(0, eq)] = words[i].substr(eq + 1);
+  }
+  return f;
+}
+template <typename T, typename Conv>
+std::vector<T> List(const std::string& text, Conv conv) {
+  std::vector<T> out;
+  std::size_t a = 0;
+  while (a < text.size()) {
+    std::size_t b = text.find(',', a);
+    if (b == std::string::npos) b = text.size();
+    if (b > a) out.push_back(conv(text.substr(a, b - a)));
+    a = b + 1;
+  }
+  return out;
+}
+std::vector<int> Ints(const std::string& t) { return List<int>(t, [](const std::string& w) { return std::atoi(w.c_str()); }); }
+std::vector<float> Floats(const std::string& t) {
+  return List<float>(t, [](const std::string& w) { return static_cast<float>(std::atof(w.c_str())); });
+}
+std::string Need(const std::map<std::string, std::string>& f, const char* key) {
+  const auto it = f.find(key);
+  if (it == f.end()) throw std::runtime_error(std::string("missing ") + key + "=");
+  return it->second;
+}
+std::string Get(const std::map<std::string, std::string>& f, const char* key, const char* fallback) {
+  const auto it = f.find(key);
+  return it == f.end() ? fallback : it->second;
+}
+}  // namespace rlw
+
+int CmdRlStep(const Args& a);
+
+int CmdRlWorker(const Args& a) {
+  if (a.Has("fixture")) return CmdRlStep(a);
+  nanochat_config cfg;
+  nanochat_model* m = nullptr;
+  {
+    Args with_model = a;
+    if (a.Has("checkpoint")) {
+      cfg = ModelFromArgs(a);
+      const bool shape_given = a.Has("preset-model") || a.Has("layers") || a.Has("hidden") || a.Has("heads");
+      if (!shape_given) ConfigFromCheckpoint(a.Str("checkpoint"), &cfg);
+      m = nanochat_model_create(&cfg, static_cast<uint64_t>(a.Int("seed", 0)));
+      if (m != nullptr) nanochat_load(m, a.Str("checkpoint").c_str());
+    } else {
+      m = LoadModel(a, &cfg);
+    }
+  }
+  if (m == nullptr) return Fail("rl_worker: model");
+  nanochat_optim_config oc;
+  if (!OptimFromArgs(a, &oc, "default")) return Fail("rl_worker");
+  nanochat_optim* opt = nanochat_optim_create(m, &oc);
+  if (opt == nullptr) return Fail("rl_worker: optimizer");
+  int step = 0;
+  std::string line;
+  char buf[1 << 16];
+  while (std::fgets(buf, sizeof(buf), stdin) != nullptr) {
+    line = buf;
+    while (!line.empty() && line.back() != '\n' && std::fgets(buf, sizeof(buf), stdin) != nullptr) line += buf;   // long lines
+    while (!line.empty() && (line.back() == '\n' || line.back() == '\r')) line.pop_back();
+    if (line.empty()) continue;
+    std::vector<std::string> words;
+    for (std::size_t i = 0; i < line.size();) {
+      std::size_t j = line.find(' ', i);
+      if (j == std::string::npos) j = line.size();
+      if (j > i) words.push_back(line.substr(i, j - i));
+      i = j + 1;
+    }
+    const std::string kind = words.empty() ? "unknown" : words[0];
+    std::string reply;
+    try {
+      const auto f = rlw::Fields(words);
+      if (kind == "ping") {
+        reply = "pong ok=1";
+      } else if (kind == "quit") {
+        reply = "quit ok=1";
+      } else if (kind == "save") {
+        nanochat_save(m, rlw::Need(f, "path").c_str());
+        reply = "save ok=1";
+      } else if (kind == "advantage") {
+        const int batch = std::atoi(rlw::Need(f, "batch").c_str()), seq = std::atoi(rlw::Need(f, "seq").c_str());
+        const std::vector<int> tokens = rlw::Ints(rlw::Get(f, "tokens", "")), targets = rlw::Ints(rlw::Get(f, "targets", ""));
+        const std::vector<float> adv = rlw::Floats(rlw::Get(f, "advantages", ""));
+        const std::size_t n = static_cast<std::size_t>(std::max(batch, 0)) * static_cast<std::size_t>(std::max(seq, 0));
+        if (batch <= 0 || seq <= 0) throw std::runtime_error("batch and seq must be positive");
+        if (tokens.size() != n || targets.size() != n || adv.size() != n)
+          throw std::runtime_error("every list must hold batch*seq = " + std::to_string(n) + " entries");
+        int valid = 0;
+        for (int t : targets) valid += t != -1 ? 1 : 0;
+        const float loss = nanochat_rl_step(m, opt, tokens.data(), targets.data(), adv.data(), batch, seq,
+                                            std::atoi(rlw::Need(f, "num_passes").c_str()),
+                                            std::atoi(rlw::Need(f, "examples_per_rank").c_str()), step + 1);
+        if (!(loss == loss)) throw std::runtime_error(nanochat_last_error());
+        if (valid > 0) ++step;
+        char out[256];
+        std::snprintf(out, sizeof(out), "advantage ok=1 step=%d loss=%.9g grad_norm=%.9g valid_targets=%d", step,
+                      static_cast<double>(loss), valid > 0 ? static_cast<double>(nanochat_optim_grad_norm(opt)) : 0.0, valid);
+        reply = out;
+      } else if (kind == "rollout") {
+        nanochat_generate_multi_params gp{};
+        gp.num_prompts = std::atoi(rlw::Need(f, "num_prompts").c_str());
+        gp.prompt_len = std::atoi(rlw::Need(f, "prompt_len").c_str());
+        const std::vector<int> prompts = rlw::Ints(rlw::Get(f, "prompts", ""));
+        if (gp.num_prompts <= 0 || gp.prompt_len <= 0 ||
+            prompts.size() != static_cast<std::size_t>(gp.num_prompts) * static_cast<std::size_t>(gp.prompt_len))
+          throw std::runtime_error("prompts must hold num_prompts * prompt_len ids");
+        gp.params.num_samples = std::atoi(rlw::Get(f, "num_samples", "1").c_str());
+        gp.params.max_tokens = std::atoi(rlw::Need(f, "max_tokens").c_str());
+        gp.params.temperature = static_cast<float>(std::atof(rlw::Get(f, "temperature", "1.0").c_str()));
+        gp.params.top_k = std::atoi(rlw::Get(f, "top_k", "0").c_str());
+        gp.params.seed = std::strtoull(rlw::Get(f, "seed", "0").c_str(), nullptr, 10);
+        gp.params.stop_id = std::atoi(rlw::Get(f, "stop_id", "-1").c_str());
+        gp.params.bos_id = std::atoi(rlw::Get(f, "bos_id", "-1").c_str());
+        nanochat_sequences seqs{};
+        nanochat_generate_multi(m, prompts.data(), &gp, &seqs);
+        std::string lengths, masks, toks;
+        for (int r = 0; r < seqs.count; ++r) {
+          lengths += (r ? "," : "") + std::to_string(seqs.lengths[r]);
+          for (int k = 0; k < seqs.lengths[r]; ++k) {
+            const int at = seqs.offsets[r] + k;
+            masks += (masks.empty() ? "" : ",") + std::to_string(static_cast<int>(seqs.mask[at]));
+            toks += (toks.empty() ? "" : ",") + std::to_string(seqs.tokens[at]);
+          }
+        }
+        reply = "rollout ok=1 num_prompts=" + std::to_string(gp.num_prompts) + " num_samples=" +
+                std::to_string(gp.params.num_samples) + " rows=" + std::to_string(seqs.count) + " lengths=" + lengths +
+                " masks=" + masks + " tokens=" + toks;
+      } else {
+        throw std::runtime_error("unknown message type " + kind);
+      }
+    } catch (const std::exception& e) {
+      std::string msg = e.what();
+      for (char& c : msg)
+        if (c == ' ' || c == '\n' || c == '\t') c = '_';
+      reply = kind + " ok=0 error=" + (msg.empty() ? "error" : msg);
+    }
+    std::printf("%s\n", reply.c_str());
+    std::fflush(stdout);
+    if (reply.rfind("quit ok=1", 0) == 0) break;
+  }
+  if (a.Has("save")) nanochat_save(m, a.Str("save").c_str());
+  nanochat_optim_free(opt);
+  nanochat_model_free(m);
+  return 0;
+}
+
 int CmdEvalBench(const Args& a) {
   nanochat_config cfg;
   nanochat_model* m = LoadModel(a, &cfg);
@@ -892,6 +1057,7 @@ int main(int argc, char** argv) {
   if (cmd == "eval") return CmdEval(a);
   if (cmd == "score") return CmdScore(a);
   if (cmd == "rl_step") return CmdRlStep(a);
+  if (cmd == "rl_worker") return CmdRlWorker(a);
   if (cmd == "eval_bench") return CmdEvalBench(a);
   if (cmd == "tok_train") return CmdTokTrain(a);
   if (cmd == "params") return CmdParams(a);

@@ -42,6 +42,16 @@ class PipeWorker:
             argv += ["--checkpoint", checkpoint]
         return cls(argv, env)
 
+    @classmethod
+    def spawn_native(cls, model_flags: Sequence[str], checkpoint: str = "", device: str = "cpu", env=None):
+        """The native worker (`nanochat_cli rl_worker`, C++ on the CPU or on a CUDA device): the same line protocol."""
+        import os
+        exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "nanochat_cli")
+        argv = [exe, "rl_worker", *model_flags, "--device", device]
+        if checkpoint:
+            argv += ["--checkpoint", checkpoint]
+        return cls(argv, env)
+
     def request(self, line: str) -> Dict[str, str]:
         self.proc.stdin.write(line + "\n")
         self.proc.stdin.flush()

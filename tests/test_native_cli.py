@@ -204,3 +204,51 @@ def test_native_eval_bench_prints_a_bench_v3_document(cli):
     assert doc["schema"] == "nanochat.bench.v3" and doc["device"] == "cpu" and row["family"] == "eval_forward"
     assert row["ms"] > 0 and row["iterations"] == 3 and row["shape"] == "B=2 T=64 L=2 C=64 V=512"
     assert 5.5 < doc["loss"] < 7.0 and doc["tokens_per_second"] > 0          # ln(512) = 6.24 for a fresh model
+
+
+def test_native_rl_worker_speaks_the_same_protocol_as_the_python_worker(tmp_path):
+    """`nanochat_cli rl_worker` against the Python `RlWorker` on the same checkpoint: the same rollouts for a seed
+    (both draw from the per-row xoshiro streams) and the same policy-gradient step."""
+    import numpy as np
+    import torch
+    from nanochat_cpp_b200.config import Config
+    from nanochat_cpp_b200.cpu_engine import CpuModel
+    from nanochat_cpp_b200.optim import Optimizer
+    from nanochat_cpp_b200.post import RlWorker
+    from nanochat_cpp_b200.post.rl_loop import PipeWorker
+    from nanochat_cpp_b200.train.checkpointer import load_checkpoint
+    cfg = Config(num_layers=2, num_heads=2, num_kv_heads=1, hidden_dim=64, seq_len=32, vocab_size=96,
+                 padded_vocab_size=128, window_pattern="SL")
+    seed_model = CpuModel(cfg, seed=3)
+    rng = np.random.default_rng(0)
+    for name in seed_model.names():
+        w = seed_model.read(name)
+        seed_model.write(name, w + 0.05 * rng.standard_normal(w.shape).astype(np.float32))
+    ckpt = str(tmp_path / "policy.ckpt")
+    seed_model.save(ckpt)
+    flags = ["--layers", "2", "--hidden", "64", "--heads", "2", "--kv-heads", "1", "--seq", "32", "--vocab", "96",
+             "--padded-vocab", "128", "--window-pattern", "SL"]
+    native = PipeWorker.spawn_native(flags, checkpoint=ckpt)
+    model, _ = load_checkpoint(ckpt, device=torch.device("cpu"), dtype=torch.float32)
+    python = RlWorker(model, Optimizer(model.params))
+    try:
+        assert native.request("ping")["ok"] == "1"
+        roll = ("rollout prompts=5,6,7,8,9,10 num_prompts=2 prompt_len=3 num_samples=3 max_tokens=6 temperature=0.9 "
+                "top_k=20 seed=11")
+        a, b = native.request(roll), python.handle(roll)
+        from nanochat_cpp_b200.post.rl_loop import _parse
+        b = _parse(b)
+        assert a["ok"] == "1" and a["rows"] == "6"
+        assert a["tokens"] == b["tokens"] and a["masks"] == b["masks"] and a["lengths"] == b["lengths"]
+        adv = ("advantage tokens=1,2,3,4,5,6,7,8 targets=2,3,4,-1,6,7,8,-1 advantages=0.5,0.5,0.5,0.5,-1,-1,-1,-1 "
+               "batch=2 seq=4 num_passes=1 examples_per_rank=2")
+        a, b = native.request(adv), _parse(python.handle(adv))
+        assert a["ok"] == "1" and a["step"] == b["step"] == "1" and a["valid_targets"] == b["valid_targets"] == "6"
+        assert abs(float(a["loss"]) - float(b["loss"])) < 1e-4
+        assert abs(float(a["grad_norm"]) - float(b["grad_norm"])) < 1e-3 * max(1.0, float(b["grad_norm"]))
+        import pytest
+        with pytest.raises(RuntimeError, match="batch\\*seq"):        # the client raises on an `ok=0` reply
+            native.request("advantage tokens=1 targets=1 advantages=1 batch=2 seq=4 num_passes=1 examples_per_rank=1")
+        assert native.request("ping")["ok"] == "1"        # a failed request leaves the worker alive
+    finally:
+        native.close()
