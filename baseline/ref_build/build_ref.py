@@ -19,7 +19,7 @@ fp32 into `baseline/_ref/cpu/` the same way): `libnanochat_ref.so`, the harness 
 `backends/{cpu,cuda}/caps.json` (a copy of the reference's declaration files plus a `b200` device row cloned from
 its `h100` row, the reference's own bring-up procedure for a new card), `build.log`.
 
-    python baseline/ref_build/build_ref.py [--ref /root/reference] [--jobs 8] [--backend cuda|cpu]
+    python baseline/ref_build/build_ref.py [--ref <reference checkout>] [--jobs 8] [--backend cuda|cpu]
 """
 from __future__ import annotations
 

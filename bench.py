@@ -243,6 +243,21 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(times[0]), float(times[1])
 
+    # every rank must hold the same compute parameters after the same steps: a checksum over the bf16 buffer's bits,
+    # min and max over ranks (outside the timed regions)
+    dp_check = None
+    if world > 1:
+        trainer.wait_for_weights()
+        bits = trainer.model.params.value.view(torch.int16)
+        digest = (bits.sum(dtype=torch.int64) + 3 * bits[::7].sum(dtype=torch.int64)
+                  + 5 * bits[1::5].sum(dtype=torch.int64)).reshape(1)
+        lo, hi = digest.clone(), digest.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dp_check = {"params_identical_on_all_ranks": bool(lo.item() == hi.item()), "digest": int(lo.item()),
+                    "transport": transport}
+        del bits
+
     tokens_per_step = args.batch * T * world
     value = tokens_per_step * args.steps / (dev_ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
@@ -267,6 +282,7 @@ def main():
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms / args.steps, 3)},
             "gpu_launches": int(launches), "final_loss": round(last_loss, 4), "clocks": clocks,
+            "dp_check": dp_check,
             "peaks": peaks,
         }
         print(json.dumps(line))

@@ -24,6 +24,14 @@ torch::Tensor& status_tensor(int device) {
 }
 
 int* status_ptr(const torch::Tensor& like) { return status_tensor(like.get_device()).data_ptr<int>(); }
+}  // namespace
+
+namespace ncbind {
+// The device's status word, for the other binding files.
+int* device_status(int device) { return status_tensor(device).data_ptr<int>(); }
+}  // namespace ncbind
+
+namespace {
 
 int64_t read_status(int64_t device) {
   return status_tensor(static_cast<int>(device)).cpu().data_ptr<int>()[0];

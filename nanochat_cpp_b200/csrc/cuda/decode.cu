@@ -26,6 +26,7 @@ bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed); }
 void set_pdl_enabled(bool on) { g_pdl.store(on, std::memory_order_relaxed); }
 
 namespace {
+constexpr int kErrBadIndex = 7;   // status word: a position or page index outside its table (same code as ptx.cuh)
 
 __global__ void __launch_bounds__(256) kv_append_kernel(__nv_bfloat16* __restrict__ k_pool,
                                                         __nv_bfloat16* __restrict__ v_pool,
@@ -34,14 +35,22 @@ __global__ void __launch_bounds__(256) kv_append_kernel(__nv_bfloat16* __restric
                                                         const __nv_bfloat16* __restrict__ k_new, long long k_ld,
                                                         const __nv_bfloat16* __restrict__ v_new, long long v_ld,
                                                         int tokens_per_seq, int total_tokens, int page_size,
-                                                        int row_elems) {
+                                                        int row_elems, int num_pages, int* status) {
   const int tok = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (tok >= total_tokens) return;
   const int lane = threadIdx.x & 31;
   const int pos = positions[tok];
   if (pos < 0) return;
   const int b = tok / tokens_per_seq;
+  if (pos / page_size >= max_pages) {   // beyond the sequence's page table: nothing is written
+    if (lane == 0 && status != nullptr) atomicCAS(status, 0, kErrBadIndex);
+    return;
+  }
   const int page = page_table[b * max_pages + pos / page_size];
+  if (page < 0 || (num_pages > 0 && page >= num_pages)) {
+    if (lane == 0 && status != nullptr) atomicCAS(status, 0, kErrBadIndex);
+    return;
+  }
   const long long dst = (static_cast<long long>(page) * page_size + pos % page_size) * row_elems;
   const uint4* ks = reinterpret_cast<const uint4*>(k_new + static_cast<long long>(tok) * k_ld);
   const uint4* vs = reinterpret_cast<const uint4*>(v_new + static_cast<long long>(tok) * v_ld);
@@ -282,7 +291,7 @@ __global__ void __launch_bounds__(256) decode_prep_append_kernel(
     const float* __restrict__ cosT, const float* __restrict__ sinT, const int* __restrict__ positions,
     const int* __restrict__ page_table, int max_pages, int page_size, __nv_bfloat16* __restrict__ q_out,
     __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int tokens, int H, int KV, float eps,
-    float scale) {
+    float scale, int num_pages, int* status) {
   constexpr int D = 128;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // the fused projection row comes from the kernel before
@@ -293,9 +302,14 @@ __global__ void __launch_bounds__(256) decode_prep_append_kernel(
   const int lane = threadIdx.x & 31;
   const int pos = positions[tok];
   if (pos < 0) return;
-  const int page = page_table[static_cast<long long>(tok) * max_pages + pos / page_size];
+  const bool page_ok = pos / page_size < max_pages;
+  const int page = page_ok ? page_table[static_cast<long long>(tok) * max_pages + pos / page_size] : -1;
+  // a position past the page table or a page outside the pool: q is still produced, nothing goes to the cache
+  const bool cache_ok = page >= 0 && (num_pages <= 0 || page < num_pages);
+  if (!cache_ok && lane == 0 && status != nullptr) atomicCAS(status, 0, kErrBadIndex);
   const long long cache_row = (static_cast<long long>(page) * page_size + pos % page_size) * KV * D;
   if (grp == groups) {   // value row -> cache
+    if (!cache_ok) return;
     const uint4* src = reinterpret_cast<const uint4*>(v + static_cast<long long>(tok) * ld_v);
     uint4* dst = reinterpret_cast<uint4*>(v_pool + cache_row);
     for (int i = lane; i < KV * D / 8; i += 32) dst[i] = src[i];
@@ -334,6 +348,7 @@ __global__ void __launch_bounds__(256) decode_prep_append_kernel(
     y1[e] = (x1 * c[e] + x2 * sn[e]) * scale;
     y2[e] = (-x1 * sn[e] + x2 * c[e]) * scale;
   }
+  if (h >= H && !cache_ok) return;
   __nv_bfloat16* dst = h < H ? q_out + (static_cast<long long>(tok) * H + h) * D : k_pool + cache_row + (h - H) * D;
   *reinterpret_cast<uint4*>(dst + 8 * j) = pack8(y1);
   *reinterpret_cast<uint4*>(dst + 64 + 8 * j) = pack8(y2);
@@ -341,11 +356,11 @@ __global__ void __launch_bounds__(256) decode_prep_append_kernel(
 
 void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_table, int max_pages,
                const int* positions, const __nv_bfloat16* k_new, long long k_ld, const __nv_bfloat16* v_new,
-               long long v_ld, int B, int T, int page_size, int row_elems, cudaStream_t s) {
+               long long v_ld, int B, int T, int page_size, int row_elems, cudaStream_t s, int num_pages, int* status) {
   const int total = B * T;
   if (total <= 0) return;
   kv_append_kernel<<<(total + 7) / 8, 256, 0, s>>>(k_pool, v_pool, page_table, max_pages, positions, k_new, k_ld,
-                                                   v_new, v_ld, T, total, page_size, row_elems);
+                                                   v_new, v_ld, T, total, page_size, row_elems, num_pages, status);
 }
 
 // fp32 out[r, c] = cap * tanh(logits[r, c] / cap) for c < vocab: the head's soft cap, one pass over the bf16 logits
@@ -411,7 +426,7 @@ const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const _
                                const float* cosT, const float* sinT, const int* positions, const int* page_table,
                                int max_pages, int page_size, __nv_bfloat16* q_out, __nv_bfloat16* k_pool,
                                __nv_bfloat16* v_pool, int tokens, int H, int KV, int D, float eps, float scale,
-                               cudaStream_t s) {
+                               cudaStream_t s, int num_pages, int* status) {
   if (tokens <= 0) return nullptr;
   if (D != 128) return "decode_prep_append: head_dim must be 128";
   if (ld_qk % 8 || ld_v % 8 ||
@@ -422,7 +437,7 @@ const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const _
   const int units = tokens * ((H + KV + 3) / 4 + 1);
   const cudaError_t e = launch_maybe_pdl(decode_prep_append_kernel, dim3((units + 7) / 8), dim3(256), 0, s, qk, ld_qk, v,
                                          ld_v, cosT, sinT, positions, page_table, max_pages, page_size, q_out, k_pool,
-                                         v_pool, tokens, H, KV, eps, scale);
+                                         v_pool, tokens, H, KV, eps, scale, num_pages, status);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 

@@ -28,10 +28,12 @@ struct DecodeArgs {
 int decode_splits(int B, int KV, int max_keys);
 
 // Rows k_new / v_new ([B*T, row_elems], leading dimensions k_ld / v_ld) go to absolute positions positions[B*T]
-// (negative = skip) of their sequence's pages.
+// (negative = skip) of their sequence's pages. A position past the page table, a negative page, or (with
+// `num_pages` > 0, the pool's size) a page outside the pool is not written and records code 7 in `status`.
 void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_table, int max_pages,
                const int* positions, const __nv_bfloat16* k_new, long long k_ld, const __nv_bfloat16* v_new,
-               long long v_ld, int B, int T, int page_size, int row_elems, cudaStream_t s);
+               long long v_ld, int B, int T, int page_size, int row_elems, cudaStream_t s, int num_pages = 0,
+               int* status = nullptr);
 
 // Decode prologue in one launch (head_dim 128): q / k heads of the fused row `qk` ([tokens, >= (H + KV) * D], q heads
 // first) get head RMSNorm -> RoPE at positions[tok] -> scale; q goes to q_out [tokens, H, D], k and the value row
@@ -40,7 +42,7 @@ const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const _
                                const float* cosT, const float* sinT, const int* positions, const int* page_table,
                                int max_pages, int page_size, __nv_bfloat16* q_out, __nv_bfloat16* k_pool,
                                __nv_bfloat16* v_pool, int tokens, int H, int KV, int D, float eps, float scale,
-                               cudaStream_t s);
+                               cudaStream_t s, int num_pages = 0, int* status = nullptr);
 
 // out fp32 [rows, vocab] = cap * tanh(logits[:, :vocab] / cap); logits bf16 rows with leading dimension ld; vocab even.
 void softcap_logits(const __nv_bfloat16* logits, long long ld, float* out, int rows, int vocab, float cap, cudaStream_t s);

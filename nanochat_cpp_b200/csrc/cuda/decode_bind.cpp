@@ -4,6 +4,10 @@
 #include <torch/extension.h>
 
 #include "decode.h"
+
+namespace ncbind {
+int* device_status(int device);   // bindings.cpp: the device's status word
+}
 #include "pdl_launch.h"
 
 namespace {
@@ -29,7 +33,8 @@ void kv_append(Tensor& k_pool, Tensor& v_pool, const Tensor& page_table, const T
   TORCH_CHECK(row % 8 == 0 && k_new.stride(1) % 8 == 0 && v_new.stride(1) % 8 == 0, "rows must allow 16-byte copies");
   nc::kv_append(bp(k_pool), bp(v_pool), page_table.data_ptr<int>(), page_table.size(1), positions.data_ptr<int>(),
                 bp(k_new), k_new.stride(1), bp(v_new), v_new.stride(1), positions.size(0), positions.size(1),
-                k_pool.size(1), row, at::cuda::getCurrentCUDAStream());
+                k_pool.size(1), row, at::cuda::getCurrentCUDAStream(), k_pool.size(0),
+                ncbind::device_status(k_pool.get_device()));
 }
 
 // qk: [B, >= (H + KV) * D] rows of the fused projection (q heads first), v: [B, KV * D] rows (any row stride);
@@ -57,7 +62,8 @@ Tensor decode_prep_append(const Tensor& qk, const Tensor& v, const Tensor& cos, 
                                            sin.data_ptr<float>(), positions.data_ptr<int>(), page_table.data_ptr<int>(),
                                            page_table.size(1), k_pool.size(1), bp(q_out), bp(k_pool), bp(v_pool), B,
                                            static_cast<int>(H), KV, D, static_cast<float>(eps), static_cast<float>(scale),
-                                           at::cuda::getCurrentCUDAStream());
+                                           at::cuda::getCurrentCUDAStream(), k_pool.size(0),
+                                           ncbind::device_status(k_pool.get_device()));
   TORCH_CHECK(err == nullptr, err);
   return q_out;
 }

@@ -23,6 +23,7 @@ enum : int {
   kErrWaitTmemEmpty = 4,  // MMA never got the accumulator back
   kErrWaitPeer = 5,       // a peer flag never arrived
   kErrWaitOther = 6,
+  kErrBadIndex = 7,       // a token id, target or page index outside its table: the access was skipped
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

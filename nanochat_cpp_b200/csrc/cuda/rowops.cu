@@ -567,12 +567,20 @@ __global__ void __launch_bounds__(kThreads) qk_prep_bwd_kernel(const bf16* __res
 }
 
 // ------------------------------------------------------------------ value gate
+// Index checks of the gather/scatter kernels: `rows` > 0 is the size of the indexed table. An index outside it records
+// kErrBadIndex in the status word (first error wins) and the caller skips the access.
+__device__ __forceinline__ bool bad_index(int id, int rows, int* status) {
+  if (rows <= 0 || (id >= 0 && id < rows)) return false;
+  if (status != nullptr) atomicCAS(status, 0, 7 /* kErrBadIndex */);
+  return true;
+}
 constexpr int kGateCh = 12;
 __global__ void __launch_bounds__(kThreads) value_gate_fwd_kernel(const bf16* __restrict__ h, long long ldh,
                                                                   const bf16* __restrict__ ve,
                                                                   const bf16* __restrict__ gw, bf16* __restrict__ v,
                                                                   long long ldv, bf16* __restrict__ gate, int tokens,
-                                                                  int KV, int D, const int* __restrict__ ids) {
+                                                                  int KV, int D, const int* __restrict__ ids, int rows,
+                                                                  int* status) {
   const long long wid = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   if (wid >= static_cast<long long>(tokens) * KV) return;
   const int lane = threadIdx.x & 31;
@@ -583,6 +591,7 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_kernel(const bf16* __
   const float g = 3.0f / (1.0f + __expf(-pre));
   if (lane == 0) gate[static_cast<long long>(tok) * KV + kh] = f2b(g);
   bf16* vp = v + static_cast<long long>(tok) * ldv + kh * D;
+  if (ids != nullptr && bad_index(ids[tok], rows, status)) return;   // v stays as it was
   const bf16* ep = ve + (static_cast<long long>(ids ? ids[tok] : tok) * KV + kh) * D;
   for (int d = lane; d < D; d += 32) vp[d] = f2b(b2f(vp[d]) + g * b2f(ep[d]));
 }
@@ -637,7 +646,8 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_vec_kernel(const bf16
                                                                       const bf16* __restrict__ gw, bf16* __restrict__ v,
                                                                       long long ldv, bf16* __restrict__ gate,
                                                                       int tokens, int KV, int D,
-                                                                      const int* __restrict__ ids) {
+                                                                      const int* __restrict__ ids, int rows,
+                                                                      int* status) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialization
   const int lane = threadIdx.x & 31, li = lane & 15;
@@ -654,6 +664,7 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_vec_kernel(const bf16
   if (d >= D) return;
   bf16* vp = v + static_cast<long long>(tok) * ldv + kh * D + d;
   // with `ids` the embedding rows are gathered from the table on the fly (decode: no separate gather pass)
+  if (ids != nullptr && bad_index(ids[tok], rows, status)) return;
   const uint4 ev = *reinterpret_cast<const uint4*>(ve + (static_cast<long long>(ids ? ids[tok] : tok) * KV + kh) * D + d);
   const uint4 vv = *reinterpret_cast<const uint4*>(vp);
   const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
@@ -795,12 +806,17 @@ __global__ void __launch_bounds__(kThreads) smear_bwd_kernel(const bf16* __restr
 // ------------------------------------------------------------------ embeddings
 __global__ void __launch_bounds__(kThreads) embedding_fwd_kernel(const int* __restrict__ ids,
                                                                  const bf16* __restrict__ table,
-                                                                 bf16* __restrict__ out, int tokens, int dim) {
+                                                                 bf16* __restrict__ out, int tokens, int dim,
+                                                                 int rows, int* status) {
   const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (tok >= tokens) return;
   const int lane = threadIdx.x & 31;
-  const bf16* src = table + static_cast<long long>(ids[tok]) * dim;
   bf16* dst = out + static_cast<long long>(tok) * dim;
+  if (bad_index(ids[tok], rows, status)) {   // an id outside the table: a zero row, and the status word says so
+    for (int i = lane; i < dim; i += 32) dst[i] = f2b(0.0f);
+    return;
+  }
+  const bf16* src = table + static_cast<long long>(ids[tok]) * dim;
   if (dim % 8 == 0 && aligned16(src) && aligned16(dst)) {
     for (int i = lane * 8; i < dim; i += 256) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
   } else {
@@ -810,9 +826,11 @@ __global__ void __launch_bounds__(kThreads) embedding_fwd_kernel(const int* __re
 
 __global__ void __launch_bounds__(kThreads) embedding_bwd_kernel(const int* __restrict__ ids,
                                                                  const bf16* __restrict__ dout, long long ld,
-                                                                 float* __restrict__ dtable, int tokens, int dim) {
+                                                                 float* __restrict__ dtable, int tokens, int dim,
+                                                                 int rows, int* status) {
   const int tok = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (tok >= tokens) return;
+  if (bad_index(ids[tok], rows, status)) return;
   const int lane = threadIdx.x & 31;
   const bf16* src = dout + static_cast<long long>(tok) * ld;
   float* dst = dtable + static_cast<long long>(ids[tok]) * dim;
@@ -836,11 +854,12 @@ __global__ void __launch_bounds__(kThreads) embedding_bwd_sorted_kernel(const in
                                                                         const int* __restrict__ perm,
                                                                         const bf16* __restrict__ dout, long long ld,
                                                                         float* __restrict__ dtable, int tokens,
-                                                                        int dim) {
+                                                                        int dim, int rows, int* status) {
   const int i = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (i >= tokens) return;
   const int id = sorted_ids[i];
   if (i > 0 && sorted_ids[i - 1] == id) return;  // not the head of its run
+  if (bad_index(id, rows, status)) return;
   const int lane = threadIdx.x & 31;
   float* dst = dtable + static_cast<long long>(id) * dim;
   const bool vec = dim % 8 == 0 && ld % 8 == 0 && aligned16(dout) && aligned16(dst);
@@ -879,11 +898,16 @@ __global__ void __launch_bounds__(256) classifier_kernel(bf16* __restrict__ logi
                                                          const int* __restrict__ targets, float* __restrict__ losses,
                                                          const float* __restrict__ row_scale,
                                                          const float* __restrict__ dlogit_scale, int rows, int vocab,
-                                                         int padded, float softcap, int ignore_index, bool want_grad) {
+                                                         int padded, float softcap, int ignore_index, bool want_grad,
+                                                         int* status) {
   __shared__ float sh[32];
   const int row = blockIdx.x;
   bf16* lp = logits + static_cast<long long>(row) * ld;
-  const int target = targets[row];
+  int target = targets[row];
+  if (target != ignore_index && (target < 0 || target >= vocab)) {   // not a class: counted as ignored, and reported
+    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, 7 /* kErrBadIndex */);
+    target = ignore_index;
+  }
   const float inv_cap = 1.0f / softcap;
   const bool vec = (vocab % 8 == 0) && (padded % 8 == 0) && aligned16(lp) && (ld % 8 == 0);
   if (target == ignore_index) {
@@ -1000,13 +1024,17 @@ template <bool STAGE>
 __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
     bf16* __restrict__ logits, long long ld, const int* __restrict__ targets, float* __restrict__ losses,
     const float* __restrict__ row_scale, const float* __restrict__ dlogit_scale, int vocab, int padded,
-    float softcap, int ignore_index, bool want_grad) {
+    float softcap, int ignore_index, bool want_grad, int* status) {
   extern __shared__ __align__(16) unsigned char cls_smem[];
   bf16* row_s = reinterpret_cast<bf16*>(cls_smem);
   __shared__ float sh[32];
   const int row = blockIdx.x;
   bf16* lp = logits + static_cast<long long>(row) * ld;
-  const int target = targets[row];
+  int target = targets[row];
+  if (target != ignore_index && (target < 0 || target >= vocab)) {
+    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, 7 /* kErrBadIndex */);
+    target = ignore_index;
+  }
   if (target == ignore_index) {
     if (threadIdx.x == 0) losses[row] = 0.0f;
     if (want_grad) {
@@ -1189,15 +1217,16 @@ void qk_prep_bwd(const bf16* pre, long long ld_pre, const bf16* grad, long long 
                                                              seq, heads, D, eps, scale);
 }
 void value_gate_fwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, bf16* v, long long ldv,
-                    bf16* gate, int tokens, int KV, int D, cudaStream_t s, const int* ids) {
+                    bf16* gate, int tokens, int KV, int D, cudaStream_t s, const int* ids, int rows, int* status) {
   const long long n = static_cast<long long>(tokens) * KV;
   if (n <= 0) return;
   if (D % 8 == 0 && D <= 128 && ldv % 8 == 0 && aligned16(v) && aligned16(ve)) {
     launch_maybe_pdl(value_gate_fwd_vec_kernel, dim3(blocks_for_rows((n + 1) / 2)), dim3(kThreads), 0, s, h, ldh, ve,
-                     gate_w, v, ldv, gate, tokens, KV, D, ids);
+                     gate_w, v, ldv, gate, tokens, KV, D, ids, rows, status);
     return;
   }
-  value_gate_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens, KV, D, ids);
+  value_gate_fwd_kernel<<<blocks_for_rows(n), kThreads, 0, s>>>(h, ldh, ve, gate_w, v, ldv, gate, tokens, KV, D, ids,
+                                                                rows, status);
 }
 void value_gate_bwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, const bf16* gate, const bf16* dv,
                     long long lddv, bf16* dve, float* dh12, float* dgw, int tokens, int KV, int D, cudaStream_t s) {
@@ -1221,23 +1250,25 @@ void smear_bwd(const bf16* emb, const bf16* gate_w, const float* lam, const floa
   smear_bwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(emb, gate_w, lam, sig, dx0, de, dgw24, dlam, tokens,
                                                                 seq, dim);
 }
-void embedding_fwd(const int* ids, const bf16* table, bf16* out, int tokens, int dim, cudaStream_t s) {
+void embedding_fwd(const int* ids, const bf16* table, bf16* out, int tokens, int dim, cudaStream_t s, int rows,
+                   int* status) {
   if (tokens <= 0) return;
-  embedding_fwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(ids, table, out, tokens, dim);
+  embedding_fwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(ids, table, out, tokens, dim, rows, status);
 }
-void embedding_bwd(const int* ids, const bf16* dout, long long ld, float* dtable, int tokens, int dim, cudaStream_t s) {
+void embedding_bwd(const int* ids, const bf16* dout, long long ld, float* dtable, int tokens, int dim, cudaStream_t s,
+                   int rows, int* status) {
   if (tokens <= 0) return;
-  embedding_bwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(ids, dout, ld, dtable, tokens, dim);
+  embedding_bwd_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(ids, dout, ld, dtable, tokens, dim, rows, status);
 }
 void embedding_bwd_sorted(const int* sorted_ids, const int* perm, const bf16* dout, long long ld, float* dtable,
-                          int tokens, int dim, cudaStream_t s) {
+                          int tokens, int dim, cudaStream_t s, int rows, int* status) {
   if (tokens <= 0) return;
   embedding_bwd_sorted_kernel<<<blocks_for_rows(tokens), kThreads, 0, s>>>(sorted_ids, perm, dout, ld, dtable, tokens,
-                                                                           dim);
+                                                                           dim, rows, status);
 }
 void classifier_fwd_bwd(bf16* logits, long long ld, const int* targets, float* losses, const float* row_scale,
                         const float* dlogit_scale, int rows, int vocab, int padded, float softcap, int ignore_index,
-                        bool want_grad, cudaStream_t s) {
+                        bool want_grad, cudaStream_t s, int* status) {
   if (rows <= 0) return;
   const size_t row_bytes = static_cast<size_t>(padded) * sizeof(bf16);
   const bool vec = vocab % 8 == 0 && padded % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
@@ -1247,17 +1278,17 @@ void classifier_fwd_bwd(bf16* logits, long long ld, const int* targets, float* l
   }();
   if (vec && !stage) {
     classifier_smem_kernel<false><<<rows, kClsThreads, 0, s>>>(logits, ld, targets, losses, row_scale, dlogit_scale,
-                                                               vocab, padded, softcap, ignore_index, want_grad);
+                                                               vocab, padded, softcap, ignore_index, want_grad, status);
     return;
   }
   if (vec && row_bytes <= 200 * 1024) {
     cudaFuncSetAttribute(classifier_smem_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     classifier_smem_kernel<true><<<rows, kClsThreads, want_grad ? row_bytes : 0, s>>>(
-        logits, ld, targets, losses, row_scale, dlogit_scale, vocab, padded, softcap, ignore_index, want_grad);
+        logits, ld, targets, losses, row_scale, dlogit_scale, vocab, padded, softcap, ignore_index, want_grad, status);
     return;
   }
   classifier_kernel<<<rows, 256, 0, s>>>(logits, ld, targets, losses, row_scale, dlogit_scale, rows, vocab, padded,
-                                         softcap, ignore_index, want_grad);
+                                         softcap, ignore_index, want_grad, status);
 }
 void sumsq_f32(const float* g, long long n, double* out, cudaStream_t s) {
   if (n <= 0) return;

@@ -46,7 +46,8 @@ void qk_prep_bwd(const bf16* pre, long long ld_pre, const bf16* grad, long long 
 // v += 3*sigmoid(h[:, :12] . w[kh]) * ve  (in place on v); gate saved as bf16 [tokens, KV]
 void value_gate_fwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, bf16* v, long long ldv,
                     bf16* gate, int tokens, int KV, int D, cudaStream_t s,
-                    const int* ids = nullptr);   // ids: `ve` is an embedding table [vocab, KV * D], row ids[tok] is used
+                    const int* ids = nullptr, int rows = 0, int* status = nullptr);
+// ids: `ve` is an embedding table [vocab, KV * D], row ids[tok] is used
 void value_gate_bwd(const bf16* h, long long ldh, const bf16* ve, const bf16* gate_w, const bf16* gate, const bf16* dv,
                     long long lddv, bf16* dve, float* dh12, float* dgw, int tokens, int KV, int D, cudaStream_t s);
 
@@ -56,18 +57,22 @@ void smear_fwd(const bf16* emb, const bf16* gate_w, const float* lam, const bf16
 void smear_bwd(const bf16* emb, const bf16* gate_w, const float* lam, const float* sig, const bf16* dx0, bf16* de,
                float* dgw24, float* dlam, int tokens, int seq, int dim, cudaStream_t s);
 
-void embedding_fwd(const int* ids, const bf16* table, bf16* out, int tokens, int dim, cudaStream_t s);
+// `rows` > 0: the table's row count; an id outside it is skipped (forward: a zero row) and `status` gets kErrBadIndex.
+void embedding_fwd(const int* ids, const bf16* table, bf16* out, int tokens, int dim, cudaStream_t s, int rows = 0,
+                   int* status = nullptr);
 // dtable[ids[t]] += dout[t] (fp32 accumulate, vector red.global.add)
-void embedding_bwd(const int* ids, const bf16* dout, long long ld, float* dtable, int tokens, int dim, cudaStream_t s);
+void embedding_bwd(const int* ids, const bf16* dout, long long ld, float* dtable, int tokens, int dim, cudaStream_t s,
+                   int rows = 0, int* status = nullptr);
 // Same sum with a fixed order: `sorted_ids` stably sorted, `perm` the original row of each sorted position.
 void embedding_bwd_sorted(const int* sorted_ids, const int* perm, const bf16* dout, long long ld, float* dtable,
-                          int tokens, int dim, cudaStream_t s);
+                          int tokens, int dim, cudaStream_t s, int rows = 0, int* status = nullptr);
 
 // Softcap + cross entropy over [rows, padded] bf16 logits, in place: logits are overwritten by dlogits when
 // `want_grad`. dlogit_scale is a device scalar. losses[row] = 0 on ignored rows.
 void classifier_fwd_bwd(bf16* logits, long long ld, const int* targets, float* losses, const float* row_scale,
                         const float* dlogit_scale, int rows, int vocab, int padded, float softcap, int ignore_index,
-                        bool want_grad, cudaStream_t s);
+                        bool want_grad, cudaStream_t s, int* status = nullptr);
+// A target outside [0, vocab) other than `ignore_index` counts as ignored and records kErrBadIndex in `status`.
 
 // sum of squares of an fp32 span, accumulated into out[0] (double)
 void sumsq_f32(const float* g, long long n, double* out, cudaStream_t s);

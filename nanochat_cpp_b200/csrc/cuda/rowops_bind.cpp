@@ -6,7 +6,12 @@
 
 #include "rowops.h"
 
+namespace ncbind {
+int* device_status(int device);   // bindings.cpp: the device's status word
+}
+
 namespace {
+inline int* st(const torch::Tensor& like) { return ncbind::device_status(like.get_device()); }
 
 using torch::Tensor;
 using nc::bf16;
@@ -209,7 +214,7 @@ Tensor value_gate_fwd_gather(const Tensor& h, const Tensor& ids, const Tensor& t
   TORCH_CHECK(table.size(1) == KV * D, "value_gate_fwd_gather: table width");
   Tensor gate = torch::empty({h.size(0), KV}, h.options());
   nc::value_gate_fwd(bp(h), h.stride(0), bp(table), bp(gate_w), bpm(v), v.stride(0), bpm(gate), h.size(0), KV, D, cur(),
-                     ids.data_ptr<int>());
+                     ids.data_ptr<int>(), table.size(0), st(h));
   return gate;
 }
 std::vector<Tensor> value_gate_bwd(const Tensor& h, const Tensor& ve, const Tensor& gate_w, const Tensor& gate,
@@ -256,7 +261,8 @@ Tensor embedding_fwd(const Tensor& ids, const Tensor& table) {
   TORCH_CHECK(table.is_contiguous() && ids.is_contiguous(), "embedding_fwd");
   const c10::cuda::CUDAGuard g(table.device());
   Tensor out = torch::empty({ids.numel(), table.size(1)}, table.options());
-  nc::embedding_fwd(ids.data_ptr<int>(), bp(table), bpm(out), ids.numel(), table.size(1), cur());
+  nc::embedding_fwd(ids.data_ptr<int>(), bp(table), bpm(out), ids.numel(), table.size(1), cur(), table.size(0),
+                    st(table));
   return out;
 }
 void embedding_bwd(const Tensor& ids, const Tensor& dout, Tensor& dtable) {
@@ -266,7 +272,7 @@ void embedding_bwd(const Tensor& ids, const Tensor& dout, Tensor& dtable) {
   TORCH_CHECK(dtable.is_contiguous(), "embedding_bwd");
   const c10::cuda::CUDAGuard g(dout.device());
   nc::embedding_bwd(ids.data_ptr<int>(), bp(dout), dout.stride(0), dtable.data_ptr<float>(), ids.numel(),
-                    dtable.size(1), cur());
+                    dtable.size(1), cur(), dtable.size(0), st(dout));
 }
 void embedding_bwd_sorted(const Tensor& sorted_ids, const Tensor& perm, const Tensor& dout, Tensor& dtable) {
   chk(sorted_ids, torch::kInt32, "sorted_ids");
@@ -278,7 +284,8 @@ void embedding_bwd_sorted(const Tensor& sorted_ids, const Tensor& perm, const Te
               "embedding_bwd_sorted");
   const c10::cuda::CUDAGuard g(dout.device());
   nc::embedding_bwd_sorted(sorted_ids.data_ptr<int>(), perm.data_ptr<int>(), bp(dout), dout.stride(0),
-                           dtable.data_ptr<float>(), sorted_ids.numel(), dtable.size(1), cur());
+                           dtable.data_ptr<float>(), sorted_ids.numel(), dtable.size(1), cur(), dtable.size(0),
+                           st(dout));
 }
 
 // In place: `logits` becomes dlogits when want_grad. Returns per-row losses.
@@ -301,7 +308,8 @@ Tensor classifier_fwd_bwd(Tensor& logits, const Tensor& targets, int64_t vocab, 
     rs = row_scale->data_ptr<float>();
   }
   nc::classifier_fwd_bwd(bpm(logits), logits.stride(0), targets.data_ptr<int>(), losses.data_ptr<float>(), rs, ds,
-                         logits.size(0), vocab, logits.size(1), softcap, ignore_index, want_grad, cur());
+                         logits.size(0), vocab, logits.size(1), softcap, ignore_index, want_grad, cur(),
+                         st(logits));
   return losses;
 }
 

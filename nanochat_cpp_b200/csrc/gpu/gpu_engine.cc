@@ -573,7 +573,7 @@ class GpuEngine final : public DeviceEngine {
     bf16* x0 = x0_.As<bf16>(mc);
     float* rstd_e = rstd_e_.As<float>(Mr);
     float* sig = sig_.As<float>(Mr);
-    nc::embedding_fwd(tok, V(P("transformer.wte.weight")), emb_raw, Mr, C, stream_);
+    nc::embedding_fwd(tok, V(P("transformer.wte.weight")), emb_raw, Mr, C, stream_, c.padded_vocab_size, status_);
     nc::rmsnorm_fwd(emb_raw, C, emb, rstd_e, Mr, C, kRmsEps, stream_);
     const bf16* prev = cache != nullptr && cache->has_prev ? cache->prev_emb.As<bf16>(C) : nullptr;
     nc::smear_fwd(emb, V(P("smear_gate.weight")), M(P("smear_lambda")), prev, x0, sig, Mr, T, C, stream_);
@@ -604,7 +604,7 @@ class GpuEngine final : public DeviceEngine {
         bf16* gate = lb.gate.As<bf16>(static_cast<std::size_t>(Mr) * KV);
         // the gate kernel reads the embedding rows straight from the table
         nc::value_gate_fwd(h, C, V(P("value_embeds." + std::to_string(i) + ".weight")), V(LP(i, "attn.ve_gate")), v, wide,
-                           gate, Mr, KV, D, stream_, tok);
+                           gate, Mr, KV, D, stream_, tok, c.padded_vocab_size, status_);
         ++launches_;
       }
       bf16* attn = lb.attn.As<bf16>(static_cast<std::size_t>(Mr) * qd);
@@ -615,12 +615,13 @@ class GpuEngine final : public DeviceEngine {
         if (D == 128) {
           CheckLaunch(nc::decode_prep_append(qkv, wide, v, wide, cosT, sinT, positions, cache->page_table.As<int>(1),
                                              cache->pages, kPage, q1, cache->k[i].As<bf16>(1), cache->v[i].As<bf16>(1), 1,
-                                             H, KV, D, kRmsEps, kQkScale, stream_), "decode_prep_append");
+                                             H, KV, D, kRmsEps, kQkScale, stream_, cache->pages, status_),
+                      "decode_prep_append");
           ++launches_;
         } else {
           nc::qk_prep_fwd(qkv, wide, q1, hk, cosT, sinT, positions, 1, 1, H + KV, D, kRmsEps, kQkScale, stream_);
           nc::kv_append(cache->k[i].As<bf16>(1), cache->v[i].As<bf16>(1), cache->page_table.As<int>(1), cache->pages,
-                        positions, q1 + qd, hk, v, wide, 1, 1, kPage, kd, stream_);
+                        positions, q1 + qd, hk, v, wide, 1, 1, kPage, kd, stream_, cache->pages, status_);
           launches_ += 2;
         }
         nc::DecodeArgs a;
@@ -642,7 +643,7 @@ class GpuEngine final : public DeviceEngine {
         ++launches_;
         if (cache != nullptr) {
           nc::kv_append(cache->k[i].As<bf16>(1), cache->v[i].As<bf16>(1), cache->page_table.As<int>(1), cache->pages,
-                        positions, qk + qd, hk, v, wide, 1, T, kPage, kd, stream_);
+                        positions, qk + qd, hk, v, wide, 1, T, kPage, kd, stream_, cache->pages, status_);
           ++launches_;
         }
         nc::AttnArgs a;
@@ -716,7 +717,8 @@ class GpuEngine final : public DeviceEngine {
         for (std::size_t j = 0; j < host_chunk.size(); ++j) dst[j] = __bfloat162float(host_chunk[j]);
       }
       nc::classifier_fwd_bwd(logits, PV, tgt_.As<int>(1) + a, losses + a, rs != nullptr ? rs + a : nullptr,
-                             want_grad ? dscale : nullptr, rows, c.vocab_size, PV, kSoftcap, -1, want_grad, stream_);
+                             want_grad ? dscale : nullptr, rows, c.vocab_size, PV, kSoftcap, -1, want_grad, stream_,
+                             status_);
       ++launches_;
       if (want_grad) {
         Dgrad(logits, PV, V(lm), rows, PV, C, dxn_.As<bf16>(1) + static_cast<std::size_t>(a) * C, C);
@@ -842,10 +844,10 @@ class GpuEngine final : public DeviceEngine {
         bf16* ve = s_ve_.As<bf16>(static_cast<std::size_t>(Mr) * kd);
         bf16* dve = s_dve_.As<bf16>(static_cast<std::size_t>(Mr) * kd);
         dh12 = dh12_.As<float>(static_cast<std::size_t>(Mr) * kGateCh);
-        nc::embedding_fwd(tok, V(table), ve, Mr, kd, stream_);
+        nc::embedding_fwd(tok, V(table), ve, Mr, kd, stream_, c.padded_vocab_size, status_);
         nc::value_gate_bwd(h, C, ve, V(LP(i, "attn.ve_gate")), lb.gate.As<bf16>(1), dqkv + qd + kd, wide, dve, dh12,
                            G(LP(i, "attn.ve_gate")), Mr, KV, D, stream_);
-        nc::embedding_bwd(tok, dve, kd, G(table), Mr, kd, stream_);
+        nc::embedding_bwd(tok, dve, kd, G(table), Mr, kd, stream_, c.padded_vocab_size, status_);
         launches_ += 3;
       }
       bf16* dh = s_a_.As<bf16>(mc);
@@ -893,7 +895,7 @@ class GpuEngine final : public DeviceEngine {
                   G(P("smear_gate.weight")), G(P("smear_lambda")), Mr, T, C, stream_);
     bf16* de_raw = s_b_.As<bf16>(mc);
     nc::rmsnorm_bwd(emb_raw_.As<bf16>(mc), de, rstd_e_.As<float>(Mr), nullptr, de_raw, Mr, C, stream_);
-    nc::embedding_bwd(tok, de_raw, C, G(P("transformer.wte.weight")), Mr, C, stream_);
+    nc::embedding_bwd(tok, de_raw, C, G(P("transformer.wte.weight")), Mr, C, stream_, c.padded_vocab_size, status_);
     launches_ += 5;
     Join();
     have_saved_ = false;

@@ -65,14 +65,16 @@ EPI_BF16, EPI_BF16_RES, EPI_RELU2, EPI_DRELU2, EPI_F32 = 0, 1, 2, 3, 4
 
 
 def check_status(device=None) -> None:
-    """Raise if any kernel recorded a bounded-wait failure. Synchronizes the device."""
+    """Raise if any kernel recorded a failure in the device's status word: a bounded wait that ran out (codes 1-6)
+    or an index outside its table whose access was skipped (code 7). Synchronizes the device."""
     dev = None if device is None else torch.device(device).index
     if dev is None:
         dev = torch.cuda.current_device()
     code = _C.read_status(dev)
     if code != 0:
         _C.reset_status(dev)
-        raise RuntimeError(f"a kernel gave up waiting (status code {code}); see csrc/cuda/ptx.cuh")
+        what = "skipped an index outside its table" if code == 7 else "gave up waiting"
+        raise RuntimeError(f"a kernel {what} (status code {code}); see csrc/cuda/ptx.cuh")
 
 
 # ---------------------------------------------------------------------------

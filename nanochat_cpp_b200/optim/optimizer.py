@@ -133,7 +133,8 @@ class Optimizer:
         total = torch.zeros((), dtype=torch.float64, device=self.store.device)
         for s in self.store.specs:
             if self.owned(s):
-                total += self.store.g(s.name).to(torch.float64).square().sum()
+                a, b = self.adamw_slices.get(s.name, (0, s.count))
+                total += self.store.grad[s.offset + a:s.offset + b].to(torch.float64).square().sum()
         return total
 
     @torch.no_grad()

@@ -11,8 +11,11 @@ because gradients are summed over ranks after each rank scaled its backward by `
   contiguous slices.
 
 Two transports implement the same step:
-  `nccl`   - baseline: NCCL all-reduce of the flat gradient, owner update, NCCL all-reduce of the
-             masked bf16 parameter buffer (acts as the all-gather).
+  `nccl`   - baseline: the owners' gradient shards are packed into a [world, shard] staging buffer,
+             `reduce_scatter_tensor` (fp32) leaves every owner its reduced shard, the owner updates, the
+             owned bf16 parameters are packed and `all_gather_into_tensor` distributes them (on CPU ranks,
+             where gloo has no reduce-scatter, an all-reduce of the flat gradient and of a masked parameter
+             buffer stands in).
   `fused`  - the sm_100a kernels of `parallel.fused` over NVLink peer memory (reduce-scatter fused with
              the owner's update, all-gather fused into the first consuming GEMM).
 """
@@ -132,18 +135,75 @@ class DataParallel:
             opt.last_grad_norm = norm
             opt.step(step, clip_scale=clip)
             return
-        if self.world_size > 1:
+        use_rs = self.world_size > 1 and store.grad.is_cuda
+        if use_rs:
+            self._nccl_reduce_scatter()
+        elif self.world_size > 1:
             dist.all_reduce(store.grad, op=dist.ReduceOp.SUM, group=self.group)
         from .. import ops
-        norm, clip = ops.grad_norm_and_clip([store.grad], opt.config.clip)
+        if use_rs:
+            # every rank holds the reduced gradient of what it owns only: the norm is the sum of the owners' parts
+            total = self._nccl["g_shard"].square().sum(dtype=torch.float64).reshape(1)  # gaps in the shard are zero
+            dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group)
+            norm = total.sqrt().float()[0]
+            clip_v = opt.config.clip
+            clip = torch.where(norm > clip_v, clip_v / norm.clamp_min(1e-30), torch.ones_like(norm)) \
+                if clip_v and clip_v > 0 else torch.ones_like(norm)
+        else:
+            norm, clip = ops.grad_norm_and_clip([store.grad], opt.config.clip)
         opt.last_grad_norm = norm
         opt.step(step, clip_scale=clip)
-        if self.world_size > 1:
+        if use_rs:
+            self._nccl_all_gather()
+        elif self.world_size > 1:
             self._gather_params()
+
+    # ---- NCCL baseline: reduce-scatter / all-gather over packed owner shards ---------------------------------
+    def _nccl_layout(self):
+        """Views for packing: per owner rank, the (flat offset, count, position) runs of `plan_reduce_scatter`."""
+        if getattr(self, "_nccl", None) is not None:
+            return self._nccl
+        from .fused import plan_reduce_scatter
+        store = self.model.params
+        L = store.cfg.num_layers
+        placed, cap = plan_reduce_scatter(store.specs, self.owners, self.world_size, L)
+        dev = store.grad.device
+        g_stage = torch.zeros(self.world_size, cap, dtype=torch.float32, device=dev)
+        g_shard = torch.zeros(cap, dtype=torch.float32, device=dev)
+        p_stage = torch.zeros(self.world_size, cap, dtype=store.value.dtype, device=dev)
+        p_shard = torch.zeros(cap, dtype=store.value.dtype, device=dev)
+        runs = [[run for b in range(L + 2) for run in placed[r][b]] for r in range(self.world_size)]
+        pack_src = [store.grad[o:o + c] for r in range(self.world_size) for (o, c, _) in runs[r]]
+        pack_dst = [g_stage[r, p:p + c] for r in range(self.world_size) for (o, c, p) in runs[r]]
+        mine = runs[self.rank]
+        own_grad = [store.grad[o:o + c] for (o, c, _) in mine]
+        own_from_shard = [g_shard[p:p + c] for (o, c, p) in mine]
+        own_val = [store.value[o:o + c] for (o, c, _) in mine]
+        own_to_shard = [p_shard[p:p + c] for (o, c, p) in mine]
+        all_val = [store.value[o:o + c] for r in range(self.world_size) for (o, c, _) in runs[r]]
+        all_from_stage = [p_stage[r, p:p + c] for r in range(self.world_size) for (o, c, p) in runs[r]]
+        self._nccl = dict(g_stage=g_stage, g_shard=g_shard, p_stage=p_stage, p_shard=p_shard, pack_src=pack_src,
+                          pack_dst=pack_dst, own_grad=own_grad, own_from_shard=own_from_shard, own_val=own_val,
+                          own_to_shard=own_to_shard, all_val=all_val, all_from_stage=all_from_stage)
+        return self._nccl
+
+    @torch.no_grad()
+    def _nccl_reduce_scatter(self) -> None:
+        n = self._nccl_layout()
+        torch._foreach_copy_(n["pack_dst"], n["pack_src"])
+        dist.reduce_scatter_tensor(n["g_shard"], n["g_stage"].view(-1), op=dist.ReduceOp.SUM, group=self.group)
+        torch._foreach_copy_(n["own_grad"], n["own_from_shard"])
+
+    @torch.no_grad()
+    def _nccl_all_gather(self) -> None:
+        n = self._nccl_layout()
+        torch._foreach_copy_(n["own_to_shard"], n["own_val"])
+        dist.all_gather_into_tensor(n["p_stage"].view(-1), n["p_shard"], group=self.group)
+        torch._foreach_copy_(n["all_val"], n["all_from_stage"])
 
     @torch.no_grad()
     def _gather_params(self) -> None:
-        """Every rank zeroes what it does not own in the compute copy; a sum all-reduce rebuilds it."""
+        """CPU ranks: every rank zeroes what it does not own in the compute copy; a sum all-reduce rebuilds it."""
         store = self.model.params
         val = store.value
         keep = torch.zeros_like(val)
@@ -156,5 +216,3 @@ class DataParallel:
                 keep[s.offset + a:s.offset + b] = val[s.offset + a:s.offset + b]
         dist.all_reduce(keep, op=dist.ReduceOp.SUM, group=self.group)
         val.copy_(keep)
-        if store.value is store.master:
-            return

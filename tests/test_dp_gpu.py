@@ -15,7 +15,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, transport, out):
+def _worker(rank, world, port, transport, out, stands_for=1):
     import torch.distributed as dist
     from nanochat_cpp_b200.config import Config
     from nanochat_cpp_b200.parallel.dp import DataParallel
@@ -27,12 +27,14 @@ def _worker(rank, world, port, transport, out):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     cfg = Config(num_layers=4, num_heads=4, num_kv_heads=2, hidden_dim=512, seq_len=256, vocab_size=1000,
                  padded_vocab_size=1024, window_pattern="SSSL", short_window_override=128)
-    tc = TrainConfig(batch=2, grad_accum=2, num_iterations=6, seed=9)
+    # `stands_for` > 1: one rank takes the micro-batches of that many ranks (the global batch) by accumulation
+    tc = TrainConfig(batch=2, grad_accum=2 * stands_for, num_iterations=6, seed=9)
     tr = Trainer(cfg, tc, device=dev, dp=DataParallel(rank, world, transport=transport, device=dev))
     g = torch.Generator().manual_seed(3)
-    data = torch.randint(0, 200, (6, world, 2, 2, cfg.seq_len + 1), generator=g)
+    data = torch.randint(0, 200, (6, world * stands_for, 2, 2, cfg.seq_len + 1), generator=g)
     for step in range(6):
-        mb = [(data[step, rank, a, :, :-1].to(dev), data[step, rank, a, :, 1:].to(dev)) for a in range(2)]
+        mb = [(data[step, r, a, :, :-1].to(dev), data[step, r, a, :, 1:].to(dev))
+              for r in range(rank * stands_for, (rank + 1) * stands_for) for a in range(2)]
         loss = tr.train_step(mb)
     torch.cuda.synchronize()
     from nanochat_cpp_b200.ops import cuda as K
@@ -53,5 +55,18 @@ def test_fused_transport_matches_nccl(tmp_path):
         outs[transport] = torch.load(out)
     a, b = outs["nccl"]["value"], outs["fused"]["value"]
     assert abs(outs["nccl"]["loss"] - outs["fused"]["loss"]) < 5e-2
+    rel = float((a - b).norm() / (a.norm() + 1e-12))
+    assert rel < 2e-2, rel
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("transport", ["fused", "nccl"])
+def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path, transport):
+    """Two ranks with two micro-batches each == one rank that accumulates the same four micro-batches."""
+    import torch.multiprocessing as mp
+    one, two = str(tmp_path / "one.pt"), str(tmp_path / "two.pt")
+    mp.spawn(_worker, args=(1, _free_port(), "nccl", one, 2), nprocs=1, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), transport, two), nprocs=2, join=True)
+    a, b = torch.load(one)["value"], torch.load(two)["value"]
     rel = float((a - b).norm() / (a.norm() + 1e-12))
     assert rel < 2e-2, rel
