@@ -136,6 +136,34 @@ def run_decode(args):
     return 0
 
 
+def transports_agree(rank, world, dev):
+    """Three untimed steps of a small model from one initialisation on the same data under each transport: the fused
+    peer-memory path (bf16 on the wire, fixed rank order) against NCCL reduce-scatter / all-gather (fp32 on the wire).
+    Reports the relative distance of the resulting parameters and their agreement across ranks."""
+    import torch.distributed as dist
+    from nanochat_cpp_b200.config import Config
+    from nanochat_cpp_b200.parallel.dp import DataParallel
+    from nanochat_cpp_b200.train import TrainConfig, Trainer
+    cfg = Config(num_layers=4, num_heads=4, num_kv_heads=2, hidden_dim=512, seq_len=512, vocab_size=8192,
+                 padded_vocab_size=8192, window_pattern="SSSL")
+    g = torch.Generator().manual_seed(77)
+    data = torch.randint(0, 8192, (3, world, 4, cfg.seq_len + 1), generator=g)
+    out = {}
+    for name in ("nccl", "fused"):
+        tc = TrainConfig(batch=4, grad_accum=1, num_iterations=10, seed=5)
+        tr = Trainer(cfg, tc, device=dev, dp=DataParallel(rank, world, transport=name, device=dev))
+        for k in range(3):
+            rows = data[k, rank].to(dev)
+            tr.train_step([(rows[:, :-1], rows[:, 1:])])
+        tr.wait_for_weights()
+        torch.cuda.synchronize()
+        out[name] = tr.model.params.value.float().clone()
+        del tr
+    rel = ((out["nccl"] - out["fused"]).norm() / out["nccl"].norm()).reshape(1)
+    dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+    return {"fused_vs_nccl_rel_diff_after_3_steps": round(float(rel), 6), "check_model": "4L/512/seq512/vocab8192"}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -257,6 +285,10 @@ def main():
         dp_check = {"params_identical_on_all_ranks": bool(lo.item() == hi.item()), "digest": int(lo.item()),
                     "transport": transport}
         del bits
+        try:
+            dp_check.update(transports_agree(rank, world, dev))
+        except Exception as e:   # the equality probe must never cost the run its timing line
+            dp_check["fused_vs_nccl"] = f"not run: {type(e).__name__}: {e}"[:200]
 
     tokens_per_step = args.batch * T * world
     value = tokens_per_step * args.steps / (dev_ms / 1e3)

@@ -40,9 +40,14 @@ def batches(steps: int, batch: int = 4):
         yield tok[:, :-1].astype(np.int32), tok[:, 1:].astype(np.int32)
 
 
-def run_torch(steps: int):
+def run_torch(steps: int, perturb: float = 0.0):
+    """`perturb` > 0 multiplies every initial weight by (1 + perturb * n), n ~ N(0, 1): the sensitivity probe."""
     torch.manual_seed(0)
     m = GPT(CFG, "cpu", torch.float32, seed=0)
+    if perturb > 0.0:
+        g = torch.Generator().manual_seed(1)
+        m.params.master.mul_(1.0 + perturb * torch.randn(m.params.master.shape, generator=g))
+        m.params.sync_compute()
     opt = Optimizer(m.params, OptimizerConfig(**OPT), SchedulerConfig(**{**SCHED, "num_iterations": steps}))
     losses, t0 = [], time.perf_counter()
     for k, (tok, tgt) in enumerate(batches(steps), start=1):
@@ -73,6 +78,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--engine", default="both", choices=["native", "torch", "both"])
     ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--sensitivity", type=float, default=0.0,
+                    help="also run the torch engine from weights perturbed by this relative amount (e.g. 1e-7, one "
+                         "fp32 rounding step) and report how far its loss trace moves: the scale below which two "
+                         "fp32 engines cannot be told apart on this configuration")
     a = ap.parse_args()
     out = dict(config="cpu tiny: 4L/256/4h/vocab4096/seq256/batch4", steps=a.steps)
     tokens = a.steps * 4 * CFG.seq_len
@@ -94,6 +103,10 @@ def main():
             out["checkpoint_round_trip"] = dict(bit_identical=bool(same), bytes=os.path.getsize(path),
                                                 loss_before=round(nm.forward_loss(tok, tgt), 6),
                                                 loss_after=round(back.forward_loss(tok, tgt), 6))
+    if a.sensitivity > 0.0 and tm is not None:
+        _, pl, _ = run_torch(a.steps, perturb=a.sensitivity)
+        out["sensitivity"] = dict(relative_perturbation=a.sensitivity, losses=[round(x, 6) for x in pl],
+                                  max_loss_difference=float(max(abs(x - y) for x, y in zip(tl, pl))))
     if a.engine == "both":
         out["max_loss_difference"] = float(max(abs(x - y) for x, y in zip(out["torch"]["losses"],
                                                                           out["native"]["losses"])))

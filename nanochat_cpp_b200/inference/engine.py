@@ -24,29 +24,216 @@ from ..models.gpt import GPT, _heads
 PAGE_SIZE = 16
 
 
-class PagedKVCache:
-    """K/V pools per layer, one page table shared by all layers."""
+class PageAllocator:
+    """Free list over the pages of one pool. Pages are handed out on demand and come back when a sequence is reset
+    or, on windowed layers, when every key of the page has left the attention window."""
 
-    def __init__(self, cfg: Config, batch: int, max_seq: int, device, dtype, page_size: int = PAGE_SIZE):
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self._free = list(range(num_pages - 1, -1, -1))   # stack: page 0 first
+
+    @property
+    def available(self) -> int:
+        return len(self._free)
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise MemoryError("KV page pool exhausted")
+        return self._free.pop()
+
+    def release(self, page: int) -> None:
+        self._free.append(page)
+
+
+class _PageMap:
+    """Logical page -> physical page of every sequence for one family of layers (all-history or windowed), with the
+    host copy that the allocator edits and the device copy that the kernels read."""
+
+    def __init__(self, batch: int, pages_per_seq: int, pool_pages: int, device):
+        self.alloc = PageAllocator(pool_pages)
+        self.host = torch.full((batch, pages_per_seq), -1, dtype=torch.int32)
+        self.device = torch.full((batch, pages_per_seq), -1, dtype=torch.int32, device=device)
+        self.dirty = False
+        self.low = [0] * batch      # every logical page below low[row] is unmapped
+
+    def ensure(self, row: int, first_page: int, last_page: int) -> None:
+        t = self.host[row]
+        for p in range(first_page, last_page + 1):
+            if int(t[p]) < 0:
+                t[p] = self.alloc.alloc()
+                self.dirty = True
+
+    def release_below(self, row: int, page_end: int) -> None:
+        """Unmap logical pages [0, page_end) of `row`."""
+        t = self.host[row]
+        page_end = min(page_end, t.shape[0])
+        for p in range(self.low[row], page_end):
+            if int(t[p]) >= 0:
+                self.alloc.release(int(t[p]))
+                t[p] = -1
+                self.dirty = True
+        self.low[row] = max(self.low[row], page_end)
+
+    def release_all(self, row: int) -> None:
+        self.release_below(row, self.host.shape[1])
+        self.low[row] = 0
+
+    def push(self) -> None:
+        """A blocking copy (once per page boundary, not per token): the host table is edited again before the device
+        has run the steps that were queued behind an asynchronous copy, so the copy must have read it by then."""
+        if self.dirty:
+            self.device.copy_(self.host)
+            self.dirty = False
+
+
+class PagedKVCache:
+    """K/V pools per layer in 16-token pages, handed out by a free-list allocator.
+
+    Two page maps: layers that attend to the whole history ("L") keep every page of a sequence; windowed layers ("S")
+    only keep the pages that still hold a key inside the window, so their pools are sized by the window, not by the
+    sequence, and a page whose last key has left the window goes back to the free list. The kernels see only the
+    indirection (`page_table[b, position // page_size]`; an unmapped entry is -1 and is never inside the range a
+    query reads). `pool_pages` below the worst case over-subscribes the all-history pool: pages are mapped when a
+    sequence reaches them and `MemoryError` is raised when none is left.
+
+    The reference's cache is one contiguous [max_seq] buffer per layer and sequence (src/generate.cc:266-300)."""
+
+    def __init__(self, cfg: Config, batch: int, max_seq: int, device, dtype, page_size: int = PAGE_SIZE,
+                 pool_pages: Optional[int] = None, windowed: bool = True):
         self.cfg, self.batch, self.max_seq, self.page_size = cfg, batch, max_seq, page_size
+        device = torch.device(device)
         self.pages_per_seq = (max_seq + page_size - 1) // page_size
-        n_pages = batch * self.pages_per_seq
-        shape = (n_pages, page_size, cfg.num_kv_heads, cfg.head_dim)
-        self.k = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(cfg.num_layers)]
-        self.v = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(cfg.num_layers)]
-        # sequence b owns pages [b*pages_per_seq, (b+1)*pages_per_seq): a static assignment through the table, so
-        # the kernels only ever see the indirection
-        self.page_table = torch.arange(n_pages, dtype=torch.int32, device=device).view(batch, self.pages_per_seq)
+        windows = [cfg.window_left(i) for i in range(cfg.num_layers)]
+        short = [w for w in windows if w is not None and 0 <= w < max_seq]
+        self.window = min(short) if (windowed and short) else -1
+        self.is_windowed = [self.window >= 0 and w is not None and 0 <= w < max_seq for w in windows]
+        n_full = batch * self.pages_per_seq if pool_pages is None else int(pool_pages)
+        # a window of w keys back plus the query touches at most (w + page) // page + 1 pages. A chunk of a long
+        # prompt needs the window before its first token and stores the window before its last: twice that.
+        s_pages = min(self.pages_per_seq, 2 * ((max(self.window, 0) + page_size) // page_size + 1))
+        n_win = batch * s_pages
+        self.full = _PageMap(batch, self.pages_per_seq, n_full, device)
+        self.win = _PageMap(batch, self.pages_per_seq, n_win, device) if any(self.is_windowed) else None
+        self.k, self.v = [], []
+        for i in range(cfg.num_layers):
+            n = n_win if self.is_windowed[i] else n_full
+            shape = (n, page_size, cfg.num_kv_heads, cfg.head_dim)
+            self.k.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
         self.seq_lens = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.lens_host = [0] * batch          # the host's copy of seq_lens (every step advances it without a sync)
         self.prev_emb = torch.zeros(batch, cfg.hidden_dim, dtype=dtype, device=device)
         self.has_prev = False
 
-    def reset(self) -> None:
-        self.seq_lens.zero_()
-        self.has_prev = False
+    # -- what the kernels read
+    @property
+    def page_table(self) -> torch.Tensor:
+        return self.full.device
+
+    def table(self, layer: int) -> torch.Tensor:
+        return self.win.device if self.is_windowed[layer] else self.full.device
+
+    def append_floor(self, new_len: int) -> int:
+        """Windowed layers keep positions >= this (a page boundary) when `new_len` tokens are in the cache."""
+        if self.window < 0:
+            return 0
+        return max(0, (new_len - 1 - self.window)) // self.page_size * self.page_size
+
+    # -- allocation (host side, before the step's kernels are launched)
+    def prepare(self, count: int, rows: Optional[Sequence[int]] = None) -> None:
+        """Map the pages that the next `count` tokens of `rows` (default: all) will be written to, release the
+        windowed pages that fall out of every later query's window, and publish the tables to the device."""
+        ps = self.page_size
+        for r in (range(self.batch) if rows is None else rows):
+            n0 = self.lens_host[r]
+            n1 = n0 + count
+            if n1 > self.max_seq:
+                raise ValueError("sequence does not fit the KV cache")
+            if count == 1 and n0 % ps:
+                continue          # decode inside a page: mapped when the page was entered, nothing to release yet
+            if count > 0:
+                self.full.ensure(r, n0 // ps, (n1 - 1) // ps)
+            if self.win is not None and count > 0:
+                # the first new query (position n0) still reads keys >= n0 - window; what lies below is released
+                self.win.release_below(r, self.append_floor(n0 + 1) // ps)
+                self.win.ensure(r, max(n0, self.append_floor(n1)) // ps, (n1 - 1) // ps)
+        self.full.push()
+        if self.win is not None:
+            self.win.push()
+
+    def advance_host(self, count: int, rows: Optional[Sequence[int]] = None) -> None:
+        for r in (range(self.batch) if rows is None else rows):
+            self.lens_host[r] += count
+
+    def reset(self, rows: Optional[Sequence[int]] = None) -> None:
+        """Forget `rows` (default: all): their pages return to the free lists."""
+        for r in (range(self.batch) if rows is None else rows):
+            self.full.release_all(r)
+            if self.win is not None:
+                self.win.release_all(r)
+            self.lens_host[r] = 0
+        if rows is None:
+            self.seq_lens.zero_()
+            self.has_prev = False
+        else:
+            self.seq_lens[torch.as_tensor(list(rows), device=self.seq_lens.device)] = 0
+        self.full.push()
+        if self.win is not None:
+            self.win.push()
+
+    def pages_in_use(self) -> dict:
+        out = {"full": self.full.alloc.num_pages - self.full.alloc.available}
+        if self.win is not None:
+            out["windowed"] = self.win.alloc.num_pages - self.win.alloc.available
+        return out
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.k + self.v)
+
+    def rows(self, index: Sequence[int]) -> "_CacheRows":
+        return _CacheRows(self, list(index))
+
+
+class _CacheRows:
+    """A subset of a cache's sequences with the attributes the forward pass reads: the pools are shared, the table
+    rows / lengths / previous embeddings are copies that `commit` writes back. Lets sequences of different lengths be
+    prefilled group by group."""
+
+    def __init__(self, parent: PagedKVCache, index: List[int]):
+        self.parent, self.index = parent, index
+        dev = parent.seq_lens.device
+        self._idx = torch.as_tensor(index, dtype=torch.long, device=dev)
+        self.cfg, self.max_seq, self.page_size, self.batch = parent.cfg, parent.max_seq, parent.page_size, len(index)
+        self.k, self.v = parent.k, parent.v
+        self.is_windowed, self.window = parent.is_windowed, parent.window
+        self.seq_lens = parent.seq_lens[self._idx].clone()
+        self.lens_host = [parent.lens_host[r] for r in index]
+        self.prev_emb = parent.prev_emb[self._idx].clone()
+        self.has_prev = parent.has_prev
+        self._tables = None
+
+    def prepare(self, count: int, rows=None) -> None:
+        self.parent.prepare(count, self.index)
+        self._tables = (self.parent.full.device[self._idx].contiguous(),
+                        None if self.parent.win is None else self.parent.win.device[self._idx].contiguous())
+
+    @property
+    def page_table(self):
+        return self._tables[0]
+
+    def table(self, layer: int):
+        return self._tables[1] if self.is_windowed[layer] else self._tables[0]
+
+    def append_floor(self, new_len: int) -> int:
+        return self.parent.append_floor(new_len)
+
+    def advance_host(self, count: int, rows=None) -> None:
+        self.parent.advance_host(count, self.index)
+        self.lens_host = [n + count for n in self.lens_host]
+
+    def commit(self) -> None:
+        self.parent.seq_lens[self._idx] = self.seq_lens
+        self.parent.prev_emb[self._idx] = self.prev_emb
 
 
 class InferenceEngine:
@@ -82,6 +269,8 @@ class InferenceEngine:
         B, T = tokens.shape
         H, KV, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         M = B * T
+        if not (self.device.type == "cuda" and torch.cuda.is_current_stream_capturing()):
+            cache.prepare(T)     # under graph capture / replay the caller has mapped the pages already
         tok = tokens.reshape(-1).to(torch.int32)
         emb_raw = ops.embedding_fwd(tok, P.v("transformer.wte.weight"))
         emb, _ = ops.rmsnorm_fwd(emb_raw)
@@ -98,12 +287,20 @@ class InferenceEngine:
                 cos, sin = cos_all[pos.long()], sin_all[pos.long()]       # [B, 1, D/2] gathered per sequence
             t0 = None
         else:
-            t0 = int(cache.seq_lens[0].item())
+            t0 = cache.lens_host[0]
+            if any(n != t0 for n in cache.lens_host):
+                raise ValueError("prefill needs every sequence at the same position; use prefill_ragged")
             cos_all, sin_all = self._rope(t0 + T)
             cos, sin = cos_all[t0:t0 + T], sin_all[t0:t0 + T]
         new_lens = cache.seq_lens + T
         fused_prologue = kernel_decode and D == 128 and cache.page_table.shape[0] == B
         pos_flat = pos.reshape(-1).contiguous()
+        # windowed layers keep only what a later query can still see: earlier positions of a long prompt are not stored
+        pos_win = pos
+        if not decode and cache.window >= 0:
+            floor = cache.append_floor(t0 + T)
+            if floor > t0:
+                pos_win = torch.where(pos >= floor, pos, torch.full_like(pos, -1))
         x = x0
         x_backout = None
         for i in range(cfg.num_layers):
@@ -127,10 +324,10 @@ class InferenceEngine:
             wl = cfg.window_left(i)
             if fused_prologue and wqkv is not None:
                 # one launch: q / k preparation, k and v appended to their pages; q comes back dense
+                table = cache.table(i)
                 q3 = ops.cuda_module().decode_prep_append(qkv, v, cos_all, sin_all, pos_flat, cache.k[i], cache.v[i],
-                                                          cache.page_table, H)
-                attn = ops.paged_decode_attention(q3, cache.k[i], cache.v[i], cache.page_table, new_lens,
-                                                  wl).view(B, 1, H, D)
+                                                          table, H)
+                attn = ops.paged_decode_attention(q3, cache.k[i], cache.v[i], table, new_lens, wl).view(B, 1, H, D)
                 x_mid = ops.linear_fwd(attn.reshape(M, H * D), m._w(i, "attn.c_proj"), residual=xr)
                 h2, _ = ops.rmsnorm_fwd(x_mid)
                 act = ops.linear_relu2_act_fwd(h2, m._w(i, "mlp.c_fc"))
@@ -144,16 +341,20 @@ class InferenceEngine:
             else:
                 q, k = ops.qk_prep_fwd(q4, k4, cos, sin)
             v4 = _heads(v, B, T, KV, D)
-            ops.kv_append(cache.k[i], cache.v[i], cache.page_table, pos, k, v4)
+            table = cache.table(i)
+            ops.kv_append(cache.k[i], cache.v[i], table, pos_win if cache.is_windowed[i] else pos, k, v4)
             if decode:
-                attn = ops.paged_decode_attention(q[:, 0], cache.k[i], cache.v[i], cache.page_table,
+                attn = ops.paged_decode_attention(q[:, 0], cache.k[i], cache.v[i], table,
                                                   new_lens, wl).view(B, 1, H, D)
             elif t0 == 0:
                 attn, _ = ops.attention_fwd(q, k, v4, wl)
             else:
-                kk = ops.paged_gather(cache.k[i], cache.page_table, t0 + T)
-                vv = ops.paged_gather(cache.v[i], cache.page_table, t0 + T)
-                attn, _ = ops.attention_fwd(q, kk.contiguous(), vv.contiguous(), wl, q_offset=t0)
+                # a continued prompt: earlier keys come from the pages, this chunk's own keys are written over them
+                # (on a windowed layer the chunk's early positions were not stored)
+                kk = ops.paged_gather(cache.k[i], table, t0 + T).contiguous()
+                vv = ops.paged_gather(cache.v[i], table, t0 + T).contiguous()
+                kk[:, t0:], vv[:, t0:] = k, v4
+                attn, _ = ops.attention_fwd(q, kk, vv, wl, q_offset=t0)
             x_mid = ops.linear_fwd(attn.reshape(M, H * D), m._w(i, "attn.c_proj"), residual=xr)
             h2, _ = ops.rmsnorm_fwd(x_mid)
             act = ops.linear_relu2_act_fwd(h2, m._w(i, "mlp.c_fc"))
@@ -161,6 +362,7 @@ class InferenceEngine:
             if i == cfg.backout_layer:
                 x_backout = x
         cache.seq_lens.add_(T)
+        cache.advance_host(T)
         cache.has_prev = True
         x_pre = ops.backout_fwd(x, x_backout, m._lam("backout_lambda"))
         xn, _ = ops.rmsnorm_fwd(x_pre)
@@ -187,10 +389,34 @@ class InferenceEngine:
     def prefill(self, cache: PagedKVCache, tokens: torch.Tensor) -> torch.Tensor:
         """tokens [B, T] (same length for every sequence). Returns logits of the last position [B, vocab]."""
         B, T = tokens.shape
-        if int(cache.seq_lens.max().item()) + T > cache.max_seq:
+        if max(cache.lens_host) + T > cache.max_seq:
             raise ValueError("prompt does not fit the KV cache")
         xn = self._forward(cache, tokens, decode=False)
         return self._logits(xn.view(B, T, -1)[:, -1])
+
+    @torch.no_grad()
+    def prefill_ragged(self, cache: PagedKVCache, prompts: Sequence[Sequence[int]]) -> torch.Tensor:
+        """Prompts of different lengths, one per sequence of the cache. Sequences of equal length are prefilled
+        together (one pass per distinct length). Returns the logits of every prompt's last position [B, vocab]."""
+        if len(prompts) != cache.batch:
+            raise ValueError("one prompt per sequence of the cache")
+        groups = {}
+        for r, p in enumerate(prompts):
+            if len(p) == 0:
+                raise ValueError("empty prompt")
+            groups.setdefault(len(p), []).append(r)
+        out = None
+        for length, rows in sorted(groups.items()):
+            view = cache.rows(rows)
+            tok = torch.tensor([list(prompts[r]) for r in rows], dtype=torch.long, device=self.device)
+            xn = self._forward(view, tok, decode=False)
+            view.commit()
+            lg = self._logits(xn.view(len(rows), length, -1)[:, -1])
+            if out is None:
+                out = torch.empty(cache.batch, lg.shape[1], dtype=lg.dtype, device=lg.device)
+            out[torch.as_tensor(rows, device=lg.device)] = lg
+        cache.has_prev = True
+        return out
 
     @torch.no_grad()
     def decode(self, cache: PagedKVCache, tokens: torch.Tensor, greedy: bool = False) -> torch.Tensor:
@@ -221,10 +447,13 @@ class InferenceEngine:
             self._graph = None
             self._graph_key = key
             self._graph_cache = cache
+            lens_host = list(cache.lens_host)
             try:
                 self._static_tok = tokens.clone()
                 # warm up on a side stream (allocations, tensor-map cache), restoring the cache state afterwards
                 lens, prev, had = cache.seq_lens.clone(), cache.prev_emb.clone(), cache.has_prev
+                lens_host = list(cache.lens_host)
+                cache.prepare(1)
                 s = torch.cuda.Stream()
                 s.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(s):
@@ -233,21 +462,26 @@ class InferenceEngine:
                 cache.seq_lens.copy_(lens)
                 cache.prev_emb.copy_(prev)
                 cache.has_prev = had
+                cache.lens_host[:] = lens_host
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self._static_out = self.decode(cache, self._static_tok, greedy)
                 cache.seq_lens.copy_(lens)
                 cache.prev_emb.copy_(prev)
                 cache.has_prev = had
+                cache.lens_host[:] = lens_host
                 self._graph = g
             except Exception:
+                cache.lens_host[:] = lens_host
                 self._graph = None
                 self._graph_cache = None
                 self.use_cuda_graph = False
                 torch.cuda.synchronize()
                 return self.decode(cache, tokens, greedy)
+        cache.prepare(1)            # page mapping is host work: before the replay, never inside the graph
         self._static_tok.copy_(tokens)
         self._graph.replay()
+        cache.advance_host(1)
         cache.has_prev = True
         return self._static_out
 
@@ -298,19 +532,32 @@ class GeneratedSequence:
 
 
 @torch.no_grad()
-def generate_multi(engine: InferenceEngine, prompts: torch.Tensor, params: GenerateParams,
+def generate_multi(engine: InferenceEngine, prompts, params: GenerateParams,
                    forced: Optional[callable] = None) -> List[GeneratedSequence]:
-    """prompts [N, L] (equal lengths). Every prompt is decoded `num_samples` times: row r = prompt r // S. A row
-    stops at `stop_id`, `bos_id`, any of `stop_ids`, or `max_tokens` (reference src/generate.cc:458-576).
+    """prompts: a tensor [N, L], or a list of token lists of any lengths (the reference's multi-prompt call takes
+    prompts of different lengths too, src/generate.cc:458-576). Every prompt is decoded `num_samples` times: row r =
+    prompt r // S. A row stops at `stop_id`, `bos_id`, any of `stop_ids`, or `max_tokens`.
     `forced(row, tokens_so_far)` may return a token to force at the next position (tool output injection)."""
-    N, Lp = prompts.shape
     S = max(1, params.num_samples)
-    rows = N * S
     dev = engine.device
-    cache = engine.new_cache(rows, Lp + params.max_tokens + 1)
-    tok = prompts.to(dev).repeat_interleave(S, dim=0)
-    logits = engine.prefill(cache, tok)
-    out = [GeneratedSequence(tok[r].tolist(), [0] * Lp) for r in range(rows)]
+    if isinstance(prompts, torch.Tensor):
+        lists = None
+        N, longest = prompts.shape
+    else:
+        lists = [list(p) for p in prompts]
+        N, longest = len(lists), max(len(p) for p in lists)
+        if all(len(p) == longest for p in lists):
+            prompts, lists = torch.tensor(lists, dtype=torch.int64), None
+    rows = N * S
+    cache = engine.new_cache(rows, longest + params.max_tokens + 1)
+    if lists is None:
+        tok = prompts.to(dev).repeat_interleave(S, dim=0)
+        logits = engine.prefill(cache, tok)
+        out = [GeneratedSequence(tok[r].tolist(), [0] * longest) for r in range(rows)]
+    else:
+        per_row = [lists[r // S] for r in range(rows)]
+        logits = engine.prefill_ragged(cache, per_row)
+        out = [GeneratedSequence(list(p), [0] * len(p)) for p in per_row]
     live = torch.ones(rows, dtype=torch.bool, device=dev)
     row_ids = torch.arange(rows, device=dev)
     stops = {s for s in (params.stop_id, params.bos_id, *params.stop_ids) if s is not None and s >= 0}

@@ -559,7 +559,7 @@ def paged_gather(pool, page_table, length):
     """Contiguous [B, length, KV, D] view of the first `length` positions of every sequence."""
     page_size = pool.shape[1]
     n_pages = (length + page_size - 1) // page_size
-    idx = page_table[:, :n_pages].long()
+    idx = page_table[:, :n_pages].long().clamp_min(0)   # unmapped (released) pages: any page, masked by the caller
     out = pool[idx]  # [B, n_pages, page, KV, D]
     B = idx.shape[0]
     return out.reshape(B, n_pages * page_size, *pool.shape[2:])[:, :length]
