@@ -977,9 +977,17 @@ float RlStep(CpuModel* model, CpuOptimizer* opt, const int* tokens, const int* t
 }
 
 // ---------------------------------------------------------------------------------------------- optimizer
+namespace {
+// Length of the warm-down in steps: the product in double, rounded half to even as Python's `round` does (the
+// reference does the same, src/optim.cc:679-685); 0.5 * 5 is 2 steps, not 3.
+int WarmdownIters(float ratio, int num_iterations) {
+  return static_cast<int>(std::nearbyint(static_cast<double>(ratio) * static_cast<double>(num_iterations)));
+}
+}  // namespace
+
 float OptimConfig::LrMultiplier(int step) const {
   const int it = step - 1;
-  const int warmdown = static_cast<int>(std::lround(static_cast<double>(warmdown_ratio) * num_iterations));
+  const int warmdown = WarmdownIters(warmdown_ratio, num_iterations);
   if (warmup_steps > 0 && it < warmup_steps) return static_cast<float>(it + 1) / static_cast<float>(warmup_steps);
   if (warmdown <= 0 || it <= num_iterations - warmdown) return 1.0f;
   const float progress = static_cast<float>(num_iterations - it) / static_cast<float>(warmdown);
@@ -987,7 +995,7 @@ float OptimConfig::LrMultiplier(int step) const {
 }
 float OptimConfig::MuonMomentum(int step) const {
   const int it = step - 1;
-  const int warmdown = static_cast<int>(std::lround(static_cast<double>(warmdown_ratio) * num_iterations));
+  const int warmdown = WarmdownIters(warmdown_ratio, num_iterations);
   const int warmdown_start = num_iterations - warmdown;
   if (muon_momentum_warmup_steps > 0.0f && it < muon_momentum_warmup_steps) {
     const float frac = it / muon_momentum_warmup_steps;

@@ -79,13 +79,13 @@ def test_kv_append_skips_positions_and_pages_outside_the_pool(K):
         table = torch.tensor([[0, 9], [2, 3]], dtype=torch.int32, device="cuda")     # page 9 is not in the pool
         # rows: (seq 0, pos 3) ok; (seq 0, pos 20) -> page 9: skipped; (seq 1, pos 40) past the table: skipped
         positions = torch.tensor([[3, 20], [40, 17]], dtype=torch.int32, device="cuda")
-        k_new = torch.randn(2, 2, KV * D, device="cuda").bfloat16()
-        v_new = torch.randn(2, 2, KV * D, device="cuda").bfloat16()
+        k_new = torch.randn(2, 2, KV, D, device="cuda").bfloat16()
+        v_new = torch.randn(2, 2, KV, D, device="cuda").bfloat16()
         K.kv_append(gk.out, gv.out, table, positions, k_new, v_new)
         torch.cuda.synchronize()
         want = torch.zeros_like(gk.out)
-        want[0, 3] = k_new[0, 0].view(KV, D)
-        want[3, 1] = k_new[1, 1].view(KV, D)
+        want[0, 3] = k_new[0, 0]
+        want[3, 1] = k_new[1, 1]
         assert torch.equal(gk.out, want)
     _expect_bad_index(K)
 

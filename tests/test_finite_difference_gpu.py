@@ -28,8 +28,10 @@ def test_attention_backward_against_differences_of_the_forward_kernel(B, T, H, K
         return float((out.float() * wb).sum())
     # a probe moves one whole head row (D elements): the change in a single score from one element is below the
     # rounding of the bf16 output row it is observed through
-    for name, x, gr in (("dq", q, dq), ("dk", k, dk), ("dv", v, dv)):
-        fd_regression(loss, x, gr, delta=2.0 ** -2, probes=96, gen=g, name=f"attention {name}", slope_tol=0.1,
+    # the loss is linear in v, so its probe can be large (exact but for the rounding of the output): four times the
+    # signal of the q / k probes over the same noise
+    for name, x, gr, delta in (("dq", q, dq, 2.0 ** -2), ("dk", k, dk, 2.0 ** -2), ("dv", v, dv, 1.0)):
+        fd_regression(loss, x, gr, delta=delta, probes=96, gen=g, name=f"attention {name}", slope_tol=0.1,
                       min_corr=0.93, block=D)
     K.check_status()
 
