@@ -186,6 +186,28 @@ def build_gpu_engine(verbose: bool = False) -> str:
     return GPU_PATH
 
 
+def build_sim(verbose: bool = False) -> str:
+    """`libcudart_sim.so`: the stand-in CUDA runtime of csrc/sim (host code only; needs the CUDA headers, no GPU).
+    Preloaded under the native CLI it lets the C++ GPU engine's host side run, checked, on a machine without a GPU."""
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    src = os.path.join(os.path.dirname(CSRC_HOST), "sim", "cudart_sim.cc")
+    if not os.path.exists(src):
+        return ""
+    out = os.path.join(HERE, "libcudart_sim.so")
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
+    key = _hash([src], "sim")
+    stamp = os.path.join(BUILD_DIR, "sim.stamp")
+    if os.path.exists(out) and os.path.exists(stamp) and open(stamp).read() == key:
+        return out
+    _run(["g++", "-shared", "-fPIC", "-O2", "-std=c++17", "-Wall", "-I", os.path.join(cuda_home, "include"), src, "-o",
+          out], os.path.join(BUILD_DIR, "sim.log"))
+    with open(stamp, "w") as f:
+        f.write(key)
+    if verbose:
+        print("built", out)
+    return out
+
+
 def build_core(verbose: bool = False) -> str:
     """Compile the host runtime (no CUDA, no torch)."""
     os.makedirs(BUILD_DIR, exist_ok=True)
@@ -239,6 +261,7 @@ def build_all(verbose: bool = False) -> None:
     build_cli(verbose)
     build_extension(verbose)
     build_gpu_engine(verbose)
+    build_sim(verbose)
 
 
 if __name__ == "__main__":
