@@ -74,7 +74,7 @@ PAGED_STEPS = 24
 
 
 def produce_paged_decode() -> "OrderedDict[str, np.ndarray]":
-    cfg = Config(num_layers=4, num_heads=4, num_kv_heads=2, hidden_dim=128, seq_len=128, vocab_size=320,
+    cfg = Config(num_layers=4, num_heads=2, num_kv_heads=1, hidden_dim=128, seq_len=128, vocab_size=320,
                  padded_vocab_size=320, rope_base=10000.0, window_pattern="SSSL", short_window_override=24)
     m = _seeded_model(cfg, seed=11)
     recs = _cfg_records(cfg)

@@ -1,5 +1,6 @@
 """Workflow sub-commands of the command line: build, test, check, devices, doctor, verify, bench, profile, attain,
-seam, prune.
+seam, prune, and the process boundary: run (sandbox), gpuq / gpu (GPU queue), session, client, sim (stand-in CUDA
+runtime), fixtures, lint, shutdown.
 
 The reference's `tools/nanochat` front end offers the same verbs around Bazel, a sandbox and a GPU queue
 (python/nanochat_cpp/cli.py: build, test, check, devices, doctor, verify, bench, profile, attain). Here they run in
@@ -209,6 +210,145 @@ def cmd_prune(a) -> int:
     return 0
 
 
+
+# ------------------------------------------------------------------------------------------------ process boundary
+def _after_dashes(rest: List[str]) -> List[str]:
+    return rest[1:] if rest[:1] == ["--"] else rest
+
+
+def cmd_run(a) -> int:
+    """`run <profile> -- cmd`: the command under that resource profile (process/sandbox.py)."""
+    from .process import sandbox
+    return sandbox.launch(a.profile, _after_dashes(a.rest), a.backend)
+
+
+def cmd_gpuq(a) -> int:
+    from .process import gpu_queue
+    return gpu_queue.main(a.rest)
+
+
+def cmd_gpu(a) -> int:
+    """`gpu [--gpus N] [--profile P] -- cmd`: submit to the GPU queue, start a worker if none is live, follow the
+    log, return the job's exit code."""
+    from .process import gpu_queue as q
+    cmd = _after_dashes(a.rest)
+    if not cmd:
+        print("gpu: no command", file=sys.stderr)
+        return 2
+    conn = q.open_db()
+    if not q.live_workers(conn):
+        subprocess.Popen([sys.executable, "-m", "nanochat_cpp_b200.process.gpu_queue", "worker", "--idle-exit", "600"],
+                         start_new_session=True, stdin=subprocess.DEVNULL, stdout=subprocess.DEVNULL,
+                         stderr=subprocess.DEVNULL)
+    job = q.submit(conn, cmd, a.gpus, a.profile)
+    print(f"[gpuq] job {job}", file=sys.stderr)
+    return q.wait_for(conn, job, follow=sys.stdout)
+
+
+def cmd_session(a) -> int:
+    from .process import supervisor
+    return supervisor.main(a.rest)
+
+
+def cmd_client(a) -> int:
+    """`client [--device cuda:N|cpu] [--profile P] -- cmd`: a program that uses the C ABI, started in the sandbox with
+    the device selected through NANOCHAT_DEVICE."""
+    from .process import sandbox
+    env = dict(os.environ, NANOCHAT_DEVICE=a.device)
+    return sandbox.launch(a.profile, _after_dashes(a.rest), "auto", env=env)
+
+
+def cmd_sim(a) -> int:
+    """`sim -- cmd`: the command with the stand-in CUDA runtime preloaded; prints the summary of its trace."""
+    from . import build as b
+    lib = b.build_sim()
+    cmd = _after_dashes(a.rest)
+    if not lib or not cmd:
+        print("sim: the stand-in runtime is not built, or no command", file=sys.stderr)
+        return 2
+    trace = a.trace or os.path.join(os.getcwd(), "cudart_sim_trace.jsonl")
+    env = dict(os.environ, LD_PRELOAD=lib, NANOCHAT_SIM_TRACE=trace, NANOCHAT_SIM_STRICT="1" if a.strict else "0")
+    rc = subprocess.run(cmd, env=env).returncode
+    try:
+        rows = [json.loads(line) for line in open(trace)]
+        summary = rows[-1] if rows and rows[-1].get("call") == "summary" else {}
+        for v in [r for r in rows if r.get("call") == "violation"][:20]:
+            print(f"[sim] {v['in']}: {v['what']}", file=sys.stderr)
+        print(json.dumps({k: summary.get(k) for k in ("launches", "tensor_maps", "violations", "live_allocations",
+                                                      "live_bytes")}))
+        if summary.get("violations"):
+            rc = rc or 1
+    except OSError:
+        pass
+    return rc
+
+
+def cmd_fixtures(a) -> int:
+    from .fixtures import generate
+    return generate.main((["--check"] if a.check else []) + a.names)
+
+
+LINT_NOTES = ("SURVEY" + ".md", "VERDICT" + ".md", "ADVICE" + ".md", "DESIGN" + ".md", "BASELINE" + ".md")
+
+
+def lint_findings(root: str = ROOT) -> List[str]:
+    """House rules that a compiler does not check: every Python file byte-compiles; GPU tests carry the gpu marker;
+    profiler commands in profiles/ leave the clocks alone; sources do not point at working notes or at paths of one
+    machine; nothing stops processes by name pattern."""
+    import re
+    out = []
+    skip = {"_work", "gpurun_out", ".git", "_build", "__pycache__", "_ref"}
+    for dirpath, dirs, files in os.walk(root):
+        dirs[:] = [d for d in dirs if d not in skip]
+        for f in files:
+            path = os.path.join(dirpath, f)
+            rel = os.path.relpath(path, root)
+            if f.endswith(".py"):
+                try:
+                    compile(open(path, errors="replace").read(), path, "exec")
+                except SyntaxError as e:
+                    out.append(f"{rel}: does not compile: line {e.lineno}: {e.msg}")
+            if f.endswith((".py", ".cu", ".cuh", ".cc", ".cpp", ".h")):
+                text = open(path, errors="replace").read()
+                for note in LINT_NOTES:
+                    if note in text:
+                        out.append(f"{rel}: names the working note {note}")
+                if re.search(r"\bpkill\s+-f\b|\bkillall\b", text) and rel != os.path.relpath(__file__, root):
+                    out.append(f"{rel}: stops processes by name pattern")
+                if re.match(r"tests/test_.*_gpu\.py$", rel.replace(os.sep, "/")) and "pytest.mark.gpu" not in text:
+                    out.append(f"{rel}: a GPU test file without the gpu marker")
+            if rel.startswith("profiles") and f.endswith((".md", ".txt")):
+                for line in open(path, errors="replace"):
+                    if re.search(r"(^|\s)ncu\s+-", line) and "--clock-control none" not in line and " -i " not in line:
+                        out.append(f"{rel}: an ncu command without --clock-control none: {line.strip()[:80]}")
+    return out
+
+
+def cmd_lint(a) -> int:
+    found = lint_findings()
+    for line in found:
+        print(line)
+    print(f"lint: {len(found)} finding(s)")
+    return 1 if found else 0
+
+
+def cmd_shutdown(a) -> int:
+    """Stop what outlives a command: live queue workers and session supervisors (each by the pid in its own record)."""
+    import signal
+    from .process import gpu_queue as q, supervisor as v
+    stopped = {"workers": 0, "sessions": 0}
+    conn = q.open_db()
+    for w in q.live_workers(conn):
+        if q.pid_alive(w["pid"]):
+            os.kill(w["pid"], signal.SIGTERM)
+            stopped["workers"] += 1
+    for rec in v.status():
+        if rec["state"] == "live" and v.stop(rec["name"]):
+            stopped["sessions"] += 1
+    print(json.dumps(stopped))
+    return 0
+
+
 def register(sub) -> None:
     import argparse
     ap = sub.add_parser("build", help="compile the CUDA extension and the host runtime in-tree")
@@ -246,3 +386,37 @@ def register(sub) -> None:
     ap = sub.add_parser("attain", help="attainment report against the roofline model")
     ap.add_argument("rest", nargs=argparse.REMAINDER)
     ap.set_defaults(fn=cmd_attain)
+    ap = sub.add_parser("run", help="run <profile> -- cmd: a command under a resource profile")
+    ap.add_argument("profile")
+    ap.add_argument("--backend", default="auto", choices=["auto", "cgroup", "rlimit", "none"])
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_run)
+    ap = sub.add_parser("gpuq", help="GPU job queue: submit | worker | list | status | cancel | logs | wait | prune")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_gpuq)
+    ap = sub.add_parser("gpu", help="gpu [--gpus N] [--profile P] -- cmd: run a command through the GPU queue")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--profile", default="gpu-test")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_gpu)
+    ap = sub.add_parser("session", help="session start | send | status | stop")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_session)
+    ap = sub.add_parser("client", help="client [--device D] [--profile P] -- cmd: a C-ABI program in the sandbox")
+    ap.add_argument("--device", default="cpu")
+    ap.add_argument("--profile", default="train")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_client)
+    ap = sub.add_parser("sim", help="sim -- cmd: run with the stand-in CUDA runtime preloaded (no GPU needed)")
+    ap.add_argument("--trace", default="")
+    ap.add_argument("--strict", action="store_true")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=cmd_sim)
+    ap = sub.add_parser("fixtures", help="produce (or --check) the package's own fixtures")
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("names", nargs="*")
+    ap.set_defaults(fn=cmd_fixtures)
+    ap = sub.add_parser("lint", help="house rules no compiler checks")
+    ap.set_defaults(fn=cmd_lint)
+    ap = sub.add_parser("shutdown", help="stop live queue workers and session supervisors")
+    ap.set_defaults(fn=cmd_shutdown)

@@ -73,7 +73,7 @@ def on_grid(shape, step=2.0 ** -4, span=1.5, gen=None, device="cuda"):
 
 
 def fd_regression(loss_fn, x, grad, *, delta=2.0 ** -4, probes=96, gen=None, min_corr=0.97, slope_tol=0.06, name="",
-                  block=1):
+                  block=1, aligned=False):
     """Central differences of `loss_fn()` (a Python float, recomputed by the kernel under test) with respect to
     `probes` random perturbations of the bf16 tensor `x` (modified in place and restored), regressed against the
     analytic gradient `grad`: the slope must be 1 within `slope_tol` and the correlation at least `min_corr`. A
@@ -81,7 +81,10 @@ def fd_regression(loss_fn, x, grad, *, delta=2.0 ** -4, probes=96, gen=None, min
 
     With `block` > 1 a probe moves `block` consecutive elements by +/- delta with random signs and is compared with
     the same signed sum of the analytic gradient: the signal of a directional derivative grows with the block while
-    the rounding noise of the bf16 outputs it is measured through does not."""
+    the rounding noise of the bf16 outputs it is measured through does not. With `aligned` the signs of a probe are
+    those of the analytic gradient on the block (times one random sign for the whole probe): the direction with the
+    largest derivative, which lets `delta` stay small enough for the function to be linear across the probe. Any
+    direction is a valid probe: a wrong gradient still predicts a derivative the kernel does not show."""
     flat = x.view(-1)
     g = grad.reshape(-1).float()
     starts = torch.randint(0, flat.numel() // block, (probes,), generator=gen, device=flat.device) * block
@@ -89,6 +92,9 @@ def fd_regression(loss_fn, x, grad, *, delta=2.0 ** -4, probes=96, gen=None, min
     for i in starts.tolist():
         old = flat[i:i + block].clone()
         sign = (torch.randint(0, 2, (block,), generator=gen, device=flat.device) * 2 - 1).to(old.dtype)
+        if aligned:
+            gs = torch.where(g[i:i + block] >= 0, 1.0, -1.0).to(old.dtype)
+            sign = gs * sign[0]
         flat[i:i + block] = old + sign * delta
         fp = loss_fn()
         flat[i:i + block] = old - sign * delta

@@ -45,6 +45,8 @@ CASES = [
     (1, 1024, 2, 2, 128, 2048),   # window larger than the sequence
     (1, 777, 2, 2, 128, 40),      # window far below a tile: rows fully masked inside edge tiles
     (2, 2048, 2, 2, 128, 1024),
+    (1, 160, 2, 2, 64, 40),       # head_dim 64: ragged length, window below a tile
+    (1, 777, 2, 1, 64, 40),
 ]
 
 
@@ -71,6 +73,7 @@ def test_forward_backward(B, T, H, KV, D, window):
 def test_strided_views_and_offsets():
     """q/k/v as column slices of one fused QKV buffer, gradients written into one dqkv buffer."""
     K = _K()
+    torch.manual_seed(77)
     B, T, H, KV, D = 2, 256, 2, 2, 128
     C = H * D
     qkv = _r(B * T, 3 * C)
@@ -84,9 +87,9 @@ def test_strided_views_and_offsets():
     dview = lambda off, nh: dqkv.as_strided((B, T, nh, D), (T * 3 * C, 3 * C, D, 1), off)
     K.attention_bwd(q, k, v, o, lse, do, 128, out=(dview(0, H), dview(C, KV), dview(2 * C, KV)))
     rdq, rdk, rdv = ref.attention_bwd(q, k, v, o_ref, lse_ref, do, 128)
-    _close(dview(0, H), rdq, 3e-2)
-    _close(dview(C, KV), rdk, 3e-2)
-    _close(dview(2 * C, KV), rdv, 3e-2)
+    _close(dview(0, H), rdq, 3e-2, "dq")          # the names select the gradient tolerance
+    _close(dview(C, KV), rdk, 3e-2, "dk")
+    _close(dview(2 * C, KV), rdv, 3e-2, "dv")
     # decode-style call: 64 new queries against 256 cached keys
     qn = _r(B, 64, H, D)
     o2, _ = K.attention_fwd(qn, k, v, 100)

@@ -30,9 +30,12 @@ def test_attention_backward_against_differences_of_the_forward_kernel(B, T, H, K
     # rounding of the bf16 output row it is observed through
     # the loss is linear in v, so its probe can be large (exact but for the rounding of the output): four times the
     # signal of the q / k probes over the same noise
-    for name, x, gr, delta in (("dq", q, dq, 2.0 ** -2), ("dk", k, dk, 2.0 ** -2), ("dv", v, dv, 1.0)):
+    # q / k probes follow the sign of the analytic gradient: the strongest direction, so 2^-4 per element is enough
+    # signal and the scores move by well under one unit (a random-sign probe large enough to be seen through the
+    # rounding of the bf16 output moves them by more, where the softmax is no longer linear)
+    for name, x, gr, delta in (("dq", q, dq, 2.0 ** -4), ("dk", k, dk, 2.0 ** -4), ("dv", v, dv, 1.0)):
         fd_regression(loss, x, gr, delta=delta, probes=96, gen=g, name=f"attention {name}", slope_tol=0.1,
-                      min_corr=0.93, block=D)
+                      min_corr=0.93, block=D, aligned=(name != "dv"))
     K.check_status()
 
 
