@@ -92,13 +92,19 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint64_t* k_empty = bars + 4;   // [3]
   uint64_t* v_full = bars + 7;    // [3]
   uint64_t* v_empty = bars + 10;  // [3]
-  // per query tile x: 9 barriers starting at bars + 13 + 9x
-  auto s_full = [&](int x, int i) { return bars + 13 + 9 * x + i; };
-  auto s_empty = [&](int x, int i) { return bars + 15 + 9 * x + i; };
-  auto p_full = [&](int x, int i) { return bars + 17 + 9 * x + i; };
-  auto p_empty = [&](int x, int i) { return bars + 19 + 9 * x + i; };
-  auto o_done = [&](int x) { return bars + 21 + 9 * x; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13 + 9 * NQ);
+  // per query tile x: 10 barriers starting at bars + 13 + 10x
+  auto s_full = [&](int x, int i) { return bars + 13 + 10 * x + i; };
+  auto s_empty = [&](int x, int i) { return bars + 15 + 10 * x + i; };
+  auto p_full = [&](int x, int i) { return bars + 17 + 10 * x + i; };
+  auto p_empty = [&](int x, int i) { return bars + 19 + 10 * x + i; };
+  // o_done flips after every P V product of the tile (the rescale path waits on it by parity: at step i the scores
+  // of tile i are already in hand, so at least i - 1 products are complete and the parity is unambiguous).
+  // o_final completes once, after the LAST product: the epilogue cannot use o_done, because a thread that has
+  // finished the last tile's probabilities only knows that n - 2 products are complete, and a parity wait cannot
+  // tell n - 2 completions from n.
+  auto o_done = [&](int x) { return bars + 21 + 10 * x; };
+  auto o_final = [&](int x) { return bars + 22 + 10 * x; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13 + 10 * NQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -133,6 +139,7 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mbar_init(p_empty(x, i), 1);
       }
       mbar_init(o_done(x), 1);
+      mbar_init(o_final(x), 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -244,6 +251,7 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
           mma_commit(p_empty(x, i & 1));
           mma_commit(o_done(x));
+          if (j == hi[x]) mma_commit(o_final(x));
         }
         mma_commit(&v_empty[st]);
         return true;
@@ -357,7 +365,7 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (lane == 0) mbar_arrive(p_full(x, sb));
     }
     if (ok && n_x > 0) {
-      if (mbar_wait(o_done(x), (n_x - 1) & 1, abort_flag, p.status, kErrWaitTmemFull)) {
+      if (mbar_wait(o_final(x), 0, abort_flag, p.status, kErrWaitTmemFull)) {
         tc_fence_after();
         const float inv_l = 1.0f / l_run;
         __nv_bfloat16* op = p.O + static_cast<long long>(b) * p.o_stride_b +

@@ -96,3 +96,20 @@ def test_strided_views_and_offsets():
     o2_ref, _ = ref.attention_fwd(qn, k, v, 100)
     _close(o2, o2_ref, 2e-2)
     K.check_status()
+
+
+@pytest.mark.parametrize("B,T,H,KV,D,window", [(1, 160, 2, 2, 64, 40), (1, 192, 2, 1, 128, 40), (2, 320, 2, 2, 64, -1)])
+def test_forward_repeats_bit_for_bit_on_short_key_sweeps(B, T, H, KV, D, window):
+    """Few key tiles per query tile: the epilogue reaches its wait for the output accumulator while products are
+    still in flight. The two-tile kernel once read the accumulator two products early there (a parity wait cannot
+    tell n - 2 completions from n); the result then changed from launch to launch."""
+    K = _K()
+    torch.manual_seed(T + D)
+    q, k, v = _r(B, T, H, D), _r(B, T, KV, D), _r(B, T, KV, D)
+    o_ref, _ = ref.attention_fwd(q, k, v, window)
+    first, _ = K.attention_fwd(q, k, v, window, variant=2)
+    _close(first, o_ref, 2e-2, "o")
+    for _ in range(200):
+        again, _ = K.attention_fwd(q, k, v, window, variant=2)
+        assert torch.equal(again, first)
+    K.check_status()
