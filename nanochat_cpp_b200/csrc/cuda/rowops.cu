@@ -227,6 +227,73 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const bf16* __res
   }
 }
 
+// Backward of h = rmsnorm(xr), xr = lam_r * x + lam_0 * x0, in one pass over the row:
+//   dxr = rstd * dh' - rstd^3 <xr, dh'> / dim * xr + residual      (dh' = dh with `extra` added to its first columns)
+//   dx = lam_r * dxr;  dx0 (+)= lam_0 * dxr;  g_lam_r += <dxr, x>;  g_lam_0 += <dxr, x0>
+// dxr never reaches memory (the unfused pair writes it as bf16 and reads it back), the scalar gradients go straight
+// into the flat gradient buffer, and the separate pass that added the value-gate's 12 columns into dh is folded in.
+__global__ void __launch_bounds__(kThreads) norm_blend_bwd_kernel(
+    const bf16* __restrict__ xr, const bf16* __restrict__ dh, const float* __restrict__ rstd,
+    const bf16* __restrict__ residual, const float* __restrict__ extra, int extra_cols, const bf16* __restrict__ x,
+    const bf16* __restrict__ x0, const float* __restrict__ lam_r, const float* __restrict__ lam_0,
+    bf16* __restrict__ dx, bf16* __restrict__ dx0, int accumulate_dx0, float* __restrict__ g_lam_r,
+    float* __restrict__ g_lam_0, int rows, int dim) {
+  __shared__ float sh[2][kWarpsPerBlock];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpsPerBlock + warp;
+  float acc_r = 0.0f, acc_0 = 0.0f;
+  if (row < rows) {
+    const long long off = static_cast<long long>(row) * dim;
+    const float* ex = extra != nullptr ? extra + static_cast<long long>(row) * extra_cols : nullptr;
+    auto load_dh = [&](int i) {
+      V8 g = ld8(dh + off + i);
+      if (ex != nullptr && i < extra_cols) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (i + e < extra_cols) g.f[e] = b2f(f2b(g.f[e] + ex[i + e]));   // the unfused path rounds this sum to bf16
+      }
+      return g;
+    };
+    float dot = 0.0f;
+    for (int i = lane * 8; i < dim; i += 256) {
+      const V8 a = ld8(xr + off + i), g = load_dh(i);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot += a.f[e] * g.f[e];
+    }
+    dot = warp_sum(dot);
+    const float r = rstd[row];
+    const float coeff = r * r * r * dot * (1.0f / static_cast<float>(dim));
+    const float kr = *lam_r, k0 = *lam_0;
+    for (int i = lane * 8; i < dim; i += 256) {
+      const V8 a = ld8(xr + off + i), g = load_dh(i), q = ld8(residual + off + i);
+      const V8 xv = ld8(x + off + i), x0v = ld8(x0 + off + i);
+      V8 d, d0;
+      if (accumulate_dx0) d0 = ld8(dx0 + off + i);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float t = r * g.f[e] - coeff * a.f[e] + q.f[e];
+        acc_r += t * xv.f[e];
+        acc_0 += t * x0v.f[e];
+        d.f[e] = kr * t;
+        d0.f[e] = (accumulate_dx0 ? d0.f[e] : 0.0f) + k0 * t;
+      }
+      st8(dx + off + i, d);
+      st8(dx0 + off + i, d0);
+    }
+  }
+  acc_r = warp_sum(acc_r);
+  acc_0 = warp_sum(acc_0);
+  if (lane == 0) sh[0][warp] = acc_r, sh[1][warp] = acc_0;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.0f, b = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarpsPerBlock; ++w) a += sh[0][w], b += sh[1][w];
+    atomicAdd(g_lam_r, a);
+    atomicAdd(g_lam_0, b);
+  }
+}
+
 // ------------------------------------------------------------------ flat elementwise + dot reductions
 // KIND 0: blend_bwd   KIND 1: backout_fwd   KIND 2: backout_bwd   KIND 3: add
 template <int KIND>
@@ -1183,6 +1250,20 @@ void blend_norm_fwd(const bf16* x, const bf16* x0, const float* lam_r, const flo
   if (rows <= 0) return;
   launch_maybe_pdl(rmsnorm_kernel<2>, dim3(blocks_for_rows(rows)), dim3(kThreads), 0, s, x, static_cast<long long>(dim),
                    x0, lam_r, lam_0, xr, h, rstd, rows, dim, eps, hq, sf);
+}
+const char* norm_blend_bwd(const bf16* xr, const bf16* dh, const float* rstd, const bf16* residual, const float* extra,
+                           int extra_cols, const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* dx,
+                           bf16* dx0, bool accumulate_dx0, float* g_lam_r, float* g_lam_0, int rows, int dim,
+                           cudaStream_t s) {
+  if (rows <= 0) return nullptr;
+  if (dim % 8 != 0 || !aligned16(xr) || !aligned16(dh) || !aligned16(residual) || !aligned16(x) || !aligned16(x0) ||
+      !aligned16(dx) || !aligned16(dx0))
+    return "norm_blend_bwd: rows must be multiples of 8 elements and 16-byte aligned";
+  if (extra != nullptr && (extra_cols <= 0 || extra_cols > dim)) return "norm_blend_bwd: bad extra column count";
+  norm_blend_bwd_kernel<<<blocks_for_rows(rows), kThreads, 0, s>>>(xr, dh, rstd, residual, extra, extra_cols, x, x0, lam_r,
+                                                                 lam_0, dx, dx0, accumulate_dx0 ? 1 : 0, g_lam_r, g_lam_0,
+                                                                 rows, dim);
+  return nullptr;
 }
 void blend_bwd(const bf16* dxr, const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* dx,
                bf16* dx0, bool accumulate_dx0, float* dlam2, long long n, cudaStream_t s) {

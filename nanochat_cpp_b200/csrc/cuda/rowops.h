@@ -24,6 +24,13 @@ void blend_norm_fwd(const bf16* x, const bf16* x0, const float* lam_r, const flo
                     float* rstd, int rows, int dim, float eps, cudaStream_t s, uint8_t* hq = nullptr,
                     uint8_t* sf = nullptr);
 // dx = lam_r*dxr ; dx0 (+)= lam_0*dxr ; dlam[0] += <dxr,x> ; dlam[1] += <dxr,x0>
+// rmsnorm backward + blend backward in one pass (see the kernel): dxr stays in registers; the two scalar gradients are
+// added into g_lam_r / g_lam_0 (device scalars inside the flat gradient); `extra` [rows, extra_cols] fp32 is added to
+// the first columns of dh first (may be null). Returns an error string for shapes it does not take.
+const char* norm_blend_bwd(const bf16* xr, const bf16* dh, const float* rstd, const bf16* residual, const float* extra,
+                           int extra_cols, const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* dx,
+                           bf16* dx0, bool accumulate_dx0, float* g_lam_r, float* g_lam_0, int rows, int dim,
+                           cudaStream_t s);
 void blend_bwd(const bf16* dxr, const bf16* x, const bf16* x0, const float* lam_r, const float* lam_0, bf16* dx,
                bf16* dx0, bool accumulate_dx0, float* dlam2, long long n, cudaStream_t s);
 // y = x - lam*xb

@@ -127,6 +127,36 @@ std::vector<Tensor> blend_bwd(const Tensor& dxr, const Tensor& x, const Tensor& 
                 accumulate, dlam.data_ptr<float>(), x.numel(), cur());
   return {dx, dlam};
 }
+// dx0 is written (or accumulated into); g_lam_r / g_lam_0 are one-element fp32 views of the gradient buffer.
+Tensor norm_blend_bwd(const Tensor& xr, const Tensor& dh, const Tensor& rstd, const Tensor& residual,
+                      const c10::optional<Tensor>& extra, const Tensor& x, const Tensor& x0, const Tensor& lam_r,
+                      const Tensor& lam_0, Tensor& dx0, bool accumulate, Tensor& g_lam_r, Tensor& g_lam_0) {
+  chk_rows(xr, "xr");
+  chk_rows(dh, "dh");
+  chk(rstd, torch::kFloat32, "rstd");
+  chk(g_lam_r, torch::kFloat32, "g_lam_r");
+  chk(g_lam_0, torch::kFloat32, "g_lam_0");
+  TORCH_CHECK(xr.is_contiguous() && dh.is_contiguous() && residual.is_contiguous() && x.is_contiguous() &&
+                  x0.is_contiguous() && dx0.is_contiguous() && dh.sizes() == xr.sizes() && residual.sizes() == xr.sizes() &&
+                  x.numel() == xr.numel() && x0.numel() == xr.numel() && dx0.numel() == xr.numel() &&
+                  rstd.numel() == xr.size(0) && g_lam_r.numel() == 1 && g_lam_0.numel() == 1,
+              "norm_blend_bwd: shapes");
+  const c10::cuda::CUDAGuard g(xr.device());
+  const float* ex = nullptr;
+  int ex_cols = 0;
+  if (extra.has_value()) {
+    chk(*extra, torch::kFloat32, "extra");
+    TORCH_CHECK(extra->is_contiguous() && extra->dim() == 2 && extra->size(0) == xr.size(0), "norm_blend_bwd: extra");
+    ex = extra->data_ptr<float>();
+    ex_cols = extra->size(1);
+  }
+  Tensor dx = torch::empty_like(xr);
+  const char* err = nc::norm_blend_bwd(bp(xr), bp(dh), rstd.data_ptr<float>(), bp(residual), ex, ex_cols, bp(x), bp(x0),
+                                       lam_r.data_ptr<float>(), lam_0.data_ptr<float>(), bpm(dx), bpm(dx0), accumulate,
+                                       g_lam_r.data_ptr<float>(), g_lam_0.data_ptr<float>(), xr.size(0), xr.size(1), cur());
+  TORCH_CHECK(err == nullptr, err);
+  return dx;
+}
 Tensor backout_fwd(const Tensor& x, const Tensor& xb, const Tensor& lam) {
   TORCH_CHECK(x.is_contiguous() && xb.is_contiguous(), "backout_fwd");
   const c10::cuda::CUDAGuard g(x.device());
@@ -352,6 +382,7 @@ void register_rowops(pybind11::module_& m) {
   m.def("value_gate_fwd_gather", &value_gate_fwd_gather);
   m.def("smear_fwd", &smear_fwd);
   m.def("smear_bwd", &smear_bwd);
+  m.def("norm_blend_bwd", &norm_blend_bwd);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("embedding_bwd_sorted", &embedding_bwd_sorted);

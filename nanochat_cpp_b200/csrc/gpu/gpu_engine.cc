@@ -34,7 +34,6 @@
 #include "../cuda/optim.h"
 #include "../cuda/rowops.h"
 #include "../host/device_engine.h"
-#include "gpu_aux.h"
 
 namespace ncb {
 namespace {
@@ -767,8 +766,6 @@ class GpuEngine final : public DeviceEngine {
     nc::backout_bwd(dx_pre, x_backout_.As<bf16>(mc), M(P("backout_lambda")), dxb, G(P("backout_lambda")),
                     static_cast<long long>(mc), stream_);
     launches_ += 2;
-    float* dlam = dlam_.As<float>(static_cast<std::size_t>(2 * c.num_layers));
-    Check(cudaMemsetAsync(dlam, 0, static_cast<std::size_t>(2 * c.num_layers) * sizeof(float), stream_), "memset");
     const bf16* x0 = x0_.As<bf16>(mc);
     bf16* dx0 = dx0_.As<bf16>(mc);
     bool have_dx0 = false;
@@ -871,22 +868,19 @@ class GpuEngine final : public DeviceEngine {
         }
       }
       Check(cudaEventRecord(side_done_[i], side_), "event");
-      if (dh12 != nullptr) {
-        nc::add_cols(dh, C, dh12, Mr, kGateCh, stream_);
-        ++launches_;
-      }
-      bf16* dxr = s_b_.As<bf16>(mc);
-      nc::rmsnorm_bwd(lb.xr.As<bf16>(1), dh, lb.rstd1.As<float>(1), dx_mid, dxr, Mr, C, stream_);
       const bf16* x_in = i == 0 ? x0 : layers_[i - 1].x_out.As<bf16>(1);
       bf16* dx_next = s_dx_[par].As<bf16>(mc);
       // this buffer's previous content (written by layer i + 2) was read by layer i + 1's side-stream products
       if (i + 1 < c.num_layers) Check(cudaStreamWaitEvent(stream_, side_done_[i + 1], 0), "wait");
-      nc::blend_bwd(dxr, x_in, x0, resid + i, x0lam + i, dx_next, dx0, have_dx0, dlam + 2 * i, static_cast<long long>(mc), stream_);
-      launches_ += 2;
+      // norm backward + blend backward + the gate's columns + both scalar gradients: one launch, dxr never stored
+      CheckLaunch(nc::norm_blend_bwd(lb.xr.As<bf16>(1), dh, lb.rstd1.As<float>(1), dx_mid, dh12, dh12 != nullptr ? kGateCh : 0,
+                                     x_in, x0, resid + i, x0lam + i, dx_next, dx0, have_dx0, G(P("resid_lambdas")) + i,
+                                     G(P("x0_lambdas")) + i, Mr, C, stream_),
+                  "norm_blend_bwd");
+      ++launches_;
       have_dx0 = true;
       dx = dx_next;
     }
-    gpu_scatter_pairs_add(G(P("resid_lambdas")), G(P("x0_lambdas")), dlam, c.num_layers, stream_);
     // embedding side
     bf16* dsum = s_b_.As<bf16>(mc);
     nc::add_bf16(dx0, dx, dsum, static_cast<long long>(mc), stream_);
@@ -896,7 +890,7 @@ class GpuEngine final : public DeviceEngine {
     bf16* de_raw = s_b_.As<bf16>(mc);
     nc::rmsnorm_bwd(emb_raw_.As<bf16>(mc), de, rstd_e_.As<float>(Mr), nullptr, de_raw, Mr, C, stream_);
     nc::embedding_bwd(tok, de_raw, C, G(P("transformer.wte.weight")), Mr, C, stream_, c.padded_vocab_size, status_);
-    launches_ += 5;
+    launches_ += 4;
     Join();
     have_saved_ = false;
   }
@@ -988,7 +982,7 @@ class GpuEngine final : public DeviceEngine {
   const bf16* x_last_ = nullptr;
   Buf tok_, tgt_, cos_, sin_, emb_raw_, emb_, x0_, rstd_e_, sig_, x_alt_, x_backout_, x_pre_, xn_, rstd_f_;
   Buf head_logits_, head_losses_, dscale_, row_scale_, dxn_, capped_, part_acc_, part_ml_;
-  Buf s_a_, s_b_, dx_pre_, dxb_, dx0_, dlam_, s_dqk_, s_ve_, s_dve_, dh12_, delta_, ds_;
+  Buf s_a_, s_b_, dx_pre_, dxb_, dx0_, s_dqk_, s_ve_, s_dve_, dh12_, delta_, ds_;
   Buf s_sum_[2], s_dpre_[2], s_dxmid_[2], s_dqkv_[2], s_dx_[2];
   std::vector<LayerBufs> layers_;
   // optimizer

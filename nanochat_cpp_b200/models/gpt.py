@@ -392,15 +392,11 @@ class GPT:
                 dh = ops.linear_dgrad(dqkv[:, qd:qd + kd], self._w(i, "attn.c_k"), residual=dh)
                 dh = ops.linear_dgrad(dqkv[:, qd + kd:], self._w(i, "attn.c_v"), residual=dh)
             del dqkv, dv2, dv4
-            if dh12 is not None:
-                dh = ops.add_cols(dh, dh12)
-            dxr = ops.rmsnorm_bwd(s["xr"], dh, s["rstd1"], residual=dx_mid)
+            # norm backward, blend backward, the gate's 12 columns and both scalar gradients in one launch
+            dx, dx0 = ops.norm_blend_bwd(s["xr"], dh, s["rstd1"], dx_mid, s["x"], x0, self._lam("resid_lambdas", i),
+                                         self._lam("x0_lambdas", i), P.g("resid_lambdas")[i:i + 1],
+                                         P.g("x0_lambdas")[i:i + 1], dx0_acc=dx0, extra=dh12)
             del dh, dx_mid, h
-            dx, dx0, dlr, dl0 = ops.blend_bwd(dxr, s["x"], x0, self._lam("resid_lambdas", i),
-                                              self._lam("x0_lambdas", i), dx0_acc=dx0)
-            P.g("resid_lambdas")[i] += dlr
-            P.g("x0_lambdas")[i] += dl0
-            del dxr
             save["layers"][i] = None
             if self.on_layer_grads_ready is not None:
                 # a layer is announced one layer late, once its side-stream products are known to be complete,

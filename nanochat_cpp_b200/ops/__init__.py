@@ -119,7 +119,7 @@ def _dispatch(name: str) -> Callable:
 _NAMES = [
     "linear_fwd", "linear_relu2_fwd", "linear_relu2_act_fwd", "linear_dgrad_relu2_act", "linear_dgrad", "linear_dgrad_relu2", "linear_wgrad",
     "linear_wgrad_relu2", "rmsnorm_fwd", "rmsnorm_apply", "rmsnorm_bwd", "add", "add_cols", "concat_qkv",
-    "backout_fwd", "backout_bwd", "blend_norm_fwd", "blend_bwd", "qk_prep_fwd", "qk_prep_bwd",
+    "backout_fwd", "backout_bwd", "blend_norm_fwd", "blend_bwd", "norm_blend_bwd", "qk_prep_fwd", "qk_prep_bwd",
     "attention_fwd", "attention_bwd", "value_gate_fwd", "value_gate_bwd", "smear_fwd", "smear_bwd",
     "embedding_fwd", "embedding_bwd", "embedding_order", "classifier_fwd_bwd", "adamw_update", "muon_update",
     "grad_norm_and_clip", "kv_append", "paged_decode_attention", "quantize_fp8", "gemm_scaled_fp8",

@@ -245,6 +245,14 @@ def blend_bwd(dxr, x, x0, lam_r, lam_0, dx0_acc=None):
     return dx, dx0, dlam[0], dlam[1]
 
 
+def norm_blend_bwd(xr, dh, rstd, residual, x, x0, lam_r, lam_0, g_lam_r, g_lam_0, dx0_acc=None, extra=None):
+    """One launch for add_cols + rmsnorm_bwd + blend_bwd + the two scalar-gradient adds (see ops.ref)."""
+    accumulate = dx0_acc is not None
+    dx0 = dx0_acc if accumulate else torch.empty_like(x)
+    dx = _C.norm_blend_bwd(xr, dh, rstd, residual, extra, x, x0, lam_r, lam_0, dx0, accumulate, g_lam_r, g_lam_0)
+    return dx.view_as(x), dx0
+
+
 def _fused_heads(a, b):
     """If `b` ([B,T,Hb,D]) starts right after the heads of `a` ([B,T,Ha,D]) in the same token rows, return
     the [B,T,Ha+Hb,D] view covering both, else None."""

@@ -185,6 +185,28 @@ def blend_bwd(dxr, x, x0, lam_r, lam_0, dx0_acc=None):
     return dx, dx0, dlr, dl0
 
 
+def norm_blend_bwd(xr, dh, rstd, residual, x, x0, lam_r, lam_0, g_lam_r, g_lam_0, dx0_acc=None, extra=None):
+    """Backward of h = rmsnorm(xr) with xr = lam_r * x + lam_0 * x0, as one operator: the definition is the chain
+    add_cols -> rmsnorm_bwd -> blend_bwd, except that dxr is not rounded to the compute dtype in between. The scalar
+    gradients are added into `g_lam_r` / `g_lam_0` (one-element views of the gradient buffer). Returns (dx, dx0)."""
+    if extra is not None:
+        dh = add_cols(dh.clone(), extra)
+    dim = xr.shape[-1]
+    acc = _acc(xr)
+    dot = (xr.to(acc) * dh.to(acc)).sum(-1, keepdim=True).float()
+    r = rstd.unsqueeze(-1)
+    dxr = r * dh.float() - (r * r * r * dot * (1.0 / dim)) * xr.float() + residual.float()
+    g_lam_r += (dxr.to(acc) * x.to(acc).view_as(dxr)).sum().float()
+    g_lam_0 += (dxr.to(acc) * x0.to(acc).view_as(dxr)).sum().float()
+    dx = (lam_r.float() * dxr).to(x.dtype).view_as(x)
+    if dx0_acc is None:
+        dx0 = (lam_0.float() * dxr).to(x.dtype).view_as(x)
+    else:
+        dx0_acc.copy_((dx0_acc.float().view_as(dxr) + lam_0.float() * dxr).to(x.dtype).view_as(dx0_acc))
+        dx0 = dx0_acc
+    return dx, dx0
+
+
 # --------------------------------------------------------------------------
 # Rotary tables and QK preparation: per-head RMSNorm -> RoPE (half split) -> scale
 # --------------------------------------------------------------------------

@@ -187,3 +187,33 @@ def test_embedding_bwd_sorted_is_exact_and_reproducible(tokens, vocab, dim):
     K.embedding_bwd(ids, wide[:, :dim], dt, order=order)
     want = ref.embedding_bwd(ids, wide[:, :dim], torch.zeros(vocab, dim, device="cuda", dtype=torch.float64)).float()
     torch.testing.assert_close(dt, want, rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("rows,dim,with_extra,accumulate", [(37, 1280, True, True), (64, 768, False, False),
+                                                            (130, 256, True, False), (9, 64, False, True)])
+def test_norm_blend_backward_fused(rows, dim, with_extra, accumulate):
+    """add_cols + rmsnorm_bwd + blend_bwd + scalar-gradient adds in one launch, against the same chain in fp32."""
+    from gpu_check import close_elementwise
+    K = _K()
+    x, x0 = _r(rows, dim), _r(rows, dim)
+    lam_r, lam_0 = torch.tensor(0.9, device="cuda"), torch.tensor(0.2, device="cuda")
+    xr = (lam_r * x.float() + lam_0 * x0.float()).to(torch.bfloat16)
+    _, rstd = ref.rmsnorm_fwd(xr)
+    dh, res = _r(rows, dim), _r(rows, dim)
+    extra = torch.randn(rows, 12, device="cuda") if with_extra else None
+    base = _r(rows, dim) if accumulate else None
+    g = torch.tensor([0.5, -0.25], device="cuda")
+    gr = g.clone()
+    want_dx, want_dx0 = ref.norm_blend_bwd(xr, dh, rstd, res, x, x0, lam_r, lam_0, gr[0:1], gr[1:2],
+                                           dx0_acc=base.clone() if accumulate else None, extra=extra)
+    acc = base.clone() if accumulate else None
+    dh_before = dh.clone()
+    dx, dx0 = K.norm_blend_bwd(xr, dh, rstd, res, x, x0, lam_r, lam_0, g[0:1], g[1:2], dx0_acc=acc, extra=extra)
+    rms = want_dx.float().square().mean().sqrt().item()
+    close_elementwise(dx, want_dx, rtol=2.0 ** -7, atol=2.0 ** -8 * rms, name="dx")
+    close_elementwise(dx0, want_dx0, rtol=2.0 ** -7, atol=2.0 ** -7 * want_dx0.float().abs().mean().item(), name="dx0")
+    assert torch.allclose(g, gr, rtol=2e-4, atol=1e-2), (g, gr)
+    assert torch.equal(dh, dh_before)                     # dh is an input here (the unfused add_cols wrote into it)
+    if accumulate:
+        assert dx0.data_ptr() == acc.data_ptr()
+    K.check_status()
