@@ -119,6 +119,8 @@ def _train_parser(sub):
     ap.add_argument("--synthetic", action="store_true", help="Zipf token stream instead of parquet shards")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--grad-accum", type=int, default=1)
+    ap.add_argument("--cuda-graph", default="auto", choices=["auto", "on", "off"],
+                    help="replay micro-batches from a CUDA graph (auto: launch-bound shapes with grad-accum >= 2)")
     ap.add_argument("--num-iterations", type=int, default=100)
     ap.add_argument("--log-every", type=int, default=10)
     ap.add_argument("--eval-every", type=int, default=0)
@@ -178,6 +180,7 @@ def cmd_train(a) -> int:
                                            muon_momentum_start=a.muon_momentum_start,
                                            muon_momentum_peak=a.muon_momentum_peak,
                                            muon_momentum_final=a.muon_momentum_final))
+    tc.cuda_graph = getattr(a, "cuda_graph", "auto")
     if a.hw_check == "on" or (a.hw_check == "auto" and dev.type == "cuda"):
         from .hwgate import run_hardware_gate
         ok, report = run_hardware_gate(dev)

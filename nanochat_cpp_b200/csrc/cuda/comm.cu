@@ -304,6 +304,33 @@ __global__ void __launch_bounds__(256) grad_reduce_local_kernel(float* __restric
 // Eight parameters per thread: the bf16 results leave as ONE 16-byte store per destination rank. NVLink carries
 // stores as packets with a fixed header, so 16-byte stores move about twice the payload per packet of the 8-byte
 // stores a four-wide kernel would issue.
+// Stores of an owner's new bf16 parameters into every rank's buffer: one plain store per rank through its peer
+// pointer, or, when the buffer has an NVLink multicast address (values.mc), ONE multimem.st: the switch replicates it
+// to every rank, this one included, so the bytes on this GPU's links drop from (world - 1) x to 1 x. The flag that
+// publishes the data is a release store issued by a later kernel on the same stream, as for the plain stores.
+// (multimem.st has no 2-byte form: single odd elements always go through the peer pointers.)
+__device__ __forceinline__ void store_all16(const PeerPtrs& values, int world, long long elem, const uint4& w) {
+  if (values.mc != nullptr) {
+    __nv_bfloat16* a = static_cast<__nv_bfloat16*>(values.mc) + elem;
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "r"(w.x), "r"(w.y), "r"(w.z),
+                 "r"(w.w)
+                 : "memory");
+    return;
+  }
+  for (int k = 0; k < world; ++k) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(values.p[k]) + elem) = w;
+}
+__device__ __forceinline__ void store_all4(const PeerPtrs& values, int world, long long elem, uint32_t w) {
+  if (values.mc != nullptr) {
+    __nv_bfloat16* a = static_cast<__nv_bfloat16*>(values.mc) + elem;
+    asm volatile("multimem.st.relaxed.sys.global.bf16x2 [%0], %1;" ::"l"(a), "r"(w) : "memory");
+    return;
+  }
+  for (int k = 0; k < world; ++k) *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(values.p[k]) + elem) = w;
+}
+__device__ __forceinline__ void store_all2(const PeerPtrs& values, int world, long long elem, __nv_bfloat16 h) {
+  for (int k = 0; k < world; ++k) (static_cast<__nv_bfloat16*>(values.p[k]) + elem)[0] = h;
+}
+
 __global__ void __launch_bounds__(256) adamw_push_kernel(float* __restrict__ master, PeerPtrs values,
                                                          long long value_offset, int world,
                                                          const float* __restrict__ grad, float* __restrict__ m,
@@ -345,8 +372,7 @@ __global__ void __launch_bounds__(256) adamw_push_kernel(float* __restrict__ mas
     uint4 w;
     w.x = pack_bf16x2(pp[0], pp[1]), w.y = pack_bf16x2(pp[2], pp[3]);
     w.z = pack_bf16x2(pp[4], pp[5]), w.w = pack_bf16x2(pp[6], pp[7]);
-    for (int r = 0; r < world; ++r)
-      reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(values.p[r]) + value_offset)[i] = w;
+    store_all16(values, world, value_offset + i * 8, w);
   }
   if (blockIdx.x == 0) {
     for (long long i = nv * 8 + threadIdx.x; i < n; i += blockDim.x) {
@@ -358,7 +384,7 @@ __global__ void __launch_bounds__(256) adamw_push_kernel(float* __restrict__ mas
       v[i] = vi;
       pi -= step_size * (mi / (sqrtf(vi * inv_bias2) + eps));
       master[i] = pi;
-      for (int r = 0; r < world; ++r) (static_cast<__nv_bfloat16*>(values.p[r]) + value_offset)[i] = __float2bfloat16_rn(pi);
+      store_all2(values, world, value_offset + i, __float2bfloat16_rn(pi));
     }
   }
 }
@@ -405,13 +431,11 @@ __global__ void __launch_bounds__(256) muon_apply_push_kernel(float* __restrict_
       reinterpret_cast<float4*>(master)[2 * i + 1] = make_float4(q[4], q[5], q[6], q[7]);
       uint4 w;
       w.x = pack_bf16x2(q[0], q[1]), w.y = pack_bf16x2(q[2], q[3]), w.z = pack_bf16x2(q[4], q[5]), w.w = pack_bf16x2(q[6], q[7]);
-      for (int k = 0; k < world; ++k)
-        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(values.p[k]) + value_offset)[i] = w;
+      store_all16(values, world, value_offset + i * 8, w);
     } else {
       reinterpret_cast<float2*>(master)[i] = make_float2(q[0], q[1]);
       const uint32_t w = pack_bf16x2(q[0], q[1]);
-      for (int k = 0; k < world; ++k)
-        reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(values.p[k]) + value_offset)[i] = w;
+      store_all4(values, world, value_offset + i * 2, w);
     }
   }
 }
@@ -453,8 +477,7 @@ __global__ void __launch_bounds__(256) muon_apply_push_batched_kernel(const long
     reinterpret_cast<float4*>(master)[2 * i + 1] = make_float4(q[4], q[5], q[6], q[7]);
     uint4 w;
     w.x = pack_bf16x2(q[0], q[1]), w.y = pack_bf16x2(q[2], q[3]), w.z = pack_bf16x2(q[4], q[5]), w.w = pack_bf16x2(q[6], q[7]);
-    for (int k = 0; k < world; ++k)
-      reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(values.p[k]) + value_offset)[i] = w;
+    store_all16(values, world, value_offset + i * 8, w);
   }
 }
 

@@ -11,6 +11,7 @@ constexpr int kMaxRanks = 8;
 
 struct PeerPtrs {
   void* p[kMaxRanks];
+  void* mc = nullptr;   // NVLink multicast address of the same (symmetric) buffer, or null: see store_all16 in comm.cu
 };
 
 struct Segment {

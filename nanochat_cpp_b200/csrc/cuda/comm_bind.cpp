@@ -11,11 +11,12 @@ namespace {
 using torch::Tensor;
 inline cudaStream_t cur() { return at::cuda::getCurrentCUDAStream(); }
 
-nc::PeerPtrs to_peers(const std::vector<int64_t>& ptrs) {
+nc::PeerPtrs to_peers(const std::vector<int64_t>& ptrs, int64_t multicast_ptr = 0) {
   TORCH_CHECK(!ptrs.empty() && ptrs.size() <= nc::kMaxRanks, "between 1 and 8 ranks are supported");
   nc::PeerPtrs p;
   for (int i = 0; i < nc::kMaxRanks; ++i) p.p[i] = nullptr;
   for (size_t i = 0; i < ptrs.size(); ++i) p.p[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(ptrs[i]));
+  p.mc = reinterpret_cast<void*>(static_cast<uintptr_t>(multicast_ptr));
   return p;
 }
 
@@ -70,10 +71,10 @@ void comm_grad_reduce_local(Tensor& grad, const Tensor& recv, int64_t recv_strid
 
 void comm_adamw_push(Tensor& master, const std::vector<int64_t>& value_ptrs, int64_t value_offset, const Tensor& grad,
                      Tensor& m, Tensor& v, double lr, double beta1, double beta2, double eps, double weight_decay,
-                     int64_t step, const c10::optional<Tensor>& grad_scale) {
+                     int64_t step, const c10::optional<Tensor>& grad_scale, int64_t multicast_ptr) {
   const c10::cuda::CUDAGuard g(master.device());
   TORCH_CHECK(master.is_contiguous() && grad.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw_push");
-  nc::comm_adamw_push(master.data_ptr<float>(), to_peers(value_ptrs), value_offset,
+  nc::comm_adamw_push(master.data_ptr<float>(), to_peers(value_ptrs, multicast_ptr), value_offset,
                       static_cast<int>(value_ptrs.size()), grad.data_ptr<float>(), m.data_ptr<float>(),
                       v.data_ptr<float>(), master.numel(), lr, beta1, beta2, eps, weight_decay, step,
                       grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, cur());
@@ -81,11 +82,11 @@ void comm_adamw_push(Tensor& master, const std::vector<int64_t>& value_ptrs, int
 
 void comm_muon_apply_push(Tensor& master, const std::vector<int64_t>& value_ptrs, int64_t value_offset,
                           const Tensor& xb, const Tensor& scale0, const Tensor& line_scale, bool lines_are_rows,
-                          double lr, double wd) {
+                          double lr, double wd, int64_t multicast_ptr) {
   const c10::cuda::CUDAGuard g(master.device());
   TORCH_CHECK(master.dim() == 2 && master.is_contiguous() && xb.is_contiguous() && master.size(1) % 2 == 0,
               "muon_apply_push");
-  nc::comm_muon_apply_push(master.data_ptr<float>(), to_peers(value_ptrs), value_offset,
+  nc::comm_muon_apply_push(master.data_ptr<float>(), to_peers(value_ptrs, multicast_ptr), value_offset,
                            static_cast<int>(value_ptrs.size()), reinterpret_cast<const __nv_bfloat16*>(xb.data_ptr()),
                            scale0.data_ptr<float>(), line_scale.data_ptr<float>(), lines_are_rows, master.size(0),
                            master.size(1), lr, wd, cur());
@@ -93,7 +94,8 @@ void comm_muon_apply_push(Tensor& master, const std::vector<int64_t>& value_ptrs
 
 void comm_muon_apply_push_batched(const Tensor& master_ptrs, const Tensor& value_offsets,
                                   const std::vector<int64_t>& value_ptrs, const Tensor& xb, const Tensor& scale0,
-                                  const Tensor& line_scale, bool lines_are_rows, double lr, double wd) {
+                                  const Tensor& line_scale, bool lines_are_rows, double lr, double wd,
+                                  int64_t multicast_ptr) {
   const c10::cuda::CUDAGuard g(xb.device());
   TORCH_CHECK(xb.dim() == 3 && xb.is_contiguous() && xb.size(2) % 8 == 0 && master_ptrs.numel() == xb.size(0) &&
                   value_offsets.numel() == xb.size(0) && master_ptrs.scalar_type() == torch::kInt64 &&
@@ -101,7 +103,7 @@ void comm_muon_apply_push_batched(const Tensor& master_ptrs, const Tensor& value
               "muon_apply_push_batched");
   nc::comm_muon_apply_push_batched(reinterpret_cast<const long long*>(master_ptrs.data_ptr<int64_t>()),
                                    reinterpret_cast<const long long*>(value_offsets.data_ptr<int64_t>()),
-                                   to_peers(value_ptrs), static_cast<int>(value_ptrs.size()),
+                                   to_peers(value_ptrs, multicast_ptr), static_cast<int>(value_ptrs.size()),
                                    reinterpret_cast<const __nv_bfloat16*>(xb.data_ptr()), scale0.data_ptr<float>(),
                                    line_scale.data_ptr<float>(), lines_are_rows, xb.size(0), xb.size(1), xb.size(2), lr,
                                    wd, cur());
@@ -116,7 +118,15 @@ void register_comm(pybind11::module_& m) {
   m.def("comm_reduce_pull", &comm_reduce_pull);
   m.def("comm_grad_push", &comm_grad_push);
   m.def("comm_grad_reduce_local", &comm_grad_reduce_local);
-  m.def("comm_adamw_push", &comm_adamw_push);
-  m.def("comm_muon_apply_push", &comm_muon_apply_push);
-  m.def("comm_muon_apply_push_batched", &comm_muon_apply_push_batched);
+  m.def("comm_adamw_push", &comm_adamw_push, pybind11::arg("master"), pybind11::arg("value_ptrs"),
+        pybind11::arg("value_offset"), pybind11::arg("grad"), pybind11::arg("m"), pybind11::arg("v"), pybind11::arg("lr"),
+        pybind11::arg("beta1"), pybind11::arg("beta2"), pybind11::arg("eps"), pybind11::arg("weight_decay"),
+        pybind11::arg("step"), pybind11::arg("grad_scale"), pybind11::arg("multicast_ptr") = 0);
+  m.def("comm_muon_apply_push", &comm_muon_apply_push, pybind11::arg("master"), pybind11::arg("value_ptrs"),
+        pybind11::arg("value_offset"), pybind11::arg("xb"), pybind11::arg("scale0"), pybind11::arg("line_scale"),
+        pybind11::arg("lines_are_rows"), pybind11::arg("lr"), pybind11::arg("wd"), pybind11::arg("multicast_ptr") = 0);
+  m.def("comm_muon_apply_push_batched", &comm_muon_apply_push_batched, pybind11::arg("master_ptrs"),
+        pybind11::arg("value_offsets"), pybind11::arg("value_ptrs"), pybind11::arg("xb"), pybind11::arg("scale0"),
+        pybind11::arg("line_scale"), pybind11::arg("lines_are_rows"), pybind11::arg("lr"), pybind11::arg("wd"),
+        pybind11::arg("multicast_ptr") = 0);
 }

@@ -61,6 +61,11 @@ def launch_count() -> int:
     """Number of this package's kernels launched so far in this process."""
     return _C.launches
 
+
+def add_launches(n: int) -> None:
+    """Account for kernels that a CUDA-graph replay launched (the wrappers only see them at capture time)."""
+    _C.launches += int(n)
+
 EPI_BF16, EPI_BF16_RES, EPI_RELU2, EPI_DRELU2, EPI_F32 = 0, 1, 2, 3, 4
 
 
@@ -88,6 +93,12 @@ _pending_weight_wait = None
 def set_weight_wait(flags, value) -> None:
     global _pending_weight_wait
     _pending_weight_wait = (flags, int(value))
+
+
+def clear_weight_wait() -> None:
+    """Drop the pending in-GEMM wait (the caller has enqueued an explicit wait kernel instead)."""
+    global _pending_weight_wait
+    _pending_weight_wait = None
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, epi=EPI_BF16, out=None, r=None, out2=None, alpha=1.0, beta=0.0,

@@ -85,6 +85,12 @@ class FusedTransport:
         self.push_stream = torch.cuda.Stream(device=self.device)
         import os
         self.reduce_mode = os.environ.get("NANOCHAT_DP_REDUCE", "push")     # push (bf16, stores) | pull (fp32, loads)
+        # how an owner's new parameters reach the other ranks: "peer" = one 16-byte store per rank through its peer
+        # pointer; "multimem" = one multimem.st to the buffer's NVLink multicast address, replicated by the switch
+        # (this GPU's outbound bytes drop from (world - 1) x to 1 x). Opt-in; falls back where the buffer has no
+        # multicast mapping.
+        self.push_mode = os.environ.get("NANOCHAT_DP_PUSH", "peer")
+        self._push_targets = None
         self.recv: Optional[SymmetricBuffer] = None
         self.recv_stride = 0
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
@@ -250,14 +256,30 @@ class FusedTransport:
         return self.flags.tensor[slot * self.world:(slot + 1) * self.world]
 
     # ------------------------------------------------------------------ pushing updates
+    def push_targets(self):
+        """(peer pointers of the parameter buffer, its multicast address or 0)."""
+        if self._push_targets is None:
+            self._push_targets = (self.value.ptrs, 0)
+            if self.push_mode == "multimem":
+                h = self.value.handle
+                mc = int(getattr(h, "multicast_ptr", 0) or 0)
+                if mc != 0:
+                    self._push_targets = (self.value.ptrs, mc + int(getattr(h, "offset", 0) or 0))
+                elif self.rank == 0:
+                    print("[dp] NANOCHAT_DP_PUSH=multimem: the parameter buffer has no multicast mapping; "
+                          "using peer stores", flush=True)
+        return self._push_targets
+
     def adamw_push(self, master, offset: int, grad, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale):
         from ..ops import cuda as K
         gs = grad_scale.reshape(1) if isinstance(grad_scale, torch.Tensor) else None
-        K._C.comm_adamw_push(master, self.value.ptrs, offset, grad, m, v, lr, beta1, beta2, eps, weight_decay, step, gs)
+        ptrs, mc = self.push_targets()
+        K._C.comm_adamw_push(master, ptrs, offset, grad, m, v, lr, beta1, beta2, eps, weight_decay, step, gs, mc)
 
     def muon_apply_push(self, master, offset: int, xb, scale0, line_scale, lines_are_rows: bool, lr: float, wd: float):
         from ..ops import cuda as K
-        K._C.comm_muon_apply_push(master, self.value.ptrs, offset, xb, scale0, line_scale, lines_are_rows, lr, wd)
+        ptrs, mc = self.push_targets()
+        K._C.comm_muon_apply_push(master, ptrs, offset, xb, scale0, line_scale, lines_are_rows, lr, wd, mc)
 
     def push_span(self, offset: int, count: int) -> None:
         """Copy a (small) span of this rank's parameter buffer to every peer with ordinary peer copies."""
@@ -290,8 +312,9 @@ class Pusher:
         def batched(scratch, masters, X, scale, line_scale, lines_are_rows, lr, wd):
             from ..ops import cuda as K
             offs = scratch.table("voff", None, values=tuple(s.offset for s in specs))
-            K._C.comm_muon_apply_push_batched(scratch.table("m", masters), offs, t.value.ptrs, X, scale, line_scale,
-                                              lines_are_rows, lr, wd)
+            ptrs, mc = t.push_targets()
+            K._C.comm_muon_apply_push_batched(scratch.table("m", masters), offs, ptrs, X, scale, line_scale,
+                                              lines_are_rows, lr, wd, mc)
         if all(s.offset % 8 == 0 for s in specs):
             apply.batched = batched
         return apply

@@ -418,5 +418,7 @@ def register(sub) -> None:
     ap.set_defaults(fn=cmd_fixtures)
     ap = sub.add_parser("lint", help="house rules no compiler checks")
     ap.set_defaults(fn=cmd_lint)
+    ap = sub.add_parser("gates", help="consistency gates: C ABI header / library / callers, stdlib isolation, fixtures, lint")
+    ap.set_defaults(fn=lambda a: __import__("nanochat_cpp_b200.gates", fromlist=["main"]).main([]))
     ap = sub.add_parser("shutdown", help="stop live queue workers and session supervisors")
     ap.set_defaults(fn=cmd_shutdown)

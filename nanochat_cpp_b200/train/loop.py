@@ -36,6 +36,9 @@ class TrainConfig:
     dtype: str = "bf16"
     head_chunk_rows: int = 11264
     fp8: object = False          # False, True / "mx", or "block" (see models.GPT)
+    # "auto": replay a micro-batch's forward + backward from a CUDA graph when the step is bound by launch rate
+    # (several small micro-batches); "on" / "off" force it. Never the headline path of a large single micro-batch.
+    cuda_graph: str = "auto"
     optim: OptimizerConfig = field(default_factory=OptimizerConfig)
     sched: SchedulerConfig = field(default_factory=SchedulerConfig)
 
@@ -61,6 +64,8 @@ class Trainer:
         if dp is not None:
             dp.attach(self.model, self.optimizer)
         self.step_count = 0
+        self._graphs = {}
+        self.graph_replays = 0
         self.last_loss: Optional[torch.Tensor] = None
         self.time_phases = False      # set for one step by the loop on logging steps
         self._phase_events = None
@@ -89,7 +94,11 @@ class Trainer:
             if timed:
                 ev["micro"][k].record()
                 m.phase_event = ev["fwd_end"][k]
-            loss = m.forward_backward(tokens, targets, grad_scale=scale)
+            loss = None
+            if self._graphable(k, accum, timed, tokens):
+                loss = self._micro_graphed(tokens, targets, scale)
+            if loss is None:
+                loss = m.forward_backward(tokens, targets, grad_scale=scale)
             total = loss if total is None else total + loss
         m.phase_event = None
         if timed:
@@ -107,6 +116,65 @@ class Trainer:
             m.refresh_fp8()
         self.last_loss = total / accum
         return self.last_loss
+
+    # ------------------------------------------------------------------ CUDA-graph micro-batches
+    def _graphable(self, k: int, accum: int, timed: bool, tokens: torch.Tensor) -> bool:
+        """A micro-batch can be replayed from a graph when nothing in it changes from step to step: no phase timers,
+        no fp8 re-quantisation, and under data parallelism not the last micro-batch (its backward launches the
+        bucket reductions, whose flag values count steps)."""
+        mode = self.tc.cuda_graph
+        if mode == "off" or self.device.type != "cuda" or timed or self.model.fp8:
+            return False
+        if self.dp is not None and k == accum - 1:
+            return False
+        if mode == "auto":
+            # launch-bound shapes only: a few thousand kernels of a few microseconds each per micro-batch
+            return accum >= 2 and tokens.numel() * self.cfg.hidden_dim <= (1 << 24)
+        return True
+
+    def _micro_graphed(self, tokens: torch.Tensor, targets: torch.Tensor, scale: float):
+        """Forward + backward of one micro-batch replayed from a CUDA graph (captured on the second step, after an
+        eager step has warmed every cache). Gradients accumulate into the flat buffer exactly as in the eager call.
+        Returns None when this call has to run eagerly."""
+        from ..ops import cuda as K
+        if self.step_count < 1:
+            return None
+        f = getattr(self.dp, "fused", None) if self.dp is not None else None
+        if f is not None and self.step_count > 0:
+            # the wait for the pushed matrices normally rides in the first GEMM; a replayed graph cannot carry this
+            # step's flag value, so it is enqueued as its own (bounded) wait kernel
+            f.wait(f.slot_muon, self.step_count)
+            K.clear_weight_wait()
+        key = (tuple(tokens.shape), tokens.dtype, targets.dtype, float(scale))
+        entry = self._graphs.get(key)
+        if entry is None:
+            if len(self._graphs) >= 2:
+                return None
+            tok_s, tgt_s = tokens.clone(), targets.clone()
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            n0 = K.launch_count()
+            try:
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                    loss_s = self.model.forward_backward(tok_s, tgt_s, grad_scale=scale)
+            except Exception as e:   # capture is an optimisation: fall back to eager launches for good
+                self.tc.cuda_graph = "off"
+                self._graphs.clear()
+                torch.cuda.synchronize(self.device)
+                if self._rank0():
+                    print(f"[train] CUDA-graph capture of the micro-batch failed ({type(e).__name__}: {e}); "
+                          "continuing with eager launches", flush=True)
+                return None
+            entry = (g, tok_s, tgt_s, loss_s, K.launch_count() - n0)
+            K.add_launches(-entry[4])       # capture enqueued nothing; replays are counted below
+            self._graphs[key] = entry
+        g, tok_s, tgt_s, loss_s, kernels = entry
+        tok_s.copy_(tokens)
+        tgt_s.copy_(targets)
+        g.replay()
+        K.add_launches(kernels)
+        self.graph_replays += 1
+        return loss_s.clone()
 
     def wait_for_weights(self) -> None:
         """Under the fused transport the owners push the new bf16 weights into every rank's buffer asynchronously

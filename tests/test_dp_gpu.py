@@ -70,3 +70,21 @@ def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path, transport):
     a, b = torch.load(one)["value"], torch.load(two)["value"]
     rel = float((a - b).norm() / (a.norm() + 1e-12))
     assert rel < 2e-2, rel
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_multicast_parameter_push_matches_peer_stores(tmp_path, monkeypatch):
+    """NANOCHAT_DP_PUSH=multimem: owners publish new parameters with one multimem.st through the NVLink multicast
+    address instead of one store per rank. Same training result as the peer-store path (where the buffer has no
+    multicast mapping the transport says so and uses peer stores, and this test still passes)."""
+    import torch.multiprocessing as mp
+    outs = {}
+    for mode in ("peer", "multimem"):
+        monkeypatch.setenv("NANOCHAT_DP_PUSH", mode)
+        out = str(tmp_path / f"{mode}.pt")
+        mp.spawn(_worker, args=(2, _free_port(), "fused", out), nprocs=2, join=True)
+        outs[mode] = torch.load(out)
+    a, b = outs["peer"]["value"], outs["multimem"]["value"]
+    assert abs(outs["peer"]["loss"] - outs["multimem"]["loss"]) < 5e-2
+    rel = float((a - b).norm() / (a.norm() + 1e-12))
+    assert rel < 2e-2, rel

@@ -43,3 +43,35 @@ def test_deterministic_mode_gives_identical_runs(monkeypatch):
         grads.append((m.params.g("transformer.wte.weight").clone(), m.params.g("value_embeds.1.weight").clone()))
     assert torch.equal(grads[0][0], grads[1][0]) and torch.equal(grads[0][1], grads[1][1])
     assert grads[0][0].abs().sum() > 0
+
+
+def test_graph_replayed_micro_batches_train_like_eager_ones():
+    """Three micro-batches per step, replayed from a CUDA graph from the second step on: the same losses and the same
+    parameters as eager launches (the graph runs the same kernels in the same order), and the launch counter keeps
+    counting the replayed kernels."""
+    from nanochat_cpp_b200.config import Config
+    from nanochat_cpp_b200.ops import cuda as K
+    from nanochat_cpp_b200.train import TrainConfig, Trainer
+    cfg = Config(num_layers=3, num_heads=2, num_kv_heads=1, hidden_dim=256, seq_len=256, vocab_size=1024,
+                 padded_vocab_size=1024, window_pattern="SL")
+    g = torch.Generator().manual_seed(5)
+    data = torch.randint(0, 300, (5, 3, 4, cfg.seq_len + 1), generator=g).cuda()
+    runs = {}
+    for mode in ("off", "on"):
+        tc = TrainConfig(batch=4, grad_accum=3, num_iterations=10, seed=7, cuda_graph=mode)
+        tr = Trainer(cfg, tc, device="cuda")
+        losses, launches = [], []
+        for step in range(5):
+            n0 = K.launch_count()
+            loss = tr.train_step([(data[step, a, :, :-1], data[step, a, :, 1:]) for a in range(3)])
+            losses.append(float(loss))
+            launches.append(K.launch_count() - n0)
+        torch.cuda.synchronize()
+        K.check_status()
+        runs[mode] = (losses, tr.model.params.master.clone(), launches, tr.graph_replays)
+    (l0, p0, n0, r0), (l1, p1, n1, r1) = runs["off"], runs["on"]
+    assert r0 == 0 and r1 == 4 * 3                      # every micro-batch of steps 2..5
+    assert max(abs(a - b) for a, b in zip(l0, l1)) < 2e-3, (l0, l1)
+    assert float((p0 - p1).norm() / p0.norm()) < 1e-2      # atomic sums differ in order from run to run
+    assert n1[1:] == n0[1:]                             # replayed kernels are counted like launched ones
+    assert l1[-1] < l1[0]
