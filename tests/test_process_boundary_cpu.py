@@ -215,3 +215,13 @@ def test_lint_is_clean_and_catches_a_planted_finding(tmp_path):
     (tmp_path / "broken.py").write_text("def f(:\n")
     found = " | ".join(T.lint_findings(str(tmp_path)))
     assert "without the gpu marker" in found and "without --clock-control none" in found and "does not compile" in found
+
+
+def test_consistency_gates_pass_and_see_a_planted_gap(tmp_path):
+    from nanochat_cpp_b200 import gates as G
+    assert G.capi_findings() == [] and G.isolation_findings() == []
+    names = G.header_functions()
+    assert len(names) >= 68 and "nanochat_model_create" in names and "nanochat_generate_multi" in names
+    fake = tmp_path / "capi.h"
+    fake.write_text("int nanochat_init(void);\n/* int nanochat_commented_out(void); */\nint nanochat_not_there(int x);\n")
+    assert G.header_functions(str(fake)) == ["nanochat_init", "nanochat_not_there"]
