@@ -143,6 +143,7 @@ def transports_agree(rank, world, dev):
     """Three untimed steps of a small model from one initialisation on the same data under each transport: the fused
     peer-memory path (bf16 on the wire, fixed rank order) against NCCL reduce-scatter / all-gather (fp32 on the wire).
     Reports the relative distance of the resulting parameters and their agreement across ranks."""
+    import torch
     import torch.distributed as dist
     from nanochat_cpp_b200.config import Config
     from nanochat_cpp_b200.parallel.dp import DataParallel

@@ -5,6 +5,15 @@
 #include <cmath>
 #include <cstring>
 #include <limits>
+#include <chrono>
+#if defined(__GLIBC__)
+#include <malloc.h>
+#endif
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <string>
 
 namespace ncb {
 
@@ -27,6 +36,49 @@ constexpr std::size_t kAlign = 64;
 #define NCB_SIMD_CLONES
 #endif
 
+// Wall-clock totals per named section of the CPU engine, printed at exit when NANOCHAT_CPU_PROFILE=1 (the CPU
+// engine's counterpart of the per-operator profile of the GPU path).
+class SectionTimer {
+ public:
+  explicit SectionTimer(const char* name) : name_(Enabled() ? name : nullptr) {
+    if (name_ != nullptr) start_ = std::chrono::steady_clock::now();
+  }
+  ~SectionTimer() {
+    if (name_ == nullptr) return;
+    const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - start_).count();
+    Table& t = table();
+    std::lock_guard<std::mutex> lock(t.mu);
+    auto& e = t.rows[name_];
+    e.first += ms;
+    e.second += 1;
+  }
+  static bool Enabled() {
+    static const bool on = [] {
+      const char* e = std::getenv("NANOCHAT_CPU_PROFILE");
+      return e != nullptr && e[0] == '1';
+    }();
+    return on;
+  }
+
+ private:
+  struct Table {
+    std::mutex mu;
+    std::map<std::string, std::pair<double, long>> rows;
+    ~Table() {
+      if (rows.empty()) return;
+      std::fprintf(stderr, "[cpu engine] section                 total ms    calls\n");
+      for (const auto& r : rows)
+        std::fprintf(stderr, "[cpu engine] %-22s %10.1f %8ld\n", r.first.c_str(), r.second.first, r.second.second);
+    }
+  };
+  static Table& table() {
+    static Table t;
+    return t;
+  }
+  const char* name_;
+  std::chrono::steady_clock::time_point start_;
+};
+
 NCB_SIMD_CLONES double Dot(const float* a, const float* b, int n) {
   double total = 0.0;
   for (int i0 = 0; i0 < n; i0 += 256) {
@@ -43,52 +95,108 @@ NCB_SIMD_CLONES void Axpy(float g, const float* x, float* y, int n) {
   for (int i = 0; i < n; ++i) y[i] += g * x[i];
 }
 
+// C[M,N] (+)= A[M,K] B[K,N], all row-major: the one product every linear layer and the Newton-Schulz iteration
+// reduce to. The micro-kernel keeps a 6 x 32 block of C in twelve 16-float accumulators and walks K with one
+// broadcast of A per row and two loads of B per step (12 multiply-adds per 2 loads, no horizontal sums). K is cut
+// into chunks of 256 whose float sums are added to C one after the other, which bounds the rounding error the way
+// the per-256 folding of Dot does. Panels of 32 columns of B stay in cache while the row blocks of A stream past.
+typedef float Vf16 __attribute__((vector_size(64), aligned(4), may_alias));   // 16 floats, unaligned access allowed
+
+template <int MR>
+NCB_SIMD_CLONES void Micro32(const float* A, std::size_t lda, const float* B, std::size_t ldb, float* C,
+                             std::size_t ldc, int K, bool accumulate) {
+  Vf16 total[MR][2];
+  for (int r = 0; r < MR; ++r)
+    for (int h = 0; h < 2; ++h)
+      total[r][h] = accumulate ? *reinterpret_cast<const Vf16*>(C + r * ldc + 16 * h) : Vf16{};
+  for (int k0 = 0; k0 < K; k0 += 256) {
+    const int k1 = std::min(K, k0 + 256);
+    Vf16 acc[MR][2];
+    for (int r = 0; r < MR; ++r) acc[r][0] = Vf16{}, acc[r][1] = Vf16{};
+    for (int k = k0; k < k1; ++k) {
+      const Vf16 b0 = *reinterpret_cast<const Vf16*>(B + k * ldb), b1 = *reinterpret_cast<const Vf16*>(B + k * ldb + 16);
+      for (int r = 0; r < MR; ++r) {
+        const float a = A[r * lda + k];     // scalar * vector: the compiler broadcasts
+        acc[r][0] += a * b0;
+        acc[r][1] += a * b1;
+      }
+    }
+    for (int r = 0; r < MR; ++r) total[r][0] += acc[r][0], total[r][1] += acc[r][1];
+  }
+  for (int r = 0; r < MR; ++r)
+    for (int h = 0; h < 2; ++h) *reinterpret_cast<Vf16*>(C + r * ldc + 16 * h) = total[r][h];
+}
+
+// Columns past the last panel of 32 (and any shape too small for a panel): plain loops, same chunking of K.
+void GemmEdge(const float* A, std::size_t lda, const float* B, std::size_t ldb, float* C, std::size_t ldc, int m0,
+              int m1, int n0, int n1, int K, bool accumulate) {
+  for (int m = m0; m < m1; ++m)
+    for (int n = n0; n < n1; ++n) {
+      float total = accumulate ? C[m * ldc + n] : 0.0f;
+      for (int k0 = 0; k0 < K; k0 += 256) {
+        float part = 0.0f;
+        for (int k = k0; k < std::min(K, k0 + 256); ++k) part += A[m * lda + k] * B[k * ldb + n];
+        total += part;
+      }
+      C[m * ldc + n] = total;
+    }
+}
+
+void GemmNN(const float* A, std::size_t lda, const float* B, std::size_t ldb, float* C, std::size_t ldc, int M, int N,
+            int K, bool accumulate) {
+  const int panels = N / 32, blocks = (M + 5) / 6;
+  const long long work = static_cast<long long>(M) * N * K;
+#pragma omp parallel for collapse(2) schedule(static) if (work > 200000)
+  for (int p = 0; p < panels; ++p)
+    for (int b = 0; b < blocks; ++b) {
+      const int m = b * 6, n = p * 32, rows = std::min(6, M - m);
+      const float* a = A + m * lda;
+      const float* bp = B + n;
+      float* c = C + m * ldc + n;
+      switch (rows) {
+        case 6: Micro32<6>(a, lda, bp, ldb, c, ldc, K, accumulate); break;
+        case 5: Micro32<5>(a, lda, bp, ldb, c, ldc, K, accumulate); break;
+        case 4: Micro32<4>(a, lda, bp, ldb, c, ldc, K, accumulate); break;
+        case 3: Micro32<3>(a, lda, bp, ldb, c, ldc, K, accumulate); break;
+        case 2: Micro32<2>(a, lda, bp, ldb, c, ldc, K, accumulate); break;
+        default: Micro32<1>(a, lda, bp, ldb, c, ldc, K, accumulate); break;
+      }
+    }
+  if (panels * 32 < N) GemmEdge(A, lda, B, ldb, C, ldc, 0, M, panels * 32, N, K, accumulate);
+}
+
+void TransposeInto(const float* src, int rows, int cols, std::vector<float>* dst) {   // dst[cols, rows]
+  dst->resize(static_cast<std::size_t>(rows) * cols);
+  float* d = dst->data();
+#pragma omp parallel for schedule(static) if (static_cast<long long>(rows) * cols > 65536)
+  for (int c0 = 0; c0 < cols; c0 += 32)
+    for (int r = 0; r < rows; ++r)
+      for (int c = c0; c < std::min(cols, c0 + 32); ++c)
+        d[static_cast<std::size_t>(c) * rows + r] = src[static_cast<std::size_t>(r) * cols + c];
+}
+
 // y[M,N] = x[M,K] w[N,K]^T (+ residual)
 void Linear(const float* x, const float* w, float* y, int M, int N, int K, const float* residual = nullptr) {
-#pragma omp parallel for schedule(static) if (static_cast<long long>(M) * N * K > 200000)
-  for (int m = 0; m < M; ++m) {
-    const float* xr = x + static_cast<std::size_t>(m) * K;
-    for (int n = 0; n < N; ++n) {
-      const std::size_t i = static_cast<std::size_t>(m) * N + n;
-      y[i] = static_cast<float>(Dot(xr, w + static_cast<std::size_t>(n) * K, K)) + (residual ? residual[i] : 0.0f);
-    }
+  if (M == 1) {   // one token (decoding): dot products straight over the rows of w, nothing to transpose
+#pragma omp parallel for schedule(static) if (static_cast<long long>(N) * K > 200000)
+    for (int n = 0; n < N; ++n)
+      y[n] = static_cast<float>(Dot(x, w + static_cast<std::size_t>(n) * K, K)) + (residual ? residual[n] : 0.0f);
+    return;
   }
+  std::vector<float> wt;
+  TransposeInto(w, N, K, &wt);   // [K, N]
+  GemmNN(x, K, wt.data(), N, y, N, M, N, K, false);
+  if (residual != nullptr) Axpy(1.0f, residual, y, M * N);
 }
 // dx[M,K] (+)= dy[M,N] w[N,K]
 void LinearDgrad(const float* dy, const float* w, float* dx, int M, int N, int K, bool accumulate) {
-#pragma omp parallel for schedule(static) if (static_cast<long long>(M) * N * K > 200000)
-  for (int m = 0; m < M; ++m) {
-    float* out = dx + static_cast<std::size_t>(m) * K;
-    if (!accumulate) std::fill(out, out + K, 0.0f);
-    // blocks of 64 output rows of w are summed in float, then added: bounded float error, vector speed
-    std::vector<float> part(static_cast<std::size_t>(K));
-    for (int n0 = 0; n0 < N; n0 += 64) {
-      std::fill(part.begin(), part.end(), 0.0f);
-      const int n1 = std::min(N, n0 + 64);
-      for (int n = n0; n < n1; ++n) {
-        const float g = dy[static_cast<std::size_t>(m) * N + n];
-        if (g != 0.0f) Axpy(g, w + static_cast<std::size_t>(n) * K, part.data(), K);
-      }
-      Axpy(1.0f, part.data(), out, K);
-    }
-  }
+  GemmNN(dy, N, w, K, dx, K, M, K, N, accumulate);
 }
 // gw[N,K] += dy[M,N]^T x[M,K]
 void LinearWgrad(const float* dy, const float* x, float* gw, int M, int N, int K) {
-#pragma omp parallel for schedule(static) if (static_cast<long long>(M) * N * K > 200000)
-  for (int n = 0; n < N; ++n) {
-    std::vector<float> part(static_cast<std::size_t>(K));
-    float* out = gw + static_cast<std::size_t>(n) * K;
-    for (int m0 = 0; m0 < M; m0 += 64) {
-      std::fill(part.begin(), part.end(), 0.0f);
-      const int m1 = std::min(M, m0 + 64);
-      for (int m = m0; m < m1; ++m) {
-        const float g = dy[static_cast<std::size_t>(m) * N + n];
-        if (g != 0.0f) Axpy(g, x + static_cast<std::size_t>(m) * K, part.data(), K);
-      }
-      Axpy(1.0f, part.data(), out, K);
-    }
-  }
+  std::vector<float> dyt;
+  TransposeInto(dy, M, N, &dyt);   // [N, M]
+  GemmNN(dyt.data(), M, x, K, gw, K, N, K, M, true);
 }
 
 // y = x * rstd per row; rstd = 1/sqrt(mean(x^2) + eps)
@@ -201,6 +309,17 @@ struct CpuModel::Saved {
 };
 
 CpuModel::CpuModel(const EngineConfig& cfg) : cfg_(cfg) {
+  // Every step allocates (and frees) its activations: tens of MB in blocks of a few MB. glibc serves such blocks
+  // with mmap and gives them back on free, so every step would fault all of those pages in again (a third of the
+  // step at the small CPU configurations). Keeping them on the heap makes the second step reuse the first one's pages.
+  static const bool heap_tuned = [] {
+#if defined(__GLIBC__)
+    mallopt(M_MMAP_THRESHOLD, 1 << 30);
+    mallopt(M_TRIM_THRESHOLD, 1 << 30);
+#endif
+    return true;
+  }();
+  (void)heap_tuned;
   const int L = cfg.num_layers, C = cfg.hidden_dim, V = cfg.padded_vocab_size;
   auto add = [&](std::string name, std::vector<std::int64_t> shape, int rows, int cols, ParamKind kind, int layer) {
     CpuParam p;
@@ -286,7 +405,9 @@ void CpuModel::InitWeights(std::uint64_t seed) {
 // ---------------------------------------------------------------------------------------------- forward
 namespace {
 
-// causal / windowed GQA attention over full sequences: q [B,T,H,D], k,v [B,T,KV,D] (token-major rows)
+// causal / windowed GQA attention over full sequences: q [B,T,H,D], k,v [B,T,KV,D] (token-major rows).
+// Scores and the weighted sums run through the vectorised Dot / Axpy (float lanes; the softmax sums fold into
+// doubles), one task per (batch, head).
 void Attention(const float* q, const float* k, const float* v, float* o, float* lse, int B, int T, int H, int KV,
                int D, int window_left) {
   const int group = H / KV;
@@ -306,17 +427,16 @@ void Attention(const float* q, const float* k, const float* v, float* o, float* 
           mx = std::max(mx, sc[j]);
         }
         double sum = 0.0;
-        for (int j = first; j <= t; ++j) sum += std::exp(static_cast<double>(sc[j] - mx));
-        const float l = mx + static_cast<float>(std::log(sum));
-        lse[(static_cast<std::size_t>(b) * H + h) * T + t] = l;
-        float* orow = o + ((static_cast<std::size_t>(b) * T + t) * H + h) * D;
-        std::vector<double> acc(static_cast<std::size_t>(D), 0.0);
         for (int j = first; j <= t; ++j) {
-          const double p = std::exp(static_cast<double>(sc[j] - l));
-          const float* vr = v + ((static_cast<std::size_t>(b) * T + j) * KV + kvh) * D;
-          for (int d = 0; d < D; ++d) acc[d] += p * vr[d];
+          sc[j] = std::exp(sc[j] - mx);
+          sum += sc[j];
         }
-        for (int d = 0; d < D; ++d) orow[d] = static_cast<float>(acc[d]);
+        lse[(static_cast<std::size_t>(b) * H + h) * T + t] = mx + static_cast<float>(std::log(sum));
+        const float inv = static_cast<float>(1.0 / sum);
+        float* orow = o + ((static_cast<std::size_t>(b) * T + t) * H + h) * D;
+        std::fill(orow, orow + D, 0.0f);
+        for (int j = first; j <= t; ++j)
+          Axpy(sc[j] * inv, v + ((static_cast<std::size_t>(b) * T + j) * KV + kvh) * D, orow, D);
       }
     }
 }
@@ -326,46 +446,33 @@ void AttentionBwd(const float* q, const float* k, const float* v, const float* o
   const int group = H / KV;
   const float scale = 1.0f / std::sqrt(static_cast<float>(D));
   std::fill(dq, dq + static_cast<std::size_t>(B) * T * H * D, 0.0f);
-  std::vector<double> dkacc(static_cast<std::size_t>(B) * T * KV * D, 0.0), dvacc(dkacc.size(), 0.0);
+  std::fill(dk, dk + static_cast<std::size_t>(B) * T * KV * D, 0.0f);
+  std::fill(dv, dv + static_cast<std::size_t>(B) * T * KV * D, 0.0f);
   // one task per (batch, kv head): the query heads of a group add into the same dK / dV rows
 #pragma omp parallel for collapse(2) schedule(static)
   for (int b = 0; b < B; ++b)
     for (int kvh = 0; kvh < KV; ++kvh)
-    for (int h = kvh * group; h < (kvh + 1) * group; ++h) {
-      for (int t = 0; t < T; ++t) {
-        const std::size_t qi = ((static_cast<std::size_t>(b) * T + t) * H + h) * D;
-        const float* qr = q + qi;
-        const float* dor = dout + qi;
-        const float* orow = o + qi;
-        double delta = 0.0;
-        for (int d = 0; d < D; ++d) delta += static_cast<double>(dor[d]) * orow[d];
-        const float l = lse[(static_cast<std::size_t>(b) * H + h) * T + t];
-        const int first = window_left < 0 ? 0 : std::max(0, t - window_left);
-        std::vector<double> dqacc(static_cast<std::size_t>(D), 0.0);
-        for (int j = first; j <= t; ++j) {
-          const std::size_t ki = ((static_cast<std::size_t>(b) * T + j) * KV + kvh) * D;
-          const float* kr = k + ki;
-          const float* vr = v + ki;
-          double s = 0.0, dp = 0.0;
-          for (int d = 0; d < D; ++d) {
-            s += static_cast<double>(qr[d]) * kr[d];
-            dp += static_cast<double>(dor[d]) * vr[d];
-          }
-          const double p = std::exp(s * scale - l);
-          const double ds = p * (dp - delta) * scale;
-          for (int d = 0; d < D; ++d) {
-            dqacc[d] += ds * kr[d];
-            dkacc[ki + d] += ds * qr[d];
-            dvacc[ki + d] += p * dor[d];
+      for (int h = kvh * group; h < (kvh + 1) * group; ++h) {
+        for (int t = 0; t < T; ++t) {
+          const std::size_t qi = ((static_cast<std::size_t>(b) * T + t) * H + h) * D;
+          const float* qr = q + qi;
+          const float* dor = dout + qi;
+          const float delta = static_cast<float>(Dot(dor, o + qi, D));
+          const float l = lse[(static_cast<std::size_t>(b) * H + h) * T + t];
+          const int first = window_left < 0 ? 0 : std::max(0, t - window_left);
+          float* dqr = dq + qi;
+          for (int j = first; j <= t; ++j) {
+            const std::size_t ki = ((static_cast<std::size_t>(b) * T + j) * KV + kvh) * D;
+            const float s = static_cast<float>(Dot(qr, k + ki, D));
+            const float dp = static_cast<float>(Dot(dor, v + ki, D));
+            const float p = std::exp(s * scale - l);
+            const float ds = p * (dp - delta) * scale;
+            Axpy(ds, k + ki, dqr, D);
+            Axpy(ds, qr, dk + ki, D);
+            Axpy(p, dor, dv + ki, D);
           }
         }
-        for (int d = 0; d < D; ++d) dq[qi + d] = static_cast<float>(dqacc[d]);
       }
-    }
-  for (std::size_t i = 0; i < dkacc.size(); ++i) {
-    dk[i] = static_cast<float>(dkacc[i]);
-    dv[i] = static_cast<float>(dvacc[i]);
-  }
 }
 
 inline float Sigmoid(float x) { return 1.0f / (1.0f + std::exp(-x)); }
@@ -383,6 +490,7 @@ void CpuModel::Trunk(const int* tokens, int B, int T, Saved* sv, std::vector<flo
   for (int m = 0; m < M; ++m) sv->pos[m] = m % T;
   BuildRope(T, D, c.rope_base, 0, &sv->cosv, &sv->sinv);
   // embedding -> norm -> smear
+  SectionTimer t_embed("fwd embed+smear");
   const float* wte = P("transformer.wte.weight");
   sv->emb_raw.resize(static_cast<std::size_t>(M) * C);
   for (int m = 0; m < M; ++m)
@@ -415,15 +523,22 @@ void CpuModel::Trunk(const int* tokens, int B, int T, Saved* sv, std::vector<flo
     const std::string pf = "transformer.h." + std::to_string(i) + ".";
     s.x = x;
     s.xr.resize(x.size());
-    for (std::size_t j = 0; j < x.size(); ++j) s.xr[j] = lam_r[i] * x[j] + lam_0[i] * sv->x0[j];
-    s.rstd1.resize(M);
-    RmsNorm(s.xr.data(), h.data(), s.rstd1.data(), M, C);
+    {
+      SectionTimer t("fwd blend+norm");
+      for (std::size_t j = 0; j < x.size(); ++j) s.xr[j] = lam_r[i] * x[j] + lam_0[i] * sv->x0[j];
+      s.rstd1.resize(M);
+      RmsNorm(s.xr.data(), h.data(), s.rstd1.data(), M, C);
+    }
     s.q_pre.resize(static_cast<std::size_t>(M) * QD);
     s.k_pre.resize(static_cast<std::size_t>(M) * KD);
     s.v.resize(static_cast<std::size_t>(M) * KD);
-    Linear(h.data(), P(pf + "attn.c_q.weight"), s.q_pre.data(), M, QD, C);
-    Linear(h.data(), P(pf + "attn.c_k.weight"), s.k_pre.data(), M, KD, C);
-    Linear(h.data(), P(pf + "attn.c_v.weight"), s.v.data(), M, KD, C);
+    {
+      SectionTimer t("fwd linear");
+      Linear(h.data(), P(pf + "attn.c_q.weight"), s.q_pre.data(), M, QD, C);
+      Linear(h.data(), P(pf + "attn.c_k.weight"), s.k_pre.data(), M, KD, C);
+      Linear(h.data(), P(pf + "attn.c_v.weight"), s.v.data(), M, KD, C);
+    }
+    SectionTimer t_gate("fwd gate+qkprep");
     if (c.has_value_embedding(i)) {
       const float* table = P("value_embeds." + std::to_string(i) + ".weight");
       const float* gate_w = P(pf + "attn.ve_gate.weight");
@@ -450,17 +565,30 @@ void CpuModel::Trunk(const int* tokens, int B, int T, Saved* sv, std::vector<flo
     QkPrep(s.k_pre.data(), s.k.data(), M, KV, D, sv->cosv.data(), sv->sinv.data(), sv->pos.data());
     s.attn.resize(static_cast<std::size_t>(M) * QD);
     s.lse.resize(static_cast<std::size_t>(B) * H * T);
-    Attention(s.q.data(), s.k.data(), s.v.data(), s.attn.data(), s.lse.data(), B, T, H, KV, D, c.window_left(i));
+    {
+      SectionTimer t("fwd attention");
+      Attention(s.q.data(), s.k.data(), s.v.data(), s.attn.data(), s.lse.data(), B, T, H, KV, D, c.window_left(i));
+    }
     s.x_mid.resize(x.size());
-    Linear(s.attn.data(), P(pf + "attn.c_proj.weight"), s.x_mid.data(), M, C, QD, s.xr.data());
+    {
+      SectionTimer t("fwd linear");
+      Linear(s.attn.data(), P(pf + "attn.c_proj.weight"), s.x_mid.data(), M, C, QD, s.xr.data());
+    }
     s.rstd2.resize(M);
     RmsNorm(s.x_mid.data(), h.data(), s.rstd2.data(), M, C);
     s.pre.resize(static_cast<std::size_t>(M) * F);
+    SectionTimer t_mlp("fwd mlp");
     Linear(h.data(), P(pf + "mlp.c_fc.weight"), s.pre.data(), M, F, C);
     std::vector<float> act(s.pre.size());
-    for (std::size_t j = 0; j < act.size(); ++j) {
-      const float r = std::max(s.pre[j], 0.0f);
-      act[j] = r * r;
+    {
+      const float* pre = s.pre.data();
+      float* ap = act.data();
+      const long long n_act = static_cast<long long>(act.size());
+#pragma omp parallel for simd schedule(static)
+      for (long long j = 0; j < n_act; ++j) {
+        const float r = std::max(pre[j], 0.0f);
+        ap[j] = r * r;
+      }
     }
     Linear(act.data(), P(pf + "mlp.c_proj.weight"), x.data(), M, C, F, s.x_mid.data());
     if (i == c.backout_layer()) sv->x_backout = x;
@@ -481,8 +609,12 @@ float CpuModel::ForwardLoss(const int* tokens, const int* targets, int B, int T,
   Trunk(tokens, B, T, sv, &sv->xn);
   const int M = B * T, C = cfg_.hidden_dim, V = cfg_.vocab_size, PV = cfg_.padded_vocab_size;
   sv->targets.assign(targets, targets + M);
-  logits_.assign(static_cast<std::size_t>(M) * PV, 0.0f);
-  Linear(sv->xn.data(), value(*Find("lm_head.weight")), logits_.data(), M, PV, C);
+  {
+    SectionTimer t("fwd head linear");
+    logits_.assign(static_cast<std::size_t>(M) * PV, 0.0f);
+    Linear(sv->xn.data(), value(*Find("lm_head.weight")), logits_.data(), M, PV, C);
+  }
+  SectionTimer t_cls("fwd classifier");
   losses_.assign(M, 0.0f);
   double total = 0.0;
   std::int64_t valid = 0;
@@ -492,11 +624,16 @@ float CpuModel::ForwardLoss(const int* tokens, const int* targets, int B, int T,
     if (tg == -1) continue;
     ++valid;
     const float* row = &logits_[static_cast<std::size_t>(m) * PV];
+    // one tanh and one exp per logit: the capped values are kept for the second sweep
+    std::vector<float> z(static_cast<std::size_t>(V));
     float mx = -std::numeric_limits<float>::infinity();
-    for (int j = 0; j < V; ++j) mx = std::max(mx, kSoftcap * std::tanh(row[j] / kSoftcap));
+    for (int j = 0; j < V; ++j) {
+      z[j] = kSoftcap * std::tanh(row[j] / kSoftcap);
+      mx = std::max(mx, z[j]);
+    }
     double sum = 0.0;
-    for (int j = 0; j < V; ++j) sum += std::exp(static_cast<double>(kSoftcap * std::tanh(row[j] / kSoftcap) - mx));
-    const float tz = (tg >= 0 && tg < V) ? kSoftcap * std::tanh(row[tg] / kSoftcap) : 0.0f;
+    for (int j = 0; j < V; ++j) sum += std::exp(z[j] - mx);
+    const float tz = (tg >= 0 && tg < V) ? z[tg] : 0.0f;
     losses_[m] = static_cast<float>(std::log(sum)) + mx - tz;
     total += losses_[m];
   }
@@ -524,17 +661,24 @@ void CpuModel::Backward(float scale, const float* row_weights, double divisor) {
     if (tg == -1) continue;
     const float* row = &logits_[static_cast<std::size_t>(m) * PV];
     float* drow = &dlogits[static_cast<std::size_t>(m) * PV];
+    // one tanh and one exp per logit: tanh is kept in the output row, exp in a scratch row, for the last sweep
+    std::vector<float> e(static_cast<std::size_t>(V));
     float mx = -std::numeric_limits<float>::infinity();
-    for (int j = 0; j < V; ++j) mx = std::max(mx, kSoftcap * std::tanh(row[j] / kSoftcap));
+    for (int j = 0; j < V; ++j) {
+      drow[j] = std::tanh(row[j] / kSoftcap);
+      mx = std::max(mx, kSoftcap * drow[j]);
+    }
     double sum = 0.0;
-    for (int j = 0; j < V; ++j) sum += std::exp(static_cast<double>(kSoftcap * std::tanh(row[j] / kSoftcap) - mx));
+    for (int j = 0; j < V; ++j) {
+      e[j] = std::exp(kSoftcap * drow[j] - mx);
+      sum += e[j];
+    }
     const float inv = static_cast<float>(1.0 / sum);
     const float rw = row_weights ? row_weights[m] : 1.0f;
     for (int j = 0; j < V; ++j) {
-      const float t = std::tanh(row[j] / kSoftcap);
-      const float p = std::exp(kSoftcap * t - mx) * inv;
+      const float t = drow[j];
       const float onehot = (j == tg) ? 1.0f : 0.0f;
-      drow[j] = (p - onehot) * (1.0f - t * t) * rw * dscale;
+      drow[j] = (e[j] * inv - onehot) * (1.0f - t * t) * rw * dscale;
     }
   }
   std::vector<float> dxn(static_cast<std::size_t>(M) * C);
@@ -1052,7 +1196,11 @@ void CpuOptimizer::Step(int step) {
   double ss = 0.0;
   for (const auto& p : model_->params()) {
     const float* g = model_->grad(p);
-    for (std::size_t i = 0; i < p.count; ++i) ss += static_cast<double>(g[i]) * g[i];
+    const long long n = static_cast<long long>(p.count);
+    double part = 0.0;
+#pragma omp parallel for simd schedule(static) reduction(+ : part) if (n > 65536)
+    for (long long i = 0; i < n; ++i) part += static_cast<double>(g[i]) * g[i];
+    ss += part;
   }
   grad_norm_ = static_cast<float>(std::sqrt(ss));
   const float clip = (cfg_.clip > 0.0f && grad_norm_ > cfg_.clip) ? cfg_.clip / grad_norm_ : 1.0f;
@@ -1066,20 +1214,32 @@ void CpuOptimizer::Step(int step) {
       const CpuParam& p = *g.params[k];
       float* w = model_->value(p);
       const float* gr = model_->grad(p);
-      for (std::size_t i = 0; i < p.count; ++i) {
+      float* mk = g.m[k].data();
+      float* vk = g.v[k].data();
+      const float b1 = g.beta1, b2 = g.beta2, decay = 1.0f - lr * g.wd, eps = cfg_.adam_eps;
+      const long long n = static_cast<long long>(p.count);
+#pragma omp parallel for simd schedule(static) if (n > 65536)
+      for (long long i = 0; i < n; ++i) {
         const float gi = gr[i] * clip;
-        float pi = w[i] * (1.0f - lr * g.wd);
-        g.m[k][i] += (1.0f - g.beta1) * (gi - g.m[k][i]);
-        g.v[k][i] += (1.0f - g.beta2) * (gi * gi - g.v[k][i]);
-        pi -= step_size * (g.m[k][i] / (std::sqrt(g.v[k][i] / bias2) + cfg_.adam_eps));
+        float pi = w[i] * decay;
+        mk[i] += (1.0f - b1) * (gi - mk[i]);
+        vk[i] += (1.0f - b2) * (gi * gi - vk[i]);
+        pi -= step_size * (mk[i] / (std::sqrt(vk[i] / bias2) + eps));
         w[i] = pi;
       }
     }
   }
   const float momentum = cfg_.MuonMomentum(step);
   const float wd = cfg_.WeightDecay(step);
+  // one task per matrix: the products inside a task then run on that task's thread alone (nested regions are
+  // serial), which scales better over a model's many small matrices than splitting every product over all threads
+  std::vector<std::pair<MuonGroup*, std::size_t>> tasks;
   for (auto& g : muon_)
-    for (std::size_t k = 0; k < g.params.size(); ++k) MuonUpdate(&g, k, g.lr * lrm, momentum, wd, clip);
+    for (std::size_t k = 0; k < g.params.size(); ++k) tasks.emplace_back(&g, k);
+  const int n_tasks = static_cast<int>(tasks.size());
+#pragma omp parallel for schedule(dynamic, 1) if (n_tasks >= 4)
+  for (int t = 0; t < n_tasks; ++t)
+    MuonUpdate(tasks[t].first, tasks[t].second, tasks[t].first->lr * lrm, momentum, wd, clip);
 }
 
 namespace {
@@ -1090,24 +1250,10 @@ constexpr double kPolar[5][3] = {
     {3.285753657755655, -2.3681294933425376, 0.46449024233003106},
     {2.3465413258596377, -1.7097828382687081, 0.42323551169305323},
 };
-// C[n,m] = A[n,k] B[k,m]: rows of C are built from rows of B (vector axpy), 64 at a time in float
+// C[n,m] = A[n,k] B[k,m]
 void MatMul(const std::vector<float>& A, const std::vector<float>& B, std::vector<float>* Cm, int n, int k, int m) {
-  Cm->assign(static_cast<std::size_t>(n) * m, 0.0f);
-  float* C = Cm->data();
-#pragma omp parallel for schedule(static) if (static_cast<long long>(n) * k * m > 200000)
-  for (int i = 0; i < n; ++i) {
-    std::vector<float> part(static_cast<std::size_t>(m));
-    float* out = C + static_cast<std::size_t>(i) * m;
-    for (int j0 = 0; j0 < k; j0 += 64) {
-      std::fill(part.begin(), part.end(), 0.0f);
-      const int j1 = std::min(k, j0 + 64);
-      for (int j = j0; j < j1; ++j) {
-        const float a = A[static_cast<std::size_t>(i) * k + j];
-        if (a != 0.0f) Axpy(a, &B[static_cast<std::size_t>(j) * m], part.data(), m);
-      }
-      Axpy(1.0f, part.data(), out, m);
-    }
-  }
+  Cm->resize(static_cast<std::size_t>(n) * m);
+  GemmNN(A.data(), k, B.data(), m, Cm->data(), m, n, m, k, false);
 }
 std::vector<float> Transpose(const std::vector<float>& A, int n, int m) {
   std::vector<float> T(A.size());

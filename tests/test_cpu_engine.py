@@ -44,7 +44,10 @@ def test_forward_backward_and_optimizer_match_debug_state(data_dir):
         assert abs(m.forward_loss(tok, tgt) - float(recs[f"step/{k}/loss"][0])) < 1e-5, k
         for n in m.names():
             err = np.abs(m.read(n) - np.array(recs[f"step/{k}/param/{n}"]).reshape(-1)).max()
-            assert err < 1e-4, (k, n, err)
+            # 2e-4: backout_lambda's gradient is near zero on this fixture, and AdamW's first steps move a parameter by
+            # the sign of its gradient; float (not double) partial sums in the vectorised products and attention
+            # change that scalar by 1.1e-4 after three steps, every other tensor by < 5e-5
+            assert err < (2e-4 if n == "backout_lambda" else 1e-4), (k, n, err)
 
 
 def test_generate_score_rl_and_checkpoint(data_dir, tmp_path):
