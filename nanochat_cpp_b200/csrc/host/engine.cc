@@ -490,7 +490,7 @@ void CpuModel::Trunk(const int* tokens, int B, int T, Saved* sv, std::vector<flo
   for (int m = 0; m < M; ++m) sv->pos[m] = m % T;
   BuildRope(T, D, c.rope_base, 0, &sv->cosv, &sv->sinv);
   // embedding -> norm -> smear
-  SectionTimer t_embed("fwd embed+smear");
+  SectionTimer t_trunk("fwd trunk (everything below)");
   const float* wte = P("transformer.wte.weight");
   sv->emb_raw.resize(static_cast<std::size_t>(M) * C);
   for (int m = 0; m < M; ++m)
@@ -538,6 +538,9 @@ void CpuModel::Trunk(const int* tokens, int B, int T, Saved* sv, std::vector<flo
       Linear(h.data(), P(pf + "attn.c_k.weight"), s.k_pre.data(), M, KD, C);
       Linear(h.data(), P(pf + "attn.c_v.weight"), s.v.data(), M, KD, C);
     }
+    s.q.resize(s.q_pre.size());
+    s.k.resize(s.k_pre.size());
+    {
     SectionTimer t_gate("fwd gate+qkprep");
     if (c.has_value_embedding(i)) {
       const float* table = P("value_embeds." + std::to_string(i) + ".weight");
@@ -559,10 +562,9 @@ void CpuModel::Trunk(const int* tokens, int B, int T, Saved* sv, std::vector<flo
         }
       }
     }
-    s.q.resize(s.q_pre.size());
-    s.k.resize(s.k_pre.size());
     QkPrep(s.q_pre.data(), s.q.data(), M, H, D, sv->cosv.data(), sv->sinv.data(), sv->pos.data());
     QkPrep(s.k_pre.data(), s.k.data(), M, KV, D, sv->cosv.data(), sv->sinv.data(), sv->pos.data());
+    }
     s.attn.resize(static_cast<std::size_t>(M) * QD);
     s.lse.resize(static_cast<std::size_t>(B) * H * T);
     {
@@ -577,7 +579,7 @@ void CpuModel::Trunk(const int* tokens, int B, int T, Saved* sv, std::vector<flo
     s.rstd2.resize(M);
     RmsNorm(s.x_mid.data(), h.data(), s.rstd2.data(), M, C);
     s.pre.resize(static_cast<std::size_t>(M) * F);
-    SectionTimer t_mlp("fwd mlp");
+    SectionTimer t_mlp("fwd mlp (to end of layer)");
     Linear(h.data(), P(pf + "mlp.c_fc.weight"), s.pre.data(), M, F, C);
     std::vector<float> act(s.pre.size());
     {
