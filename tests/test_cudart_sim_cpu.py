@@ -52,6 +52,34 @@ def test_gpu_engine_host_side_runs_clean_under_the_simulated_runtime(tmp_path):
     assert summary["live_streams"] == 0 and summary["live_events"] == 0
 
 
+@pytest.mark.skipif(not (os.path.exists(SIM) and os.path.exists(CLI) and os.path.exists(GPU)),
+                    reason="native libraries not built")
+def test_checkpoint_and_paged_generation_run_clean_under_the_simulated_runtime(tmp_path):
+    """The inference side of the C++ GPU engine: a checkpoint written by a (simulated) training step is loaded and six
+    tokens are decoded over the paged cache: prefill through the flash kernel, decode through the skinny GEMMs, the
+    fused prologue and the paged attention kernel. Every launch and tensor map passes the runtime's checks."""
+    model = ["--layers", "4", "--hidden", "256", "--heads", "2", "--kv-heads", "1", "--vocab", "1024", "--seq", "256"]
+    ck = str(tmp_path / "m.ckpt")
+    env = dict(os.environ, LD_PRELOAD=SIM, NANOCHAT_SIM_STRICT="1", NANOCHAT_SIM_TRACE=str(tmp_path / "t1.jsonl"))
+    p = subprocess.run([CLI, "train", "--device", "cuda:0", "--synthetic-zipf", *model, "--batch", "2",
+                        "--num-iterations", "1", "--checkpoint", ck], env=env, capture_output=True, text=True,
+                       timeout=300, cwd=str(tmp_path))
+    assert p.returncode == 0 and os.path.getsize(ck) > 1 << 20, p.stderr[-1500:]
+    trace = str(tmp_path / "t2.jsonl")
+    env["NANOCHAT_SIM_TRACE"] = trace
+    p = subprocess.run([CLI, "generate", "--device", "cuda:0", "--model", ck, *model, "--tokens", "1,2,3,4,5",
+                        "--max-tokens", "6"], env=env, capture_output=True, text=True, timeout=300, cwd=str(tmp_path))
+    assert p.returncode == 0, p.stderr[-1500:]
+    assert p.stdout.strip().startswith("1,2,3,4,5,") and len(p.stdout.strip().split(",")) == 11
+    rows = _trace(trace)
+    summary = rows[-1]
+    assert summary["violations"] == 0
+    per = summary["per_kernel"]
+    for needle in ("paged_decode_kernel", "decode_prep_append_kernel", "gemm_skinny_kernel", "attention_fwd2_kernel",
+                   "softcap_logits_kernel"):
+        assert any(needle in k for k in per), needle
+
+
 BAD_PROGRAM = textwrap.dedent("""
     #include <cuda.h>
     #include <cuda_runtime_api.h>
