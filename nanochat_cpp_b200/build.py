@@ -208,6 +208,35 @@ def build_sim(verbose: bool = False) -> str:
     return out
 
 
+def build_emu(verbose: bool = False) -> str:
+    """`libnc_emu.so`: the CUDA-core kernels of csrc/cuda compiled by the host compiler over csrc/emu/cuda_emu.h
+    (every CUDA thread a fiber). Needs the CUDA headers, no GPU and no nvcc."""
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    emu_dir = os.path.join(os.path.dirname(CSRC_HOST), "emu")
+    srcs = [os.path.join(emu_dir, f) for f in ("emu_kernels.cc", "emu_optim.cc", "emu_decode.cc", "emu_runtime.cc")]
+    if not all(os.path.exists(f) for f in srcs):
+        return ""
+    out = os.path.join(HERE, "libnc_emu.so")
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
+    deps = srcs + [os.path.join(emu_dir, "cuda_emu.h")] + glob.glob(os.path.join(CSRC_CUDA, "*.cuh")) + \
+        glob.glob(os.path.join(CSRC_CUDA, "*.h")) + \
+        [os.path.join(CSRC_CUDA, f) for f in ("rowops.cu", "optim.cu", "decode.cu")]
+    key = _hash(deps, "emu-nsa")
+    stamp = os.path.join(BUILD_DIR, "emu.stamp")
+    if os.path.exists(out) and os.path.exists(stamp) and open(stamp).read() == key:
+        return out
+    # -fno-strict-aliasing: device code reads a register vector through a pointer of its element type as a matter of
+    # course; nvcc gives that the obvious meaning, a host compiler only with this flag
+    _run(["g++", "-O2", "-g", "-std=c++20", "-fPIC", "-shared", "-fno-strict-aliasing", "-I",
+          os.path.join(cuda_home, "include"), "-I", CSRC_CUDA]
+         + srcs + ["-o", out], os.path.join(BUILD_DIR, "emu.log"))
+    with open(stamp, "w") as f:
+        f.write(key)
+    if verbose:
+        print("built", out)
+    return out
+
+
 def build_core(verbose: bool = False) -> str:
     """Compile the host runtime (no CUDA, no torch)."""
     os.makedirs(BUILD_DIR, exist_ok=True)
@@ -262,6 +291,7 @@ def build_all(verbose: bool = False) -> None:
     build_extension(verbose)
     build_gpu_engine(verbose)
     build_sim(verbose)
+    build_emu(verbose)
 
 
 if __name__ == "__main__":

@@ -6,6 +6,8 @@
 // is bandwidth-bound (every cached key and value is read once per step), so this kernel streams K and V pages
 // with 16-byte loads and keeps the online softmax in fp32 registers: CTAs cover (key split, kv head, sequence),
 // the query heads of a group share the K / V traffic, and a small combine kernel merges the key splits.
+#include "host_build.h"
+
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>
@@ -15,7 +17,9 @@
 
 #include <atomic>
 
+#ifndef NC_EMU
 #include "pdl_launch.h"
+#endif
 
 namespace nc {
 
@@ -99,8 +103,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) paged_decode_kernel(
   __shared__ float sm_m[G][GROUPS], sm_l[G][GROUPS];
   __shared__ float sm_acc[G][GROUPS][D];
   // the projection GEMM behind this kernel (programmatic serialization) may set itself up while keys are streamed
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");   // q and the appended K / V row come from the kernel before
+  NC_PDL_PROLOGUE();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   // a length beyond what the page table covers is clamped: the table is never indexed out of range
   const int len = min(seq_lens[b], max_pages * page_size);
@@ -254,6 +257,7 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const float* __restri
   out[head * D + d] = __float2bfloat16_rn(ls > 0.0f ? a / ls : 0.0f);
 }
 
+#ifndef NC_EMU
 template <int D>
 const char* launch_decode(const DecodeArgs& a, cudaStream_t s) {
   const int splits = a.splits < 1 ? 1 : a.splits;
@@ -278,6 +282,7 @@ const char* launch_decode(const DecodeArgs& a, cudaStream_t s) {
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
+#endif  // !NC_EMU
 
 }  // namespace
 
@@ -293,8 +298,7 @@ __global__ void __launch_bounds__(256) decode_prep_append_kernel(
     __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int tokens, int H, int KV, float eps,
     float scale, int num_pages, int* status) {
   constexpr int D = 128;
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");   // the fused projection row comes from the kernel before
+  NC_PDL_PROLOGUE();
   const int groups = (H + KV + 3) / 4;                  // head groups of the q / k part
   const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (unit >= tokens * (groups + 1)) return;
@@ -354,6 +358,7 @@ __global__ void __launch_bounds__(256) decode_prep_append_kernel(
   *reinterpret_cast<uint4*>(dst + 64 + 8 * j) = pack8(y2);
 }
 
+#ifndef NC_EMU
 void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_table, int max_pages,
                const int* positions, const __nv_bfloat16* k_new, long long k_ld, const __nv_bfloat16* v_new,
                long long v_ld, int B, int T, int page_size, int row_elems, cudaStream_t s, int num_pages, int* status) {
@@ -362,6 +367,7 @@ void kv_append(__nv_bfloat16* k_pool, __nv_bfloat16* v_pool, const int* page_tab
   kv_append_kernel<<<(total + 7) / 8, 256, 0, s>>>(k_pool, v_pool, page_table, max_pages, positions, k_new, k_ld,
                                                    v_new, v_ld, T, total, page_size, row_elems, num_pages, status);
 }
+#endif  // !NC_EMU
 
 // fp32 out[r, c] = cap * tanh(logits[r, c] / cap) for c < vocab: the head's soft cap, one pass over the bf16 logits
 // (two elements per thread; the same float operations as the elementwise definition).
@@ -375,12 +381,14 @@ __global__ void __launch_bounds__(256) softcap_logits_kernel(const __nv_bfloat16
   dst[0] = cap * tanhf(__bfloat162float(src[0]) / cap);
   if (c + 1 < vocab) dst[1] = cap * tanhf(__bfloat162float(src[1]) / cap);
 }
+#ifndef NC_EMU
 void softcap_logits(const __nv_bfloat16* lg, long long ld, float* out, int rows, int vocab, float cap, cudaStream_t s) {
   if (rows <= 0 || vocab <= 0) return;
   const long long pairs = (static_cast<long long>(rows) * vocab + 1) / 2;   // vocab even: pairs never straddle rows
   softcap_logits_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, s>>>(lg, ld, out, rows, vocab, cap);
 }
 
+#endif  // !NC_EMU
 // out[r] = index of the largest of logits[r, 0 .. vocab): greedy decoding straight from the bf16 logits (the soft
 // cap is monotonic, so the fp32 capped copy is not needed). Ties go to the lowest index, as in the definition.
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* __restrict__ lg, long long ld, int vocab,
@@ -417,11 +425,14 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
     out[blockIdx.x] = arg == 0x7fffffff ? 0 : arg;   // a row of NaNs or -inf: index 0
   }
 }
+#ifndef NC_EMU
 void argmax_rows(const __nv_bfloat16* lg, long long ld, long long* out, int rows, int vocab, cudaStream_t s) {
   if (rows <= 0 || vocab <= 0) return;
   argmax_rows_kernel<<<rows, 256, 0, s>>>(lg, ld, vocab, out);
 }
+#endif  // !NC_EMU
 
+#ifndef NC_EMU
 const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const __nv_bfloat16* v, long long ld_v,
                                const float* cosT, const float* sinT, const int* positions, const int* page_table,
                                int max_pages, int page_size, __nv_bfloat16* q_out, __nv_bfloat16* k_pool,
@@ -440,6 +451,7 @@ const char* decode_prep_append(const __nv_bfloat16* qk, long long ld_qk, const _
                                          v_pool, tokens, H, KV, eps, scale, num_pages, status);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
+#endif  // !NC_EMU
 
 int decode_splits(int B, int KV, int max_keys) {
   const int target = 148 * 4;  // four 128-thread CTAs per SM keep enough loads in flight
@@ -450,11 +462,13 @@ int decode_splits(int B, int KV, int max_keys) {
   return splits < 1 ? 1 : splits;
 }
 
+#ifndef NC_EMU
 const char* paged_decode_attention(const DecodeArgs& a, cudaStream_t s) {
   if (a.H % a.KV) return "paged_decode_attention: heads must be a multiple of kv heads";
   if (a.D == 128) return launch_decode<128>(a, s);
   if (a.D == 64) return launch_decode<64>(a, s);
   return "paged_decode_attention: head_dim must be 64 or 128";
 }
+#endif  // !NC_EMU
 
 }  // namespace nc

@@ -3,6 +3,8 @@
 // (backends/cuda/kernels/muon.cu:83-464); here the momentum / Nesterov / row-norm stage, the row
 // rescale + bf16 cast, and the NorMuon-scaled cautious update are one kernel each, and the Polar
 // Express products run on the tcgen05 GEMM (batched over the matrices of a group).
+#include "host_build.h"
+
 #include "optim.h"
 
 #include <stdint.h>
@@ -370,6 +372,7 @@ inline int grid_for(long long n, int per_thread) {
 
 }  // namespace
 
+#ifndef NC_EMU
 void adamw_update(float* master, __nv_bfloat16* value, const float* grad, float* m, float* v, long long n, float lr,
                   float beta1, float beta2, float eps, float weight_decay, int step, const float* grad_scale,
                   cudaStream_t s) {
@@ -444,5 +447,7 @@ void muon_apply_batched(const long long* master_ptrs, const long long* value_ptr
   muon_apply_batched_kernel<<<dim3(static_cast<unsigned>(blocks), P), 256, 0, s>>>(
       master_ptrs, value_ptrs, xb, scale0, line_scale, lines_are_rows, rows, cols, lr, weight_decay);
 }
+
+#endif  // !NC_EMU
 
 }  // namespace nc

@@ -5,10 +5,14 @@
 // rms_norm.cu, qk_prep.cu, pointwise.cu, value_gate.cu, smear.cu, embedding.cu, classifier.cu,
 // grad_norm.cu) with fewer, wider passes: e.g. the residual blend and the pre-attention norm are one
 // kernel, and the classifier forward and backward are one sweep over a logits chunk.
+#include "host_build.h"
+
 #include "rowops.h"
 
 #include "mx_quant.cuh"
+#ifndef NC_EMU
 #include "pdl_launch.h"
+#endif
 
 #include <math_constants.h>
 
@@ -84,8 +88,7 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const bf16* __restric
                                                            int dim, float eps, uint8_t* __restrict__ yq = nullptr,
                                                            uint8_t* __restrict__ sf = nullptr) {
   // a GEMM launched behind this kernel with programmatic serialization may set itself up while the rows are normed
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialization
+  NC_PDL_PROLOGUE();
   const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -668,7 +671,7 @@ __global__ void __launch_bounds__(kThreads) value_gate_bwd_kernel(
     const bf16* __restrict__ h, long long ldh, const bf16* __restrict__ ve, const bf16* __restrict__ gw,
     const bf16* __restrict__ gate, const bf16* __restrict__ dv, long long lddv, bf16* __restrict__ dve,
     float* __restrict__ dh12, float* __restrict__ dgw, int tokens, int KV, int D) {
-  extern __shared__ float sh_dgw[];  // KV*12
+  NC_DYNAMIC_SHARED(float, sh_dgw);  // KV*12
   for (int i = threadIdx.x; i < KV * kGateCh; i += blockDim.x) sh_dgw[i] = 0.0f;
   __syncthreads();
   const int lane = threadIdx.x & 31;
@@ -715,8 +718,7 @@ __global__ void __launch_bounds__(kThreads) value_gate_fwd_vec_kernel(const bf16
                                                                       int tokens, int KV, int D,
                                                                       const int* __restrict__ ids, int rows,
                                                                       int* status) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialization
+  NC_PDL_PROLOGUE();
   const int lane = threadIdx.x & 31, li = lane & 15;
   const long long pair = (static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   const bool valid = pair < static_cast<long long>(tokens) * KV;
@@ -750,7 +752,7 @@ __global__ void __launch_bounds__(kThreads) value_gate_bwd_vec_kernel(
     const bf16* __restrict__ h, long long ldh, const bf16* __restrict__ ve, const bf16* __restrict__ gw,
     const bf16* __restrict__ gate, const bf16* __restrict__ dv, long long lddv, bf16* __restrict__ dve,
     float* __restrict__ dh12, float* __restrict__ dgw, int tokens, int KV, int D) {
-  extern __shared__ float sh_dgw[];  // KV*12
+  NC_DYNAMIC_SHARED(float, sh_dgw);  // KV*12
   for (int i = threadIdx.x; i < KV * kGateCh; i += blockDim.x) sh_dgw[i] = 0.0f;
   __syncthreads();
   const int lane = threadIdx.x & 31, li = lane & 15, half = lane >> 4;
@@ -904,8 +906,12 @@ __global__ void __launch_bounds__(kThreads) embedding_bwd_kernel(const int* __re
   if (dim % 4 == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
     for (int i = lane * 4; i < dim; i += 128) {
       const float a = b2f(src[i]), b = b2f(src[i + 1]), c = b2f(src[i + 2]), d = b2f(src[i + 3]);
+#ifdef NC_EMU
+      atomicAdd(dst + i, a), atomicAdd(dst + i + 1, b), atomicAdd(dst + i + 2, c), atomicAdd(dst + i + 3, d);
+#else
       asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "f"(a), "f"(b), "f"(c), "f"(d)
                    : "memory");
+#endif
     }
   } else {
     for (int i = lane; i < dim; i += 32) atomicAdd(dst + i, b2f(src[i]));
@@ -1071,6 +1077,10 @@ __global__ void __launch_bounds__(256) classifier_kernel(bf16* __restrict__ logi
 // maximum unnecessary: exp(z - cap) cannot overflow and its sum over any vocabulary stays far above the fp32
 // denormal range. tanh is the single-instruction approximation (relative error 2^-11, four times finer than the
 // bf16 rounding of its input). Per element: tanh + ex2 in each sweep.
+#ifdef NC_EMU
+__device__ __forceinline__ float tanh_fast(float x) { return std::tanh(x); }
+__device__ __forceinline__ float ex2_fast(float x) { return std::exp2(x); }
+#else
 __device__ __forceinline__ float tanh_fast(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -1081,6 +1091,7 @@ __device__ __forceinline__ float ex2_fast(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+#endif
 
 constexpr int kClsThreads = 512;
 
@@ -1092,7 +1103,7 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
     bf16* __restrict__ logits, long long ld, const int* __restrict__ targets, float* __restrict__ losses,
     const float* __restrict__ row_scale, const float* __restrict__ dlogit_scale, int vocab, int padded,
     float softcap, int ignore_index, bool want_grad, int* status) {
-  extern __shared__ __align__(16) unsigned char cls_smem[];
+  NC_DYNAMIC_SHARED(unsigned char, cls_smem);
   bf16* row_s = reinterpret_cast<bf16*>(cls_smem);
   __shared__ float sh[32];
   const int row = blockIdx.x;
@@ -1229,6 +1240,7 @@ inline int flat_grid(long long n) {
 }  // namespace
 
 // ------------------------------------------------------------------ launchers
+#ifndef NC_EMU
 void rmsnorm_fwd(const bf16* x, long long ldx, bf16* y, float* rstd, int rows, int dim, float eps, cudaStream_t s,
                  uint8_t* yq, uint8_t* sf) {
   if (rows <= 0) return;
@@ -1381,5 +1393,7 @@ void sumsq_f32(const float* g, long long n, double* out, cudaStream_t s) {
 void finish_norm(const double* sumsq, float clip, float* norm_clip, cudaStream_t s) {
   finish_norm_kernel<<<1, 1, 0, s>>>(sumsq, clip, norm_clip);
 }
+
+#endif  // !NC_EMU
 
 }  // namespace nc

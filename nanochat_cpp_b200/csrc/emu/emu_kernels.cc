@@ -1,0 +1,84 @@
+// Entry points (C ABI, for ctypes) that run kernels of csrc/cuda on the host through cuda_emu.h. This file includes
+// the kernel sources themselves: what runs here is the code the device runs.
+#define NC_EMU
+#include "../cuda/rowops.cu"
+
+namespace nc {
+namespace {
+emu::Dim Grid1(long long blocks) { return emu::Dim{static_cast<unsigned>(blocks), 1, 1}; }
+emu::Dim Block1(int threads) { return emu::Dim{static_cast<unsigned>(threads), 1, 1}; }
+bf16* B(void* p) { return static_cast<bf16*>(p); }
+const bf16* B(const void* p) { return static_cast<const bf16*>(p); }
+}  // namespace
+}  // namespace nc
+
+using nc::B;
+
+extern "C" {
+
+// mode 0: y = norm(x), rstd saved. mode 2: xr = lam_r x + lam_0 x0, y = norm(xr).
+void nc_emu_rmsnorm(int mode, const void* x, const void* x0, const float* lam_r, const float* lam_0, void* xr, void* y,
+                    float* rstd, int rows, int dim, float eps) {
+  const auto grid = nc::Grid1(nc::blocks_for_rows(rows));
+  if (mode == 0)
+    emu::launch(grid, nc::Block1(nc::kThreads), 0, [&] {
+      nc::rmsnorm_kernel<0>(B(x), dim, nullptr, nullptr, nullptr, nullptr, B(y), rstd, rows, dim, eps);
+    });
+  else
+    emu::launch(grid, nc::Block1(nc::kThreads), 0, [&] {
+      nc::rmsnorm_kernel<2>(B(x), dim, B(x0), lam_r, lam_0, B(xr), B(y), rstd, rows, dim, eps);
+    });
+}
+
+void nc_emu_rmsnorm_bwd(const void* x, const void* dy, const float* rstd, const void* residual, void* dx, int rows,
+                        int dim) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(rows)), nc::Block1(nc::kThreads), 0,
+              [&] { nc::rmsnorm_bwd_kernel(B(x), B(dy), rstd, B(residual), B(dx), rows, dim); });
+}
+
+void nc_emu_norm_blend_bwd(const void* xr, const void* dh, const float* rstd, const void* residual, const float* extra,
+                           int extra_cols, const void* x, const void* x0, const float* lam_r, const float* lam_0,
+                           void* dx, void* dx0, int accumulate, float* g_lam_r, float* g_lam_0, int rows, int dim) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(rows)), nc::Block1(nc::kThreads), 0, [&] {
+    nc::norm_blend_bwd_kernel(B(xr), B(dh), rstd, B(residual), extra, extra_cols, B(x), B(x0), lam_r, lam_0, B(dx),
+                              B(dx0), accumulate, g_lam_r, g_lam_0, rows, dim);
+  });
+}
+
+void nc_emu_qk_prep_fwd(const void* in, long long ld_in, void* out, long long ld_out, const float* cosT,
+                        const float* sinT, const int* positions, int tokens, int seq, int heads, int D, float eps,
+                        float scale) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(tokens)), nc::Block1(nc::kThreads), 0, [&] {
+    nc::qk_prep_fwd_kernel(B(in), ld_in, B(out), ld_out, cosT, sinT, positions, tokens, seq, heads, D, eps, scale);
+  });
+}
+
+void nc_emu_embedding_fwd(const int* ids, const void* table, void* out, int tokens, int dim, int rows, int* status) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(tokens)), nc::Block1(nc::kThreads), 0,
+              [&] { nc::embedding_fwd_kernel(ids, B(table), B(out), tokens, dim, rows, status); });
+}
+
+void nc_emu_embedding_bwd(const int* ids, const void* dout, long long ld, float* dtable, int tokens, int dim, int rows,
+                          int* status) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(tokens)), nc::Block1(nc::kThreads), 0,
+              [&] { nc::embedding_bwd_kernel(ids, B(dout), ld, dtable, tokens, dim, rows, status); });
+}
+
+void nc_emu_embedding_bwd_sorted(const int* sorted_ids, const int* perm, const void* dout, long long ld, float* dtable,
+                                 int tokens, int dim, int rows, int* status) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(tokens)), nc::Block1(nc::kThreads), 0, [&] {
+    nc::embedding_bwd_sorted_kernel(sorted_ids, perm, B(dout), ld, dtable, tokens, dim, rows, status);
+  });
+}
+
+// Softcap + cross entropy over bf16 logits, in place (the generic kernel: one block of 256 threads per row).
+void nc_emu_classifier(void* logits, long long ld, const int* targets, float* losses, const float* row_scale,
+                       const float* dlogit_scale, int rows, int vocab, int padded, float softcap, int ignore_index,
+                       int want_grad, int* status) {
+  emu::launch(nc::Grid1(rows), nc::Block1(256), 0, [&] {
+    nc::classifier_kernel(B(logits), ld, targets, losses, row_scale, dlogit_scale, rows, vocab, padded, softcap,
+                          ignore_index, want_grad != 0, status);
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,195 @@
+"""The CUDA-core kernels of csrc/cuda, compiled by the host compiler (csrc/emu/cuda_emu.h: every CUDA thread a fiber,
+shuffles and barriers as rendezvous) and run here, on a machine without a GPU, against the PyTorch definitions of the
+same operators. What is executed is the kernels' own source: index arithmetic, vector tails, masks, reductions."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import nanochat_cpp_b200
+from nanochat_cpp_b200.ops import ref
+
+LIB = os.path.join(os.path.dirname(nanochat_cpp_b200.__file__), "libnc_emu.so")
+pytestmark = pytest.mark.skipif(not os.path.exists(LIB), reason="host build of the kernels not present")
+
+
+@pytest.fixture(scope="module")
+def E():
+    return ctypes.CDLL(LIB)
+
+
+def P(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def bf(*shape, scale=1.0, gen=None):
+    return (torch.randn(*shape, generator=gen) * scale).to(torch.bfloat16).contiguous()
+
+
+def close(got, want, rtol=2.0 ** -7, atol=2.0 ** -8):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    bound = atol * want.abs().mean().clamp_min(1e-6) + rtol * want.abs()
+    assert (err <= bound).all(), float((err - bound).max())
+
+
+@pytest.mark.parametrize("rows,dim", [(19, 256), (8, 1280), (5, 40), (33, 100)])
+def test_rmsnorm_forward_and_backward(E, rows, dim):
+    g = torch.Generator().manual_seed(rows + dim)
+    x, dy, res = bf(rows, dim, gen=g), bf(rows, dim, gen=g), bf(rows, dim, gen=g)
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows)
+    E.nc_emu_rmsnorm(0, P(x), None, None, None, None, P(y), P(rstd), rows, dim, ctypes.c_float(1e-6))
+    yr, rr = ref.rmsnorm_fwd(x, 1e-6)
+    close(y, yr)
+    assert torch.allclose(rstd, rr, rtol=1e-5)
+    dx = torch.empty_like(x)
+    E.nc_emu_rmsnorm_bwd(P(x), P(dy), P(rstd), P(res), P(dx), rows, dim)
+    close(dx, ref.rmsnorm_bwd(x, dy, rr, res))
+
+
+@pytest.mark.parametrize("rows,dim,extra_cols,accumulate", [(19, 256, 12, 1), (8, 1280, 0, 0), (40, 64, 12, 0)])
+def test_fused_norm_blend_backward(E, rows, dim, extra_cols, accumulate):
+    g = torch.Generator().manual_seed(7)
+    x, x0, dh, res = (bf(rows, dim, gen=g) for _ in range(4))
+    lam_r, lam_0 = torch.tensor([0.9]), torch.tensor([0.2])
+    xr = (lam_r * x.float() + lam_0 * x0.float()).to(torch.bfloat16)
+    _, rstd = ref.rmsnorm_fwd(xr, 1e-6)
+    extra = torch.randn(rows, extra_cols, generator=g) if extra_cols else None
+    base = bf(rows, dim, gen=g) if accumulate else None
+    gsc = torch.tensor([0.25, -0.5])
+    want_g = gsc.clone()
+    want_dx, want_dx0 = ref.norm_blend_bwd(xr, dh, rstd, res, x, x0, lam_r[0], lam_0[0], want_g[0:1], want_g[1:2],
+                                           dx0_acc=base.clone() if accumulate else None, extra=extra)
+    dx = torch.empty_like(x)
+    dx0 = base.clone() if accumulate else torch.empty_like(x)
+    E.nc_emu_norm_blend_bwd(P(xr), P(dh), P(rstd), P(res), P(extra) if extra is not None else None, extra_cols, P(x),
+                            P(x0), P(lam_r), P(lam_0), P(dx), P(dx0), accumulate, P(gsc[0:1]), P(gsc[1:2]), rows, dim)
+    close(dx, want_dx)
+    close(dx0, want_dx0, atol=2.0 ** -7)
+    assert torch.allclose(gsc, want_g, rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("heads,D", [(3, 64), (2, 128)])
+def test_qk_preparation(E, heads, D):
+    g = torch.Generator().manual_seed(D)
+    B_, T = 2, 9
+    x = bf(B_, T, heads, D, gen=g)
+    cos, sin = ref.build_rope(T, D, 10000.0, "cpu")
+    out = torch.empty_like(x)
+    E.nc_emu_qk_prep_fwd(P(x), ctypes.c_longlong(heads * D), P(out), ctypes.c_longlong(heads * D), P(cos.contiguous()),
+                         P(sin.contiguous()), None, B_ * T, T, heads, D, ctypes.c_float(1e-6), ctypes.c_float(1.2))
+    want, _ = ref.qk_prep_fwd(x, x, cos, sin, 1e-6, 1.2)
+    close(out, want)
+
+
+def test_embedding_kernels_check_their_indices(E):
+    g = torch.Generator().manual_seed(1)
+    table = bf(50, 64, gen=g)
+    ids = torch.tensor([3, 50, 7, -1, 49, 3], dtype=torch.int32)
+    out = torch.full((6, 64), 7.0, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32)
+    E.nc_emu_embedding_fwd(P(ids), P(table), P(out), 6, 64, 50, P(status))
+    assert torch.equal(out[[0, 2, 4, 5]], table[[3, 7, 49, 3]]) and not out[[1, 3]].any()
+    assert int(status) == 7                                  # an id outside the table was skipped and reported
+    dout = bf(6, 64, gen=g)
+    want = torch.zeros(50, 64)
+    for r, i in enumerate(ids.tolist()):
+        if 0 <= i < 50:
+            want[i] += dout[r].float()
+    for sorted_order in (False, True):
+        dt = torch.zeros(50, 64)
+        status.zero_()
+        if sorted_order:
+            s, perm = torch.sort(ids, stable=True)
+            s32, perm32 = s.int().contiguous(), perm.int().contiguous()      # named: they must outlive the call
+            E.nc_emu_embedding_bwd_sorted(P(s32), P(perm32), P(dout), ctypes.c_longlong(64), P(dt), 6, 64, 50,
+                                          P(status))
+        else:
+            E.nc_emu_embedding_bwd(P(ids), P(dout), ctypes.c_longlong(64), P(dt), 6, 64, 50, P(status))
+        assert torch.allclose(dt, want, atol=1e-6) and int(status) == 7
+
+
+def test_softcap_cross_entropy(E):
+    g = torch.Generator().manual_seed(2)
+    rows, vocab, padded = 7, 250, 256
+    logits = bf(rows, padded, scale=4.0, gen=g)
+    targets = torch.randint(0, vocab, (rows,), generator=g).int()
+    targets[2] = -1
+    targets[5] = vocab + 3                                   # outside the vocabulary: ignored, reported
+    work = logits.clone()
+    losses = torch.empty(rows)
+    scale = torch.tensor([0.5])
+    status = torch.zeros(1, dtype=torch.int32)
+    E.nc_emu_classifier(P(work), ctypes.c_longlong(padded), P(targets), P(losses), None, P(scale), rows, vocab, padded,
+                        ctypes.c_float(15.0), -1, 1, P(status))
+    ok = torch.tensor([t not in (2, 5) for t in range(rows)])
+    safe_t = torch.where(ok, targets, torch.zeros_like(targets))
+    want_l, want_d = ref.classifier_fwd_bwd(logits[ok].clone(), safe_t[ok], vocab, dlogit_scale=0.5)
+    assert torch.allclose(losses[ok], want_l.float(), rtol=2e-3, atol=2e-3)
+    assert not losses[~ok].any() and not work[~ok].any()
+    close(work[ok][:, :vocab], want_d[:, :vocab], rtol=2.0 ** -6, atol=2.0 ** -5)
+    assert not work[:, vocab:].any()
+    assert int(status) == 7
+
+
+@pytest.mark.parametrize("n", [4096 + 3, 17])
+def test_adamw_kernel(E, n):
+    g = torch.Generator().manual_seed(n)
+    master, grad = torch.randn(n, generator=g), torch.randn(n, generator=g)
+    m, v = torch.rand(n, generator=g) * 0.1, torch.rand(n, generator=g) * 0.01
+    rm, rmm, rv = master.clone(), m.clone(), v.clone()
+    value = torch.zeros(n, dtype=torch.bfloat16)
+    scale = torch.tensor([0.5])
+    kw = dict(lr=0.01, beta1=0.8, beta2=0.95, eps=1e-10, weight_decay=0.01, step=3)
+    f = ctypes.c_float
+    E.nc_emu_adamw(P(master), P(value), P(grad), P(m), P(v), ctypes.c_longlong(n), f(kw["lr"]), f(kw["beta1"]),
+                   f(kw["beta2"]), f(kw["eps"]), f(kw["weight_decay"]), kw["step"], P(scale), 3)
+    ref.adamw_update(rm, None, grad, rmm, rv, grad_scale=0.5, **kw)
+    assert torch.allclose(master, rm, rtol=1e-5, atol=1e-6) and torch.allclose(m, rmm, rtol=1e-6)
+    assert torch.allclose(v, rv, rtol=1e-6) and torch.equal(value, master.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("B,H,KV,D,window,splits", [(3, 4, 2, 64, -1, 1), (2, 4, 1, 128, 20, 3), (2, 2, 2, 128, -1, 2)])
+def test_paged_decode_attention(E, B, H, KV, D, window, splits):
+    """Split-KV single-query attention over 16-token pages with a shuffled page table, GQA and a left window."""
+    g = torch.Generator().manual_seed(B * 100 + D + splits)
+    page, max_pages = 16, 6
+    pages = B * max_pages
+    k_pool, v_pool = bf(pages, page, KV, D, gen=g), bf(pages, page, KV, D, gen=g)
+    table = torch.randperm(pages, generator=g).int().view(B, max_pages).contiguous()
+    lens = torch.tensor([37, 90, 5][:B], dtype=torch.int32)
+    q = bf(B, H, D, gen=g)
+    out = torch.zeros(B, H, D, dtype=torch.bfloat16)
+    part_acc = torch.zeros(B, H, splits, D)
+    part_ml = torch.zeros(B, H, splits, 2)
+    scale = 1.0 / D ** 0.5
+    rc = E.nc_emu_paged_decode(P(q), P(k_pool), P(v_pool), P(table), max_pages, P(lens), B, H, KV, D, page, window,
+                               ctypes.c_float(scale), splits, P(part_acc), P(part_ml), P(out))
+    assert rc == 0
+    want = ref.paged_decode_attention(q, k_pool, v_pool, table, lens, window, scale)
+    close(out, want, rtol=2.0 ** -6, atol=2.0 ** -6)
+
+
+def test_kv_append_and_argmax(E):
+    g = torch.Generator().manual_seed(4)
+    pages, page, KV, D = 4, 16, 2, 64
+    k_pool, v_pool = torch.zeros(pages, page, KV, D, dtype=torch.bfloat16), torch.zeros(pages, page, KV, D,
+                                                                                        dtype=torch.bfloat16)
+    table = torch.tensor([[0, 9], [2, 3]], dtype=torch.int32)
+    positions = torch.tensor([[3, 20], [40, 17]], dtype=torch.int32)
+    k_new, v_new = bf(2, 2, KV, D, gen=g), bf(2, 2, KV, D, gen=g)
+    status = torch.zeros(1, dtype=torch.int32)
+    E.nc_emu_kv_append(P(k_pool), P(v_pool), P(table), 2, P(positions), P(k_new), ctypes.c_longlong(KV * D), P(v_new),
+                       ctypes.c_longlong(KV * D), 2, 2, page, KV * D, pages, P(status))
+    want = torch.zeros_like(k_pool)
+    want[0, 3], want[3, 1] = k_new[0, 0], k_new[1, 1]
+    assert torch.equal(k_pool, want) and int(status) == 7
+    logits = bf(5, 300, gen=g)
+    logits[1, 250] = 50.0                                     # beyond the vocabulary: must not win
+    logits[2, 7] = logits[2, 100] = 40.0                      # a tie: the lowest index
+    out = torch.zeros(5, dtype=torch.int64)
+    E.nc_emu_argmax_rows(P(logits), ctypes.c_longlong(300), P(out), 5, 250)
+    assert torch.equal(out, logits[:, :250].float().argmax(dim=-1)) and int(out[2]) == 7
