@@ -213,14 +213,14 @@ def build_emu(verbose: bool = False) -> str:
     (every CUDA thread a fiber). Needs the CUDA headers, no GPU and no nvcc."""
     os.makedirs(BUILD_DIR, exist_ok=True)
     emu_dir = os.path.join(os.path.dirname(CSRC_HOST), "emu")
-    srcs = [os.path.join(emu_dir, f) for f in ("emu_kernels.cc", "emu_optim.cc", "emu_decode.cc", "emu_runtime.cc")]
+    srcs = [os.path.join(emu_dir, f) for f in ("emu_kernels.cc", "emu_optim.cc", "emu_decode.cc", "emu_comm.cc", "emu_runtime.cc")]
     if not all(os.path.exists(f) for f in srcs):
         return ""
     out = os.path.join(HERE, "libnc_emu.so")
     cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
     deps = srcs + [os.path.join(emu_dir, "cuda_emu.h")] + glob.glob(os.path.join(CSRC_CUDA, "*.cuh")) + \
         glob.glob(os.path.join(CSRC_CUDA, "*.h")) + \
-        [os.path.join(CSRC_CUDA, f) for f in ("rowops.cu", "optim.cu", "decode.cu")]
+        [os.path.join(CSRC_CUDA, f) for f in ("rowops.cu", "optim.cu", "decode.cu", "comm.cu")]
     key = _hash(deps, "emu-nsa")
     stamp = os.path.join(BUILD_DIR, "emu.stamp")
     if os.path.exists(out) and os.path.exists(stamp) and open(stamp).read() == key:

@@ -11,6 +11,8 @@
 // Ordering across ranks uses flag words in symmetric memory: a rank publishes "bucket b of step s is
 // final" after its backward kernels (stream order), the owner spins on the flags of all ranks before it
 // loads. Every spin is bounded by a time budget and reports through the status word; nothing traps.
+#include "host_build.h"
+
 #include "comm.h"
 
 #include <stdint.h>
@@ -310,6 +312,7 @@ __global__ void __launch_bounds__(256) grad_reduce_local_kernel(float* __restric
 // publishes the data is a release store issued by a later kernel on the same stream, as for the plain stores.
 // (multimem.st has no 2-byte form: single odd elements always go through the peer pointers.)
 __device__ __forceinline__ void store_all16(const PeerPtrs& values, int world, long long elem, const uint4& w) {
+#ifndef NC_EMU
   if (values.mc != nullptr) {
     __nv_bfloat16* a = static_cast<__nv_bfloat16*>(values.mc) + elem;
     asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "r"(w.x), "r"(w.y), "r"(w.z),
@@ -317,14 +320,17 @@ __device__ __forceinline__ void store_all16(const PeerPtrs& values, int world, l
                  : "memory");
     return;
   }
+#endif
   for (int k = 0; k < world; ++k) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(values.p[k]) + elem) = w;
 }
 __device__ __forceinline__ void store_all4(const PeerPtrs& values, int world, long long elem, uint32_t w) {
+#ifndef NC_EMU
   if (values.mc != nullptr) {
     __nv_bfloat16* a = static_cast<__nv_bfloat16*>(values.mc) + elem;
     asm volatile("multimem.st.relaxed.sys.global.bf16x2 [%0], %1;" ::"l"(a), "r"(w) : "memory");
     return;
   }
+#endif
   for (int k = 0; k < world; ++k) *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(values.p[k]) + elem) = w;
 }
 __device__ __forceinline__ void store_all2(const PeerPtrs& values, int world, long long elem, __nv_bfloat16 h) {
@@ -490,6 +496,7 @@ inline int grid_for(long long n, int per_thread, int cap) {
 
 }  // namespace
 
+#ifndef NC_EMU
 void comm_signal(const PeerPtrs& flags, int world, int my_rank, int slot, int value, cudaStream_t s) {
   signal_kernel<<<1, 32, 0, s>>>(flags, world, my_rank, slot, value);
 }
@@ -561,5 +568,7 @@ void comm_muon_apply_push_batched(const long long* master_ptrs, const long long*
   muon_apply_push_batched_kernel<<<dim3(gx, P), 256, 0, s>>>(master_ptrs, value_offsets, values, world, xb, scale0,
                                                              line_scale, lines_are_rows, rows, cols, lr, weight_decay);
 }
+
+#endif  // !NC_EMU
 
 }  // namespace nc

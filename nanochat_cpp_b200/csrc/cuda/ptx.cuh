@@ -26,6 +26,21 @@ enum : int {
   kErrBadIndex = 7,       // a token id, target or page index outside its table: the access was skipped
 };
 
+#ifdef NC_EMU
+// Host build (csrc/emu): only what the CUDA-core kernels use has a host form - the clock and the cross-GPU flag
+// accesses below. The tensor-core / TMA / mbarrier wrappers of this header stay PTX and must not be called there.
+}  // namespace nc
+#include <chrono>
+namespace nc {
+inline uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p)); }
+inline unsigned long long globaltimer_ns() {
+  return static_cast<unsigned long long>(
+      std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count());
+}
+inline void __nanosleep(unsigned) {}
+inline void __threadfence_system() {}
+inline void __threadfence() {}
+#else
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -35,6 +50,7 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+#endif
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
@@ -108,6 +124,10 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // ---------------------------------------------------------------- cross-GPU flags
 constexpr unsigned long long kPeerWaitBudgetNs = 20000000000ull;  // 20 s: a peer may be a whole step behind
 
+#ifdef NC_EMU
+inline int ld_acquire_sys(const int* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+inline void st_release_sys(int* p, int v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
+#else
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -116,6 +136,7 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+#endif
 // Wait until flags[i] >= value for i in [0, count). Returns false (status <- kErrWaitPeer) on expiry.
 __device__ __forceinline__ bool wait_flags_bounded(const int* flags, int count, int value, int* status,
                                                    unsigned long long budget_ns = kPeerWaitBudgetNs) {

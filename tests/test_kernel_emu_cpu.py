@@ -193,3 +193,98 @@ def test_kv_append_and_argmax(E):
     out = torch.zeros(5, dtype=torch.int64)
     E.nc_emu_argmax_rows(P(logits), ctypes.c_longlong(300), P(out), 5, 250)
     assert torch.equal(out, logits[:, :250].float().argmax(dim=-1)) and int(out[2]) == 7
+
+
+def _ptrs(tensors):
+    arr = (ctypes.c_longlong * len(tensors))(*[t.data_ptr() for t in tensors])
+    return arr
+
+
+def test_bf16_push_reduce_scatter_across_four_emulated_ranks(E):
+    """The transport's reduce-scatter on the CPU: every "rank" pushes what the others own (bf16, scaled) into their
+    receive slots and publishes its flag; every owner then reduces in fixed rank order in fp32. Odd run lengths
+    exercise the partial-vector tails, NaN-filled receive buffers show an element nobody pushed."""
+    world, n, scale = 4, 1 << 14, 0.5
+    g = torch.Generator().manual_seed(12)
+    grads = [torch.randn(n, generator=g) for _ in range(world)]
+    orig = [t.clone() for t in grads]
+    runs = {r: [(r * 2048, 2048 - 3 * r), (10000 + r * 40, 37)] for r in range(world)}
+    placed, cap = {}, 0
+    for r in range(world):
+        pos, rows = 0, []
+        for off, cnt in runs[r]:
+            rows.append((off, cnt, pos))
+            pos += (cnt + 7) // 8 * 8
+        placed[r], cap = rows, max(cap, pos)
+    recv = [torch.full((world * cap,), float("nan"), dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.zeros(2 * world, dtype=torch.int32) for _ in range(world)]
+    for src in range(world):
+        rows, first = [], 0
+        for owner in range(world):
+            if owner == src:
+                continue
+            for off, cnt, pos in placed[owner]:
+                rows.append([first, off, pos, owner, cnt])
+                first += (cnt + 7) // 8
+        segs = torch.tensor(rows, dtype=torch.int64)
+        E.nc_emu_grad_push(P(grads[src]), _ptrs(recv), world, ctypes.c_longlong(cap), src, P(segs), len(rows),
+                           ctypes.c_longlong(first), ctypes.c_float(scale), 3)
+        E.nc_emu_comm_signal(_ptrs(flags), world, src, 1, 3)
+    status = torch.zeros(1, dtype=torch.int32)
+    for owner in range(world):
+        assert flags[owner][world:2 * world].tolist() == [3] * world      # every rank's flag arrived at this owner
+        rows, first = [], 0
+        for off, cnt, pos in placed[owner]:
+            rows.append([first, off, pos, cnt])
+            first += (cnt + 7) // 8
+        segs = torch.tensor(rows, dtype=torch.int64)
+        acc = torch.zeros(1, dtype=torch.float64)
+        E.nc_emu_grad_reduce_local(P(grads[owner]), P(recv[owner]), ctypes.c_longlong(cap), world, owner, P(segs),
+                                   len(rows), ctypes.c_longlong(first), ctypes.c_float(scale), P(flags[owner]), 1, 3,
+                                   P(acc), P(status), 2)
+        ss = 0.0
+        for off, cnt, _ in placed[owner]:
+            want = torch.zeros(cnt)
+            for r in range(world):
+                part = orig[r][off:off + cnt] * scale
+                want += part if r == owner else part.to(torch.bfloat16).float()
+            assert torch.allclose(grads[owner][off:off + cnt], want, rtol=2e-6, atol=1e-7), (owner, off)
+            ss += float(want.double().square().sum())
+        assert abs(float(acc) - ss) <= 1e-6 * ss
+        mask = torch.ones(n, dtype=torch.bool)
+        for off, cnt, _ in placed[owner]:
+            mask[off:off + cnt] = False
+        assert torch.equal(grads[owner][mask], orig[owner][mask])           # nothing outside the owned runs moved
+    assert int(status) == 0
+
+
+def test_a_wait_for_a_flag_nobody_sets_gives_up_with_a_status(E):
+    flags = torch.zeros(8, dtype=torch.int32)
+    flags[4:8] = torch.tensor([2, 2, 1, 2])                    # rank 2 is one step behind in slot 1
+    status = torch.zeros(1, dtype=torch.int32)
+    E.nc_emu_comm_wait(P(flags), 4, 1, 2, P(status), ctypes.c_ulonglong(20_000_000))     # 20 ms
+    assert int(status) == 5
+    status.zero_()
+    flags[6] = 2
+    E.nc_emu_comm_wait(P(flags), 4, 1, 2, P(status), ctypes.c_ulonglong(20_000_000))
+    assert int(status) == 0
+
+
+def test_adamw_update_pushed_into_every_rank(E):
+    world, n, off = 3, 2048 + 5, 64
+    g = torch.Generator().manual_seed(9)
+    values = [torch.zeros(4096, dtype=torch.bfloat16) for _ in range(world)]
+    master, grad = torch.randn(n, generator=g), torch.randn(n, generator=g)
+    m, v = torch.zeros(n), torch.zeros(n)
+    rm, rmm, rv = master.clone(), m.clone(), v.clone()
+    scale = torch.tensor([0.5])
+    kw = dict(lr=0.01, beta1=0.8, beta2=0.95, eps=1e-10, weight_decay=0.01, step=3)
+    f = ctypes.c_float
+    E.nc_emu_adamw_push(P(master), _ptrs(values), world, ctypes.c_longlong(off), P(grad), P(m), P(v), ctypes.c_longlong(n),
+                        f(kw["lr"]), f(kw["beta1"]), f(kw["beta2"]), f(kw["eps"]), f(kw["weight_decay"]), kw["step"],
+                        P(scale), 2)
+    ref.adamw_update(rm, None, grad, rmm, rv, grad_scale=0.5, **kw)
+    assert torch.allclose(master, rm, rtol=1e-5, atol=1e-6)
+    for val in values:
+        assert torch.equal(val[off:off + n], master.to(torch.bfloat16))
+        assert not val[:off].any() and not val[off + n:].any()
