@@ -175,6 +175,8 @@ class FusedTransport:
             for off, cnt, pos in placed[self.rank][b]:
                 rows.append([first, off, pos, cnt])
                 first += (cnt + 7) // 8
+            if len(rows) > 64:
+                raise ValueError("a rank owns more than 64 runs in one bucket (the reduction kernel's segment table)")
             bk["own_rows"] = torch.tensor(rows if rows else [[0, 0, 0, 0]], dtype=torch.int64,
                                           device=self.device).reshape(-1, 4)
             bk["own_n"], bk["own_vec"] = len(rows), first

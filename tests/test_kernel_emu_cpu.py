@@ -288,3 +288,72 @@ def test_adamw_update_pushed_into_every_rank(E):
     for val in values:
         assert torch.equal(val[off:off + n], master.to(torch.bfloat16))
         assert not val[:off].any() and not val[off + n:].any()
+
+
+@pytest.mark.parametrize("world", [8, 3])
+def test_whole_model_reduce_scatter_plan_on_emulated_ranks(E, world):
+    """The transport's plan for a real parameter list (ownership of Muon matrices and AdamW slices, buckets per layer,
+    receive layout) driven through the kernels for every rank and every bucket: each owner ends up with the scaled
+    sum of all ranks' gradients on exactly the elements it owns, in every bucket, at eight ranks as at three."""
+    import types
+    from nanochat_cpp_b200.config import Config
+    from nanochat_cpp_b200.models.params import param_specs
+    from nanochat_cpp_b200.parallel import dp
+    from nanochat_cpp_b200.parallel.fused import plan_reduce_scatter
+    cfg = Config(num_layers=3, num_heads=2, num_kv_heads=1, hidden_dim=128, seq_len=64, vocab_size=200,
+                 padded_vocab_size=256, window_pattern="SL")
+    specs = param_specs(cfg)
+    owners = dp.assign_owners(types.SimpleNamespace(specs=specs, cfg=cfg), world)
+    L = cfg.num_layers
+    placed, cap = plan_reduce_scatter(specs, owners, world, L)
+    total = max(s.offset + s.count for s in specs)
+    g = torch.Generator().manual_seed(world)
+    grads = [torch.randn(total, generator=g) for _ in range(world)]
+    orig = torch.stack(grads)
+    scale = 1.0 / world
+    recv = [torch.full((world * max(cap, 8),), float("nan"), dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.zeros((L + 4) * world, dtype=torch.int32) for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32)
+    for b in range(L + 2):
+        for src in range(world):
+            rows, first = [], 0
+            for r in range(world):
+                if r == src:
+                    continue
+                for off, cnt, pos in placed[r][b]:
+                    rows.append([first, off, pos, r, cnt])
+                    first += (cnt + 7) // 8
+            assert len(rows) <= 128
+            if rows:
+                segs = torch.tensor(rows, dtype=torch.int64)
+                E.nc_emu_grad_push(P(grads[src]), _ptrs(recv), world, ctypes.c_longlong(cap), src, P(segs), len(rows),
+                                   ctypes.c_longlong(first), ctypes.c_float(scale), 2)
+            E.nc_emu_comm_signal(_ptrs(flags), world, src, b, 1)
+        for owner in range(world):
+            rows, first = [], 0
+            for off, cnt, pos in placed[owner][b]:
+                rows.append([first, off, pos, cnt])
+                first += (cnt + 7) // 8
+            if not rows:
+                continue
+            segs = torch.tensor(rows, dtype=torch.int64)
+            acc = torch.zeros(1, dtype=torch.float64)
+            E.nc_emu_grad_reduce_local(P(grads[owner]), P(recv[owner]), ctypes.c_longlong(cap), world, owner, P(segs),
+                                       len(rows), ctypes.c_longlong(first), ctypes.c_float(scale), P(flags[owner]), b, 1,
+                                       P(acc), P(status), 2)
+    assert int(status) == 0
+    covered = torch.zeros(total, dtype=torch.int32)
+    for owner in range(world):
+        for b in range(L + 2):
+            for off, cnt, _ in placed[owner][b]:
+                covered[off:off + cnt] += 1
+                want = orig[owner, off:off + cnt] * scale
+                for r in range(world):
+                    if r != owner:
+                        want = want + (orig[r, off:off + cnt] * scale).to(torch.bfloat16).float()
+                # fixed rank order in the kernel; the sum here adds the owner's term first: equal to fp32 rounding
+                assert torch.allclose(grads[owner][off:off + cnt], want, rtol=1e-5, atol=1e-6), (owner, b, off)
+    live = torch.zeros(total, dtype=torch.bool)
+    for s in specs:
+        live[s.offset:s.offset + s.count] = True
+    assert torch.equal(covered[live], torch.ones_like(covered[live]))      # every parameter has exactly one owner
