@@ -46,6 +46,8 @@ def main(argv=None) -> int:
     ap.add_argument("--mb", type=int, default=256, help="size of the fp32 gradient bucket in MB")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--ctas", type=int, default=296,
+                    help="CTAs of the two gradient kernels (the transport's default is 2 per SM = 296)")
     a = ap.parse_args(argv)
     from ..ops import cuda as K
     from ..train import mfu
@@ -74,11 +76,11 @@ def main(argv=None) -> int:
     acc = torch.zeros(1, dtype=torch.float64, device=dev)
 
     def push():
-        C.comm_grad_push(grad, rptrs, cap, me, push_rows, first, 1.0 / world, 64)
+        C.comm_grad_push(grad, rptrs, cap, me, push_rows, first, 1.0 / world, a.ctas)
 
     def reduce_local():                                # flag value 0: every "peer" has already arrived
         C.comm_grad_reduce_local(grad, recv[me], cap, world, me, own_rows, share // 8, 1.0 / world, flags[me], 1,
-                                 0, acc, status, 64)
+                                 0, acc, status, a.ctas)
 
     # AdamW + push of the owned slice into `world` parameter buffers
     values = [torch.zeros(n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
