@@ -104,7 +104,7 @@ def run_train(args, sampler_cls):
         now = time.perf_counter()
         line = line.rstrip("\n")
         tail.append(line)
-        del tail[:-12]
+        del tail[:-40]
         m = STEP_RE.match(line)
         if m:
             steps.append((int(m.group(1)), now, float(m.group(4)), float(m.group(3)), m.group(2),
@@ -133,6 +133,14 @@ def run_train(args, sampler_cls):
         pass
     if error is None and len(steps) < total:
         error = "reference process ended early: " + " | ".join(tail[-4:])[-400:]
+    log_dir = os.environ.get("NANOCHAT_REF_LOG_DIR")
+    if log_dir and (error is not None or os.environ.get("NANOCHAT_REF_LOG_ALWAYS") == "1"):
+        try:       # the last lines of this rank's reference process, for the record of a failed run
+            os.makedirs(log_dir, exist_ok=True)
+            with open(os.path.join(log_dir, f"reference_rank{rank}.log"), "w") as f:
+                f.write("\n".join(tail) + "\n")
+        except OSError:
+            pass
     if error is not None:
         return None, error
     timed = steps[args.warmup:total]
@@ -187,8 +195,12 @@ def main(args, sampler_cls=None) -> int:
         failed = float(vals[2]) > 0
         if not failed:
             rec["dev_ms"], rec["e2e_ms"] = float(vals[0]), float(vals[1])
-        elif err is None:
-            err = "another rank's reference process failed"
+        else:
+            # every rank's own account: the first one that is not just "a peer went away" names the cause
+            said = [None] * world
+            dist.all_gather_object(said, err)
+            own = [f"rank {r}: {e}" for r, e in enumerate(said) if e and "timed out waiting for a peer" not in e]
+            err = (own[0] if own else next((f"rank {r}: {e}" for r, e in enumerate(said) if e), err))[:600]
     if rank == 0:
         if err is not None:
             print(json.dumps({"impl": "reference", "unavailable": err}))
