@@ -96,8 +96,8 @@ class FusedTransport:
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
         self.buckets: List[dict] = []
         self.num_slots = 0
-        self.reduce_ctas = 148 * 2
-        self.push_ctas = 148 * 2
+        self.reduce_ctas = int(os.environ.get("NANOCHAT_DP_REDUCE_CTAS", 148 * 2))
+        self.push_ctas = int(os.environ.get("NANOCHAT_DP_PUSH_CTAS", 148 * 2))
 
     # ------------------------------------------------------------------ allocation
     def allocator(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
