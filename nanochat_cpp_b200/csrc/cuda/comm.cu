@@ -535,11 +535,13 @@ void comm_grad_reduce_local(float* grad, const __nv_bfloat16* recv, long long re
 }
 void comm_adamw_push(float* master, const PeerPtrs& values, long long value_offset, int world, const float* grad,
                      float* m, float* v, long long n, float lr, float beta1, float beta2, float eps,
-                     float weight_decay, int step, const float* grad_scale, cudaStream_t s) {
+                     float weight_decay, int step, const float* grad_scale, cudaStream_t s, int max_ctas) {
   if (n <= 0) return;
   const float bias1 = 1.0f - powf(beta1, static_cast<float>(step));
   const float bias2 = 1.0f - powf(beta2, static_cast<float>(step));
-  adamw_push_kernel<<<grid_for(n, 8, 148 * 8), 256, 0, s>>>(master, values, value_offset, world, grad, m, v, n, lr,
+  // max_ctas: eight CTAs of 256 threads fill every thread slot of an SM; beside the Newton-Schulz products (one
+  // 200 KB CTA per SM) the caller asks for two, so that those CTAs can become resident at once
+  adamw_push_kernel<<<grid_for(n, 8, max_ctas > 0 ? max_ctas : 148 * 8), 256, 0, s>>>(master, values, value_offset, world, grad, m, v, n, lr,
                                                            beta1, beta2, eps, weight_decay, 1.0f / bias2, lr / bias1,
                                                            grad_scale);
 }

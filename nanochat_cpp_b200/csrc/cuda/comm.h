@@ -56,7 +56,7 @@ void comm_grad_reduce_local(float* grad, const __nv_bfloat16* recv, long long re
 // (values.p[r] + value_offset): the all-gather is the update's store.
 void comm_adamw_push(float* master, const PeerPtrs& values, long long value_offset, int world, const float* grad,
                      float* m, float* v, long long n, float lr, float beta1, float beta2, float eps,
-                     float weight_decay, int step, const float* grad_scale, cudaStream_t s);
+                     float weight_decay, int step, const float* grad_scale, cudaStream_t s, int max_ctas = 0);
 
 // Muon's last stage (cautious decay + update) for one matrix, pushing the bf16 result to every rank.
 void comm_muon_apply_push(float* master, const PeerPtrs& values, long long value_offset, int world,

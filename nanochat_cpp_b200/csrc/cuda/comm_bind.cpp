@@ -71,13 +71,13 @@ void comm_grad_reduce_local(Tensor& grad, const Tensor& recv, int64_t recv_strid
 
 void comm_adamw_push(Tensor& master, const std::vector<int64_t>& value_ptrs, int64_t value_offset, const Tensor& grad,
                      Tensor& m, Tensor& v, double lr, double beta1, double beta2, double eps, double weight_decay,
-                     int64_t step, const c10::optional<Tensor>& grad_scale, int64_t multicast_ptr) {
+                     int64_t step, const c10::optional<Tensor>& grad_scale, int64_t multicast_ptr, int64_t max_ctas) {
   const c10::cuda::CUDAGuard g(master.device());
   TORCH_CHECK(master.is_contiguous() && grad.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw_push");
   nc::comm_adamw_push(master.data_ptr<float>(), to_peers(value_ptrs, multicast_ptr), value_offset,
                       static_cast<int>(value_ptrs.size()), grad.data_ptr<float>(), m.data_ptr<float>(),
                       v.data_ptr<float>(), master.numel(), lr, beta1, beta2, eps, weight_decay, step,
-                      grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, cur());
+                      grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, cur(), static_cast<int>(max_ctas));
 }
 
 void comm_muon_apply_push(Tensor& master, const std::vector<int64_t>& value_ptrs, int64_t value_offset,
@@ -121,7 +121,8 @@ void register_comm(pybind11::module_& m) {
   m.def("comm_adamw_push", &comm_adamw_push, pybind11::arg("master"), pybind11::arg("value_ptrs"),
         pybind11::arg("value_offset"), pybind11::arg("grad"), pybind11::arg("m"), pybind11::arg("v"), pybind11::arg("lr"),
         pybind11::arg("beta1"), pybind11::arg("beta2"), pybind11::arg("eps"), pybind11::arg("weight_decay"),
-        pybind11::arg("step"), pybind11::arg("grad_scale"), pybind11::arg("multicast_ptr") = 0);
+        pybind11::arg("step"), pybind11::arg("grad_scale"), pybind11::arg("multicast_ptr") = 0,
+        pybind11::arg("max_ctas") = 0);
   m.def("comm_muon_apply_push", &comm_muon_apply_push, pybind11::arg("master"), pybind11::arg("value_ptrs"),
         pybind11::arg("value_offset"), pybind11::arg("xb"), pybind11::arg("scale0"), pybind11::arg("line_scale"),
         pybind11::arg("lines_are_rows"), pybind11::arg("lr"), pybind11::arg("wd"), pybind11::arg("multicast_ptr") = 0);

@@ -98,6 +98,7 @@ class FusedTransport:
         self.num_slots = 0
         self.reduce_ctas = int(os.environ.get("NANOCHAT_DP_REDUCE_CTAS", 148 * 2))
         self.push_ctas = int(os.environ.get("NANOCHAT_DP_PUSH_CTAS", 148 * 2))
+        self.adamw_ctas = int(os.environ.get("NANOCHAT_DP_ADAMW_CTAS", 148 * 2))
 
     # ------------------------------------------------------------------ allocation
     def allocator(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -276,7 +277,10 @@ class FusedTransport:
         from ..ops import cuda as K
         gs = grad_scale.reshape(1) if isinstance(grad_scale, torch.Tensor) else None
         ptrs, mc = self.push_targets()
-        K._C.comm_adamw_push(master, ptrs, offset, grad, m, v, lr, beta1, beta2, eps, weight_decay, step, gs, mc)
+        # two CTAs per SM: the slices run on a side stream beside the Newton-Schulz products, whose CTAs (one per SM,
+        # most of its shared memory) must still find room to become resident
+        K._C.comm_adamw_push(master, ptrs, offset, grad, m, v, lr, beta1, beta2, eps, weight_decay, step, gs, mc,
+                             self.adamw_ctas)
 
     def muon_apply_push(self, master, offset: int, xb, scale0, line_scale, lines_are_rows: bool, lr: float, wd: float):
         from ..ops import cuda as K
