@@ -71,6 +71,38 @@ void nc_emu_embedding_bwd_sorted(const int* sorted_ids, const int* perm, const v
   });
 }
 
+// v += gate * ve (in place), gate saved; with `ids` the value embedding rows are gathered from `ve` as a table.
+void nc_emu_value_gate_fwd(const void* h, long long ldh, const void* ve, const void* gate_w, void* v, long long ldv,
+                           void* gate, int tokens, int KV, int D, const int* ids, int rows, int* status) {
+  const long long pairs = (static_cast<long long>(tokens) * KV + 1) / 2;
+  emu::launch(nc::Grid1(nc::blocks_for_rows(pairs)), nc::Block1(nc::kThreads), 0, [&] {
+    nc::value_gate_fwd_vec_kernel(B(h), ldh, B(ve), B(gate_w), B(v), ldv, B(gate), tokens, KV, D, ids, rows, status);
+  });
+}
+
+void nc_emu_value_gate_bwd(const void* h, long long ldh, const void* ve, const void* gate_w, const void* gate,
+                           const void* dv, long long lddv, void* dve, float* dh12, float* dgw, int tokens, int KV,
+                           int D) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(tokens)), nc::Block1(nc::kThreads), KV * nc::kGateCh * sizeof(float), [&] {
+    nc::value_gate_bwd_vec_kernel(B(h), ldh, B(ve), B(gate_w), B(gate), B(dv), lddv, B(dve), dh12, dgw, tokens, KV, D);
+  });
+}
+
+void nc_emu_smear_fwd(const void* emb, const void* gate_w, const float* lam, const void* prev, void* x0, float* sig,
+                      int tokens, int seq, int dim) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(tokens)), nc::Block1(nc::kThreads), 0,
+              [&] { nc::smear_fwd_kernel(B(emb), B(gate_w), lam, B(prev), B(x0), sig, tokens, seq, dim); });
+}
+
+void nc_emu_qk_prep_bwd(const void* pre, long long ld_pre, const void* grad, long long ld_grad, void* out,
+                        long long ld_out, const float* cosT, const float* sinT, int tokens, int seq, int heads, int D,
+                        float eps, float scale) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(tokens)), nc::Block1(nc::kThreads), 0, [&] {
+    nc::qk_prep_bwd_kernel(B(pre), ld_pre, B(grad), ld_grad, B(out), ld_out, cosT, sinT, tokens, seq, heads, D, eps,
+                           scale);
+  });
+}
+
 // Softcap + cross entropy over bf16 logits, in place (the generic kernel: one block of 256 threads per row).
 void nc_emu_classifier(void* logits, long long ld, const int* targets, float* losses, const float* row_scale,
                        const float* dlogit_scale, int rows, int vocab, int padded, float softcap, int ignore_index,

@@ -357,3 +357,59 @@ def test_whole_model_reduce_scatter_plan_on_emulated_ranks(E, world):
     for s in specs:
         live[s.offset:s.offset + s.count] = True
     assert torch.equal(covered[live], torch.ones_like(covered[live]))      # every parameter has exactly one owner
+
+
+def test_value_gate_forward_with_gathered_rows_and_backward(E):
+    g = torch.Generator().manual_seed(21)
+    M, C, KV, D, vocab = 11, 128, 2, 64, 30
+    h = bf(M, C, gen=g)
+    table = bf(vocab, KV * D, gen=g)
+    gw = bf(KV, 12, scale=0.3, gen=g)
+    ids = torch.randint(0, vocab, (M,), generator=g).int()
+    ids[4] = vocab + 2                                         # outside the table: that row keeps its value
+    v0 = bf(M, KV * D, gen=g)
+    v = v0.clone()
+    gate = torch.zeros(M, KV, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32)
+    E.nc_emu_value_gate_fwd(P(h), ctypes.c_longlong(C), P(table), P(gw), P(v), ctypes.c_longlong(KV * D), P(gate), M, KV, D,
+                            P(ids), vocab, P(status))
+    ok = torch.ones(M, dtype=torch.bool)
+    ok[4] = False
+    ve = table[ids.long().clamp_max(vocab - 1)]
+    want_v, want_gate = ref.value_gate_fwd(h, ve, gw, v0, D)
+    close(v[ok], want_v[ok])
+    close(gate[ok], want_gate[ok])
+    assert torch.equal(v[4], v0[4]) and int(status) == 7
+    # backward on the rows' own value embeddings
+    dv = bf(M, KV * D, gen=g)
+    dve = torch.zeros(M, KV * D, dtype=torch.bfloat16)
+    dh12 = torch.zeros(M, 12)
+    dgw = torch.zeros(KV, 12)
+    E.nc_emu_value_gate_bwd(P(h), ctypes.c_longlong(C), P(ve.contiguous()), P(gw), P(want_gate.contiguous()), P(dv),
+                            ctypes.c_longlong(KV * D), P(dve), P(dh12), P(dgw), M, KV, D)
+    r_dve, r_dh12, r_dgw = ref.value_gate_bwd(h, ve, gw, want_gate, dv, D)
+    close(dve, r_dve)
+    assert torch.allclose(dh12, r_dh12, rtol=2e-2, atol=2e-2) and torch.allclose(dgw, r_dgw, rtol=2e-2, atol=5e-2)
+
+
+def test_smear_forward_and_qk_preparation_backward(E):
+    g = torch.Generator().manual_seed(31)
+    B_, T, C = 2, 7, 64
+    emb = bf(B_ * T, C, gen=g)
+    gw = bf(24, scale=0.3, gen=g)
+    lam = torch.tensor([0.4])
+    x0 = torch.zeros_like(emb)
+    sig = torch.zeros(B_ * T)
+    E.nc_emu_smear_fwd(P(emb), P(gw), P(lam), None, P(x0), P(sig), B_ * T, T, C)
+    want_x0, want_sig = ref.smear_fwd(emb, gw, lam[0], T)
+    close(x0, want_x0)
+    assert torch.allclose(sig, want_sig.reshape(-1), rtol=1e-4, atol=1e-5)
+    heads, D = 3, 64
+    pre, grad = bf(B_, T, heads, D, gen=g), bf(B_, T, heads, D, gen=g)
+    cos, sin = ref.build_rope(T, D, 10000.0, "cpu")
+    out = torch.zeros_like(pre)
+    E.nc_emu_qk_prep_bwd(P(pre), ctypes.c_longlong(heads * D), P(grad), ctypes.c_longlong(heads * D), P(out),
+                         ctypes.c_longlong(heads * D), P(cos.contiguous()), P(sin.contiguous()), B_ * T, T, heads, D,
+                         ctypes.c_float(1e-6), ctypes.c_float(1.2))
+    want, _ = ref.qk_prep_bwd(pre, pre, grad, grad, cos, sin, 1e-6, 1.2)
+    close(out, want, rtol=2.0 ** -6, atol=2.0 ** -6)
