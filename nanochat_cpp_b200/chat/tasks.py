@@ -21,7 +21,8 @@ class Task:
     eval_type = "generative"     # or "categorical"
 
     def __init__(self, rows: Sequence[dict], start: int = 0, stop: Optional[int] = None, step: int = 1):
-        self.rows = list(rows)[start:stop:step]
+        # a row source that can slice itself without reading every row (a parquet-backed dataset) stays lazy
+        self.rows = rows.lazy_slice(start, stop, step) if hasattr(rows, "lazy_slice") else list(rows)[start:stop:step]
 
     @classmethod
     def from_jsonl(cls, path: str, **kw):
@@ -121,7 +122,12 @@ def extract_program(completion: str) -> str:
 
 class HumanEval(Task):
     """Rows: {"prompt", "canonical_solution", "entry_point", "test"}. Programs run in a child interpreter with a
-    time limit."""
+    time limit; pass `executor=` (a callable `code -> result with .success`, e.g. `bridge.hub_data.code_executor()`)
+    to run them under resource limits in a scrubbed environment instead."""
+
+    def __init__(self, rows, *args, executor=None, **kw):
+        super().__init__(rows, *args, **kw)
+        self.executor = executor
 
     def get_example(self, i):
         r = self.rows[i]
@@ -132,6 +138,8 @@ class HumanEval(Task):
     def evaluate(self, conversation, reply, timeout: float = 5.0):
         program = "\n\n".join([extract_imports(conversation["messages"][0]["content"]), extract_program(reply),
                                conversation["test"], f"check({conversation['entry_point']})"])
+        if self.executor is not None:
+            return bool(self.executor(program).success)
         try:
             return subprocess.run([sys.executable, "-I", "-c", program], capture_output=True,
                                   timeout=timeout).returncode == 0
