@@ -8,6 +8,9 @@
   isolation   the process-boundary modules (sandbox, GPU queue, supervisor) import only the standard library: they
               must start on a machine where the package's native parts are not built yet;
   fixtures    the committed fixtures of this package are what its producers give today (fixtures/generate.py --check);
+  contract    both CPU engines (PyTorch operators, native C++) stay inside the per-record bounds of
+              model_specs/nanochat-default.tolerances.json on the reference's fp32 fixtures, the files have the recorded
+              SHA-256, and every record of each file resolves to a bound;
   lint        the house rules of `tools_cli.lint_findings`.
 
 The reference keeps the same kind of facts in step with generators and gates of its own (tools/gen_capi_mirrors.py,
@@ -99,11 +102,22 @@ def fixture_findings() -> List[str]:
     return out
 
 
+def contract_findings() -> List[str]:
+    from . import contract as K
+    contracts = K.load_tolerances()
+    out = []
+    for file in K.PRODUCERS:
+        for engine in K.ENGINES:
+            out += [f"contract: {file} [{engine}] {b}" for b in K.run_fixture(file, engine, contracts=contracts)]
+    return out
+
+
 def run_all(skip_fixtures: bool = False) -> Dict[str, List[str]]:
     from .tools_cli import lint_findings
     res = {"capi": capi_findings(), "isolation": isolation_findings(), "lint": lint_findings()}
     if not skip_fixtures:
         res["fixtures"] = fixture_findings()
+        res["contract"] = contract_findings()
     return res
 
 
