@@ -420,6 +420,9 @@ def register(sub) -> None:
     ap.set_defaults(fn=cmd_lint)
     ap = sub.add_parser("gates", help="consistency gates: C ABI header / library / callers, stdlib isolation, fixtures, lint")
     ap.set_defaults(fn=lambda a: __import__("nanochat_cpp_b200.gates", fromlist=["main"]).main([]))
+    ap = sub.add_parser("pgo", help="pgo init | measure | trace | analyze | compare | report: the measured half of the optimisation loop")
+    ap.add_argument("rest", nargs=argparse.REMAINDER)
+    ap.set_defaults(fn=lambda a: __import__("nanochat_cpp_b200.perf.pgo", fromlist=["main"]).main(a.rest))
     ap = sub.add_parser("contract", help="contract verify [--engine E] | table: per-record tolerance contract of the parity fixtures")
     ap.add_argument("rest", nargs=argparse.REMAINDER)
     ap.set_defaults(fn=lambda a: __import__("nanochat_cpp_b200.contract", fromlist=["main"]).main(a.rest or ["verify"]))
