@@ -990,6 +990,8 @@ __global__ void __launch_bounds__(256) classifier_kernel(bf16* __restrict__ logi
     }
     return;
   }
+  // read before the gradient pass of any warp can overwrite it (see classifier_smem_kernel)
+  const float target_logit = threadIdx.x == 0 ? b2f(lp[target]) : 0.0f;
   // pass 1: online max / sum of exp over the capped logits
   float m = -CUDART_INF_F, l = 0.0f;
   if (vec) {
@@ -1029,9 +1031,8 @@ __global__ void __launch_bounds__(256) classifier_kernel(bf16* __restrict__ logi
     __syncthreads();
   }
   const float lsum = block_sum(m == -CUDART_INF_F ? 0.0f : l * __expf(m - bm), sh);
-  const bool in_range = target >= 0 && target < vocab;
   if (threadIdx.x == 0) {
-    const float tz = in_range ? softcap * tanh_acc(b2f(lp[target]) * inv_cap) : 0.0f;
+    const float tz = softcap * tanh_acc(target_logit * inv_cap);
     losses[row] = logf(lsum) + bm - tz;
   }
   if (!want_grad) return;
@@ -1123,6 +1124,10 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
   }
   const float inv_cap = 1.0f / softcap;
   const float c2 = softcap * 1.4426950408889634f;  // cap * log2(e): exp(z - cap) = 2^(c2 * (t - 1))
+  // The target's logit is read here, before anything is written: after the block-wide sum other warps go straight
+  // on to overwrite the row with its gradient, and a read at that point would race with the thread that owns
+  // the target's position.
+  const float target_logit = threadIdx.x == 0 ? b2f(lp[target]) : 0.0f;
   float l = 0.0f;
   // four 16-byte loads per thread are issued before any of them is used: 32 KB in flight per CTA
   constexpr int kBatch = 4;
@@ -1150,11 +1155,7 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
     }
   }
   const float lsum = block_sum(l, sh);
-  const bool in_range = target >= 0 && target < vocab;
-  if (threadIdx.x == 0) {
-    const float tz = in_range ? softcap * tanh_fast(b2f(lp[target]) * inv_cap) : 0.0f;
-    losses[row] = logf(lsum) + softcap - tz;
-  }
+  if (threadIdx.x == 0) losses[row] = logf(lsum) + softcap - softcap * tanh_fast(target_logit * inv_cap);
   if (!want_grad) return;  // block_sum ended with a barrier: every thread's part of the row is in shared memory
   const float inv = 1.0f / lsum;
   const float scale = *dlogit_scale;

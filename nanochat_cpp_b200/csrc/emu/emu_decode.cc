@@ -59,4 +59,26 @@ void nc_emu_argmax_rows(const void* logits, long long ld, long long* out, int ro
               [&] { nc::argmax_rows_kernel(static_cast<const bf*>(logits), ld, vocab, out); });
 }
 
+// Decode prologue (head_dim 128): q and k heads of the fused projection rows normalised, rotated and scaled; k and the
+// value row written into their page.
+void nc_emu_decode_prep_append(const void* qk, long long ld_qk, const void* v, long long ld_v, const float* cosT,
+                               const float* sinT, const int* positions, const int* page_table, int max_pages,
+                               int page_size, void* q_out, void* k_pool, void* v_pool, int tokens, int H, int KV,
+                               float eps, float scale, int num_pages, int* status) {
+  const int groups = (H + KV + 3) / 4;
+  const int units = tokens * (groups + 1);
+  emu::launch(emu::Dim{static_cast<unsigned>((units + 7) / 8), 1, 1}, emu::Dim{256, 1, 1}, 0, [&] {
+    nc::decode_prep_append_kernel(static_cast<const bf*>(qk), ld_qk, static_cast<const bf*>(v), ld_v, cosT, sinT,
+                                  positions, page_table, max_pages, page_size, static_cast<bf*>(q_out),
+                                  static_cast<bf*>(k_pool), static_cast<bf*>(v_pool), tokens, H, KV, eps, scale,
+                                  num_pages, status);
+  });
+}
+
+void nc_emu_softcap_logits(const void* logits, long long ld, float* out, int rows, int vocab, float cap) {
+  const long long pairs = static_cast<long long>(rows) * vocab / 2;
+  emu::launch(emu::Dim{static_cast<unsigned>((pairs + 255) / 256), 1, 1}, emu::Dim{256, 1, 1}, 0,
+              [&] { nc::softcap_logits_kernel(static_cast<const bf*>(logits), ld, out, rows, vocab, cap); });
+}
+
 }  // extern "C"

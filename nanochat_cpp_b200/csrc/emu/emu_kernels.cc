@@ -113,4 +113,44 @@ void nc_emu_classifier(void* logits, long long ld, const int* targets, float* lo
   });
 }
 
+// The kernel the training step uses by default: 512 threads per row, 16-byte accesses, fixed-cap maximum. `stage`
+// parks the row in dynamic shared memory between the two sweeps.
+void nc_emu_classifier_smem(int stage, void* logits, long long ld, const int* targets, float* losses,
+                            const float* row_scale, const float* dlogit_scale, int rows, int vocab, int padded,
+                            float softcap, int ignore_index, int want_grad, int* status) {
+  if (stage)
+    emu::launch(nc::Grid1(rows), nc::Block1(nc::kClsThreads), want_grad ? static_cast<size_t>(padded) * 2 : 0, [&] {
+      nc::classifier_smem_kernel<true>(B(logits), ld, targets, losses, row_scale, dlogit_scale, vocab, padded, softcap,
+                                       ignore_index, want_grad != 0, status);
+    });
+  else
+    emu::launch(nc::Grid1(rows), nc::Block1(nc::kClsThreads), 0, [&] {
+      nc::classifier_smem_kernel<false>(B(logits), ld, targets, losses, row_scale, dlogit_scale, vocab, padded, softcap,
+                                        ignore_index, want_grad != 0, status);
+    });
+}
+
+void nc_emu_smear_bwd(const void* emb, const void* gate_w, const float* lam, const float* sig, const void* dx0, void* de,
+                      float* dgw24, float* dlam, int tokens, int seq, int dim) {
+  emu::launch(nc::Grid1(nc::blocks_for_rows(tokens)), nc::Block1(nc::kThreads), 0, [&] {
+    nc::smear_bwd_kernel(B(emb), B(gate_w), lam, sig, B(dx0), B(de), dgw24, dlam, tokens, seq, dim);
+  });
+}
+
+// Gradient norm over several fp32 spans: one sum-of-squares launch per span into one fp64 accumulator, then the
+// norm and the clip factor (out2[0], out2[1]).
+void nc_emu_grad_norm(const long long* spans, const long long* lengths, int count, double* acc, float clip, float* out2,
+                      int blocks) {
+  *acc = 0.0;
+  for (int i = 0; i < count; ++i)
+    emu::launch(nc::Grid1(blocks), nc::Block1(256), 0,
+                [&] { nc::sumsq_kernel(reinterpret_cast<const float*>(spans[i]), lengths[i], acc); });
+  emu::launch(nc::Grid1(1), nc::Block1(1), 0, [&] { nc::finish_norm_kernel(acc, clip, out2); });
+}
+
+void nc_emu_add_cols(void* dh, long long ld, const float* extra, int rows, int ncols) {
+  emu::launch(nc::Grid1((rows * ncols + 255) / 256), nc::Block1(256), 0,
+              [&] { nc::add_cols_kernel(B(dh), ld, extra, rows, ncols); });
+}
+
 }  // extern "C"

@@ -24,4 +24,50 @@ void nc_emu_muon_nesterov(const float* grad, float* buf1, float* x, float* row_s
               [&] { nc::muon_nesterov_kernel(grad, buf1, x, row_sumsq, rows, cols, momentum, grad_scale); });
 }
 
+// The element-wise stages of a batched Muon step for one shape group, in the order optim/muon_cuda.py launches them,
+// with the Newton-Schulz products left out (X passes from the first half to the second unchanged): momentum and
+// row sums, equilibration scales, scaled bf16 X, line sums of squares, Muon+ / NorMuon statistics, update.
+void nc_emu_muon_group_no_ns(const long long* grad_ptrs, const long long* buf1_ptrs, const long long* buf2_ptrs,
+                             const long long* master_ptrs, const long long* value_ptrs, float* x32, float* row_ss,
+                             float* row_scale, float* all_scale, void* X, float* line_ss, float* scale,
+                             float* line_scale, int P, int rows, int cols, float momentum, float beta2, float lr,
+                             float weight_decay, const float* grad_scale) {
+  using bf = __nv_bfloat16;
+  const unsigned up = static_cast<unsigned>(P);
+  const emu::Dim by_rows{static_cast<unsigned>((rows + 7) / 8), up, 1}, b256{256, 1, 1};
+  const bool reduce_cols = rows >= cols;
+  const int lines = reduce_cols ? rows : cols, line_len = reduce_cols ? cols : rows;
+  emu::launch(by_rows, b256, 0, [&] {
+    nc::muon_nesterov_batched_kernel(grad_ptrs, buf1_ptrs, x32, row_ss, rows, cols, momentum, grad_scale);
+  });
+  emu::launch(emu::Dim{up, 1, 1}, b256, 0, [&] { nc::muon_prescale_kernel(row_ss, row_scale, all_scale, rows); });
+  emu::launch(by_rows, b256, 0, [&] {
+    nc::muon_scale_rows_batched_kernel(x32, row_scale, all_scale, static_cast<bf*>(X), rows, cols);
+  });
+  const emu::Dim line_grid = reduce_cols ? by_rows : emu::Dim{static_cast<unsigned>((cols / 2 + 255) / 256), up, 1};
+  emu::launch(line_grid, b256, 0,
+              [&] { nc::muon_line_sumsq_kernel(static_cast<const bf*>(X), line_ss, rows, cols, reduce_cols); });
+  emu::launch(emu::Dim{up, 1, 1}, b256, 0, [&] {
+    nc::muon_poststats_kernel(line_ss, buf2_ptrs, scale, line_scale, lines, line_len,
+                              std::sqrt(static_cast<float>(rows < cols ? rows : cols)), beta2);
+  });
+  long long blocks = (static_cast<long long>(rows) * cols / 2 + 255) / 256;
+  if (blocks > 16) blocks = 16;  // grid-stride loop: fewer blocks than the device launch, same coverage
+  emu::launch(emu::Dim{static_cast<unsigned>(blocks), up, 1}, b256, 0, [&] {
+    nc::muon_apply_batched_kernel(master_ptrs, value_ptrs, static_cast<const bf*>(X), scale, line_scale, reduce_cols,
+                                  rows, cols, lr, weight_decay);
+  });
+}
+
+void nc_emu_relu2(const void* x, void* y, long long n, int blocks) {
+  emu::launch(emu::Dim{static_cast<unsigned>(blocks), 1, 1}, emu::Dim{256, 1, 1}, 0, [&] {
+    nc::relu2_kernel(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n);
+  });
+}
+
+void nc_emu_cast(const float* x, void* y, long long n, int blocks) {
+  emu::launch(emu::Dim{static_cast<unsigned>(blocks), 1, 1}, emu::Dim{256, 1, 1}, 0,
+              [&] { nc::cast_kernel(x, static_cast<__nv_bfloat16*>(y), n); });
+}
+
 }  // extern "C"

@@ -413,3 +413,143 @@ def test_smear_forward_and_qk_preparation_backward(E):
                          ctypes.c_float(1e-6), ctypes.c_float(1.2))
     want, _ = ref.qk_prep_bwd(pre, pre, grad, grad, cos, sin, 1e-6, 1.2)
     close(out, want, rtol=2.0 ** -6, atol=2.0 ** -6)
+
+
+@pytest.mark.parametrize("stage", [0, 1])
+@pytest.mark.parametrize("vocab,padded", [(4096, 4096), (8200, 8256)])
+def test_softcap_cross_entropy_vector_kernel(E, stage, vocab, padded):
+    """The kernel of the training step (512 threads per row, 16-byte accesses, fixed-cap maximum), with the row
+    re-read from memory and with the row parked in shared memory."""
+    g = torch.Generator().manual_seed(vocab + stage)
+    rows = 5
+    logits = bf(rows, padded, scale=6.0, gen=g)
+    targets = torch.randint(0, vocab, (rows,), generator=g, dtype=torch.int32)
+    targets[1] = -1                       # ignored
+    targets[3] = vocab + 3                # out of range: treated as ignored, reported
+    scale, rs = torch.tensor([0.37]), torch.rand(rows, generator=g)
+    ok = torch.tensor([True, False, True, False, True])
+    safe = torch.where(ok, targets, torch.full_like(targets, -1))
+    want_l, want_d = ref.classifier_fwd_bwd(logits.clone(), safe, vocab, dlogit_scale=scale[0], row_scale=rs)
+    work, losses, status = logits.clone(), torch.full((rows,), 9.0), torch.zeros(1, dtype=torch.int32)
+    E.nc_emu_classifier_smem(stage, P(work), ctypes.c_longlong(padded), P(targets), P(losses), P(rs), P(scale), rows,
+                             vocab, padded, ctypes.c_float(15.0), -1, 1, P(status))
+    assert int(status) == 7
+    assert torch.allclose(losses, want_l.float(), rtol=2e-3, atol=1e-4)
+    assert float(work[~ok].abs().max()) == 0.0 and float(work[:, vocab:].abs().sum()) == 0.0
+    err = (work.float() - want_d.float()).abs()
+    assert float(err.max()) <= 2e-2 * float(want_d.float().abs().max())
+    # loss only: the logits stay as they were
+    work2, losses2 = logits.clone(), torch.zeros(rows)
+    E.nc_emu_classifier_smem(stage, P(work2), ctypes.c_longlong(padded), P(targets), P(losses2), None, P(scale), rows,
+                             vocab, padded, ctypes.c_float(15.0), -1, 0, P(status))
+    assert torch.equal(work2, logits) and torch.allclose(losses2, losses)
+
+
+def test_smear_backward_and_column_add(E):
+    g = torch.Generator().manual_seed(21)
+    B, T, dim = 2, 9, 64
+    tokens = B * T
+    emb, dx0, gw = bf(tokens, dim, gen=g), bf(tokens, dim, gen=g), bf(24, scale=0.3, gen=g)
+    lam = torch.tensor([0.4])
+    x0 = torch.empty_like(emb)
+    sig = torch.empty(tokens)
+    E.nc_emu_smear_fwd(P(emb), P(gw), P(lam), None, P(x0), P(sig), tokens, T, dim)
+    de, dgw, dlam = torch.empty_like(emb), torch.zeros(24), torch.zeros(1)
+    E.nc_emu_smear_bwd(P(emb), P(gw), P(lam), P(sig), P(dx0), P(de), P(dgw), P(dlam), tokens, T, dim)
+    want_de, want_dgw, want_dlam = ref.smear_bwd(emb, gw, lam, sig, dx0, T)
+    close(de, want_de.reshape(tokens, dim))
+    assert torch.allclose(dgw, want_dgw.float().reshape(-1), rtol=2e-2, atol=2e-2 * float(want_dgw.abs().max()))
+    assert torch.allclose(dlam, want_dlam.float().reshape(-1), rtol=2e-2, atol=1e-3)
+    rows, ld, ncols = 7, 40, 12
+    dh, extra = bf(rows, ld, gen=g), torch.randn(rows, ncols, generator=g)
+    want = dh.clone()
+    want[:, :ncols] = (dh[:, :ncols].float() + extra).to(torch.bfloat16)
+    E.nc_emu_add_cols(P(dh), ctypes.c_longlong(ld), P(extra), rows, ncols)
+    assert torch.equal(dh, want)
+
+
+def test_gradient_norm_and_clip_over_several_spans(E):
+    g = torch.Generator().manual_seed(5)
+    spans = [torch.randn(n, generator=g) for n in (100_003, 17, 4096, 1)]      # tails of every length class
+    acc, out = torch.zeros(1, dtype=torch.float64), torch.zeros(2)
+    E.nc_emu_grad_norm(_ptrs(spans), (ctypes.c_longlong * 4)(*[s.numel() for s in spans]), 4, P(acc),
+                       ctypes.c_float(1.0), P(out), 3)
+    norm = torch.cat(spans).double().norm()
+    assert abs(float(out[0]) - float(norm)) < 1e-3 and abs(float(out[1]) - 1.0 / float(norm)) < 1e-7
+    E.nc_emu_grad_norm(_ptrs(spans), (ctypes.c_longlong * 4)(*[s.numel() for s in spans]), 4, P(acc),
+                       ctypes.c_float(0.0), P(out), 3)
+    assert float(out[1]) == 1.0
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 128), (128, 64), (96, 96)])
+def test_muon_elementwise_stages(E, rows, cols):
+    """Momentum, equilibration, bf16 hand-over, Muon+ / NorMuon statistics and the cautious update for a group of three
+    matrices, against the definition run with no Newton-Schulz iteration."""
+    import math
+    g = torch.Generator().manual_seed(rows * 3 + cols)
+    Pn = 3
+    grads = [torch.randn(rows, cols, generator=g) * 0.02 for _ in range(Pn)]
+    master = [torch.randn(rows, cols, generator=g) * 0.05 for _ in range(Pn)]
+    buf1 = [torch.randn(rows, cols, generator=g) * 0.01 for _ in range(Pn)]
+    lines = rows if rows >= cols else cols
+    buf2 = [torch.rand(lines, generator=g) * 1e-4 for _ in range(Pn)]
+    values = [m.to(torch.bfloat16) for m in master]
+    gs = torch.tensor([0.5])
+    kw = dict(lr=0.02, momentum=0.9, beta2=0.95, weight_decay=0.1)
+    rm, rb1, rb2 = torch.stack(master).clone(), torch.stack(buf1).clone(), torch.stack(buf2).clone()
+    rv = torch.stack(values).clone()
+    ref.muon_update(torch.stack(grads), rm, rv, rb1, rb2, ns_steps=0, grad_scale=0.5, **kw)
+    x32, X = torch.empty(Pn, rows, cols), torch.empty(Pn, rows, cols, dtype=torch.bfloat16)
+    row_ss, row_scale, all_scale = torch.empty(Pn, rows), torch.empty(Pn, rows), torch.empty(Pn)
+    line_ss, scale, line_scale = torch.empty(Pn, lines), torch.empty(Pn), torch.empty(Pn, lines)
+    before = [m.clone() for m in master]
+    E.nc_emu_muon_group_no_ns(_ptrs(grads), _ptrs(buf1), _ptrs(buf2), _ptrs(master), _ptrs(values), P(x32), P(row_ss),
+                              P(row_scale), P(all_scale), P(X), P(line_ss), P(scale), P(line_scale), Pn, rows, cols,
+                              ctypes.c_float(kw["momentum"]), ctypes.c_float(kw["beta2"]), ctypes.c_float(kw["lr"]),
+                              ctypes.c_float(kw["weight_decay"]), P(gs))
+    assert torch.allclose(torch.stack(buf1), rb1, rtol=1e-5, atol=1e-8)
+    assert torch.allclose(torch.stack(buf2), rb2, rtol=2e-2, atol=1e-7)          # X passed through bf16
+    # after equilibration and normalisation every matrix has Frobenius norm 1 / 1.01
+    assert torch.allclose(X.float().flatten(1).norm(dim=1), torch.full((Pn,), 1 / 1.01), rtol=5e-3)
+    upd, want = torch.stack(master) - torch.stack(before), rm - torch.stack(before)
+    assert float((upd - want).norm() / want.norm()) < 1e-2
+    assert float(upd.flatten(1).norm(dim=1).mean()) > 0.5 * kw["lr"] * math.sqrt(min(rows, cols))
+    for p in range(Pn):
+        assert torch.equal(values[p], master[p].to(torch.bfloat16))
+
+
+def test_decode_prologue_and_soft_capped_logits(E):
+    g = torch.Generator().manual_seed(12)
+    B, H, KV, D, page, pages = 3, 4, 2, 128, 16, 6
+    qkv = bf(B, (H + 2 * KV) * D, gen=g)
+    qk, v = qkv[:, :(H + KV) * D], qkv[:, (H + KV) * D:]
+    cos, sin = ref.build_rope(64, D, 10000.0)
+    cos, sin = cos.reshape(64, D // 2).float().contiguous(), sin.reshape(64, D // 2).float().contiguous()
+    positions = torch.tensor([5, 33, 16], dtype=torch.int32)
+    table = torch.tensor([[0, -1, -1], [1, 2, 3], [4, 5, -1]], dtype=torch.int32)
+    k_pool = torch.zeros(pages, page, KV, D, dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    q_out, status = torch.empty(B, H, D, dtype=torch.bfloat16), torch.zeros(1, dtype=torch.int32)
+    E.nc_emu_decode_prep_append(P(qk), ctypes.c_longlong(qkv.stride(0)), P(v), ctypes.c_longlong(qkv.stride(0)), P(cos),
+                                P(sin), P(positions), P(table), 3, page, P(q_out), P(k_pool), P(v_pool), B, H, KV,
+                                ctypes.c_float(1e-6), ctypes.c_float(1.2), pages, P(status))
+    assert int(status) == 0
+    for b in range(B):
+        pos = int(positions[b])
+        c, s = cos[pos].view(1, 1, 1, D // 2), sin[pos].view(1, 1, 1, D // 2)
+        qw, kw_ = ref.qk_prep_fwd(qk[b, :H * D].reshape(1, 1, H, D), qk[b, H * D:].reshape(1, 1, KV, D), c, s, 1e-6, 1.2)
+        close(q_out[b], qw.reshape(H, D))
+        pg = int(table[b, pos // page])
+        close(k_pool[pg, pos % page], kw_.reshape(KV, D))
+        assert torch.equal(v_pool[pg, pos % page], v[b].reshape(KV, D))
+    assert int((k_pool.float().abs().sum((1, 2, 3)) > 0).sum()) == 3            # one page touched per sequence
+    # a position whose page is not mapped: skipped and reported
+    positions[0] = 20
+    E.nc_emu_decode_prep_append(P(qk), ctypes.c_longlong(qkv.stride(0)), P(v), ctypes.c_longlong(qkv.stride(0)), P(cos),
+                                P(sin), P(positions), P(table), 3, page, P(q_out), P(k_pool), P(v_pool), B, H, KV,
+                                ctypes.c_float(1e-6), ctypes.c_float(1.2), pages, P(status))
+    assert int(status) == 7
+    logits = bf(3, 72, scale=20.0, gen=g)
+    out = torch.empty(3, 70)
+    E.nc_emu_softcap_logits(P(logits), ctypes.c_longlong(72), P(out), 3, 70, ctypes.c_float(15.0))
+    assert torch.allclose(out, 15.0 * torch.tanh(logits[:, :70].float() / 15.0), rtol=1e-5, atol=1e-5)
