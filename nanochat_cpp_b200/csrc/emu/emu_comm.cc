@@ -59,4 +59,18 @@ void nc_emu_adamw_push(float* master, const long long* value_ptrs, int world, lo
   });
 }
 
+// The Muon update of a shape group with the new bf16 parameters stored into every rank's parameter buffer
+// (value_offsets: element offset of each matrix in those buffers).
+void nc_emu_muon_apply_push_batched(const long long* master_ptrs, const long long* value_offsets,
+                                    const long long* value_ptrs, int world, const void* xb, const float* scale0,
+                                    const float* line_scale, int lines_are_rows, int P, int rows, int cols, float lr,
+                                    float weight_decay, int ctas) {
+  const nc::PeerPtrs values = Peers(value_ptrs, world);
+  emu::launch(emu::Dim{static_cast<unsigned>(ctas), static_cast<unsigned>(P), 1}, D1(256), 0, [&] {
+    nc::muon_apply_push_batched_kernel(master_ptrs, value_offsets, values, world,
+                                       static_cast<const __nv_bfloat16*>(xb), scale0, line_scale, lines_are_rows != 0,
+                                       rows, cols, lr, weight_decay);
+  });
+}
+
 }  // extern "C"

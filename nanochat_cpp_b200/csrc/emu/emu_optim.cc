@@ -70,4 +70,13 @@ void nc_emu_cast(const float* x, void* y, long long n, int blocks) {
               [&] { nc::cast_kernel(x, static_cast<__nv_bfloat16*>(y), n); });
 }
 
+void nc_emu_muon_apply_batched(const long long* master_ptrs, const long long* value_ptrs, const void* xb,
+                               const float* scale0, const float* line_scale, int lines_are_rows, int P, int rows,
+                               int cols, float lr, float weight_decay, int ctas) {
+  emu::launch(emu::Dim{static_cast<unsigned>(ctas), static_cast<unsigned>(P), 1}, emu::Dim{256, 1, 1}, 0, [&] {
+    nc::muon_apply_batched_kernel(master_ptrs, value_ptrs, static_cast<const __nv_bfloat16*>(xb), scale0, line_scale,
+                                  lines_are_rows != 0, rows, cols, lr, weight_decay);
+  });
+}
+
 }  // extern "C"

@@ -553,3 +553,35 @@ def test_decode_prologue_and_soft_capped_logits(E):
     out = torch.empty(3, 70)
     E.nc_emu_softcap_logits(P(logits), ctypes.c_longlong(72), P(out), 3, 70, ctypes.c_float(15.0))
     assert torch.allclose(out, 15.0 * torch.tanh(logits[:, :70].float() / 15.0), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("rows,cols,lines_are_rows", [(64, 128, 0), (128, 64, 1)])
+def test_muon_update_pushed_into_every_rank(E, rows, cols, lines_are_rows):
+    """The data-parallel form of the Muon update writes the same master weights as the local form, bit for bit, and
+    leaves their bf16 copy at each matrix's offset in every rank's parameter buffer (and nowhere else)."""
+    g = torch.Generator().manual_seed(rows + cols)
+    Pn, world = 3, 4
+    lines = rows if lines_are_rows else cols
+    X = bf(Pn, rows, cols, scale=0.1, gen=g)
+    scale0, line_scale = torch.rand(Pn, generator=g) + 0.5, torch.rand(Pn, lines, generator=g) + 0.5
+    local = [torch.randn(rows, cols, generator=g) * 0.05 for _ in range(Pn)]
+    pushed = [m.clone() for m in local]
+    local_vals = [torch.zeros(rows, cols, dtype=torch.bfloat16) for _ in range(Pn)]
+    E.nc_emu_muon_apply_batched(_ptrs(local), _ptrs(local_vals), P(X), P(scale0), P(line_scale), lines_are_rows, Pn,
+                                rows, cols, ctypes.c_float(0.02), ctypes.c_float(0.1), 5)
+    n = rows * cols
+    offsets = [16, 16 + n + 64, 16 + 2 * n + 128]                    # gaps between the matrices stay untouched
+    total = offsets[-1] + n + 40
+    bufs = [torch.full((total,), 7.0, dtype=torch.bfloat16) for _ in range(world)]
+    E.nc_emu_muon_apply_push_batched(_ptrs(pushed), (ctypes.c_longlong * Pn)(*offsets), _ptrs(bufs), world, P(X),
+                                     P(scale0), P(line_scale), lines_are_rows, Pn, rows, cols, ctypes.c_float(0.02),
+                                     ctypes.c_float(0.1), 3)
+    for p in range(Pn):
+        assert torch.equal(pushed[p], local[p])
+    keep = torch.ones(total, dtype=torch.bool)
+    for p, off in enumerate(offsets):
+        keep[off:off + n] = False
+        for r in range(world):
+            assert torch.equal(bufs[r][off:off + n], local_vals[p].reshape(-1)), (p, r)
+    for r in range(world):
+        assert bool((bufs[r][keep] == 7.0).all())
