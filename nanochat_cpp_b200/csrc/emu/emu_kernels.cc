@@ -153,4 +153,15 @@ void nc_emu_add_cols(void* dh, long long ld, const float* extra, int rows, int n
               [&] { nc::add_cols_kernel(B(dh), ld, extra, rows, ncols); });
 }
 
+// Self-test of the scheduler: 64 threads write their index in the order in which they first run, then meet at a
+// barrier and write it again in the order in which they leave it.
+void nc_emu_selftest_order(int* first_run, int* after_barrier) {
+  int n1 = 0, n2 = 0;
+  emu::launch(nc::Grid1(1), nc::Block1(64), 0, [&] {
+    first_run[n1++] = static_cast<int>(threadIdx.x);
+    __syncthreads();
+    after_barrier[n2++] = static_cast<int>(threadIdx.x);
+  });
+}
+
 }  // extern "C"

@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <memory>
+#include <utility>
 #include <vector>
 
 namespace emu {
@@ -44,6 +45,17 @@ struct Block {
   std::vector<char> shared;
   const std::function<void()>* body = nullptr;
 };
+
+// Order in which the runnable fibers of a block are resumed in each pass: 0 ascending thread index, 1 descending,
+// 2 a fresh pseudo-random permutation per pass. A kernel whose result depends on the order has a race between
+// threads that no barrier orders; running it under several schedules and comparing the outputs finds such races.
+int g_schedule_mode = 0;
+unsigned long long g_schedule_state = 1;
+
+unsigned NextRandom() {
+  g_schedule_state = g_schedule_state * 6364136223846793005ull + 1442695040888963407ull;
+  return static_cast<unsigned>(g_schedule_state >> 33);
+}
 
 thread_local Block* g_block = nullptr;
 thread_local ThreadState g_outside;   // coordinates seen by code that is not inside a launch
@@ -150,6 +162,8 @@ void launch(Dim grid, Dim block, size_t dynamic_shared_bytes, const std::functio
   b.shared.assign(dynamic_shared_bytes + 16, 0);
   Block* outer = g_block;
   g_block = &b;
+  std::vector<int> order(static_cast<size_t>(threads));
+  for (int t = 0; t < threads; ++t) order[static_cast<size_t>(t)] = g_schedule_mode == 1 ? threads - 1 - t : t;
   for (unsigned bz = 0; bz < grid.z; ++bz)
     for (unsigned by = 0; by < grid.y; ++by)
       for (unsigned bx = 0; bx < grid.x; ++bx) {
@@ -173,7 +187,11 @@ void launch(Dim grid, Dim block, size_t dynamic_shared_bytes, const std::functio
         }
         // round-robin until every fiber has returned; a full pass in which nothing changes is a deadlock
         while (b.live > 0) {
-          for (int t = 0; t < threads && b.live > 0; ++t) {
+          if (g_schedule_mode == 2) {
+            for (int i = threads - 1; i > 0; --i) std::swap(order[static_cast<size_t>(i)], order[NextRandom() % (i + 1)]);
+          }
+          for (int k = 0; k < threads && b.live > 0; ++k) {
+            const int t = order[static_cast<size_t>(k)];
             if (b.fibers[static_cast<size_t>(t)].done) continue;
             b.current = t;
             swapcontext(&b.scheduler, &b.fibers[static_cast<size_t>(t)].ctx);
@@ -185,3 +203,9 @@ void launch(Dim grid, Dim block, size_t dynamic_shared_bytes, const std::functio
 }
 
 }  // namespace emu
+
+// mode: 0 ascending, 1 descending, 2 random per pass (seeded). Applies to every later launch of this process.
+extern "C" void nc_emu_set_schedule(int mode, unsigned long long seed) {
+  emu::g_schedule_mode = mode;
+  emu::g_schedule_state = seed * 2 + 1;
+}

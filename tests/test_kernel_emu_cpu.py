@@ -15,9 +15,17 @@ LIB = os.path.join(os.path.dirname(nanochat_cpp_b200.__file__), "libnc_emu.so")
 pytestmark = pytest.mark.skipif(not os.path.exists(LIB), reason="host build of the kernels not present")
 
 
-@pytest.fixture(scope="module")
-def E():
-    return ctypes.CDLL(LIB)
+SCHEDULES = {"ascending": 0, "descending": 1, "shuffled": 2}
+
+
+@pytest.fixture(scope="module", params=list(SCHEDULES))
+def E(request):
+    """Every test of this file runs under three fiber schedules (threads of a block resumed in ascending, descending
+    and per-pass shuffled order). The kernels have to give the expected result under each: an ordering between
+    threads that no barrier, shuffle or atomic enforces shows up as a failure of one of the three."""
+    lib = ctypes.CDLL(LIB)
+    lib.nc_emu_set_schedule(SCHEDULES[request.param], ctypes.c_ulonglong(20240229))
+    return lib
 
 
 def P(t):
@@ -585,3 +593,19 @@ def test_muon_update_pushed_into_every_rank(E, rows, cols, lines_are_rows):
             assert torch.equal(bufs[r][off:off + n], local_vals[p].reshape(-1)), (p, r)
     for r in range(world):
         assert bool((bufs[r][keep] == 7.0).all())
+
+
+def test_the_three_schedules_differ(request):
+    lib = ctypes.CDLL(LIB)
+    seen = {}
+    for name, mode in SCHEDULES.items():
+        lib.nc_emu_set_schedule(mode, ctypes.c_ulonglong(7))
+        a, b = torch.zeros(64, dtype=torch.int32), torch.zeros(64, dtype=torch.int32)
+        lib.nc_emu_selftest_order(P(a), P(b))
+        assert sorted(a.tolist()) == list(range(64)) and sorted(b.tolist()) == list(range(64))
+        seen[name] = (a.tolist(), b.tolist())
+    assert seen["ascending"][0] == list(range(64)) and seen["descending"][0] == list(range(63, -1, -1))
+    assert seen["shuffled"][0] not in (seen["ascending"][0], seen["descending"][0])
+    # the thread that completes a barrier goes on first: leaving order is not arrival order
+    assert seen["ascending"][1][0] == 63 and seen["descending"][1][0] == 0
+    lib.nc_emu_set_schedule(0, ctypes.c_ulonglong(1))
