@@ -136,7 +136,7 @@ FAMILIES = [
     ("muon", "fused_muon", "optim.muon_* + batched tcgen05 Newton-Schulz"),
     ("adamw", "fused_adamw", "optim.adamw / comm.adamw_push"),
     ("decode_attention", "paged_kv_decode", "decode.paged_decode (split-KV)"),
-    ("gradient_sync", "peer_reduce_scatter", "comm.reduce_pull + update-and-push"),
+    ("gradient_sync", "peer_reduce_scatter", "comm.grad_push + grad_reduce_local + update-and-push"),
 ]
 
 
