@@ -1081,6 +1081,7 @@ __global__ void __launch_bounds__(256) classifier_kernel(bf16* __restrict__ logi
 #ifdef NC_EMU
 __device__ __forceinline__ float tanh_fast(float x) { return std::tanh(x); }
 __device__ __forceinline__ float ex2_fast(float x) { return std::exp2(x); }
+__device__ __forceinline__ float lg2_fast(float x) { return std::log2(x); }
 #else
 __device__ __forceinline__ float tanh_fast(float x) {
   float y;
@@ -1092,6 +1093,11 @@ __device__ __forceinline__ float ex2_fast(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float lg2_fast(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 #endif
 
 constexpr int kClsThreads = 512;
@@ -1099,7 +1105,14 @@ constexpr int kClsThreads = 512;
 // STAGE: the row is parked in shared memory between the two passes (one CTA per SM for a 64K-entry row). Without it
 // the second pass reads the row again through L2, where the first pass left it, and several CTAs share an SM, so one
 // CTA's exponentials overlap another's loads and stores.
-template <bool STAGE>
+// CACHE (without STAGE, gradient wanted): the first sweep writes e = exp(z - cap) back over the logit it came from,
+// as bf16, and the second sweep rebuilds both factors of the gradient from it: p = e / sum and, since
+// log2(e) = cap * log2(e) * (t - 1), 1 - t = -log2(e) / c2 and 1 - t^2 = (1 - t)(1 + t). That is one lg2 in place of
+// a tanh and an ex2: three special-function operations per logit instead of four, on a kernel that is bound by that
+// unit. The row stays in L2 between the sweeps either way; the extra store of the first sweep is overwritten by the
+// gradient before it has to leave L2. e carries bf16 rounding (2^-9 relative) into p, of the size of the rounding the
+// gradient itself gets; 1 - t comes out with an absolute error of about 1e-4.
+template <bool STAGE, bool CACHE = false>
 __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
     bf16* __restrict__ logits, long long ld, const int* __restrict__ targets, float* __restrict__ losses,
     const float* __restrict__ row_scale, const float* __restrict__ dlogit_scale, int vocab, int padded,
@@ -1127,7 +1140,11 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
   // The target's logit is read here, before anything is written: after the block-wide sum other warps go straight
   // on to overwrite the row with its gradient, and a read at that point would race with the thread that owns
   // the target's position.
-  const float target_logit = threadIdx.x == 0 ? b2f(lp[target]) : 0.0f;
+  // (With CACHE the first sweep overwrites the row itself, so there the thread that owns the target's vector hands
+  // its logit over through shared memory.)
+  __shared__ float sh_target;
+  float target_logit = (!CACHE && threadIdx.x == 0) ? b2f(lp[target]) : 0.0f;
+  const bool cache = CACHE && want_grad;
   float l = 0.0f;
   // four 16-byte loads per thread are issued before any of them is used: 32 KB in flight per CTA
   constexpr int kBatch = 4;
@@ -1146,18 +1163,31 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
       if (i >= vocab) break;
       if (STAGE && want_grad) *reinterpret_cast<uint4*>(row_s + i) = raw[u];
       const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+      if (CACHE && static_cast<unsigned>(target - i) < 8u) {
+        const uint32_t tw = w[(target - i) >> 1];
+        sh_target = __uint_as_float(((target - i) & 1) ? (tw & 0xffff0000u) : (tw << 16));
+      }
+      uint32_t packed[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float t0 = tanh_fast(__uint_as_float(w[e] << 16) * inv_cap);
         const float t1 = tanh_fast(__uint_as_float(w[e] & 0xffff0000u) * inv_cap);
-        l += ex2_fast(fmaf(c2, t0, -c2)) + ex2_fast(fmaf(c2, t1, -c2));
+        const float e0 = ex2_fast(fmaf(c2, t0, -c2)), e1 = ex2_fast(fmaf(c2, t1, -c2));
+        l += e0 + e1;
+        if (CACHE) {
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
+          packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
       }
+      if (cache) *reinterpret_cast<uint4*>(lp + i) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
   }
   const float lsum = block_sum(l, sh);
+  if (CACHE) target_logit = sh_target;  // written before the barriers of block_sum
   if (threadIdx.x == 0) losses[row] = logf(lsum) + softcap - softcap * tanh_fast(target_logit * inv_cap);
   if (!want_grad) return;  // block_sum ended with a barrier: every thread's part of the row is in shared memory
   const float inv = 1.0f / lsum;
+  const float neg_inv_c2 = -1.0f / c2;
   const float scale = *dlogit_scale;
   const float rs = row_scale ? row_scale[row] : 1.0f;
   for (int i = threadIdx.x * 8; i < padded; i += kClsThreads * 8) {
@@ -1168,15 +1198,23 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
       uint32_t o[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float t0 = tanh_fast(__uint_as_float(w[e] << 16) * inv_cap);
-        const float t1 = tanh_fast(__uint_as_float(w[e] & 0xffff0000u) * inv_cap);
-        const float p0 = ex2_fast(fmaf(c2, t0, -c2)) * inv;
-        const float p1 = ex2_fast(fmaf(c2, t1, -c2)) * inv;
+        float p0, p1, d0, d1;  // probability and 1 - t^2
+        if (CACHE) {
+          const float e0 = __uint_as_float(w[e] << 16), e1 = __uint_as_float(w[e] & 0xffff0000u);
+          const float s0 = lg2_fast(e0) * neg_inv_c2, s1 = lg2_fast(e1) * neg_inv_c2;  // 1 - t
+          p0 = e0 * inv, p1 = e1 * inv;
+          d0 = s0 * (2.0f - s0), d1 = s1 * (2.0f - s1);
+        } else {
+          const float t0 = tanh_fast(__uint_as_float(w[e] << 16) * inv_cap);
+          const float t1 = tanh_fast(__uint_as_float(w[e] & 0xffff0000u) * inv_cap);
+          p0 = ex2_fast(fmaf(c2, t0, -c2)) * inv, p1 = ex2_fast(fmaf(c2, t1, -c2)) * inv;
+          d0 = 1.0f - t0 * t0, d1 = 1.0f - t1 * t1;
+        }
         const float h0 = (i + 2 * e == target) ? 1.0f : 0.0f;
         const float h1 = (i + 2 * e + 1 == target) ? 1.0f : 0.0f;
         // rounded once before the loss scale, as the two-pass definition does
-        const float g0 = b2f(f2b((p0 - h0) * (1.0f - t0 * t0) * rs)) * scale;
-        const float g1 = b2f(f2b((p1 - h1) * (1.0f - t1 * t1) * rs)) * scale;
+        const float g0 = b2f(f2b((p0 - h0) * d0 * rs)) * scale;
+        const float g1 = b2f(f2b((p1 - h1) * d1 * rs)) * scale;
         const __nv_bfloat162 pk = __floats2bfloat162_rn(g0, g1);
         o[e] = *reinterpret_cast<const uint32_t*>(&pk);
       }
@@ -1370,9 +1408,17 @@ void classifier_fwd_bwd(bf16* logits, long long ld, const int* targets, float* l
     const char* e = getenv("NANOCHAT_CLS_STAGE");
     return e != nullptr && e[0] == '1';
   }();
+  static const bool cache = [] {
+    const char* e = getenv("NANOCHAT_CLS_CACHE");
+    return e == nullptr || e[0] != '0';
+  }();
   if (vec && !stage) {
-    classifier_smem_kernel<false><<<rows, kClsThreads, 0, s>>>(logits, ld, targets, losses, row_scale, dlogit_scale,
-                                                               vocab, padded, softcap, ignore_index, want_grad, status);
+    if (cache && want_grad)
+      classifier_smem_kernel<false, true><<<rows, kClsThreads, 0, s>>>(
+          logits, ld, targets, losses, row_scale, dlogit_scale, vocab, padded, softcap, ignore_index, want_grad, status);
+    else
+      classifier_smem_kernel<false><<<rows, kClsThreads, 0, s>>>(logits, ld, targets, losses, row_scale, dlogit_scale,
+                                                                 vocab, padded, softcap, ignore_index, want_grad, status);
     return;
   }
   if (vec && row_bytes <= 200 * 1024) {

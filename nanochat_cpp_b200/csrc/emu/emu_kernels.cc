@@ -114,11 +114,16 @@ void nc_emu_classifier(void* logits, long long ld, const int* targets, float* lo
 }
 
 // The kernel the training step uses by default: 512 threads per row, 16-byte accesses, fixed-cap maximum. `stage`
-// parks the row in dynamic shared memory between the two sweeps.
+// parks the row in dynamic shared memory between the two sweeps; stage 2 is the variant that caches exp(z - cap) in place.
 void nc_emu_classifier_smem(int stage, void* logits, long long ld, const int* targets, float* losses,
                             const float* row_scale, const float* dlogit_scale, int rows, int vocab, int padded,
                             float softcap, int ignore_index, int want_grad, int* status) {
-  if (stage)
+  if (stage == 2)
+    emu::launch(nc::Grid1(rows), nc::Block1(nc::kClsThreads), 0, [&] {
+      nc::classifier_smem_kernel<false, true>(B(logits), ld, targets, losses, row_scale, dlogit_scale, vocab, padded,
+                                              softcap, ignore_index, want_grad != 0, status);
+    });
+  else if (stage)
     emu::launch(nc::Grid1(rows), nc::Block1(nc::kClsThreads), want_grad ? static_cast<size_t>(padded) * 2 : 0, [&] {
       nc::classifier_smem_kernel<true>(B(logits), ld, targets, losses, row_scale, dlogit_scale, vocab, padded, softcap,
                                        ignore_index, want_grad != 0, status);

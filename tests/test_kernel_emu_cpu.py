@@ -423,11 +423,11 @@ def test_smear_forward_and_qk_preparation_backward(E):
     close(out, want, rtol=2.0 ** -6, atol=2.0 ** -6)
 
 
-@pytest.mark.parametrize("stage", [0, 1])
+@pytest.mark.parametrize("stage", [0, 1, 2])
 @pytest.mark.parametrize("vocab,padded", [(4096, 4096), (8200, 8256)])
 def test_softcap_cross_entropy_vector_kernel(E, stage, vocab, padded):
     """The kernel of the training step (512 threads per row, 16-byte accesses, fixed-cap maximum), with the row
-    re-read from memory and with the row parked in shared memory."""
+    re-read from memory, with the row parked in shared memory, and with exp(z - cap) cached in place (2)."""
     g = torch.Generator().manual_seed(vocab + stage)
     rows = 5
     logits = bf(rows, padded, scale=6.0, gen=g)
