@@ -320,6 +320,157 @@ __global__ void __launch_bounds__(256) muon_apply_batched_kernel(const long long
   }
 }
 
+// The whole Muon step of a stack of small matrices (rows * cols <= 1024, e.g. the 10 x 12 value-gate projections and the
+// 1 x 24 smear gate), one CTA per matrix, fp32 in shared memory: momentum and Nesterov blend, row equilibration and
+// Frobenius normalisation, `ns_steps` Polar Express iterations, Muon+ rescale, NorMuon second moment and line step,
+// cautious decay and update. Same arithmetic, in the same order, as the definition in ops/ref.py::muon_update
+// (reference backends/cpu/kernels.cc:1614-1810); sums that the definition takes in double are taken in double here.
+constexpr int kTinyMax = 1024;   // elements of one matrix
+constexpr int kTinySide = 32;    // the smaller dimension
+
+// Block-wide sum in a fixed order (every thread adds the same 128 partial sums): the result does not depend on how
+// the warps are scheduled.
+__device__ __forceinline__ double tiny_sum(double v, double* red) {
+  __syncthreads();
+  red[threadIdx.x] = v;
+  __syncthreads();
+  double t = 0.0;
+  for (int w = 0; w < static_cast<int>(blockDim.x); ++w) t += red[w];
+  return t;
+}
+
+struct TinyCoeffs {
+  float c[5][3];
+};
+
+__global__ void __launch_bounds__(128) muon_tiny_kernel(const long long* __restrict__ grad_ptrs,
+                                                        const long long* __restrict__ buf1_ptrs,
+                                                        const long long* __restrict__ buf2_ptrs,
+                                                        const long long* __restrict__ master_ptrs,
+                                                        const long long* __restrict__ value_ptrs, int rows, int cols,
+                                                        float mu, float beta2, float lr, float wd, int ns_steps,
+                                                        const float* grad_scale, TinyCoeffs coeffs) {
+  __shared__ float X[kTinyMax], Y[kTinyMax], A[kTinySide * kTinySide], Bm[kTinySide * kTinySide];
+  __shared__ float line[kTinyMax];   // per-row scale, later per-line step (lines <= rows * cols)
+  __shared__ double red[128];
+  const int p = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+  const int n = rows * cols;
+  const float* grad = reinterpret_cast<const float*>(grad_ptrs[p]);
+  float* buf1 = reinterpret_cast<float*>(buf1_ptrs[p]);
+  float* buf2 = reinterpret_cast<float*>(buf2_ptrs[p]);
+  float* master = reinterpret_cast<float*>(master_ptrs[p]);
+  __nv_bfloat16* value = value_ptrs != nullptr ? reinterpret_cast<__nv_bfloat16*>(value_ptrs[p]) : nullptr;
+  const float gs = grad_scale ? *grad_scale : 1.0f;
+  // 1. momentum, Nesterov blend
+  double ss = 0.0;
+  for (int i = tid; i < n; i += nt) {
+    const float g = grad[i] * gs;
+    const float b = buf1[i] + (1.0f - mu) * (g - buf1[i]);
+    buf1[i] = b;
+    const float x = (1.0f - mu) * g + mu * b;
+    X[i] = x;
+    ss += static_cast<double>(x) * x;
+  }
+  // 2. every row to the mean row norm
+  const float frob = static_cast<float>(sqrt(tiny_sum(ss, red)));
+  const float target = frob / sqrtf(static_cast<float>(rows));
+  for (int r = tid; r < rows; r += nt) {
+    double rs = 0.0;
+    for (int c = 0; c < cols; ++c) rs += static_cast<double>(X[r * cols + c]) * X[r * cols + c];
+    line[r] = target / fmaxf(static_cast<float>(sqrt(rs)), 1e-6f);
+  }
+  __syncthreads();
+  ss = 0.0;
+  for (int i = tid; i < n; i += nt) {
+    const float x = X[i] * line[i / cols];
+    X[i] = x;
+    ss += static_cast<double>(x) * x;
+  }
+  // 3. Frobenius normalisation
+  const float frob2 = static_cast<float>(sqrt(tiny_sum(ss, red)));
+  const float inv_norm = 1.0f / (frob2 * 1.01f + 1e-6f);
+  for (int i = tid; i < n; i += nt) X[i] *= inv_norm;
+  __syncthreads();
+  // 4. Polar Express: A = X^T X (tall) or X X^T, B = cb A + cc A A, X = ca X + X B (tall) or ca X + B X
+  const bool tall = rows > cols;
+  const int k = tall ? cols : rows;   // side of A
+  float* Xc = X;
+  float* Xn = Y;
+  for (int it = 0; it < ns_steps && it < 5; ++it) {
+    const float ca = coeffs.c[it][0], cb = coeffs.c[it][1], cc = coeffs.c[it][2];
+    for (int e = tid; e < k * k; e += nt) {
+      const int i = e / k, j = e - i * k;
+      float acc = 0.0f;
+      if (tall) {
+        for (int r = 0; r < rows; ++r) acc += Xc[r * cols + i] * Xc[r * cols + j];
+      } else {
+        for (int c = 0; c < cols; ++c) acc += Xc[i * cols + c] * Xc[j * cols + c];
+      }
+      A[e] = acc;
+    }
+    __syncthreads();
+    for (int e = tid; e < k * k; e += nt) {
+      const int i = e / k, j = e - i * k;
+      float acc = 0.0f;
+      for (int q = 0; q < k; ++q) acc += A[i * k + q] * A[q * k + j];
+      Bm[e] = cb * A[e] + cc * acc;
+    }
+    __syncthreads();
+    for (int e = tid; e < n; e += nt) {
+      const int r = e / cols, c = e - r * cols;
+      float acc = 0.0f;
+      if (tall) {
+        for (int q = 0; q < cols; ++q) acc += Xc[r * cols + q] * Bm[q * k + c];
+      } else {
+        for (int q = 0; q < rows; ++q) acc += Bm[r * k + q] * Xc[q * cols + c];
+      }
+      Xn[e] = ca * Xc[e] + acc;
+    }
+    __syncthreads();
+    float* t = Xc;
+    Xc = Xn;
+    Xn = t;
+  }
+  // 5. Muon+: snap the norm to sqrt(min(rows, cols))
+  ss = 0.0;
+  for (int i = tid; i < n; i += nt) ss += static_cast<double>(Xc[i]) * Xc[i];
+  const float frob3 = static_cast<float>(sqrt(tiny_sum(ss, red)));
+  const float snap = sqrtf(static_cast<float>(rows < cols ? rows : cols)) / fmaxf(frob3, 1e-6f);
+  for (int i = tid; i < n; i += nt) Xc[i] *= snap;
+  __syncthreads();
+  // 6. NorMuon: second moment per line (rows when rows >= cols, else columns), normalised step
+  const bool reduce_cols = rows >= cols;
+  const int lines = reduce_cols ? rows : cols, line_len = reduce_cols ? cols : rows;
+  double tv = 0.0, ts = 0.0;
+  for (int l = tid; l < lines; l += nt) {
+    double acc = 0.0;
+    for (int q = 0; q < line_len; ++q) {
+      const float x = reduce_cols ? Xc[l * cols + q] : Xc[q * cols + l];
+      acc += static_cast<double>(x) * x;
+    }
+    const float v = static_cast<float>(acc / line_len);
+    const float b = buf2[l] + (1.0f - beta2) * (v - buf2[l]);
+    buf2[l] = b;
+    const float step = 1.0f / sqrtf(fmaxf(b, 1e-10f));
+    line[l] = step;
+    tv += v;
+    ts += static_cast<double>(v * static_cast<float>(line_len)) * step * step;
+  }
+  const float v_norm = sqrtf(static_cast<float>(tiny_sum(tv, red)) * static_cast<float>(line_len));
+  const float denom = fmaxf(static_cast<float>(sqrt(tiny_sum(ts, red))), 1e-10f);
+  const float kscale = v_norm / denom;
+  // 7. cautious decay and update
+  for (int i = tid; i < n; i += nt) {
+    const int r = i / cols, c = i - r * cols;
+    const float x = Xc[i] * (line[reduce_cols ? r : c] * kscale);
+    const float pm = master[i];
+    const float decay = (x * pm >= 0.0f) ? lr * wd * pm : 0.0f;
+    const float q = pm - lr * x - decay;
+    master[i] = q;
+    if (value != nullptr) value[i] = __float2bfloat16_rn(q);
+  }
+}
+
 __global__ void __launch_bounds__(256) relu2_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                                     long long n) {
   const long long nv = n / 8;
@@ -407,6 +558,21 @@ void relu2_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, cudaStrea
 void cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s) {
   if (n <= 0) return;
   cast_kernel<<<grid_for(n, 4), 256, 0, s>>>(x, y, n);
+}
+
+const char* muon_tiny(const long long* grad_ptrs, const long long* buf1_ptrs, const long long* buf2_ptrs,
+                      const long long* master_ptrs, const long long* value_ptrs, int P, int rows, int cols, float momentum,
+                      float beta2, float lr, float weight_decay, int ns_steps, const float* grad_scale,
+                      const double (*coeffs)[3], cudaStream_t s) {
+  if (P <= 0) return nullptr;
+  if (rows <= 0 || cols <= 0 || rows * cols > kTinyMax || (rows < cols ? rows : cols) > kTinySide)
+    return "muon_tiny: at most 1024 elements per matrix and 32 on the smaller side";
+  TinyCoeffs c;
+  for (int i = 0; i < 5; ++i)
+    for (int j = 0; j < 3; ++j) c.c[i][j] = static_cast<float>(coeffs[i][j]);
+  muon_tiny_kernel<<<P, 128, 0, s>>>(grad_ptrs, buf1_ptrs, buf2_ptrs, master_ptrs, value_ptrs, rows, cols, momentum, beta2,
+                                    lr, weight_decay, ns_steps, grad_scale, c);
+  return nullptr;
 }
 
 void muon_nesterov_batched(const long long* grad_ptrs, const long long* buf1_ptrs, float* x, float* row_sumsq, int P,

@@ -39,6 +39,13 @@ void muon_apply_batched(const long long* master_ptrs, const long long* value_ptr
                         const float* scale0, const float* line_scale, bool lines_are_rows, int P, int rows, int cols,
                         float lr, float weight_decay, cudaStream_t s);
 // relu(x)^2 elementwise (bf16)
+// Whole Muon step of P small matrices (rows * cols <= 1024, smaller side <= 32) given by pointer tables, one launch.
+// coeffs: the five (a, b, c) triples of the Polar Express iteration. Returns an error text for a shape it does not take.
+const char* muon_tiny(const long long* grad_ptrs, const long long* buf1_ptrs, const long long* buf2_ptrs,
+                      const long long* master_ptrs, const long long* value_ptrs, int P, int rows, int cols, float momentum,
+                      float beta2, float lr, float weight_decay, int ns_steps, const float* grad_scale,
+                      const double (*coeffs)[3], cudaStream_t s);
+
 void relu2_bf16(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, cudaStream_t s);
 // bf16 <- fp32 cast of a span
 void cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s);

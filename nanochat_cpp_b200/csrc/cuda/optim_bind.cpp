@@ -124,6 +124,33 @@ void register_optim(pybind11::module_& m) {
                        scale.data_ptr<float>(), line_scale.data_ptr<float>(), line_ss.size(0), line_ss.size(1), line_len,
                        target_norm, beta2, at::cuda::getCurrentCUDAStream());
   });
+  m.def("muon_tiny", [](const Tensor& grad_ptrs, const Tensor& buf1_ptrs, const Tensor& buf2_ptrs,
+                        const Tensor& master_ptrs, const c10::optional<Tensor>& value_ptrs, int64_t rows, int64_t cols,
+                        double momentum, double beta2, double lr, double wd, int64_t ns_steps,
+                        const c10::optional<Tensor>& grad_scale, const std::vector<std::vector<double>>& coeffs) {
+    const c10::cuda::CUDAGuard g(grad_ptrs.device());
+    const int64_t P = grad_ptrs.numel();
+    for (const Tensor* t : {&grad_ptrs, &buf1_ptrs, &buf2_ptrs, &master_ptrs})
+      TORCH_CHECK(t->scalar_type() == torch::kInt64 && t->is_contiguous() && t->numel() == P && t->is_cuda(),
+                  "muon_tiny: pointer tables are int64 device tensors of one length");
+    TORCH_CHECK(!value_ptrs.has_value() || (value_ptrs->scalar_type() == torch::kInt64 && value_ptrs->numel() == P),
+                "muon_tiny: value table");
+    TORCH_CHECK(coeffs.size() == 5, "muon_tiny: five coefficient triples");
+    double c[5][3];
+    for (int i = 0; i < 5; ++i) {
+      TORCH_CHECK(coeffs[i].size() == 3, "muon_tiny: five coefficient triples");
+      for (int j = 0; j < 3; ++j) c[i][j] = coeffs[i][j];
+    }
+    auto tab = [](const Tensor& t) { return reinterpret_cast<const long long*>(t.data_ptr<int64_t>()); };
+    const char* err = nc::muon_tiny(tab(grad_ptrs), tab(buf1_ptrs), tab(buf2_ptrs), tab(master_ptrs),
+                                    value_ptrs.has_value() ? tab(*value_ptrs) : nullptr, static_cast<int>(P),
+                                    static_cast<int>(rows), static_cast<int>(cols), static_cast<float>(momentum),
+                                    static_cast<float>(beta2), static_cast<float>(lr), static_cast<float>(wd),
+                                    static_cast<int>(ns_steps),
+                                    grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, c,
+                                    at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(err == nullptr, err);
+  });
   m.def("muon_nesterov", &muon_nesterov);
   m.def("muon_scale_rows", &muon_scale_rows);
   m.def("muon_apply", &muon_apply);

@@ -79,4 +79,18 @@ void nc_emu_muon_apply_batched(const long long* master_ptrs, const long long* va
   });
 }
 
+// The one-launch Muon step of P small matrices. coeffs: 15 floats, five (a, b, c) triples.
+void nc_emu_muon_tiny(const long long* grad_ptrs, const long long* buf1_ptrs, const long long* buf2_ptrs,
+                      const long long* master_ptrs, const long long* value_ptrs, int P, int rows, int cols,
+                      float momentum, float beta2, float lr, float weight_decay, int ns_steps, const float* grad_scale,
+                      const float* coeffs) {
+  nc::TinyCoeffs c;
+  for (int i = 0; i < 5; ++i)
+    for (int j = 0; j < 3; ++j) c.c[i][j] = coeffs[i * 3 + j];
+  emu::launch(emu::Dim{static_cast<unsigned>(P), 1, 1}, emu::Dim{128, 1, 1}, 0, [&] {
+    nc::muon_tiny_kernel(grad_ptrs, buf1_ptrs, buf2_ptrs, master_ptrs, value_ptrs, rows, cols, momentum, beta2, lr,
+                         weight_decay, ns_steps, grad_scale, c);
+  });
+}
+
 }  // extern "C"

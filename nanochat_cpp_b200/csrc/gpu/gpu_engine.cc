@@ -92,7 +92,8 @@ struct MuonGroupState {
   float lr = 0;
   std::vector<std::size_t> params;     // indices into the parameter table
   Buf buf1, buf2, x32, X, Y, A, B, row_ss, row_scale, all_scale, line_ss, scale, line_scale, tables;
-  bool on_host = false;                // too small for the batched kernels: updated on the host
+  bool on_host = false;                // a shape neither device path takes: updated on the host
+  bool tiny = false;                   // small matrices (the gate projections): one launch does the whole group's step
   std::vector<std::vector<float>> h_buf1, h_buf2;
 };
 struct AdamGroupState {
@@ -270,6 +271,10 @@ class GpuEngine final : public DeviceEngine {
         grp->rows = p.rows, grp->cols = p.cols;
         grp->lr = c.matrix_lr * f * std::sqrt(std::max(1.0f, static_cast<float>(p.rows) / static_cast<float>(p.cols)));
         grp->on_host = std::min(p.rows, p.cols) < 64 || p.rows % 8 != 0 || p.cols % 8 != 0;
+        if (grp->on_host && static_cast<long long>(p.rows) * p.cols <= 1024 && std::min(p.rows, p.cols) <= 32) {
+          grp->on_host = false;
+          grp->tiny = true;
+        }
       }
       grp->params.push_back(i);
     }
@@ -293,9 +298,11 @@ class GpuEngine final : public DeviceEngine {
       const std::size_t k = static_cast<std::size_t>(std::min(g.rows, g.cols));
       Check(cudaMemsetAsync(g.buf1.As<float>(P * n), 0, P * n * sizeof(float), stream_), "memset");
       Check(cudaMemsetAsync(g.buf2.As<float>(P * lines), 0, P * lines * sizeof(float), stream_), "memset");
-      g.x32.As<float>(P * n), g.X.As<bf16>(P * n), g.Y.As<bf16>(P * n), g.A.As<bf16>(P * k * k), g.B.As<bf16>(P * k * k);
-      g.row_ss.As<float>(P * g.rows), g.row_scale.As<float>(P * g.rows), g.all_scale.As<float>(P);
-      g.line_ss.As<float>(P * lines), g.scale.As<float>(P), g.line_scale.As<float>(P * lines);
+      if (!g.tiny) {
+        g.x32.As<float>(P * n), g.X.As<bf16>(P * n), g.Y.As<bf16>(P * n), g.A.As<bf16>(P * k * k), g.B.As<bf16>(P * k * k);
+        g.row_ss.As<float>(P * g.rows), g.row_scale.As<float>(P * g.rows), g.all_scale.As<float>(P);
+        g.line_ss.As<float>(P * lines), g.scale.As<float>(P), g.line_scale.As<float>(P * lines);
+      }
       // address tables: gradients, buf1 slices, buf2 slices, masters, values
       std::vector<long long> t(5 * P);
       for (std::size_t j = 0; j < P; ++j) {
@@ -349,6 +356,13 @@ class GpuEngine final : public DeviceEngine {
           have_host_clip = true;
         }
         MuonOnHost(&g, g.lr * lrm, momentum, wd, host_clip);
+      } else if (g.tiny) {
+        const int P = static_cast<int>(g.params.size());
+        const long long* t = g.tables.As<long long>(1);
+        const char* err = nc::muon_tiny(t, t + P, t + 2 * P, t + 3 * P, t + 4 * P, P, g.rows, g.cols, momentum,
+                                        ocfg_.muon_beta2, g.lr * lrm, wd, ocfg_.muon_ns_steps, clip, kPolar, stream_);
+        if (err != nullptr) throw std::runtime_error(err);
+        ++launches_;
       } else {
         MuonOnDevice(&g, g.lr * lrm, momentum, wd, clip);
       }

@@ -179,6 +179,28 @@ class Optimizer:
                                 ns_steps=cfg.muon_ns_steps, grad_scale=clip_scale,
                                 apply_fn=None if self.pusher is None else self.pusher.make_muon_apply(mine))
                 continue
+            if use_kernels and g.rows * g.cols <= 1024 and min(g.rows, g.cols) <= 32 and \
+                    all(st.g(s.name).is_contiguous() for s in mine):
+                # the small gate projections: the whole Muon step of the group in one launch (fp32, one CTA per matrix)
+                from ..ops import cuda as K
+                from ..ops.ref import POLAR_COEFFS
+                key = ("tiny", g.rows, g.cols)
+                tabs = self._muon_scratch.get(key)
+                ptrs = tuple(t.data_ptr() for s in mine for t in (st.g(s.name), self.state[s.name]["buf1"],
+                                                                   self.state[s.name]["buf2"], st.m(s.name),
+                                                                   st.v(s.name)))
+                if tabs is None or tabs[0] != ptrs:
+                    cols5 = [torch.tensor(ptrs[k::5], dtype=torch.int64, device=st.device) for k in range(5)]
+                    tabs = (ptrs, cols5)
+                    self._muon_scratch[key] = tabs
+                gt, b1t, b2t, mt, vt = tabs[1]
+                K._C.muon_tiny(gt, b1t, b2t, mt, vt, g.rows, g.cols, momentum, cfg.muon_beta2, g.lr * lrm, wd,
+                               cfg.muon_ns_steps, None if clip_scale is None else clip_scale.reshape(1),
+                               [list(c) for c in POLAR_COEFFS])
+                if self.pusher is not None:
+                    for s in mine:
+                        self.pusher.push_span(s.offset, s.count)
+                continue
             grads = torch.stack([st.g(s.name) for s in mine])
             master = torch.stack([st.m(s.name) for s in mine])
             buf1 = torch.stack([self.state[s.name]["buf1"] for s in mine])

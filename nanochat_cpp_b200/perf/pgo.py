@@ -51,13 +51,15 @@ from typing import Dict, List, Optional
 # kernel / operator name -> family, first match wins
 FAMILIES = (
     ("comm", r"grad_push|grad_reduce|reduce_pull|adamw_push|muon_apply_push|ncclDevKernel|nccl|all_?gather|reduce_?scatter"),
-    ("attention_bwd", r"attention_bwd|attn_delta|attention_delta"),
+    ("attention_bwd", r"attention_bwd|attention_dq|attn_delta|attention_delta"),
     ("attention_fwd", r"attention_fwd|attention_fwd2"),
     ("decode", r"paged_decode|decode_prep|kv_append|gemm_skinny|decode_"),
     ("classifier", r"classifier"),
     ("gemm", r"gemm_|linear_|cutlass|cublas|sgemm|gemv|fp8_mx|mxfp8"),
     ("optimizer", r"adamw|muon|newton|sumsq|grad_norm|clip|polar"),
-    ("rows", r"rmsnorm|norm_blend|blend|qk_prep|value_gate|smear|backout|embedding|relu|add_cols|rope|\badd\b"),
+    ("rows", r"rmsnorm|norm_blend|blend|qk_prep|value_gate|smear|backout|embedding|relu|add_cols|rope|flat_kernel|\badd\b"),
+    ("framework", r"at::native|vectorized_elementwise|elementwise_kernel|CatArray|copy_kernel|launch_clamp|where_kernel|"
+                  r"reduce_kernel|fill|index_"),
 )
 
 

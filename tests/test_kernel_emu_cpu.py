@@ -609,3 +609,31 @@ def test_the_three_schedules_differ(request):
     # the thread that completes a barrier goes on first: leaving order is not arrival order
     assert seen["ascending"][1][0] == 63 and seen["descending"][1][0] == 0
     lib.nc_emu_set_schedule(0, ctypes.c_ulonglong(1))
+
+
+@pytest.mark.parametrize("rows,cols,Pn", [(10, 12, 4), (1, 24, 1), (12, 10, 3), (32, 32, 2), (5, 5, 2)])
+def test_one_launch_muon_step_of_small_matrices(E, rows, cols, Pn):
+    """The gate projections are too small for the batched tensor-core path: their whole Muon step is one kernel, held
+    here to the definition (fp32 throughout, five Polar Express iterations)."""
+    g = torch.Generator().manual_seed(rows * 100 + cols)
+    grads = [torch.randn(rows, cols, generator=g) * 0.02 for _ in range(Pn)]
+    master = [torch.randn(rows, cols, generator=g) * 0.05 for _ in range(Pn)]
+    buf1 = [torch.randn(rows, cols, generator=g) * 0.01 for _ in range(Pn)]
+    lines = rows if rows >= cols else cols
+    buf2 = [torch.rand(lines, generator=g) * 1e-3 for _ in range(Pn)]
+    values = [torch.zeros(rows, cols, dtype=torch.bfloat16) for _ in range(Pn)]
+    kw = dict(lr=0.02, momentum=0.9, beta2=0.95, weight_decay=0.1)
+    rm, rb1, rb2 = torch.stack(master).clone(), torch.stack(buf1).clone(), torch.stack(buf2).clone()
+    ref.muon_update(torch.stack(grads), rm, None, rb1, rb2, ns_steps=5, grad_scale=0.5, **kw)
+    coeffs = torch.tensor(ref.POLAR_COEFFS, dtype=torch.float32).contiguous()
+    gs = torch.tensor([0.5])
+    before = torch.stack(master).clone()
+    E.nc_emu_muon_tiny(_ptrs(grads), _ptrs(buf1), _ptrs(buf2), _ptrs(master), _ptrs(values), Pn, rows, cols,
+                       ctypes.c_float(kw["momentum"]), ctypes.c_float(kw["beta2"]), ctypes.c_float(kw["lr"]),
+                       ctypes.c_float(kw["weight_decay"]), 5, P(gs), P(coeffs))
+    assert torch.allclose(torch.stack(buf1), rb1, rtol=1e-6, atol=1e-9)
+    assert torch.allclose(torch.stack(buf2), rb2, rtol=1e-3, atol=1e-9)
+    upd, want = torch.stack(master) - before, rm - before
+    assert float((upd - want).norm() / want.norm()) < 1e-3, float((upd - want).norm() / want.norm())
+    for p in range(Pn):
+        assert torch.equal(values[p], master[p].to(torch.bfloat16))
