@@ -1225,28 +1225,29 @@ __global__ void __launch_bounds__(kClsThreads) classifier_smem_kernel(
 }
 
 // ------------------------------------------------------------------ gradient norm
-// Sum of squares of an fp32 span in fp64. Each thread squares and adds 64 values in fp32 (four independent 16-byte
-// loads in flight, partial sums of at most 16 terms each) before it touches the fp64 accumulator: the conversion
-// and the double add are rare enough that the kernel runs at memory speed.
-__global__ void __launch_bounds__(256) sumsq_kernel(const float* __restrict__ g, long long n, double* out) {
+// Sum of squares of an fp32 span in fp64. Each thread keeps eight 16-byte loads in flight, squares and adds their 32
+// values in fp32 (four partial sums of eight terms) and only then touches the fp64 accumulator, so the conversion and
+// the double add are rare. Six blocks of 256 threads are resident per SM (the register bound asks for at most 42):
+// about 190 KB in flight per SM, which is what HBM latency needs; the grid is exactly the resident blocks.
+constexpr int kSumsqBlocksPerSm = 6;
+__global__ void __launch_bounds__(256, kSumsqBlocksPerSm) sumsq_kernel(const float* __restrict__ g, long long n,
+                                                                       double* out) {
   __shared__ double shd[8];
   double acc = 0.0;
   const long long nv = n / 4;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const float4* g4 = reinterpret_cast<const float4*>(g);
-  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nv; i0 += stride * 16) {
+  constexpr int U = 8;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nv; i0 += stride * U) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      v[u] = i < nv ? g4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      float4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const long long i = i0 + (r * 4 + u) * stride;
-        v[u] = i < nv ? g4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) part[u] += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
-    }
+    for (int u = 0; u < U; ++u) part[u & 3] += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
     acc += static_cast<double>(part[0] + part[1]) + static_cast<double>(part[2] + part[3]);
   }
   if (blockIdx.x == 0) {
@@ -1434,7 +1435,8 @@ void sumsq_f32(const float* g, long long n, double* out, cudaStream_t s) {
   if (n <= 0) return;
   long long b = (n / 4 + 255) / 256;
   if (b < 1) b = 1;
-  if (b > 148 * 8) b = 148 * 8;
+  // a grid of exactly the resident blocks, each striding over the span, has no partial last wave
+  if (b > 148 * kSumsqBlocksPerSm) b = 148 * kSumsqBlocksPerSm;
   sumsq_kernel<<<static_cast<int>(b), 256, 0, s>>>(g, n, out);
 }
 void finish_norm(const double* sumsq, float clip, float* norm_clip, cudaStream_t s) {
