@@ -4,7 +4,7 @@
     pgo init    --root DIR --name TARGET --measure-cmd "python bench.py --steps 8 --warmup 3" \\
                 [--trace-cmd "..."] [--runs 2] [--stage base] [--device b200]
     pgo measure --root DIR --name TARGET --before | --after
-    pgo trace   --root DIR --name TARGET            # runs the trace command, or: --launches FILE / --operators FILE
+    pgo trace   --root DIR --name TARGET            # runs the trace command, or: --launches FILE [--between KERNEL] / --operators FILE
     pgo analyze --root DIR --name TARGET
     pgo compare --root DIR --name TARGET [--idea ID] [--apply]
     pgo report  --root DIR --name TARGET
@@ -179,6 +179,24 @@ def read_launch_list(path) -> List[dict]:
     return out
 
 
+def cut_one_period(path, marker: str, out_path) -> int:
+    """Writes to `out_path` the part of an `ncu --csv` launch list between the last two launches whose kernel name
+    contains `marker` (exclusive of the first, inclusive of the second): one step of a loop that launches the marker
+    kernel once per iteration. Returns the number of launches kept."""
+    lines = Path(path).read_text(errors="replace").splitlines()
+    start = next((i for i, l in enumerate(lines) if l.startswith('"ID"')), None)
+    if start is None:
+        raise ValueError(f"{path}: no ncu CSV header")
+    body = lines[start + 1:]
+    names = [row.get("Kernel Name", "") for row in csv.DictReader(lines[start:])]
+    hits = [i for i, n in enumerate(names) if marker in n]
+    if len(hits) < 2:
+        raise ValueError(f"{path}: fewer than two launches of a kernel named like '{marker}'")
+    a, b = hits[-2], hits[-1]
+    Path(out_path).write_text("\n".join([lines[start]] + body[a + 1:b + 1]) + "\n")
+    return b - a
+
+
 def short_kernel_name(full: str) -> str:
     m = re.search(r"([A-Za-z_][A-Za-z0-9_]*)\s*(<[^()]*>)?\s*\(", full)
     return m.group(1) if m else full[:60]
@@ -197,10 +215,13 @@ def read_operator_table(path) -> Dict[str, dict]:
     return {"operators": ops, "step_ms": step_ms}
 
 
-def trace(t: Target, launches=None, operators=None, steps: int = 1, runner=None) -> dict:
+def trace(t: Target, launches=None, operators=None, steps: int = 1, runner=None, between: Optional[str] = None) -> dict:
     d = t.path(t.iter_dir(), "trace")
     d.mkdir(parents=True, exist_ok=True)
     spec = t.spec
+    if launches and between:
+        cut_one_period(launches, between, d / "launches.csv")
+        launches, steps = d / "launches.csv", 1
     if not launches and not operators:
         if not spec.get("trace_cmd"):
             raise SystemExit("the target has no trace command; pass --launches and / or --operators")
@@ -376,6 +397,8 @@ def main(argv=None) -> int:
     p.add_argument("--launches", default=None)
     p.add_argument("--operators", default=None)
     p.add_argument("--steps", type=int, default=1, help="training steps the launch list covers")
+    p.add_argument("--between", default=None, metavar="KERNEL",
+                   help="keep only the launches between the last two launches of this kernel (one step of the loop)")
     common(sub.add_parser("analyze"))
     p = common(sub.add_parser("compare"))
     p.add_argument("--idea", default=None)
@@ -392,7 +415,7 @@ def main(argv=None) -> int:
         print(f"{rec['which']}: {rec['median_ms']:.2f} ms/step over {len(rec['samples_ms'])} runs "
               f"(spread {100 * rec['spread_rel']:.1f} %)")
     elif a.verb == "trace":
-        print(json.dumps(trace(t, a.launches, a.operators, a.steps)))
+        print(json.dumps(trace(t, a.launches, a.operators, a.steps, between=a.between)))
     elif a.verb == "analyze":
         res = analyze(t)
         for s in res["signatures"][:8]:

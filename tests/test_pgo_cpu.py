@@ -91,6 +91,28 @@ def test_one_iteration_of_the_loop(tmp_path):
     assert (tmp_path / "d20-base" / "RESULT.md").read_text() == text
 
 
+def test_one_step_is_cut_out_of_a_longer_launch_list(tmp_path):
+    rows = ["==PROF== banner", HEADER]
+    seq = ["warm_kernel(int)"] * 3
+    for step in range(3):
+        seq += ["nc::finish_norm_kernel(double const*)", "nc::adamw_kernel(float*)", "void nc::gemm_pair_kernel<1>(int)",
+                "nc::sumsq_kernel(float const*)"]
+    for i, k in enumerate(seq):
+        rows.append(_row(i, k, 1000 * (i + 1)))
+    src = tmp_path / "long.csv"
+    src.write_text("\n".join(rows) + "\n")
+    assert pgo.cut_one_period(src, "finish_norm", tmp_path / "one.csv") == 4
+    kept = pgo.read_launch_list(tmp_path / "one.csv")
+    assert [pgo.short_kernel_name(r["kernel"]) for r in kept] == ["adamw_kernel", "gemm_pair_kernel", "sumsq_kernel",
+                                                                   "finish_norm_kernel"]
+    assert kept[0]["ns"] == 1000 * (3 + 4 + 1 + 1)          # the second step's first kernel after the marker
+    t = pgo.init(tmp_path, "cut", "cmd")
+    rec = pgo.trace(t, launches=src, between="finish_norm")
+    assert rec["steps_in_launch_list"] == 1 and len(pgo.read_launch_list(t.path("iter-01", "trace", "launches.csv"))) == 4
+    with pytest.raises(ValueError, match="fewer than two"):
+        pgo.cut_one_period(src, "no_such_kernel", tmp_path / "x.csv")
+
+
 def test_throttled_runs_and_missing_lines_are_rejected(tmp_path):
     t = pgo.init(tmp_path, "x", "cmd", runs=1)
     with pytest.raises(SystemExit, match="no JSON line"):
