@@ -207,7 +207,7 @@ def read_operator_table(path) -> Dict[str, dict]:
     ops, step_ms = {}, None
     for line in Path(path).read_text().splitlines():
         m = re.search(r"fwd\+bwd\s+([0-9.]+)\s*ms,\s*optimizer\s+([0-9.]+)\s*ms", line)
-        if m:
+        if m and step_ms is None:          # the first such line heads the table; later ones may quote older runs
             step_ms = float(m.group(1)) + float(m.group(2))
         m = re.match(r"^([A-Za-z_][\w+() ]*?)\s+([0-9.]+)\s+([0-9]+)\s*$", line)
         if m and not line.startswith("#"):

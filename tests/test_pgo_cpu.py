@@ -127,7 +127,10 @@ def test_throttled_runs_and_missing_lines_are_rejected(tmp_path):
 def test_operator_table_of_the_committed_step_profile(tmp_path):
     path = os.path.join(ROOT, "profiles", "step_profile_d20_batch32.txt")
     tab = pgo.read_operator_table(path)
-    assert abs(tab["step_ms"] - (235.66 + 22.33)) < 1e-6 and tab["operators"]["attention_bwd"]["calls"] == 20
+    head = next(l for l in open(path) if "fwd+bwd" in l and "optimizer" in l)
+    nums = [float(x) for x in __import__("re").findall(r"([0-9]+\.[0-9]+) ms", head)]
+    assert abs(tab["step_ms"] - (nums[0] + nums[1])) < 1e-6 and 200 < tab["step_ms"] < 300
+    assert tab["operators"]["attention_bwd"]["calls"] == 20
     t = pgo.init(tmp_path, "d20", "cmd")
     pgo.trace(t, operators=path)
     a = pgo.analyze(t)
