@@ -38,6 +38,20 @@ class SymmetricBuffer:
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
 
 
+def push_rows(placed, rank: int, world: int, bucket: int):
+    """The push table of one rank for one bucket: rows (first_vec, src_off, dst_pos, dst_rank, count) over the elements
+    other ranks own, and the number of 16-byte vectors in all. Destinations come in rotated order (rank + 1,
+    rank + 2, ...): the kernel walks the table front to back, so with every rank starting at rank 0 all senders would
+    store into the same receiver at the same time and share its one inbound link."""
+    rows, first = [], 0
+    for k in range(1, world):
+        r = (rank + k) % world
+        for off, cnt, pos in placed[r][bucket]:
+            rows.append([first, off, pos, r, cnt])
+            first += (cnt + 7) // 8
+    return rows, first
+
+
 def plan_reduce_scatter(specs, owners: Dict[str, int], world: int, L: int):
     """Layout of the bf16 reduce-scatter, a pure function of the parameter list (every rank computes the same).
 
@@ -160,13 +174,7 @@ class FusedTransport:
         self.recv_stride = cap
         self.recv = SymmetricBuffer(max(cap, 8) * self.world, torch.bfloat16, self.device, self.group)
         for b, bk in enumerate(self.buckets):
-            rows, first = [], 0
-            for r in range(self.world):
-                if r == self.rank:
-                    continue
-                for off, cnt, pos in placed[r][b]:
-                    rows.append([first, off, pos, r, cnt])
-                    first += (cnt + 7) // 8
+            rows, first = push_rows(placed, self.rank, self.world, b)
             if len(rows) > 128:
                 raise ValueError("a bucket pushes more than 128 segments (the kernel's segment table)")
             bk["push_rows"] = torch.tensor(rows if rows else [[0, 0, 0, 0, 0]], dtype=torch.int64,

@@ -307,7 +307,7 @@ def test_whole_model_reduce_scatter_plan_on_emulated_ranks(E, world):
     from nanochat_cpp_b200.config import Config
     from nanochat_cpp_b200.models.params import param_specs
     from nanochat_cpp_b200.parallel import dp
-    from nanochat_cpp_b200.parallel.fused import plan_reduce_scatter
+    from nanochat_cpp_b200.parallel.fused import plan_reduce_scatter, push_rows
     cfg = Config(num_layers=3, num_heads=2, num_kv_heads=1, hidden_dim=128, seq_len=64, vocab_size=200,
                  padded_vocab_size=256, window_pattern="SL")
     specs = param_specs(cfg)
@@ -324,14 +324,10 @@ def test_whole_model_reduce_scatter_plan_on_emulated_ranks(E, world):
     status = torch.zeros(1, dtype=torch.int32)
     for b in range(L + 2):
         for src in range(world):
-            rows, first = [], 0
-            for r in range(world):
-                if r == src:
-                    continue
-                for off, cnt, pos in placed[r][b]:
-                    rows.append([first, off, pos, r, cnt])
-                    first += (cnt + 7) // 8
+            rows, first = push_rows(placed, src, world, b)          # the table the transport itself builds
             assert len(rows) <= 128
+            if len(rows) > 1 and world > 2:                           # rotated: the first destination follows the sender
+                assert rows[0][3] == next(r for r in ((src + k) % world for k in range(1, world)) if placed[r][b])
             if rows:
                 segs = torch.tensor(rows, dtype=torch.int64)
                 E.nc_emu_grad_push(P(grads[src]), _ptrs(recv), world, ctypes.c_longlong(cap), src, P(segs), len(rows),
